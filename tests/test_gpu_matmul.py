@@ -1,0 +1,145 @@
+"""Quantized / fp16 matmul (decode GEMV and token-batched GEMM) against the CPU oracle.
+
+Tolerance of this floating-point path: max-abs 2e-2 and cosine >= 0.9995 (tests/util.py).
+The reference's own tests use |a-b| <= max(0.01, 0.01 * max(|a|,|b|)) on uniform(-5, 5) data
+(src/tensor/ops.rs:2914-3257); both criteria are checked on the reference's two shapes.
+"""
+import numpy as np
+import pytest
+
+from oracle import oracle
+from tests.util import assert_close, is_approx_eps
+
+pytestmark = pytest.mark.gpu
+
+KINDS = ["fp16", "int8", "nf4"]
+
+
+def _make_matrix(wrk, ctx, kind, w):
+    """w: (M, K) f16 → (wrk.Matrix, oracle tuple (kind, matrix, scale))."""
+    t = ctx.from_numpy(w)
+    if kind == "fp16":
+        return wrk.Matrix.fp16(t), (oracle.MAT_FP16, w, None)
+    if kind == "int8":
+        q, mm = oracle.quantize_mat_int8(w)
+        return wrk.Matrix.quant_u8(t), (oracle.MAT_INT8, q, mm)
+    q, am = oracle.quantize_mat_nf4(w)
+    return wrk.Matrix.quant_nf4(t), (oracle.MAT_NF4, q, am)
+
+
+def _run(wrk, ctx, kind, K, M, N, *, turbo, in_dt=np.float16, out_dt=np.float32, act=0, wscale=0.02, xscale=1.0,
+         seed=0, uniform=False):
+    rng = np.random.default_rng(seed)
+    if uniform:
+        w = (10.0 * (rng.random((M, K), dtype=np.float32) - 0.5)).astype(np.float16)
+        x = (10.0 * (rng.random((N, K), dtype=np.float32) - 0.5)).astype(in_dt)
+    else:
+        w = (rng.standard_normal((M, K), dtype=np.float32) * wscale).astype(np.float16)
+        x = (rng.standard_normal((N, K), dtype=np.float32) * xscale).astype(in_dt)
+    mat, (okind, om, oscale) = _make_matrix(wrk, ctx, kind, w)
+    t_x = ctx.from_numpy(x)
+    t_y = ctx.tensor(wrk.F16 if out_dt == np.float16 else wrk.F32, [M, N])
+    ctx.run(mat.matmul_op(t_x, t_y, act=act, turbo=turbo))
+    got = t_y.numpy().reshape(N, M)
+    want = np.zeros((N, M), dtype=out_dt)
+    oracle.matmul(okind, om, oscale, x, want, act=act, mode=1 if turbo else 0)
+    return got, want
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("c,r,t", [(2560, 2048, 64), (320, 64, 320)])
+def test_reference_test_shapes(wrk, ctx, kind, c, r, t):
+    # (C, R, T) of test_matmul_int8 / test_matmul_nf4, uniform(-5, 5) data, both vec and mat forms
+    if kind == "nf4" and c % 64:
+        pytest.skip("NF4 blocks of 64 need K % 64 == 0")
+    for turbo in (False, True):
+        got, want = _run(wrk, ctx, kind, c, r, t, turbo=turbo, uniform=True, seed=42)
+        assert is_approx_eps(got, want, 0.01).all(), f"{kind} turbo={turbo}"
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("n", [1, 2, 3, 7, 8, 9, 16, 17, 32, 33])
+def test_token_counts(wrk, ctx, kind, n):
+    got, want = _run(wrk, ctx, kind, 1024, 256, n, turbo=(n % 32 == 0), seed=n)
+    assert_close(got, want, f"{kind} n={n}")
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("k,m", [(2048, 2048), (2048, 7168), (7168, 2048), (4096, 4096), (128, 16), (256, 20),
+                                  (14336, 4096)])
+def test_decode_shapes(wrk, ctx, kind, k, m):
+    got, want = _run(wrk, ctx, kind, k, m, 1, turbo=False, seed=k + m)
+    assert_close(got, want, f"{kind} {k}x{m}")
+
+
+@pytest.mark.parametrize("kind", KINDS)
+def test_dtypes_and_activations(wrk, ctx, kind):
+    for in_dt, out_dt, act in [(np.float32, np.float32, 0), (np.float16, np.float16, 1), (np.float32, np.float16, 2),
+                               (np.float16, np.float32, 6)]:
+        got, want = _run(wrk, ctx, kind, 768, 512, 5, turbo=False, in_dt=in_dt, out_dt=out_dt, act=act, seed=act)
+        assert_close(got, want, f"{kind} {in_dt.__name__}->{out_dt.__name__} act={act}")
+
+
+@pytest.mark.parametrize("kind", KINDS)
+def test_views_with_offsets(wrk, ctx, kind):
+    # input is slice z = 3 of a [K, T, 5] buffer (the v6 att_sx layout); output slice z = 1 of [M, T, 2]
+    K, M, T = 512, 256, 4
+    rng = np.random.default_rng(5)
+    w = (rng.standard_normal((M, K), dtype=np.float32) * 0.02).astype(np.float16)
+    xs = rng.standard_normal((5, T, K), dtype=np.float32).astype(np.float16)
+    mat, (okind, om, oscale) = _make_matrix(wrk, ctx, kind, w)
+    t_x = ctx.from_numpy(xs)
+    t_y = ctx.tensor(wrk.F32, [M, T, 2], zeros=True)
+    ctx.run(mat.matmul_op(t_x.view(z=3), t_y.view(z=1), turbo=False))
+    got = t_y.numpy().reshape(2, T, M)
+    want = np.zeros((2, T, M), dtype=np.float32)
+    oracle.matmul(okind, om, oscale, oracle.View(xs, z=3), oracle.View(want, z=1))
+    assert_close(got[1], want[1], kind)
+    assert (got[0] == 0).all()
+
+
+def test_batched_fp16(wrk, ctx):
+    # the v6 token-shift adapter: matrix [32, C, 5] x input [32, T, 5] → [C, T, 5]
+    K, M, T, B = 32, 768, 3, 5
+    rng = np.random.default_rng(6)
+    w = (rng.standard_normal((B, M, K), dtype=np.float32) * 0.1).astype(np.float16)
+    x = rng.standard_normal((B, T, K), dtype=np.float32).astype(np.float16)
+    mat = wrk.Matrix.fp16(ctx.from_numpy(w))
+    t_x, t_y = ctx.from_numpy(x), ctx.tensor(wrk.F16, [M, T, B])
+    ctx.run(mat.matmul_op(t_x, t_y, turbo=False))
+    want = np.zeros((B, T, M), dtype=np.float16)
+    oracle.matmul(oracle.MAT_FP16, w, None, x, want)
+    assert_close(t_y.numpy().reshape(B, T, M), want, "batched fp16")
+
+
+def test_odd_k_falls_back(wrk, ctx):
+    # K not a multiple of the quantization block: the shape-agnostic kernel takes over
+    got, want = _run(wrk, ctx, "int8", 320, 64, 3, turbo=False, seed=1)
+    assert_close(got, want, "int8 K=320")
+
+
+def test_full_size_linearity(wrk, ctx):
+    # size-independent property at a 7B shape: W(a x1 + b x2) = a W x1 + b W x2 (within fp16 rounding of x)
+    K, M = 4096, 14336
+    rng = np.random.default_rng(77)
+    w = (rng.standard_normal((M, K), dtype=np.float32) * 0.02).astype(np.float16)
+    mat = wrk.Matrix.quant_u8(ctx.from_numpy(w))
+    x1 = rng.standard_normal(K, dtype=np.float32).astype(np.float16)
+    x2 = rng.standard_normal(K, dtype=np.float32).astype(np.float16)
+    xs = np.stack([x1, x2, (x1.astype(np.float32) * 0.5 + x2.astype(np.float32) * 0.25).astype(np.float16)])
+    t_y = ctx.tensor(wrk.F32, [M, 3])
+    ctx.run(mat.matmul_op(ctx.from_numpy(xs), t_y, turbo=False))
+    y = t_y.numpy().reshape(3, M)
+    assert_close(y[2], 0.5 * y[0] + 0.25 * y[1], "linearity", max_abs=1e-2)
+
+
+def test_shape_and_type_errors(wrk, ctx):
+    w = ctx.from_numpy(np.zeros((64, 128), dtype=np.float16))
+    mat = wrk.Matrix.quant_u8(w)
+    x = ctx.tensor(wrk.F16, [128, 2])
+    with pytest.raises(wrk.WrkError) as e:
+        mat.matmul_op(x, ctx.tensor(wrk.F32, [63, 2]))
+    assert e.value.status == -5
+    with pytest.raises(wrk.WrkError) as e:
+        mat.matmul_op(ctx.tensor(wrk.U8, [128, 2]), ctx.tensor(wrk.F32, [64, 2]))
+    assert e.value.status == -2

@@ -1,0 +1,172 @@
+"""Supporting ops of the v5/v6/v7 jobs against the CPU oracle (layer/group norm, l2 norm, token
+shift, channel mix, add/mul with activations, activate, blit, transpose, lerp, affine, control_k)."""
+import numpy as np
+import pytest
+
+from oracle import oracle
+from tests.util import assert_close
+
+pytestmark = pytest.mark.gpu
+
+DT = {np.float16: 1, np.float32: 0}
+
+
+def _wdt(wrk, dt):
+    return wrk.F16 if dt == np.float16 else wrk.F32
+
+
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+@pytest.mark.parametrize("C,T", [(768, 5), (2048, 1), (64, 3)])
+def test_layer_norm(wrk, ctx, dtype, C, T):
+    rng = np.random.default_rng(C + T)
+    x = (rng.standard_normal((T, C)) * 3 + 1).astype(dtype)
+    w = (1 + rng.standard_normal(C) * 0.02).astype(np.float16)
+    b = (rng.standard_normal(C) * 0.02).astype(np.float16)
+    t_x = ctx.from_numpy(x)
+    ctx.run(wrk.layer_norm(ctx.from_numpy(w), ctx.from_numpy(b), t_x, 1e-5))
+    ref = x.copy()
+    oracle.layer_norm(w, b, ref, 1e-5)
+    assert_close(t_x.numpy().reshape(T, C), ref, "layer_norm")
+
+
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+def test_group_norm(wrk, ctx, dtype):
+    rng = np.random.default_rng(1)
+    S, H, T = 64, 12, 7
+    x = (rng.standard_normal((T, H, S)) * 2).astype(dtype)
+    w = (1 + rng.standard_normal((H, S)) * 0.1).astype(np.float16)
+    b = (rng.standard_normal((H, S)) * 0.1).astype(np.float16)
+    t_x = ctx.from_numpy(x)
+    ctx.run(wrk.group_norm(ctx.from_numpy(w), ctx.from_numpy(b), t_x, 64e-5))
+    ref = x.copy()
+    oracle.group_norm(w, b, ref, 64e-5, H)
+    assert_close(t_x.numpy().reshape(T, H, S), ref, "group_norm")
+
+
+def test_l2_norm(wrk, ctx):
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((5, 8, 64)).astype(np.float16)
+    t_x = ctx.from_numpy(x)
+    ctx.run(wrk.l2_norm(t_x, 1e-12))
+    ref = x.copy()
+    oracle.l2_norm(ref, 1e-12)
+    assert_close(t_x.numpy().reshape(x.shape), ref, "l2_norm")
+
+
+@pytest.mark.parametrize("reversed_", [True, False])
+@pytest.mark.parametrize("per_token", [True, False])
+def test_token_shift(wrk, ctx, reversed_, per_token):
+    rng = np.random.default_rng(3)
+    C, B, count = 256, 3, 5 if per_token else 1
+    cursors = oracle.pack_cursors([(0, 0, 4), (2, 4, 1), (1, 5, 6)])
+    T = 11
+    state = rng.standard_normal((B, 66, C)).astype(np.float32)
+    x = rng.standard_normal((T, C)).astype(np.float16)
+    tm = rng.uniform(0, 1, (count, T if per_token else 1, C)).astype(np.float16)
+    out = np.zeros((count, T, C), dtype=np.float16)
+    t_state, t_out = ctx.from_numpy(state), ctx.tensor(wrk.F16, [C, T, count])
+    ctx.run(wrk.token_shift(ctx.from_numpy(cursors), ctx.from_numpy(tm), t_state.view(y=(0, 65)), ctx.from_numpy(x),
+                            t_out, reversed_))
+    oracle.token_shift(cursors, tm, oracle.View(state, y=(0, 65)), x, out, reversed_)
+    assert_close(t_out.numpy().reshape(out.shape), out, "token_shift")
+
+
+@pytest.mark.parametrize("v7", [False, True])
+def test_channel_mix(wrk, ctx, v7):
+    rng = np.random.default_rng(4)
+    C, B, T = 256, 3, 11
+    cursors = oracle.pack_cursors([(0, 0, 4), (2, 4, 1), (1, 5, 6)])
+    state = rng.standard_normal((B, 66, C)).astype(np.float32)
+    r = rng.standard_normal((T, C)).astype(np.float16)
+    v = rng.standard_normal((T, C)).astype(np.float16)
+    x = rng.standard_normal((T, C)).astype(np.float16)
+    t_state, t_x = ctx.from_numpy(state), ctx.from_numpy(x)
+    if v7:
+        op = wrk.channel_mix_v7(ctx.from_numpy(cursors), t_state.view(y=65), ctx.from_numpy(v), t_x)
+    else:
+        op = wrk.channel_mix(ctx.from_numpy(cursors), t_state.view(y=65), ctx.from_numpy(r), ctx.from_numpy(v), t_x)
+    ctx.run(op)
+    ref_x, ref_state = x.copy(), state.copy()
+    oracle.channel_mix(cursors, oracle.View(ref_state, y=65), None if v7 else r, v, ref_x, v7=v7)
+    assert_close(t_x.numpy().reshape(T, C), ref_x, "x")
+    assert np.array_equal(t_state.numpy().reshape(state.shape), ref_state)
+
+
+def test_binary_broadcast_and_activations(wrk, ctx):
+    rng = np.random.default_rng(5)
+    C, T, B = 128, 6, 5
+    out0 = rng.standard_normal((B, T, C)).astype(np.float16)
+    for shape in [(B, T, C), (B, 1, C), (1, 1, C)]:
+        for is_mul, acts in [(False, (0, 0, 6)), (True, (7, 0, 0)), (False, (0, 0, 0)), (True, (0, 1, 2))]:
+            inp = rng.standard_normal(shape).astype(np.float32)
+            t_out = ctx.from_numpy(out0)
+            fn = wrk.mul_activate if is_mul else wrk.add_activate
+            ctx.run(fn(ctx.from_numpy(inp), t_out, *acts))
+            ref = out0.copy()
+            oracle.binary(is_mul, inp, ref, *acts)
+            assert_close(t_out.numpy().reshape(ref.shape), ref, f"binary {shape} {is_mul} {acts}")
+
+
+@pytest.mark.parametrize("act", range(8))
+def test_activate(wrk, ctx, act):
+    rng = np.random.default_rng(act)
+    x = rng.standard_normal((3, 4, 64)).astype(np.float32)
+    t_x = ctx.from_numpy(x)
+    ctx.run(wrk.activate(t_x, act))
+    ref = x.copy()
+    oracle.activate(ref, act)
+    assert_close(t_x.numpy().reshape(x.shape), ref, f"act {act}", max_abs=1e-4)
+
+
+def test_blit_views_and_transpose(wrk, ctx):
+    rng = np.random.default_rng(6)
+    src = rng.standard_normal((4, 7, 64)).astype(np.float16)
+    t_dst = ctx.tensor(wrk.F32, [64, 3, 9], zeros=True)
+    ctx.run(wrk.blit(ctx.from_numpy(src).view(y=(2, 5), z=1), t_dst.view(z=4)))
+    ref = np.zeros((9, 3, 64), dtype=np.float32)
+    oracle.blit(oracle.View(src, y=(2, 5), z=1), oracle.View(ref, z=4))
+    assert np.array_equal(t_dst.numpy().reshape(ref.shape), ref)
+    t_tr = ctx.tensor(wrk.F16, [64, 4, 7])
+    ctx.run(wrk.transpose(ctx.from_numpy(src), t_tr))
+    assert np.array_equal(t_tr.numpy().reshape(7, 4, 64), src.transpose(1, 0, 2))
+    with pytest.raises(wrk.WrkError) as e:
+        wrk.blit(ctx.from_numpy(src), t_dst)
+    assert e.value.status == -5
+
+
+@pytest.mark.parametrize("reversed_", [True, False])
+def test_lerp_affine_control_k(wrk, ctx, reversed_):
+    rng = np.random.default_rng(7)
+    T, C = 5, 128
+    a = rng.standard_normal((T, C)).astype(np.float16)
+    b = rng.standard_normal((T, C)).astype(np.float16)
+    f = rng.uniform(0, 1, (T, C)).astype(np.float16)
+    t_b = ctx.from_numpy(b)
+    ctx.run(wrk.lerp(ctx.from_numpy(a), t_b, ctx.from_numpy(f), reversed_))
+    ref = b.copy()
+    oracle.lerp(a, ref, f, reversed_)
+    assert_close(t_b.numpy().reshape(T, C), ref, "lerp")
+    ctx.run(wrk.affine(t_b, 0.5, 0.0))
+    oracle.affine(ref, 0.5, 0.0)
+    assert_close(t_b.numpy().reshape(T, C), ref, "affine")
+    p = rng.uniform(0, 1, C).astype(np.float16)
+    ctx.run(wrk.control_k_v7(ctx.from_numpy(p), ctx.from_numpy(f), t_b))
+    oracle.control_k_v7(p, f, ref)
+    assert_close(t_b.numpy().reshape(T, C), ref, "control_k")
+
+
+def test_op_list_encode_and_graph(wrk, ctx):
+    # deferred ops: nothing runs at build time; a list runs in order; a graph replays the same work
+    x = np.ones((2, 64), dtype=np.float32)
+    t_x = ctx.from_numpy(x)
+    ops = wrk.op_list([wrk.affine(t_x, 2.0, 1.0), wrk.affine(t_x, 3.0, 0.0)])
+    assert ops.num_atoms() == 2
+    assert np.array_equal(t_x.numpy().reshape(x.shape), x)
+    cmd = ctx.encode(ops, use_graph=True)
+    before = ctx.launch_count()
+    cmd.submit()
+    assert np.array_equal(t_x.numpy().reshape(x.shape), (x * 2 + 1) * 3)
+    cmd.submit()
+    assert np.array_equal(t_x.numpy().reshape(x.shape), (((x * 2 + 1) * 3) * 2 + 1) * 3)
+    assert ctx.launch_count() - before == 4
+    assert ctx.device_status() == 0

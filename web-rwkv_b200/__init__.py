@@ -1,0 +1,432 @@
+"""ctypes harness over libwrk.so, the sm_100a library behind include/wrk.h.
+
+This package is the Python-side mirror of the reference crate's operator interface
+(`TensorOp`, `Matrix`, tensors and views; src/tensor/ops.rs, src/tensor/matrix.rs) used by the
+tests and the benchmark.  It contains no compute of its own and no fallback: every call goes
+through the C ABI, and importing `lib()` fails loudly when the CUDA library has not been built.
+
+Shapes follow the reference: ``[x, y, z, w]`` with ``x`` fastest.  A numpy array of shape
+``(w, z, y, x)`` (trailing axis fastest) maps to the tensor shape ``[x, y, z, w]``.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libwrk.so")
+
+F32, F16, U8, U16, U32 = 0, 1, 2, 3, 4
+ACT_NONE, ACT_SQUARED_RELU, ACT_TANH, ACT_STABLE_EXP, ACT_OPPOSITE_EXP, ACT_SOFTPLUS, ACT_SIGMOID, ACT_SILU = range(8)
+QUANT_NONE, QUANT_INT8, QUANT_NF4, QUANT_SF4 = range(4)
+RNN_LAST, RNN_FULL, RNN_NONE = range(3)
+DIM_AUTO = 0xFFFFFFFF
+
+_NP = {F32: np.float32, F16: np.float16, U8: np.uint8, U16: np.uint16, U32: np.uint32}
+_DT = {np.dtype(v): k for k, v in _NP.items()}
+
+
+class WrkError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__(f"wrk status {status}: {message}")
+        self.status = status
+        self.message = message
+
+
+class CView(ctypes.Structure):
+    _fields_ = [("tensor", ctypes.c_void_p), ("shape", ctypes.c_uint32 * 4), ("stride", ctypes.c_uint32 * 4),
+                ("offset", ctypes.c_uint32 * 4)]
+
+
+_lib = None
+
+
+def lib():
+    """The loaded C library.  Raises if libwrk.so is missing: there is no CPU fallback."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} not found: build it with `python web-rwkv_b200/build.py` "
+                              "(there is no CPU fallback for the CUDA path)")
+        _lib = ctypes.CDLL(LIB_PATH)
+        _lib.wrk_last_error_message.restype = ctypes.c_char_p
+        _lib.wrk_build_arch.restype = ctypes.c_char_p
+    return _lib
+
+
+def check(status):
+    if status != 0:
+        raise WrkError(status, lib().wrk_last_error_message().decode())
+
+
+def _shape4(shape):
+    s = list(shape) + [1] * (4 - len(shape))
+    return (ctypes.c_uint32 * 4)(*s)
+
+
+def np_to_shape(arr):
+    """numpy (…, y, x) → reference [x, y, z, w]."""
+    s = list(arr.shape)[::-1]
+    assert len(s) <= 4
+    return s + [1] * (4 - len(s))
+
+
+class Context:
+    def __init__(self, device=0):
+        self.handle = ctypes.c_void_p()
+        check(lib().wrk_context_create(device, ctypes.byref(self.handle)))
+
+    def close(self):
+        if self.handle:
+            lib().wrk_context_destroy(self.handle)
+            self.handle = ctypes.c_void_p()
+
+    def synchronize(self):
+        check(lib().wrk_context_synchronize(self.handle))
+
+    def device_status(self):
+        s = ctypes.c_int32()
+        check(lib().wrk_context_device_status(self.handle, ctypes.byref(s)))
+        return s.value
+
+    def launch_count(self):
+        n = ctypes.c_uint64()
+        check(lib().wrk_context_launch_count(self.handle, ctypes.byref(n)))
+        return n.value
+
+    def timer_start(self):
+        check(lib().wrk_timer_start(self.handle))
+
+    def timer_stop(self):
+        ms = ctypes.c_float()
+        check(lib().wrk_timer_stop(self.handle, ctypes.byref(ms)))
+        return ms.value
+
+    # tensors
+    def tensor(self, dtype, shape, zeros=False):
+        h = ctypes.c_void_p()
+        fn = lib().wrk_tensor_zeros if zeros else lib().wrk_tensor_create
+        check(fn(self.handle, dtype, _shape4(shape), ctypes.byref(h)))
+        return Tensor(self, h)
+
+    def from_numpy(self, arr, shape=None):
+        arr = np.ascontiguousarray(arr)
+        dtype = _DT[arr.dtype]
+        shape = np_to_shape(arr) if shape is None else list(shape)
+        h = ctypes.c_void_p()
+        check(lib().wrk_tensor_from_data(self.handle, dtype, _shape4(shape), arr.ctypes.data_as(ctypes.c_void_p),
+                                         ctypes.c_size_t(arr.nbytes), ctypes.byref(h)))
+        return Tensor(self, h)
+
+    def run(self, op):
+        check(lib().wrk_run(self.handle, op.handle))
+
+    def encode(self, op, use_graph=False):
+        h = ctypes.c_void_p()
+        check(lib().wrk_encode(self.handle, op.handle, int(use_graph), ctypes.byref(h)))
+        return Commands(self, h)
+
+
+class Commands:
+    def __init__(self, ctx, handle):
+        self.ctx, self.handle = ctx, handle
+
+    def submit(self):
+        check(lib().wrk_submit(self.ctx.handle, self.handle))
+
+    def __del__(self):
+        if self.handle and _lib is not None:
+            _lib.wrk_commands_release(self.handle)
+            self.handle = None
+
+
+class Tensor:
+    def __init__(self, ctx, handle):
+        self.ctx, self.handle = ctx, handle
+
+    def __del__(self):
+        if getattr(self, "handle", None) and _lib is not None:
+            _lib.wrk_tensor_release(self.handle)
+            self.handle = None
+
+    @property
+    def shape(self):
+        s = (ctypes.c_uint32 * 4)()
+        check(lib().wrk_tensor_shape(self.handle, s))
+        return list(s)
+
+    @property
+    def dtype(self):
+        d = ctypes.c_int32()
+        check(lib().wrk_tensor_dtype(self.handle, ctypes.byref(d)))
+        return d.value
+
+    def numpy(self):
+        """Read back as a numpy array of shape (w, z, y, x)."""
+        shape = self.shape
+        arr = np.empty(shape[::-1], dtype=_NP[self.dtype])
+        check(lib().wrk_tensor_back(self.handle, arr.ctypes.data_as(ctypes.c_void_p), ctypes.c_size_t(arr.nbytes)))
+        return arr
+
+    def load(self, arr):
+        arr = np.ascontiguousarray(arr, dtype=_NP[self.dtype])
+        check(lib().wrk_tensor_load(self.handle, arr.ctypes.data_as(ctypes.c_void_p), ctypes.c_size_t(arr.nbytes)))
+
+    def reshape(self, x, y=1, z=1, w=1):
+        h = ctypes.c_void_p()
+        check(lib().wrk_tensor_reshape(self.handle, _shape4([x, y, z, w]), ctypes.byref(h)))
+        return Tensor(self.ctx, h)
+
+    def view(self, x=None, y=None, z=None, w=None):
+        """Half-open ranges per axis (None = whole axis, int = single index)."""
+        shape = self.shape
+        start, end = [], []
+        for dim, r in zip(shape, (x, y, z, w)):
+            if r is None:
+                start.append(0), end.append(dim)
+            elif isinstance(r, int):
+                start.append(r), end.append(r + 1)
+            else:
+                start.append(r[0]), end.append(r[1])
+        v = CView()
+        check(lib().wrk_tensor_view(self.handle, _shape4(start), _shape4(end), ctypes.byref(v)))
+        return View(self, v)
+
+    def as_view(self):
+        v = CView()
+        check(lib().wrk_tensor_as_view(self.handle, ctypes.byref(v)))
+        return View(self, v)
+
+
+class View:
+    def __init__(self, tensor, cview):
+        self.tensor, self.c = tensor, cview  # keeps the tensor alive
+
+
+def _v(x):
+    """Tensor or View → pointer to a wrk_view."""
+    if isinstance(x, Tensor):
+        x = x.as_view()
+    return ctypes.byref(x.c), x
+
+
+class Op:
+    def __init__(self, handle, keep=()):
+        self.handle, self.keep = handle, keep
+
+    def __del__(self):
+        if self.handle and _lib is not None:
+            _lib.wrk_op_release(self.handle)
+            self.handle = None
+
+    def num_atoms(self):
+        n = ctypes.c_uint64()
+        check(lib().wrk_op_num_atoms(self.handle, ctypes.byref(n)))
+        return n.value
+
+
+def _mk(fn_name, *args, keep=()):
+    h = ctypes.c_void_p()
+    check(getattr(lib(), fn_name)(*args, ctypes.byref(h)))
+    return Op(h, keep)
+
+
+def _t(x):
+    return x.handle if x is not None else None
+
+
+def op_list(ops):
+    arr = (ctypes.c_void_p * len(ops))(*[o.handle for o in ops])
+    return _mk("wrk_op_list", arr, ctypes.c_size_t(len(ops)), keep=tuple(ops))
+
+
+def quantize_mat_int8(input, minmax, output):
+    return _mk("wrk_op_quantize_mat_int8", _t(input), _t(minmax), _t(output), keep=(input, minmax, output))
+
+
+def quantize_mat_nf4(input, quant, absmax, output):
+    return _mk("wrk_op_quantize_mat_nf4", _t(input), _t(quant), _t(absmax), _t(output),
+               keep=(input, quant, absmax, output))
+
+
+def matmul_vec_fp16(matrix, input, output, act=ACT_NONE, sparse=False):
+    (pi, ki), (po, ko) = _v(input), _v(output)
+    return _mk("wrk_op_matmul_vec_fp16", _t(matrix), pi, po, act, int(sparse), keep=(matrix, ki, ko))
+
+
+def matmul_vec_int8(matrix, minmax, input, output, act=ACT_NONE, sparse=False):
+    (pi, ki), (po, ko) = _v(input), _v(output)
+    return _mk("wrk_op_matmul_vec_int8", _t(matrix), _t(minmax), pi, po, act, int(sparse),
+               keep=(matrix, minmax, ki, ko))
+
+
+def matmul_vec_nf4(matrix, quant, absmax, input, output, act=ACT_NONE, sparse=False):
+    (pi, ki), (po, ko) = _v(input), _v(output)
+    return _mk("wrk_op_matmul_vec_nf4", _t(matrix), _t(quant), _t(absmax), pi, po, act, int(sparse),
+               keep=(matrix, quant, absmax, ki, ko))
+
+
+def matmul_mat_fp16(matrix, input, output, act=ACT_NONE):
+    (pm, km), (pi, ki), (po, ko) = _v(matrix), _v(input), _v(output)
+    return _mk("wrk_op_matmul_mat_fp16", pm, pi, po, act, keep=(km, ki, ko))
+
+
+def matmul_mat_int8(matrix, minmax, input, output, act=ACT_NONE):
+    (pm, km), (pi, ki), (po, ko) = _v(matrix), _v(input), _v(output)
+    return _mk("wrk_op_matmul_mat_int8", pm, _t(minmax), pi, po, act, keep=(km, minmax, ki, ko))
+
+
+def matmul_mat_nf4(matrix, quant, absmax, input, output, act=ACT_NONE):
+    (pm, km), (pi, ki), (po, ko) = _v(matrix), _v(input), _v(output)
+    return _mk("wrk_op_matmul_mat_nf4", pm, _t(quant), _t(absmax), pi, po, act, keep=(km, quant, absmax, ki, ko))
+
+
+def time_mix_v5(cursors, time_decay, time_first, state, k, v, r, x):
+    ps, ks = _v(state)
+    return _mk("wrk_op_time_mix_v5", _t(cursors), _t(time_decay), _t(time_first), ps, _t(k), _t(v), _t(r), _t(x),
+               keep=(cursors, time_decay, time_first, ks, k, v, r, x))
+
+
+def time_mix_v6(cursors, time_decay, time_first, state, k, v, r, x):
+    ps, ks = _v(state)
+    return _mk("wrk_op_time_mix_v6", _t(cursors), _t(time_decay), _t(time_first), ps, _t(k), _t(v), _t(r), _t(x),
+               keep=(cursors, time_decay, time_first, ks, k, v, r, x))
+
+
+def time_mix_v7(cursors, state, r, w, n, x):
+    ps, ks = _v(state)
+    return _mk("wrk_op_time_mix_v7", _t(cursors), ps, _t(r), _t(w), _t(n), _t(x), keep=(cursors, ks, r, w, n, x))
+
+
+def time_first_v7(u, r, n, x):
+    return _mk("wrk_op_time_first_v7", _t(u), _t(r), _t(n), _t(x), keep=(u, r, n, x))
+
+
+def layer_norm(w, b, x, eps):
+    return _mk("wrk_op_layer_norm", _t(w), _t(b), _t(x), ctypes.c_float(eps), keep=(w, b, x))
+
+
+def group_norm(w, b, x, eps):
+    return _mk("wrk_op_group_norm", _t(w), _t(b), _t(x), ctypes.c_float(eps), keep=(w, b, x))
+
+
+def l2_norm(x, eps):
+    return _mk("wrk_op_l2_norm", _t(x), ctypes.c_float(eps), keep=(x,))
+
+
+def token_shift(cursors, time_mix, state, input, output, reversed):
+    (pt, kt), (ps, ks) = _v(time_mix), _v(state)
+    return _mk("wrk_op_token_shift", _t(cursors), pt, ps, _t(input), _t(output), int(reversed),
+               keep=(cursors, kt, ks, input, output))
+
+
+def channel_mix(cursors, state, r, v, x):
+    ps, ks = _v(state)
+    return _mk("wrk_op_channel_mix", _t(cursors), ps, _t(r), _t(v), _t(x), keep=(cursors, ks, r, v, x))
+
+
+def channel_mix_v7(cursors, state, v, x):
+    ps, ks = _v(state)
+    return _mk("wrk_op_channel_mix_v7", _t(cursors), ps, _t(v), _t(x), keep=(cursors, ks, v, x))
+
+
+def add_activate(input, output, act_x=ACT_NONE, act_y=ACT_NONE, act_out=ACT_NONE):
+    (pi, ki), (po, ko) = _v(input), _v(output)
+    return _mk("wrk_op_add_activate", pi, po, act_x, act_y, act_out, keep=(ki, ko))
+
+
+def add(input, output):
+    return add_activate(input, output)
+
+
+def mul_activate(input, output, act_x=ACT_NONE, act_y=ACT_NONE, act_out=ACT_NONE):
+    (pi, ki), (po, ko) = _v(input), _v(output)
+    return _mk("wrk_op_mul_activate", pi, po, act_x, act_y, act_out, keep=(ki, ko))
+
+
+def mul(input, output):
+    return mul_activate(input, output)
+
+
+def activate(x, act):
+    px, kx = _v(x)
+    return _mk("wrk_op_activate", px, act, keep=(kx,))
+
+
+def blit(input, output):
+    (pi, ki), (po, ko) = _v(input), _v(output)
+    return _mk("wrk_op_blit", pi, po, keep=(ki, ko))
+
+
+def transpose(input, output):
+    (pi, ki), (po, ko) = _v(input), _v(output)
+    return _mk("wrk_op_transpose", pi, po, keep=(ki, ko))
+
+
+def lerp(input, output, factor, reversed):
+    (pi, ki), (po, ko), (pf, kf) = _v(input), _v(output), _v(factor)
+    return _mk("wrk_op_lerp", pi, po, pf, int(reversed), keep=(ki, ko, kf))
+
+
+def affine(x, scale, bias):
+    return _mk("wrk_op_affine", _t(x), ctypes.c_float(scale), ctypes.c_float(bias), keep=(x,))
+
+
+def control_k_v7(p, a, k):
+    (pa, ka), (pk, kk) = _v(a), _v(k)
+    return _mk("wrk_op_control_k_v7", _t(p), pa, pk, keep=(p, ka, kk))
+
+
+def nf4_table():
+    t = (ctypes.c_float * 16)()
+    check(lib().wrk_nf4_table(t))
+    return np.array(list(t), dtype=np.float32)
+
+
+class Matrix:
+    """`Matrix` of src/tensor/matrix.rs: Fp16 / Int8 {w, m} / Fp4 {q, w, m}."""
+
+    def __init__(self, ctx, handle):
+        self.ctx, self.handle = ctx, handle
+
+    def __del__(self):
+        if self.handle and _lib is not None:
+            _lib.wrk_matrix_release(self.handle)
+            self.handle = None
+
+    @staticmethod
+    def fp16(tensor):
+        h = ctypes.c_void_p()
+        check(lib().wrk_matrix_fp16(tensor.handle, ctypes.byref(h)))
+        return Matrix(tensor.ctx, h)
+
+    @staticmethod
+    def quant_u8(tensor):
+        h = ctypes.c_void_p()
+        check(lib().wrk_matrix_quant_u8(tensor.handle, ctypes.byref(h)))
+        return Matrix(tensor.ctx, h)
+
+    @staticmethod
+    def quant_nf4(tensor):
+        h = ctypes.c_void_p()
+        check(lib().wrk_matrix_quant_nf4(tensor.handle, ctypes.byref(h)))
+        return Matrix(tensor.ctx, h)
+
+    def parts(self):
+        kind = ctypes.c_int32()
+        w, m, q = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_void_p()
+        check(lib().wrk_matrix_parts(self.handle, ctypes.byref(kind), ctypes.byref(w), ctypes.byref(m),
+                                     ctypes.byref(q)))
+        out = []
+        for h in (w, m, q):
+            if h:
+                check(lib().wrk_tensor_retain(h))
+                out.append(Tensor(self.ctx, ctypes.c_void_p(h.value)))
+            else:
+                out.append(None)
+        return kind.value, out[0], out[1], out[2]
+
+    def matmul_op(self, input, output, act=ACT_NONE, turbo=False, sparse=False):
+        (pi, ki), (po, ko) = _v(input), _v(output)
+        fn = "wrk_matrix_matmul_op_sparse" if sparse else "wrk_matrix_matmul_op"
+        return _mk(fn, self.handle, pi, po, act, int(turbo), keep=(self, ki, ko))

@@ -1,0 +1,71 @@
+// Launchers of the sm_100a kernels.  Host code calls only these; each returns the launch status.
+#pragma once
+
+#include "../common.h"
+
+namespace wrk {
+namespace k {
+
+enum MatKind { MAT_FP16 = 0, MAT_INT8 = 1, MAT_NF4 = 2 };
+
+// ---- quantizers (quant.cu) -------------------------------------------------------------
+cudaError_t quantize_int8(const __half* input, size_t len, __half* minmax, uint8_t* output, int num_sms,
+                          cudaStream_t stream);
+cudaError_t quantize_nf4(const __half* input, size_t len, const float* table, bool table_sorted, __half* absmax,
+                         uint8_t* output, int num_sms, cudaStream_t stream);
+
+// ---- quantized / fp16 matmul (matmul.cu) --------------------------------------------------
+struct MatmulArgs {
+    int kind;              // MatKind
+    const void* matrix;    // [K (or K/2 bytes), M, B] row-major rows
+    const __half* scale;   // Int8: (min, max) per 128 flat elements; NF4: absmax per 64; else null
+    const float* table;    // NF4: 16 floats on the device
+    uint32_t K, M, B;
+    uint32_t N;            // tokens
+    DView in;              // [K, N, B]
+    DView out;             // [M, N, B]
+    int act;
+    // Optional second operand set fused into the same launch is not supported here.
+};
+cudaError_t matmul(const MatmulArgs& a, int num_sms, cudaStream_t stream);
+
+// ---- WKV recurrences (wkv.cu) ------------------------------------------------------------
+struct WkvArgs {
+    const uint32_t* cursors;  // packed [T] or wide [3 * T]
+    int wide;
+    DView state;              // f32 [C, S + 1, B]
+    uint32_t S, H, T, B;
+    int dtype;                // dtype of k, v, r, x (v5/v6) or r, w, n, x (v7)
+    const float* time_decay;  // v5: [S, H]; v6: [S, H, T]
+    const float* time_first;  // v5/v6: [S, H]
+    int per_token_decay;      // v6 = 1, v5 = 0
+    const void* k;            // v5/v6
+    const void* v;
+    const void* r;            // all
+    const void* w;            // v7 raw decay
+    const void* n;            // v7 stacked k, v, a, kk: [S, H, T, 4]
+    void* x;
+    int32_t* status;          // device status word
+};
+cudaError_t time_mix_v56(const WkvArgs& a, cudaStream_t stream);
+cudaError_t time_mix_v7(const WkvArgs& a, cudaStream_t stream);
+cudaError_t time_first_v7(const __half* u, int dtype, const void* r, const void* n, void* x, uint32_t S,
+                          uint32_t H, uint32_t T, cudaStream_t stream);
+
+// ---- supporting ops (support.cu) -----------------------------------------------------------
+cudaError_t layer_norm(const __half* w, const __half* b, int dtype, void* x, uint32_t C, uint32_t rows,
+                       uint32_t wrows, float eps, cudaStream_t stream);
+cudaError_t l2_norm(int dtype, void* x, uint32_t C, uint32_t rows, float eps, cudaStream_t stream);
+cudaError_t token_shift(const uint32_t* cursors, int wide, DView time_mix, DView state, DView input, DView output,
+                        int reversed, cudaStream_t stream);
+cudaError_t channel_mix(const uint32_t* cursors, int wide, DView state, int dtype, const void* r, const void* v,
+                        void* x, uint32_t C, uint32_t T, int v7, cudaStream_t stream);
+cudaError_t binary(int is_mul, DView input, DView output, int act_x, int act_y, int act_out, cudaStream_t stream);
+cudaError_t activate(DView x, int act, cudaStream_t stream);
+cudaError_t blit(DView input, DView output, int transpose, cudaStream_t stream);
+cudaError_t lerp(DView input, DView output, DView factor, int reversed, cudaStream_t stream);
+cudaError_t affine(int dtype, void* x, size_t len, float scale, float bias, cudaStream_t stream);
+cudaError_t control_k_v7(const __half* p, DView a, DView k, cudaStream_t stream);
+
+}  // namespace k
+}  // namespace wrk

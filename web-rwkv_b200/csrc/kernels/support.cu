@@ -1,0 +1,250 @@
+// Supporting ops of the v5/v6/v7 jobs: normalisation, token shift, channel mix and the
+// elementwise/broadcast/copy ops.  These are the op-by-op ("strict") forms that mirror the
+// reference's operator list one to one; every tensor the reference stores as fp16 is a rounding
+// point here as well.  They are latency-bound on the activations of a single job and are not
+// individually roofline-graded.
+#include "device.cuh"
+
+namespace wrk {
+namespace k {
+
+namespace {
+
+constexpr int kEw = 256;
+
+inline int ew_grid(size_t n) {
+    size_t g = (n + kEw - 1) / kEw;
+    if (g < 1) g = 1;
+    if (g > 148 * 16) g = 148 * 16;
+    return (int)g;
+}
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    v = warp_sum(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    if (nw == 1) return v;
+    __syncthreads();  // scratch may still be read from a previous call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float s = 0.f;
+    for (int w = 0; w < nw; ++w) s += scratch[w];
+    return s;
+}
+
+// layer_norm.wgsl: per row of C, (x - mean) * rsqrt(var + eps) * w + b; var = E[(x - mean)^2].
+__global__ void layer_norm_kernel(const __half* w, const __half* b, int dtype, void* x, uint32_t C, uint32_t rows,
+                                  uint32_t wrows, float eps) {
+    __shared__ float scratch[32];
+    for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const size_t base = (size_t)row * C;
+        float s = 0.f;
+        for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) s += dload(x, dtype, base + c);
+        const float mean = block_sum(s, scratch) / (float)C;
+        float m2 = 0.f;
+        for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) {
+            const float d = dload(x, dtype, base + c) - mean;
+            m2 += d * d;
+        }
+        const float var = block_sum(m2, scratch) / (float)C + eps;
+        const float dev = rsqrtf(var);
+        const size_t wb = (size_t)(row % wrows) * C;
+        for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) {
+            const float v = (dload(x, dtype, base + c) - mean) * dev;
+            dstore(x, dtype, base + c, fmaf(v, __half2float(w[wb + c]), __half2float(b[wb + c])));
+        }
+    }
+}
+
+// normalize.wgsl l2_norm: x * rsqrt(sum x^2 + eps) per row of C.
+__global__ void l2_norm_kernel(int dtype, void* x, uint32_t C, uint32_t rows, float eps) {
+    __shared__ float scratch[32];
+    for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const size_t base = (size_t)row * C;
+        float s = 0.f;
+        for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) {
+            const float v = dload(x, dtype, base + c);
+            s += v * v;
+        }
+        const float norm = rsqrtf(block_sum(s, scratch) + eps);
+        for (uint32_t c = threadIdx.x; c < C; c += blockDim.x)
+            dstore(x, dtype, base + c, dload(x, dtype, base + c) * norm);
+    }
+}
+
+// token_shift.wgsl: out[c, t, z] = mix(x_t, prev, f) (reversed) or mix(prev, x_t, f); prev is the
+// previous token of the same sequence or, at the sequence's first token of the job, the carry row.
+__global__ void token_shift_kernel(const uint32_t* cursors, int wide, DView tm, DView state, DView in, DView out,
+                                   int reversed) {
+    const uint32_t C = out.shape[0], T = out.shape[1], Z = out.shape[2];
+    const size_t total = (size_t)C * T * Z;
+    for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t c = o % C, t = (o / C) % T, z = o / ((size_t)C * T);
+        const CursorD cu = cursor_at(cursors, wide, t);
+        const float f = dload(tm.base, tm.dtype, tm.index(c, tm.shape[1] == 1 ? 0 : t, z));
+        const float cur = dload(in.base, in.dtype, in.index(c, t, 0));
+        const float prev = (t == cu.token) ? static_cast<const float*>(state.base)[state.index(c, 0, cu.batch)]
+                                           : dload(in.base, in.dtype, in.index(c, t - 1, 0));
+        const float a = reversed ? cur : prev, b = reversed ? prev : cur;
+        dstore(out.base, out.dtype, out.index(c, t, z), a * (1.0f - f) + b * f);
+    }
+}
+
+// channel_mix.wgsl: carry row <- x_in at the sequence's last token; x = sigmoid(r) * v (v7: x = v).
+__global__ void channel_mix_kernel(const uint32_t* cursors, int wide, DView state, int dtype, const void* r,
+                                   const void* v, void* x, uint32_t C, uint32_t T, int v7) {
+    const size_t total = (size_t)C * T;
+    for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t c = o % C, t = o / C;
+        const CursorD cu = cursor_at(cursors, wide, t);
+        if (t - cu.token + 1u == cu.len)
+            static_cast<float*>(state.base)[state.index(c, 0, cu.batch)] = dload(x, dtype, o);
+        if (v7) {
+            dstore(x, dtype, o, dload(v, dtype, o));
+        } else {
+            const float rr = 1.0f / (1.0f + expf(-dload(r, dtype, o)));
+            dstore(x, dtype, o, rr * dload(v, dtype, o));
+        }
+    }
+}
+
+__global__ void binary_kernel(int is_mul, DView in, DView out, int act_x, int act_y, int act_out) {
+    const uint32_t C = out.shape[0], T = out.shape[1], B = out.shape[2];
+    const size_t total = (size_t)C * T * B;
+    for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t c = o % C, t = (o / C) % T, b = o / ((size_t)C * T);
+        const float xi = dload(in.base, in.dtype, in.index(c, in.shape[1] == 1 ? 0 : t, in.shape[2] == 1 ? 0 : b));
+        const size_t oi = out.index(c, t, b);
+        const float ax = activate_f(act_x, xi), ay = activate_f(act_y, dload(out.base, out.dtype, oi));
+        dstore(out.base, out.dtype, oi, activate_f(act_out, is_mul ? ax * ay : ax + ay));
+    }
+}
+
+__global__ void activate_kernel(DView x, int act) {
+    const uint32_t C = x.shape[0], T = x.shape[1], B = x.shape[2];
+    const size_t total = (size_t)C * T * B;
+    for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t c = o % C, t = (o / C) % T, b = o / ((size_t)C * T);
+        const size_t i = x.index(c, t, b);
+        dstore(x.base, x.dtype, i, activate_f(act, dload(x.base, x.dtype, i)));
+    }
+}
+
+__global__ void blit_kernel(DView in, DView out, int transpose) {
+    const uint32_t C = in.shape[0], T = in.shape[1], B = in.shape[2];
+    const size_t total = (size_t)C * T * B;
+    for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t c = o % C, t = (o / C) % T, b = o / ((size_t)C * T);
+        const float v = dload(in.base, in.dtype, in.index(c, t, b));
+        dstore(out.base, out.dtype, transpose ? out.index(c, b, t) : out.index(c, t, b), v);
+    }
+}
+
+__global__ void lerp_kernel(DView in, DView out, DView f, int reversed) {
+    const uint32_t C = out.shape[0], T = out.shape[1], B = out.shape[2];
+    const size_t total = (size_t)C * T * B;
+    for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t c = o % C, t = (o / C) % T, b = o / ((size_t)C * T);
+        const float ff = dload(f.base, f.dtype, f.index(c, f.shape[1] == 1 ? 0 : t, f.shape[2] == 1 ? 0 : b));
+        const float xi = dload(in.base, in.dtype, in.index(c, t, b));
+        const size_t oi = out.index(c, t, b);
+        const float yo = dload(out.base, out.dtype, oi);
+        const float a = reversed ? yo : xi, bb = reversed ? xi : yo;
+        dstore(out.base, out.dtype, oi, a * (1.0f - ff) + bb * ff);
+    }
+}
+
+__global__ void affine_kernel(int dtype, void* x, size_t len, float scale, float bias) {
+    for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < len; o += (size_t)gridDim.x * blockDim.x)
+        dstore(x, dtype, o, scale * dload(x, dtype, o) + bias);
+}
+
+__global__ void control_k_kernel(const __half* p, DView a, DView k) {
+    const uint32_t C = k.shape[0], T = k.shape[1], B = k.shape[2];
+    const size_t total = (size_t)C * T * B;
+    for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t c = o % C, t = (o / C) % T, b = o / ((size_t)C * T);
+        const float pp = __half2float(p[c]);
+        const float av = dload(a.base, a.dtype, a.index(c, t, b));
+        const size_t ki = k.index(c, t, b);
+        dstore(k.base, k.dtype, ki, dload(k.base, k.dtype, ki) * (1.0f + (av - 1.0f) * pp));
+    }
+}
+
+}  // namespace
+
+cudaError_t layer_norm(const __half* w, const __half* b, int dtype, void* x, uint32_t C, uint32_t rows, uint32_t wrows,
+                       float eps, cudaStream_t stream) {
+    if (rows == 0 || C == 0) return cudaSuccess;
+    const int block = C <= 256 ? 32 : 256;
+    const uint32_t grid = rows < 148u * 32u ? rows : 148u * 32u;
+    layer_norm_kernel<<<grid, block, 0, stream>>>(w, b, dtype, x, C, rows, wrows, eps);
+    return cudaGetLastError();
+}
+
+cudaError_t l2_norm(int dtype, void* x, uint32_t C, uint32_t rows, float eps, cudaStream_t stream) {
+    if (rows == 0 || C == 0) return cudaSuccess;
+    const int block = C <= 256 ? 32 : 256;
+    const uint32_t grid = rows < 148u * 32u ? rows : 148u * 32u;
+    l2_norm_kernel<<<grid, block, 0, stream>>>(dtype, x, C, rows, eps);
+    return cudaGetLastError();
+}
+
+cudaError_t token_shift(const uint32_t* cursors, int wide, DView time_mix, DView state, DView input, DView output,
+                        int reversed, cudaStream_t stream) {
+    const size_t total = (size_t)output.shape[0] * output.shape[1] * output.shape[2];
+    if (total == 0) return cudaSuccess;
+    token_shift_kernel<<<ew_grid(total), kEw, 0, stream>>>(cursors, wide, time_mix, state, input, output, reversed);
+    return cudaGetLastError();
+}
+
+cudaError_t channel_mix(const uint32_t* cursors, int wide, DView state, int dtype, const void* r, const void* v,
+                        void* x, uint32_t C, uint32_t T, int v7, cudaStream_t stream) {
+    const size_t total = (size_t)C * T;
+    if (total == 0) return cudaSuccess;
+    channel_mix_kernel<<<ew_grid(total), kEw, 0, stream>>>(cursors, wide, state, dtype, r, v, x, C, T, v7);
+    return cudaGetLastError();
+}
+
+cudaError_t binary(int is_mul, DView input, DView output, int act_x, int act_y, int act_out, cudaStream_t stream) {
+    const size_t total = (size_t)output.shape[0] * output.shape[1] * output.shape[2];
+    if (total == 0) return cudaSuccess;
+    binary_kernel<<<ew_grid(total), kEw, 0, stream>>>(is_mul, input, output, act_x, act_y, act_out);
+    return cudaGetLastError();
+}
+
+cudaError_t activate(DView x, int act, cudaStream_t stream) {
+    const size_t total = (size_t)x.shape[0] * x.shape[1] * x.shape[2];
+    if (total == 0) return cudaSuccess;
+    activate_kernel<<<ew_grid(total), kEw, 0, stream>>>(x, act);
+    return cudaGetLastError();
+}
+
+cudaError_t blit(DView input, DView output, int transpose, cudaStream_t stream) {
+    const size_t total = (size_t)input.shape[0] * input.shape[1] * input.shape[2];
+    if (total == 0) return cudaSuccess;
+    blit_kernel<<<ew_grid(total), kEw, 0, stream>>>(input, output, transpose);
+    return cudaGetLastError();
+}
+
+cudaError_t lerp(DView input, DView output, DView factor, int reversed, cudaStream_t stream) {
+    const size_t total = (size_t)output.shape[0] * output.shape[1] * output.shape[2];
+    if (total == 0) return cudaSuccess;
+    lerp_kernel<<<ew_grid(total), kEw, 0, stream>>>(input, output, factor, reversed);
+    return cudaGetLastError();
+}
+
+cudaError_t affine(int dtype, void* x, size_t len, float scale, float bias, cudaStream_t stream) {
+    if (len == 0) return cudaSuccess;
+    affine_kernel<<<ew_grid(len), kEw, 0, stream>>>(dtype, x, len, scale, bias);
+    return cudaGetLastError();
+}
+
+cudaError_t control_k_v7(const __half* p, DView a, DView k, cudaStream_t stream) {
+    const size_t total = (size_t)k.shape[0] * k.shape[1] * k.shape[2];
+    if (total == 0) return cudaSuccess;
+    control_k_kernel<<<ew_grid(total), kEw, 0, stream>>>(p, a, k);
+    return cudaGetLastError();
+}
+
+}  // namespace k
+}  // namespace wrk

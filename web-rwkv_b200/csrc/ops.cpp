@@ -1,0 +1,630 @@
+// Op builders: the `TensorOp::*` constructors of src/tensor/ops.rs restated over CUDA launches.
+// Each builder performs the reference's shape checks, returns the same error kinds, and yields a
+// deferred op; nothing runs until the op is submitted.
+#include <cmath>
+
+#include "common.h"
+#include "kernels/kernels.h"
+
+using namespace wrk;
+
+namespace {
+
+inline int cursors_wide(const wrk_tensor* cursors, uint32_t T) {
+    // packed: one u32 per token ([T]); wide: three u32 per token ([3, T] or [3 * T])
+    return cursors->len() == (size_t)3 * T && T != 0 ? 1 : 0;
+}
+
+int32_t check_cursors(const wrk_tensor* cursors, uint32_t T) {
+    WRK_REQUIRE(cursors->dtype == WRK_U32, WRK_ERR_TYPE, "data type mismatch: cursors must be u32");
+    WRK_REQUIRE(cursors->len() == T || cursors->len() == (size_t)3 * T, WRK_ERR_SHAPE,
+                "tensor shape not match (cursors): %zu entries for %u tokens", cursors->len(), T);
+    return WRK_OK;
+}
+
+#define REQ_FLOAT(t, what) \
+    WRK_REQUIRE(is_float((t)->dtype), WRK_ERR_TYPE, "data type mismatch: %s must be f32 or f16", what)
+#define REQ_DTYPE(t, dt, what) \
+    WRK_REQUIRE((t)->dtype == (dt), WRK_ERR_TYPE, "data type mismatch: %s has dtype %d, expected %d", what, (t)->dtype, (int)(dt))
+#define REQ_NN(...)                                                                      \
+    do {                                                                                 \
+        const void* _p[] = {__VA_ARGS__};                                                \
+        for (auto q : _p) WRK_REQUIRE(q, WRK_ERR_INVALID_ARGUMENT, "null argument");     \
+    } while (0)
+
+int32_t matmul_common(const char* name, int kind, wrk_tensor* matrix, wrk_tensor* scale, wrk_tensor* quant,
+                      const wrk_view* input, const wrk_view* output, int32_t act, wrk_op** out) {
+    REQ_NN(matrix, input, output, out, input->tensor, output->tensor);
+    REQ_FLOAT(input->tensor, "input");
+    REQ_FLOAT(output->tensor, "output");
+    WRK_REQUIRE(act >= WRK_ACT_NONE && act <= WRK_ACT_SILU, WRK_ERR_INVALID_ARGUMENT, "unknown activation %d", act);
+    const uint32_t m = output->shape[0], n = output->shape[1], b = output->shape[2];
+    const uint32_t k = input->shape[0];
+    if (kind == k::MAT_FP16) {
+        REQ_DTYPE(matrix, WRK_F16, "matrix");
+        WRK_TRY(check_shape("matrix", matrix->shape, k, m, b, 1));
+    } else if (kind == k::MAT_INT8) {
+        REQ_NN(scale);
+        REQ_DTYPE(matrix, WRK_U8, "matrix");
+        REQ_DTYPE(scale, WRK_F16, "minmax");
+        const size_t len = matrix->len();
+        WRK_TRY(check_shape("minmax", scale->shape, (uint32_t)(((len << 1) + 127) / 128), 1, 1, 1));
+        WRK_TRY(check_shape("matrix", matrix->shape, k, m, b, 1));
+    } else {
+        REQ_NN(scale, quant);
+        REQ_DTYPE(matrix, WRK_U8, "matrix");
+        REQ_DTYPE(scale, WRK_F16, "absmax");
+        REQ_DTYPE(quant, WRK_F32, "quant");
+        WRK_TRY(check_shape("quant", quant->shape, 16, 1, 1, 1));
+        const size_t len = matrix->len() << 1;
+        WRK_TRY(check_shape("absmax", scale->shape, (uint32_t)((len + 63) / 64), 1, 1, 1));
+        WRK_TRY(check_shape("matrix", matrix->shape, k >> 1, m, b, 1));
+    }
+    WRK_TRY(check_view("input", input, k, n, b, 1));
+    WRK_TRY(check_view("output", output, m, n, b, 1));
+
+    k::MatmulArgs a{};
+    a.kind = kind;
+    a.matrix = matrix->ptr();
+    a.scale = scale ? static_cast<const __half*>(scale->ptr()) : nullptr;
+    a.table = quant ? static_cast<const float*>(quant->ptr()) : nullptr;
+    a.K = k;
+    a.M = m;
+    a.B = b;
+    a.N = n;
+    a.in = make_dview(*input);
+    a.out = make_dview(*output);
+    a.act = act;
+    const int sms = matrix->ctx->num_sms;
+    *out = new_atom(name, [a, sms](cudaStream_t s) { return k::matmul(a, sms, s); },
+                    {matrix, scale, quant, input->tensor, output->tensor});
+    return WRK_OK;
+}
+
+int32_t time_mix_v56(const char* name, int per_token, wrk_tensor* cursors, wrk_tensor* time_decay,
+                     wrk_tensor* time_first, const wrk_view* state, wrk_tensor* k, wrk_tensor* v, wrk_tensor* r,
+                     wrk_tensor* x, wrk_op** out) {
+    REQ_NN(cursors, time_decay, time_first, state, state->tensor, k, v, r, x, out);
+    REQ_FLOAT(x, "x");
+    REQ_DTYPE(k, x->dtype, "k");
+    REQ_DTYPE(v, x->dtype, "v");
+    REQ_DTYPE(r, x->dtype, "r");
+    REQ_DTYPE(time_decay, WRK_F32, "time_decay");
+    REQ_DTYPE(time_first, WRK_F32, "time_first");
+    REQ_DTYPE(state->tensor, WRK_F32, "state");
+    const Shape4 sh = x->shape;
+    const uint32_t S = sh[0], H = sh[1], T = sh[2], stride = S * H;
+    WRK_TRY(check_shape("x", sh, S, H, T, 1));
+    WRK_TRY(check_shape("k", k->shape, S, H, T, 1));
+    WRK_TRY(check_shape("v", v->shape, S, H, T, 1));
+    WRK_TRY(check_shape("r", r->shape, S, H, T, 1));
+    if (per_token) WRK_TRY(check_shape("time_decay", time_decay->shape, S, H, T, 1));
+    else WRK_TRY(check_shape("time_decay", time_decay->shape, S, H, 1, 1));
+    WRK_TRY(check_shape("time_first", time_first->shape, S, H, 1, 1));
+    WRK_TRY(check_view("state", state, stride, S + 1, state->shape[2], 1));
+    WRK_TRY(check_cursors(cursors, T));
+    WRK_REQUIRE(S == 32 || S == 64 || S == 128, WRK_ERR_UNSUPPORTED, "head size %u not built (32, 64, 128)", S);
+
+    k::WkvArgs a{};
+    a.cursors = static_cast<const uint32_t*>(cursors->ptr());
+    a.wide = cursors_wide(cursors, T);
+    a.state = make_dview(*state);
+    a.S = S; a.H = H; a.T = T; a.B = state->shape[2];
+    a.dtype = x->dtype;
+    a.time_decay = static_cast<const float*>(time_decay->ptr());
+    a.time_first = static_cast<const float*>(time_first->ptr());
+    a.per_token_decay = per_token;
+    a.k = k->ptr(); a.v = v->ptr(); a.r = r->ptr(); a.x = x->ptr();
+    a.status = x->ctx->device_status;
+    *out = new_atom(name, [a](cudaStream_t s) { return k::time_mix_v56(a, s); },
+                    {cursors, time_decay, time_first, state->tensor, k, v, r, x});
+    return WRK_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t wrk_nf4_table(float table[16]) {
+    // Float4Quant::new, src/tensor/matrix.rs:48-70 (the NormalFloat4 code book)
+    static const float q[16] = {-1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+                                -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+                                0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
+                                0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
+    WRK_REQUIRE(table, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    for (int i = 0; i < 16; ++i) table[i] = q[i];
+    return WRK_OK;
+}
+
+int32_t wrk_op_quantize_mat_int8(wrk_tensor* input, wrk_tensor* minmax, wrk_tensor* output, wrk_op** out) {
+    REQ_NN(input, minmax, output, out);
+    REQ_DTYPE(input, WRK_F16, "input");
+    REQ_DTYPE(minmax, WRK_F16, "minmax");
+    REQ_DTYPE(output, WRK_U8, "output");
+    const Shape4 sh = output->shape;
+    const size_t minmax_len = (sh.len() + 127) / 128;
+    WRK_TRY(check_shape("input", input->shape, sh[0], sh[1], sh[2], sh[3]));
+    WRK_TRY(check_shape("minmax", minmax->shape, (uint32_t)(minmax_len << 1), 1, 1, 1));
+    const __half* in = static_cast<const __half*>(input->ptr());
+    __half* mm = static_cast<__half*>(minmax->ptr());
+    uint8_t* o = static_cast<uint8_t*>(output->ptr());
+    const size_t len = sh.len();
+    const int sms = output->ctx->num_sms;
+    *out = new_atom("quantize_mat_int8", [=](cudaStream_t s) { return k::quantize_int8(in, len, mm, o, sms, s); },
+                    {input, minmax, output});
+    return WRK_OK;
+}
+
+int32_t wrk_op_quantize_mat_nf4(wrk_tensor* input, wrk_tensor* quant, wrk_tensor* absmax, wrk_tensor* output,
+                                wrk_op** out) {
+    REQ_NN(input, quant, absmax, output, out);
+    REQ_DTYPE(input, WRK_F16, "input");
+    REQ_DTYPE(quant, WRK_F32, "quant");
+    REQ_DTYPE(absmax, WRK_F16, "absmax");
+    REQ_DTYPE(output, WRK_U8, "output");
+    const Shape4 sh = output->shape;
+    const size_t in_len = sh.len() << 1;
+    WRK_TRY(check_shape("input", input->shape, sh[0] << 1, sh[1], sh[2], sh[3]));
+    WRK_TRY(check_shape("absmax", absmax->shape, (uint32_t)((in_len + 63) / 64), 1, 1, 1));
+    WRK_TRY(check_shape("quant", quant->shape, 16, 1, 1, 1));
+    // The bracketing search needs a strictly ascending code book with sane gaps; otherwise the
+    // kernel runs the reference's 16-way scan.  Reading the table back is a one-off at load time.
+    float table[16];
+    WRK_TRY(wrk_tensor_back(quant, table, sizeof table));
+    bool sorted = true;
+    for (int i = 0; i + 1 < 16; ++i)
+        if (!(table[i + 1] - table[i] > 1e-4f)) sorted = false;
+    const __half* in = static_cast<const __half*>(input->ptr());
+    const float* q = static_cast<const float*>(quant->ptr());
+    __half* am = static_cast<__half*>(absmax->ptr());
+    uint8_t* o = static_cast<uint8_t*>(output->ptr());
+    const int sms = output->ctx->num_sms;
+    *out = new_atom("quantize_mat_nf4",
+                    [=](cudaStream_t s) { return k::quantize_nf4(in, in_len, q, sorted, am, o, sms, s); },
+                    {input, quant, absmax, output});
+    return WRK_OK;
+}
+
+int32_t wrk_op_matmul_vec_fp16(wrk_tensor* matrix, const wrk_view* input, const wrk_view* output, int32_t act,
+                               int32_t sparse, wrk_op** out) {
+    (void)sparse;  // skipping all-zero input groups never changes the result (matmul_vec_fp16.wgsl)
+    return matmul_common("matmul_vec_fp16", k::MAT_FP16, matrix, nullptr, nullptr, input, output, act, out);
+}
+
+int32_t wrk_op_matmul_vec_int8(wrk_tensor* matrix, wrk_tensor* minmax, const wrk_view* input, const wrk_view* output,
+                               int32_t act, int32_t sparse, wrk_op** out) {
+    (void)sparse;
+    return matmul_common("matmul_vec_int8", k::MAT_INT8, matrix, minmax, nullptr, input, output, act, out);
+}
+
+int32_t wrk_op_matmul_vec_nf4(wrk_tensor* matrix, wrk_tensor* quant, wrk_tensor* absmax, const wrk_view* input,
+                              const wrk_view* output, int32_t act, int32_t sparse, wrk_op** out) {
+    (void)sparse;
+    return matmul_common("matmul_vec_nf4", k::MAT_NF4, matrix, absmax, quant, input, output, act, out);
+}
+
+static int32_t whole_matrix(const wrk_view* matrix, wrk_tensor** t) {
+    REQ_NN(matrix, matrix->tensor);
+    // the reference's matrix-matrix kernels index the scales with the unsliced row stride
+    // (matmul_mat_int8.wgsl:99-104): only whole-tensor views are meaningful
+    for (int i = 0; i < 4; ++i)
+        WRK_REQUIRE(matrix->offset[i] == 0 && matrix->shape[i] == matrix->tensor->shape.v[i] &&
+                        matrix->stride[i] == matrix->tensor->shape.v[i],
+                    WRK_ERR_SLICE_INVALID, "slice not contiguous: matrix views must cover the whole tensor");
+    *t = matrix->tensor;
+    return WRK_OK;
+}
+
+int32_t wrk_op_matmul_mat_fp16(const wrk_view* matrix, const wrk_view* input, const wrk_view* output, int32_t act,
+                               wrk_op** out) {
+    wrk_tensor* m = nullptr;
+    WRK_TRY(whole_matrix(matrix, &m));
+    return matmul_common("matmul_mat_fp16", k::MAT_FP16, m, nullptr, nullptr, input, output, act, out);
+}
+
+int32_t wrk_op_matmul_mat_int8(const wrk_view* matrix, wrk_tensor* minmax, const wrk_view* input,
+                               const wrk_view* output, int32_t act, wrk_op** out) {
+    wrk_tensor* m = nullptr;
+    WRK_TRY(whole_matrix(matrix, &m));
+    return matmul_common("matmul_mat_int8", k::MAT_INT8, m, minmax, nullptr, input, output, act, out);
+}
+
+int32_t wrk_op_matmul_mat_nf4(const wrk_view* matrix, wrk_tensor* quant, wrk_tensor* absmax, const wrk_view* input,
+                              const wrk_view* output, int32_t act, wrk_op** out) {
+    wrk_tensor* m = nullptr;
+    WRK_TRY(whole_matrix(matrix, &m));
+    return matmul_common("matmul_mat_nf4", k::MAT_NF4, m, absmax, quant, input, output, act, out);
+}
+
+int32_t wrk_op_time_mix_v5(wrk_tensor* cursors, wrk_tensor* time_decay, wrk_tensor* time_first, const wrk_view* state,
+                           wrk_tensor* k, wrk_tensor* v, wrk_tensor* r, wrk_tensor* x, wrk_op** out) {
+    return time_mix_v56("time_mix_v5", 0, cursors, time_decay, time_first, state, k, v, r, x, out);
+}
+
+int32_t wrk_op_time_mix_v6(wrk_tensor* cursors, wrk_tensor* time_decay, wrk_tensor* time_first, const wrk_view* state,
+                           wrk_tensor* k, wrk_tensor* v, wrk_tensor* r, wrk_tensor* x, wrk_op** out) {
+    return time_mix_v56("time_mix_v6", 1, cursors, time_decay, time_first, state, k, v, r, x, out);
+}
+
+int32_t wrk_op_time_mix_v7(wrk_tensor* cursors, const wrk_view* state, wrk_tensor* r, wrk_tensor* w, wrk_tensor* n,
+                           wrk_tensor* x, wrk_op** out) {
+    REQ_NN(cursors, state, state->tensor, r, w, n, x, out);
+    REQ_FLOAT(x, "x");
+    REQ_DTYPE(r, x->dtype, "r");
+    REQ_DTYPE(w, x->dtype, "w");
+    REQ_DTYPE(n, x->dtype, "n");
+    REQ_DTYPE(state->tensor, WRK_F32, "state");
+    const Shape4 sh = x->shape;
+    const uint32_t S = sh[0], H = sh[1], T = sh[2], stride = S * H;
+    WRK_TRY(check_shape("x", sh, S, H, T, 1));
+    WRK_TRY(check_shape("r", r->shape, S, H, T, 1));
+    WRK_TRY(check_shape("w", w->shape, S, H, T, 1));
+    WRK_TRY(check_shape("n", n->shape, S, H, T, 4));
+    WRK_TRY(check_view("state", state, stride, S + 1, state->shape[2], 1));
+    WRK_TRY(check_cursors(cursors, T));
+    WRK_REQUIRE(S == 32 || S == 64 || S == 128, WRK_ERR_UNSUPPORTED, "head size %u not built (32, 64, 128)", S);
+    k::WkvArgs a{};
+    a.cursors = static_cast<const uint32_t*>(cursors->ptr());
+    a.wide = cursors_wide(cursors, T);
+    a.state = make_dview(*state);
+    a.S = S; a.H = H; a.T = T; a.B = state->shape[2];
+    a.dtype = x->dtype;
+    a.r = r->ptr(); a.w = w->ptr(); a.n = n->ptr(); a.x = x->ptr();
+    a.status = x->ctx->device_status;
+    *out = new_atom("time_mix_v7", [a](cudaStream_t s) { return k::time_mix_v7(a, s); },
+                    {cursors, state->tensor, r, w, n, x});
+    return WRK_OK;
+}
+
+int32_t wrk_op_time_first_v7(wrk_tensor* u, wrk_tensor* r, wrk_tensor* n, wrk_tensor* x, wrk_op** out) {
+    REQ_NN(u, r, n, x, out);
+    REQ_FLOAT(x, "x");
+    REQ_DTYPE(u, WRK_F16, "u");
+    REQ_DTYPE(r, x->dtype, "r");
+    REQ_DTYPE(n, x->dtype, "n");
+    const Shape4 sh = x->shape;
+    const uint32_t S = sh[0], H = sh[1], T = sh[2];
+    WRK_TRY(check_shape("x", sh, S, H, T, 1));
+    WRK_TRY(check_shape("r", r->shape, S, H, T, 1));
+    WRK_TRY(check_shape("u", u->shape, S, H, 1, 1));
+    WRK_TRY(check_shape("n", n->shape, S, H, T, 4));
+    const __half* up = static_cast<const __half*>(u->ptr());
+    const void *rp = r->ptr(), *np = n->ptr();
+    void* xp = x->ptr();
+    const int dt = x->dtype;
+    *out = new_atom("time_first_v7", [=](cudaStream_t s) { return k::time_first_v7(up, dt, rp, np, xp, S, H, T, s); },
+                    {u, r, n, x});
+    return WRK_OK;
+}
+
+// ---- supporting ops ----------------------------------------------------------------------
+
+static int32_t norm_common(const char* name, bool group, wrk_tensor* w, wrk_tensor* b, wrk_tensor* x, float eps,
+                           wrk_op** out) {
+    REQ_NN(w, b, x, out);
+    REQ_FLOAT(x, "x");
+    REQ_DTYPE(w, WRK_F16, "w");
+    REQ_DTYPE(b, WRK_F16, "b");
+    const Shape4 sh = x->shape;
+    WRK_TRY(check_shape("x", sh, sh[0], sh[1], sh[2], 1));
+    uint32_t rows, wrows;
+    if (group) {
+        WRK_TRY(check_shape("w", w->shape, sh[0], sh[1], 1, 1));
+        WRK_TRY(check_shape("b", b->shape, sh[0], sh[1], 1, 1));
+        rows = sh[1] * sh[2];
+        wrows = sh[1];
+    } else {
+        WRK_TRY(check_shape("w", w->shape, sh[0], 1, 1, 1));
+        WRK_TRY(check_shape("b", b->shape, sh[0], 1, 1, 1));
+        rows = sh[1] * sh[2];
+        wrows = 1;
+    }
+    const __half* wp = static_cast<const __half*>(w->ptr());
+    const __half* bp = static_cast<const __half*>(b->ptr());
+    void* xp = x->ptr();
+    const int dt = x->dtype;
+    const uint32_t C = sh[0];
+    *out = new_atom(name, [=](cudaStream_t s) { return k::layer_norm(wp, bp, dt, xp, C, rows, wrows, eps, s); },
+                    {w, b, x});
+    return WRK_OK;
+}
+
+int32_t wrk_op_layer_norm(wrk_tensor* w, wrk_tensor* b, wrk_tensor* x, float eps, wrk_op** out) {
+    return norm_common("layer_norm", false, w, b, x, eps, out);
+}
+
+int32_t wrk_op_group_norm(wrk_tensor* w, wrk_tensor* b, wrk_tensor* x, float eps, wrk_op** out) {
+    return norm_common("group_norm", true, w, b, x, eps, out);
+}
+
+int32_t wrk_op_l2_norm(wrk_tensor* x, float eps, wrk_op** out) {
+    REQ_NN(x, out);
+    REQ_FLOAT(x, "x");
+    const Shape4 sh = x->shape;
+    void* xp = x->ptr();
+    const int dt = x->dtype;
+    const uint32_t C = sh[0], rows = sh[1] * sh[2];
+    *out = new_atom("l2_norm", [=](cudaStream_t s) { return k::l2_norm(dt, xp, C, rows, eps, s); }, {x});
+    return WRK_OK;
+}
+
+int32_t wrk_op_token_shift(wrk_tensor* cursors, const wrk_view* time_mix, const wrk_view* state, wrk_tensor* input,
+                           wrk_tensor* output, int32_t reversed, wrk_op** out) {
+    REQ_NN(cursors, time_mix, time_mix->tensor, state, state->tensor, input, output, out);
+    REQ_FLOAT(time_mix->tensor, "time_mix");
+    REQ_FLOAT(input, "input");
+    REQ_FLOAT(output, "output");
+    REQ_DTYPE(state->tensor, WRK_F32, "state");
+    const Shape4 sh = output->shape;
+    const uint32_t C = sh[0], T = sh[1], count = sh[2];
+    if (!(input->shape == Shape4{{C, T, count, 1}}) && !(input->shape == Shape4{{C, T, 1, 1}}))
+        return check_shape("input", input->shape, C, T, 1, 1);
+    if (!view_is(*time_mix, C, T, count, 1) && !view_is(*time_mix, C, 1, 1, 1))
+        return check_view("time_mix", time_mix, C, 1, 1, 1);
+    WRK_TRY(check_view("state", state, C, state->shape[1], state->shape[2], 1));
+    WRK_TRY(check_cursors(cursors, T));
+    const uint32_t* cp = static_cast<const uint32_t*>(cursors->ptr());
+    const int wide = cursors_wide(cursors, T);
+    DView tm = make_dview(*time_mix), st = make_dview(*state), in = make_dview(input), o = make_dview(output);
+    *out = new_atom("token_shift", [=](cudaStream_t s) { return k::token_shift(cp, wide, tm, st, in, o, reversed, s); },
+                    {cursors, time_mix->tensor, state->tensor, input, output});
+    return WRK_OK;
+}
+
+static int32_t channel_mix_common(const char* name, int v7, wrk_tensor* cursors, const wrk_view* state, wrk_tensor* r,
+                                  wrk_tensor* v, wrk_tensor* x, wrk_op** out) {
+    REQ_NN(cursors, state, state->tensor, v, x, out);
+    REQ_FLOAT(x, "x");
+    REQ_DTYPE(v, x->dtype, "v");
+    REQ_DTYPE(state->tensor, WRK_F32, "state");
+    const Shape4 sh = x->shape;
+    WRK_TRY(check_shape("x", sh, sh[0], sh[1], 1, 1));
+    WRK_TRY(check_shape("v", v->shape, sh[0], sh[1], 1, 1));
+    if (!v7) {
+        REQ_NN(r);
+        REQ_DTYPE(r, x->dtype, "r");
+        WRK_TRY(check_shape("r", r->shape, sh[0], sh[1], 1, 1));
+    }
+    WRK_TRY(check_view("state", state, sh[0], 1, state->shape[2], 1));
+    WRK_TRY(check_cursors(cursors, sh[1]));
+    const uint32_t* cp = static_cast<const uint32_t*>(cursors->ptr());
+    const int wide = cursors_wide(cursors, sh[1]);
+    DView st = make_dview(*state);
+    const void* rp = r ? r->ptr() : nullptr;
+    const void* vp = v->ptr();
+    void* xp = x->ptr();
+    const int dt = x->dtype;
+    const uint32_t C = sh[0], T = sh[1];
+    *out = new_atom(name, [=](cudaStream_t s) { return k::channel_mix(cp, wide, st, dt, rp, vp, xp, C, T, v7, s); },
+                    {cursors, state->tensor, r, v, x});
+    return WRK_OK;
+}
+
+int32_t wrk_op_channel_mix(wrk_tensor* cursors, const wrk_view* state, wrk_tensor* r, wrk_tensor* v, wrk_tensor* x,
+                           wrk_op** out) {
+    return channel_mix_common("channel_mix", 0, cursors, state, r, v, x, out);
+}
+
+int32_t wrk_op_channel_mix_v7(wrk_tensor* cursors, const wrk_view* state, wrk_tensor* v, wrk_tensor* x, wrk_op** out) {
+    return channel_mix_common("channel_mix_v7", 1, cursors, state, nullptr, v, x, out);
+}
+
+static int32_t binary_common(const char* name, int is_mul, const wrk_view* input, const wrk_view* output, int32_t act_x,
+                             int32_t act_y, int32_t act_out, wrk_op** out) {
+    REQ_NN(input, input->tensor, output, output->tensor, out);
+    REQ_FLOAT(input->tensor, "input");
+    REQ_FLOAT(output->tensor, "output");
+    const uint32_t C = output->shape[0], T = output->shape[1], B = output->shape[2];
+    if (!view_is(*input, C, T, B, 1) && !view_is(*input, C, 1, B, 1) && !view_is(*input, C, T, 1, 1) &&
+        !view_is(*input, C, 1, 1, 1))
+        return check_view("input", input, C, T, B, 1);
+    WRK_TRY(check_view("output", output, C, T, B, 1));
+    DView in = make_dview(*input), o = make_dview(*output);
+    *out = new_atom(name, [=](cudaStream_t s) { return k::binary(is_mul, in, o, act_x, act_y, act_out, s); },
+                    {input->tensor, output->tensor});
+    return WRK_OK;
+}
+
+int32_t wrk_op_add_activate(const wrk_view* input, const wrk_view* output, int32_t act_x, int32_t act_y,
+                            int32_t act_out, wrk_op** out) {
+    return binary_common("add", 0, input, output, act_x, act_y, act_out, out);
+}
+
+int32_t wrk_op_mul_activate(const wrk_view* input, const wrk_view* output, int32_t act_x, int32_t act_y,
+                            int32_t act_out, wrk_op** out) {
+    return binary_common("mul", 1, input, output, act_x, act_y, act_out, out);
+}
+
+int32_t wrk_op_activate(const wrk_view* x, int32_t act, wrk_op** out) {
+    REQ_NN(x, x->tensor, out);
+    REQ_FLOAT(x->tensor, "x");
+    DView xv = make_dview(*x);
+    *out = new_atom("activate", [=](cudaStream_t s) { return k::activate(xv, act, s); }, {x->tensor});
+    return WRK_OK;
+}
+
+int32_t wrk_op_blit(const wrk_view* input, const wrk_view* output, wrk_op** out) {
+    REQ_NN(input, input->tensor, output, output->tensor, out);
+    REQ_FLOAT(input->tensor, "input");
+    REQ_FLOAT(output->tensor, "output");
+    WRK_TRY(check_view("input", input, output->shape[0], output->shape[1], output->shape[2], output->shape[3]));
+    DView in = make_dview(*input), o = make_dview(*output);
+    *out = new_atom("blit", [=](cudaStream_t s) { return k::blit(in, o, 0, s); }, {input->tensor, output->tensor});
+    return WRK_OK;
+}
+
+int32_t wrk_op_transpose(const wrk_view* input, const wrk_view* output, wrk_op** out) {
+    REQ_NN(input, input->tensor, output, output->tensor, out);
+    REQ_FLOAT(input->tensor, "input");
+    REQ_FLOAT(output->tensor, "output");
+    WRK_TRY(check_view("input", input, input->shape[0], input->shape[1], input->shape[2], 1));
+    WRK_TRY(check_view("output", output, input->shape[0], input->shape[2], input->shape[1], 1));
+    DView in = make_dview(*input), o = make_dview(*output);
+    *out = new_atom("transpose", [=](cudaStream_t s) { return k::blit(in, o, 1, s); }, {input->tensor, output->tensor});
+    return WRK_OK;
+}
+
+int32_t wrk_op_lerp(const wrk_view* input, const wrk_view* output, const wrk_view* factor, int32_t reversed,
+                    wrk_op** out) {
+    REQ_NN(input, input->tensor, output, output->tensor, factor, factor->tensor, out);
+    REQ_FLOAT(input->tensor, "input");
+    REQ_FLOAT(output->tensor, "output");
+    REQ_FLOAT(factor->tensor, "factor");
+    const uint32_t C = output->shape[0], T = output->shape[1], B = output->shape[2];
+    if (!view_is(*factor, C, T, B, 1) && !view_is(*factor, C, 1, B, 1) && !view_is(*factor, C, T, 1, 1) &&
+        !view_is(*factor, C, 1, 1, 1))
+        return check_view("factor", factor, C, T, B, 1);
+    WRK_TRY(check_view("input", input, C, T, B, 1));
+    WRK_TRY(check_view("output", output, C, T, B, 1));
+    DView in = make_dview(*input), o = make_dview(*output), f = make_dview(*factor);
+    *out = new_atom("lerp", [=](cudaStream_t s) { return k::lerp(in, o, f, reversed, s); },
+                    {input->tensor, output->tensor, factor->tensor});
+    return WRK_OK;
+}
+
+int32_t wrk_op_affine(wrk_tensor* x, float scale, float bias, wrk_op** out) {
+    REQ_NN(x, out);
+    REQ_FLOAT(x, "x");
+    void* xp = x->ptr();
+    const int dt = x->dtype;
+    const size_t len = x->len();
+    *out = new_atom("affine", [=](cudaStream_t s) { return k::affine(dt, xp, len, scale, bias, s); }, {x});
+    return WRK_OK;
+}
+
+int32_t wrk_op_control_k_v7(wrk_tensor* p, const wrk_view* a, const wrk_view* k, wrk_op** out) {
+    REQ_NN(p, a, a->tensor, k, k->tensor, out);
+    REQ_DTYPE(p, WRK_F16, "p");
+    REQ_FLOAT(a->tensor, "a");
+    REQ_FLOAT(k->tensor, "k");
+    const uint32_t C = k->shape[0], T = k->shape[1], B = k->shape[2];
+    WRK_TRY(check_view("a", a, C, T, B, 1));
+    WRK_TRY(check_shape("p", p->shape, C, 1, 1, 1));
+    const __half* pp = static_cast<const __half*>(p->ptr());
+    DView av = make_dview(*a), kv = make_dview(*k);
+    *out = new_atom("control_k_v7", [=](cudaStream_t s) { return k::control_k_v7(pp, av, kv, s); },
+                    {p, a->tensor, k->tensor});
+    return WRK_OK;
+}
+
+// ---- Matrix ---------------------------------------------------------------------------------
+
+int32_t wrk_matrix_fp16(wrk_tensor* w, wrk_matrix** out) {
+    REQ_NN(w, out);
+    REQ_DTYPE(w, WRK_F16, "matrix");
+    auto m = new wrk_matrix();
+    m->kind = 0;
+    wrk_tensor_retain(w);
+    m->w = w;
+    *out = m;
+    return WRK_OK;
+}
+
+int32_t wrk_matrix_quant_u8(wrk_tensor* matrix, wrk_matrix** out) {
+    REQ_NN(matrix, out);
+    REQ_DTYPE(matrix, WRK_F16, "matrix");
+    wrk_context* ctx = matrix->ctx;
+    const Shape4 sh = matrix->shape;
+    wrk_tensor *w = nullptr, *m = nullptr;
+    WRK_TRY(tensor_alloc(ctx, WRK_U8, sh.v, false, &w));
+    const uint32_t ms[4] = {(uint32_t)(((sh.len() << 1) + 127) / 128), 1, 1, 1};
+    int32_t s = tensor_alloc(ctx, WRK_F16, ms, false, &m);
+    wrk_op* op = nullptr;
+    if (s == WRK_OK) s = wrk_op_quantize_mat_int8(matrix, m, w, &op);
+    if (s == WRK_OK) s = wrk_run(ctx, op);
+    wrk_op_release(op);
+    if (s != WRK_OK) {
+        wrk_tensor_release(w);
+        wrk_tensor_release(m);
+        return s;
+    }
+    auto mat = new wrk_matrix();
+    mat->kind = 1;
+    mat->w = w;
+    mat->m = m;
+    *out = mat;
+    return WRK_OK;
+}
+
+int32_t wrk_matrix_quant_fp4(wrk_tensor* matrix, const float table[16], wrk_matrix** out) {
+    REQ_NN(matrix, table, out);
+    REQ_DTYPE(matrix, WRK_F16, "matrix");
+    wrk_context* ctx = matrix->ctx;
+    const Shape4 sh = matrix->shape;
+    WRK_REQUIRE(sh[0] % 2 == 0, WRK_ERR_SHAPE, "tensor shape not match: NF4 needs an even row length, got %u", sh[0]);
+    wrk_tensor *w = nullptr, *m = nullptr, *q = nullptr;
+    const uint32_t ws[4] = {sh[0] / 2, sh[1], sh[2], sh[3]};
+    const uint32_t ms[4] = {(uint32_t)((sh.len() + 63) / 64), 1, 1, 1};
+    const uint32_t qs[4] = {16, 1, 1, 1};
+    int32_t s = tensor_alloc(ctx, WRK_U8, ws, false, &w);
+    if (s == WRK_OK) s = tensor_alloc(ctx, WRK_F16, ms, false, &m);
+    if (s == WRK_OK) s = wrk_tensor_from_data(ctx, WRK_F32, qs, table, 16 * sizeof(float), &q);
+    wrk_op* op = nullptr;
+    if (s == WRK_OK) s = wrk_op_quantize_mat_nf4(matrix, q, m, w, &op);
+    if (s == WRK_OK) s = wrk_run(ctx, op);
+    wrk_op_release(op);
+    if (s != WRK_OK) {
+        wrk_tensor_release(w);
+        wrk_tensor_release(m);
+        wrk_tensor_release(q);
+        return s;
+    }
+    auto mat = new wrk_matrix();
+    mat->kind = 2;
+    mat->w = w;
+    mat->m = m;
+    mat->q = q;
+    *out = mat;
+    return WRK_OK;
+}
+
+int32_t wrk_matrix_quant_nf4(wrk_tensor* matrix, wrk_matrix** out) {
+    float table[16];
+    wrk_nf4_table(table);
+    return wrk_matrix_quant_fp4(matrix, table, out);
+}
+
+int32_t wrk_matrix_release(wrk_matrix* m) {
+    if (!m) return WRK_OK;
+    if (m->refs.fetch_sub(1) == 1) delete m;
+    return WRK_OK;
+}
+
+int32_t wrk_matrix_parts(wrk_matrix* mat, int32_t* kind, wrk_tensor** w, wrk_tensor** m, wrk_tensor** q) {
+    REQ_NN(mat);
+    if (kind) *kind = mat->kind;
+    if (w) *w = mat->w;
+    if (m) *m = mat->m;
+    if (q) *q = mat->q;
+    return WRK_OK;
+}
+
+static int32_t matrix_matmul(wrk_matrix* m, const wrk_view* input, const wrk_view* output, int32_t act, int32_t turbo,
+                             int32_t sparse, wrk_op** out) {
+    REQ_NN(m, input, output, out);
+    wrk_view mv;
+    WRK_TRY(wrk_tensor_as_view(m->w, &mv));
+    switch (m->kind) {
+        case 0:
+            return turbo ? wrk_op_matmul_mat_fp16(&mv, input, output, act, out)
+                         : wrk_op_matmul_vec_fp16(m->w, input, output, act, sparse, out);
+        case 1:
+            return turbo ? wrk_op_matmul_mat_int8(&mv, m->m, input, output, act, out)
+                         : wrk_op_matmul_vec_int8(m->w, m->m, input, output, act, sparse, out);
+        default:
+            return turbo ? wrk_op_matmul_mat_nf4(&mv, m->q, m->m, input, output, act, out)
+                         : wrk_op_matmul_vec_nf4(m->w, m->q, m->m, input, output, act, sparse, out);
+    }
+}
+
+int32_t wrk_matrix_matmul_op(wrk_matrix* m, const wrk_view* input, const wrk_view* output, int32_t act, int32_t turbo,
+                             wrk_op** out) {
+    return matrix_matmul(m, input, output, act, turbo, 0, out);
+}
+
+int32_t wrk_matrix_matmul_op_sparse(wrk_matrix* m, const wrk_view* input, const wrk_view* output, int32_t act,
+                                    int32_t turbo, wrk_op** out) {
+    return matrix_matmul(m, input, output, act, turbo, 1, out);
+}
+
+}  // extern "C"
