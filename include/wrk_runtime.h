@@ -1,0 +1,114 @@
+/* wrk_runtime.h — C ABI of the v5/v6/v7 `run()` jobs: model building with per-layer
+ * quantization, recurrent state, token chunking (`token_chunk_size`, `num_batch`) and the
+ * dispatch → load → submit → back job protocol of the reference crate.
+ *
+ * Status codes, tensors and ops are those of wrk.h.  Citations are path:line inside
+ * cryscan/web-rwkv.
+ */
+#ifndef WRK_RUNTIME_H
+#define WRK_RUNTIME_H
+
+#include "wrk.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct wrk_model_builder wrk_model_builder; /* `ModelBuilder<R>`, src/runtime/model.rs:137-185 */
+typedef struct wrk_model wrk_model;                 /* `v5::Model` / `v6::Model` / `v7::Model` */
+typedef struct wrk_bundle wrk_bundle;               /* `Bundle<f16>` + its `State`, src/runtime/v6.rs:489-521 */
+typedef struct wrk_rnn_input wrk_rnn_input;         /* `RnnInput`, src/runtime/infer/rnn.rs:194-228 */
+typedef struct wrk_rnn_iter wrk_rnn_iter;           /* `RnnIter`, src/runtime/infer/rnn.rs:274-335 */
+typedef struct wrk_job wrk_job;                     /* `RnnJob`, src/runtime/v6.rs:408-477 */
+
+/* `ModelInfo`, src/runtime/model.rs:24-76 (+ `ModelCustomInfo`: v6 {time_mix, time_decay},
+ * v7 {w, a, g, v}). version is 5, 6 or 7. */
+typedef struct {
+    uint32_t version;
+    uint32_t num_layer;
+    uint32_t num_emb;
+    uint32_t num_hidden;
+    uint32_t num_vocab;
+    uint32_t num_head;
+    uint32_t custom[4];
+} wrk_model_info;
+
+/* ---- ModelBuilder: the `Reader` trait (src/runtime/loader.rs:44-74) is fed tensor by tensor ---- */
+int32_t wrk_model_builder_create(wrk_context* ctx, wrk_model_builder** out); /* ModelBuilder::new */
+int32_t wrk_model_builder_destroy(wrk_model_builder* b);
+/* One safetensors entry: fp16 data, shape outermost-first as stored in the file (a weight of M rows
+ * and K columns is {M, K}).  The bytes are copied. */
+int32_t wrk_model_builder_add_tensor(wrk_model_builder* b, const char* name, const uint64_t* shape, uint32_t ndim,
+                                     const void* data_f16, size_t bytes);
+int32_t wrk_model_builder_quant(wrk_model_builder* b, uint32_t layer, int32_t quant); /* ModelBuilder::quant */
+int32_t wrk_model_builder_rescale(wrk_model_builder* b, uint32_t value);             /* ModelBuilder::rescale */
+int32_t wrk_model_builder_sep(wrk_model_builder* b, uint32_t value);                 /* ModelBuilder::sep */
+/* Loader::info (src/runtime/loader.rs:208-324) on the tensors added so far. */
+int32_t wrk_model_builder_info(wrk_model_builder* b, wrk_model_info* info);
+/* ModelBuilder::build_v5 / build_v6 / build_v7 (src/runtime/v5.rs:922-1082, v6.rs:995-1172,
+ * v7.rs:1038-1226), chosen by the version Loader::info finds. */
+int32_t wrk_model_builder_build(wrk_model_builder* b, wrk_model** out);
+
+int32_t wrk_model_info_get(const wrk_model* m, wrk_model_info* info);
+int32_t wrk_model_retain(wrk_model* m);
+int32_t wrk_model_release(wrk_model* m);
+/* A layer's matrix by field name ("att.w_k", "att.w_v", "att.w_r", "att.w_g", "att.w_o", "ffn.w_k",
+ * "ffn.w_v", "ffn.w_r"; layer = UINT32_MAX with "head.w").  Borrowed: valid while the model lives. */
+int32_t wrk_model_matrix(wrk_model* m, uint32_t layer, const char* name, wrk_matrix** out);
+
+/* ---- Bundle + State (src/runtime/model.rs:78-120, src/runtime/v6.rs:142-266, 499-521) ---- */
+int32_t wrk_bundle_create(wrk_model* model, uint32_t num_batch, wrk_bundle** out); /* Bundle::<f16>::new */
+int32_t wrk_bundle_release(wrk_bundle* b);
+/* Cursor format uploaded with every job: 0 (default) = three u32 per token, exact for any run length;
+ * 1 = the reference's packed u32 (8-bit batch, 16-bit token, 8-bit len: src/tensor/mod.rs:53-60). */
+int32_t wrk_bundle_set_packed_cursors(wrk_bundle* b, int32_t packed);
+/* Build jobs as CUDA graphs (default 1) or as plain launch lists (0). */
+int32_t wrk_bundle_set_use_graph(wrk_bundle* b, int32_t use_graph);
+/* 1 (default): jobs may use fused kernels in place of runs of reference ops; 0: one launch per
+ * reference op, every intermediate tensor materialised with the reference's dtypes. */
+int32_t wrk_bundle_set_fused(wrk_bundle* b, int32_t fused);
+int32_t wrk_state_num_batch(wrk_bundle* b, uint32_t* num_batch);                 /* State::num_batch */
+int32_t wrk_state_init_shape(wrk_bundle* b, uint32_t shape[4]);                  /* State::init_shape */
+int32_t wrk_state_load(wrk_bundle* b, const float* host, size_t bytes, uint32_t batch); /* State::load */
+int32_t wrk_state_back(wrk_bundle* b, uint32_t batch, float* host, size_t bytes);       /* State::back */
+/* The per-layer state tensor [C, S + 2, num_batch] (borrowed), as State::att / State::ffn slice it. */
+int32_t wrk_state_layer(wrk_bundle* b, uint32_t layer, wrk_tensor** out);
+
+/* ---- RnnInput / RnnIter / RnnInfo::redirect (src/runtime/infer/rnn.rs) ---- */
+int32_t wrk_rnn_input_create(uint32_t num_batch, uint32_t token_chunk_size, wrk_rnn_input** out); /* RnnInput::new */
+int32_t wrk_rnn_input_destroy(wrk_rnn_input* in);
+int32_t wrk_rnn_input_set_option(wrk_rnn_input* in, uint32_t batch, int32_t option);
+int32_t wrk_rnn_input_append(wrk_rnn_input* in, uint32_t batch, const uint32_t* tokens, size_t count); /* RnnInputBatch::append */
+int32_t wrk_rnn_input_token_chunk_size(const wrk_rnn_input* in, uint32_t* size);
+int32_t wrk_rnn_input_num_token(const wrk_rnn_input* in, uint64_t* count);
+int32_t wrk_rnn_input_remaining(const wrk_rnn_input* in, uint32_t batch, uint64_t* count);
+int32_t wrk_rnn_input_step(wrk_rnn_input* in);                                   /* JobInput::step */
+/* `(&input).into_iter()` and `RnnIter::next`: per batch the token count of the next job and its
+ * Option<RnnOption> (WRK_RNN_NONE = None). */
+int32_t wrk_rnn_iter_create(const wrk_rnn_input* in, wrk_rnn_iter** out);
+int32_t wrk_rnn_iter_next(wrk_rnn_iter* it, uint32_t* lens, int32_t* options);
+int32_t wrk_rnn_iter_destroy(wrk_rnn_iter* it);
+/* RnnInfo::redirect: headers (capacity = total tokens), and per batch the [start, end) ranges in the
+ * input and output tensors (2 * num_batch entries each). */
+int32_t wrk_rnn_redirect(const uint32_t* lens, const int32_t* options, uint32_t num_batch, uint32_t* headers,
+                         uint32_t* num_headers, uint32_t* inputs, uint32_t* outputs);
+
+/* ---- Dispatcher / Job (src/runtime/mod.rs:36-58, src/runtime/v6.rs:408-477, 583-697) ---- */
+int32_t wrk_bundle_dispatch(wrk_bundle* b, const uint32_t* lens, const int32_t* options, wrk_job** out);
+/* Job::load: the chunk's tokens, batch after batch (sum(lens) entries). */
+int32_t wrk_job_load(wrk_job* job, const uint32_t* tokens, size_t count);
+int32_t wrk_job_submit(wrk_job* job);
+/* Job::back: waits, copies the [num_vocab_padded, num_header] f32 logits to `logits` (capacity in
+ * floats) and reports per batch the [start, end) header rows (2 * num_batch entries). */
+int32_t wrk_job_back(wrk_job* job, float* logits, size_t capacity, uint32_t* outputs, uint32_t* num_headers);
+int32_t wrk_job_num_kernels(const wrk_job* job, uint64_t* count);
+int32_t wrk_job_release(wrk_job* job);
+
+/* SimpleRuntime::infer (src/runtime/mod.rs:237-262): next chunk → dispatch → load → submit → back →
+ * step.  Returns WRK_ERR_INPUT_EXHAUSTED when no token is left. */
+int32_t wrk_runtime_infer(wrk_bundle* b, wrk_rnn_input* in, float* logits, size_t capacity, uint32_t* outputs,
+                          uint32_t* num_headers);
+#ifdef __cplusplus
+}
+#endif
+#endif /* WRK_RUNTIME_H */

@@ -20,7 +20,8 @@ def assert_close(got, want, what="", max_abs=MAX_ABS, min_cos=MIN_COS):
     want = np.asarray(want, dtype=np.float64)
     assert got.shape == want.shape, f"{what}: shape {got.shape} vs {want.shape}"
     assert np.isfinite(got).all(), f"{what}: non-finite values"
-    err = float(np.max(np.abs(got - want))) if got.size else 0.0
+    # absolute for values up to 1, relative above (an fp16 result of magnitude 24 has an ulp of 0.016)
+    err = float(np.max(np.abs(got - want) / np.maximum(1.0, np.abs(want)))) if got.size else 0.0
     cos = cosine(got, want)
     assert err <= max_abs, f"{what}: max-abs {err:.4g} > {max_abs}"
     assert cos >= min_cos, f"{what}: cosine {cos:.6f} < {min_cos}"
