@@ -1,0 +1,174 @@
+"""End-to-end run() jobs (v5 / v6 / v7) against the full-model CPU oracle: packed weights bit for
+bit, logits and recurrent state within max-abs 2e-2 / cosine >= 0.9995, across chunked prefill,
+mixed batches and decode.  The reference has no model-level test; the oracle restates its op lists.
+"""
+import importlib
+
+import numpy as np
+import pytest
+
+from oracle import model as omodel
+from oracle import oracle
+from tests.util import assert_close
+
+pytestmark = pytest.mark.gpu
+
+rt = importlib.import_module("web-rwkv_b200.runtime")
+synth = importlib.import_module("web-rwkv_b200.synth")
+LAST, FULL, NONE = 0, 1, 2
+
+
+def _build(ctx, config, quant, seed=1000, num_layer=None):
+    tensors = synth.make_model(config, seed=seed, num_layer=num_layer)
+    model = rt.ModelBuilder(ctx).add_tensors(tensors).quant(quant).build()
+    ref = omodel.OracleModel(tensors, quant)
+    return tensors, model, ref
+
+
+def _drive(bundle, ref, batches, chunk, wide=True):
+    """Runs the same RnnInput through the CUDA runtime and the oracle; yields per-job logits pairs."""
+    nb = len(batches)
+    inp = rt.RnnInput(batches, chunk)
+    remaining = [list(t) for t, _ in batches]
+    state = ref.init_state(nb)
+    pairs = []
+    while inp.num_token():
+        info = inp.iter().next()
+        got = [g.copy() for g in bundle.infer(inp)]
+        want = ref.run(state, remaining, info, wide=wide)
+        remaining = [r[l:] for r, (l, _) in zip(remaining, info)]
+        pairs.append((info, got, want))
+    return pairs, state
+
+
+def _check(pairs, bundle, state):
+    for info, got, want in pairs:
+        for b, (g, w) in enumerate(zip(got, want)):
+            assert g.shape == w.shape, (info, b, g.shape, w.shape)
+            if g.size:
+                assert_close(g, w, f"logits batch {b} job {info}")
+    for b in range(bundle.num_batch):
+        got_state = bundle.state_back(b)
+        want_state = np.stack([s[b] for s in state])
+        assert_close(got_state, want_state, f"state batch {b}")
+
+
+@pytest.mark.parametrize("config,quant", [
+    ("v6-tiny", {0: 1, 1: 2}),      # layer 0 Int8, layer 1 NF4, layer 2 fp16
+    ("v5-tiny", {0: 1, 1: 2}),
+    ("v7-tiny", {0: 1, 1: 2}),
+])
+def test_mixed_batches_chunked_prefill_then_decode(ctx, config, quant):
+    rng = np.random.default_rng(2001)
+    tensors, model, ref = _build(ctx, config, quant)
+    bundle = rt.Bundle(model, 4)
+    V = model.info.num_vocab
+    batches = [(rng.integers(0, V - 1, 70).tolist(), LAST), (rng.integers(0, V - 1, 1).tolist(), LAST), ([], FULL),
+               (rng.integers(0, V - 1, 37).tolist(), FULL)]
+    pairs, state = _drive(bundle, ref, batches, 64)
+    assert len(pairs) >= 2
+    _check(pairs, bundle, state)
+
+
+@pytest.mark.parametrize("config", ["v6-tiny", "v5-tiny", "v7-tiny"])
+@pytest.mark.parametrize("fused", [False, True])
+def test_decode_loop(ctx, config, fused):
+    rng = np.random.default_rng(2002)
+    tensors, model, ref = _build(ctx, config, {0: 1, 1: 1, 2: 1})
+    bundle = rt.Bundle(model, 1)
+    bundle.set_fused(fused)
+    V = model.info.num_vocab
+    prompt = rng.integers(0, V - 1, 9).tolist()
+    state = ref.init_state(1)
+    inp = rt.RnnInput([(prompt, LAST)], 32)
+    got = bundle.infer(inp)[0].copy()
+    want = ref.run(state, [prompt], [(len(prompt), LAST)])[0]
+    assert_close(got, want, "prompt logits")
+    for step in range(6):  # greedy decode on the oracle's token so both sides see the same input
+        tok = int(np.argmax(want[-1]))
+        inp.append(0, [tok])
+        got = bundle.infer(inp)[0].copy()
+        want = ref.run(state, [[tok]], [(1, LAST)])[0]
+        assert_close(got, want, f"decode step {step}")
+    assert_close(bundle.state_back(0), np.stack([s[0] for s in state]), "state")
+
+
+def test_packed_bytes_and_scales_match_the_oracle(ctx):
+    tensors, model, ref = _build(ctx, "v6-tiny", {0: 1, 1: 2})
+    names = {"att.w_k": "w_k", "att.w_v": "w_v", "att.w_r": "w_r", "att.w_g": "w_g", "att.w_o": "w_o",
+             "ffn.w_k": "ffn_k", "ffn.w_v": "ffn_v", "ffn.w_r": "ffn_r"}
+    for layer in (0, 1):
+        for cname, oname in names.items():
+            kind, w, m, q = model.matrix_parts(layer, cname)
+            want = ref.layers[layer][oname]
+            assert kind == want.kind
+            assert np.array_equal(w.reshape(want.w.shape), want.w), (layer, cname)
+            assert np.array_equal(m.reshape(-1).view(np.uint16), want.scale.view(np.uint16)), (layer, cname)
+    kind, w, m, q = model.matrix_parts(None, "head.w")
+    assert kind == 0 and np.array_equal(w.reshape(tensors["head.weight"].shape), tensors["head.weight"])
+
+
+def test_rescale_discount_is_applied_before_quantization(ctx):
+    # rescale = 2: layers 2.. have output / ffn value weights halved in fp16 *before* packing
+    tensors = synth.make_model("v6-tiny", seed=5)
+    model = rt.ModelBuilder(ctx).add_tensors(tensors).quant({0: 1, 1: 1, 2: 1}).rescale(2).build()
+    ref = omodel.OracleModel(tensors, {0: 1, 1: 1, 2: 1}, rescale=2)
+    for cname, oname in (("att.w_o", "w_o"), ("ffn.w_v", "ffn_v"), ("att.w_k", "w_k")):
+        kind, w, m, q = model.matrix_parts(2, cname)
+        assert np.array_equal(w.reshape(ref.layers[2][oname].w.shape), ref.layers[2][oname].w)
+        assert np.array_equal(m.reshape(-1).view(np.uint16), ref.layers[2][oname].scale.view(np.uint16))
+    bundle = rt.Bundle(model, 1)
+    rng = np.random.default_rng(1)
+    prompt = rng.integers(0, 511, 33).tolist()
+    pairs, state = _drive(bundle, ref, [(prompt, FULL)], 32)
+    _check(pairs, bundle, state)
+
+
+def test_packed_cursors_reproduce_the_reference_wrap(ctx):
+    # a single sequence receiving 256 tokens in one job: packed len wraps to 0 and neither carry row is
+    # written (the reference's behaviour); the wide cursor form carries them
+    tensors, model, ref = _build(ctx, "v6-tiny", {})
+    rng = np.random.default_rng(3)
+    prompt = rng.integers(0, 511, 256).tolist()
+    for packed in (True, False):
+        bundle = rt.Bundle(model, 1)
+        bundle.set_packed_cursors(packed)
+        pairs, state = _drive(bundle, ref, [(prompt, LAST)], 256, wide=not packed)
+        _check(pairs, bundle, state)
+        carry = bundle.state_back(0)[:, 0, :]
+        assert (carry == 0).all() == packed
+
+
+def test_state_load_back_and_errors(ctx):
+    tensors, model, ref = _build(ctx, "v6-tiny", {})
+    bundle = rt.Bundle(model, 2)
+    shape = bundle.state_shape()
+    assert shape == [256, 66, 3, 1]
+    rng = np.random.default_rng(4)
+    st = rng.standard_normal((3, 66, 256)).astype(np.float32)
+    bundle.state_load(st, 1)
+    assert np.array_equal(bundle.state_back(1), st)
+    assert (bundle.state_back(0) == 0).all()
+    wrk = importlib.import_module("web-rwkv_b200")
+    with pytest.raises(wrk.WrkError) as e:
+        bundle.state_load(st, 2)
+    assert e.value.status == -7
+    with pytest.raises(wrk.WrkError) as e:
+        bundle.infer(rt.RnnInput([([], LAST), ([], LAST)], 32))
+    assert e.value.status == -30
+    with pytest.raises(wrk.WrkError) as e:
+        rt.ModelBuilder(ctx).add_tensors({"emb.weight": np.zeros((8, 64), np.float16)}).build()
+    assert e.value.status in (-20, -21)
+
+
+def test_config1_v6_0p1b_int8_256_tokens_chunk_32(ctx):
+    # BASELINE config 1: n_embd 768, 12 layers, FFN 2688, vocab 65536, all layers Int8, one sequence of
+    # 256 uniform-random tokens, token_chunk_size 32, num_batch 1
+    rng = np.random.default_rng(2001)
+    quant = {i: 1 for i in range(12)}
+    tensors, model, ref = _build(ctx, "v6-0.1b", quant, seed=1001)
+    bundle = rt.Bundle(model, 1)
+    prompt = rng.integers(0, 65535, 256).tolist()
+    pairs, state = _drive(bundle, ref, [(prompt, LAST)], 32)
+    assert len(pairs) == 8 and pairs[-1][1][0].shape == (1, 65536)
+    _check(pairs, bundle, state)

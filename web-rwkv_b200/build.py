@@ -20,6 +20,9 @@ SOURCES = [
     "kernels/matmul.cu",
     "kernels/wkv.cu",
     "kernels/support.cu",
+    "runtime/rnn.cpp",
+    "runtime/model.cpp",
+    "runtime/bundle.cpp",
 ]
 
 NVCC_FLAGS = [

@@ -1,0 +1,714 @@
+// Bundle, State and the dispatch → load → submit → back job protocol of the v5/v6/v7 runtimes.
+//
+// dispatch() builds, per job shape, the same operator list the reference builds in
+// dispatch_layer / dispatch_header (src/runtime/v5.rs:656-920, v6.rs:701-992, v7.rs:716-1036) with the
+// same buffer dtypes (Bundle<f16>), encodes it once (optionally as a CUDA graph: the analogue of the
+// reference's pre-encoded command buffers) and caches it by (num_token, header rows).  load() gathers
+// the embeddings on the host like the reference (v6.rs:423-459) into pinned memory and uploads them
+// with the cursors; back() reads the [vocab, num_header] fp32 logits into the caller's buffer.
+// Hooks (v6.rs:366-406) are not built.
+#include <cstring>
+#include <list>
+
+#include "runtime.h"
+
+using namespace wrk;
+using namespace wrk::rt;
+
+namespace {
+
+constexpr float LN_EPS = 1.0e-5f, GN_EPS = 64.0e-5f, L2_EPS = 1.0e-12f;
+
+struct Buffers {
+    std::unordered_map<std::string, TensorH> t;
+    wrk_tensor* operator[](const char* name) const { return t.at(name).p; }
+};
+
+struct CachedJob {
+    std::shared_ptr<Buffers> buffer, header;
+    RnnRedirect redirect;
+    wrk_commands* commands = nullptr;
+    uint32_t num_token = 0, num_header = 0;
+    uint64_t tick = 0;
+    ~CachedJob() {
+        if (commands) wrk_commands_release(commands);
+    }
+};
+
+}  // namespace
+
+struct wrk_bundle {
+    std::atomic<int> refs{1};
+    wrk_model* model = nullptr;
+    uint32_t num_batch = 0;
+    std::vector<TensorH> state;  // per layer f32 [C, S + 2, num_batch]
+    bool packed_cursors = false, use_graph = true, fused = true;
+    std::map<uint32_t, std::shared_ptr<Buffers>> buffers, headers;
+    std::map<std::vector<uint32_t>, std::shared_ptr<CachedJob>> jobs;
+    uint64_t tick = 0;
+    // pinned staging
+    uint16_t* stage_input = nullptr;
+    uint32_t* stage_cursors = nullptr;
+    size_t stage_tokens = 0;
+    std::mutex mutex;
+    ~wrk_bundle() {
+        jobs.clear();
+        if (stage_input) cudaFreeHost(stage_input);
+        if (stage_cursors) cudaFreeHost(stage_cursors);
+        state.clear();
+        if (model) wrk_model_release(model);
+    }
+};
+
+struct wrk_job {
+    wrk_bundle* bundle = nullptr;
+    std::shared_ptr<CachedJob> job;
+    RnnInfo info;
+};
+
+namespace {
+
+struct OpList {
+    std::vector<wrk_op*> ops;
+    ~OpList() {
+        for (auto o : ops) wrk_op_release(o);
+    }
+};
+
+#define ADD(call)                   \
+    do {                            \
+        wrk_op* _o = nullptr;       \
+        WRK_TRY(call);              \
+        ops.ops.push_back(_o);      \
+    } while (0)
+
+wrk_view V(wrk_tensor* t) {
+    wrk_view v;
+    wrk_tensor_as_view(t, &v);
+    return v;
+}
+wrk_view Vz(wrk_tensor* t, uint32_t z) {  // t.view(.., .., z, ..)
+    wrk_view v = V(t);
+    v.shape[2] = 1;
+    v.offset[2] = z;
+    return v;
+}
+wrk_view Vy(wrk_tensor* t, uint32_t y0, uint32_t y1) {  // t.view(.., y0..y1, .., ..)
+    wrk_view v = V(t);
+    v.shape[1] = y1 - y0;
+    v.offset[1] = y0;
+    return v;
+}
+
+int32_t reshape(wrk_tensor* t, uint32_t x, uint32_t y, uint32_t z, uint32_t w, TensorH* out) {
+    const uint32_t s[4] = {x, y, z, w};
+    wrk_tensor* r = nullptr;
+    WRK_TRY(wrk_tensor_reshape(t, s, &r));
+    *out = TensorH(r);
+    return WRK_OK;
+}
+
+int32_t alloc(wrk_context* ctx, Buffers& b, const char* name, int dtype, uint32_t x, uint32_t y, uint32_t z = 1) {
+    const uint32_t s[4] = {x, y, z, 1};
+    wrk_tensor* t = nullptr;
+    WRK_TRY(wrk_tensor_create(ctx, (wrk_dtype)dtype, s, &t));
+    b.t[name] = TensorH(t);
+    return WRK_OK;
+}
+
+// Runtime<f16>::new of each version (v5.rs:258-315, v6.rs:268-345, v7.rs:279-363)
+int32_t make_runtime(wrk_bundle* bd, uint32_t T, std::shared_ptr<Buffers>* out) {
+    const wrk_model_info& info = bd->model->info;
+    wrk_context* ctx = bd->model->ctx;
+    auto b = std::make_shared<Buffers>();
+    const uint32_t C = info.num_emb, F = info.num_hidden;
+    const int H16 = WRK_F16, F32 = WRK_F32;
+    WRK_TRY(alloc(ctx, *b, "cursors", WRK_U32, bd->packed_cursors ? T : 3 * T, 1));
+    WRK_TRY(alloc(ctx, *b, "input", H16, C, T));
+    WRK_TRY(alloc(ctx, *b, "x", H16, C, T));
+    if (info.version == 7) {
+        for (auto n : {"att_x", "att_v0", "att_rx", "att_wx", "att_kx", "att_vx", "att_ax", "att_gx", "att_r", "att_w",
+                       "att_k", "att_v", "att_a", "att_g", "att_o", "att_kk", "att_vv", "ffn_x", "ffn_kx", "ffn_v"})
+            WRK_TRY(alloc(ctx, *b, n, H16, C, T));
+        WRK_TRY(alloc(ctx, *b, "att_n", H16, C, T, 4));
+        WRK_TRY(alloc(ctx, *b, "aux_w", H16, info.custom[0], T));
+        WRK_TRY(alloc(ctx, *b, "aux_a", H16, info.custom[1], T));
+        WRK_TRY(alloc(ctx, *b, "aux_g", H16, info.custom[2], T));
+        WRK_TRY(alloc(ctx, *b, "aux_v", H16, info.custom[3], T));
+        WRK_TRY(alloc(ctx, *b, "ffn_k", H16, F, T));
+    } else {
+        WRK_TRY(alloc(ctx, *b, "aux_x", F32, C, T));
+        for (auto n : {"att_x", "att_g", "att_o", "ffn_x", "ffn_kx", "ffn_rx", "ffn_v", "ffn_r"})
+            WRK_TRY(alloc(ctx, *b, n, H16, C, T));
+        for (auto n : {"att_k", "att_v", "att_r"}) WRK_TRY(alloc(ctx, *b, n, F32, C, T));
+        WRK_TRY(alloc(ctx, *b, "ffn_k", H16, F, T));
+        if (info.version == 6) {
+            WRK_TRY(alloc(ctx, *b, "att_xx", H16, C, T));
+            WRK_TRY(alloc(ctx, *b, "att_sx", H16, C, T, 5));
+            WRK_TRY(alloc(ctx, *b, "att_w", H16, info.custom[1], T));
+            WRK_TRY(alloc(ctx, *b, "time_mix_x", H16, info.custom[0], 5, T));
+            WRK_TRY(alloc(ctx, *b, "time_mix_t", H16, info.custom[0], T, 5));
+            WRK_TRY(alloc(ctx, *b, "time_mix", H16, C, T, 5));
+            WRK_TRY(alloc(ctx, *b, "time_decay", F32, C, T));
+        } else {
+            for (auto n : {"att_kx", "att_vx", "att_rx", "att_gx"}) WRK_TRY(alloc(ctx, *b, n, H16, C, T));
+        }
+    }
+    *out = b;
+    return WRK_OK;
+}
+
+int32_t make_header(wrk_bundle* bd, uint32_t num_header, std::shared_ptr<Buffers>* out) {
+    const wrk_model_info& info = bd->model->info;
+    auto b = std::make_shared<Buffers>();
+    WRK_TRY(alloc(bd->model->ctx, *b, "head_x", WRK_F16, info.num_emb, num_header));
+    uint32_t vocab = 0;
+    {
+        uint32_t s[4];
+        wrk_tensor* w = nullptr;
+        wrk_matrix_parts(bd->model->head_w, nullptr, &w, nullptr, nullptr);
+        wrk_tensor_shape(w, s);
+        vocab = s[1];
+    }
+    WRK_TRY(alloc(bd->model->ctx, *b, "head_o", WRK_F32, vocab, num_header));
+    *out = b;
+    return WRK_OK;
+}
+
+int32_t matmul(OpList& ops, wrk_matrix* m, wrk_view in, wrk_view out, int32_t act, bool turbo, bool sparse = false) {
+    wrk_op* _o = nullptr;
+    if (sparse) WRK_TRY(wrk_matrix_matmul_op_sparse(m, &in, &out, act, turbo, &_o));
+    else WRK_TRY(wrk_matrix_matmul_op(m, &in, &out, act, turbo, &_o));
+    ops.ops.push_back(_o);
+    return WRK_OK;
+}
+
+int32_t token_shift(OpList& ops, wrk_tensor* cursors, wrk_view mix, wrk_view state, wrk_tensor* in, wrk_tensor* out,
+                    bool reversed) {
+    ADD(wrk_op_token_shift(cursors, &mix, &state, in, out, reversed, &_o));
+    return WRK_OK;
+}
+
+int32_t blit(OpList& ops, wrk_view in, wrk_view out) {
+    ADD(wrk_op_blit(&in, &out, &_o));
+    return WRK_OK;
+}
+
+int32_t add(OpList& ops, wrk_view in, wrk_view out, int32_t act_out = WRK_ACT_NONE) {
+    ADD(wrk_op_add_activate(&in, &out, WRK_ACT_NONE, WRK_ACT_NONE, act_out, &_o));
+    return WRK_OK;
+}
+
+// State::att / State::ffn, v6.rs:187-197
+wrk_view state_att(wrk_bundle* bd, uint32_t layer, uint32_t S) { return Vy(bd->state[layer], 0, S + 1); }
+wrk_view state_ffn(wrk_bundle* bd, uint32_t layer, uint32_t S) { return Vy(bd->state[layer], S + 1, S + 2); }
+
+// dispatch_layer of v5 (v5.rs:656-885) and v6 (v6.rs:701-958)
+int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, uint32_t T) {
+    const wrk_model_info& info = bd->model->info;
+    const Layer& L = bd->model->layers[index];
+    const uint32_t C = info.num_emb, S = C / info.num_head;
+    const bool turbo = T % WRK_MIN_TOKEN_CHUNK_SIZE == 0;
+    const bool v6 = info.version == 6;
+    wrk_tensor* cursors = B["cursors"];
+
+    TensorH time_first, time_decay, aux_x, att_k, att_v, att_r;
+    WRK_TRY(reshape(L.time_first, S, WRK_DIM_AUTO, 1, 1, &time_first));
+    if (v6) WRK_TRY(reshape(B["time_decay"], S, WRK_DIM_AUTO, T, 1, &time_decay));
+    else WRK_TRY(reshape(L.time_decay, S, WRK_DIM_AUTO, 1, 1, &time_decay));
+    WRK_TRY(reshape(B["aux_x"], S, WRK_DIM_AUTO, T, 1, &aux_x));
+    WRK_TRY(reshape(B["att_k"], S, WRK_DIM_AUTO, T, 1, &att_k));
+    WRK_TRY(reshape(B["att_v"], S, WRK_DIM_AUTO, T, 1, &att_v));
+    WRK_TRY(reshape(B["att_r"], S, WRK_DIM_AUTO, T, 1, &att_r));
+
+    WRK_TRY(blit(ops, V(B["x"]), V(B["att_x"])));
+    ADD(wrk_op_layer_norm(L.att_ln.w, L.att_ln.b, B["att_x"], LN_EPS, &_o));
+    if (v6) {
+        TensorH time_mix_x;
+        WRK_TRY(reshape(B["time_mix_x"], WRK_DIM_AUTO, T, 1, 1, &time_mix_x));
+        WRK_TRY(token_shift(ops, cursors, V(L.time_mix_x), state_att(bd, index, S), B["att_x"], B["att_xx"], true));
+        WRK_TRY(matmul(ops, L.time_mix_w1, V(B["att_xx"]), V(time_mix_x), WRK_ACT_TANH, turbo));
+        {
+            const wrk_view in = V(B["time_mix_x"]), out = V(B["time_mix_t"]);
+            ADD(wrk_op_transpose(&in, &out, &_o));
+        }
+        WRK_TRY(matmul(ops, L.time_mix_w2, V(B["time_mix_t"]), V(B["time_mix"]), WRK_ACT_NONE, turbo));
+        WRK_TRY(add(ops, V(L.time_mix), V(B["time_mix"])));
+        WRK_TRY(token_shift(ops, cursors, V(B["time_mix"]), state_att(bd, index, S), B["att_x"], B["att_sx"], true));
+        WRK_TRY(matmul(ops, L.att_w_k, Vz(B["att_sx"], 1), V(B["att_k"]), WRK_ACT_NONE, turbo));
+        WRK_TRY(matmul(ops, L.att_w_v, Vz(B["att_sx"], 2), V(B["att_v"]), WRK_ACT_NONE, turbo));
+        WRK_TRY(matmul(ops, L.att_w_r, Vz(B["att_sx"], 3), V(B["att_r"]), WRK_ACT_NONE, turbo));
+        WRK_TRY(matmul(ops, L.att_w_g, Vz(B["att_sx"], 4), V(B["att_g"]), WRK_ACT_NONE, turbo));
+        WRK_TRY(matmul(ops, L.time_decay_w1, Vz(B["att_sx"], 0), V(B["att_w"]), WRK_ACT_TANH, turbo));
+        WRK_TRY(matmul(ops, L.time_decay_w2, V(B["att_w"]), V(B["time_decay"]), WRK_ACT_NONE, turbo));
+        WRK_TRY(add(ops, V(L.time_decay), V(B["time_decay"])));
+        {
+            const wrk_view td = V(B["time_decay"]);
+            ADD(wrk_op_activate(&td, WRK_ACT_STABLE_EXP, &_o));
+        }
+    } else {
+        WRK_TRY(token_shift(ops, cursors, V(L.time_mix_k), state_att(bd, index, S), B["att_x"], B["att_kx"], false));
+        WRK_TRY(token_shift(ops, cursors, V(L.time_mix_v), state_att(bd, index, S), B["att_x"], B["att_vx"], false));
+        WRK_TRY(token_shift(ops, cursors, V(L.time_mix_r), state_att(bd, index, S), B["att_x"], B["att_rx"], false));
+        WRK_TRY(token_shift(ops, cursors, V(L.time_mix_g), state_att(bd, index, S), B["att_x"], B["att_gx"], false));
+        WRK_TRY(matmul(ops, L.att_w_k, V(B["att_kx"]), V(B["att_k"]), WRK_ACT_NONE, turbo));
+        WRK_TRY(matmul(ops, L.att_w_v, V(B["att_vx"]), V(B["att_v"]), WRK_ACT_NONE, turbo));
+        WRK_TRY(matmul(ops, L.att_w_r, V(B["att_rx"]), V(B["att_r"]), WRK_ACT_NONE, turbo));
+        WRK_TRY(matmul(ops, L.att_w_g, V(B["att_gx"]), V(B["att_g"]), WRK_ACT_NONE, turbo));
+    }
+    WRK_TRY(blit(ops, V(B["att_x"]), V(B["aux_x"])));
+    {
+        const wrk_view st = state_att(bd, index, S);
+        if (v6) ADD(wrk_op_time_mix_v6(cursors, time_decay, time_first, &st, att_k, att_v, att_r, aux_x, &_o));
+        else ADD(wrk_op_time_mix_v5(cursors, time_decay, time_first, &st, att_k, att_v, att_r, aux_x, &_o));
+    }
+    ADD(wrk_op_group_norm(L.gn.w, L.gn.b, aux_x, GN_EPS, &_o));
+    WRK_TRY(blit(ops, V(B["aux_x"]), V(B["att_x"])));
+    {
+        const wrk_view g = V(B["att_g"]), x = V(B["att_x"]);
+        ADD(wrk_op_mul_activate(&g, &x, WRK_ACT_SILU, WRK_ACT_NONE, WRK_ACT_NONE, &_o));
+    }
+    WRK_TRY(matmul(ops, L.att_w_o, V(B["att_x"]), V(B["att_o"]), WRK_ACT_NONE, turbo));
+    WRK_TRY(add(ops, V(B["att_o"]), V(B["x"])));
+
+    WRK_TRY(blit(ops, V(B["x"]), V(B["ffn_x"])));
+    ADD(wrk_op_layer_norm(L.ffn_ln.w, L.ffn_ln.b, B["ffn_x"], LN_EPS, &_o));
+    WRK_TRY(token_shift(ops, cursors, V(L.ffn_time_mix_k), state_ffn(bd, index, S), B["ffn_x"], B["ffn_kx"], v6));
+    WRK_TRY(token_shift(ops, cursors, V(L.ffn_time_mix_r), state_ffn(bd, index, S), B["ffn_x"], B["ffn_rx"], v6));
+    WRK_TRY(matmul(ops, L.ffn_w_k, V(B["ffn_kx"]), V(B["ffn_k"]), WRK_ACT_SQUARED_RELU, turbo));
+    WRK_TRY(matmul(ops, L.ffn_w_v, V(B["ffn_k"]), V(B["ffn_v"]), WRK_ACT_NONE, turbo, true));
+    WRK_TRY(matmul(ops, L.ffn_w_r, V(B["ffn_rx"]), V(B["ffn_r"]), WRK_ACT_NONE, turbo));
+    {
+        const wrk_view st = state_ffn(bd, index, S);
+        ADD(wrk_op_channel_mix(cursors, &st, B["ffn_r"], B["ffn_v"], B["ffn_x"], &_o));
+    }
+    WRK_TRY(add(ops, V(B["ffn_x"]), V(B["x"])));
+    if ((index + 1) % bd->model->rescale == 0) ADD(wrk_op_affine(B["x"], 0.5f, 0.0f, &_o));
+    return WRK_OK;
+}
+
+// dispatch_layer of v7 (v7.rs:716-1007)
+int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, uint32_t T) {
+    const wrk_model_info& info = bd->model->info;
+    const Layer& L = bd->model->layers[index];
+    const uint32_t C = info.num_emb, S = C / info.num_head;
+    const bool turbo = T % WRK_MIN_TOKEN_CHUNK_SIZE == 0;
+    wrk_tensor* cursors = B["cursors"];
+
+    TensorH att_kk, att_x, att_r, att_w, att_n;
+    WRK_TRY(reshape(B["att_kk"], S, WRK_DIM_AUTO, T, 1, &att_kk));
+    WRK_TRY(reshape(B["att_x"], S, WRK_DIM_AUTO, T, 1, &att_x));
+    WRK_TRY(reshape(B["att_r"], S, WRK_DIM_AUTO, T, 1, &att_r));
+    WRK_TRY(reshape(B["att_w"], S, WRK_DIM_AUTO, T, 1, &att_w));
+    WRK_TRY(reshape(B["att_n"], S, WRK_DIM_AUTO, T, 4, &att_n));
+
+    WRK_TRY(blit(ops, V(B["x"]), V(B["att_x"])));
+    ADD(wrk_op_layer_norm(L.att_ln.w, L.att_ln.b, B["att_x"], LN_EPS, &_o));
+    const wrk_view sa = state_att(bd, index, S);
+    WRK_TRY(token_shift(ops, cursors, V(L.x_r), sa, B["att_x"], B["att_rx"], true));
+    WRK_TRY(token_shift(ops, cursors, V(L.x_w), sa, B["att_x"], B["att_wx"], true));
+    WRK_TRY(token_shift(ops, cursors, V(L.x_k), sa, B["att_x"], B["att_kx"], true));
+    WRK_TRY(token_shift(ops, cursors, V(L.x_v), sa, B["att_x"], B["att_vx"], true));
+    WRK_TRY(token_shift(ops, cursors, V(L.x_a), sa, B["att_x"], B["att_ax"], true));
+    WRK_TRY(token_shift(ops, cursors, V(L.x_g), sa, B["att_x"], B["att_gx"], true));
+    WRK_TRY(matmul(ops, L.att_w_r, V(B["att_rx"]), V(B["att_r"]), WRK_ACT_NONE, turbo));
+    WRK_TRY(matmul(ops, L.att_w_k, V(B["att_kx"]), V(B["att_k"]), WRK_ACT_NONE, turbo));
+    WRK_TRY(matmul(ops, L.att_w_v, V(B["att_vx"]), V(B["att_v"]), WRK_ACT_NONE, turbo));
+    WRK_TRY(matmul(ops, L.w1, V(B["att_wx"]), V(B["aux_w"]), WRK_ACT_TANH, turbo));
+    WRK_TRY(matmul(ops, L.w2, V(B["aux_w"]), V(B["att_w"]), WRK_ACT_NONE, turbo));
+    WRK_TRY(add(ops, V(L.w0), V(B["att_w"])));
+    WRK_TRY(matmul(ops, L.a1, V(B["att_ax"]), V(B["aux_a"]), WRK_ACT_NONE, turbo));
+    WRK_TRY(matmul(ops, L.a2, V(B["aux_a"]), V(B["att_a"]), WRK_ACT_NONE, turbo));
+    WRK_TRY(add(ops, V(L.a0), V(B["att_a"]), WRK_ACT_SIGMOID));
+    WRK_TRY(matmul(ops, L.g1, V(B["att_gx"]), V(B["aux_g"]), WRK_ACT_SIGMOID, turbo));
+    WRK_TRY(matmul(ops, L.g2, V(B["aux_g"]), V(B["att_g"]), WRK_ACT_NONE, turbo));
+    WRK_TRY(blit(ops, V(B["att_k"]), V(B["att_kk"])));
+    {
+        const wrk_view kk = V(L.k_k), o = V(B["att_kk"]);
+        ADD(wrk_op_mul_activate(&kk, &o, WRK_ACT_NONE, WRK_ACT_NONE, WRK_ACT_NONE, &_o));
+    }
+    ADD(wrk_op_l2_norm(att_kk, L2_EPS, &_o));
+    {
+        const wrk_view a = V(B["att_a"]), k = V(B["att_k"]);
+        ADD(wrk_op_control_k_v7(L.k_a, &a, &k, &_o));
+    }
+    if (index == 0) {
+        WRK_TRY(blit(ops, V(B["att_v"]), V(B["att_v0"])));
+    } else {
+        WRK_TRY(matmul(ops, L.v1, V(B["att_vx"]), V(B["aux_v"]), WRK_ACT_NONE, turbo));
+        WRK_TRY(matmul(ops, L.v2, V(B["aux_v"]), V(B["att_vv"]), WRK_ACT_NONE, turbo));
+        WRK_TRY(add(ops, V(L.v0), V(B["att_vv"]), WRK_ACT_SIGMOID));
+        const wrk_view in = V(B["att_v0"]), out = V(B["att_v"]), f = V(B["att_vv"]);
+        ADD(wrk_op_lerp(&in, &out, &f, 1, &_o));
+    }
+    WRK_TRY(blit(ops, V(B["att_k"]), Vz(B["att_n"], 0)));
+    WRK_TRY(blit(ops, V(B["att_v"]), Vz(B["att_n"], 1)));
+    WRK_TRY(blit(ops, V(B["att_a"]), Vz(B["att_n"], 2)));
+    WRK_TRY(blit(ops, V(B["att_kk"]), Vz(B["att_n"], 3)));
+    ADD(wrk_op_time_mix_v7(cursors, &sa, att_r, att_w, att_n, att_x, &_o));
+    ADD(wrk_op_group_norm(L.gn.w, L.gn.b, att_x, GN_EPS, &_o));
+    ADD(wrk_op_time_first_v7(L.r_k, att_r, att_n, att_x, &_o));
+    {
+        const wrk_view g = V(B["att_g"]), x = V(B["att_x"]);
+        ADD(wrk_op_mul_activate(&g, &x, WRK_ACT_NONE, WRK_ACT_NONE, WRK_ACT_NONE, &_o));
+    }
+    WRK_TRY(matmul(ops, L.att_w_o, V(B["att_x"]), V(B["att_o"]), WRK_ACT_NONE, turbo));
+    WRK_TRY(add(ops, V(B["att_o"]), V(B["x"])));
+
+    WRK_TRY(blit(ops, V(B["x"]), V(B["ffn_x"])));
+    ADD(wrk_op_layer_norm(L.ffn_ln.w, L.ffn_ln.b, B["ffn_x"], LN_EPS, &_o));
+    WRK_TRY(token_shift(ops, cursors, V(L.ffn_x_k), state_ffn(bd, index, S), B["ffn_x"], B["ffn_kx"], true));
+    WRK_TRY(matmul(ops, L.ffn_w_k, V(B["ffn_kx"]), V(B["ffn_k"]), WRK_ACT_SQUARED_RELU, turbo));
+    WRK_TRY(matmul(ops, L.ffn_w_v, V(B["ffn_k"]), V(B["ffn_v"]), WRK_ACT_NONE, turbo, true));
+    {
+        const wrk_view st = state_ffn(bd, index, S);
+        ADD(wrk_op_channel_mix_v7(cursors, &st, B["ffn_v"], B["ffn_x"], &_o));
+    }
+    WRK_TRY(add(ops, V(B["ffn_x"]), V(B["x"])));
+    if ((index + 1) % bd->model->rescale == 0) ADD(wrk_op_affine(B["x"], 0.5f, 0.0f, &_o));
+    return WRK_OK;
+}
+
+// Bundle::dispatch body (v6.rs:586-697) for a job with at least one token.
+int32_t build_job(wrk_bundle* bd, const RnnInfo& info, CachedJob* job) {
+    wrk_model* m = bd->model;
+    const uint32_t T = job->num_token, NH = job->num_header;
+    const Buffers& B = *job->buffer;
+    const Buffers& Hd = *job->header;
+    OpList ops;
+
+    // embed: layer norm on the uploaded rows, then copy into x
+    ADD(wrk_op_layer_norm(m->embed_ln.w, m->embed_ln.b, B["input"], LN_EPS, &_o));
+    WRK_TRY(blit(ops, V(B["input"]), V(B["x"])));
+    for (uint32_t i = 0; i < m->info.num_layer; ++i) {
+        if (m->info.version == 7) WRK_TRY(layer_v7(bd, ops, B, i, T));
+        else WRK_TRY(layer_v56(bd, ops, B, i, T));
+        if ((i + 1) % m->sep == 0) ADD(wrk_op_sep(&_o));
+    }
+    // RnnRedirect::op (rnn.rs:102-133): gather the rows that need logits into head_x
+    wrk_tensor* head_x = nullptr;
+    if (T == 1 || T == NH) {
+        head_x = B["x"];
+    } else {
+        head_x = Hd["head_x"];
+        const auto& h = job->redirect.headers;
+        size_t start = 0, end = 1;
+        while (end <= h.size()) {
+            if (end == h.size() || h[end - 1] + 1 != h[end]) {
+                const uint32_t first = h[start], last = h[end - 1];
+                WRK_TRY(blit(ops, Vy(B["x"], first, last + 1), Vy(Hd["head_x"], (uint32_t)start, (uint32_t)end)));
+                start = end;
+            }
+            ++end;
+        }
+    }
+    if (NH > 0) {
+        ADD(wrk_op_layer_norm(m->head_ln.w, m->head_ln.b, head_x, LN_EPS, &_o));
+        WRK_TRY(matmul(ops, m->head_w, V(head_x), V(Hd["head_o"]), WRK_ACT_NONE, NH % WRK_MIN_TOKEN_CHUNK_SIZE == 0));
+    }
+    wrk_op* list = nullptr;
+    WRK_TRY(wrk_op_list(ops.ops.data(), ops.ops.size(), &list));
+    int32_t s = wrk_encode(m->ctx, list, bd->use_graph ? 1 : 0, &job->commands);
+    wrk_op_release(list);
+    return s;
+}
+
+int32_t ensure_staging(wrk_bundle* bd, size_t tokens) {
+    if (tokens <= bd->stage_tokens) return WRK_OK;
+    wrk_context* ctx = bd->model->ctx;
+    WRK_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (bd->stage_input) cudaFreeHost(bd->stage_input);
+    if (bd->stage_cursors) cudaFreeHost(bd->stage_cursors);
+    bd->stage_input = nullptr;
+    bd->stage_cursors = nullptr;
+    size_t cap = 64;
+    while (cap < tokens) cap *= 2;
+    WRK_CUDA(cudaMallocHost(&bd->stage_input, cap * bd->model->info.num_emb * 2));
+    WRK_CUDA(cudaMallocHost(&bd->stage_cursors, cap * 3 * sizeof(uint32_t)));
+    bd->stage_tokens = cap;
+    return WRK_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t wrk_bundle_create(wrk_model* model, uint32_t num_batch, wrk_bundle** out) {
+    WRK_REQUIRE(model && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(num_batch >= 1, WRK_ERR_INVALID_ARGUMENT, "num_batch must be at least 1");
+    auto b = new wrk_bundle();
+    wrk_model_retain(model);
+    b->model = model;
+    b->num_batch = num_batch;
+    const wrk_model_info& info = model->info;
+    const uint32_t S = info.num_emb / info.num_head;
+    const uint32_t shape[4] = {info.num_emb, S + 2, num_batch, 1};
+    for (uint32_t l = 0; l < info.num_layer; ++l) {
+        wrk_tensor* t = nullptr;
+        int32_t s = wrk_tensor_zeros(model->ctx, WRK_F32, shape, &t);
+        if (s != WRK_OK) {
+            delete b;
+            return s;
+        }
+        b->state.emplace_back(t);
+    }
+    *out = b;
+    return WRK_OK;
+}
+
+int32_t wrk_bundle_release(wrk_bundle* b) {
+    if (!b) return WRK_OK;
+    if (b->refs.fetch_sub(1) == 1) {
+        cudaStreamSynchronize(b->model->ctx->stream);
+        delete b;
+    }
+    return WRK_OK;
+}
+
+static void drop_caches(wrk_bundle* b) {
+    cudaStreamSynchronize(b->model->ctx->stream);
+    b->jobs.clear();
+    b->buffers.clear();
+    b->headers.clear();
+}
+
+int32_t wrk_bundle_set_packed_cursors(wrk_bundle* b, int32_t packed) {
+    WRK_REQUIRE(b, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    if (b->packed_cursors != (packed != 0)) drop_caches(b);
+    b->packed_cursors = packed != 0;
+    return WRK_OK;
+}
+
+int32_t wrk_bundle_set_use_graph(wrk_bundle* b, int32_t use_graph) {
+    WRK_REQUIRE(b, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    if (b->use_graph != (use_graph != 0)) drop_caches(b);
+    b->use_graph = use_graph != 0;
+    return WRK_OK;
+}
+
+int32_t wrk_bundle_set_fused(wrk_bundle* b, int32_t fused) {
+    WRK_REQUIRE(b, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    if (b->fused != (fused != 0)) drop_caches(b);
+    b->fused = fused != 0;
+    return WRK_OK;
+}
+
+int32_t wrk_state_num_batch(wrk_bundle* b, uint32_t* num_batch) {
+    WRK_REQUIRE(b && num_batch, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    *num_batch = b->num_batch;
+    return WRK_OK;
+}
+
+int32_t wrk_state_init_shape(wrk_bundle* b, uint32_t shape[4]) {
+    WRK_REQUIRE(b && shape, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    const wrk_model_info& info = b->model->info;
+    shape[0] = info.num_emb;
+    shape[1] = info.num_emb / info.num_head + 2;
+    shape[2] = info.num_layer;
+    shape[3] = 1;
+    return WRK_OK;
+}
+
+// State::load, v6.rs:199-206: host tensor [C, S + 2, L] → slot `batch` of every layer
+int32_t wrk_state_load(wrk_bundle* b, const float* host, size_t bytes, uint32_t batch) {
+    WRK_REQUIRE(b && host, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    const wrk_model_info& info = b->model->info;
+    const size_t per_layer = (size_t)info.num_emb * (info.num_emb / info.num_head + 2);
+    WRK_REQUIRE(bytes == per_layer * info.num_layer * 4, WRK_ERR_SIZE, "data size not match: %zu vs. %zu", bytes,
+                per_layer * info.num_layer * 4);
+    if (batch >= b->num_batch)
+        return set_error(WRK_ERR_BATCH_OUT_OF_RANGE, "batch %u out of range of max %u", batch, b->num_batch);
+    wrk_context* ctx = b->model->ctx;
+    for (uint32_t l = 0; l < info.num_layer; ++l)
+        WRK_CUDA(cudaMemcpyAsync(static_cast<float*>(b->state[l].p->ptr()) + batch * per_layer, host + l * per_layer,
+                                 per_layer * 4, cudaMemcpyHostToDevice, ctx->stream));
+    WRK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return WRK_OK;
+}
+
+// State::back, v6.rs:141-159
+int32_t wrk_state_back(wrk_bundle* b, uint32_t batch, float* host, size_t bytes) {
+    WRK_REQUIRE(b && host, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    const wrk_model_info& info = b->model->info;
+    const size_t per_layer = (size_t)info.num_emb * (info.num_emb / info.num_head + 2);
+    WRK_REQUIRE(bytes == per_layer * info.num_layer * 4, WRK_ERR_SIZE, "data size not match: %zu vs. %zu", bytes,
+                per_layer * info.num_layer * 4);
+    if (batch >= b->num_batch)
+        return set_error(WRK_ERR_BATCH_OUT_OF_RANGE, "batch %u out of range of max %u", batch, b->num_batch);
+    wrk_context* ctx = b->model->ctx;
+    for (uint32_t l = 0; l < info.num_layer; ++l)
+        WRK_CUDA(cudaMemcpyAsync(host + l * per_layer, static_cast<float*>(b->state[l].p->ptr()) + batch * per_layer,
+                                 per_layer * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    WRK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return WRK_OK;
+}
+
+int32_t wrk_state_layer(wrk_bundle* b, uint32_t layer, wrk_tensor** out) {
+    WRK_REQUIRE(b && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(layer < b->state.size(), WRK_ERR_INVALID_ARGUMENT, "layer %u out of range", layer);
+    *out = b->state[layer];
+    return WRK_OK;
+}
+
+int32_t wrk_bundle_dispatch(wrk_bundle* b, const uint32_t* lens, const int32_t* options, wrk_job** out) {
+    WRK_REQUIRE(b && lens && options && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    std::lock_guard<std::mutex> lock(b->mutex);
+    auto job = new wrk_job();
+    job->bundle = b;
+    job->info.lens.assign(lens, lens + b->num_batch);
+    job->info.options.assign(options, options + b->num_batch);
+    const uint32_t T = job->info.num_token();
+    RnnRedirect rd = redirect(job->info);
+
+    // cache key: the job's structure depends only on num_token and on which rows need logits
+    std::vector<uint32_t> key;
+    key.push_back(T);
+    key.insert(key.end(), rd.headers.begin(), rd.headers.end());
+    auto it = b->jobs.find(key);
+    std::shared_ptr<CachedJob> cj;
+    if (it != b->jobs.end()) {
+        cj = it->second;
+    } else {
+        cj = std::make_shared<CachedJob>();
+        cj->num_token = T;
+        cj->num_header = (uint32_t)rd.headers.size();
+        cj->redirect = rd;
+        int32_t s = WRK_OK;
+        if (T > 0) {
+            auto& rb = b->buffers[T];
+            if (!rb) s = make_runtime(b, T, &rb);
+            cj->buffer = rb;
+            if (s == WRK_OK) {
+                auto& hb = b->headers[cj->num_header];
+                if (!hb) s = make_header(b, cj->num_header, &hb);
+                cj->header = hb;
+            }
+            if (s == WRK_OK) s = build_job(b, job->info, cj.get());
+        }
+        if (s != WRK_OK) {
+            delete job;
+            return s;
+        }
+        // bounded cache, least recently used first (ResourceCache, src/tensor/cache.rs:21-117)
+        if (b->jobs.size() >= 64) {
+            auto victim = b->jobs.begin();
+            for (auto j = b->jobs.begin(); j != b->jobs.end(); ++j)
+                if (j->second->tick < victim->second->tick) victim = j;
+            cudaStreamSynchronize(b->model->ctx->stream);
+            b->jobs.erase(victim);
+        }
+        b->jobs[key] = cj;
+    }
+    cj->tick = ++b->tick;
+    cj->redirect = rd;  // per-batch ranges differ between jobs that share a structure
+    job->job = cj;
+    *out = job;
+    return WRK_OK;
+}
+
+// Job::load, v6.rs:423-459
+int32_t wrk_job_load(wrk_job* job, const uint32_t* tokens, size_t count) {
+    WRK_REQUIRE(job && (tokens || count == 0), WRK_ERR_INVALID_ARGUMENT, "null argument");
+    wrk_bundle* b = job->bundle;
+    const uint32_t T = job->info.num_token();
+    WRK_REQUIRE(count == T, WRK_ERR_SIZE, "data size not match: %zu vs. %u", count, T);
+    if (T == 0) return WRK_OK;
+    std::lock_guard<std::mutex> lock(b->mutex);
+    wrk_model* m = b->model;
+    wrk_context* ctx = m->ctx;
+    const uint32_t C = m->info.num_emb;
+    WRK_TRY(ensure_staging(b, T));
+    // the previous upload from the staging buffers must have been consumed
+    WRK_CUDA(cudaStreamSynchronize(ctx->stream));
+    for (uint32_t t = 0; t < T; ++t) {
+        const uint32_t tok = tokens[t];
+        WRK_REQUIRE(tok < m->num_vocab_padded, WRK_ERR_INVALID_ARGUMENT, "token %u out of vocabulary %u", tok,
+                    m->num_vocab_padded);
+        std::memcpy(b->stage_input + (size_t)t * C, m->embed_host + (size_t)tok * C, (size_t)C * 2);
+    }
+    // cursors: one record per token, identical for all tokens of a sequence (tensor/mod.rs:47-85)
+    uint32_t p = 0;
+    for (uint32_t batch = 0; batch < b->num_batch; ++batch) {
+        const uint32_t len = job->info.lens[batch];
+        for (uint32_t i = 0; i < len; ++i) {
+            if (b->packed_cursors) {
+                b->stage_cursors[p + i] = (batch & 0xffu) | ((p & 0xffffu) << 8) | ((len & 0xffu) << 24);
+            } else {
+                b->stage_cursors[3 * (p + i)] = batch;
+                b->stage_cursors[3 * (p + i) + 1] = p;
+                b->stage_cursors[3 * (p + i) + 2] = len;
+            }
+        }
+        p += len;
+    }
+    const Buffers& B = *job->job->buffer;
+    WRK_CUDA(cudaMemcpyAsync(B["cursors"]->ptr(), b->stage_cursors, (b->packed_cursors ? T : 3 * T) * sizeof(uint32_t),
+                             cudaMemcpyHostToDevice, ctx->stream));
+    WRK_CUDA(cudaMemcpyAsync(B["input"]->ptr(), b->stage_input, (size_t)T * C * 2, cudaMemcpyHostToDevice, ctx->stream));
+    return WRK_OK;
+}
+
+int32_t wrk_job_submit(wrk_job* job) {
+    WRK_REQUIRE(job, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    if (!job->job->commands) return WRK_OK;
+    return wrk_submit(job->bundle->model->ctx, job->job->commands);
+}
+
+// Job::back, v6.rs:466-476
+int32_t wrk_job_back(wrk_job* job, float* logits, size_t capacity, uint32_t* outputs, uint32_t* num_headers) {
+    WRK_REQUIRE(job, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    wrk_bundle* b = job->bundle;
+    wrk_context* ctx = b->model->ctx;
+    const CachedJob& cj = *job->job;
+    if (num_headers) *num_headers = cj.num_header;
+    if (outputs)
+        for (uint32_t i = 0; i < b->num_batch; ++i) {
+            outputs[2 * i] = cj.redirect.outputs[i].first;
+            outputs[2 * i + 1] = cj.redirect.outputs[i].second;
+        }
+    if (cj.num_token == 0 || cj.num_header == 0) {
+        WRK_CUDA(cudaStreamSynchronize(ctx->stream));
+        return WRK_OK;
+    }
+    wrk_tensor* head_o = (*cj.header)["head_o"];
+    WRK_REQUIRE(logits && capacity >= head_o->len(), WRK_ERR_SIZE, "data size not match: %zu vs. %zu", capacity,
+                head_o->len());
+    WRK_CUDA(cudaMemcpyAsync(logits, head_o->ptr(), head_o->bytes(), cudaMemcpyDeviceToHost, ctx->stream));
+    WRK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return WRK_OK;
+}
+
+int32_t wrk_job_num_kernels(const wrk_job* job, uint64_t* count) {
+    WRK_REQUIRE(job && count, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    *count = job->job->commands ? job->job->commands->num_kernels : 0;
+    return WRK_OK;
+}
+
+int32_t wrk_job_release(wrk_job* job) {
+    delete job;
+    return WRK_OK;
+}
+
+// SimpleRuntime::infer, src/runtime/mod.rs:237-262
+int32_t wrk_runtime_infer(wrk_bundle* b, wrk_rnn_input* in, float* logits, size_t capacity, uint32_t* outputs,
+                          uint32_t* num_headers) {
+    WRK_REQUIRE(b && in, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(in->batches.size() == b->num_batch, WRK_ERR_BATCH, "batch size not match: %zu vs. %u",
+                in->batches.size(), b->num_batch);
+    RnnIter it = make_iter(*in);
+    RnnInfo info = it.next();
+    if (info.num_token() == 0) return set_error(WRK_ERR_INPUT_EXHAUSTED, "input iterator exhausted");
+    std::vector<uint32_t> chunk;
+    for (uint32_t i = 0; i < b->num_batch; ++i)
+        chunk.insert(chunk.end(), in->batches[i].tokens.begin(), in->batches[i].tokens.begin() + info.lens[i]);
+    wrk_job* job = nullptr;
+    WRK_TRY(wrk_bundle_dispatch(b, info.lens.data(), info.options.data(), &job));
+    int32_t s = wrk_job_load(job, chunk.data(), chunk.size());
+    if (s == WRK_OK) s = wrk_job_submit(job);
+    if (s == WRK_OK) s = wrk_job_back(job, logits, capacity, outputs, num_headers);
+    wrk_job_release(job);
+    if (s == WRK_OK) s = wrk_rnn_input_step(in);
+    return s;
+}
+
+}  // extern "C"

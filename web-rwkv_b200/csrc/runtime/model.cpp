@@ -1,0 +1,489 @@
+// Model building: Loader::info, load-time transforms, per-layer quantization.
+// Restates src/runtime/loader.rs (version sniffing, vector/matrix loaders, discount, padding) and
+// ModelBuilder::build_v5 / build_v6 / build_v7 over the C ABI of wrk.h.  LoRA merging is not built.
+#include <cmath>
+#include <cstring>
+
+#include "runtime.h"
+
+using namespace wrk;
+using namespace wrk::rt;
+
+wrk_model::~wrk_model() {
+    if (embed_host) cudaFreeHost(embed_host);
+}
+
+namespace {
+
+struct Loader {
+    wrk_model_builder* b;
+    wrk_context* ctx;
+
+    const wrk_model_builder::Entry* find(const std::string& name) const {
+        auto it = b->tensors.find(name);
+        return it == b->tensors.end() ? nullptr : &it->second;
+    }
+    bool contains(const std::string& name) const { return find(name) != nullptr; }
+
+    int32_t entry(const std::string& name, const wrk_model_builder::Entry** e) const {
+        *e = find(name);
+        if (!*e) return set_error(WRK_ERR_MISSING_TENSOR, "tensor %s not found", name.c_str());
+        return WRK_OK;
+    }
+
+    // Shape::from_slice_rev, src/tensor/shape.rs:113-124
+    static int32_t rev_shape(const std::vector<uint64_t>& s, uint32_t out[4]) {
+        out[0] = out[1] = out[2] = out[3] = 1;
+        WRK_REQUIRE(s.size() >= 1 && s.size() <= 4, WRK_ERR_DEDUCE, "cannot deduce dimension");
+        for (size_t i = 0; i < s.size(); ++i) out[i] = (uint32_t)s[s.size() - 1 - i];
+        return WRK_OK;
+    }
+
+    // load_vector_f16, src/runtime/loader.rs:514-565: flattened to [n, 1, 1, 1]
+    int32_t vector_f16(const std::string& name, TensorH* out) const {
+        const wrk_model_builder::Entry* e;
+        WRK_TRY(entry(name, &e));
+        const uint32_t shape[4] = {(uint32_t)e->data.size(), 1, 1, 1};
+        wrk_tensor* t = nullptr;
+        WRK_TRY(wrk_tensor_from_data(ctx, WRK_F16, shape, e->data.data(), e->data.size() * 2, &t));
+        *out = TensorH(t);
+        return WRK_OK;
+    }
+
+    // load_vector_f32, src/runtime/loader.rs:393-426: f16 → f32 on the host
+    int32_t vector_f32(const std::string& name, TensorH* out) const {
+        const wrk_model_builder::Entry* e;
+        WRK_TRY(entry(name, &e));
+        std::vector<float> f(e->data.size());
+        for (size_t i = 0; i < f.size(); ++i) f[i] = __half2float(__ushort_as_half(e->data[i]));
+        const uint32_t shape[4] = {(uint32_t)f.size(), 1, 1, 1};
+        wrk_tensor* t = nullptr;
+        WRK_TRY(wrk_tensor_from_data(ctx, WRK_F32, shape, f.data(), f.size() * 4, &t));
+        *out = TensorH(t);
+        return WRK_OK;
+    }
+
+    // load_vector_exp_exp_f32, src/runtime/loader.rs:472-512: f32 vector, then StableExp on the device
+    int32_t vector_exp_exp_f32(const std::string& name, TensorH* out) const {
+        WRK_TRY(vector_f32(name, out));
+        wrk_view v;
+        WRK_TRY(wrk_tensor_as_view(*out, &v));
+        wrk_op* op = nullptr;
+        WRK_TRY(wrk_op_activate(&v, WRK_ACT_STABLE_EXP, &op));
+        int32_t s = wrk_run(ctx, op);
+        wrk_op_release(op);
+        return s;
+    }
+
+    // load_matrix_f16, src/runtime/loader.rs:567-592 (optionally padded to multiples of 8: :688-707)
+    int32_t matrix_f16(const std::string& name, bool padded, float discount, TensorH* out) const {
+        const wrk_model_builder::Entry* e;
+        WRK_TRY(entry(name, &e));
+        uint32_t shape[4];
+        WRK_TRY(rev_shape(e->shape, shape));
+        const uint16_t* src = e->data.data();
+        std::vector<uint16_t> tmp;
+        if (discount != 1.0f) {
+            // f16(discount * f32(x)) on the host, src/runtime/loader.rs:660-661
+            tmp.resize(e->data.size());
+            for (size_t i = 0; i < tmp.size(); ++i)
+                tmp[i] = __half_as_ushort(__float2half_rn(discount * __half2float(__ushort_as_half(e->data[i]))));
+            src = tmp.data();
+        }
+        std::vector<uint16_t> pad;
+        if (padded && (shape[0] % 8 || shape[1] % 8)) {
+            const uint32_t px = (shape[0] + 7) / 8 * 8, py = (shape[1] + 7) / 8 * 8;
+            pad.assign((size_t)px * py * shape[2] * shape[3], 0);
+            for (size_t z = 0; z < (size_t)shape[2] * shape[3]; ++z)
+                for (uint32_t y = 0; y < shape[1]; ++y)
+                    std::memcpy(&pad[(z * py + y) * px], &src[(z * shape[1] + y) * shape[0]], shape[0] * 2);
+            shape[0] = px;
+            shape[1] = py;
+            src = pad.data();
+        }
+        const size_t n = (size_t)shape[0] * shape[1] * shape[2] * shape[3];
+        wrk_tensor* t = nullptr;
+        WRK_TRY(wrk_tensor_from_data(ctx, WRK_F16, shape, src, n * 2, &t));
+        *out = TensorH(t);
+        return WRK_OK;
+    }
+
+    int32_t matrix_fp16(const std::string& name, MatrixH* out) const {
+        TensorH t;
+        WRK_TRY(matrix_f16(name, false, 1.0f, &t));
+        wrk_matrix* m = nullptr;
+        WRK_TRY(wrk_matrix_fp16(t, &m));
+        *out = MatrixH(m);
+        return WRK_OK;
+    }
+
+    // load_matrix / load_matrix_discount, src/runtime/loader.rs:709-762
+    int32_t matrix(const std::string& name, int32_t quant, float discount, MatrixH* out) const {
+        TensorH t;
+        WRK_TRY(matrix_f16(name, false, discount, &t));
+        wrk_matrix* m = nullptr;
+        switch (quant) {
+            case WRK_QUANT_NONE: WRK_TRY(wrk_matrix_fp16(t, &m)); break;
+            case WRK_QUANT_INT8: WRK_TRY(wrk_matrix_quant_u8(t, &m)); break;
+            case WRK_QUANT_NF4: WRK_TRY(wrk_matrix_quant_nf4(t, &m)); break;
+            default:
+                return set_error(WRK_ERR_UNSUPPORTED,
+                                 "Quant::SF4 needs the Student-t code book of a third-party crate; pass a table to "
+                                 "wrk_matrix_quant_fp4 instead");
+        }
+        *out = MatrixH(m);
+        // the fp16 staging tensor is released here; the stream orders its reuse after the quantizer
+        return WRK_OK;
+    }
+
+    int32_t layer_norm(const std::string& prefix, LayerNorm* ln) const {
+        WRK_TRY(vector_f16(prefix + ".weight", &ln->w));
+        WRK_TRY(vector_f16(prefix + ".bias", &ln->b));
+        return WRK_OK;
+    }
+
+    int32_t group_norm(const std::string& prefix, uint32_t num_head, LayerNorm* ln) const {
+        TensorH w, b;
+        WRK_TRY(vector_f16(prefix + ".weight", &w));
+        WRK_TRY(vector_f16(prefix + ".bias", &b));
+        const uint32_t shape[4] = {WRK_DIM_AUTO, num_head, 1, 1};
+        wrk_tensor *rw = nullptr, *rb = nullptr;
+        WRK_TRY(wrk_tensor_reshape(w, shape, &rw));
+        ln->w = TensorH(rw);
+        WRK_TRY(wrk_tensor_reshape(b, shape, &rb));
+        ln->b = TensorH(rb);
+        return WRK_OK;
+    }
+};
+
+// Loader::info, src/runtime/loader.rs:208-324.
+int32_t sniff_info(const wrk_model_builder* b, wrk_model_info* info) {
+    Loader ld{const_cast<wrk_model_builder*>(b), b->ctx};
+    uint32_t num_layer = 0;
+    for (auto& kv : b->tensors) {
+        const std::string& n = kv.first;
+        if (n.rfind("blocks.", 0) == 0) {
+            const size_t dot = n.find('.', 7);
+            if (dot == std::string::npos) continue;
+            num_layer = std::max<uint32_t>(num_layer, (uint32_t)std::stoul(n.substr(7, dot - 7)));
+        }
+    }
+    num_layer += 1;
+    auto all = [&](std::initializer_list<const char*> names) {
+        for (auto n : names)
+            if (!ld.contains(n)) return false;
+        return true;
+    };
+    const bool v4 = all({"blocks.0.att.time_decay", "blocks.0.att.time_first", "blocks.0.att.time_mix_k",
+                         "blocks.0.att.time_mix_v", "blocks.0.att.time_mix_r"});
+    const bool v5 = all({"blocks.0.att.gate.weight", "blocks.0.att.ln_x.weight", "blocks.0.att.ln_x.bias"});
+    const bool v6 = all({"blocks.0.att.time_mix_x", "blocks.0.att.time_mix_w", "blocks.0.att.time_mix_k",
+                         "blocks.0.att.time_mix_v", "blocks.0.att.time_mix_r", "blocks.0.att.time_mix_g",
+                         "blocks.0.att.time_mix_w1", "blocks.0.att.time_mix_w2", "blocks.0.att.time_decay_w1",
+                         "blocks.0.att.time_decay_w2", "blocks.0.ffn.time_mix_k", "blocks.0.ffn.time_mix_r"});
+    const bool v7 = all({"blocks.0.att.x_r", "blocks.0.att.x_w", "blocks.0.att.x_k", "blocks.0.att.x_v",
+                         "blocks.0.att.x_a", "blocks.0.att.x_g", "blocks.0.att.w0", "blocks.0.att.w1",
+                         "blocks.0.att.w2", "blocks.0.att.a0", "blocks.0.att.a1", "blocks.0.att.a2",
+                         "blocks.0.att.g1", "blocks.0.att.g2", "blocks.0.att.r_k", "blocks.0.att.k_k",
+                         "blocks.0.att.k_a"});
+    uint32_t version;
+    if (v7) version = 7;
+    else if (v6) version = 6;
+    else if (v5) version = 5;
+    else if (v4)
+        return set_error(WRK_ERR_UNSUPPORTED, "RWKV v4 models are outside this library's path (v5, v6, v7 only)");
+    else
+        return set_error(WRK_ERR_INVALID_VERSION, "invalid model version");
+
+    const wrk_model_builder::Entry *embed, *ffn;
+    WRK_TRY(ld.entry("emb.weight", &embed));
+    WRK_TRY(ld.entry("blocks.0.ffn.key.weight", &ffn));
+    WRK_REQUIRE(embed->shape.size() == 2 && ffn->shape.size() == 2, WRK_ERR_SHAPE, "tensor shape not match: emb/ffn");
+    std::memset(info, 0, sizeof *info);
+    info->version = version;
+    info->num_layer = num_layer;
+    info->num_emb = (uint32_t)embed->shape[1];
+    info->num_hidden = (uint32_t)ffn->shape[0];
+    info->num_vocab = (uint32_t)embed->shape[0];
+    const wrk_model_builder::Entry* e;
+    if (version == 7) {
+        WRK_TRY(ld.entry("blocks.0.att.r_k", &e));
+        info->num_head = (uint32_t)e->shape[0];
+        WRK_TRY(ld.entry("blocks.0.att.w1", &e));
+        info->custom[0] = (uint32_t)e->shape[0];
+        WRK_TRY(ld.entry("blocks.0.att.a1", &e));
+        info->custom[1] = (uint32_t)e->shape[0];
+        WRK_TRY(ld.entry("blocks.0.att.g1", &e));
+        info->custom[2] = (uint32_t)e->shape[0];
+        WRK_TRY(ld.entry("blocks.1.att.v1", &e));
+        info->custom[3] = (uint32_t)e->shape[0];
+    } else {
+        WRK_TRY(ld.entry("blocks.0.att.time_first", &e));
+        info->num_head = (uint32_t)e->shape[0];
+        if (version == 6) {
+            WRK_TRY(ld.entry("blocks.0.att.time_mix_w1", &e));
+            info->custom[0] = (uint32_t)e->shape[0] / 5;
+            WRK_TRY(ld.entry("blocks.0.att.time_decay_w1", &e));
+            info->custom[1] = (uint32_t)e->shape[0];
+        }
+    }
+    return WRK_OK;
+}
+
+int32_t build_common(const Loader& ld, wrk_model* m) {
+    const wrk_model_info& info = m->info;
+    WRK_TRY(ld.layer_norm("blocks.0.ln0", &m->embed_ln));
+    WRK_TRY(ld.layer_norm("ln_out", &m->head_ln));
+    // embedding table stays on the host, padded to a multiple of 8 rows (load_matrix_f16_padded_cpu)
+    const wrk_model_builder::Entry* e;
+    WRK_TRY(ld.entry("emb.weight", &e));
+    m->num_vocab_padded = (info.num_vocab + 7) / 8 * 8;
+    const size_t bytes = (size_t)m->num_vocab_padded * info.num_emb * 2;
+    WRK_CUDA(cudaMallocHost(&m->embed_host, bytes));
+    std::memset(m->embed_host, 0, bytes);
+    std::memcpy(m->embed_host, e->data.data(), e->data.size() * 2);
+    // head: never quantized; v6 / v7 pad it, v5 does not (v5.rs:956, v6.rs:1029, v7.rs:1073)
+    TensorH head;
+    WRK_TRY(ld.matrix_f16("head.weight", info.version != 5, 1.0f, &head));
+    wrk_matrix* hm = nullptr;
+    WRK_TRY(wrk_matrix_fp16(head, &hm));
+    m->head_w = MatrixH(hm);
+    return WRK_OK;
+}
+
+int32_t quant_of(const wrk_model_builder* b, uint32_t layer) {
+    auto it = b->quant.find(layer);
+    return it == b->quant.end() ? WRK_QUANT_NONE : it->second;
+}
+
+// ModelBuilder::build_v5 (src/runtime/v5.rs:922-1082) and build_v6 (src/runtime/v6.rs:995-1172)
+int32_t build_v56(const Loader& ld, wrk_model* m) {
+    const wrk_model_info& info = m->info;
+    wrk_context* ctx = m->ctx;
+    m->layers.resize(info.num_layer);
+    for (uint32_t layer = 0; layer < info.num_layer; ++layer) {
+        Layer& L = m->layers[layer];
+        const int32_t quant = quant_of(ld.b, layer);
+        const float discount = std::ldexp(1.0f, -(int)(layer / m->rescale));
+        const std::string blk = "blocks." + std::to_string(layer);
+        const std::string att = blk + ".att", ffn = blk + ".ffn";
+        WRK_TRY(ld.layer_norm(blk + ".ln1", &L.att_ln));
+        WRK_TRY(ld.vector_f32(att + ".time_first", &L.time_first));
+        if (info.version == 5) {
+            WRK_TRY(ld.vector_exp_exp_f32(att + ".time_decay", &L.time_decay));
+            WRK_TRY(ld.vector_f16(att + ".time_mix_k", &L.time_mix_k));
+            WRK_TRY(ld.vector_f16(att + ".time_mix_v", &L.time_mix_v));
+            WRK_TRY(ld.vector_f16(att + ".time_mix_r", &L.time_mix_r));
+            WRK_TRY(ld.vector_f16(att + ".time_mix_g", &L.time_mix_g));
+        } else {
+            WRK_TRY(ld.vector_f16(att + ".time_decay", &L.time_decay));
+            WRK_TRY(ld.vector_f16(att + ".time_mix_x", &L.time_mix_x));
+            // five static mixes stacked as [C, 1, 5] in the order w, k, v, r, g (v6.rs:1063-1080)
+            const uint32_t shape[4] = {info.num_emb, 1, 5, 1};
+            wrk_tensor* tm = nullptr;
+            WRK_TRY(wrk_tensor_zeros(ctx, WRK_F16, shape, &tm));
+            L.time_mix = TensorH(tm);
+            const char* names[5] = {".time_mix_w", ".time_mix_k", ".time_mix_v", ".time_mix_r", ".time_mix_g"};
+            for (uint32_t i = 0; i < 5; ++i) {
+                const wrk_model_builder::Entry* e;
+                WRK_TRY(ld.entry(att + names[i], &e));
+                WRK_REQUIRE(e->data.size() == info.num_emb, WRK_ERR_SHAPE, "tensor shape not match: %s",
+                            (att + names[i]).c_str());
+                WRK_CUDA(cudaMemcpyAsync(static_cast<uint16_t*>(tm->ptr()) + (size_t)i * info.num_emb, e->data.data(),
+                                         (size_t)info.num_emb * 2, cudaMemcpyHostToDevice, ctx->stream));
+            }
+            WRK_CUDA(cudaStreamSynchronize(ctx->stream));
+            WRK_TRY(ld.matrix_fp16(att + ".time_decay_w1", &L.time_decay_w1));
+            WRK_TRY(ld.matrix_fp16(att + ".time_decay_w2", &L.time_decay_w2));
+            WRK_TRY(ld.matrix_fp16(att + ".time_mix_w1", &L.time_mix_w1));
+            WRK_TRY(ld.matrix_fp16(att + ".time_mix_w2", &L.time_mix_w2));
+        }
+        WRK_TRY(ld.group_norm(att + ".ln_x", info.num_head, &L.gn));
+        WRK_TRY(ld.matrix(att + ".key.weight", quant, 1.0f, &L.att_w_k));
+        WRK_TRY(ld.matrix(att + ".value.weight", quant, 1.0f, &L.att_w_v));
+        WRK_TRY(ld.matrix(att + ".receptance.weight", quant, 1.0f, &L.att_w_r));
+        WRK_TRY(ld.matrix(att + ".gate.weight", quant, 1.0f, &L.att_w_g));
+        WRK_TRY(ld.matrix(att + ".output.weight", quant, discount, &L.att_w_o));
+        WRK_TRY(ld.layer_norm(blk + ".ln2", &L.ffn_ln));
+        WRK_TRY(ld.vector_f16(ffn + ".time_mix_k", &L.ffn_time_mix_k));
+        WRK_TRY(ld.vector_f16(ffn + ".time_mix_r", &L.ffn_time_mix_r));
+        WRK_TRY(ld.matrix(ffn + ".receptance.weight", quant, 1.0f, &L.ffn_w_r));
+        WRK_TRY(ld.matrix(ffn + ".key.weight", quant, 1.0f, &L.ffn_w_k));
+        WRK_TRY(ld.matrix(ffn + ".value.weight", quant, discount, &L.ffn_w_v));
+        WRK_CUDA(cudaStreamSynchronize(ctx->stream));  // frees the fp16 staging of this layer (v6.rs:1135-1139)
+    }
+    return WRK_OK;
+}
+
+// ModelBuilder::build_v7, src/runtime/v7.rs:1038-1226
+int32_t build_v7(const Loader& ld, wrk_model* m) {
+    const wrk_model_info& info = m->info;
+    wrk_context* ctx = m->ctx;
+    m->layers.resize(info.num_layer);
+    for (uint32_t layer = 0; layer < info.num_layer; ++layer) {
+        Layer& L = m->layers[layer];
+        const int32_t quant = quant_of(ld.b, layer);
+        const float discount = std::ldexp(1.0f, -(int)(layer / m->rescale));
+        const std::string blk = "blocks." + std::to_string(layer);
+        const std::string att = blk + ".att", ffn = blk + ".ffn";
+        WRK_TRY(ld.layer_norm(blk + ".ln1", &L.att_ln));
+        WRK_TRY(ld.vector_f16(att + ".x_r", &L.x_r));
+        WRK_TRY(ld.vector_f16(att + ".x_w", &L.x_w));
+        WRK_TRY(ld.vector_f16(att + ".x_k", &L.x_k));
+        WRK_TRY(ld.vector_f16(att + ".x_v", &L.x_v));
+        WRK_TRY(ld.vector_f16(att + ".x_a", &L.x_a));
+        WRK_TRY(ld.vector_f16(att + ".x_g", &L.x_g));
+        WRK_TRY(ld.vector_f16(att + ".w0", &L.w0));
+        WRK_TRY(ld.vector_f16(att + ".a0", &L.a0));
+        WRK_TRY(ld.matrix_fp16(att + ".w1", &L.w1));
+        WRK_TRY(ld.matrix_fp16(att + ".w2", &L.w2));
+        WRK_TRY(ld.matrix_fp16(att + ".a1", &L.a1));
+        WRK_TRY(ld.matrix_fp16(att + ".a2", &L.a2));
+        WRK_TRY(ld.matrix_fp16(att + ".g1", &L.g1));
+        WRK_TRY(ld.matrix_fp16(att + ".g2", &L.g2));
+        if (layer == 0) {  // placeholders, never used (v7.rs:1114-1121)
+            L.v0 = L.a0;
+            L.v1 = L.a1;
+            L.v2 = L.a2;
+        } else {
+            WRK_TRY(ld.vector_f16(att + ".v0", &L.v0));
+            WRK_TRY(ld.matrix_fp16(att + ".v1", &L.v1));
+            WRK_TRY(ld.matrix_fp16(att + ".v2", &L.v2));
+        }
+        WRK_TRY(ld.matrix_f16(att + ".r_k", false, 1.0f, &L.r_k));
+        WRK_TRY(ld.vector_f16(att + ".k_k", &L.k_k));
+        WRK_TRY(ld.vector_f16(att + ".k_a", &L.k_a));
+        WRK_TRY(ld.group_norm(att + ".ln_x", info.num_head, &L.gn));
+        WRK_TRY(ld.matrix(att + ".key.weight", quant, 1.0f, &L.att_w_k));
+        WRK_TRY(ld.matrix(att + ".value.weight", quant, 1.0f, &L.att_w_v));
+        WRK_TRY(ld.matrix(att + ".receptance.weight", quant, 1.0f, &L.att_w_r));
+        WRK_TRY(ld.matrix(att + ".output.weight", quant, discount, &L.att_w_o));
+        WRK_TRY(ld.layer_norm(blk + ".ln2", &L.ffn_ln));
+        WRK_TRY(ld.vector_f16(ffn + ".x_k", &L.ffn_x_k));
+        WRK_TRY(ld.matrix(ffn + ".key.weight", quant, 1.0f, &L.ffn_w_k));
+        WRK_TRY(ld.matrix(ffn + ".value.weight", quant, discount, &L.ffn_w_v));
+        WRK_CUDA(cudaStreamSynchronize(ctx->stream));
+    }
+    return WRK_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t wrk_model_builder_create(wrk_context* ctx, wrk_model_builder** out) {
+    WRK_REQUIRE(ctx && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    auto b = new wrk_model_builder();
+    b->ctx = ctx;
+    *out = b;
+    return WRK_OK;
+}
+
+int32_t wrk_model_builder_destroy(wrk_model_builder* b) {
+    delete b;
+    return WRK_OK;
+}
+
+int32_t wrk_model_builder_add_tensor(wrk_model_builder* b, const char* name, const uint64_t* shape, uint32_t ndim,
+                                     const void* data_f16, size_t bytes) {
+    WRK_REQUIRE(b && name && shape && (data_f16 || bytes == 0), WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(ndim >= 1 && ndim <= 4, WRK_ERR_DEDUCE, "cannot deduce dimension");
+    size_t n = 1;
+    for (uint32_t i = 0; i < ndim; ++i) n *= shape[i];
+    WRK_REQUIRE(n * 2 == bytes, WRK_ERR_SIZE, "data size not match: %zu vs. %zu", n * 2, bytes);
+    auto& e = b->tensors[name];
+    e.shape.assign(shape, shape + ndim);
+    e.data.resize(n);
+    std::memcpy(e.data.data(), data_f16, bytes);
+    return WRK_OK;
+}
+
+int32_t wrk_model_builder_quant(wrk_model_builder* b, uint32_t layer, int32_t quant) {
+    WRK_REQUIRE(b, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(quant >= WRK_QUANT_NONE && quant <= WRK_QUANT_SF4, WRK_ERR_INVALID_ARGUMENT, "unknown quant %d", quant);
+    b->quant[layer] = quant;
+    return WRK_OK;
+}
+
+int32_t wrk_model_builder_rescale(wrk_model_builder* b, uint32_t value) {
+    WRK_REQUIRE(b, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    b->rescale = value == 0 ? SIZE_MAX : value;  // ModelBuilder::rescale: 0 disables (model.rs:160-166)
+    return WRK_OK;
+}
+
+int32_t wrk_model_builder_sep(wrk_model_builder* b, uint32_t value) {
+    WRK_REQUIRE(b, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    b->sep = value == 0 ? SIZE_MAX : value;
+    return WRK_OK;
+}
+
+int32_t wrk_model_builder_info(wrk_model_builder* b, wrk_model_info* info) {
+    WRK_REQUIRE(b && info, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    return sniff_info(b, info);
+}
+
+int32_t wrk_model_builder_build(wrk_model_builder* b, wrk_model** out) {
+    WRK_REQUIRE(b && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    auto m = new wrk_model();
+    m->ctx = b->ctx;
+    int32_t s = sniff_info(b, &m->info);
+    if (s == WRK_OK) {
+        const size_t def_rescale = m->info.version == 7 ? 1024 : 6;  // Model::DEFAULT_RESCALE
+        m->rescale = b->rescale ? b->rescale : def_rescale;
+        m->sep = b->sep ? b->sep : 1024;
+        WRK_REQUIRE(m->info.num_emb % m->info.num_head == 0, WRK_ERR_SHAPE, "num_emb %u not divisible by num_head %u",
+                    m->info.num_emb, m->info.num_head);
+        Loader ld{b, b->ctx};
+        s = build_common(ld, m);
+        if (s == WRK_OK) s = m->info.version == 7 ? build_v7(ld, m) : build_v56(ld, m);
+    }
+    if (s != WRK_OK) {
+        delete m;
+        return s;
+    }
+    *out = m;
+    return WRK_OK;
+}
+
+int32_t wrk_model_info_get(const wrk_model* m, wrk_model_info* info) {
+    WRK_REQUIRE(m && info, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    *info = m->info;
+    return WRK_OK;
+}
+
+int32_t wrk_model_retain(wrk_model* m) {
+    WRK_REQUIRE(m, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    m->refs.fetch_add(1);
+    return WRK_OK;
+}
+
+int32_t wrk_model_release(wrk_model* m) {
+    if (!m) return WRK_OK;
+    if (m->refs.fetch_sub(1) == 1) delete m;
+    return WRK_OK;
+}
+
+int32_t wrk_model_matrix(wrk_model* m, uint32_t layer, const char* name, wrk_matrix** out) {
+    WRK_REQUIRE(m && name && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    const std::string n = name;
+    if (n == "head.w") {
+        *out = m->head_w;
+        return WRK_OK;
+    }
+    WRK_REQUIRE(layer < m->layers.size(), WRK_ERR_INVALID_ARGUMENT, "layer %u out of range", layer);
+    Layer& L = m->layers[layer];
+    wrk_matrix* r = nullptr;
+    if (n == "att.w_k") r = L.att_w_k;
+    else if (n == "att.w_v") r = L.att_w_v;
+    else if (n == "att.w_r") r = L.att_w_r;
+    else if (n == "att.w_g") r = L.att_w_g;
+    else if (n == "att.w_o") r = L.att_w_o;
+    else if (n == "ffn.w_k") r = L.ffn_w_k;
+    else if (n == "ffn.w_v") r = L.ffn_w_v;
+    else if (n == "ffn.w_r") r = L.ffn_w_r;
+    WRK_REQUIRE(r, WRK_ERR_INVALID_ARGUMENT, "no matrix %s in layer %u", name, layer);
+    *out = r;
+    return WRK_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,257 @@
+"""ctypes harness over the run() job API of include/wrk_runtime.h: ModelBuilder, Bundle/State,
+RnnInput chunking and the dispatch → load → submit → back protocol (src/runtime/*.rs)."""
+import ctypes
+
+import numpy as np
+
+from . import (QUANT_INT8, QUANT_NF4, QUANT_NONE, RNN_FULL, RNN_LAST, RNN_NONE, Context, Matrix, Tensor, WrkError,
+               check, lib)
+
+
+class ModelInfo(ctypes.Structure):
+    _fields_ = [("version", ctypes.c_uint32), ("num_layer", ctypes.c_uint32), ("num_emb", ctypes.c_uint32),
+                ("num_hidden", ctypes.c_uint32), ("num_vocab", ctypes.c_uint32), ("num_head", ctypes.c_uint32),
+                ("custom", ctypes.c_uint32 * 4)]
+
+
+class ModelBuilder:
+    """`ModelBuilder` (src/runtime/model.rs:137-185) fed tensor by tensor instead of through a Reader."""
+
+    def __init__(self, ctx):
+        self.ctx = ctx
+        self.handle = ctypes.c_void_p()
+        check(lib().wrk_model_builder_create(ctx.handle, ctypes.byref(self.handle)))
+
+    def __del__(self):
+        if getattr(self, "handle", None):
+            lib().wrk_model_builder_destroy(self.handle)
+            self.handle = None
+
+    def add_tensor(self, name, arr):
+        arr = np.ascontiguousarray(arr, dtype=np.float16)
+        shape = (ctypes.c_uint64 * arr.ndim)(*arr.shape)
+        check(lib().wrk_model_builder_add_tensor(self.handle, name.encode(), shape, arr.ndim,
+                                                 arr.ctypes.data_as(ctypes.c_void_p), ctypes.c_size_t(arr.nbytes)))
+        return self
+
+    def add_tensors(self, items):
+        for name, arr in (items.items() if isinstance(items, dict) else items):
+            self.add_tensor(name, arr)
+        return self
+
+    def quant(self, mapping):
+        for layer, q in mapping.items():
+            check(lib().wrk_model_builder_quant(self.handle, layer, q))
+        return self
+
+    def rescale(self, value):
+        check(lib().wrk_model_builder_rescale(self.handle, value))
+        return self
+
+    def info(self):
+        info = ModelInfo()
+        check(lib().wrk_model_builder_info(self.handle, ctypes.byref(info)))
+        return info
+
+    def build(self):
+        h = ctypes.c_void_p()
+        check(lib().wrk_model_builder_build(self.handle, ctypes.byref(h)))
+        return Model(self.ctx, h)
+
+
+class Model:
+    def __init__(self, ctx, handle):
+        self.ctx, self.handle = ctx, handle
+
+    def __del__(self):
+        if getattr(self, "handle", None):
+            lib().wrk_model_release(self.handle)
+            self.handle = None
+
+    @property
+    def info(self):
+        info = ModelInfo()
+        check(lib().wrk_model_info_get(self.handle, ctypes.byref(info)))
+        return info
+
+    def matrix_parts(self, layer, name):
+        """(kind, w, m, q) numpy arrays of a layer's matrix, for packing-parity checks."""
+        h = ctypes.c_void_p()
+        check(lib().wrk_model_matrix(self.handle, 0xFFFFFFFF if layer is None else layer, name.encode(),
+                                     ctypes.byref(h)))
+        lib().wrk_matrix_parts  # borrowed handle: wrap without taking ownership of the matrix
+        m = Matrix(self.ctx, None)
+        m.handle = h
+        try:
+            kind, w, mm, q = m.parts()
+            return kind, w.numpy(), (mm.numpy() if mm is not None else None), (q.numpy() if q is not None else None)
+        finally:
+            m.handle = None
+
+
+class RnnInput:
+    """`RnnInput` (src/runtime/infer/rnn.rs:194-253)."""
+
+    def __init__(self, batches, token_chunk_size):
+        """batches: list of (tokens, option) with option RNN_LAST or RNN_FULL."""
+        self.handle = ctypes.c_void_p()
+        self.num_batch = len(batches)
+        check(lib().wrk_rnn_input_create(len(batches), token_chunk_size, ctypes.byref(self.handle)))
+        for b, (tokens, option) in enumerate(batches):
+            check(lib().wrk_rnn_input_set_option(self.handle, b, option))
+            self.append(b, tokens)
+
+    def __del__(self):
+        if getattr(self, "handle", None):
+            lib().wrk_rnn_input_destroy(self.handle)
+            self.handle = None
+
+    def append(self, batch, tokens):
+        arr = np.ascontiguousarray(tokens, dtype=np.uint32)
+        check(lib().wrk_rnn_input_append(self.handle, batch, arr.ctypes.data_as(ctypes.c_void_p),
+                                         ctypes.c_size_t(arr.size)))
+
+    @property
+    def token_chunk_size(self):
+        v = ctypes.c_uint32()
+        check(lib().wrk_rnn_input_token_chunk_size(self.handle, ctypes.byref(v)))
+        return v.value
+
+    def num_token(self):
+        v = ctypes.c_uint64()
+        check(lib().wrk_rnn_input_num_token(self.handle, ctypes.byref(v)))
+        return v.value
+
+    def remaining(self, batch):
+        v = ctypes.c_uint64()
+        check(lib().wrk_rnn_input_remaining(self.handle, batch, ctypes.byref(v)))
+        return v.value
+
+    def step(self):
+        check(lib().wrk_rnn_input_step(self.handle))
+
+    def iter(self):
+        return RnnIter(self)
+
+
+class RnnIter:
+    def __init__(self, inp):
+        self.num_batch = inp.num_batch
+        self.handle = ctypes.c_void_p()
+        check(lib().wrk_rnn_iter_create(inp.handle, ctypes.byref(self.handle)))
+
+    def __del__(self):
+        if getattr(self, "handle", None):
+            lib().wrk_rnn_iter_destroy(self.handle)
+            self.handle = None
+
+    def next(self):
+        """[(len, option)] per batch; option RNN_NONE stands for None."""
+        lens = (ctypes.c_uint32 * self.num_batch)()
+        opts = (ctypes.c_int32 * self.num_batch)()
+        check(lib().wrk_rnn_iter_next(self.handle, lens, opts))
+        return [(lens[i], opts[i]) for i in range(self.num_batch)]
+
+
+def redirect(info):
+    """RnnInfo::redirect → (headers, inputs, outputs)."""
+    n = len(info)
+    lens = (ctypes.c_uint32 * n)(*[l for l, _ in info])
+    opts = (ctypes.c_int32 * n)(*[o for _, o in info])
+    total = sum(l for l, _ in info)
+    headers = (ctypes.c_uint32 * max(total, 1))()
+    nh = ctypes.c_uint32()
+    inputs = (ctypes.c_uint32 * (2 * n))()
+    outputs = (ctypes.c_uint32 * (2 * n))()
+    check(lib().wrk_rnn_redirect(lens, opts, n, headers, ctypes.byref(nh), inputs, outputs))
+    return (list(headers[: nh.value]), [(inputs[2 * i], inputs[2 * i + 1]) for i in range(n)],
+            [(outputs[2 * i], outputs[2 * i + 1]) for i in range(n)])
+
+
+class Bundle:
+    """`Bundle<f16>` + `State` (src/runtime/v6.rs:489-521, src/runtime/model.rs:78-120)."""
+
+    def __init__(self, model, num_batch):
+        self.model, self.num_batch = model, num_batch
+        self.handle = ctypes.c_void_p()
+        check(lib().wrk_bundle_create(model.handle, num_batch, ctypes.byref(self.handle)))
+        info = model.info
+        self.vocab = (info.num_vocab + 7) // 8 * 8 if info.version != 5 else info.num_vocab
+
+    def __del__(self):
+        if getattr(self, "handle", None):
+            lib().wrk_bundle_release(self.handle)
+            self.handle = None
+
+    def set_packed_cursors(self, packed):
+        check(lib().wrk_bundle_set_packed_cursors(self.handle, int(packed)))
+
+    def set_use_graph(self, use):
+        check(lib().wrk_bundle_set_use_graph(self.handle, int(use)))
+
+    def set_fused(self, fused):
+        check(lib().wrk_bundle_set_fused(self.handle, int(fused)))
+
+    def state_shape(self):
+        s = (ctypes.c_uint32 * 4)()
+        check(lib().wrk_state_init_shape(self.handle, s))
+        return list(s)
+
+    def state_back(self, batch):
+        s = self.state_shape()
+        arr = np.empty((s[2], s[1], s[0]), dtype=np.float32)
+        check(lib().wrk_state_back(self.handle, batch, arr.ctypes.data_as(ctypes.c_void_p), ctypes.c_size_t(arr.nbytes)))
+        return arr
+
+    def state_load(self, arr, batch):
+        arr = np.ascontiguousarray(arr, dtype=np.float32)
+        check(lib().wrk_state_load(self.handle, arr.ctypes.data_as(ctypes.c_void_p), ctypes.c_size_t(arr.nbytes), batch))
+
+    def dispatch(self, info):
+        lens = (ctypes.c_uint32 * self.num_batch)(*[l for l, _ in info])
+        opts = (ctypes.c_int32 * self.num_batch)(*[o for _, o in info])
+        h = ctypes.c_void_p()
+        check(lib().wrk_bundle_dispatch(self.handle, lens, opts, ctypes.byref(h)))
+        return Job(self, h, sum(l for l, _ in info))
+
+    def infer(self, inp, logits=None):
+        """SimpleRuntime::infer: returns per batch an array (rows, vocab) of fp32 logits (0 rows if none)."""
+        if logits is None:
+            logits = np.empty((max(inp.token_chunk_size, 1), self.vocab), dtype=np.float32)
+        outs = (ctypes.c_uint32 * (2 * self.num_batch))()
+        nh = ctypes.c_uint32()
+        check(lib().wrk_runtime_infer(self.handle, inp.handle, logits.ctypes.data_as(ctypes.c_void_p),
+                                      ctypes.c_size_t(logits.size), outs, ctypes.byref(nh)))
+        return [logits[outs[2 * i]: outs[2 * i + 1]] for i in range(self.num_batch)]
+
+
+class Job:
+    def __init__(self, bundle, handle, num_token):
+        self.bundle, self.handle, self.num_token = bundle, handle, num_token
+
+    def __del__(self):
+        if getattr(self, "handle", None):
+            lib().wrk_job_release(self.handle)
+            self.handle = None
+
+    def load(self, tokens):
+        arr = np.ascontiguousarray(tokens, dtype=np.uint32)
+        check(lib().wrk_job_load(self.handle, arr.ctypes.data_as(ctypes.c_void_p), ctypes.c_size_t(arr.size)))
+
+    def submit(self):
+        check(lib().wrk_job_submit(self.handle))
+
+    def back(self, logits=None):
+        nb = self.bundle.num_batch
+        if logits is None:
+            logits = np.empty((max(self.num_token, 1), self.bundle.vocab), dtype=np.float32)
+        outs = (ctypes.c_uint32 * (2 * nb))()
+        nh = ctypes.c_uint32()
+        check(lib().wrk_job_back(self.handle, logits.ctypes.data_as(ctypes.c_void_p), ctypes.c_size_t(logits.size),
+                                 outs, ctypes.byref(nh)))
+        return [logits[outs[2 * i]: outs[2 * i + 1]] for i in range(nb)]
+
+    def num_kernels(self):
+        n = ctypes.c_uint64()
+        check(lib().wrk_job_num_kernels(self.handle, ctypes.byref(n)))
+        return n.value
