@@ -97,10 +97,16 @@ int32_t wrk_rnn_redirect(const uint32_t* lens, const int32_t* options, uint32_t 
 int32_t wrk_bundle_dispatch(wrk_bundle* b, const uint32_t* lens, const int32_t* options, wrk_job** out);
 /* Job::load: the chunk's tokens, batch after batch (sum(lens) entries). */
 int32_t wrk_job_load(wrk_job* job, const uint32_t* tokens, size_t count);
+/* Job::load for `Token::Embed` inputs (src/runtime/infer/mod.rs:21-25) that already live on the device:
+ * rows [row0, row0 + num_token) of `embeds` ([num_emb, rows] fp16) become the job's input; cursors are
+ * uploaded as in wrk_job_load.  Stream ordered, no host synchronisation. */
+int32_t wrk_job_load_embed(wrk_job* job, wrk_tensor* embeds, uint32_t row0);
 int32_t wrk_job_submit(wrk_job* job);
 /* Job::back: waits, copies the [num_vocab_padded, num_header] f32 logits to `logits` (capacity in
  * floats) and reports per batch the [start, end) header rows (2 * num_batch entries). */
 int32_t wrk_job_back(wrk_job* job, float* logits, size_t capacity, uint32_t* outputs, uint32_t* num_headers);
+/* The job's logits tensor [num_vocab_padded, num_header] f32 on the device (borrowed). */
+int32_t wrk_job_output(wrk_job* job, wrk_tensor** out);
 int32_t wrk_job_num_kernels(const wrk_job* job, uint64_t* count);
 int32_t wrk_job_release(wrk_job* job);
 

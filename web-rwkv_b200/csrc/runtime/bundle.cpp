@@ -21,6 +21,7 @@ constexpr float LN_EPS = 1.0e-5f, GN_EPS = 64.0e-5f, L2_EPS = 1.0e-12f;
 
 struct Buffers {
     std::unordered_map<std::string, TensorH> t;
+    std::vector<uint32_t> cursor_lens;  // per-batch lens of the cursors currently held in t["cursors"]
     wrk_tensor* operator[](const char* name) const { return t.at(name).p; }
 };
 
@@ -606,27 +607,16 @@ int32_t wrk_bundle_dispatch(wrk_bundle* b, const uint32_t* lens, const int32_t* 
     return WRK_OK;
 }
 
-// Job::load, v6.rs:423-459
-int32_t wrk_job_load(wrk_job* job, const uint32_t* tokens, size_t count) {
-    WRK_REQUIRE(job && (tokens || count == 0), WRK_ERR_INVALID_ARGUMENT, "null argument");
+// cursors: one record per token, identical for all tokens of a sequence (tensor/mod.rs:47-85).
+// Jobs of the same shape carry the same cursors, so the upload is skipped when nothing changed.
+static int32_t upload_cursors(wrk_job* job) {
     wrk_bundle* b = job->bundle;
+    wrk_context* ctx = b->model->ctx;
     const uint32_t T = job->info.num_token();
-    WRK_REQUIRE(count == T, WRK_ERR_SIZE, "data size not match: %zu vs. %u", count, T);
-    if (T == 0) return WRK_OK;
-    std::lock_guard<std::mutex> lock(b->mutex);
-    wrk_model* m = b->model;
-    wrk_context* ctx = m->ctx;
-    const uint32_t C = m->info.num_emb;
+    CachedJob& cj = *job->job;
+    if (cj.buffer->cursor_lens == job->info.lens) return WRK_OK;
     WRK_TRY(ensure_staging(b, T));
-    // the previous upload from the staging buffers must have been consumed
     WRK_CUDA(cudaStreamSynchronize(ctx->stream));
-    for (uint32_t t = 0; t < T; ++t) {
-        const uint32_t tok = tokens[t];
-        WRK_REQUIRE(tok < m->num_vocab_padded, WRK_ERR_INVALID_ARGUMENT, "token %u out of vocabulary %u", tok,
-                    m->num_vocab_padded);
-        std::memcpy(b->stage_input + (size_t)t * C, m->embed_host + (size_t)tok * C, (size_t)C * 2);
-    }
-    // cursors: one record per token, identical for all tokens of a sequence (tensor/mod.rs:47-85)
     uint32_t p = 0;
     for (uint32_t batch = 0; batch < b->num_batch; ++batch) {
         const uint32_t len = job->info.lens[batch];
@@ -641,9 +631,64 @@ int32_t wrk_job_load(wrk_job* job, const uint32_t* tokens, size_t count) {
         }
         p += len;
     }
-    const Buffers& B = *job->job->buffer;
+    const Buffers& B = *cj.buffer;
     WRK_CUDA(cudaMemcpyAsync(B["cursors"]->ptr(), b->stage_cursors, (b->packed_cursors ? T : 3 * T) * sizeof(uint32_t),
                              cudaMemcpyHostToDevice, ctx->stream));
+    WRK_CUDA(cudaStreamSynchronize(ctx->stream));  // the staging buffer is reused by the next job
+    cj.buffer->cursor_lens = job->info.lens;
+    return WRK_OK;
+}
+
+int32_t wrk_job_load_embed(wrk_job* job, wrk_tensor* embeds, uint32_t row0) {
+    WRK_REQUIRE(job && embeds, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    wrk_bundle* b = job->bundle;
+    const uint32_t T = job->info.num_token();
+    if (T == 0) return WRK_OK;
+    std::lock_guard<std::mutex> lock(b->mutex);
+    wrk_model* m = b->model;
+    const uint32_t C = m->info.num_emb;
+    WRK_REQUIRE(embeds->dtype == WRK_F16, WRK_ERR_TYPE, "data type mismatch: embeds must be f16");
+    WRK_REQUIRE(embeds->shape[0] == C, WRK_ERR_SHAPE, "tensor shape not match (embeds): row length %u vs. %u",
+                embeds->shape[0], C);
+    if ((size_t)row0 + T > embeds->len() / C)
+        return set_error(WRK_ERR_SLICE_OUT_OF_RANGE, "slice %u..%u out of range for dimension size %zu", row0, row0 + T,
+                         embeds->len() / C);
+    WRK_TRY(upload_cursors(job));
+    const Buffers& B = *job->job->buffer;
+    WRK_CUDA(cudaMemcpyAsync(B["input"]->ptr(), static_cast<const uint16_t*>(embeds->ptr()) + (size_t)row0 * C,
+                             (size_t)T * C * 2, cudaMemcpyDeviceToDevice, m->ctx->stream));
+    return WRK_OK;
+}
+
+int32_t wrk_job_output(wrk_job* job, wrk_tensor** out) {
+    WRK_REQUIRE(job && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(job->job->header, WRK_ERR_EMPTY, "list must not be empty: the job has no output");
+    *out = (*job->job->header)["head_o"];
+    return WRK_OK;
+}
+
+// Job::load, v6.rs:423-459
+int32_t wrk_job_load(wrk_job* job, const uint32_t* tokens, size_t count) {
+    WRK_REQUIRE(job && (tokens || count == 0), WRK_ERR_INVALID_ARGUMENT, "null argument");
+    wrk_bundle* b = job->bundle;
+    const uint32_t T = job->info.num_token();
+    WRK_REQUIRE(count == T, WRK_ERR_SIZE, "data size not match: %zu vs. %u", count, T);
+    if (T == 0) return WRK_OK;
+    std::lock_guard<std::mutex> lock(b->mutex);
+    wrk_model* m = b->model;
+    wrk_context* ctx = m->ctx;
+    const uint32_t C = m->info.num_emb;
+    WRK_TRY(ensure_staging(b, T));
+    WRK_TRY(upload_cursors(job));
+    // the previous upload from the staging buffers must have been consumed
+    WRK_CUDA(cudaStreamSynchronize(ctx->stream));
+    for (uint32_t t = 0; t < T; ++t) {
+        const uint32_t tok = tokens[t];
+        WRK_REQUIRE(tok < m->num_vocab_padded, WRK_ERR_INVALID_ARGUMENT, "token %u out of vocabulary %u", tok,
+                    m->num_vocab_padded);
+        std::memcpy(b->stage_input + (size_t)t * C, m->embed_host + (size_t)tok * C, (size_t)C * 2);
+    }
+    const Buffers& B = *job->job->buffer;
     WRK_CUDA(cudaMemcpyAsync(B["input"]->ptr(), b->stage_input, (size_t)T * C * 2, cudaMemcpyHostToDevice, ctx->stream));
     return WRK_OK;
 }

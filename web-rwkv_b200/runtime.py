@@ -255,3 +255,15 @@ class Job:
         n = ctypes.c_uint64()
         check(lib().wrk_job_num_kernels(self.handle, ctypes.byref(n)))
         return n.value
+
+
+def job_load_embed(job, embeds, row0):
+    """Job::load for device-resident `Token::Embed` rows."""
+    check(lib().wrk_job_load_embed(job.handle, embeds.handle, row0))
+
+
+def job_output(job):
+    h = ctypes.c_void_p()
+    check(lib().wrk_job_output(job.handle, ctypes.byref(h)))
+    check(lib().wrk_tensor_retain(h))
+    return Tensor(job.bundle.model.ctx, h)
