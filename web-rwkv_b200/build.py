@@ -20,6 +20,7 @@ SOURCES = [
     "kernels/matmul.cu",
     "kernels/wkv.cu",
     "kernels/support.cu",
+    "kernels/decode.cu",
     "runtime/rnn.cpp",
     "runtime/model.cpp",
     "runtime/bundle.cpp",

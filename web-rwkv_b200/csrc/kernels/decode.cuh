@@ -1,0 +1,107 @@
+// Fused decode path (few tokens per job): argument blocks of the kernels in decode.cu.
+#pragma once
+
+#include "kernels.h"
+
+namespace wrk {
+namespace k {
+
+constexpr int kMaxProblems = 5;
+constexpr int kDecodeMaxTokens = 8;  // one MMA n-tile
+
+// One weight matrix of a grouped weight-streaming launch: out[t][m] = epilogue(act(W[m,:] . x[t,:])).
+struct GemvProblem {
+    const uint8_t* w;      // rows of K elements (fp16: 2K bytes, Int8: K bytes, NF4: K/2 bytes)
+    const __half* scale;   // Int8 (min, max) per 128; NF4 absmax per 64; fp16: null
+    int32_t kind;          // MatKind
+    uint32_t K, M;
+    const __half* x;       // [T][K] fp16; null = take prologue vector x_sel
+    int32_t x_sel;
+    void* out;             // [T][M]
+    int32_t out_dtype;
+    int32_t act;
+};
+
+enum GemvPrologue { PRO_NONE = 0, PRO_LN = 1, PRO_LN_SHIFT1 = 2, PRO_LN_SHIFT2 = 3 };
+enum GemvEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_CHANNEL_MIX = 2 };
+
+// Row range of one problem handled by a CTA.
+struct GemvSegment {
+    int32_t problem, row0, row1, pad;
+};
+constexpr int kSegmentsPerCta = 3;
+
+struct FusedGemvArgs {
+    GemvProblem p[kMaxProblems];
+    int32_t num_problems;
+    uint32_t T;
+    const GemvSegment* segments;  // [grid][kSegmentsPerCta], row0 == row1 marks an unused entry
+    const float* table;           // NF4 code book (device)
+    int32_t* status;
+    // prologue: layer norm of `ln_x` (+ token shift against the carry row `state`)
+    int32_t prologue;
+    const __half* ln_x;           // [T][C] residual stream
+    const __half* ln_w;
+    const __half* ln_b;
+    float ln_eps;
+    uint32_t C;
+    const uint32_t* cursors;
+    int32_t wide;
+    DView state;                  // f32 carry row (row 0 of the view)
+    const __half* mix0;           // [C] token-shift factors of prologue vector 0 / 1
+    const __half* mix1;
+    int32_t reversed;
+    __half* ln_out;               // [T][C] normalised rows, written by CTA 0 (null = skip)
+    // epilogue
+    int32_t epilogue;
+    __half* xres;                 // [T][M] residual stream updated in place
+    const __half* cm_r;           // channel mix: receptance [T][M]
+    const __half* cm_x;           // channel mix: normalised ffn input [T][M] (becomes the carry row)
+    DView cm_state;
+    float rescale;                // 1.0 or 0.5 applied to the residual stream after the add
+};
+
+cudaError_t fused_gemv(const FusedGemvArgs& a, int grid, cudaStream_t stream);
+size_t fused_gemv_smem(uint32_t T, uint32_t Kmax, uint32_t C, int prologue);
+
+// v6 data-dependent token shift: time_mix_w2 (5 x [D -> C]) + static mixes + 5-way shift.
+struct TmixArgs {
+    const __half* w2;        // [5][C][D] fp16
+    const __half* tmx;       // [T][5 * D] fp16 (tanh'ed adapter activations)
+    const __half* mix;       // [5][C] static mixes
+    const __half* att_x;     // [T][C] normalised input
+    const uint32_t* cursors;
+    int32_t wide;
+    DView state;             // carry row
+    __half* sx;              // [5][T][C]
+    uint32_t C, D, T;
+};
+cudaError_t tmix_shift_v6(const TmixArgs& a, cudaStream_t stream);
+
+// v5 / v6 time-mix block: decay adapter (v6), WKV recurrence, group norm, gate.
+struct Wkv6Args {
+    const uint32_t* cursors;
+    int32_t wide;
+    DView state;             // f32 [C, S + 1, B]
+    uint32_t H, T, B;
+    int32_t per_token_decay; // v6
+    const __half* tdw;       // v6: [T][D] tanh'ed decay adapter activations
+    const __half* td_w2;     // v6: [C][D] fp16
+    const __half* td0;       // v6: [C] fp16 static decay
+    const float* td5;        // v5: [C] f32 decay, already exp(-exp(.))
+    uint32_t D;
+    const float* time_first; // [C]
+    const float* k;          // [T][C] f32
+    const float* v;
+    const float* r;
+    const __half* g;         // [T][C] fp16 gate pre-activation
+    const __half* att_x;     // [T][C] normalised input (carry source)
+    const __half* gn_w;      // [C]
+    const __half* gn_b;
+    float gn_eps;
+    __half* out;             // [T][C] gated output
+};
+cudaError_t wkv56_fused(const Wkv6Args& a, cudaStream_t stream);
+
+}  // namespace k
+}  // namespace wrk

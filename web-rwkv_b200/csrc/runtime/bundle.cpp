@@ -10,6 +10,7 @@
 #include <cstring>
 #include <list>
 
+#include "../kernels/decode.cuh"
 #include "runtime.h"
 
 using namespace wrk;
@@ -31,6 +32,7 @@ struct CachedJob {
     wrk_commands* commands = nullptr;
     uint32_t num_token = 0, num_header = 0;
     uint64_t tick = 0;
+    std::vector<TensorH> tables;  // per-launch row partitions of the fused path
     ~CachedJob() {
         if (commands) wrk_commands_release(commands);
     }
@@ -370,6 +372,288 @@ int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, 
     return WRK_OK;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Fused v6 job for a few tokens (decode): seven weight-streaming launches per layer, chained with
+// programmatic dependent launch.  Same arithmetic and fp16 rounding points as the op-by-op list.
+// ---------------------------------------------------------------------------------------------
+
+struct MatInfo {
+    int kind;
+    const uint8_t* w;
+    const __half* scale;
+    const float* table;
+    uint32_t K, M;
+};
+
+MatInfo mat_info(wrk_matrix* m) {
+    MatInfo r{};
+    r.kind = m->kind == 0 ? k::MAT_FP16 : m->kind == 1 ? k::MAT_INT8 : k::MAT_NF4;
+    r.w = static_cast<const uint8_t*>(m->w->ptr());
+    r.scale = m->m ? static_cast<const __half*>(m->m->ptr()) : nullptr;
+    r.table = m->q ? static_cast<const float*>(m->q->ptr()) : nullptr;
+    r.K = m->kind == 2 ? m->w->shape[0] * 2 : m->w->shape[0];
+    r.M = m->w->shape[1];
+    return r;
+}
+
+bool mat_fusable(const MatInfo& m) {
+    const uint32_t need = m.kind == k::MAT_INT8 ? 128 : m.kind == k::MAT_NF4 ? 64 : 32;
+    return m.K % need == 0 && m.K % 8 == 0;
+}
+
+k::GemvProblem problem(const MatInfo& m, const __half* x, int x_sel, void* out, int out_dtype, int act) {
+    k::GemvProblem p{};
+    p.w = m.w;
+    p.scale = m.scale;
+    p.kind = m.kind;
+    p.K = m.K;
+    p.M = m.M;
+    p.x = x;
+    p.x_sel = x_sel;
+    p.out = out;
+    p.out_dtype = out_dtype;
+    p.act = act;
+    return p;
+}
+
+// Cuts the concatenated rows of the launch's matrices into one contiguous range per CTA, balanced by
+// weight bytes, and uploads the table.
+int32_t make_partition(wrk_context* ctx, k::FusedGemvArgs& a, int grid, CachedJob* job) {
+    std::vector<k::GemvSegment> table((size_t)grid * k::kSegmentsPerCta, k::GemvSegment{0, 0, 0, 0});
+    double total = 0;
+    std::vector<double> cost(a.num_problems);
+    for (int i = 0; i < a.num_problems; ++i) {
+        const k::GemvProblem& p = a.p[i];
+        cost[i] = p.kind == k::MAT_FP16 ? p.K * 2.0 : p.kind == k::MAT_INT8 ? p.K * 1.03125 : p.K * 0.53125;
+        total += cost[i] * p.M;
+    }
+    int prob = 0;
+    uint32_t row = 0;
+    double done = 0;
+    for (int c = 0; c < grid; ++c) {
+        const double target = total * (c + 1) / grid;
+        int nseg = 0;
+        while (prob < a.num_problems && nseg < k::kSegmentsPerCta) {
+            const k::GemvProblem& p = a.p[prob];
+            uint32_t take = (uint32_t)std::max(0.0, std::ceil((target - done) / cost[prob] - 1e-9));
+            if (c == grid - 1) take = p.M - row;  // the last CTA takes whatever is left
+            take = std::min(take, p.M - row);
+            if (take > 0) {
+                table[(size_t)c * k::kSegmentsPerCta + nseg] = k::GemvSegment{prob, (int32_t)row, (int32_t)(row + take), 0};
+                ++nseg;
+                row += take;
+                done += take * cost[prob];
+            }
+            if (row == p.M) {
+                ++prob;
+                row = 0;
+                if (c == grid - 1) continue;
+            }
+            if (done >= target - 1e-6 && c != grid - 1) break;
+        }
+    }
+    WRK_REQUIRE(prob == a.num_problems, WRK_ERR_UNSUPPORTED, "row partition overflow: too many small matrices per CTA");
+    const uint32_t shape[4] = {(uint32_t)(table.size() * 4), 1, 1, 1};
+    wrk_tensor* t = nullptr;
+    WRK_TRY(wrk_tensor_from_data(ctx, WRK_U32, shape, table.data(), table.size() * sizeof(k::GemvSegment), &t));
+    job->tables.emplace_back(t);
+    a.segments = static_cast<const k::GemvSegment*>(t->ptr());
+    return WRK_OK;
+}
+
+int32_t add_fused_gemv(wrk_context* ctx, OpList& ops, CachedJob* job, k::FusedGemvArgs a, const char* name,
+                       std::initializer_list<const wrk_tensor*> keep) {
+    const int grid = ctx->num_sms;
+    a.status = ctx->device_status;
+    for (int i = 0; i < a.num_problems; ++i)
+        if (a.p[i].kind == k::MAT_NF4 && a.table == nullptr)
+            return set_error(WRK_ERR_INVALID_ARGUMENT, "NF4 problem without a code book");
+    WRK_TRY(make_partition(ctx, a, grid, job));
+    ops.ops.push_back(new_atom(name, [a, grid](cudaStream_t s) { return k::fused_gemv(a, grid, s); }, keep));
+    return WRK_OK;
+}
+
+const __half* H(wrk_tensor* t) { return static_cast<const __half*>(t->ptr()); }
+__half* Hm(wrk_tensor* t) { return static_cast<__half*>(t->ptr()); }
+
+bool fused_v6_supported(wrk_bundle* bd, uint32_t T) {
+    const wrk_model_info& info = bd->model->info;
+    if (!bd->fused || info.version != 6 || T == 0 || T > (uint32_t)k::kDecodeMaxTokens) return false;
+    if (info.num_emb / info.num_head != 64 || info.num_emb % 128 || info.custom[0] % 8 || info.custom[0] > 64 ||
+        info.custom[1] % 8 || info.custom[1] > 64)
+        return false;
+    for (auto& L : bd->model->layers)
+        for (wrk_matrix* m : {L.att_w_k.p, L.att_w_v.p, L.att_w_r.p, L.att_w_g.p, L.att_w_o.p, L.ffn_w_k.p, L.ffn_w_v.p,
+                              L.ffn_w_r.p, L.time_mix_w1.p, L.time_decay_w1.p})
+            if (!mat_fusable(mat_info(m))) return false;
+    if (!mat_fusable(mat_info(bd->model->head_w))) return false;
+    const uint32_t kmax = std::max(info.num_emb, info.num_hidden);
+    return k::fused_gemv_smem(T, kmax, info.num_emb, k::PRO_NONE) <= 200 * 1024 &&
+           k::fused_gemv_smem(T, info.num_emb, info.num_emb, k::PRO_LN_SHIFT2) <= 200 * 1024;
+}
+
+int32_t layer_v6_fused(wrk_bundle* bd, OpList& ops, CachedJob* job, const Buffers& B, uint32_t index, uint32_t T) {
+    const wrk_model_info& info = bd->model->info;
+    wrk_context* ctx = bd->model->ctx;
+    const Layer& L = bd->model->layers[index];
+    const uint32_t C = info.num_emb, S = 64, F = info.num_hidden;
+    const uint32_t* cursors = static_cast<const uint32_t*>(B["cursors"]->ptr());
+    const int wide = bd->packed_cursors ? 0 : 1;
+    const DView st_att = make_dview(state_att(bd, index, S)), st_ffn = make_dview(state_ffn(bd, index, S));
+    const float* table = nullptr;
+    for (wrk_matrix* m : {L.att_w_k.p, L.att_w_o.p, L.ffn_w_k.p})
+        if (m->q) table = static_cast<const float*>(m->q->ptr());
+
+    // A: layer norm + shift(time_mix_x) -> adapter W1 (tanh)
+    {
+        k::FusedGemvArgs a{};
+        a.T = T;
+        a.C = C;
+        a.prologue = k::PRO_LN_SHIFT1;
+        a.ln_x = H(B["x"]);
+        a.ln_w = H(L.att_ln.w);
+        a.ln_b = H(L.att_ln.b);
+        a.ln_eps = LN_EPS;
+        a.cursors = cursors;
+        a.wide = wide;
+        a.state = st_att;
+        a.mix0 = H(L.time_mix_x);
+        a.reversed = 1;
+        a.ln_out = Hm(B["att_x"]);
+        a.num_problems = 1;
+        a.p[0] = problem(mat_info(L.time_mix_w1), nullptr, 0, B["time_mix_x"]->ptr(), WRK_F16, WRK_ACT_TANH);
+        a.epilogue = k::EPI_STORE;
+        a.rescale = 1.0f;
+        WRK_TRY(add_fused_gemv(ctx, ops, job, a, "fused_ln_shift_adapter", {B["x"], B["att_x"], B["time_mix_x"], L.time_mix_w1.p->w}));
+    }
+    // B: adapter W2 + static mixes + five-way token shift
+    {
+        k::TmixArgs a{};
+        a.w2 = H(L.time_mix_w2.p->w);
+        a.tmx = H(B["time_mix_x"]);
+        a.mix = H(L.time_mix);
+        a.att_x = H(B["att_x"]);
+        a.cursors = cursors;
+        a.wide = wide;
+        a.state = st_att;
+        a.sx = Hm(B["att_sx"]);
+        a.C = C;
+        a.D = info.custom[0];
+        a.T = T;
+        ops.ops.push_back(new_atom("fused_tmix_shift", [a](cudaStream_t s) { return k::tmix_shift_v6(a, s); },
+                                   {B["time_mix_x"], B["att_x"], B["att_sx"], L.time_mix_w2.p->w, L.time_mix.p}));
+    }
+    // C: key / value / receptance / gate + decay adapter W1 in one launch
+    {
+        const __half* sx = H(B["att_sx"]);
+        const size_t plane = (size_t)T * C;
+        k::FusedGemvArgs a{};
+        a.T = T;
+        a.C = C;
+        a.prologue = k::PRO_NONE;
+        a.table = table;
+        a.num_problems = 5;
+        a.p[0] = problem(mat_info(L.att_w_k), sx + 1 * plane, 0, B["att_k"]->ptr(), WRK_F32, WRK_ACT_NONE);
+        a.p[1] = problem(mat_info(L.att_w_v), sx + 2 * plane, 0, B["att_v"]->ptr(), WRK_F32, WRK_ACT_NONE);
+        a.p[2] = problem(mat_info(L.att_w_r), sx + 3 * plane, 0, B["att_r"]->ptr(), WRK_F32, WRK_ACT_NONE);
+        a.p[3] = problem(mat_info(L.att_w_g), sx + 4 * plane, 0, B["att_g"]->ptr(), WRK_F16, WRK_ACT_NONE);
+        a.p[4] = problem(mat_info(L.time_decay_w1), sx, 0, B["att_w"]->ptr(), WRK_F16, WRK_ACT_TANH);
+        a.epilogue = k::EPI_STORE;
+        a.rescale = 1.0f;
+        WRK_TRY(add_fused_gemv(ctx, ops, job, a, "fused_att_linear",
+                               {B["att_sx"], B["att_k"], B["att_v"], B["att_r"], B["att_g"], B["att_w"]}));
+    }
+    // D: decay adapter W2 + WKV + group norm + gate
+    {
+        k::Wkv6Args a{};
+        a.cursors = cursors;
+        a.wide = wide;
+        a.state = st_att;
+        a.H = info.num_head;
+        a.T = T;
+        a.B = bd->num_batch;
+        a.per_token_decay = 1;
+        a.tdw = H(B["att_w"]);
+        a.td_w2 = H(L.time_decay_w2.p->w);
+        a.td0 = H(L.time_decay);
+        a.D = info.custom[1];
+        a.time_first = static_cast<const float*>(L.time_first.p->ptr());
+        a.k = static_cast<const float*>(B["att_k"]->ptr());
+        a.v = static_cast<const float*>(B["att_v"]->ptr());
+        a.r = static_cast<const float*>(B["att_r"]->ptr());
+        a.g = H(B["att_g"]);
+        a.att_x = H(B["att_x"]);
+        a.gn_w = H(L.gn.w);
+        a.gn_b = H(L.gn.b);
+        a.gn_eps = GN_EPS;
+        a.out = Hm(B["att_xx"]);
+        ops.ops.push_back(new_atom("fused_wkv6", [a](cudaStream_t s) { return k::wkv56_fused(a, s); },
+                                   {B["att_w"], B["att_k"], B["att_v"], B["att_r"], B["att_g"], B["att_x"], B["att_xx"],
+                                    bd->state[index].p}));
+    }
+    // E: output projection + residual
+    {
+        k::FusedGemvArgs a{};
+        a.T = T;
+        a.C = C;
+        a.prologue = k::PRO_NONE;
+        a.table = table;
+        a.num_problems = 1;
+        a.p[0] = problem(mat_info(L.att_w_o), H(B["att_xx"]), 0, nullptr, WRK_F16, WRK_ACT_NONE);
+        a.epilogue = k::EPI_RESIDUAL;
+        a.xres = Hm(B["x"]);
+        a.rescale = 1.0f;
+        WRK_TRY(add_fused_gemv(ctx, ops, job, a, "fused_att_out", {B["att_xx"], B["x"]}));
+    }
+    // F: layer norm + two shifts -> ffn key (squared ReLU) and receptance
+    {
+        k::FusedGemvArgs a{};
+        a.T = T;
+        a.C = C;
+        a.prologue = k::PRO_LN_SHIFT2;
+        a.table = table;
+        a.ln_x = H(B["x"]);
+        a.ln_w = H(L.ffn_ln.w);
+        a.ln_b = H(L.ffn_ln.b);
+        a.ln_eps = LN_EPS;
+        a.cursors = cursors;
+        a.wide = wide;
+        a.state = st_ffn;
+        a.mix0 = H(L.ffn_time_mix_k);
+        a.mix1 = H(L.ffn_time_mix_r);
+        a.reversed = 1;
+        a.ln_out = Hm(B["ffn_x"]);
+        a.num_problems = 2;
+        a.p[0] = problem(mat_info(L.ffn_w_k), nullptr, 0, B["ffn_k"]->ptr(), WRK_F16, WRK_ACT_SQUARED_RELU);
+        a.p[1] = problem(mat_info(L.ffn_w_r), nullptr, 1, B["ffn_r"]->ptr(), WRK_F16, WRK_ACT_NONE);
+        a.epilogue = k::EPI_STORE;
+        a.rescale = 1.0f;
+        WRK_TRY(add_fused_gemv(ctx, ops, job, a, "fused_ffn_in", {B["x"], B["ffn_x"], B["ffn_k"], B["ffn_r"]}));
+    }
+    // G: ffn value + channel mix + residual (+ rescale)
+    {
+        k::FusedGemvArgs a{};
+        a.T = T;
+        a.C = C;
+        a.prologue = k::PRO_NONE;
+        a.table = table;
+        a.cursors = cursors;
+        a.wide = wide;
+        a.num_problems = 1;
+        a.p[0] = problem(mat_info(L.ffn_w_v), H(B["ffn_k"]), 0, nullptr, WRK_F16, WRK_ACT_NONE);
+        a.epilogue = k::EPI_CHANNEL_MIX;
+        a.xres = Hm(B["x"]);
+        a.cm_r = H(B["ffn_r"]);
+        a.cm_x = H(B["ffn_x"]);
+        a.cm_state = st_ffn;
+        a.rescale = (index + 1) % bd->model->rescale == 0 ? 0.5f : 1.0f;
+        WRK_TRY(add_fused_gemv(ctx, ops, job, a, "fused_ffn_out", {B["ffn_k"], B["ffn_r"], B["ffn_x"], B["x"], bd->state[index].p}));
+    }
+    (void)F;
+    return WRK_OK;
+}
+
 // Bundle::dispatch body (v6.rs:586-697) for a job with at least one token.
 int32_t build_job(wrk_bundle* bd, const RnnInfo& info, CachedJob* job) {
     wrk_model* m = bd->model;
@@ -381,8 +665,10 @@ int32_t build_job(wrk_bundle* bd, const RnnInfo& info, CachedJob* job) {
     // embed: layer norm on the uploaded rows, then copy into x
     ADD(wrk_op_layer_norm(m->embed_ln.w, m->embed_ln.b, B["input"], LN_EPS, &_o));
     WRK_TRY(blit(ops, V(B["input"]), V(B["x"])));
+    const bool fused = fused_v6_supported(bd, T);
     for (uint32_t i = 0; i < m->info.num_layer; ++i) {
-        if (m->info.version == 7) WRK_TRY(layer_v7(bd, ops, B, i, T));
+        if (fused) WRK_TRY(layer_v6_fused(bd, ops, job, B, i, T));
+        else if (m->info.version == 7) WRK_TRY(layer_v7(bd, ops, B, i, T));
         else WRK_TRY(layer_v56(bd, ops, B, i, T));
         if ((i + 1) % m->sep == 0) ADD(wrk_op_sep(&_o));
     }
@@ -403,7 +689,22 @@ int32_t build_job(wrk_bundle* bd, const RnnInfo& info, CachedJob* job) {
             ++end;
         }
     }
-    if (NH > 0) {
+    if (NH > 0 && fused && NH <= (uint32_t)k::kDecodeMaxTokens) {
+        // layer norm as the prologue of the (fp16) head's weight-streaming launch
+        k::FusedGemvArgs a{};
+        a.T = NH;
+        a.C = m->info.num_emb;
+        a.prologue = k::PRO_LN;
+        a.ln_x = H(head_x);
+        a.ln_w = H(m->head_ln.w);
+        a.ln_b = H(m->head_ln.b);
+        a.ln_eps = LN_EPS;
+        a.num_problems = 1;
+        a.p[0] = problem(mat_info(m->head_w), nullptr, 0, Hd["head_o"]->ptr(), WRK_F32, WRK_ACT_NONE);
+        a.epilogue = k::EPI_STORE;
+        a.rescale = 1.0f;
+        WRK_TRY(add_fused_gemv(m->ctx, ops, job, a, "fused_head", {head_x, Hd["head_o"]}));
+    } else if (NH > 0) {
         ADD(wrk_op_layer_norm(m->head_ln.w, m->head_ln.b, head_x, LN_EPS, &_o));
         WRK_TRY(matmul(ops, m->head_w, V(head_x), V(Hd["head_o"]), WRK_ACT_NONE, NH % WRK_MIN_TOKEN_CHUNK_SIZE == 0));
     }
