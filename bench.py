@@ -346,7 +346,7 @@ def main():
         "gpu_launches": int(gpu_launches),
         "kernels_per_token": int(kernels_per_token),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": peak_kind, "traffic": traffic, "kernel": "matmul_mma_kernel<int8> (T = 1)",
+                     "peak_kind": peak_kind, "traffic": traffic, "kernel": "fused_gemv_kernel (Int8 weights, T = 1, standalone launches)",
                      "algorithmic_bytes_per_launch": bytes_per_launch, "us_per_launch": sec_per_launch * 1e6,
                      "launches_timed": launches * 20},
         "decode_step": {"algorithmic_bytes_per_token": total_bytes, "gemv_share": gemv_bytes / total_bytes,

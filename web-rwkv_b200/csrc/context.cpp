@@ -513,3 +513,11 @@ int32_t wrk_run(wrk_context* ctx, wrk_op* op) {
 }
 
 }  // extern "C"
+
+#ifdef WRK_TRACE
+namespace wrk { namespace k { cudaError_t debug_trace_read(unsigned long long* host, unsigned int* n); } }
+extern "C" int32_t wrk_debug_trace_read(unsigned long long* host, unsigned int* n) {
+    WRK_CUDA(wrk::k::debug_trace_read(host, n));
+    return WRK_OK;
+}
+#endif

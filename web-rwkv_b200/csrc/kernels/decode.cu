@@ -6,8 +6,8 @@
 //   * fused_gemv_kernel is a grouped weight-streaming kernel.  A launch covers several matrices (e.g.
 //     key / value / receptance / gate + the decay adapter); the concatenated row space is cut into one
 //     contiguous row range per CTA (balanced by bytes, one CTA per SM slot), and each CTA pulls its rows
-//     into shared memory with 1-D TMA bulk copies (cp.async.bulk + mbarrier complete_tx), 16 rows x 2 KB
-//     per slot, two slots in flight.
+//     into shared memory with 1-D TMA bulk copies (cp.async.bulk + mbarrier complete_tx), 16 rows x 1 KB
+//     (+ their block scales) per slot, four or more slots in flight.
 //   * every kernel here is launched with programmatic dependent launch: it signals its dependents at
 //     once, issues the TMA copies of its first weight tiles, and only then executes griddepcontrol.wait.
 //     Weights are never written during a job, so the next kernel's weights are already landing in shared
@@ -28,10 +28,11 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = 8;
-constexpr int PB = 2048;          // bytes of one weight row per tile part
+constexpr int PB = 1024;          // bytes of one weight row per tile part
 constexpr int PITCH = PB + 16;    // shared-memory row pitch: consecutive rows shift by one 16-byte bank group
-constexpr int SLOT = 16 * PITCH;  // one tile part: 16 rows
-constexpr int NSLOT = 2;
+constexpr int SCP = 80;           // pitch of a row's scales inside a slot (<= 64 bytes of data)
+constexpr int SLOT = 16 * PITCH + 16 * SCP;  // one tile part: 16 rows of weights, then their scales
+constexpr int MAX_SLOTS = 6;
 constexpr int GROUP_ROWS = 64;    // rows accumulated in registers at a time (4 MMA row tiles)
 constexpr uint32_t kSpinLimit = 1u << 22;
 
@@ -39,6 +40,25 @@ constexpr uint32_t kSpinLimit = 1u << 22;
 __host__ __device__ inline uint32_t sums_floats(uint32_t T, uint32_t kmax) {
     return (T * ((kmax + 127) / 128) + 3) / 4 * 4 + 4;
 }
+
+// Optional stage timestamps (builds with -DWRK_TRACE only): CTA 0 appends (stage, globaltimer ns).
+#ifdef WRK_TRACE
+__device__ unsigned long long g_trace[1 << 16];
+__device__ unsigned int g_trace_n;
+__device__ __forceinline__ void trace(int stage) {
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        const unsigned int i = atomicAdd(&g_trace_n, 1u);
+        if (i < (1u << 15)) {
+            g_trace[2 * i] = (unsigned long long)stage;
+            g_trace[2 * i + 1] = t;
+        }
+    }
+}
+#else
+__device__ __forceinline__ void trace(int) {}
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -94,6 +114,10 @@ __device__ __forceinline__ uint32_t bytes_to_half2(uint32_t w, uint32_t sel) {
 __device__ __forceinline__ uint32_t row_bytes(const GemvProblem& p) {
     return p.kind == MAT_FP16 ? p.K * 2 : p.kind == MAT_INT8 ? p.K : p.K / 2;
 }
+// scales can ride the TMA when every row's scale run starts on a 16-byte boundary
+__device__ __forceinline__ bool scales_by_tma(const GemvProblem& p) {
+    return p.K % 512 == 0 && (reinterpret_cast<uintptr_t>(p.scale) & 15) == 0;
+}
 __device__ __forceinline__ uint32_t part_elems(int kind) { return kind == MAT_FP16 ? PB / 2 : kind == MAT_INT8 ? PB : PB * 2; }
 
 // Position in a CTA's sequence of tile parts: segment -> group of <= 64 rows -> K part -> row tile.
@@ -142,9 +166,20 @@ __device__ __forceinline__ void issue_tile(const FusedGemvArgs& a, const GemvSeg
     const uint32_t bytes = min((uint32_t)PB, rb - it.part * PB);
     const int row0 = it.group0 + 16 * it.tile;
     const int nr = min(16, it.gend - row0);
-    if (lane == 0) mbar_expect_tx(bar, (uint32_t)nr * bytes);
+    // block scales of the same rows and K range travel with the tile when their rows are 16-byte aligned
+    const uint32_t sbytes = p.kind == MAT_INT8 ? bytes / 32 : p.kind == MAT_NF4 ? bytes / 16 : 0;  // per row
+    const uint32_t srow = p.K / 32;  // bytes of scales per weight row (Int8: 4 per 128, NF4: 2 per 64)
+    const bool stma = sbytes != 0 && scales_by_tma(p);
+    if (lane == 0) mbar_expect_tx(bar, (uint32_t)nr * (bytes + (stma ? sbytes : 0)));
     __syncwarp();
-    if (lane < nr) tma_bulk_g2s(slot + lane * PITCH, p.w + (size_t)(row0 + lane) * rb + (size_t)it.part * PB, bytes, bar);
+    if (lane < nr) {
+        tma_bulk_g2s(slot + lane * PITCH, p.w + (size_t)(row0 + lane) * rb + (size_t)it.part * PB, bytes, bar);
+        if (stma)
+            tma_bulk_g2s(slot + 16 * PITCH + lane * SCP,
+                         reinterpret_cast<const uint8_t*>(p.scale) + (size_t)(row0 + lane) * srow +
+                             (size_t)it.part * (p.kind == MAT_INT8 ? PB / 32 : PB / 16),
+                         sbytes, bar);
+    }
 }
 
 __device__ __forceinline__ float block_sum_256(float v, float* scratch) {
@@ -159,27 +194,60 @@ __device__ __forceinline__ float block_sum_256(float v, float* scratch) {
 }
 
 // Layer norm of a.ln_x rows (+ token shift) into xgen[v][t][c] (fp16, pitch xp).
+// Each thread keeps its channels of a row in registers (C <= 8 * kThreads * kLnVec).
+constexpr int kLnVec = 4;  // groups of 8 channels per thread: C <= 8192
 __device__ void run_prologue(const FusedGemvArgs& a, __half* xgen, uint32_t xp, __half* lnrow, float* scratch) {
     const uint32_t C = a.C, T = a.T;
+    const uint32_t ngrp = C / 8;  // 16-byte groups per row
     for (uint32_t t = 0; t < T; ++t) {
+        float v[kLnVec][8];
         float s = 0.f;
-        for (uint32_t c = threadIdx.x; c < C; c += kThreads) s += __half2float(a.ln_x[(size_t)t * C + c]);
+#pragma unroll
+        for (int q = 0; q < kLnVec; ++q) {
+            const uint32_t gi = threadIdx.x + q * kThreads;
+            if (gi < ngrp) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(a.ln_x + (size_t)t * C + gi * 8);
+                const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(h[e]);
+                    v[q][2 * e] = f.x;
+                    v[q][2 * e + 1] = f.y;
+                    s += f.x + f.y;
+                }
+            }
+        }
         const float mean = block_sum_256(s, scratch) / (float)C;
         float m2 = 0.f;
-        for (uint32_t c = threadIdx.x; c < C; c += kThreads) {
-            const float d = __half2float(a.ln_x[(size_t)t * C + c]) - mean;
-            m2 += d * d;
-        }
+#pragma unroll
+        for (int q = 0; q < kLnVec; ++q)
+            if (threadIdx.x + q * kThreads < ngrp)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float d = v[q][e] - mean;
+                    m2 += d * d;
+                }
         const float dev = rsqrtf(block_sum_256(m2, scratch) / (float)C + a.ln_eps);
-        for (uint32_t c = threadIdx.x; c < C; c += kThreads) {
-            const float v = (__half2float(a.ln_x[(size_t)t * C + c]) - mean) * dev;
-            const __half h = __float2half_rn(fmaf(v, __half2float(a.ln_w[c]), __half2float(a.ln_b[c])));
-            lnrow[(size_t)t * xp + c] = h;
-            if (a.ln_out != nullptr && blockIdx.x == 0) a.ln_out[(size_t)t * C + c] = h;
+#pragma unroll
+        for (int q = 0; q < kLnVec; ++q) {
+            const uint32_t gi = threadIdx.x + q * kThreads;
+            if (gi < ngrp) {
+                const uint4 wraw = *reinterpret_cast<const uint4*>(a.ln_w + gi * 8);
+                const uint4 braw = *reinterpret_cast<const uint4*>(a.ln_b + gi * 8);
+                const __half* wh = reinterpret_cast<const __half*>(&wraw);
+                const __half* bh = reinterpret_cast<const __half*>(&braw);
+                uint4 outv;
+                __half* oh = reinterpret_cast<__half*>(&outv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    oh[e] = __float2half_rn(fmaf((v[q][e] - mean) * dev, __half2float(wh[e]), __half2float(bh[e])));
+                *reinterpret_cast<uint4*>(lnrow + (size_t)t * xp + gi * 8) = outv;
+                if (a.ln_out != nullptr && blockIdx.x == 0) *reinterpret_cast<uint4*>(a.ln_out + (size_t)t * C + gi * 8) = outv;
+            }
         }
     }
     __syncthreads();
-    if (a.prologue == PRO_LN) return;  // xgen aliases lnrow
+    if (a.prologue == PRO_LN) return;  // the vectors are the normalised rows themselves
     const int nv = a.prologue == PRO_LN_SHIFT2 ? 2 : 1;
     for (uint32_t t = 0; t < T; ++t) {
         const CursorD cu = cursor_at(a.cursors, a.wide, t);
@@ -188,9 +256,9 @@ __device__ void run_prologue(const FusedGemvArgs& a, __half* xgen, uint32_t xp, 
             const float prev = (t == cu.token) ? static_cast<const float*>(a.state.base)[a.state.index(c, 0, cu.batch)]
                                                : __half2float(lnrow[(size_t)(t - 1) * xp + c]);
             const float lhs = a.reversed ? cur : prev, rhs = a.reversed ? prev : cur;
-            for (int v = 0; v < nv; ++v) {
-                const float f = __half2float((v == 0 ? a.mix0 : a.mix1)[c]);
-                xgen[((size_t)v * T + t) * xp + c] = __float2half_rn(lhs * (1.0f - f) + rhs * f);
+            for (int vi = 0; vi < nv; ++vi) {
+                const float f = __half2float((vi == 0 ? a.mix0 : a.mix1)[c]);
+                xgen[((size_t)vi * T + t) * xp + c] = __float2half_rn(lhs * (1.0f - f) + rhs * f);
             }
         }
     }
@@ -199,7 +267,7 @@ __device__ void run_prologue(const FusedGemvArgs& a, __half* xgen, uint32_t xp, 
 
 __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemvArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ uint64_t full[NSLOT];
+    __shared__ uint64_t full[MAX_SLOTS];
     __shared__ float scratch[kWarps];
     __shared__ __half lut[16];
     __shared__ int aborted;
@@ -213,21 +281,22 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
     for (int i = 0; i < a.num_problems; ++i) kmax = max(kmax, a.p[i].K);
     const uint32_t xp = (a.prologue != PRO_NONE ? a.C : kmax) + 8;  // halfs per activation row
     uint8_t* slots = smem;
-    float* red = reinterpret_cast<float*>(slots + NSLOT * SLOT);           // [kWarps][GROUP_ROWS][T]
+    const int NSLOT = a.num_slots;
+    float* red = reinterpret_cast<float*>(slots + (size_t)NSLOT * SLOT);   // [kWarps][GROUP_ROWS][T]
     float* sums = red + (size_t)kWarps * GROUP_ROWS * T;                    // [T][kmax / 128]
     __half* xs = reinterpret_cast<__half*>(sums + sums_floats(T, kmax));    // staged x or prologue rows
     __half* lnrow = xs;                                                     // PRO_LN: vectors = normalised rows
     __half* xgen = a.prologue == PRO_LN ? xs : xs + (size_t)T * xp;         // shifted vectors follow the rows
 
     if (threadIdx.x == 0) {
-        mbar_init(&full[0], 1);
-        mbar_init(&full[1], 1);
+        for (int i = 0; i < MAX_SLOTS; ++i) mbar_init(&full[i], 1);
         aborted = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
     if (threadIdx.x < 16 && a.table != nullptr) lut[threadIdx.x] = __float2half_rn(a.table[threadIdx.x]);
     __syncthreads();
+    trace(100);
     pdl_launch_dependents();
 
     // weights do not depend on earlier kernels: start streaming before waiting for them
@@ -242,10 +311,13 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
             ++issued;
         }
     }
+    trace(101);
     pdl_wait();
+    trace(102);
 
     if (a.prologue != PRO_NONE && (cons.valid || blockIdx.x == 0)) run_prologue(a, xgen, xp, lnrow, scratch);
 
+    trace(103);
     float acc[GROUP_ROWS / 16][4];
     int staged_problem = -1;
     uint32_t consumed = 0;
@@ -265,7 +337,7 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
                 for (uint32_t i = threadIdx.x; i < T * (p.K / 8); i += kThreads) {
                     const uint32_t tok = i / (p.K / 8), k8 = i % (p.K / 8);
                     *reinterpret_cast<uint4*>(xs + (size_t)tok * xp + k8 * 8) =
-                        *reinterpret_cast<const uint4*>(p.x + (size_t)tok * p.K + k8 * 8);
+                        *reinterpret_cast<const uint4*>(p.x + (size_t)tok * p.x_stride + k8 * 8);
                 }
                 __syncthreads();
             }
@@ -291,14 +363,23 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
         }
 
         const int slot_i = consumed % NSLOT;
+        trace(104);
         mbar_wait(&full[slot_i], (consumed / NSLOT) & 1, a.status, &aborted);
+        trace(105);
         const uint8_t* slot = slots + slot_i * SLOT;
         const uint32_t rb = row_bytes(p);
         const uint32_t bytes = min((uint32_t)PB, rb - cons.part * PB);
         const int rowA = cons.group0 + 16 * cons.tile + g, rowB = rowA + 8;
         const bool xval = (uint32_t)g < T;
+        const bool stma = p.kind != MAT_FP16 && scales_by_tma(p);
         const __half* xrow = xv + (size_t)(xval ? g : 0) * xp + (size_t)cons.part * part_elems(p.kind);
-        float* ac = acc[cons.tile];
+        float ac[4];
+#pragma unroll
+        for (int i = 0; i < GROUP_ROWS / 16; ++i)
+            if (i == cons.tile) {
+                ac[0] = acc[i][0]; ac[1] = acc[i][1]; ac[2] = acc[i][2]; ac[3] = acc[i][3];
+            }
+        const uint8_t* sslot = slot + 16 * PITCH;  // this tile part's scales, SCP bytes per row
 
         if (p.kind == MAT_INT8) {
             const uint32_t nblk = p.K / 128;
@@ -311,8 +392,13 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
                 const uint4 wb0 = *reinterpret_cast<const uint4*>(pa + 8 * PITCH),
                             wb1 = *reinterpret_cast<const uint4*>(pa + 8 * PITCH + 64);
                 float2 mmA = make_float2(0.f, 0.f), mmB = mmA;
-                if (vA) mmA = __half22float2(__ldg(sc + (size_t)rowA * nblk + blk));
-                if (vB) mmB = __half22float2(__ldg(sc + (size_t)rowB * nblk + blk));
+                if (stma) {
+                    mmA = __half22float2(*reinterpret_cast<const __half2*>(sslot + g * SCP + c * 4));
+                    mmB = __half22float2(*reinterpret_cast<const __half2*>(sslot + (g + 8) * SCP + c * 4));
+                } else {
+                    if (vA) mmA = __half22float2(__ldg(sc + (size_t)rowA * nblk + blk));
+                    if (vB) mmB = __half22float2(__ldg(sc + (size_t)rowB * nblk + blk));
+                }
                 const uint32_t wa[8] = {wa0.x, wa0.y, wa0.z, wa0.w, wa1.x, wa1.y, wa1.z, wa1.w};
                 const uint32_t wb[8] = {wb0.x, wb0.y, wb0.z, wb0.w, wb1.x, wb1.y, wb1.z, wb1.w};
                 float d[4] = {0.f, 0.f, 0.f, 0.f};
@@ -341,8 +427,14 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
                 const uint32_t blk = cons.part * (PB / 32) + c;
                 const uint8_t* pa = slot + g * PITCH + c * 32 + 8 * t4;
                 const uint2 wa = *reinterpret_cast<const uint2*>(pa), wb = *reinterpret_cast<const uint2*>(pa + 8 * PITCH);
-                const float aA = vA ? __half2float(__ldg(p.scale + (size_t)rowA * nblk + blk)) : 0.f;
-                const float aB = vB ? __half2float(__ldg(p.scale + (size_t)rowB * nblk + blk)) : 0.f;
+                float aA, aB;
+                if (stma) {
+                    aA = __half2float(*reinterpret_cast<const __half*>(sslot + g * SCP + c * 2));
+                    aB = __half2float(*reinterpret_cast<const __half*>(sslot + (g + 8) * SCP + c * 2));
+                } else {
+                    aA = vA ? __half2float(__ldg(p.scale + (size_t)rowA * nblk + blk)) : 0.f;
+                    aB = vB ? __half2float(__ldg(p.scale + (size_t)rowB * nblk + blk)) : 0.f;
+                }
                 const uint32_t wau[2] = {wa.x, wa.y}, wbu[2] = {wb.x, wb.y};
                 float d[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -377,6 +469,11 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
             }
         }
 
+#pragma unroll
+        for (int i = 0; i < GROUP_ROWS / 16; ++i)
+            if (i == cons.tile) {
+                acc[i][0] = ac[0]; acc[i][1] = ac[1]; acc[i][2] = ac[2]; acc[i][3] = ac[3];
+            }
         const bool finish = cons.last_part_of_group();
         const int fin_group0 = cons.group0, fin_gend = cons.gend, fin_problem = sg.problem;
         __syncthreads();  // everyone is done with this slot (and with `red` of the previous group)
@@ -418,7 +515,7 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
             const uint32_t m = fin_group0 + row;
             const size_t oi = (size_t)tok * fp.M + m;
             if (a.epilogue == EPI_STORE) {
-                dstore(fp.out, fp.out_dtype, oi, s);
+                dstore(fp.out, fp.out_dtype, (size_t)tok * fp.out_stride + m, s);
             } else if (a.epilogue == EPI_RESIDUAL) {
                 // att_o is an fp16 tensor in the reference; x += att_o is rounded to fp16 again
                 const float o16 = __half2float(__float2half_rn(s));
@@ -441,8 +538,24 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
             }
         }
         // `red` is reused by the next group only after the __syncthreads that follows its first tile part
+        trace(106);
     }
+    trace(107);
 }
+
+#ifdef WRK_TRACE
+}  // namespace
+cudaError_t debug_trace_read(unsigned long long* host, unsigned int* n) {
+    cudaError_t e = cudaMemcpyFromSymbol(n, g_trace_n, sizeof(unsigned int));
+    if (e != cudaSuccess) return e;
+    e = cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * (1 << 16));
+    unsigned int zero = 0;
+    cudaMemcpyToSymbol(g_trace_n, &zero, sizeof zero);
+    return e;
+}
+namespace {
+#endif
+
 
 // ---- v6 data-dependent token shift ---------------------------------------------------------------
 // sx[i][t][c] = mix(att_x[t][c], prev[t][c], f16(f16(W2[i][c][:] . tmx[t][i*D:(i+1)*D]) + mix[i][c]))
@@ -617,9 +730,49 @@ cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaSt
 
 }  // namespace
 
-size_t fused_gemv_smem(uint32_t T, uint32_t Kmax, uint32_t C, int prologue) {
+// Cuts the concatenated rows of the launch's matrices into one contiguous range per CTA, balanced by
+// weight bytes.  Returns false when a CTA would need more than kSegmentsPerCta ranges.
+bool fused_gemv_partition(const FusedGemvArgs& a, int grid, std::vector<GemvSegment>& table) {
+    table.assign((size_t)grid * kSegmentsPerCta, GemvSegment{0, 0, 0, 0});
+    double total = 0;
+    std::vector<double> cost(a.num_problems);
+    for (int i = 0; i < a.num_problems; ++i) {
+        const GemvProblem& p = a.p[i];
+        cost[i] = p.kind == MAT_FP16 ? p.K * 2.0 : p.kind == MAT_INT8 ? p.K * 1.03125 : p.K * 0.53125;
+        total += cost[i] * p.M;
+    }
+    int prob = 0;
+    uint32_t row = 0;
+    double done = 0;
+    for (int c = 0; c < grid; ++c) {
+        const bool last = c == grid - 1;
+        const double target = total * (c + 1) / grid;
+        int nseg = 0;
+        while (prob < a.num_problems && nseg < kSegmentsPerCta) {
+            const GemvProblem& p = a.p[prob];
+            uint32_t take = p.M - row;
+            if (!last) {
+                const double want = std::ceil((target - done) / cost[prob] - 1e-9);
+                take = (uint32_t)std::min<double>(take, std::max(0.0, want));
+            }
+            if (take > 0) {
+                table[(size_t)c * kSegmentsPerCta + nseg++] = GemvSegment{prob, (int32_t)row, (int32_t)(row + take), 0};
+                row += take;
+                done += take * cost[prob];
+            }
+            if (row == p.M) {
+                ++prob;
+                row = 0;
+            }
+            if (!last && done >= target - 1e-6) break;
+        }
+    }
+    return prob == a.num_problems;
+}
+
+size_t fused_gemv_smem(uint32_t T, uint32_t Kmax, uint32_t C, int prologue, int num_slots) {
     const uint32_t xp = (prologue != PRO_NONE ? C : Kmax) + 8;
-    size_t bytes = (size_t)NSLOT * SLOT;
+    size_t bytes = (size_t)num_slots * SLOT;
     bytes += (size_t)kWarps * GROUP_ROWS * T * sizeof(float);
     bytes += (size_t)sums_floats(T, Kmax) * sizeof(float);
     const size_t rows = prologue == PRO_NONE || prologue == PRO_LN ? T : prologue == PRO_LN_SHIFT1 ? 2 * T : 3 * T;
@@ -627,10 +780,19 @@ size_t fused_gemv_smem(uint32_t T, uint32_t Kmax, uint32_t C, int prologue) {
     return bytes + 64;
 }
 
-cudaError_t fused_gemv(const FusedGemvArgs& a, int grid, cudaStream_t stream) {
+int fused_gemv_slots(uint32_t T, uint32_t Kmax, uint32_t C, int prologue) {
+    // as many slots as keep two CTAs (this kernel's and the next one's) resident per SM
+    int n = MAX_SLOTS;
+    while (n > 2 && fused_gemv_smem(T, Kmax, C, prologue, n) > 112 * 1024) --n;
+    return n;
+}
+
+cudaError_t fused_gemv(const FusedGemvArgs& a_in, int grid, cudaStream_t stream) {
+    FusedGemvArgs a = a_in;
     uint32_t kmax = 0;
     for (int i = 0; i < a.num_problems; ++i) kmax = std::max(kmax, a.p[i].K);
-    const size_t smem = fused_gemv_smem(a.T, kmax, a.C, a.prologue);
+    a.num_slots = fused_gemv_slots(a.T, kmax, a.C, a.prologue);
+    const size_t smem = fused_gemv_smem(a.T, kmax, a.C, a.prologue, a.num_slots);
     static size_t configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(fused_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);

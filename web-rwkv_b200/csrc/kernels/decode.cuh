@@ -15,9 +15,11 @@ struct GemvProblem {
     const __half* scale;   // Int8 (min, max) per 128; NF4 absmax per 64; fp16: null
     int32_t kind;          // MatKind
     uint32_t K, M;
-    const __half* x;       // [T][K] fp16; null = take prologue vector x_sel
+    const __half* x;       // [T] rows of K fp16, x_stride elements apart; null = take prologue vector x_sel
     int32_t x_sel;
-    void* out;             // [T][M]
+    uint32_t x_stride;
+    void* out;             // [T] rows of M, out_stride elements apart
+    uint32_t out_stride;
     int32_t out_dtype;
     int32_t act;
 };
@@ -34,6 +36,7 @@ constexpr int kSegmentsPerCta = 3;
 struct FusedGemvArgs {
     GemvProblem p[kMaxProblems];
     int32_t num_problems;
+    int32_t num_slots;            // filled by the launcher
     uint32_t T;
     const GemvSegment* segments;  // [grid][kSegmentsPerCta], row0 == row1 marks an unused entry
     const float* table;           // NF4 code book (device)
@@ -62,7 +65,8 @@ struct FusedGemvArgs {
 };
 
 cudaError_t fused_gemv(const FusedGemvArgs& a, int grid, cudaStream_t stream);
-size_t fused_gemv_smem(uint32_t T, uint32_t Kmax, uint32_t C, int prologue);
+bool fused_gemv_partition(const FusedGemvArgs& a, int grid, std::vector<GemvSegment>& table);
+size_t fused_gemv_smem(uint32_t T, uint32_t Kmax, uint32_t C, int prologue, int num_slots);
 
 // v6 data-dependent token shift: time_mix_w2 (5 x [D -> C]) + static mixes + 5-way shift.
 struct TmixArgs {

@@ -4,6 +4,7 @@
 #include <cmath>
 
 #include "common.h"
+#include "kernels/decode.cuh"
 #include "kernels/kernels.h"
 
 using namespace wrk;
@@ -76,6 +77,48 @@ int32_t matmul_common(const char* name, int kind, wrk_tensor* matrix, wrk_tensor
     a.out = make_dview(*output);
     a.act = act;
     const int sms = matrix->ctx->num_sms;
+    // few tokens, fp16 activations, whole rows: the TMA weight-streaming kernel of the decode path
+    const uint32_t need = kind == k::MAT_INT8 ? 128 : kind == k::MAT_NF4 ? 64 : 32;
+    const size_t in_row0 = a.in.index(0, 0, 0), out_row0 = a.out.index(0, 0, 0);
+    const bool stream_ok = b == 1 && n >= 1 && n <= (uint32_t)k::kDecodeMaxTokens && a.in.dtype == WRK_F16 &&
+                           k % need == 0 && in_row0 % 8 == 0 && a.in.stride[0] % 8 == 0 &&
+                           k::fused_gemv_smem(n, k, k, k::PRO_NONE, 2) <= 200 * 1024;
+    if (stream_ok) {
+        k::FusedGemvArgs f{};
+        f.T = n;
+        f.C = k;
+        f.prologue = k::PRO_NONE;
+        f.epilogue = k::EPI_STORE;
+        f.table = a.table;
+        f.status = matrix->ctx->device_status;
+        f.rescale = 1.0f;
+        f.num_problems = 1;
+        k::GemvProblem& p = f.p[0];
+        p.w = static_cast<const uint8_t*>(a.matrix);
+        p.scale = a.scale;
+        p.kind = kind;
+        p.K = k;
+        p.M = m;
+        p.x = static_cast<const __half*>(a.in.base) + in_row0;
+        p.x_stride = a.in.stride[0];
+        p.out = a.out.dtype == WRK_F16 ? static_cast<void*>(static_cast<__half*>(a.out.base) + out_row0)
+                                       : static_cast<void*>(static_cast<float*>(a.out.base) + out_row0);
+        p.out_stride = a.out.stride[0];
+        p.out_dtype = a.out.dtype;
+        p.act = act;
+        std::vector<k::GemvSegment> table;
+        if (k::fused_gemv_partition(f, sms, table)) {
+            const uint32_t tshape[4] = {(uint32_t)(table.size() * 4), 1, 1, 1};
+            wrk_tensor* tt = nullptr;
+            WRK_TRY(wrk_tensor_from_data(matrix->ctx, WRK_U32, tshape, table.data(),
+                                         table.size() * sizeof(k::GemvSegment), &tt));
+            f.segments = static_cast<const k::GemvSegment*>(tt->ptr());
+            *out = new_atom(name, [f, sms](cudaStream_t s) { return k::fused_gemv(f, sms, s); },
+                            {matrix, scale, quant, input->tensor, output->tensor, tt});
+            wrk_tensor_release(tt);  // the atom keeps the buffer alive
+            return WRK_OK;
+        }
+    }
     *out = new_atom(name, [a, sms](cudaStream_t s) { return k::matmul(a, sms, s); },
                     {matrix, scale, quant, input->tensor, output->tensor});
     return WRK_OK;

@@ -411,49 +411,19 @@ k::GemvProblem problem(const MatInfo& m, const __half* x, int x_sel, void* out, 
     p.M = m.M;
     p.x = x;
     p.x_sel = x_sel;
+    p.x_stride = m.K;
     p.out = out;
+    p.out_stride = m.M;
     p.out_dtype = out_dtype;
     p.act = act;
     return p;
 }
 
-// Cuts the concatenated rows of the launch's matrices into one contiguous range per CTA, balanced by
-// weight bytes, and uploads the table.
+// Row partition of a fused launch, uploaded once when the job is built.
 int32_t make_partition(wrk_context* ctx, k::FusedGemvArgs& a, int grid, CachedJob* job) {
-    std::vector<k::GemvSegment> table((size_t)grid * k::kSegmentsPerCta, k::GemvSegment{0, 0, 0, 0});
-    double total = 0;
-    std::vector<double> cost(a.num_problems);
-    for (int i = 0; i < a.num_problems; ++i) {
-        const k::GemvProblem& p = a.p[i];
-        cost[i] = p.kind == k::MAT_FP16 ? p.K * 2.0 : p.kind == k::MAT_INT8 ? p.K * 1.03125 : p.K * 0.53125;
-        total += cost[i] * p.M;
-    }
-    int prob = 0;
-    uint32_t row = 0;
-    double done = 0;
-    for (int c = 0; c < grid; ++c) {
-        const double target = total * (c + 1) / grid;
-        int nseg = 0;
-        while (prob < a.num_problems && nseg < k::kSegmentsPerCta) {
-            const k::GemvProblem& p = a.p[prob];
-            uint32_t take = (uint32_t)std::max(0.0, std::ceil((target - done) / cost[prob] - 1e-9));
-            if (c == grid - 1) take = p.M - row;  // the last CTA takes whatever is left
-            take = std::min(take, p.M - row);
-            if (take > 0) {
-                table[(size_t)c * k::kSegmentsPerCta + nseg] = k::GemvSegment{prob, (int32_t)row, (int32_t)(row + take), 0};
-                ++nseg;
-                row += take;
-                done += take * cost[prob];
-            }
-            if (row == p.M) {
-                ++prob;
-                row = 0;
-                if (c == grid - 1) continue;
-            }
-            if (done >= target - 1e-6 && c != grid - 1) break;
-        }
-    }
-    WRK_REQUIRE(prob == a.num_problems, WRK_ERR_UNSUPPORTED, "row partition overflow: too many small matrices per CTA");
+    std::vector<k::GemvSegment> table;
+    WRK_REQUIRE(k::fused_gemv_partition(a, grid, table), WRK_ERR_UNSUPPORTED,
+                "row partition overflow: too many small matrices per CTA");
     const uint32_t shape[4] = {(uint32_t)(table.size() * 4), 1, 1, 1};
     wrk_tensor* t = nullptr;
     WRK_TRY(wrk_tensor_from_data(ctx, WRK_U32, shape, table.data(), table.size() * sizeof(k::GemvSegment), &t));
@@ -489,8 +459,8 @@ bool fused_v6_supported(wrk_bundle* bd, uint32_t T) {
             if (!mat_fusable(mat_info(m))) return false;
     if (!mat_fusable(mat_info(bd->model->head_w))) return false;
     const uint32_t kmax = std::max(info.num_emb, info.num_hidden);
-    return k::fused_gemv_smem(T, kmax, info.num_emb, k::PRO_NONE) <= 200 * 1024 &&
-           k::fused_gemv_smem(T, info.num_emb, info.num_emb, k::PRO_LN_SHIFT2) <= 200 * 1024;
+    return k::fused_gemv_smem(T, kmax, info.num_emb, k::PRO_NONE, 2) <= 200 * 1024 &&
+           k::fused_gemv_smem(T, info.num_emb, info.num_emb, k::PRO_LN_SHIFT2, 2) <= 200 * 1024 && info.num_emb <= 8192;
 }
 
 int32_t layer_v6_fused(wrk_bundle* bd, OpList& ops, CachedJob* job, const Buffers& B, uint32_t index, uint32_t T) {
