@@ -5,11 +5,14 @@
 // around never letting the stream of weights stop:
 //   * fused_gemv_kernel is a grouped weight-streaming kernel.  A launch covers several matrices (e.g.
 //     key / value / receptance / gate + the decay adapter); the concatenated row space is cut into one
-//     contiguous row range per CTA (balanced by bytes, one CTA per SM slot), and each CTA pulls its rows
-//     into shared memory with 1-D TMA bulk copies (cp.async.bulk + mbarrier complete_tx), 16 rows x 1 KB
-//     (+ their block scales) per slot, four or more slots in flight.
+//     contiguous row range per CTA (balanced by bytes, one CTA per SM slot), and each CTA pulls exactly its
+//     rows into shared memory with asynchronous 16-byte copies (cp.async, one commit group per tile part of
+//     16 rows x 1 KB + its block scales), four to six tile parts in flight.  Per-row bulk-TMA copies were
+//     measured first: the TMA unit serialises them (~50 ns each, 32 per tile part), which cost more than
+//     the copy itself; a 2-D tensor-map box would fetch whole 16-row boxes and over-read the 13.8-row
+//     shares a 2048-row matrix leaves per SM.
 //   * every kernel here is launched with programmatic dependent launch: it signals its dependents at
-//     once, issues the TMA copies of its first weight tiles, and only then executes griddepcontrol.wait.
+//     once, issues the copies of its first weight tiles, and only then executes griddepcontrol.wait.
 //     Weights are never written during a job, so the next kernel's weights are already landing in shared
 //     memory while the previous kernel is still finishing.
 //   * layer norm + token shift run as a per-CTA prologue (every CTA recomputes the few-KB vector instead
@@ -34,25 +37,35 @@ constexpr int SCP = 80;           // pitch of a row's scales inside a slot (<= 6
 constexpr int SLOT = 16 * PITCH + 16 * SCP;  // one tile part: 16 rows of weights, then their scales
 constexpr int MAX_SLOTS = 6;
 constexpr int GROUP_ROWS = 64;    // rows accumulated in registers at a time (4 MMA row tiles)
-constexpr uint32_t kSpinLimit = 1u << 22;
 
 // floats reserved for the per-block activation sums (keeps what follows 16-byte aligned)
 __host__ __device__ inline uint32_t sums_floats(uint32_t T, uint32_t kmax) {
     return (T * ((kmax + 127) / 128) + 3) / 4 * 4 + 4;
 }
 
-// Optional stage timestamps (builds with -DWRK_TRACE only): CTA 0 appends (stage, globaltimer ns).
+// Optional stage timestamps (builds with -DWRK_TRACE only): CTA 0 records (stage, globaltimer ns) in
+// shared memory and appends them to a global log when the kernel ends.
 #ifdef WRK_TRACE
 __device__ unsigned long long g_trace[1 << 16];
 __device__ unsigned int g_trace_n;
+__shared__ unsigned long long s_trace[128];
+__shared__ unsigned int s_trace_n;
 __device__ __forceinline__ void trace(int stage) {
     if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        const unsigned int i = atomicAdd(&g_trace_n, 1u);
-        if (i < (1u << 15)) {
-            g_trace[2 * i] = (unsigned long long)stage;
-            g_trace[2 * i + 1] = t;
+        if (stage == 100) s_trace_n = 0;
+        if (s_trace_n < 64) {
+            s_trace[2 * s_trace_n] = (unsigned long long)stage;
+            s_trace[2 * s_trace_n + 1] = t;
+            ++s_trace_n;
+        }
+        if (stage == 107) {
+            const unsigned int base = atomicAdd(&g_trace_n, s_trace_n);
+            for (unsigned int i = 0; i < s_trace_n && base + i < (1u << 15); ++i) {
+                g_trace[2 * (base + i)] = s_trace[2 * i];
+                g_trace[2 * (base + i) + 1] = s_trace[2 * i + 1];
+            }
         }
     }
 }
@@ -62,39 +75,6 @@ __device__ __forceinline__ void trace(int) {}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.b32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: gives up after kSpinLimit polls, records WRK_ERR_TIMEOUT and lets the kernel run to its
-// end (results are then meaningless, the host sees the status word).
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int32_t* status, volatile int* aborted) {
-    if (*aborted) return;
-    for (uint32_t i = 0; i < kSpinLimit; ++i)
-        if (mbar_try_wait(bar, parity)) return;
-    *aborted = 1;
-    atomicExch(status, (int32_t)WRK_ERR_TIMEOUT);
-}
-__device__ __forceinline__ void tma_bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
-                     smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
@@ -113,10 +93,6 @@ __device__ __forceinline__ uint32_t bytes_to_half2(uint32_t w, uint32_t sel) {
 
 __device__ __forceinline__ uint32_t row_bytes(const GemvProblem& p) {
     return p.kind == MAT_FP16 ? p.K * 2 : p.kind == MAT_INT8 ? p.K : p.K / 2;
-}
-// scales can ride the TMA when every row's scale run starts on a 16-byte boundary
-__device__ __forceinline__ bool scales_by_tma(const GemvProblem& p) {
-    return p.K % 512 == 0 && (reinterpret_cast<uintptr_t>(p.scale) & 15) == 0;
 }
 __device__ __forceinline__ uint32_t part_elems(int kind) { return kind == MAT_FP16 ? PB / 2 : kind == MAT_INT8 ? PB : PB * 2; }
 
@@ -158,27 +134,55 @@ struct TileIter {
     __device__ bool last_part_of_group() const { return part == nparts - 1 && tile == ntile - 1; }
 };
 
-// Issue the TMA copies of one tile part (warp 0 only).
+// Asynchronous global -> shared copies (LDGSTS): 16 bytes for weights, 4 bytes for block scales.
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait(int pending) {
+    switch (pending) {
+        case 0: asm volatile("cp.async.wait_group 0;\n" ::: "memory"); break;
+        case 1: asm volatile("cp.async.wait_group 1;\n" ::: "memory"); break;
+        case 2: asm volatile("cp.async.wait_group 2;\n" ::: "memory"); break;
+        case 3: asm volatile("cp.async.wait_group 3;\n" ::: "memory"); break;
+        case 4: asm volatile("cp.async.wait_group 4;\n" ::: "memory"); break;
+        default: asm volatile("cp.async.wait_group 5;\n" ::: "memory"); break;
+    }
+}
+
+// Block scales ride along with the tile when pairs of them are 4-byte aligned in every row.
+__device__ __forceinline__ bool scales_async(const GemvProblem& p) {
+    return p.kind == MAT_INT8 || (p.kind == MAT_NF4 && p.K % 128 == 0);
+}
+
+// All threads issue the copies of one tile part: exactly the CTA's rows, nothing more.
 __device__ __forceinline__ void issue_tile(const FusedGemvArgs& a, const GemvSegment* segs, const TileIter& it,
-                                           uint8_t* slot, uint64_t* bar, int lane) {
+                                           uint8_t* slot) {
     const GemvProblem& p = a.p[segs[it.seg].problem];
     const uint32_t rb = row_bytes(p);
     const uint32_t bytes = min((uint32_t)PB, rb - it.part * PB);
     const int row0 = it.group0 + 16 * it.tile;
     const int nr = min(16, it.gend - row0);
-    // block scales of the same rows and K range travel with the tile when their rows are 16-byte aligned
-    const uint32_t sbytes = p.kind == MAT_INT8 ? bytes / 32 : p.kind == MAT_NF4 ? bytes / 16 : 0;  // per row
-    const uint32_t srow = p.K / 32;  // bytes of scales per weight row (Int8: 4 per 128, NF4: 2 per 64)
-    const bool stma = sbytes != 0 && scales_by_tma(p);
-    if (lane == 0) mbar_expect_tx(bar, (uint32_t)nr * (bytes + (stma ? sbytes : 0)));
-    __syncwarp();
-    if (lane < nr) {
-        tma_bulk_g2s(slot + lane * PITCH, p.w + (size_t)(row0 + lane) * rb + (size_t)it.part * PB, bytes, bar);
-        if (stma)
-            tma_bulk_g2s(slot + 16 * PITCH + lane * SCP,
-                         reinterpret_cast<const uint8_t*>(p.scale) + (size_t)(row0 + lane) * srow +
-                             (size_t)it.part * (p.kind == MAT_INT8 ? PB / 32 : PB / 16),
-                         sbytes, bar);
+    const uint32_t cpr = bytes / 16;
+    const uint8_t* src = p.w + (size_t)row0 * rb + (size_t)it.part * PB;
+    for (uint32_t i = threadIdx.x; i < (uint32_t)nr * cpr; i += kThreads) {
+        const uint32_t r = i / cpr, c = i % cpr;
+        cp_async16(slot + r * PITCH + c * 16, src + (size_t)r * rb + c * 16);
+    }
+    if (scales_async(p)) {
+        // Int8: one (min, max) pair = 4 bytes per 128 weights; NF4: two absmax = 4 bytes per 128 weights
+        const uint32_t per_row = p.kind == MAT_INT8 ? bytes / 128 : bytes / 64;  // 4-byte units in this part
+        const uint32_t row_units = p.K / 128;
+        const uint32_t part_units = p.kind == MAT_INT8 ? PB / 128 : PB / 64;
+        const uint8_t* sc = reinterpret_cast<const uint8_t*>(p.scale);
+        uint8_t* sslot = slot + 16 * PITCH;
+        for (uint32_t i = threadIdx.x; i < (uint32_t)nr * per_row; i += kThreads) {
+            const uint32_t r = i / per_row, u = i % per_row;
+            cp_async4(sslot + r * SCP + u * 4, sc + ((size_t)(row0 + r) * row_units + it.part * part_units + u) * 4);
+        }
     }
 }
 
@@ -267,10 +271,8 @@ __device__ void run_prologue(const FusedGemvArgs& a, __half* xgen, uint32_t xp, 
 
 __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemvArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ uint64_t full[MAX_SLOTS];
     __shared__ float scratch[kWarps];
     __shared__ __half lut[16];
-    __shared__ int aborted;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
     const uint32_t T = a.T;
@@ -288,29 +290,27 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
     __half* lnrow = xs;                                                     // PRO_LN: vectors = normalised rows
     __half* xgen = a.prologue == PRO_LN ? xs : xs + (size_t)T * xp;         // shifted vectors follow the rows
 
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < MAX_SLOTS; ++i) mbar_init(&full[i], 1);
-        aborted = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-    }
     if (threadIdx.x < 16 && a.table != nullptr) lut[threadIdx.x] = __float2half_rn(a.table[threadIdx.x]);
     __syncthreads();
     trace(100);
     pdl_launch_dependents();
+    trace(109);
 
     // weights do not depend on earlier kernels: start streaming before waiting for them
     TileIter prod, cons;
     prod.start(a, segs);
     cons = prod;
     uint32_t issued = 0;
-    if (warp == 0) {
-        for (int s = 0; s < NSLOT && prod.valid; ++s) {
-            issue_tile(a, segs, prod, slots + s * SLOT, &full[s], lane);
+    trace(110);
+    for (int s = 0; s < NSLOT; ++s) {
+        if (prod.valid) {
+            issue_tile(a, segs, prod, slots + s * SLOT);
             prod.next(a, segs);
             ++issued;
         }
+        cp_async_commit();  // one group per slot, empty or not: the group count stays uniform
     }
+    trace(111);
     trace(101);
     pdl_wait();
     trace(102);
@@ -331,17 +331,34 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
             xv = xs;
         }
         if (staged_problem != sg.problem) {
-            // stage x (explicit inputs) and the per-128-block sums of the values the MMA will see
+            // stage x (explicit inputs) and the per-128-block sums of the values the MMA will see:
+            // 16 consecutive lanes cover one block of 128, so the sums come from the registers in flight
             __syncthreads();
             if (p.x != nullptr) {
-                for (uint32_t i = threadIdx.x; i < T * (p.K / 8); i += kThreads) {
-                    const uint32_t tok = i / (p.K / 8), k8 = i % (p.K / 8);
-                    *reinterpret_cast<uint4*>(xs + (size_t)tok * xp + k8 * 8) =
-                        *reinterpret_cast<const uint4*>(p.x + (size_t)tok * p.x_stride + k8 * 8);
+                const uint32_t groups = p.K / 8, total = T * groups;
+                for (uint32_t i0 = 0; i0 < total; i0 += kThreads) {
+                    const uint32_t i = i0 + threadIdx.x;
+                    float sum = 0.f;
+                    uint32_t tok = 0, k8 = 0;
+                    if (i < total) {
+                        tok = i / groups;
+                        k8 = i % groups;
+                        const uint4 raw = *reinterpret_cast<const uint4*>(p.x + (size_t)tok * p.x_stride + k8 * 8);
+                        *reinterpret_cast<uint4*>(xs + (size_t)tok * xp + k8 * 8) = raw;
+                        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 f = __half22float2(h[e]);
+                            sum += f.x + f.y;
+                        }
+                    }
+                    if (p.kind == MAT_INT8) {
+#pragma unroll
+                        for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off, 16);
+                        if (i < total && (k8 & 15) == 0) sums[tok * (p.K / 128) + (k8 >> 4)] = sum;
+                    }
                 }
-                __syncthreads();
-            }
-            if (p.kind == MAT_INT8) {
+            } else if (p.kind == MAT_INT8) {
                 const uint32_t nblk = p.K / 128;
                 for (uint32_t u = warp; u < T * nblk; u += kWarps) {
                     const uint32_t tok = u / nblk, blk = u % nblk;
@@ -364,14 +381,15 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
 
         const int slot_i = consumed % NSLOT;
         trace(104);
-        mbar_wait(&full[slot_i], (consumed / NSLOT) & 1, a.status, &aborted);
+        cp_async_wait(NSLOT - 1);  // this thread's copies of tile part `consumed` have landed ...
+        __syncthreads();           // ... and everyone else's
         trace(105);
         const uint8_t* slot = slots + slot_i * SLOT;
         const uint32_t rb = row_bytes(p);
         const uint32_t bytes = min((uint32_t)PB, rb - cons.part * PB);
         const int rowA = cons.group0 + 16 * cons.tile + g, rowB = rowA + 8;
         const bool xval = (uint32_t)g < T;
-        const bool stma = p.kind != MAT_FP16 && scales_by_tma(p);
+        const bool stma = scales_async(p);
         const __half* xrow = xv + (size_t)(xval ? g : 0) * xp + (size_t)cons.part * part_elems(p.kind);
         float ac[4];
 #pragma unroll
@@ -479,13 +497,13 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
         __syncthreads();  // everyone is done with this slot (and with `red` of the previous group)
         ++consumed;
         cons.next(a, segs);
-        if (warp == 0 && prod.valid) {
-            // refill the slot just released with the tile part two steps ahead
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-            issue_tile(a, segs, prod, slots + slot_i * SLOT, &full[slot_i], lane);
+        if (prod.valid) {
+            // refill the slot just released with the tile part NSLOT steps ahead
+            issue_tile(a, segs, prod, slots + slot_i * SLOT);
             prod.next(a, segs);
             ++issued;
         }
+        cp_async_commit();
         if (!finish) continue;
 
         // ---- group finished: cross-warp reduction and epilogue ----
@@ -783,7 +801,7 @@ size_t fused_gemv_smem(uint32_t T, uint32_t Kmax, uint32_t C, int prologue, int 
 int fused_gemv_slots(uint32_t T, uint32_t Kmax, uint32_t C, int prologue) {
     // as many slots as keep two CTAs (this kernel's and the next one's) resident per SM
     int n = MAX_SLOTS;
-    while (n > 2 && fused_gemv_smem(T, Kmax, C, prologue, n) > 112 * 1024) --n;
+    while (n > 2 && fused_gemv_smem(T, Kmax, C, prologue, n) > 100 * 1024) --n;
     return n;
 }
 
