@@ -29,13 +29,8 @@ namespace k {
 
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kWarps = 8;
-constexpr int PB = 1024;          // bytes of one weight row per tile part
-constexpr int PITCH = PB + 16;    // shared-memory row pitch: consecutive rows shift by one 16-byte bank group
-constexpr int SCP = 80;           // pitch of a row's scales inside a slot (<= 64 bytes of data)
-constexpr int SLOT = 16 * PITCH + 16 * SCP;  // one tile part: 16 rows of weights, then their scales
-constexpr int MAX_SLOTS = 6;
+constexpr int kThreads = 512;
+constexpr int kWarps = 16;
 constexpr int GROUP_ROWS = 64;    // rows accumulated in registers at a time (4 MMA row tiles)
 
 // floats reserved for the per-block activation sums (keeps what follows 16-byte aligned)
@@ -85,105 +80,179 @@ __device__ __forceinline__ void mma16816(float d[4], uint32_t a0, uint32_t a1, u
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t bytes_to_half2(uint32_t w, uint32_t sel) {
-    const uint32_t h = __byte_perm(w, 0x64646464u, sel);  // 0x6400 | q = 1024 + q
-    const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&h), __float2half2_rn(1024.0f));
-    return *reinterpret_cast<const uint32_t*>(&v);
-}
-
 __device__ __forceinline__ uint32_t row_bytes(const GemvProblem& p) {
     return p.kind == MAT_FP16 ? p.K * 2 : p.kind == MAT_INT8 ? p.K : p.K / 2;
 }
-__device__ __forceinline__ uint32_t part_elems(int kind) { return kind == MAT_FP16 ? PB / 2 : kind == MAT_INT8 ? PB : PB * 2; }
 
-// Position in a CTA's sequence of tile parts: segment -> group of <= 64 rows -> K part -> row tile.
-struct TileIter {
-    int seg, group0, part, tile;
-    int ntile, nparts, gend;  // of the current group
-    bool valid;
+// One warp-level work item covers CHUNK_BYTES of 16 weight rows (an MMA row tile): Int8 one 128-weight
+// block per row, fp16 64 weights, NF4 four 64-weight blocks.  Lane (g, t4) reads 16-byte (NF4: 8-byte)
+// pieces of rows g and g + 8.
+constexpr int CHUNK_BYTES = 128;
 
-    __device__ void enter(const FusedGemvArgs& a, const GemvSegment* segs) {
-        while (seg < kSegmentsPerCta && segs[seg].row0 >= segs[seg].row1) ++seg;
-        valid = seg < kSegmentsPerCta;
-        if (!valid) return;
-        const GemvSegment& s = segs[seg];
-        gend = min(group0 + GROUP_ROWS, s.row1);
-        ntile = (gend - group0 + 15) / 16;
-        nparts = (row_bytes(a.p[s.problem]) + PB - 1) / PB;
-    }
-    __device__ void start(const FusedGemvArgs& a, const GemvSegment* segs) {
-        seg = 0;
-        part = tile = 0;
-        while (seg < kSegmentsPerCta && segs[seg].row0 >= segs[seg].row1) ++seg;
-        group0 = seg < kSegmentsPerCta ? segs[seg].row0 : 0;
-        enter(a, segs);
-    }
-    __device__ void next(const FusedGemvArgs& a, const GemvSegment* segs) {
-        if (++tile < ntile) return;
-        tile = 0;
-        if (++part < nparts) return;
-        part = 0;
-        group0 += GROUP_ROWS;
-        if (group0 >= segs[seg].row1) {
-            ++seg;
-            while (seg < kSegmentsPerCta && segs[seg].row0 >= segs[seg].row1) ++seg;
-            if (seg < kSegmentsPerCta) group0 = segs[seg].row0;
-        }
-        enter(a, segs);
-    }
-    __device__ bool last_part_of_group() const { return part == nparts - 1 && tile == ntile - 1; }
+// One work item in registers: this lane's pieces of rows g and g + 8 and their block scales.
+struct Item {
+    uint4 q[4];     // Int8 / fp16: rowA lo, rowA hi, rowB lo, rowB hi; NF4: blocks (0,1) A, (2,3) A, (0,1) B, (2,3) B
+    uint32_t s[4];  // Int8: s[0] = (min, max) of rowA as half2, s[1] = rowB; NF4: absmax pairs A01, A23, B01, B23
 };
 
-// Asynchronous global -> shared copies (LDGSTS): 16 bytes for weights, 4 bytes for block scales.
-__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+// The CTA's row ranges, kept in registers.
+struct Segs {
+    int prob[kSegmentsPerCta], r0[kSegmentsPerCta], r1[kSegmentsPerCta];
+    __device__ __forceinline__ int P(int s) const { return s == 0 ? prob[0] : s == 1 ? prob[1] : prob[2]; }
+    __device__ __forceinline__ int R0(int s) const { return s == 0 ? r0[0] : s == 1 ? r0[1] : r0[2]; }
+    __device__ __forceinline__ int R1(int s) const { return s == 0 ? r1[0] : s == 1 ? r1[1] : r1[2]; }
+};
+
+// ---- per-warp staging ring --------------------------------------------------------------------
+// Each warp streams its own work items through a private ring in shared memory with cp.async: a lane
+// copies exactly the pieces it will later feed to the MMA into its own 16-byte cells, so reading them back
+// needs no barrier (a thread sees its own completed cp.async data after wait_group) and is conflict free.
+constexpr int kRing = 2;                          // items in flight per warp
+constexpr int ITEM_BYTES = 32 * (4 * 16 + 4 * 4);  // per lane: four 16-byte pieces + four scale words
+
+__device__ __forceinline__ void cp_async16z(void* dst, const void* src, bool valid) {
+    const uint32_t n = valid ? 16u : 0u;  // src-size 0: the cell is zero-filled, nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(n) : "memory");
 }
-__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+__device__ __forceinline__ void cp_async8z(void* dst, const void* src, bool valid) {
+    const uint32_t n = valid ? 8u : 0u;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async4z(void* dst, const void* src, bool valid) {
+    const uint32_t n = valid ? 4u : 0u;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(n) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait(int pending) {
-    switch (pending) {
-        case 0: asm volatile("cp.async.wait_group 0;\n" ::: "memory"); break;
-        case 1: asm volatile("cp.async.wait_group 1;\n" ::: "memory"); break;
-        case 2: asm volatile("cp.async.wait_group 2;\n" ::: "memory"); break;
-        case 3: asm volatile("cp.async.wait_group 3;\n" ::: "memory"); break;
-        case 4: asm volatile("cp.async.wait_group 4;\n" ::: "memory"); break;
-        default: asm volatile("cp.async.wait_group 5;\n" ::: "memory"); break;
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// How the 16 warps share a group of <= 64 rows (nt = 1..4 MMA row tiles of nchunk chunks each): warp w owns
+// row tile w % nt and every kways-th chunk of it starting at chunk w / nt, kways = 16 / nt.  A warp keeps the
+// partial results of its tile in registers for the whole group, so the per-item work is loads + MMAs only.
+struct GroupMap {
+    int tile, ks, kways, cnt;  // cnt = items of this warp in the group
+};
+__device__ __forceinline__ GroupMap map_group(int nrows, int nchunk, int warp) {
+    GroupMap m;
+    const int nt = (nrows + 15) >> 4;
+    if (nt <= 1) {
+        m.tile = 0, m.ks = warp, m.kways = 16;
+    } else if (nt == 2) {
+        m.tile = warp & 1, m.ks = warp >> 1, m.kways = 8;
+    } else if (nt == 3) {
+        m.tile = warp % 3, m.ks = warp / 3, m.kways = 5;
+    } else {
+        m.tile = warp & 3, m.ks = warp >> 2, m.kways = 4;
     }
+    const int left = nchunk - m.ks;
+    m.cnt = (m.ks < m.kways && left > 0) ? (left + m.kways - 1) / m.kways : 0;
+    return m;
 }
 
-// Block scales ride along with the tile when pairs of them are 4-byte aligned in every row.
-__device__ __forceinline__ bool scales_async(const GemvProblem& p) {
-    return p.kind == MAT_INT8 || (p.kind == MAT_NF4 && p.K % 128 == 0);
-}
+// The copy side of a warp: walks the same (segment, group, item) sequence as the compute side, kRing items
+// ahead, with the addresses of the current group kept as row pointer + running byte offset.
+struct Loader {
+    int seg, group0;     // current group; seg == kSegmentsPerCta when the CTA's work is exhausted
+    int left;            // items of this warp not yet issued in the group
+    uint32_t off, step;  // byte offset of the next chunk within a row; kways * CHUNK_BYTES
+    uint32_t rb, rb8;    // row bytes; distance from row g to row g + 8 (0 when that row does not exist)
+    uint32_t sb8;        // same distance in the scale table
+    int kind;
+    bool vA, vB;
+    const uint8_t* pa;  // row g of the warp's tile + this lane's byte offset
+    const uint8_t* sa;  // row g's block scales
 
-// All threads issue the copies of one tile part: exactly the CTA's rows, nothing more.
-__device__ __forceinline__ void issue_tile(const FusedGemvArgs& a, const GemvSegment* segs, const TileIter& it,
-                                           uint8_t* slot) {
-    const GemvProblem& p = a.p[segs[it.seg].problem];
-    const uint32_t rb = row_bytes(p);
-    const uint32_t bytes = min((uint32_t)PB, rb - it.part * PB);
-    const int row0 = it.group0 + 16 * it.tile;
-    const int nr = min(16, it.gend - row0);
-    const uint32_t cpr = bytes / 16;
-    const uint8_t* src = p.w + (size_t)row0 * rb + (size_t)it.part * PB;
-    for (uint32_t i = threadIdx.x; i < (uint32_t)nr * cpr; i += kThreads) {
-        const uint32_t r = i / cpr, c = i % cpr;
-        cp_async16(slot + r * PITCH + c * 16, src + (size_t)r * rb + c * 16);
+    __device__ __forceinline__ bool valid() const { return seg < kSegmentsPerCta; }
+
+    __device__ __forceinline__ void enter_group(const FusedGemvArgs& a, const Segs& sg, int warp, int lane) {
+        const GemvProblem& p = a.p[sg.P(seg)];
+        rb = row_bytes(p);
+        kind = p.kind;
+        const int gend = min(group0 + GROUP_ROWS, sg.R1(seg));
+        const GroupMap m = map_group(gend - group0, (int)((rb + CHUNK_BYTES - 1) / CHUNK_BYTES), warp);
+        left = m.cnt;
+        off = (uint32_t)m.ks * CHUNK_BYTES;
+        step = (uint32_t)m.kways * CHUNK_BYTES;
+        const int g = lane >> 2, t4 = lane & 3;
+        const int rowA = group0 + 16 * m.tile + g;
+        vA = rowA < gend;
+        vB = rowA + 8 < gend;
+        const size_t ra = (size_t)(vA ? rowA : group0);
+        pa = p.w + ra * rb + (kind == MAT_NF4 ? 8 : 16) * t4;
+        rb8 = vB ? 8u * rb : 0u;
+        const uint32_t srow = kind == MAT_INT8 ? (p.K / 128) * 4 : kind == MAT_NF4 ? (p.K / 64) * 2 : 0;  // scale bytes per row
+        sa = reinterpret_cast<const uint8_t*>(p.scale) + ra * srow;
+        sb8 = vB ? 8u * srow : 0u;
     }
-    if (scales_async(p)) {
-        // Int8: one (min, max) pair = 4 bytes per 128 weights; NF4: two absmax = 4 bytes per 128 weights
-        const uint32_t per_row = p.kind == MAT_INT8 ? bytes / 128 : bytes / 64;  // 4-byte units in this part
-        const uint32_t row_units = p.K / 128;
-        const uint32_t part_units = p.kind == MAT_INT8 ? PB / 128 : PB / 64;
-        const uint8_t* sc = reinterpret_cast<const uint8_t*>(p.scale);
-        uint8_t* sslot = slot + 16 * PITCH;
-        for (uint32_t i = threadIdx.x; i < (uint32_t)nr * per_row; i += kThreads) {
-            const uint32_t r = i / per_row, u = i % per_row;
-            cp_async4(sslot + r * SCP + u * 4, sc + ((size_t)(row0 + r) * row_units + it.part * part_units + u) * 4);
+    __device__ __forceinline__ void settle(const FusedGemvArgs& a, const Segs& sg, int warp, int lane) {
+        while (valid() && left <= 0) {
+            group0 += GROUP_ROWS;
+            if (group0 >= sg.R1(seg)) {
+                ++seg;
+                while (seg < kSegmentsPerCta && sg.R0(seg) >= sg.R1(seg)) ++seg;
+                if (seg >= kSegmentsPerCta) return;
+                group0 = sg.R0(seg);
+            }
+            enter_group(a, sg, warp, lane);
         }
     }
+    __device__ __forceinline__ void start(const FusedGemvArgs& a, const Segs& sg, int warp, int lane) {
+        seg = 0;
+        left = 0;
+        while (seg < kSegmentsPerCta && sg.R0(seg) >= sg.R1(seg)) ++seg;
+        if (!valid()) return;
+        group0 = sg.R0(seg);
+        enter_group(a, sg, warp, lane);
+        settle(a, sg, warp, lane);
+    }
+    // Issues the copies of the current item into ring cell `cell` (nothing when exhausted) and steps on.
+    __device__ __forceinline__ void issue(const FusedGemvArgs& a, const Segs& sg, uint8_t* cell, int warp, int lane) {
+        if (!valid()) return;
+        const uint8_t* A = pa + off;
+        const uint8_t* B = A + rb8;
+        uint8_t* wq = cell + lane * 16;           // piece i at wq + i * 512
+        uint8_t* ws = cell + 4 * 512 + lane * 4;  // scale word i at ws + i * 128
+        if (kind == MAT_NF4) {
+            // four 64-weight blocks of 32 bytes, 8 bytes of each per lane: cells hold (blk0, blk1), (blk2, blk3)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const bool in = off + 32 * j < rb;
+                cp_async8z(wq + (j >> 1) * 512 + (j & 1) * 8, A + 32 * j, in && vA);
+                cp_async8z(wq + (2 + (j >> 1)) * 512 + (j & 1) * 8, B + 32 * j, in && vB);
+            }
+            // absmax pairs (blocks 0-1, 2-3) of both rows; K is a multiple of 128 here, so pairs are 4-byte aligned
+            const uint8_t* SA = sa + (off >> 4);
+            const uint8_t* SB = SA + sb8;
+            cp_async4z(ws, SA, vA && off < rb);
+            cp_async4z(ws + 128, SA + 4, vA && off + 64 < rb);
+            cp_async4z(ws + 256, SB, vB && off < rb);
+            cp_async4z(ws + 384, SB + 4, vB && off + 64 < rb);
+        } else {
+            const bool hi = off + 64 < rb;  // fp16 rows may end after the first 64 bytes of the chunk
+            cp_async16z(wq, A, vA);
+            cp_async16z(wq + 512, A + 64, vA && hi);
+            cp_async16z(wq + 1024, B, vB);
+            cp_async16z(wq + 1536, B + 64, vB && hi);
+            if (kind == MAT_INT8) {
+                const uint8_t* SA = sa + (off >> 5);
+                cp_async4z(ws, SA, vA);
+                cp_async4z(ws + 128, SA + sb8, vB);
+            }
+        }
+        off += step;
+        --left;
+        settle(a, sg, warp, lane);
+    }
+};
+
+__device__ __forceinline__ Item read_item(const uint8_t* cell, int lane) {
+    Item it;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        it.q[i] = *reinterpret_cast<const uint4*>(cell + i * 512 + lane * 16);
+        it.s[i] = *reinterpret_cast<const uint32_t*>(cell + 4 * 512 + i * 128 + lane * 4);
+    }
+    return it;
 }
 
 __device__ __forceinline__ float block_sum_256(float v, float* scratch) {
@@ -198,12 +267,39 @@ __device__ __forceinline__ float block_sum_256(float v, float* scratch) {
 }
 
 // Layer norm of a.ln_x rows (+ token shift) into xgen[v][t][c] (fp16, pitch xp).
-// Each thread keeps its channels of a row in registers (C <= 8 * kThreads * kLnVec).
-constexpr int kLnVec = 4;  // groups of 8 channels per thread: C <= 8192
-__device__ void run_prologue(const FusedGemvArgs& a, __half* xgen, uint32_t xp, __half* lnrow, float* scratch) {
+// Each thread owns kLnVec groups of 8 channels (C <= 8 * kThreads * kLnVec) through both passes.  The
+// per-channel parameters were copied into shared memory before the grid dependency was awaited
+// (stage_prologue_params): the norm weight sits in row 0 of lnrow, the bias in pbias, the shift factors in
+// row 0 of each xgen region.  Rows are produced last token first, so every parameter row is consumed by its
+// owner thread before that thread overwrites it with row 0's result.
+constexpr int kLnVec = 2;  // groups of 8 channels per thread: C <= 8192
+__device__ __forceinline__ void stage_prologue_params(const FusedGemvArgs& a, __half* xgen, uint32_t xp, __half* lnrow,
+                                                      __half* pbias) {
+    const uint32_t ngrp = a.C / 8;
+    const int nv = a.prologue == PRO_LN ? 0 : a.prologue == PRO_LN_SHIFT2 ? 2 : 1;
+#pragma unroll
+    for (int q = 0; q < kLnVec; ++q) {
+        const uint32_t gi = threadIdx.x + q * kThreads;
+        if (gi < ngrp) {
+            cp_async16z(lnrow + gi * 8, a.ln_w + gi * 8, true);
+            cp_async16z(pbias + gi * 8, a.ln_b + gi * 8, true);
+            for (int vi = 0; vi < nv; ++vi)
+                cp_async16z(xgen + (size_t)vi * a.T * xp + gi * 8, (vi == 0 ? a.mix0 : a.mix1) + gi * 8, true);
+        }
+    }
+}
+
+__device__ void run_prologue(const FusedGemvArgs& a, __half* xgen, uint32_t xp, __half* lnrow, const __half* pbias,
+                             float* scratch) {
     const uint32_t C = a.C, T = a.T;
     const uint32_t ngrp = C / 8;  // 16-byte groups per row
-    for (uint32_t t = 0; t < T; ++t) {
+    const bool shift = a.prologue != PRO_LN;
+    // decode (T == 1): the carry row of the token shift goes in flight together with the input row
+    const bool early = shift && T == 1;
+    float prev1[kLnVec][8];
+    CursorD cu0 = CursorD{0, 0, 1};
+    if (early) cu0 = cursor_at(a.cursors, a.wide, 0);
+    for (int t = (int)T - 1; t >= 0; --t) {
         float v[kLnVec][8];
         float s = 0.f;
 #pragma unroll
@@ -221,6 +317,16 @@ __device__ void run_prologue(const FusedGemvArgs& a, __half* xgen, uint32_t xp, 
                 }
             }
         }
+        if (early) {
+#pragma unroll
+            for (int q = 0; q < kLnVec; ++q) {
+                const uint32_t gi = threadIdx.x + q * kThreads;
+                if (gi < ngrp)
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        prev1[q][e] = static_cast<const float*>(a.state.base)[a.state.index(gi * 8 + e, 0, cu0.batch)];
+            }
+        }
         const float mean = block_sum_256(s, scratch) / (float)C;
         float m2 = 0.f;
 #pragma unroll
@@ -236,8 +342,8 @@ __device__ void run_prologue(const FusedGemvArgs& a, __half* xgen, uint32_t xp, 
         for (int q = 0; q < kLnVec; ++q) {
             const uint32_t gi = threadIdx.x + q * kThreads;
             if (gi < ngrp) {
-                const uint4 wraw = *reinterpret_cast<const uint4*>(a.ln_w + gi * 8);
-                const uint4 braw = *reinterpret_cast<const uint4*>(a.ln_b + gi * 8);
+                const uint4 wraw = *reinterpret_cast<const uint4*>(lnrow + gi * 8);
+                const uint4 braw = *reinterpret_cast<const uint4*>(pbias + gi * 8);
                 const __half* wh = reinterpret_cast<const __half*>(&wraw);
                 const __half* bh = reinterpret_cast<const __half*>(&braw);
                 uint4 outv;
@@ -250,23 +356,183 @@ __device__ void run_prologue(const FusedGemvArgs& a, __half* xgen, uint32_t xp, 
             }
         }
     }
-    __syncthreads();
-    if (a.prologue == PRO_LN) return;  // the vectors are the normalised rows themselves
-    const int nv = a.prologue == PRO_LN_SHIFT2 ? 2 : 1;
-    for (uint32_t t = 0; t < T; ++t) {
-        const CursorD cu = cursor_at(a.cursors, a.wide, t);
-        for (uint32_t c = threadIdx.x; c < C; c += kThreads) {
-            const float cur = __half2float(lnrow[(size_t)t * xp + c]);
-            const float prev = (t == cu.token) ? static_cast<const float*>(a.state.base)[a.state.index(c, 0, cu.batch)]
-                                               : __half2float(lnrow[(size_t)(t - 1) * xp + c]);
-            const float lhs = a.reversed ? cur : prev, rhs = a.reversed ? prev : cur;
-            for (int vi = 0; vi < nv; ++vi) {
-                const float f = __half2float((vi == 0 ? a.mix0 : a.mix1)[c]);
-                xgen[((size_t)vi * T + t) * xp + c] = __float2half_rn(lhs * (1.0f - f) + rhs * f);
+    if (shift) {
+        const int nv = a.prologue == PRO_LN_SHIFT2 ? 2 : 1;
+        for (int t = (int)T - 1; t >= 0; --t) {
+            const CursorD cu = early ? cu0 : cursor_at(a.cursors, a.wide, (uint32_t)t);
+#pragma unroll
+            for (int q = 0; q < kLnVec; ++q) {
+                const uint32_t gi = threadIdx.x + q * kThreads;
+                if (gi >= ngrp) continue;
+                const uint4 craw = *reinterpret_cast<const uint4*>(lnrow + (size_t)t * xp + gi * 8);
+                const __half* ch = reinterpret_cast<const __half*>(&craw);
+                float prev[8];
+                if (early) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) prev[e] = prev1[q][e];
+                } else if ((uint32_t)t == cu.token) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        prev[e] = static_cast<const float*>(a.state.base)[a.state.index(gi * 8 + e, 0, cu.batch)];
+                } else {
+                    const uint4 praw = *reinterpret_cast<const uint4*>(lnrow + (size_t)(t - 1) * xp + gi * 8);
+                    const __half* ph = reinterpret_cast<const __half*>(&praw);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) prev[e] = __half2float(ph[e]);
+                }
+                for (int vi = 0; vi < nv; ++vi) {
+                    __half* region = xgen + (size_t)vi * T * xp;
+                    const uint4 fraw = *reinterpret_cast<const uint4*>(region + gi * 8);  // shift factors (row 0)
+                    const __half* fh = reinterpret_cast<const __half*>(&fraw);
+                    uint4 outv;
+                    __half* oh = reinterpret_cast<__half*>(&outv);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float cur = __half2float(ch[e]), f = __half2float(fh[e]);
+                        const float lhs = a.reversed ? cur : prev[e], rhs = a.reversed ? prev[e] : cur;
+                        oh[e] = __float2half_rn(lhs * (1.0f - f) + rhs * f);
+                    }
+                    *reinterpret_cast<uint4*>(region + (size_t)t * xp + gi * 8) = outv;
+                }
             }
         }
     }
     __syncthreads();
+}
+
+// Operands of the launch's epilogue for one output, fetched before the weights are multiplied so that
+// their memory round trip overlaps the main loop.
+struct EpiOperands {
+    float xres, r, cmx;
+    CursorD cu;
+};
+__device__ __forceinline__ EpiOperands epilogue_fetch(const FusedGemvArgs& a, const GemvProblem& p, uint32_t m, int tok) {
+    EpiOperands e;
+    e.xres = e.r = e.cmx = 0.f;
+    e.cu = CursorD{0, 0, 1};
+    if (a.epilogue == EPI_STORE) return e;
+    const size_t oi = (size_t)tok * p.M + m;
+    e.xres = __half2float(a.xres[oi]);
+    if (a.epilogue == EPI_CHANNEL_MIX) {
+        e.cu = cursor_at(a.cursors, a.wide, tok);
+        e.cmx = __half2float(a.cm_x[oi]);
+        if (a.cm_r != nullptr) e.r = __half2float(a.cm_r[oi]);
+    }
+    return e;
+}
+
+// Activation + the launch's epilogue for output (token tok, row m) of problem p.
+__device__ __forceinline__ void epilogue_one(const FusedGemvArgs& a, const GemvProblem& p, uint32_t m, int tok, float s,
+                                             const EpiOperands& e) {
+    s = activate_f(p.act, s);
+    const size_t oi = (size_t)tok * p.M + m;
+    if (a.epilogue == EPI_STORE) {
+        dstore(p.out, p.out_dtype, (size_t)tok * p.out_stride + m, s);
+    } else if (a.epilogue == EPI_RESIDUAL) {
+        // att_o is an fp16 tensor in the reference; x += att_o is rounded to fp16 again
+        const float o16 = __half2float(__float2half_rn(s));
+        a.xres[oi] = __float2half_rn(a.rescale * __half2float(__float2half_rn(e.xres + o16)));
+    } else {
+        // channel mix: carry row <- normalised ffn input at a sequence's last token;
+        // x += sigmoid(r) * v with the reference's fp16 rounding points
+        if ((uint32_t)tok - e.cu.token + 1u == e.cu.len)
+            static_cast<float*>(a.cm_state.base)[a.cm_state.index(m, 0, e.cu.batch)] = e.cmx;
+        const float v16 = __half2float(__float2half_rn(s));
+        float mixed = v16;
+        if (a.cm_r != nullptr) {
+            const float rr = 1.0f / (1.0f + expf(-e.r));
+            mixed = rr * v16;
+        }
+        const float o16 = __half2float(__float2half_rn(mixed));
+        const __half sum16 = __float2half_rn(e.xres + o16);
+        a.xres[oi] = a.rescale == 1.0f ? sum16 : __float2half_rn(a.rescale * __half2float(sum16));
+    }
+}
+
+// Multiplies one work item with the staged activations: out[0..3] = rows g / g + 8 x tokens 2 t4 / 2 t4 + 1.
+// The k-steps of an item alternate between two independent accumulators.
+__device__ __forceinline__ void consume_item(const GemvProblem& p, const Item& it, int c, const __half* xrow, bool xval,
+                                             const float* sums, uint32_t T, int t4, const __half* lut, float out[4]) {
+    if (p.kind == MAT_INT8) {
+        const uint32_t wa[8] = {it.q[0].x, it.q[0].y, it.q[0].z, it.q[0].w, it.q[1].x, it.q[1].y, it.q[1].z, it.q[1].w};
+        const uint32_t wb[8] = {it.q[2].x, it.q[2].y, it.q[2].z, it.q[2].w, it.q[3].x, it.q[3].y, it.q[3].z, it.q[3].w};
+        float d[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) d[i][0] = d[i][1] = d[i][2] = d[i][3] = 0.f;
+#pragma unroll
+        for (int s2 = 0; s2 < 4; ++s2) {
+            const uint32_t kk = c * 128 + (s2 < 2 ? 16 * t4 + 8 * s2 : 64 + 16 * t4 + 8 * (s2 - 2));
+            uint4 xq = make_uint4(0, 0, 0, 0);
+            if (xval) xq = *reinterpret_cast<const uint4*>(xrow + kk);
+            // bytes enter as 1024 + q (0x6400 | q): exact in fp16; the offset leaves through the block's sum of x
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t ua = wa[2 * s2 + h], ub = wb[2 * s2 + h];
+                mma16816(d[s2 & 1], __byte_perm(ua, 0x64646464u, 0x4140), __byte_perm(ub, 0x64646464u, 0x4140),
+                         __byte_perm(ua, 0x64646464u, 0x4342), __byte_perm(ub, 0x64646464u, 0x4342), h == 0 ? xq.x : xq.z,
+                         h == 0 ? xq.y : xq.w);
+            }
+        }
+        const float2 mmA = __half22float2(*reinterpret_cast<const __half2*>(&it.s[0]));
+        const float2 mmB = __half22float2(*reinterpret_cast<const __half2*>(&it.s[1]));
+        const uint32_t nblk = p.K / 128;
+        const uint32_t tk0 = 2 * t4, tk1 = tk0 + 1;
+        const float s0 = tk0 < T ? sums[tk0 * nblk + c] : 0.f, s1 = tk1 < T ? sums[tk1 * nblk + c] : 0.f;
+        const float sA = (mmA.y - mmA.x) * (1.0f / 255.0f), sB = (mmB.y - mmB.x) * (1.0f / 255.0f);
+        const float oA = mmA.x - 1024.0f * sA, oB = mmB.x - 1024.0f * sB;
+        out[0] = sA * (d[0][0] + d[1][0]) + oA * s0;
+        out[1] = sA * (d[0][1] + d[1][1]) + oA * s1;
+        out[2] = sB * (d[0][2] + d[1][2]) + oB * s0;
+        out[3] = sB * (d[0][3] + d[1][3]) + oB * s1;
+    } else if (p.kind == MAT_NF4) {
+        const uint32_t qa[8] = {it.q[0].x, it.q[0].y, it.q[0].z, it.q[0].w, it.q[1].x, it.q[1].y, it.q[1].z, it.q[1].w};
+        const uint32_t qb[8] = {it.q[2].x, it.q[2].y, it.q[2].z, it.q[2].w, it.q[3].x, it.q[3].y, it.q[3].z, it.q[3].w};
+        out[0] = out[1] = out[2] = out[3] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {  // four absmax blocks of 64 weights
+            const __half2 sa2 = *reinterpret_cast<const __half2*>(&it.s[j >> 1]);
+            const __half2 sb2 = *reinterpret_cast<const __half2*>(&it.s[2 + (j >> 1)]);
+            const float aA = __half2float((j & 1) ? __high2half(sa2) : __low2half(sa2));
+            const float aB = __half2float((j & 1) ? __high2half(sb2) : __low2half(sb2));
+            float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int s2 = 0; s2 < 2; ++s2) {
+                uint4 xq = make_uint4(0, 0, 0, 0);
+                if (xval && (uint32_t)(c * 256 + j * 64) < p.K)
+                    xq = *reinterpret_cast<const uint4*>(xrow + c * 256 + j * 64 + 16 * t4 + 8 * s2);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t ua = qa[2 * j + s2] >> (16 * h), ub = qb[2 * j + s2] >> (16 * h);
+                    const __half2 a0 = __halves2half2(lut[ua & 15u], lut[(ua >> 4) & 15u]);
+                    const __half2 a2 = __halves2half2(lut[(ua >> 8) & 15u], lut[(ua >> 12) & 15u]);
+                    const __half2 a1 = __halves2half2(lut[ub & 15u], lut[(ub >> 4) & 15u]);
+                    const __half2 a3 = __halves2half2(lut[(ub >> 8) & 15u], lut[(ub >> 12) & 15u]);
+                    mma16816(d, *reinterpret_cast<const uint32_t*>(&a0), *reinterpret_cast<const uint32_t*>(&a1),
+                             *reinterpret_cast<const uint32_t*>(&a2), *reinterpret_cast<const uint32_t*>(&a3),
+                             h == 0 ? xq.x : xq.z, h == 0 ? xq.y : xq.w);
+                }
+            }
+            out[0] = fmaf(d[0], aA, out[0]);
+            out[1] = fmaf(d[1], aA, out[1]);
+            out[2] = fmaf(d[2], aB, out[2]);
+            out[3] = fmaf(d[3], aB, out[3]);
+        }
+    } else {
+        // 64 fp16 weights per row: two 16-byte pieces per lane and row, independent accumulators
+        float d[2][4];
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {
+            d[hlf][0] = d[hlf][1] = d[hlf][2] = d[hlf][3] = 0.f;
+            const uint4 wa = it.q[hlf], wb = it.q[2 + hlf];
+            uint4 xq = make_uint4(0, 0, 0, 0);
+            if (xval && (uint32_t)(c * 64 + hlf * 32) < p.K)
+                xq = *reinterpret_cast<const uint4*>(xrow + c * 64 + hlf * 32 + 8 * t4);
+            mma16816(d[hlf], wa.x, wb.x, wa.y, wb.y, xq.x, xq.y);
+            mma16816(d[hlf], wa.z, wb.z, wa.w, wb.w, xq.z, xq.w);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) out[e] = d[0][e] + d[1][e];
+    }
 }
 
 __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemvArgs a) {
@@ -276,61 +542,82 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
     const uint32_t T = a.T;
-    const GemvSegment* segs = a.segments + (size_t)blockIdx.x * kSegmentsPerCta;
 
     // shared memory carve-up (all offsets multiples of 16 bytes)
     uint32_t kmax = 0;
     for (int i = 0; i < a.num_problems; ++i) kmax = max(kmax, a.p[i].K);
-    const uint32_t xp = (a.prologue != PRO_NONE ? a.C : kmax) + 8;  // halfs per activation row
-    uint8_t* slots = smem;
-    const int NSLOT = a.num_slots;
-    float* red = reinterpret_cast<float*>(slots + (size_t)NSLOT * SLOT);   // [kWarps][GROUP_ROWS][T]
-    float* sums = red + (size_t)kWarps * GROUP_ROWS * T;                    // [T][kmax / 128]
-    __half* xs = reinterpret_cast<__half*>(sums + sums_floats(T, kmax));    // staged x or prologue rows
-    __half* lnrow = xs;                                                     // PRO_LN: vectors = normalised rows
-    __half* xgen = a.prologue == PRO_LN ? xs : xs + (size_t)T * xp;         // shifted vectors follow the rows
+    const uint32_t xp = (a.prologue != PRO_NONE ? a.C : kmax) + 8;      // halfs per activation row
+    uint8_t* ring = smem + (size_t)warp * kRing * ITEM_BYTES;            // this warp's staging cells
+    float* red = reinterpret_cast<float*>(smem + (size_t)kWarps * kRing * ITEM_BYTES);  // [GROUP_ROWS][T] accumulator
+    float* sums = red + (size_t)GROUP_ROWS * kDecodeMaxTokens;           // [T][kmax / 128]
+    __half* xs = reinterpret_cast<__half*>(sums + sums_floats(T, kmax)); // staged x or prologue rows
+    __half* lnrow = xs;                                                  // PRO_LN: vectors = normalised rows
+    __half* xgen = a.prologue == PRO_LN ? xs : xs + (size_t)T * xp;      // shifted vectors follow the rows
+    const uint32_t pro_rows = a.prologue == PRO_LN ? T : a.prologue == PRO_LN_SHIFT1 ? 2 * T : 3 * T;
+    __half* pbias = xs + (size_t)pro_rows * xp;                          // layer-norm bias (prologues only)
 
     if (threadIdx.x < 16 && a.table != nullptr) lut[threadIdx.x] = __float2half_rn(a.table[threadIdx.x]);
-    __syncthreads();
     trace(100);
     pdl_launch_dependents();
-    trace(109);
 
-    // weights do not depend on earlier kernels: start streaming before waiting for them
-    TileIter prod, cons;
-    prod.start(a, segs);
-    cons = prod;
-    uint32_t issued = 0;
-    trace(110);
-    for (int s = 0; s < NSLOT; ++s) {
-        if (prod.valid) {
-            issue_tile(a, segs, prod, slots + s * SLOT);
-            prod.next(a, segs);
-            ++issued;
+    // ---- everything up to the wait touches only weights: each warp fetches its first item ----
+    Segs sg;
+    {
+        const int4* tab = reinterpret_cast<const int4*>(a.segments + (size_t)blockIdx.x * kSegmentsPerCta);
+#pragma unroll
+        for (int i = 0; i < kSegmentsPerCta; ++i) {
+            const int4 e = __ldg(tab + i);
+            sg.prob[i] = e.x;
+            sg.r0[i] = e.y;
+            sg.r1[i] = e.z;
         }
-        cp_async_commit();  // one group per slot, empty or not: the group count stays uniform
     }
-    trace(111);
+    int first_seg = 0;
+    while (first_seg < kSegmentsPerCta && sg.R0(first_seg) >= sg.R1(first_seg)) ++first_seg;
+    const bool any_work = first_seg < kSegmentsPerCta;
+    const bool pro = a.prologue != PRO_NONE && (any_work || blockIdx.x == 0);
+    if (pro) stage_prologue_params(a, xgen, xp, lnrow, pbias);
+    cp_async_commit();
+    Loader ld;
+    ld.start(a, sg, warp, lane);
+    uint32_t consumed = 0;
+#ifdef WRK_TRACE
+    long long clk_acc[4] = {0, 0, 0, 0}, clk_t[4] = {0, 0, 0, 0};
+#define WRK_CLK(i)                                                            \
+    do {                                                                      \
+        asm volatile("mov.u64 %0, %%clock64;" : "=l"(clk_t[i])::"memory");     \
+        if (i > 0) clk_acc[i] += clk_t[i] - clk_t[i - 1];                     \
+        else clk_acc[0] += 1;                                                 \
+    } while (0)
+#else
+#define WRK_CLK(i)
+#endif
+#pragma unroll
+    for (int d = 0; d < kRing; ++d) {
+        ld.issue(a, sg, ring + d * ITEM_BYTES, warp, lane);
+        cp_async_commit();  // one group per cell, empty or not
+    }
     trace(101);
     pdl_wait();
     trace(102);
 
-    if (a.prologue != PRO_NONE && (cons.valid || blockIdx.x == 0)) run_prologue(a, xgen, xp, lnrow, scratch);
-
+    if (pro) {
+        cp_async_wait<kRing>();  // this thread's parameter copies (it is their only reader)
+        run_prologue(a, xgen, xp, lnrow, pbias, scratch);
+    }
     trace(103);
-    float acc[GROUP_ROWS / 16][4];
+
     int staged_problem = -1;
-    uint32_t consumed = 0;
-    while (cons.valid) {
-        const GemvSegment& sg = segs[cons.seg];
-        const GemvProblem& p = a.p[sg.problem];
-        const __half* xv;  // this problem's activations in shared memory, pitch xp
-        if (p.x == nullptr) {
-            xv = xgen + (size_t)p.x_sel * T * xp;
-        } else {
-            xv = xs;
-        }
-        if (staged_problem != sg.problem) {
+    for (int seg = first_seg; seg < kSegmentsPerCta; ++seg) {
+        const int r0 = sg.R0(seg), r1 = sg.R1(seg);
+        if (r0 >= r1) continue;
+        const int problem = sg.P(seg);
+        const GemvProblem& p = a.p[problem];
+        const __half* xv = p.x == nullptr ? xgen + (size_t)p.x_sel * T * xp : xs;
+#ifdef WRK_TRACE
+        if (a.debug & 1) staged_problem = problem;
+#endif
+        if (staged_problem != problem) {
             // stage x (explicit inputs) and the per-128-block sums of the values the MMA will see:
             // 16 consecutive lanes cover one block of 128, so the sums come from the registers in flight
             __syncthreads();
@@ -369,195 +656,77 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
                     if (lane == 0) sums[tok * nblk + blk] = s;
                 }
             }
-            __syncthreads();
-            staged_problem = sg.problem;
+            staged_problem = problem;
         }
-        if (cons.part == 0 && cons.tile == 0) {
-#pragma unroll
-            for (int i = 0; i < GROUP_ROWS / 16; ++i)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
-        }
-
-        const int slot_i = consumed % NSLOT;
-        trace(104);
-        cp_async_wait(NSLOT - 1);  // this thread's copies of tile part `consumed` have landed ...
-        __syncthreads();           // ... and everyone else's
-        trace(105);
-        const uint8_t* slot = slots + slot_i * SLOT;
-        const uint32_t rb = row_bytes(p);
-        const uint32_t bytes = min((uint32_t)PB, rb - cons.part * PB);
-        const int rowA = cons.group0 + 16 * cons.tile + g, rowB = rowA + 8;
         const bool xval = (uint32_t)g < T;
-        const bool stma = scales_async(p);
-        const __half* xrow = xv + (size_t)(xval ? g : 0) * xp + (size_t)cons.part * part_elems(p.kind);
-        float ac[4];
-#pragma unroll
-        for (int i = 0; i < GROUP_ROWS / 16; ++i)
-            if (i == cons.tile) {
-                ac[0] = acc[i][0]; ac[1] = acc[i][1]; ac[2] = acc[i][2]; ac[3] = acc[i][3];
-            }
-        const uint8_t* sslot = slot + 16 * PITCH;  // this tile part's scales, SCP bytes per row
+        const __half* xrow = xv + (size_t)(xval ? g : 0) * xp;
+        const int nchunk = (row_bytes(p) + CHUNK_BYTES - 1) / CHUNK_BYTES;
 
-        if (p.kind == MAT_INT8) {
-            const uint32_t nblk = p.K / 128;
-            const __half2* sc = reinterpret_cast<const __half2*>(p.scale);
-            const bool vA = rowA < cons.gend, vB = rowB < cons.gend;
-            for (uint32_t c = warp; c < bytes / 128; c += kWarps) {
-                const uint32_t blk = cons.part * (PB / 128) + c;
-                const uint8_t* pa = slot + g * PITCH + c * 128 + 16 * t4;
-                const uint4 wa0 = *reinterpret_cast<const uint4*>(pa), wa1 = *reinterpret_cast<const uint4*>(pa + 64);
-                const uint4 wb0 = *reinterpret_cast<const uint4*>(pa + 8 * PITCH),
-                            wb1 = *reinterpret_cast<const uint4*>(pa + 8 * PITCH + 64);
-                float2 mmA = make_float2(0.f, 0.f), mmB = mmA;
-                if (stma) {
-                    mmA = __half22float2(*reinterpret_cast<const __half2*>(sslot + g * SCP + c * 4));
-                    mmB = __half22float2(*reinterpret_cast<const __half2*>(sslot + (g + 8) * SCP + c * 4));
-                } else {
-                    if (vA) mmA = __half22float2(__ldg(sc + (size_t)rowA * nblk + blk));
-                    if (vB) mmB = __half22float2(__ldg(sc + (size_t)rowB * nblk + blk));
-                }
-                const uint32_t wa[8] = {wa0.x, wa0.y, wa0.z, wa0.w, wa1.x, wa1.y, wa1.z, wa1.w};
-                const uint32_t wb[8] = {wb0.x, wb0.y, wb0.z, wb0.w, wb1.x, wb1.y, wb1.z, wb1.w};
-                float d[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int group0 = r0; group0 < r1; group0 += GROUP_ROWS) {
+            const int gend = min(group0 + GROUP_ROWS, r1);
+            const int nrows = gend - group0;
+            // nrows * T <= kThreads: one output per thread
+            const int orow = (int)threadIdx.x / (int)T, otok = (int)threadIdx.x - orow * (int)T;
+            const bool has_out = (int)threadIdx.x < nrows * (int)T;
+            EpiOperands eo;
+            if (has_out) {
+                red[threadIdx.x] = 0.f;
+                eo = epilogue_fetch(a, p, (uint32_t)(group0 + orow), otok);
+            }
+            __syncthreads();  // accumulator cleared, staged x and sums visible
+            trace(104);
+            // each warp walks its chunks of its row tile, keeping the tile's partial results in registers
+            const GroupMap gm = map_group(nrows, nchunk, warp);
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            int c = gm.ks;
+            for (int i = 0; i < gm.cnt; ++i, c += gm.kways) {
+#ifdef WRK_TRACE
+                if (a.debug & 2) break;
+#endif
+                WRK_CLK(0);
+                cp_async_wait<kRing - 1>();  // this lane's copies of the oldest item in flight have landed
+                WRK_CLK(1);
+                uint8_t* cell = ring + (consumed % kRing) * ITEM_BYTES;
+                const Item it = read_item(cell, lane);
+                // refill the cell with the item kRing steps ahead (the reads above are complete: `it` is in registers)
+                ld.issue(a, sg, cell, warp, lane);
+                cp_async_commit();
+                ++consumed;
+                WRK_CLK(2);
+                float out[4];
+                consume_item(p, it, c, xrow, xval, sums, T, t4, lut, out);
 #pragma unroll
-                for (int s2 = 0; s2 < 4; ++s2) {
-                    const uint32_t kk = c * 128 + (s2 < 2 ? 16 * t4 + 8 * s2 : 64 + 16 * t4 + 8 * (s2 - 2));
-                    uint4 xq = make_uint4(0, 0, 0, 0);
-                    if (xval) xq = *reinterpret_cast<const uint4*>(xrow + kk);
-                    mma16816(d, bytes_to_half2(wa[2 * s2], 0x4140), bytes_to_half2(wb[2 * s2], 0x4140),
-                             bytes_to_half2(wa[2 * s2], 0x4342), bytes_to_half2(wb[2 * s2], 0x4342), xq.x, xq.y);
-                    mma16816(d, bytes_to_half2(wa[2 * s2 + 1], 0x4140), bytes_to_half2(wb[2 * s2 + 1], 0x4140),
-                             bytes_to_half2(wa[2 * s2 + 1], 0x4342), bytes_to_half2(wb[2 * s2 + 1], 0x4342), xq.z, xq.w);
-                }
+                for (int e = 0; e < 4; ++e) acc[e] += out[e];
+                WRK_CLK(3);
+            }
+            if (gm.cnt > 0) {
+                const int rA = 16 * gm.tile + g, rB = rA + 8;
                 const uint32_t tk0 = 2 * t4, tk1 = tk0 + 1;
-                const float s0 = tk0 < T ? sums[tk0 * nblk + blk] : 0.f, s1 = tk1 < T ? sums[tk1 * nblk + blk] : 0.f;
-                const float sA = (mmA.y - mmA.x) * (1.0f / 255.0f), sB = (mmB.y - mmB.x) * (1.0f / 255.0f);
-                ac[0] += sA * d[0] + mmA.x * s0;
-                ac[1] += sA * d[1] + mmA.x * s1;
-                ac[2] += sB * d[2] + mmB.x * s0;
-                ac[3] += sB * d[3] + mmB.x * s1;
-            }
-        } else if (p.kind == MAT_NF4) {
-            const uint32_t nblk = p.K / 64;
-            const bool vA = rowA < cons.gend, vB = rowB < cons.gend;
-            for (uint32_t c = warp; c < bytes / 32; c += kWarps) {
-                const uint32_t blk = cons.part * (PB / 32) + c;
-                const uint8_t* pa = slot + g * PITCH + c * 32 + 8 * t4;
-                const uint2 wa = *reinterpret_cast<const uint2*>(pa), wb = *reinterpret_cast<const uint2*>(pa + 8 * PITCH);
-                float aA, aB;
-                if (stma) {
-                    aA = __half2float(*reinterpret_cast<const __half*>(sslot + g * SCP + c * 2));
-                    aB = __half2float(*reinterpret_cast<const __half*>(sslot + (g + 8) * SCP + c * 2));
-                } else {
-                    aA = vA ? __half2float(__ldg(p.scale + (size_t)rowA * nblk + blk)) : 0.f;
-                    aB = vB ? __half2float(__ldg(p.scale + (size_t)rowB * nblk + blk)) : 0.f;
+                if (rA < nrows) {
+                    if (tk0 < T) atomicAdd(&red[rA * T + tk0], acc[0]);
+                    if (tk1 < T) atomicAdd(&red[rA * T + tk1], acc[1]);
                 }
-                const uint32_t wau[2] = {wa.x, wa.y}, wbu[2] = {wb.x, wb.y};
-                float d[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int s2 = 0; s2 < 2; ++s2) {
-                    uint4 xq = make_uint4(0, 0, 0, 0);
-                    if (xval) xq = *reinterpret_cast<const uint4*>(xrow + c * 64 + 16 * t4 + 8 * s2);
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const uint32_t qa = wau[s2] >> (16 * h), qb = wbu[s2] >> (16 * h);
-                        const __half2 a0 = __halves2half2(lut[qa & 15u], lut[(qa >> 4) & 15u]);
-                        const __half2 a2 = __halves2half2(lut[(qa >> 8) & 15u], lut[(qa >> 12) & 15u]);
-                        const __half2 a1 = __halves2half2(lut[qb & 15u], lut[(qb >> 4) & 15u]);
-                        const __half2 a3 = __halves2half2(lut[(qb >> 8) & 15u], lut[(qb >> 12) & 15u]);
-                        mma16816(d, *reinterpret_cast<const uint32_t*>(&a0), *reinterpret_cast<const uint32_t*>(&a1),
-                                 *reinterpret_cast<const uint32_t*>(&a2), *reinterpret_cast<const uint32_t*>(&a3),
-                                 h == 0 ? xq.x : xq.z, h == 0 ? xq.y : xq.w);
-                    }
+                if (rB < nrows) {
+                    if (tk0 < T) atomicAdd(&red[rB * T + tk0], acc[2]);
+                    if (tk1 < T) atomicAdd(&red[rB * T + tk1], acc[3]);
                 }
-                ac[0] = fmaf(d[0], aA, ac[0]);
-                ac[1] = fmaf(d[1], aA, ac[1]);
-                ac[2] = fmaf(d[2], aB, ac[2]);
-                ac[3] = fmaf(d[3], aB, ac[3]);
             }
-        } else {
-            for (uint32_t c = warp; c < bytes / 64; c += kWarps) {
-                const uint8_t* pa = slot + g * PITCH + c * 64 + 16 * t4;
-                const uint4 wa = *reinterpret_cast<const uint4*>(pa), wb = *reinterpret_cast<const uint4*>(pa + 8 * PITCH);
-                uint4 xq = make_uint4(0, 0, 0, 0);
-                if (xval) xq = *reinterpret_cast<const uint4*>(xrow + c * 32 + 8 * t4);
-                mma16816(ac, wa.x, wb.x, wa.y, wb.y, xq.x, xq.y);
-                mma16816(ac, wa.z, wb.z, wa.w, wb.w, xq.z, xq.w);
-            }
+            trace(105);
+            __syncthreads();
+            if (has_out) epilogue_one(a, p, (uint32_t)(group0 + orow), otok, red[threadIdx.x], eo);
+            __syncthreads();  // the accumulator is free again
+            trace(106);
         }
-
-#pragma unroll
-        for (int i = 0; i < GROUP_ROWS / 16; ++i)
-            if (i == cons.tile) {
-                acc[i][0] = ac[0]; acc[i][1] = ac[1]; acc[i][2] = ac[2]; acc[i][3] = ac[3];
-            }
-        const bool finish = cons.last_part_of_group();
-        const int fin_group0 = cons.group0, fin_gend = cons.gend, fin_problem = sg.problem;
-        __syncthreads();  // everyone is done with this slot (and with `red` of the previous group)
-        ++consumed;
-        cons.next(a, segs);
-        if (prod.valid) {
-            // refill the slot just released with the tile part NSLOT steps ahead
-            issue_tile(a, segs, prod, slots + slot_i * SLOT);
-            prod.next(a, segs);
-            ++issued;
-        }
-        cp_async_commit();
-        if (!finish) continue;
-
-        // ---- group finished: cross-warp reduction and epilogue ----
-        const GemvProblem& fp = a.p[fin_problem];
-#pragma unroll
-        for (int i = 0; i < GROUP_ROWS / 16; ++i) {
-            const int r0 = 16 * i + g;
-            const uint32_t tk0 = 2 * t4, tk1 = tk0 + 1;
-            float* r = red + (size_t)warp * GROUP_ROWS * T;
-            if (tk0 < T) {
-                r[(size_t)r0 * T + tk0] = acc[i][0];
-                r[(size_t)(r0 + 8) * T + tk0] = acc[i][2];
-            }
-            if (tk1 < T) {
-                r[(size_t)r0 * T + tk1] = acc[i][1];
-                r[(size_t)(r0 + 8) * T + tk1] = acc[i][3];
-            }
-        }
-        __syncthreads();
-        const int nrows = fin_gend - fin_group0;
-        for (int o = threadIdx.x; o < nrows * (int)T; o += kThreads) {
-            const int row = o % nrows, tok = o / nrows;
-            float s = 0.f;
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) s += red[((size_t)w * GROUP_ROWS + row) * T + tok];
-            s = activate_f(fp.act, s);
-            const uint32_t m = fin_group0 + row;
-            const size_t oi = (size_t)tok * fp.M + m;
-            if (a.epilogue == EPI_STORE) {
-                dstore(fp.out, fp.out_dtype, (size_t)tok * fp.out_stride + m, s);
-            } else if (a.epilogue == EPI_RESIDUAL) {
-                // att_o is an fp16 tensor in the reference; x += att_o is rounded to fp16 again
-                const float o16 = __half2float(__float2half_rn(s));
-                a.xres[oi] = __float2half_rn(a.rescale * __half2float(__float2half_rn(__half2float(a.xres[oi]) + o16)));
-            } else {
-                // channel mix: carry row <- normalised ffn input at a sequence's last token;
-                // x += sigmoid(r) * v with the reference's fp16 rounding points
-                const CursorD cu = cursor_at(a.cursors, a.wide, tok);
-                if ((uint32_t)tok - cu.token + 1u == cu.len)
-                    static_cast<float*>(a.cm_state.base)[a.cm_state.index(m, 0, cu.batch)] = __half2float(a.cm_x[oi]);
-                const float v16 = __half2float(__float2half_rn(s));
-                float mixed = v16;
-                if (a.cm_r != nullptr) {
-                    const float rr = 1.0f / (1.0f + expf(-__half2float(a.cm_r[oi])));
-                    mixed = rr * v16;
-                }
-                const float o16 = __half2float(__float2half_rn(mixed));
-                const __half sum16 = __float2half_rn(__half2float(a.xres[oi]) + o16);
-                a.xres[oi] = a.rescale == 1.0f ? sum16 : __float2half_rn(a.rescale * __half2float(sum16));
-            }
-        }
-        // `red` is reused by the next group only after the __syncthreads that follows its first tile part
-        trace(106);
     }
+#ifdef WRK_TRACE
+    if (blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 7)) {
+        const unsigned int base = atomicAdd(&g_trace_n, 4u);
+        for (int k2 = 0; k2 < 4; ++k2) {
+            g_trace[2 * (base + k2)] = 200 + warp * 4 + k2;
+            g_trace[2 * (base + k2) + 1] = (unsigned long long)clk_acc[k2];
+        }
+    }
+#endif
     trace(107);
 }
 
@@ -586,19 +755,28 @@ __global__ void __launch_bounds__(256) tmix_shift_kernel(const TmixArgs a) {
     const bool active = o < 5 * C;
     const uint32_t i = active ? o / C : 0, c = active ? o % C : 0;
     uint4 wreg[8];  // D <= 64 halfs
+    float mu = 0.f;
     if (active) {
         const uint4* wp = reinterpret_cast<const uint4*>(a.w2 + ((size_t)i * C + c) * D);
-        for (uint32_t j = 0; j < D / 8; ++j) wreg[j] = wp[j];
+#pragma unroll
+        for (uint32_t j = 0; j < 8; ++j)
+            if (j < D / 8) wreg[j] = wp[j];
+        mu = __half2float(a.mix[(size_t)i * C + c]);
     }
     pdl_wait();
+    // every input of token 0 goes in flight before the first barrier: one memory round trip, not four
     for (uint32_t j = threadIdx.x; j < T * 5 * D; j += blockDim.x) s_tmx[j] = a.tmx[j];
+    const CursorD cu0 = cursor_at(a.cursors, a.wide, 0);
+    const float cur0 = active ? __half2float(a.att_x[c]) : 0.f;
+    const float prev0 = (active && cu0.token == 0) ? static_cast<const float*>(a.state.base)[a.state.index(c, 0, cu0.batch)] : 0.f;
     __syncthreads();
     if (!active) return;
-    const float mu = __half2float(a.mix[(size_t)i * C + c]);
     for (uint32_t t = 0; t < T; ++t) {
         float acc = 0.f;
         const __half* xv = s_tmx + (size_t)t * 5 * D + i * D;
-        for (uint32_t j = 0; j < D / 8; ++j) {
+#pragma unroll
+        for (uint32_t j = 0; j < 8; ++j) {
+            if (j >= D / 8) break;
             const __half2* w2 = reinterpret_cast<const __half2*>(&wreg[j]);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -609,44 +787,68 @@ __global__ void __launch_bounds__(256) tmix_shift_kernel(const TmixArgs a) {
         }
         // time_mix buffer is fp16: matmul result rounded, then the static mix added and rounded again
         const float f = __half2float(__float2half_rn(__half2float(__float2half_rn(acc)) + mu));
-        const CursorD cu = cursor_at(a.cursors, a.wide, t);
-        const float cur = __half2float(a.att_x[(size_t)t * C + c]);
-        const float prev = (t == cu.token) ? static_cast<const float*>(a.state.base)[a.state.index(c, 0, cu.batch)]
-                                           : __half2float(a.att_x[(size_t)(t - 1) * C + c]);
+        float cur, prev;
+        if (t == 0) {
+            cur = cur0;
+            prev = prev0;
+        } else {
+            const CursorD cu = cursor_at(a.cursors, a.wide, t);
+            cur = __half2float(a.att_x[(size_t)t * C + c]);
+            prev = (t == cu.token) ? static_cast<const float*>(a.state.base)[a.state.index(c, 0, cu.batch)]
+                                   : __half2float(a.att_x[(size_t)(t - 1) * C + c]);
+        }
         a.sx[((size_t)i * T + t) * C + c] = __float2half_rn(cur * (1.0f - f) + prev * f);
     }
 }
 
 // ---- v5 / v6 time-mix block: decay adapter, WKV, group norm, gate --------------------------------
+// One CTA per (head, batch slot), 4 * S threads: thread (q, j) owns rows [q S/4, (q+1) S/4) of state column j,
+// a quarter of the decay-adapter dot product of channel j and a quarter of output j's sum.
 template <int S>
-__global__ void __launch_bounds__(S) wkv56_fused_kernel(const Wkv6Args a) {
-    __shared__ float sk[S], sr[S], sw[S], su[S], red[4];
-    __shared__ __half s_tdw[64 * kDecodeMaxTokens];
+__global__ void __launch_bounds__(4 * S) wkv56_fused_kernel(const Wkv6Args a) {
+    constexpr int Q = 4, SI = S / Q;
+    __shared__ float sk[S], sr[S], sw[S], su[S], part[Q][S], red[Q * S / 32];
+    __shared__ __half s_tdw[128];
     __shared__ uint32_t s_start, s_count;
     pdl_launch_dependents();
-    const uint32_t h = blockIdx.x, slot = blockIdx.y, j = threadIdx.x;
+    const uint32_t h = blockIdx.x, slot = blockIdx.y, j = threadIdx.x % S, q = threadIdx.x / S;
     const uint32_t C = S * a.H, c = h * S + j;
+    const uint32_t dq = a.D / Q;  // adapter inputs per quarter (a multiple of 8, at most 32)
 
-    // state column, decay-adapter row and per-channel constants do not depend on this job's kernels...
-    uint4 w2reg[8];
+    // the decay-adapter row and the per-channel constants do not depend on this job's kernels...
+    uint4 w2reg[4];
+    float td_static = 0.f, td5 = 0.f;
     if (a.per_token_decay) {
-        const uint4* wp = reinterpret_cast<const uint4*>(a.td_w2 + (size_t)c * a.D);
-        for (uint32_t q = 0; q < a.D / 8; ++q) w2reg[q] = wp[q];
+        const uint4* wp = reinterpret_cast<const uint4*>(a.td_w2 + (size_t)c * a.D + q * dq);
+#pragma unroll
+        for (uint32_t e = 0; e < 4; ++e)
+            if (e < dq / 8) w2reg[e] = wp[e];
+        td_static = __half2float(a.td0[c]);
+    } else {
+        td5 = a.td5[c];
     }
-    su[j] = a.time_first[c];
-    const float td_static = a.per_token_decay ? __half2float(a.td0[c]) : 0.f;
+    if (q == 0) su[j] = a.time_first[c];
     const float gw = __half2float(a.gn_w[c]), gb = __half2float(a.gn_b[c]);
     pdl_wait();  // ...the state does (the previous token's job wrote it), and so do the cursors
 
+    // the state rows are needed whatever the cursors say: get their loads in flight first
+    float st[SI];
+#pragma unroll
+    for (int i = 0; i < SI; ++i) st[i] = static_cast<const float*>(a.state.base)[a.state.index(c, 1 + q * SI + i, slot)];
+
     // run of tokens of this batch slot
-    if (j == 0) {
-        s_start = 0xffffffffu;
-        s_count = 0;
-    }
-    __syncthreads();
-    {
+    uint32_t start, count;
+    if (a.T == 1) {
+        start = 0;
+        count = cursor_at(a.cursors, a.wide, 0).batch == slot ? 1u : 0u;
+    } else {
+        if (threadIdx.x == 0) {
+            s_start = 0xffffffffu;
+            s_count = 0;
+        }
+        __syncthreads();
         uint32_t mn = 0xffffffffu, cnt = 0;
-        for (uint32_t t = j; t < a.T; t += S) {
+        for (uint32_t t = threadIdx.x; t < a.T; t += Q * S) {
             const CursorD cu = cursor_at(a.cursors, a.wide, t);
             if (cu.batch == slot) {
                 mn = min(mn, t);
@@ -657,78 +859,85 @@ __global__ void __launch_bounds__(S) wkv56_fused_kernel(const Wkv6Args a) {
             atomicMin(&s_start, mn);
             atomicAdd(&s_count, cnt);
         }
+        __syncthreads();
+        start = s_start;
+        count = s_count;
     }
-    __syncthreads();
-    const uint32_t start = s_start, count = s_count;
     if (count == 0) return;
-
-    float st[S];
-#pragma unroll
-    for (int i = 0; i < S; ++i) st[i] = static_cast<const float*>(a.state.base)[a.state.index(c, 1 + i, slot)];
 
     for (uint32_t n = 0; n < count; ++n) {
         const uint32_t t = start + n;
         const size_t ti = (size_t)t * C + c;
+        // all of the token's inputs go in flight together
+        const float kj = a.k[ti], rj = a.r[ti], vj = a.v[ti];
+        const float gg = __half2float(a.g[ti]), ax = __half2float(a.att_x[ti]);
+        __half tdh = __float2half_rn(0.f);
+        if (a.per_token_decay && threadIdx.x < a.D) tdh = a.tdw[(size_t)t * a.D + threadIdx.x];
+        const CursorD cu = cursor_at(a.cursors, a.wide, t);
+        __syncthreads();  // the previous token's readers are done
+        if (q == 0) {
+            sk[j] = kj;
+            sr[j] = rj;
+        }
+        if (a.per_token_decay && threadIdx.x < a.D) s_tdw[threadIdx.x] = tdh;
         __syncthreads();
-        if (a.per_token_decay)
-            for (uint32_t q = j; q < a.D; q += S) s_tdw[q] = a.tdw[(size_t)t * a.D + q];
-        sk[j] = a.k[ti];
-        sr[j] = a.r[ti];
-        __syncthreads();
-        float wj;
         if (a.per_token_decay) {
             float acc = 0.f;
-            for (uint32_t q = 0; q < a.D / 8; ++q) {
-                const __half2* w2 = reinterpret_cast<const __half2*>(&w2reg[q]);
+            const __half* xv = s_tdw + q * dq;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 wf = __half22float2(w2[e]);
-                    acc = fmaf(wf.x, __half2float(s_tdw[q * 8 + 2 * e]), acc);
-                    acc = fmaf(wf.y, __half2float(s_tdw[q * 8 + 2 * e + 1]), acc);
+            for (uint32_t e = 0; e < 4; ++e) {
+                if (e >= dq / 8) break;
+                const __half2* w2 = reinterpret_cast<const __half2*>(&w2reg[e]);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float2 wf = __half22float2(w2[u]);
+                    acc = fmaf(wf.x, __half2float(xv[e * 8 + 2 * u]), acc);
+                    acc = fmaf(wf.y, __half2float(xv[e * 8 + 2 * u + 1]), acc);
                 }
             }
-            wj = expf(-expf(acc + td_static));  // time_decay buffer is f32: no rounding before the activation
-        } else {
-            wj = a.td5[c];
+            part[q][j] = acc;
+            __syncthreads();
+            // time_decay buffer is f32: no rounding before the activation
+            if (q == 0) sw[j] = expf(-expf(((part[0][j] + part[1][j]) + (part[2][j] + part[3][j])) + td_static));
+        } else if (q == 0) {
+            sw[j] = td5;
         }
-        sw[j] = wj;
         __syncthreads();
-        const float vj = a.v[ti];
-        float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+        float y0 = 0.f, y1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < S; i += 4) {
+        for (int ii = 0; ii < SI; ii += 2) {
+            const int i = q * SI + ii;
             float kv;
-            kv = sk[i] * vj;     y0 += sr[i] * fmaf(su[i], kv, st[i]);             st[i] = fmaf(sw[i], st[i], kv);
-            kv = sk[i + 1] * vj; y1 += sr[i + 1] * fmaf(su[i + 1], kv, st[i + 1]); st[i + 1] = fmaf(sw[i + 1], st[i + 1], kv);
-            kv = sk[i + 2] * vj; y2 += sr[i + 2] * fmaf(su[i + 2], kv, st[i + 2]); st[i + 2] = fmaf(sw[i + 2], st[i + 2], kv);
-            kv = sk[i + 3] * vj; y3 += sr[i + 3] * fmaf(su[i + 3], kv, st[i + 3]); st[i + 3] = fmaf(sw[i + 3], st[i + 3], kv);
+            kv = sk[i] * vj;     y0 += sr[i] * fmaf(su[i], kv, st[ii]);             st[ii] = fmaf(sw[i], st[ii], kv);
+            kv = sk[i + 1] * vj; y1 += sr[i + 1] * fmaf(su[i + 1], kv, st[ii + 1]); st[ii + 1] = fmaf(sw[i + 1], st[ii + 1], kv);
         }
-        const float y = (y0 + y1) + (y2 + y3);
-        const CursorD cu = cursor_at(a.cursors, a.wide, t);
-        if (t - cu.token + 1u == cu.len)
-            static_cast<float*>(a.state.base)[a.state.index(c, 0, slot)] = __half2float(a.att_x[ti]);
-        // group norm over the head's S outputs (f32 buffer in the reference), then fp16, then the gate
+        part[q][j] = y0 + y1;
+        if (q == 0 && t - cu.token + 1u == cu.len) static_cast<float*>(a.state.base)[a.state.index(c, 0, slot)] = ax;
+        __syncthreads();
+        const float y = (part[0][j] + part[1][j]) + (part[2][j] + part[3][j]);
+        // group norm over the head's S outputs (f32 buffer in the reference), then fp16, then the gate;
+        // every quarter repeats it on the same values, quarter 0 stores
+        const uint32_t wbase = q * (S / 32);
         float s = warp_sum(y);
-        if ((j & 31) == 0) red[j >> 5] = s;
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
         __syncthreads();
         float tot = 0.f;
-        for (int w = 0; w < S / 32; ++w) tot += red[w];
+        for (int w = 0; w < S / 32; ++w) tot += red[wbase + w];
         const float mean = tot / (float)S;
         const float dlt = y - mean;
         __syncthreads();
         s = warp_sum(dlt * dlt);
-        if ((j & 31) == 0) red[j >> 5] = s;
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
         __syncthreads();
         tot = 0.f;
-        for (int w = 0; w < S / 32; ++w) tot += red[w];
+        for (int w = 0; w < S / 32; ++w) tot += red[wbase + w];
         const float dev = rsqrtf(tot / (float)S + a.gn_eps);
         const float gn16 = __half2float(__float2half_rn(fmaf(dlt * dev, gw, gb)));
-        const float gg = __half2float(a.g[ti]);
         const float silu = gg / (1.0f + expf(-gg));
-        a.out[ti] = __float2half_rn(silu * gn16);
+        if (q == 0) a.out[ti] = __float2half_rn(silu * gn16);
     }
 #pragma unroll
-    for (int i = 0; i < S; ++i) static_cast<float*>(a.state.base)[a.state.index(c, 1 + i, slot)] = st[i];
+    for (int i = 0; i < SI; ++i) static_cast<float*>(a.state.base)[a.state.index(c, 1 + q * SI + i, slot)] = st[i];
 }
 
 template <typename Kernel, typename Args>
@@ -788,34 +997,29 @@ bool fused_gemv_partition(const FusedGemvArgs& a, int grid, std::vector<GemvSegm
     return prob == a.num_problems;
 }
 
-size_t fused_gemv_smem(uint32_t T, uint32_t Kmax, uint32_t C, int prologue, int num_slots) {
+size_t fused_gemv_smem(uint32_t T, uint32_t Kmax, uint32_t C, int prologue, int /*num_slots*/) {
     const uint32_t xp = (prologue != PRO_NONE ? C : Kmax) + 8;
-    size_t bytes = (size_t)num_slots * SLOT;
-    bytes += (size_t)kWarps * GROUP_ROWS * T * sizeof(float);
+    size_t bytes = (size_t)kWarps * kRing * ITEM_BYTES + (size_t)GROUP_ROWS * kDecodeMaxTokens * sizeof(float);
     bytes += (size_t)sums_floats(T, Kmax) * sizeof(float);
-    const size_t rows = prologue == PRO_NONE || prologue == PRO_LN ? T : prologue == PRO_LN_SHIFT1 ? 2 * T : 3 * T;
+    // activation rows (+ one row of layer-norm bias for the prologues)
+    const size_t rows = prologue == PRO_NONE ? T : (prologue == PRO_LN ? T : prologue == PRO_LN_SHIFT1 ? 2 * T : 3 * T) + 1;
     bytes += rows * xp * sizeof(__half);
     return bytes + 64;
 }
 
-int fused_gemv_slots(uint32_t T, uint32_t Kmax, uint32_t C, int prologue) {
-    // as many slots as keep two CTAs (this kernel's and the next one's) resident per SM
-    int n = MAX_SLOTS;
-    while (n > 2 && fused_gemv_smem(T, Kmax, C, prologue, n) > 100 * 1024) --n;
-    return n;
-}
-
 cudaError_t fused_gemv(const FusedGemvArgs& a_in, int grid, cudaStream_t stream) {
     FusedGemvArgs a = a_in;
+#ifdef WRK_TRACE
+    if (const char* e = getenv("WRK_DEBUG_SKIP")) a.debug = atoi(e);
+#endif
     uint32_t kmax = 0;
     for (int i = 0; i < a.num_problems; ++i) kmax = std::max(kmax, a.p[i].K);
-    a.num_slots = fused_gemv_slots(a.T, kmax, a.C, a.prologue);
-    const size_t smem = fused_gemv_smem(a.T, kmax, a.C, a.prologue, a.num_slots);
-    static size_t configured = 0;
-    if (smem > configured) {
+    const size_t smem = fused_gemv_smem(a.T, kmax, a.C, a.prologue, 0);
+    static bool configured = false;
+    if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(fused_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return e;
-        configured = 200 * 1024;
+        configured = true;
     }
     return launch_pdl(fused_gemv_kernel, dim3(grid), dim3(kThreads), smem, stream, a);
 }
@@ -827,7 +1031,7 @@ cudaError_t tmix_shift_v6(const TmixArgs& a, cudaStream_t stream) {
 }
 
 cudaError_t wkv56_fused(const Wkv6Args& a, cudaStream_t stream) {
-    return launch_pdl(wkv56_fused_kernel<64>, dim3(a.H, a.B), dim3(64), 0, stream, a);
+    return launch_pdl(wkv56_fused_kernel<64>, dim3(a.H, a.B), dim3(256), 0, stream, a);
 }
 
 }  // namespace k

@@ -36,7 +36,8 @@ constexpr int kSegmentsPerCta = 3;
 struct FusedGemvArgs {
     GemvProblem p[kMaxProblems];
     int32_t num_problems;
-    int32_t num_slots;            // filled by the launcher
+    int32_t num_slots;            // unused
+    int32_t debug;                // ablation mask (WRK_TRACE builds only)
     uint32_t T;
     const GemvSegment* segments;  // [grid][kSegmentsPerCta], row0 == row1 marks an unused entry
     const float* table;           // NF4 code book (device)

@@ -77,8 +77,8 @@ int32_t matmul_common(const char* name, int kind, wrk_tensor* matrix, wrk_tensor
     a.out = make_dview(*output);
     a.act = act;
     const int sms = matrix->ctx->num_sms;
-    // few tokens, fp16 activations, whole rows: the TMA weight-streaming kernel of the decode path
-    const uint32_t need = kind == k::MAT_INT8 ? 128 : kind == k::MAT_NF4 ? 64 : 32;
+    // few tokens, fp16 activations, whole rows: the weight-streaming kernel of the decode path
+    const uint32_t need = kind == k::MAT_FP16 ? 32 : 128;
     const size_t in_row0 = a.in.index(0, 0, 0), out_row0 = a.out.index(0, 0, 0);
     const bool stream_ok = b == 1 && n >= 1 && n <= (uint32_t)k::kDecodeMaxTokens && a.in.dtype == WRK_F16 &&
                            k % need == 0 && in_row0 % 8 == 0 && a.in.stride[0] % 8 == 0 &&

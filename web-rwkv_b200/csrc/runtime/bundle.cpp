@@ -398,7 +398,7 @@ MatInfo mat_info(wrk_matrix* m) {
 }
 
 bool mat_fusable(const MatInfo& m) {
-    const uint32_t need = m.kind == k::MAT_INT8 ? 128 : m.kind == k::MAT_NF4 ? 64 : 32;
+    const uint32_t need = m.kind == k::MAT_FP16 ? 32 : 128;
     return m.K % need == 0 && m.K % 8 == 0;
 }
 
@@ -451,7 +451,7 @@ bool fused_v6_supported(wrk_bundle* bd, uint32_t T) {
     const wrk_model_info& info = bd->model->info;
     if (!bd->fused || info.version != 6 || T == 0 || T > (uint32_t)k::kDecodeMaxTokens) return false;
     if (info.num_emb / info.num_head != 64 || info.num_emb % 128 || info.custom[0] % 8 || info.custom[0] > 64 ||
-        info.custom[1] % 8 || info.custom[1] > 64)
+        info.custom[1] % 32 || info.custom[1] > 128)
         return false;
     for (auto& L : bd->model->layers)
         for (wrk_matrix* m : {L.att_w_k.p, L.att_w_v.p, L.att_w_r.p, L.att_w_g.p, L.att_w_o.p, L.ffn_w_k.p, L.ffn_w_v.p,
