@@ -231,6 +231,25 @@ int32_t wrk_matrix_matmul_op_sparse(wrk_matrix* m, const wrk_view* input, const 
 /* The default NF4 table of Float4Quant::new, matrix.rs:48-70. */
 int32_t wrk_nf4_table(float table[16]);
 
+/* ---- No counterpart in the reference ----
+ * y[t][m] = act(W[m][:] . x[t][:]) for an Int8 matrix (the layout quantize_mat_int8 produces: u8 W[m][k], f16
+ * (min, max) per 128-weight block), f16 x[t][k], f32 y[t][m], all raw device pointers, launched on `cuda_stream`
+ * of `device`, which must be the current device.  The call allocates nothing, on the device or through any
+ * library: the only scratch the kernel needs, its table of row ranges per CTA, lives in a static device array
+ * of 512 ranges (24 KB).  It is for callers that must not allocate where they stand: inside a region the
+ * application has fenced off from the allocator (all device memory handed to its own arena up front, so a
+ * cudaMalloc would fail or stall every stream of the process), or on a latency-critical thread that may not
+ * take the allocator's locks.
+ *   - The first call on a device also looks up the array's address and the device's SM count; make that call
+ *     once at start-up, before any stream capture.  Later calls only launch kernels.
+ *   - num_ctas = 0 uses one CTA per SM; more than 512 is refused with WRK_ERR_SIZE.  k must be a multiple of
+ *     128 small enough for t rows of x to be staged in shared memory, 1 <= t <= 8; else WRK_ERR_SHAPE.
+ *   - Every call on a device rewrites the same array (nothing in it has to be zero beforehand): two calls
+ *     that can run at the same time, from two streams or two threads, race.  Order them on one stream.
+ * matrix and x must be 16-byte aligned. */
+int32_t wrk_gemv_int8_static(int32_t device, void* cuda_stream, const void* matrix, const void* minmax, const void* x,
+                             void* y, uint32_t k, uint32_t m, uint32_t t, int32_t act, uint32_t num_ctas);
+
 #ifdef __cplusplus
 }
 #endif

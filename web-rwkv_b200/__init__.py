@@ -430,3 +430,21 @@ class Matrix:
         (pi, ki), (po, ko) = _v(input), _v(output)
         fn = "wrk_matrix_matmul_op_sparse" if sparse else "wrk_matrix_matmul_op"
         return _mk(fn, self.handle, pi, po, act, int(turbo), keep=(self, ki, ko))
+
+
+def gemv_int8_static(ctx, matrix, minmax, x, y, act=ACT_NONE, num_ctas=0, device=0):
+    """`wrk_gemv_int8_static` (no counterpart in the reference): y[t][m] = act(W[m][:] . x[t][:]) on the context's
+    stream without any allocation; the kernel's row-range table sits in a static device array (512 CTAs at most).
+    `matrix` u8 [k, m], `minmax` f16 pairs, `x` f16 [k, t], `y` f32 [m, t]."""
+    ptrs = []
+    for t in (matrix, minmax, x, y):
+        p = ctypes.c_void_p()
+        check(lib().wrk_tensor_device_ptr(t.handle, ctypes.byref(p)))
+        ptrs.append(p)
+    stream = ctypes.c_void_p()
+    check(lib().wrk_context_stream(ctx.handle, ctypes.byref(stream)))
+    k, m = matrix.shape[0], matrix.shape[1]
+    t = x.shape[1]
+    check(lib().wrk_gemv_int8_static(ctypes.c_int32(device), stream, ptrs[0], ptrs[1], ptrs[2], ptrs[3],
+                                     ctypes.c_uint32(k), ctypes.c_uint32(m), ctypes.c_uint32(t), ctypes.c_int32(act),
+                                     ctypes.c_uint32(num_ctas)))

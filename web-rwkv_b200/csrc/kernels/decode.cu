@@ -24,6 +24,8 @@
 #include "decode.cuh"
 #include "device.cuh"
 
+#include <mutex>
+
 namespace wrk {
 namespace k {
 
@@ -1032,6 +1034,108 @@ cudaError_t tmix_shift_v6(const TmixArgs& a, cudaStream_t stream) {
 
 cudaError_t wkv56_fused(const Wkv6Args& a, cudaStream_t stream) {
     return launch_pdl(wkv56_fused_kernel<64>, dim3(a.H, a.B), dim3(256), 0, stream, a);
+}
+
+// ---- Int8 GEMV with its row-range table in static device memory -------------------------------------
+// Same kernel as fused_gemv; the table it reads sits in the array below instead of in a tensor, and a
+// one-thread kernel fills it on the caller's stream right before the multiply, so no call allocates.
+// Every call on a device uses the same array: calls that overlap in time (two streams, two threads) race.
+namespace {
+
+static __device__ __align__(256) GemvSegment g_static_segments[kStaticGemvMaxCtas * kSegmentsPerCta];
+
+// The partition fused_gemv_partition computes for a single matrix, with the same double arithmetic
+// (explicitly rounded operations, so no fused multiply-add changes a row split).  Every entry of the
+// CTAs' ranges is written, so the array needs no particular contents beforehand.
+__global__ void static_partition_kernel(GemvSegment* table, uint32_t K, uint32_t M, int grid) {
+    if (blockIdx.x != 0 || threadIdx.x != 0) return;
+    const double cost = __dmul_rn((double)K, 1.03125);
+    const double total = __dmul_rn(cost, (double)M);
+    uint32_t row = 0;
+    double done = 0.0;
+    for (int c = 0; c < grid; ++c) {
+        GemvSegment* e = table + (size_t)c * kSegmentsPerCta;
+        for (int i = 0; i < kSegmentsPerCta; ++i) e[i] = GemvSegment{0, 0, 0, 0};
+        if (row >= M) continue;
+        uint32_t take = M - row;
+        if (c != grid - 1) {
+            const double target = __ddiv_rn(__dmul_rn(total, (double)(c + 1)), (double)grid);
+            const double want = ceil(__dsub_rn(__ddiv_rn(__dsub_rn(target, done), cost), 1e-9));
+            take = (uint32_t)fmin((double)take, fmax(0.0, want));
+        }
+        if (take > 0) {
+            e[0] = GemvSegment{0, (int32_t)row, (int32_t)(row + take), 0};
+            row += take;
+            done = __dadd_rn(done, __dmul_rn((double)take, cost));
+        }
+    }
+}
+
+struct StaticSetup {
+    GemvSegment* table = nullptr;
+    int sms = 0;
+    bool ready = false;
+};
+StaticSetup g_static_setup[kStaticGemvMaxDevices];
+std::mutex g_static_mutex;
+
+}  // namespace
+
+int gemv_int8_static(int device, cudaStream_t stream, const uint8_t* w, const __half* minmax, const __half* x, float* y,
+                     uint32_t K, uint32_t M, uint32_t T, int act, uint32_t num_ctas, cudaError_t* cuda_error) {
+    *cuda_error = cudaSuccess;
+    if (device < 0 || device >= kStaticGemvMaxDevices) return SG_BAD_DEVICE;
+    int current = -1;
+    if ((*cuda_error = cudaGetDevice(&current)) != cudaSuccess) return SG_CUDA;
+    if (current != device) return SG_BAD_DEVICE;
+    StaticSetup& su = g_static_setup[device];
+    {
+        // first call on this device: the array's address, the SM count and the kernel's shared-memory limit
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (!su.ready) {
+            void* ptr = nullptr;
+            if ((*cuda_error = cudaGetSymbolAddress(&ptr, g_static_segments)) != cudaSuccess) return SG_CUDA;
+            if ((*cuda_error = cudaDeviceGetAttribute(&su.sms, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess)
+                return SG_CUDA;
+            if ((*cuda_error = cudaFuncSetAttribute(fused_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    200 * 1024)) != cudaSuccess)
+                return SG_CUDA;
+            su.table = static_cast<GemvSegment*>(ptr);
+            su.ready = true;
+        }
+    }
+    if (K == 0 || M == 0 || K % 128 != 0 || T == 0 || T > (uint32_t)kDecodeMaxTokens || M > 0x7fffffffu) return SG_BAD_SHAPE;
+    const size_t smem = fused_gemv_smem(T, K, K, PRO_NONE, 0);
+    if (smem > 200 * 1024) return SG_BAD_SHAPE;
+    const int grid = num_ctas == 0 ? su.sms : (int)num_ctas;
+    if (num_ctas > (uint32_t)kStaticGemvMaxCtas || grid > kStaticGemvMaxCtas) return SG_TOO_MANY_CTAS;
+
+    FusedGemvArgs a{};
+    a.T = T;
+    a.C = K;
+    a.prologue = PRO_NONE;
+    a.epilogue = EPI_STORE;
+    a.rescale = 1.0f;
+    a.num_problems = 1;
+    a.segments = su.table;
+    GemvProblem& p = a.p[0];
+    p.w = w;
+    p.scale = minmax;
+    p.kind = MAT_INT8;
+    p.K = K;
+    p.M = M;
+    p.x = x;
+    p.x_stride = K;
+    p.out = y;
+    p.out_stride = M;
+    p.out_dtype = WRK_F32;
+    p.act = act;
+    static_partition_kernel<<<1, 32, 0, stream>>>(su.table, K, M, grid);
+    if ((*cuda_error = cudaGetLastError()) != cudaSuccess) return SG_CUDA;
+    // a plain launch: the multiply reads the table at once, so it must not start before the fill kernel ends
+    fused_gemv_kernel<<<grid, kThreads, smem, stream>>>(a);
+    if ((*cuda_error = cudaGetLastError()) != cudaSuccess) return SG_CUDA;
+    return SG_OK;
 }
 
 }  // namespace k

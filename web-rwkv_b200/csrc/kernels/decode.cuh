@@ -108,5 +108,14 @@ struct Wkv6Args {
 };
 cudaError_t wkv56_fused(const Wkv6Args& a, cudaStream_t stream);
 
+// Int8 GEMV (y[t][m] = act(W[m][:] . x[t][:]), f16 x, f32 y) whose row-range table lives in a static
+// device array of kStaticGemvMaxCtas ranges: neither the first call on a device (which looks the array up)
+// nor any later one allocates.  `device` must be the current device.  Returns a StaticGemvError.
+constexpr int kStaticGemvMaxCtas = 512;
+constexpr int kStaticGemvMaxDevices = 64;
+enum StaticGemvError { SG_OK = 0, SG_TOO_MANY_CTAS = 1, SG_BAD_SHAPE = 2, SG_BAD_DEVICE = 3, SG_CUDA = 4 };
+int gemv_int8_static(int device, cudaStream_t stream, const uint8_t* w, const __half* minmax, const __half* x, float* y,
+                     uint32_t K, uint32_t M, uint32_t T, int act, uint32_t num_ctas, cudaError_t* cuda_error);
+
 }  // namespace k
 }  // namespace wrk

@@ -671,3 +671,35 @@ int32_t wrk_matrix_matmul_op_sparse(wrk_matrix* m, const wrk_view* input, const 
 }
 
 }  // extern "C"
+
+// ---- no counterpart in the reference: Int8 GEMV that never allocates ----
+extern "C" int32_t wrk_gemv_int8_static(int32_t device, void* cuda_stream, const void* matrix, const void* minmax,
+                                        const void* x, void* y, uint32_t k, uint32_t m, uint32_t t, int32_t act,
+                                        uint32_t num_ctas) {
+    WRK_REQUIRE(matrix && minmax && x && y, WRK_ERR_INVALID_ARGUMENT, "null device pointer");
+    WRK_REQUIRE((reinterpret_cast<uintptr_t>(matrix) | reinterpret_cast<uintptr_t>(x)) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(minmax) % 4 == 0 && reinterpret_cast<uintptr_t>(y) % 4 == 0,
+                WRK_ERR_INVALID_ARGUMENT, "matrix and x must be 16-byte aligned, minmax and y 4-byte aligned");
+    WRK_REQUIRE(act >= 0 && act <= 7, WRK_ERR_INVALID_ARGUMENT, "unknown activation %d", act);
+    cudaError_t ce = cudaSuccess;
+    const int r = wrk::k::gemv_int8_static(device, static_cast<cudaStream_t>(cuda_stream), static_cast<const uint8_t*>(matrix),
+                                           static_cast<const __half*>(minmax), static_cast<const __half*>(x),
+                                           static_cast<float*>(y), k, m, t, act, num_ctas, &ce);
+    switch (r) {
+        case wrk::k::SG_OK: return WRK_OK;
+        case wrk::k::SG_TOO_MANY_CTAS:
+            return wrk::set_error(WRK_ERR_SIZE,
+                                  "the static row-range table holds %d CTAs; %u requested (0 = one per SM of the device)",
+                                  wrk::k::kStaticGemvMaxCtas, num_ctas);
+        case wrk::k::SG_BAD_SHAPE:
+            return wrk::set_error(WRK_ERR_SHAPE,
+                                  "unsupported size k = %u, m = %u, t = %u: k must be a non-zero multiple of 128 whose "
+                                  "staged activations fit in shared memory, m >= 1, 1 <= t <= %d",
+                                  k, m, t, wrk::k::kDecodeMaxTokens);
+        case wrk::k::SG_BAD_DEVICE:
+            return wrk::set_error(WRK_ERR_INVALID_ARGUMENT, "device %d must be the current CUDA device (and below %d)", device,
+                                  wrk::k::kStaticGemvMaxDevices);
+        default:
+            return wrk::set_error(WRK_ERR_CUDA, "static Int8 GEMV failed: %s", cudaGetErrorString(ce));
+    }
+}
