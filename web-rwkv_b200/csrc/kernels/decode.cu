@@ -33,7 +33,7 @@ namespace {
 
 constexpr int kThreads = 512;
 constexpr int kWarps = 16;
-constexpr int GROUP_ROWS = 64;    // rows accumulated in registers at a time (4 MMA row tiles)
+constexpr int GROUP_ROWS = 64;  // rows (4 MMA row tiles) whose partial results meet in shared memory at once
 
 // floats reserved for the per-block activation sums (keeps what follows 16-byte aligned)
 __host__ __device__ inline uint32_t sums_floats(uint32_t T, uint32_t kmax) {
@@ -51,13 +51,13 @@ __device__ __forceinline__ void trace(int stage) {
     if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        if (stage == 100) s_trace_n = 0;
+        if (stage % 20 == 0) s_trace_n = 0;
         if (s_trace_n < 64) {
             s_trace[2 * s_trace_n] = (unsigned long long)stage;
             s_trace[2 * s_trace_n + 1] = t;
             ++s_trace_n;
         }
-        if (stage == 107) {
+        if (stage % 20 == 7) {
             const unsigned int base = atomicAdd(&g_trace_n, s_trace_n);
             for (unsigned int i = 0; i < s_trace_n && base + i < (1u << 15); ++i) {
                 g_trace[2 * (base + i)] = s_trace[2 * i];
@@ -94,7 +94,7 @@ constexpr int CHUNK_BYTES = 128;
 // One work item in registers: this lane's pieces of rows g and g + 8 and their block scales.
 struct Item {
     uint4 q[4];     // Int8 / fp16: rowA lo, rowA hi, rowB lo, rowB hi; NF4: blocks (0,1) A, (2,3) A, (0,1) B, (2,3) B
-    uint32_t s[4];  // Int8: s[0] = (min, max) of rowA as half2, s[1] = rowB; NF4: absmax pairs A01, A23, B01, B23
+    uint32_t s[4];  // Int8: s[0] = (min, max) of rowA as half2, s[2] = rowB; NF4: absmax pairs A01, A23, B01, B23
 };
 
 // The CTA's row ranges, kept in registers.
@@ -106,11 +106,13 @@ struct Segs {
 };
 
 // ---- per-warp staging ring --------------------------------------------------------------------
-// Each warp streams its own work items through a private ring in shared memory with cp.async: a lane
-// copies exactly the pieces it will later feed to the MMA into its own 16-byte cells, so reading them back
-// needs no barrier (a thread sees its own completed cp.async data after wait_group) and is conflict free.
-constexpr int kRing = 2;                          // items in flight per warp
-constexpr int ITEM_BYTES = 32 * (4 * 16 + 4 * 4);  // per lane: four 16-byte pieces + four scale words
+// Each warp streams its own work items through a private ring of cells in shared memory with cp.async.  A
+// lane copies exactly the 16-byte pieces it will later feed to the MMA into its own slots, so reading them
+// back is conflict free; the block scales of the item's 16 rows are copied once per row (by the lanes
+// t4 = 0 / 2 for Int8, all four for NF4) and read after a warp barrier.
+constexpr int kMinRing = 2, kMaxRing = 4;          // items in flight per warp (chosen per launch)
+constexpr int CELL_DATA = 32 * 4 * 16;             // per lane: four 16-byte pieces
+constexpr int CELL_BYTES = CELL_DATA + 16 * 8;     // + 8 bytes of block scales per row
 
 __device__ __forceinline__ void cp_async16z(void* dst, const void* src, bool valid) {
     const uint32_t n = valid ? 16u : 0u;  // src-size 0: the cell is zero-filled, nothing is read
@@ -127,133 +129,101 @@ __device__ __forceinline__ void cp_async4z(void* dst, const void* src, bool vali
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
-
-// How the 16 warps share a group of <= 64 rows (nt = 1..4 MMA row tiles of nchunk chunks each): warp w owns
-// row tile w % nt and every kways-th chunk of it starting at chunk w / nt, kways = 16 / nt.  A warp keeps the
-// partial results of its tile in registers for the whole group, so the per-item work is loads + MMAs only.
-struct GroupMap {
-    int tile, ks, kways, cnt;  // cnt = items of this warp in the group
-};
-__device__ __forceinline__ GroupMap map_group(int nrows, int nchunk, int warp) {
-    GroupMap m;
-    const int nt = (nrows + 15) >> 4;
-    if (nt <= 1) {
-        m.tile = 0, m.ks = warp, m.kways = 16;
-    } else if (nt == 2) {
-        m.tile = warp & 1, m.ks = warp >> 1, m.kways = 8;
-    } else if (nt == 3) {
-        m.tile = warp % 3, m.ks = warp / 3, m.kways = 5;
-    } else {
-        m.tile = warp & 3, m.ks = warp >> 2, m.kways = 4;
-    }
-    const int left = nchunk - m.ks;
-    m.cnt = (m.ks < m.kways && left > 0) ? (left + m.kways - 1) / m.kways : 0;
-    return m;
+// all but the newest n groups of this thread have landed (n = 1 .. kMaxRing)
+__device__ __forceinline__ void cp_async_wait_dyn(int n) {
+    if (n <= 1) cp_async_wait<1>();
+    else if (n == 2) cp_async_wait<2>();
+    else if (n == 3) cp_async_wait<3>();
+    else cp_async_wait<4>();
 }
 
-// The copy side of a warp: walks the same (segment, group, item) sequence as the compute side, kRing items
-// ahead, with the addresses of the current group kept as row pointer + running byte offset.
+// Work mapping inside a CTA: its row ranges are walked in MMA row tiles of 16 rows; the 16 warps split a
+// tile's chunks (warp w takes chunks w, w + 16, ...), keep their partial results in registers, and meet in
+// shared memory once per tile.  The copy side of a warp walks the same (range, tile, chunk) sequence as its
+// compute side, `depth` items ahead.  Tiles are taken in groups of four: one barrier and one pass of sums
+// and epilogues per 64 rows.
 struct Loader {
-    int seg, group0;     // current group; seg == kSegmentsPerCta when the CTA's work is exhausted
-    int left;            // items of this warp not yet issued in the group
-    uint32_t off, step;  // byte offset of the next chunk within a row; kways * CHUNK_BYTES
-    uint32_t rb, rb8;    // row bytes; distance from row g to row g + 8 (0 when that row does not exist)
-    uint32_t sb8;        // same distance in the scale table
+    int seg, row0, r1, c, nchunk;  // seg == kSegmentsPerCta: the CTA's work is exhausted
     int kind;
-    bool vA, vB;
-    const uint8_t* pa;  // row g of the warp's tile + this lane's byte offset
-    const uint8_t* sa;  // row g's block scales
+    uint32_t rb, srow;             // bytes per weight row / per row of the scale table
+    const uint8_t* wbase;          // matrix + this lane's byte offset inside a chunk
+    const uint8_t* sbase;          // scale table
 
     __device__ __forceinline__ bool valid() const { return seg < kSegmentsPerCta; }
 
-    __device__ __forceinline__ void enter_group(const FusedGemvArgs& a, const Segs& sg, int warp, int lane) {
-        const GemvProblem& p = a.p[sg.P(seg)];
-        rb = row_bytes(p);
-        kind = p.kind;
-        const int gend = min(group0 + GROUP_ROWS, sg.R1(seg));
-        const GroupMap m = map_group(gend - group0, (int)((rb + CHUNK_BYTES - 1) / CHUNK_BYTES), warp);
-        left = m.cnt;
-        off = (uint32_t)m.ks * CHUNK_BYTES;
-        step = (uint32_t)m.kways * CHUNK_BYTES;
-        const int g = lane >> 2, t4 = lane & 3;
-        const int rowA = group0 + 16 * m.tile + g;
-        vA = rowA < gend;
-        vB = rowA + 8 < gend;
-        const size_t ra = (size_t)(vA ? rowA : group0);
-        pa = p.w + ra * rb + (kind == MAT_NF4 ? 8 : 16) * t4;
-        rb8 = vB ? 8u * rb : 0u;
-        const uint32_t srow = kind == MAT_INT8 ? (p.K / 128) * 4 : kind == MAT_NF4 ? (p.K / 64) * 2 : 0;  // scale bytes per row
-        sa = reinterpret_cast<const uint8_t*>(p.scale) + ra * srow;
-        sb8 = vB ? 8u * srow : 0u;
-    }
-    __device__ __forceinline__ void settle(const FusedGemvArgs& a, const Segs& sg, int warp, int lane) {
-        while (valid() && left <= 0) {
-            group0 += GROUP_ROWS;
-            if (group0 >= sg.R1(seg)) {
-                ++seg;
-                while (seg < kSegmentsPerCta && sg.R0(seg) >= sg.R1(seg)) ++seg;
-                if (seg >= kSegmentsPerCta) return;
-                group0 = sg.R0(seg);
-            }
-            enter_group(a, sg, warp, lane);
+    // first range at or after `seg` in which this warp has chunks
+    __device__ __forceinline__ void enter(const FusedGemvArgs& a, const Segs& sg, int warp, int lane) {
+        for (; seg < kSegmentsPerCta; ++seg) {
+            if (sg.R0(seg) >= sg.R1(seg)) continue;
+            const GemvProblem& p = a.p[sg.P(seg)];
+            rb = row_bytes(p);
+            nchunk = (int)((rb + CHUNK_BYTES - 1) / CHUNK_BYTES);
+            if (warp >= nchunk) continue;
+            kind = p.kind;
+            srow = kind == MAT_INT8 ? (p.K / 128) * 4 : kind == MAT_NF4 ? (p.K / 64) * 2 : 0;
+            wbase = p.w + (kind == MAT_NF4 ? 8 : 16) * (lane & 3);
+            sbase = reinterpret_cast<const uint8_t*>(p.scale);
+            row0 = sg.R0(seg);
+            r1 = sg.R1(seg);
+            c = warp;
+            return;
         }
     }
-    __device__ __forceinline__ void start(const FusedGemvArgs& a, const Segs& sg, int warp, int lane) {
-        seg = 0;
-        left = 0;
-        while (seg < kSegmentsPerCta && sg.R0(seg) >= sg.R1(seg)) ++seg;
-        if (!valid()) return;
-        group0 = sg.R0(seg);
-        enter_group(a, sg, warp, lane);
-        settle(a, sg, warp, lane);
-    }
-    // Issues the copies of the current item into ring cell `cell` (nothing when exhausted) and steps on.
+    // Issues the copies of the current item into `cell` (nothing when exhausted) and steps to the next one.
     __device__ __forceinline__ void issue(const FusedGemvArgs& a, const Segs& sg, uint8_t* cell, int warp, int lane) {
         if (!valid()) return;
-        const uint8_t* A = pa + off;
-        const uint8_t* B = A + rb8;
-        uint8_t* wq = cell + lane * 16;           // piece i at wq + i * 512
-        uint8_t* ws = cell + 4 * 512 + lane * 4;  // scale word i at ws + i * 128
+        const int g = lane >> 2, t4 = lane & 3;
+        const bool vA = row0 + g < r1, vB = row0 + g + 8 < r1;
+        const uint32_t off = (uint32_t)c * CHUNK_BYTES;
+        const uint8_t* A = wbase + (size_t)(vA ? row0 + g : row0) * rb + off;
+        const uint8_t* B = vB ? A + 8 * (size_t)rb : A;
+        uint8_t* wq = cell + lane * 16;  // piece i at wq + i * 512
+        const int sr = g + 8 * (t4 >> 1), sh = t4 & 1;  // scale row / half copied by this lane
+        const bool vS = row0 + sr < r1;
+        const uint8_t* S = sbase + (size_t)(vS ? row0 + sr : row0) * srow;
+        uint8_t* ws = cell + CELL_DATA + sr * 8 + sh * 4;
         if (kind == MAT_NF4) {
-            // four 64-weight blocks of 32 bytes, 8 bytes of each per lane: cells hold (blk0, blk1), (blk2, blk3)
+            // four 64-weight blocks of 32 bytes, 8 bytes of each per lane: slots hold (blk0, blk1), (blk2, blk3)
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const bool in = off + 32 * j < rb;
                 cp_async8z(wq + (j >> 1) * 512 + (j & 1) * 8, A + 32 * j, in && vA);
                 cp_async8z(wq + (2 + (j >> 1)) * 512 + (j & 1) * 8, B + 32 * j, in && vB);
             }
-            // absmax pairs (blocks 0-1, 2-3) of both rows; K is a multiple of 128 here, so pairs are 4-byte aligned
-            const uint8_t* SA = sa + (off >> 4);
-            const uint8_t* SB = SA + sb8;
-            cp_async4z(ws, SA, vA && off < rb);
-            cp_async4z(ws + 128, SA + 4, vA && off + 64 < rb);
-            cp_async4z(ws + 256, SB, vB && off < rb);
-            cp_async4z(ws + 384, SB + 4, vB && off + 64 < rb);
+            // absmax of blocks (0, 1) or (2, 3): K is a multiple of 128, so the pairs are 4-byte aligned
+            cp_async4z(ws, S + (off >> 4) + sh * 4, vS && off + 64 * sh < rb);
         } else {
             const bool hi = off + 64 < rb;  // fp16 rows may end after the first 64 bytes of the chunk
             cp_async16z(wq, A, vA);
             cp_async16z(wq + 512, A + 64, vA && hi);
             cp_async16z(wq + 1024, B, vB);
             cp_async16z(wq + 1536, B + 64, vB && hi);
-            if (kind == MAT_INT8) {
-                const uint8_t* SA = sa + (off >> 5);
-                cp_async4z(ws, SA, vA);
-                cp_async4z(ws + 128, SA + sb8, vB);
+            if (kind == MAT_INT8 && sh == 0) cp_async4z(ws, S + (off >> 5), vS);
+        }
+        c += kWarps;
+        if (c >= nchunk) {
+            c = warp;
+            row0 += 16;
+            if (row0 >= r1) {
+                ++seg;
+                enter(a, sg, warp, lane);
             }
         }
-        off += step;
-        --left;
-        settle(a, sg, warp, lane);
     }
 };
 
+// This lane's registers of the item in `cell` (after its copies have landed and the warp has synchronised).
 __device__ __forceinline__ Item read_item(const uint8_t* cell, int lane) {
     Item it;
+    const int g = lane >> 2;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        it.q[i] = *reinterpret_cast<const uint4*>(cell + i * 512 + lane * 16);
-        it.s[i] = *reinterpret_cast<const uint32_t*>(cell + 4 * 512 + i * 128 + lane * 4);
-    }
+    for (int i = 0; i < 4; ++i) it.q[i] = *reinterpret_cast<const uint4*>(cell + i * 512 + lane * 16);
+    const uint2 sa = *reinterpret_cast<const uint2*>(cell + CELL_DATA + g * 8);
+    const uint2 sb = *reinterpret_cast<const uint2*>(cell + CELL_DATA + (g + 8) * 8);
+    it.s[0] = sa.x;  // Int8: (min, max) of row g; NF4: absmax of blocks 0, 1
+    it.s[1] = sa.y;  //                            NF4: absmax of blocks 2, 3
+    it.s[2] = sb.x;  // same for row g + 8
+    it.s[3] = sb.y;
     return it;
 }
 
@@ -275,10 +245,11 @@ __device__ __forceinline__ float block_sum_256(float v, float* scratch) {
 // row 0 of each xgen region.  Rows are produced last token first, so every parameter row is consumed by its
 // owner thread before that thread overwrites it with row 0's result.
 constexpr int kLnVec = 2;  // groups of 8 channels per thread: C <= 8192
+template <int PRO>
 __device__ __forceinline__ void stage_prologue_params(const FusedGemvArgs& a, __half* xgen, uint32_t xp, __half* lnrow,
                                                       __half* pbias) {
     const uint32_t ngrp = a.C / 8;
-    const int nv = a.prologue == PRO_LN ? 0 : a.prologue == PRO_LN_SHIFT2 ? 2 : 1;
+    constexpr int nv = PRO == PRO_LN ? 0 : PRO == PRO_LN_SHIFT2 ? 2 : 1;
 #pragma unroll
     for (int q = 0; q < kLnVec; ++q) {
         const uint32_t gi = threadIdx.x + q * kThreads;
@@ -291,11 +262,12 @@ __device__ __forceinline__ void stage_prologue_params(const FusedGemvArgs& a, __
     }
 }
 
+template <int PRO>
 __device__ void run_prologue(const FusedGemvArgs& a, __half* xgen, uint32_t xp, __half* lnrow, const __half* pbias,
                              float* scratch) {
     const uint32_t C = a.C, T = a.T;
     const uint32_t ngrp = C / 8;  // 16-byte groups per row
-    const bool shift = a.prologue != PRO_LN;
+    constexpr bool shift = PRO != PRO_LN;
     // decode (T == 1): the carry row of the token shift goes in flight together with the input row
     const bool early = shift && T == 1;
     float prev1[kLnVec][8];
@@ -359,7 +331,7 @@ __device__ void run_prologue(const FusedGemvArgs& a, __half* xgen, uint32_t xp, 
         }
     }
     if (shift) {
-        const int nv = a.prologue == PRO_LN_SHIFT2 ? 2 : 1;
+        constexpr int nv = PRO == PRO_LN_SHIFT2 ? 2 : 1;
         for (int t = (int)T - 1; t >= 0; --t) {
             const CursorD cu = early ? cu0 : cursor_at(a.cursors, a.wide, (uint32_t)t);
 #pragma unroll
@@ -408,14 +380,15 @@ struct EpiOperands {
     float xres, r, cmx;
     CursorD cu;
 };
+template <int EPI>
 __device__ __forceinline__ EpiOperands epilogue_fetch(const FusedGemvArgs& a, const GemvProblem& p, uint32_t m, int tok) {
     EpiOperands e;
     e.xres = e.r = e.cmx = 0.f;
     e.cu = CursorD{0, 0, 1};
-    if (a.epilogue == EPI_STORE) return e;
+    if (EPI == EPI_STORE) return e;
     const size_t oi = (size_t)tok * p.M + m;
     e.xres = __half2float(a.xres[oi]);
-    if (a.epilogue == EPI_CHANNEL_MIX) {
+    if (EPI == EPI_CHANNEL_MIX) {
         e.cu = cursor_at(a.cursors, a.wide, tok);
         e.cmx = __half2float(a.cm_x[oi]);
         if (a.cm_r != nullptr) e.r = __half2float(a.cm_r[oi]);
@@ -424,13 +397,14 @@ __device__ __forceinline__ EpiOperands epilogue_fetch(const FusedGemvArgs& a, co
 }
 
 // Activation + the launch's epilogue for output (token tok, row m) of problem p.
+template <int EPI>
 __device__ __forceinline__ void epilogue_one(const FusedGemvArgs& a, const GemvProblem& p, uint32_t m, int tok, float s,
                                              const EpiOperands& e) {
     s = activate_f(p.act, s);
     const size_t oi = (size_t)tok * p.M + m;
-    if (a.epilogue == EPI_STORE) {
+    if (EPI == EPI_STORE) {
         dstore(p.out, p.out_dtype, (size_t)tok * p.out_stride + m, s);
-    } else if (a.epilogue == EPI_RESIDUAL) {
+    } else if (EPI == EPI_RESIDUAL) {
         // att_o is an fp16 tensor in the reference; x += att_o is rounded to fp16 again
         const float o16 = __half2float(__float2half_rn(s));
         a.xres[oi] = __float2half_rn(a.rescale * __half2float(__float2half_rn(e.xres + o16)));
@@ -476,7 +450,7 @@ __device__ __forceinline__ void consume_item(const GemvProblem& p, const Item& i
             }
         }
         const float2 mmA = __half22float2(*reinterpret_cast<const __half2*>(&it.s[0]));
-        const float2 mmB = __half22float2(*reinterpret_cast<const __half2*>(&it.s[1]));
+        const float2 mmB = __half22float2(*reinterpret_cast<const __half2*>(&it.s[2]));
         const uint32_t nblk = p.K / 128;
         const uint32_t tk0 = 2 * t4, tk1 = tk0 + 1;
         const float s0 = tk0 < T ? sums[tk0 * nblk + c] : 0.f, s1 = tk1 < T ? sums[tk1 * nblk + c] : 0.f;
@@ -537,32 +511,35 @@ __device__ __forceinline__ void consume_item(const GemvProblem& p, const Item& i
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemvArgs a) {
+#ifndef WRK_GEMV_MIN_CTAS
+#define WRK_GEMV_MIN_CTAS 2
+#endif
+template <int PRO, int EPI>
+__global__ void __launch_bounds__(kThreads, WRK_GEMV_MIN_CTAS) fused_gemv_kernel(const FusedGemvArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float scratch[kWarps];
     __shared__ __half lut[16];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
     const uint32_t T = a.T;
+    const int depth = a.ring_depth;
 
     // shared memory carve-up (all offsets multiples of 16 bytes)
-    uint32_t kmax = 0;
-    for (int i = 0; i < a.num_problems; ++i) kmax = max(kmax, a.p[i].K);
-    const uint32_t xp = (a.prologue != PRO_NONE ? a.C : kmax) + 8;      // halfs per activation row
-    uint8_t* ring = smem + (size_t)warp * kRing * ITEM_BYTES;            // this warp's staging cells
-    float* red = reinterpret_cast<float*>(smem + (size_t)kWarps * kRing * ITEM_BYTES);  // [GROUP_ROWS][T] accumulator
-    float* sums = red + (size_t)GROUP_ROWS * kDecodeMaxTokens;           // [T][kmax / 128]
-    __half* xs = reinterpret_cast<__half*>(sums + sums_floats(T, kmax)); // staged x or prologue rows
+    const uint32_t xp = (PRO != PRO_NONE ? a.C : a.kmax) + 8;            // halfs per activation row
+    uint8_t* ring = smem + (size_t)warp * depth * CELL_BYTES;            // this warp's staging cells
+    float* part = reinterpret_cast<float*>(smem + (size_t)kWarps * depth * CELL_BYTES);  // [kWarps][GROUP_ROWS * T] partial results
+    float* sums = part + kWarps * GROUP_ROWS * T;                        // [T][kmax / 128]
+    __half* xs = reinterpret_cast<__half*>(sums + sums_floats(T, a.kmax));  // staged x or prologue rows
     __half* lnrow = xs;                                                  // PRO_LN: vectors = normalised rows
-    __half* xgen = a.prologue == PRO_LN ? xs : xs + (size_t)T * xp;      // shifted vectors follow the rows
-    const uint32_t pro_rows = a.prologue == PRO_LN ? T : a.prologue == PRO_LN_SHIFT1 ? 2 * T : 3 * T;
+    __half* xgen = PRO == PRO_LN ? xs : xs + (size_t)T * xp;             // shifted vectors follow the rows
+    const uint32_t pro_rows = PRO == PRO_LN ? T : PRO == PRO_LN_SHIFT1 ? 2 * T : 3 * T;
     __half* pbias = xs + (size_t)pro_rows * xp;                          // layer-norm bias (prologues only)
 
     if (threadIdx.x < 16 && a.table != nullptr) lut[threadIdx.x] = __float2half_rn(a.table[threadIdx.x]);
     trace(100);
     pdl_launch_dependents();
 
-    // ---- everything up to the wait touches only weights: each warp fetches its first item ----
+    // ---- everything up to the wait touches only weights: each warp fetches its first items ----
     Segs sg;
     {
         const int4* tab = reinterpret_cast<const int4*>(a.segments + (size_t)blockIdx.x * kSegmentsPerCta);
@@ -574,51 +551,54 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
             sg.r1[i] = e.z;
         }
     }
-    int first_seg = 0;
-    while (first_seg < kSegmentsPerCta && sg.R0(first_seg) >= sg.R1(first_seg)) ++first_seg;
-    const bool any_work = first_seg < kSegmentsPerCta;
-    const bool pro = a.prologue != PRO_NONE && (any_work || blockIdx.x == 0);
-    if (pro) stage_prologue_params(a, xgen, xp, lnrow, pbias);
-    cp_async_commit();
+    const bool any_work = sg.r0[0] < sg.r1[0] || sg.r0[1] < sg.r1[1] || sg.r0[2] < sg.r1[2];
+    const bool pro = PRO != PRO_NONE && (any_work || blockIdx.x == 0);
+    if (PRO != PRO_NONE) {
+        if (pro) stage_prologue_params<PRO>(a, xgen, xp, lnrow, pbias);
+        cp_async_commit();
+    }
     Loader ld;
-    ld.start(a, sg, warp, lane);
-    uint32_t consumed = 0;
+    ld.seg = 0;
+    ld.enter(a, sg, warp, lane);
+    int cs_slot = 0;
 #ifdef WRK_TRACE
-    long long clk_acc[4] = {0, 0, 0, 0}, clk_t[4] = {0, 0, 0, 0};
-#define WRK_CLK(i)                                                            \
-    do {                                                                      \
-        asm volatile("mov.u64 %0, %%clock64;" : "=l"(clk_t[i])::"memory");     \
-        if (i > 0) clk_acc[i] += clk_t[i] - clk_t[i - 1];                     \
-        else clk_acc[0] += 1;                                                 \
+    // cycle accounting of warps 0 and 7 of CTA 0: clk_acc[i] = cycles between stamps i - 1 and i
+    long long clk_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}, clk_last = 0;
+#define WRK_CLK(i)                                                             \
+    do {                                                                       \
+        long long now_;                                                        \
+        asm volatile("mov.u64 %0, %%clock64;" : "=l"(now_)::"memory");          \
+        if (i == 0) clk_acc[0] += 1;                                           \
+        else clk_acc[i] += now_ - clk_last;                                    \
+        clk_last = now_;                                                       \
     } while (0)
 #else
 #define WRK_CLK(i)
 #endif
-#pragma unroll
-    for (int d = 0; d < kRing; ++d) {
-        ld.issue(a, sg, ring + d * ITEM_BYTES, warp, lane);
+#pragma unroll 1
+    for (int d = 0; d < depth; ++d) {
+        ld.issue(a, sg, ring + d * CELL_BYTES, warp, lane);
         cp_async_commit();  // one group per cell, empty or not
     }
     trace(101);
     pdl_wait();
     trace(102);
 
-    if (pro) {
-        cp_async_wait<kRing>();  // this thread's parameter copies (it is their only reader)
-        run_prologue(a, xgen, xp, lnrow, pbias, scratch);
+    if (PRO != PRO_NONE && pro) {
+        cp_async_wait_dyn(depth);  // this thread's parameter copies (it is their only reader)
+        run_prologue<PRO>(a, xgen, xp, lnrow, pbias, scratch);
     }
     trace(103);
 
     int staged_problem = -1;
-    for (int seg = first_seg; seg < kSegmentsPerCta; ++seg) {
+    const int last_seg = sg.r0[2] < sg.r1[2] ? 2 : sg.r0[1] < sg.r1[1] ? 1 : 0;
+#pragma unroll 1
+    for (int seg = 0; seg < kSegmentsPerCta; ++seg) {
         const int r0 = sg.R0(seg), r1 = sg.R1(seg);
         if (r0 >= r1) continue;
         const int problem = sg.P(seg);
         const GemvProblem& p = a.p[problem];
         const __half* xv = p.x == nullptr ? xgen + (size_t)p.x_sel * T * xp : xs;
-#ifdef WRK_TRACE
-        if (a.debug & 1) staged_problem = problem;
-#endif
         if (staged_problem != problem) {
             // stage x (explicit inputs) and the per-128-block sums of the values the MMA will see:
             // 16 consecutive lanes cover one block of 128, so the sums come from the registers in flight
@@ -631,7 +611,7 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
                     uint32_t tok = 0, k8 = 0;
                     if (i < total) {
                         tok = i / groups;
-                        k8 = i % groups;
+                        k8 = i - tok * groups;
                         const uint4 raw = *reinterpret_cast<const uint4*>(p.x + (size_t)tok * p.x_stride + k8 * 8);
                         *reinterpret_cast<uint4*>(xs + (size_t)tok * xp + k8 * 8) = raw;
                         const __half2* h = reinterpret_cast<const __half2*>(&raw);
@@ -650,7 +630,7 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
             } else if (p.kind == MAT_INT8) {
                 const uint32_t nblk = p.K / 128;
                 for (uint32_t u = warp; u < T * nblk; u += kWarps) {
-                    const uint32_t tok = u / nblk, blk = u % nblk;
+                    const uint32_t tok = u / nblk, blk = u - tok * nblk;
                     const uint2 raw = *reinterpret_cast<const uint2*>(xv + (size_t)tok * xp + blk * 128 + lane * 4);
                     const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
                     const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
@@ -658,73 +638,83 @@ __global__ void __launch_bounds__(kThreads, 2) fused_gemv_kernel(const FusedGemv
                     if (lane == 0) sums[tok * nblk + blk] = s;
                 }
             }
+            __syncthreads();
+            trace(110);
             staged_problem = problem;
         }
         const bool xval = (uint32_t)g < T;
         const __half* xrow = xv + (size_t)(xval ? g : 0) * xp;
-        const int nchunk = (row_bytes(p) + CHUNK_BYTES - 1) / CHUNK_BYTES;
+        const int nchunk = (int)((row_bytes(p) + CHUNK_BYTES - 1) / CHUNK_BYTES);
+        trace(104);
 
+#pragma unroll 1
         for (int group0 = r0; group0 < r1; group0 += GROUP_ROWS) {
-            const int gend = min(group0 + GROUP_ROWS, r1);
-            const int nrows = gend - group0;
-            // nrows * T <= kThreads: one output per thread
+            const int gn = min(GROUP_ROWS, r1 - group0);
+            // the group's outputs belong to the first gn * T threads; their epilogue operands go in flight now
             const int orow = (int)threadIdx.x / (int)T, otok = (int)threadIdx.x - orow * (int)T;
-            const bool has_out = (int)threadIdx.x < nrows * (int)T;
+            const bool has_out = (int)threadIdx.x < gn * (int)T;
             EpiOperands eo;
-            if (has_out) {
-                red[threadIdx.x] = 0.f;
-                eo = epilogue_fetch(a, p, (uint32_t)(group0 + orow), otok);
-            }
-            __syncthreads();  // accumulator cleared, staged x and sums visible
-            trace(104);
-            // each warp walks its chunks of its row tile, keeping the tile's partial results in registers
-            const GroupMap gm = map_group(nrows, nchunk, warp);
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            int c = gm.ks;
-            for (int i = 0; i < gm.cnt; ++i, c += gm.kways) {
-#ifdef WRK_TRACE
-                if (a.debug & 2) break;
-#endif
-                WRK_CLK(0);
-                cp_async_wait<kRing - 1>();  // this lane's copies of the oldest item in flight have landed
-                WRK_CLK(1);
-                uint8_t* cell = ring + (consumed % kRing) * ITEM_BYTES;
-                const Item it = read_item(cell, lane);
-                // refill the cell with the item kRing steps ahead (the reads above are complete: `it` is in registers)
-                ld.issue(a, sg, cell, warp, lane);
-                cp_async_commit();
-                ++consumed;
-                WRK_CLK(2);
-                float out[4];
-                consume_item(p, it, c, xrow, xval, sums, T, t4, lut, out);
+            if (has_out) eo = epilogue_fetch<EPI>(a, p, (uint32_t)(group0 + orow), otok);
+
+            float* mine = part + (size_t)warp * GROUP_ROWS * T;
+#pragma unroll 1
+            for (int row0 = group0; row0 < group0 + gn; row0 += 16) {
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+                for (int c = warp; c < nchunk; c += kWarps) {
+                    WRK_CLK(0);
+                    cp_async_wait_dyn(depth - 1);  // this lane's copies of the oldest item in flight have landed
+                    __syncwarp();                  // ... and so have the other lanes' (the rows' block scales)
+                    WRK_CLK(1);
+                    uint8_t* cell = ring + cs_slot * CELL_BYTES;
+                    const Item it = read_item(cell, lane);
+                    __syncwarp();  // every lane has read the cell: refill it with the item `depth` steps ahead
+                    WRK_CLK(2);
+                    ld.issue(a, sg, cell, warp, lane);
+                    cp_async_commit();
+                    if (++cs_slot == depth) cs_slot = 0;
+                    WRK_CLK(3);
+                    float out[4];
+                    consume_item(p, it, c, xrow, xval, sums, T, t4, lut, out);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) acc[e] += out[e];
-                WRK_CLK(3);
-            }
-            if (gm.cnt > 0) {
-                const int rA = 16 * gm.tile + g, rB = rA + 8;
+                    for (int e = 0; e < 4; ++e) acc[e] += out[e];
+                    WRK_CLK(4);
+                }
+                // this warp's partial results of the tile's 16 rows
                 const uint32_t tk0 = 2 * t4, tk1 = tk0 + 1;
-                if (rA < nrows) {
-                    if (tk0 < T) atomicAdd(&red[rA * T + tk0], acc[0]);
-                    if (tk1 < T) atomicAdd(&red[rA * T + tk1], acc[1]);
+                float* dst = mine + (size_t)(row0 - group0) * T;
+                if (tk0 < T) {
+                    dst[g * T + tk0] = acc[0];
+                    dst[(g + 8) * T + tk0] = acc[2];
                 }
-                if (rB < nrows) {
-                    if (tk0 < T) atomicAdd(&red[rB * T + tk0], acc[2]);
-                    if (tk1 < T) atomicAdd(&red[rB * T + tk1], acc[3]);
+                if (tk1 < T) {
+                    dst[g * T + tk1] = acc[1];
+                    dst[(g + 8) * T + tk1] = acc[3];
                 }
             }
-            trace(105);
+            WRK_CLK(5);
+            trace(108);
             __syncthreads();
-            if (has_out) epilogue_one(a, p, (uint32_t)(group0 + orow), otok, red[threadIdx.x], eo);
-            __syncthreads();  // the accumulator is free again
-            trace(106);
+            trace(109);
+            WRK_CLK(6);
+            // the 16 warps' partial results are summed in warp order (deterministic)
+            if (has_out) {
+                const float* src = part + threadIdx.x;
+                float s = 0.f;
+#pragma unroll
+                for (int w = 0; w < kWarps; ++w) s += src[(size_t)w * GROUP_ROWS * T];
+                epilogue_one<EPI>(a, p, (uint32_t)(group0 + orow), otok, s, eo);
+            }
+            if (group0 + GROUP_ROWS < r1 || seg < last_seg) __syncthreads();  // the slabs are written again
+            WRK_CLK(7);
         }
+        trace(105);
     }
 #ifdef WRK_TRACE
     if (blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 7)) {
-        const unsigned int base = atomicAdd(&g_trace_n, 4u);
-        for (int k2 = 0; k2 < 4; ++k2) {
-            g_trace[2 * (base + k2)] = 200 + warp * 4 + k2;
+        const unsigned int base = atomicAdd(&g_trace_n, 8u);
+        for (int k2 = 0; k2 < 8; ++k2) {
+            g_trace[2 * (base + k2)] = 200 + warp * 8 + k2;
             g_trace[2 * (base + k2) + 1] = (unsigned long long)clk_acc[k2];
         }
     }
@@ -750,6 +740,7 @@ namespace {
 // sx[i][t][c] = mix(att_x[t][c], prev[t][c], f16(f16(W2[i][c][:] . tmx[t][i*D:(i+1)*D]) + mix[i][c]))
 __global__ void __launch_bounds__(256) tmix_shift_kernel(const TmixArgs a) {
     extern __shared__ __half s_tmx[];  // [T][5 * D]
+    trace(120);
     pdl_launch_dependents();
     const uint32_t C = a.C, D = a.D, T = a.T;
     // the adapter weights of this thread do not depend on earlier kernels
@@ -765,13 +756,16 @@ __global__ void __launch_bounds__(256) tmix_shift_kernel(const TmixArgs a) {
             if (j < D / 8) wreg[j] = wp[j];
         mu = __half2float(a.mix[(size_t)i * C + c]);
     }
+    trace(121);
     pdl_wait();
+    trace(122);
     // every input of token 0 goes in flight before the first barrier: one memory round trip, not four
     for (uint32_t j = threadIdx.x; j < T * 5 * D; j += blockDim.x) s_tmx[j] = a.tmx[j];
     const CursorD cu0 = cursor_at(a.cursors, a.wide, 0);
     const float cur0 = active ? __half2float(a.att_x[c]) : 0.f;
     const float prev0 = (active && cu0.token == 0) ? static_cast<const float*>(a.state.base)[a.state.index(c, 0, cu0.batch)] : 0.f;
     __syncthreads();
+    trace(123);
     if (!active) return;
     for (uint32_t t = 0; t < T; ++t) {
         float acc = 0.f;
@@ -801,6 +795,7 @@ __global__ void __launch_bounds__(256) tmix_shift_kernel(const TmixArgs a) {
         }
         a.sx[((size_t)i * T + t) * C + c] = __float2half_rn(cur * (1.0f - f) + prev * f);
     }
+    trace(127);
 }
 
 // ---- v5 / v6 time-mix block: decay adapter, WKV, group norm, gate --------------------------------
@@ -812,6 +807,7 @@ __global__ void __launch_bounds__(4 * S) wkv56_fused_kernel(const Wkv6Args a) {
     __shared__ float sk[S], sr[S], sw[S], su[S], part[Q][S], red[Q * S / 32];
     __shared__ __half s_tdw[128];
     __shared__ uint32_t s_start, s_count;
+    trace(140);
     pdl_launch_dependents();
     const uint32_t h = blockIdx.x, slot = blockIdx.y, j = threadIdx.x % S, q = threadIdx.x / S;
     const uint32_t C = S * a.H, c = h * S + j;
@@ -831,7 +827,9 @@ __global__ void __launch_bounds__(4 * S) wkv56_fused_kernel(const Wkv6Args a) {
     }
     if (q == 0) su[j] = a.time_first[c];
     const float gw = __half2float(a.gn_w[c]), gb = __half2float(a.gn_b[c]);
+    trace(141);
     pdl_wait();  // ...the state does (the previous token's job wrote it), and so do the cursors
+    trace(142);
 
     // the state rows are needed whatever the cursors say: get their loads in flight first
     float st[SI];
@@ -877,6 +875,7 @@ __global__ void __launch_bounds__(4 * S) wkv56_fused_kernel(const Wkv6Args a) {
         if (a.per_token_decay && threadIdx.x < a.D) tdh = a.tdw[(size_t)t * a.D + threadIdx.x];
         const CursorD cu = cursor_at(a.cursors, a.wide, t);
         __syncthreads();  // the previous token's readers are done
+        trace(143);
         if (q == 0) {
             sk[j] = kj;
             sr[j] = rj;
@@ -913,6 +912,7 @@ __global__ void __launch_bounds__(4 * S) wkv56_fused_kernel(const Wkv6Args a) {
             kv = sk[i] * vj;     y0 += sr[i] * fmaf(su[i], kv, st[ii]);             st[ii] = fmaf(sw[i], st[ii], kv);
             kv = sk[i + 1] * vj; y1 += sr[i + 1] * fmaf(su[i + 1], kv, st[ii + 1]); st[ii + 1] = fmaf(sw[i + 1], st[ii + 1], kv);
         }
+        trace(144);
         part[q][j] = y0 + y1;
         if (q == 0 && t - cu.token + 1u == cu.len) static_cast<float*>(a.state.base)[a.state.index(c, 0, slot)] = ax;
         __syncthreads();
@@ -937,9 +937,11 @@ __global__ void __launch_bounds__(4 * S) wkv56_fused_kernel(const Wkv6Args a) {
         const float gn16 = __half2float(__float2half_rn(fmaf(dlt * dev, gw, gb)));
         const float silu = gg / (1.0f + expf(-gg));
         if (q == 0) a.out[ti] = __float2half_rn(silu * gn16);
+        trace(145);
     }
 #pragma unroll
     for (int i = 0; i < SI; ++i) static_cast<float*>(a.state.base)[a.state.index(c, 1 + q * SI + i, slot)] = st[i];
+    trace(147);
 }
 
 template <typename Kernel, typename Args>
@@ -999,9 +1001,10 @@ bool fused_gemv_partition(const FusedGemvArgs& a, int grid, std::vector<GemvSegm
     return prob == a.num_problems;
 }
 
-size_t fused_gemv_smem(uint32_t T, uint32_t Kmax, uint32_t C, int prologue, int /*num_slots*/) {
+size_t fused_gemv_smem(uint32_t T, uint32_t Kmax, uint32_t C, int prologue, int depth) {
+    depth = std::min(std::max(depth, kMinRing), kMaxRing);
     const uint32_t xp = (prologue != PRO_NONE ? C : Kmax) + 8;
-    size_t bytes = (size_t)kWarps * kRing * ITEM_BYTES + (size_t)GROUP_ROWS * kDecodeMaxTokens * sizeof(float);
+    size_t bytes = (size_t)kWarps * depth * CELL_BYTES + (size_t)kWarps * GROUP_ROWS * T * sizeof(float);
     bytes += (size_t)sums_floats(T, Kmax) * sizeof(float);
     // activation rows (+ one row of layer-norm bias for the prologues)
     const size_t rows = prologue == PRO_NONE ? T : (prologue == PRO_LN ? T : prologue == PRO_LN_SHIFT1 ? 2 * T : 3 * T) + 1;
@@ -1009,21 +1012,58 @@ size_t fused_gemv_smem(uint32_t T, uint32_t Kmax, uint32_t C, int prologue, int 
     return bytes + 64;
 }
 
-cudaError_t fused_gemv(const FusedGemvArgs& a_in, int grid, cudaStream_t stream) {
-    FusedGemvArgs a = a_in;
-#ifdef WRK_TRACE
-    if (const char* e = getenv("WRK_DEBUG_SKIP")) a.debug = atoi(e);
-#endif
+namespace {
+
+// Two CTAs fit on an SM while each stays below this (228 KB per SM, 1 KB reserved per CTA): the next launch's
+// CTAs then start fetching weights beside the running ones.
+constexpr size_t kCoResidentSmem = 113 * 1024;
+
+// Fills the launch-derived fields (largest K, ring depth) and returns the dynamic shared memory size.
+size_t fused_gemv_prepare(FusedGemvArgs& a) {
     uint32_t kmax = 0;
     for (int i = 0; i < a.num_problems; ++i) kmax = std::max(kmax, a.p[i].K);
-    const size_t smem = fused_gemv_smem(a.T, kmax, a.C, a.prologue, 0);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(fused_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    a.kmax = kmax;
+    int depth = kMaxRing;
+    while (depth > kMinRing && fused_gemv_smem(a.T, kmax, a.C, a.prologue, depth) > kCoResidentSmem) --depth;
+    a.ring_depth = depth;
+    return fused_gemv_smem(a.T, kmax, a.C, a.prologue, depth);
+}
+
+template <int PRO, int EPI>
+cudaError_t launch_fused_gemv(const FusedGemvArgs& a, int grid, size_t smem, cudaStream_t stream, bool pdl) {
+    static bool configured[kStaticGemvMaxDevices] = {};
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (device < kStaticGemvMaxDevices && !configured[device]) {
+        e = cudaFuncSetAttribute(fused_gemv_kernel<PRO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured[device] = true;
     }
-    return launch_pdl(fused_gemv_kernel, dim3(grid), dim3(kThreads), smem, stream, a);
+    if (pdl) return launch_pdl(fused_gemv_kernel<PRO, EPI>, dim3(grid), dim3(kThreads), smem, stream, a);
+    fused_gemv_kernel<PRO, EPI><<<grid, kThreads, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t dispatch_fused_gemv(const FusedGemvArgs& a, int grid, size_t smem, cudaStream_t stream, bool pdl) {
+    if (a.prologue == PRO_NONE) {
+        if (a.epilogue == EPI_STORE) return launch_fused_gemv<PRO_NONE, EPI_STORE>(a, grid, smem, stream, pdl);
+        if (a.epilogue == EPI_RESIDUAL) return launch_fused_gemv<PRO_NONE, EPI_RESIDUAL>(a, grid, smem, stream, pdl);
+        if (a.epilogue == EPI_CHANNEL_MIX) return launch_fused_gemv<PRO_NONE, EPI_CHANNEL_MIX>(a, grid, smem, stream, pdl);
+    } else if (a.epilogue == EPI_STORE) {
+        if (a.prologue == PRO_LN) return launch_fused_gemv<PRO_LN, EPI_STORE>(a, grid, smem, stream, pdl);
+        if (a.prologue == PRO_LN_SHIFT1) return launch_fused_gemv<PRO_LN_SHIFT1, EPI_STORE>(a, grid, smem, stream, pdl);
+        if (a.prologue == PRO_LN_SHIFT2) return launch_fused_gemv<PRO_LN_SHIFT2, EPI_STORE>(a, grid, smem, stream, pdl);
+    }
+    return cudaErrorInvalidValue;  // a prologue with a residual epilogue is not instantiated
+}
+
+}  // namespace
+
+cudaError_t fused_gemv(const FusedGemvArgs& a_in, int grid, cudaStream_t stream) {
+    FusedGemvArgs a = a_in;
+    const size_t smem = fused_gemv_prepare(a);
+    return dispatch_fused_gemv(a, grid, smem, stream, true);
 }
 
 cudaError_t tmix_shift_v6(const TmixArgs& a, cudaStream_t stream) {
@@ -1090,23 +1130,19 @@ int gemv_int8_static(int device, cudaStream_t stream, const uint8_t* w, const __
     if (current != device) return SG_BAD_DEVICE;
     StaticSetup& su = g_static_setup[device];
     {
-        // first call on this device: the array's address, the SM count and the kernel's shared-memory limit
+        // first call on this device: the array's address and the SM count
         std::lock_guard<std::mutex> lock(g_static_mutex);
         if (!su.ready) {
             void* ptr = nullptr;
             if ((*cuda_error = cudaGetSymbolAddress(&ptr, g_static_segments)) != cudaSuccess) return SG_CUDA;
             if ((*cuda_error = cudaDeviceGetAttribute(&su.sms, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess)
                 return SG_CUDA;
-            if ((*cuda_error = cudaFuncSetAttribute(fused_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                    200 * 1024)) != cudaSuccess)
-                return SG_CUDA;
             su.table = static_cast<GemvSegment*>(ptr);
             su.ready = true;
         }
     }
     if (K == 0 || M == 0 || K % 128 != 0 || T == 0 || T > (uint32_t)kDecodeMaxTokens || M > 0x7fffffffu) return SG_BAD_SHAPE;
-    const size_t smem = fused_gemv_smem(T, K, K, PRO_NONE, 0);
-    if (smem > 200 * 1024) return SG_BAD_SHAPE;
+    if (fused_gemv_smem(T, K, K, PRO_NONE, kMinRing) > 200 * 1024) return SG_BAD_SHAPE;
     const int grid = num_ctas == 0 ? su.sms : (int)num_ctas;
     if (num_ctas > (uint32_t)kStaticGemvMaxCtas || grid > kStaticGemvMaxCtas) return SG_TOO_MANY_CTAS;
 
@@ -1130,11 +1166,11 @@ int gemv_int8_static(int device, cudaStream_t stream, const uint8_t* w, const __
     p.out_stride = M;
     p.out_dtype = WRK_F32;
     p.act = act;
+    const size_t smem = fused_gemv_prepare(a);
     static_partition_kernel<<<1, 32, 0, stream>>>(su.table, K, M, grid);
     if ((*cuda_error = cudaGetLastError()) != cudaSuccess) return SG_CUDA;
     // a plain launch: the multiply reads the table at once, so it must not start before the fill kernel ends
-    fused_gemv_kernel<<<grid, kThreads, smem, stream>>>(a);
-    if ((*cuda_error = cudaGetLastError()) != cudaSuccess) return SG_CUDA;
+    if ((*cuda_error = dispatch_fused_gemv(a, grid, smem, stream, false)) != cudaSuccess) return SG_CUDA;
     return SG_OK;
 }
 

@@ -36,8 +36,8 @@ constexpr int kSegmentsPerCta = 3;
 struct FusedGemvArgs {
     GemvProblem p[kMaxProblems];
     int32_t num_problems;
-    int32_t num_slots;            // unused
-    int32_t debug;                // ablation mask (WRK_TRACE builds only)
+    int32_t ring_depth;           // staging cells per warp (filled in by fused_gemv)
+    uint32_t kmax;                // largest K of the launch (filled in by fused_gemv)
     uint32_t T;
     const GemvSegment* segments;  // [grid][kSegmentsPerCta], row0 == row1 marks an unused entry
     const float* table;           // NF4 code book (device)
@@ -67,7 +67,8 @@ struct FusedGemvArgs {
 
 cudaError_t fused_gemv(const FusedGemvArgs& a, int grid, cudaStream_t stream);
 bool fused_gemv_partition(const FusedGemvArgs& a, int grid, std::vector<GemvSegment>& table);
-size_t fused_gemv_smem(uint32_t T, uint32_t Kmax, uint32_t C, int prologue, int num_slots);
+// Dynamic shared memory of a launch with `depth` staging cells per warp (clamped to the supported 2 .. 4).
+size_t fused_gemv_smem(uint32_t T, uint32_t Kmax, uint32_t C, int prologue, int depth);
 
 // v6 data-dependent token shift: time_mix_w2 (5 x [D -> C]) + static mixes + 5-way shift.
 struct TmixArgs {
