@@ -18,6 +18,7 @@ SOURCES = [
     "ops.cpp",
     "kernels/quant.cu",
     "kernels/matmul.cu",
+    "kernels/gemm_umma.cu",
     "kernels/wkv.cu",
     "kernels/support.cu",
     "kernels/decode.cu",

@@ -25,9 +25,12 @@ struct MatmulArgs {
     DView in;              // [K, N, B]
     DView out;             // [M, N, B]
     int act;
-    // Optional second operand set fused into the same launch is not supported here.
+    int32_t* status;       // device status word (bounded waits report here); may be null
 };
 cudaError_t matmul(const MatmulArgs& a, int num_sms, cudaStream_t stream);
+// Tensor-memory (tcgen05) GEMM for N >= 16 tokens (gemm_umma.cu).
+bool matmul_umma_supported(const MatmulArgs& a);
+cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t stream);
 
 // ---- WKV recurrences (wkv.cu) ------------------------------------------------------------
 struct WkvArgs {

@@ -76,6 +76,7 @@ int32_t matmul_common(const char* name, int kind, wrk_tensor* matrix, wrk_tensor
     a.in = make_dview(*input);
     a.out = make_dview(*output);
     a.act = act;
+    a.status = matrix->ctx->device_status;
     const int sms = matrix->ctx->num_sms;
     // few tokens, fp16 activations, whole rows: the weight-streaming kernel of the decode path
     const uint32_t need = kind == k::MAT_FP16 ? 32 : 128;
