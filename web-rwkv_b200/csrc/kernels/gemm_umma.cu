@@ -1,18 +1,24 @@
-// Tensor-memory GEMM for the prefill / batched path (matmul_mat_fp16 / int8 / nf4 with more than a few
-// tokens): out[n][m] = act(sum_k W[m][k] * x[n][k]).
+// Tensor-memory GEMM for the prefill / batched path (matmul_mat_fp16 / int8 / nf4 with 16 or more tokens):
+// out[n][m] = act(sum_k W[m][k] * x[n][k]).
 //
-// One CTA owns a 128-row slice of W and up to 256 tokens.  Eight producer warps walk K in steps of 64:
-// they read the packed weights (u8 + per-128 (min, max), 4-bit + per-64 absmax, or fp16), dequantize them
-// to fp16 in registers and store them, together with the fp16 activations of the step, into shared
-// memory in the K-major 128-byte-swizzled layout tcgen05 reads.  A ninth warp issues the MMAs
-// (tcgen05.mma.cta_group::1.kind::f16, M = 128, N = token tile, K = 16 per instruction) into a TMEM
-// accumulator of 128 lanes x N fp32 columns and releases each stage through tcgen05.commit.  After the
-// last step the producer warps read the accumulator back with tcgen05.ld (warp w reads lanes
-// 32 (w % 4) ..), apply the activation and store token-major rows.
-//
+// One CTA owns a 128-row slice of W and up to 256 tokens and walks K in steps of 64.  Warp roles:
+//   * warp 9 (one lane) streams the packed weight tiles with TMA (cp.async.bulk.tensor.2d): 128 rows x 64
+//     (Int8) or 32 (NF4) bytes per step into a ring of raw stages several steps ahead of their use; fp16
+//     weights go straight into the A operand stage through a 128-byte-swizzled tensor map;
+//   * warp 10 (one lane) streams the fp16 activations of the step, [tokens x 64] through a 128-byte-swizzled
+//     tensor map, into the B operand stage (rows past the last token are zero-filled by the TMA unit);
+//   * warps 0-7 dequantize: each thread turns 32 weights of one row into fp16 (f32 math, one rounding) and
+//     stores them in the K-major 128-byte-swizzled layout tcgen05 reads; the (min, max) / absmax values of
+//     the next 256 columns are fetched with cp.async while the current ones are in use;
+//   * warp 8 (one lane) issues tcgen05.mma.cta_group::1.kind::f16 (M = 128, N = token tile, K = 16, four per
+//     step) into a TMEM accumulator of 128 lanes x N fp32 columns and releases the stage with tcgen05.commit;
+//   * after the last step warps 0-7 read the accumulator back with tcgen05.ld (warp w reads lanes
+//     32 (w % 4) ..), apply the activation and store token-major rows.
 // Weights enter the MMA as fp16(fma(q, (max - min) / 255, min)) resp. fp16(table[nib] * absmax), computed in
-// f32 and rounded once; the accumulation is fp32.  Every wait on an mbarrier is bounded: on a timeout the kernel records
-// WRK_ERR_TIMEOUT in the context's status word, stops waiting and still frees its TMEM columns.
+// f32 and rounded once; the accumulation is fp32.  Every wait on an mbarrier is bounded: on a timeout the
+// kernel records WRK_ERR_TIMEOUT in the context's status word, stops waiting and still frees its TMEM.
+#include <cuda.h>
+
 #include "device.cuh"
 #include "kernels.h"
 
@@ -23,11 +29,14 @@ namespace {
 
 constexpr int BM = 128;             // weight rows per CTA (UMMA M)
 constexpr int BK = 64;              // K per stage: one 128-byte swizzle atom of fp16
-constexpr int kProducerWarps = 8;
-constexpr int kUmmaThreads = (kProducerWarps + 1) * 32;
-constexpr int kMaxStages = 6;
+constexpr int kDequantWarps = 8;
+constexpr int kMmaWarp = 8, kWeightTmaWarp = 9;  // warp 10 streams the activations
+constexpr int kUmmaThreads = 11 * 32;
+constexpr int kMaxStages = 6;       // operand stages
+constexpr int kMaxRaw = 8;          // raw weight stages
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr uint32_t A_STAGE_BYTES = BM * BK * 2;  // 16 KB
+constexpr uint32_t SCALE_SLOT_BYTES = BM * 8;    // 8 bytes of scales per row and 256 columns
 
 struct UmmaParams {
     const uint8_t* w;
@@ -35,12 +44,12 @@ struct UmmaParams {
     const float* table;
     int kind;
     uint32_t K, M, N;
-    DView in, out;
+    DView out;
     int act;
     uint32_t n_tile;    // tokens per CTA: multiple of 16, <= 256
     uint32_t tmem_cols; // power of two >= max(32, n_tile)
-    uint32_t stages;
-    int vec_in;         // activations readable as 16-byte (fp16) / 32-byte (fp32) groups
+    uint32_t stages;    // operand stages
+    uint32_t raw;       // raw weight stages (quantized kinds)
     int32_t* status;
 };
 
@@ -51,6 +60,20 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+// 2-D tiled TMA load (no multicast) of the box at (x, y) into dst, completing on bar.
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint32_t x, uint32_t y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(
+                     smem_addr(dst)),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async8z(void* dst, const void* src, bool valid) {
+    const uint32_t n = valid ? 8u : 0u;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(smem_addr(dst)), "l"(src), "r"(n) : "memory");
 }
 // Waits for the phase with the given parity; gives up after kSpinLimit polls (or at once when another
 // wait of this CTA has already given up) and reports it.
@@ -116,114 +139,78 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 
 __device__ __forceinline__ uint32_t pack_half2(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
 
-// 32 consecutive weights of one row (k0 .. k0 + 31) as four 16-byte groups of fp16.
-__device__ __forceinline__ void dequant32(const UmmaParams& p, uint32_t m, uint32_t k0, const float2* lut2, uint4 out[4]) {
-    if (m >= p.M) {
+
+// 32 (Int8) weights of one row, raw bytes in `q0, q1`, block scale (min, max) -> four 16-byte groups of fp16.
+__device__ __forceinline__ void dequant_int8(uint4 q0, uint4 q1, uint32_t minmax, uint4 out[4]) {
+    // f32 dequantization, one rounding to fp16 per weight: the errors of a row are independent, none is
+    // shared by a whole block
+    const float2 mm = __half22float2(*reinterpret_cast<const __half2*>(&minmax));
+    const float sc = (mm.y - mm.x) * (1.0f / 255.0f), mn = mm.x;
+    const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    uint32_t h[16];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) out[j] = make_uint4(0, 0, 0, 0);
-        return;
+    for (int i = 0; i < 8; ++i) {
+        // byte b -> float 8388608 + b (0x4B000000 | b), minus 8388608: b exactly
+        const float f0 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7650)) - 8388608.0f;
+        const float f1 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7651)) - 8388608.0f;
+        const float f2 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7652)) - 8388608.0f;
+        const float f3 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7653)) - 8388608.0f;
+        h[2 * i] = pack_half2(__floats2half2_rn(fmaf(f0, sc, mn), fmaf(f1, sc, mn)));
+        h[2 * i + 1] = pack_half2(__floats2half2_rn(fmaf(f2, sc, mn), fmaf(f3, sc, mn)));
     }
-    if (p.kind == MAT_FP16) {
-        const uint4* src = reinterpret_cast<const uint4*>(p.w + ((size_t)m * p.K + k0) * 2);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) out[j] = __ldg(src + j);
-    } else if (p.kind == MAT_INT8) {
-        // f32 dequantization (q / 255 scaled as in the reference up to the order of the two roundings), one
-        // rounding to fp16 per weight: the errors of a row are independent, none is shared by a whole block
-        const size_t e = (size_t)m * p.K + k0;
-        const uint4* src = reinterpret_cast<const uint4*>(p.w + e);
-        const uint4 q0 = __ldg(src), q1 = __ldg(src + 1);
-        const float2 mm = __half22float2(__ldg(reinterpret_cast<const __half2*>(p.scale) + e / 128));
-        const float sc = (mm.y - mm.x) * (1.0f / 255.0f), mn = mm.x;
-        const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-        uint32_t h[16];
+    for (int j = 0; j < 4; ++j) out[j] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
+}
+// 32 NF4 weights (16 bytes, low nibble first) of one 64-weight block with absmax `am`.
+__device__ __forceinline__ void dequant_nf4(uint4 q, float am, const float2* lut2, uint4 out[4]) {
+    const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+    uint32_t h[16];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            // byte b -> float 8388608 + b (0x4B000000 | b), minus 8388608: b exactly
-            const float f0 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7650)) - 8388608.0f;
-            const float f1 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7651)) - 8388608.0f;
-            const float f2 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7652)) - 8388608.0f;
-            const float f3 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7653)) - 8388608.0f;
-            h[2 * i] = pack_half2(__floats2half2_rn(fmaf(f0, sc, mn), fmaf(f1, sc, mn)));
-            h[2 * i + 1] = pack_half2(__floats2half2_rn(fmaf(f2, sc, mn), fmaf(f3, sc, mn)));
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const float2 pair = lut2[(words[i] >> (8 * b)) & 0xffu];  // (table[lo nibble], table[hi nibble])
+            h[4 * i + b] = pack_half2(__floats2half2_rn(pair.x * am, pair.y * am));
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) out[j] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
-    } else {
-        // NF4: 16 bytes, low nibble first; one absmax per 64 weights; f32 product rounded once
-        const size_t e = (size_t)m * p.K + k0;
-        const uint4 q = __ldg(reinterpret_cast<const uint4*>(p.w + e / 2));
-        const float am = __half2float(__ldg(p.scale + e / 64));
-        const uint32_t words[4] = {q.x, q.y, q.z, q.w};
-        uint32_t h[16];
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                const float2 pair = lut2[(words[i] >> (8 * b)) & 0xffu];  // (table[lo nibble], table[hi nibble])
-                h[4 * i + b] = pack_half2(__floats2half2_rn(pair.x * am, pair.y * am));
-            }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) out[j] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
-    }
+    for (int j = 0; j < 4; ++j) out[j] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
 }
 
-// Eight activations x[n][k0 .. k0 + 7] as fp16 (zeros beyond the last token).
-__device__ __forceinline__ uint4 load_x8(const UmmaParams& p, uint32_t n, uint32_t k0) {
-    if (n >= p.N) return make_uint4(0, 0, 0, 0);
-    const size_t i = p.in.index(k0, n, 0);
-    if (p.in.dtype == WRK_F16) {
-        const __half* src = static_cast<const __half*>(p.in.base) + i;
-        if (p.vec_in) return *reinterpret_cast<const uint4*>(src);
-        __half v[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = src[e];
-        return *reinterpret_cast<uint4*>(v);
-    }
-    const float* src = static_cast<const float*>(p.in.base) + i;
-    float f[8];
-    if (p.vec_in) {
-        const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
-        f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
-    } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = src[e];
-    }
-    uint4 r;
-    r.x = pack_half2(__floats2half2_rn(f[0], f[1]));
-    r.y = pack_half2(__floats2half2_rn(f[2], f[3]));
-    r.z = pack_half2(__floats2half2_rn(f[4], f[5]));
-    r.w = pack_half2(__floats2half2_rn(f[6], f[7]));
-    return r;
-}
-
-__global__ void __launch_bounds__(kUmmaThreads, 1) matmul_umma_kernel(const UmmaParams p) {
+__global__ void __launch_bounds__(kUmmaThreads, 1)
+matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], done_bar;
+    __shared__ uint64_t ab_full[kMaxStages], ab_empty[kMaxStages], raw_full[kMaxRaw], raw_empty[kMaxRaw], done_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ float2 lut2[256];
     __shared__ int abort_flag;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool quantized = p.kind != MAT_FP16;
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t b_bytes = p.n_tile * BK * 2;
-    const uint32_t stage_bytes = A_STAGE_BYTES + b_bytes;
+    const uint32_t stage_bytes = A_STAGE_BYTES + b_bytes;                   // [A | B], both 1024-byte aligned
+    const uint32_t raw_row = p.kind == MAT_INT8 ? 64u : 32u;                // raw bytes per row and step
+    const uint32_t raw_bytes = BM * raw_row;
+    uint8_t* raw_base = smem + (size_t)p.stages * stage_bytes;              // raw weight stages
+    uint8_t* scale_base = raw_base + (size_t)p.raw * raw_bytes;             // [2][BM][8 bytes]
     const uint32_t m0 = blockIdx.x * BM, n0 = blockIdx.y * p.n_tile;
     const uint32_t nk = p.K / BK;
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.stages; ++s) {
-            mbar_init(&full_bar[s], kProducerWarps);
-            mbar_init(&empty_bar[s], 1);
+            mbar_init(&ab_full[s], quantized ? kDequantWarps + 1 : 2);  // dequant warps (or the weight TMA) + activation TMA
+            mbar_init(&ab_empty[s], 1);
+        }
+        for (uint32_t r = 0; r < p.raw; ++r) {
+            mbar_init(&raw_full[r], 1);
+            mbar_init(&raw_empty[r], kDequantWarps);
         }
         mbar_init(&done_bar, 1);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (p.kind == MAT_NF4 && threadIdx.x < 256) {
-        lut2[threadIdx.x] = make_float2(p.table[threadIdx.x & 15], p.table[threadIdx.x >> 4]);
-    }
-    if (warp == kProducerWarps) {
+    if (p.kind == MAT_NF4 && threadIdx.x < 256) lut2[threadIdx.x] = make_float2(p.table[threadIdx.x & 15], p.table[threadIdx.x >> 4]);
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(&tmem_base_slot)), "r"(p.tmem_cols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
@@ -233,25 +220,48 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) matmul_umma_kernel(const Umma
     tc_fence_after();
     const uint32_t tmem_d = tmem_base_slot;
 
-    if (warp < kProducerWarps) {
-        // ---- producers: dequantized weights and activations of one K step per stage ----
-        const uint32_t row = threadIdx.x >> 1, half = threadIdx.x & 1;  // 256 threads: 128 rows x two 32-weight halves
-        for (uint32_t kt = 0; kt < nk; ++kt) {
-            const uint32_t s = kt % p.stages, use = kt / p.stages;
-            if (use > 0) mbar_wait(&empty_bar[s], (use - 1) & 1, &abort_flag, p.status);
-            uint8_t* sa = smem + (size_t)s * stage_bytes;
-            uint8_t* sb = sa + A_STAGE_BYTES;
-            uint4 wv[4];
-            dequant32(p, m0 + row, kt * BK + half * 32, lut2, wv);
+    if (warp < kDequantWarps) {
+        if (quantized) {
+            // ---- dequantizers: thread (row, half) owns 32 weights of a row per step ----
+            const uint32_t row = threadIdx.x >> 1, half = threadIdx.x & 1;
+            const uint32_t m = m0 + row;
+            const uint32_t nsuper = (nk + 3) / 4;  // scale slots cover 256 columns = four steps
+            const uint8_t* srow = reinterpret_cast<const uint8_t*>(p.scale) + (size_t)m * (p.K / 256) * 8;
+            if (half == 0) cp_async8z(scale_base + row * 8, srow, m < p.M);
+            asm volatile("cp.async.commit_group;\n" ::: "memory");
+            for (uint32_t kt = 0; kt < nk; ++kt) {
+                if ((kt & 3) == 0) {
+                    const uint32_t j = kt >> 2;
+                    __syncwarp();  // both threads of a row are done with the slot about to be refilled
+                    if (half == 0 && j + 1 < nsuper)
+                        cp_async8z(scale_base + ((j + 1) & 1) * SCALE_SLOT_BYTES + row * 8, srow + (size_t)(j + 1) * 8, m < p.M);
+                    asm volatile("cp.async.commit_group;\n" ::: "memory");
+                    asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+                    __syncwarp();  // the sibling thread's copy is visible
+                }
+                const uint32_t r = kt % p.raw, ruse = kt / p.raw;
+                mbar_wait(&raw_full[r], ruse & 1, &abort_flag, p.status);
+                const uint8_t* rs = raw_base + (size_t)r * raw_bytes + row * raw_row + half * (raw_row / 2);
+                uint4 q0 = *reinterpret_cast<const uint4*>(rs), q1 = make_uint4(0, 0, 0, 0);
+                if (p.kind == MAT_INT8) q1 = *reinterpret_cast<const uint4*>(rs + 16);
+                const uint8_t* ss = scale_base + ((kt >> 2) & 1) * SCALE_SLOT_BYTES + row * 8;
+                uint4 wv[4];
+                if (p.kind == MAT_INT8) {
+                    dequant_int8(q0, q1, *reinterpret_cast<const uint32_t*>(ss + ((kt >> 1) & 1) * 4), wv);
+                } else {
+                    dequant_nf4(q0, __half2float(*reinterpret_cast<const __half*>(ss + (kt & 3) * 2)), lut2, wv);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&raw_empty[r]);  // the raw stage may be refilled
+                const uint32_t s = kt % p.stages, use = kt / p.stages;
+                if (use > 0) mbar_wait(&ab_empty[s], (use - 1) & 1, &abort_flag, p.status);
+                uint8_t* sa = smem + (size_t)s * stage_bytes;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(sa + sw128_offset(row, half * 4 + j)) = wv[j];
-            for (uint32_t q = threadIdx.x; q < p.n_tile * 8; q += kProducerWarps * 32) {
-                const uint32_t tok = q >> 3, ch = q & 7;
-                *reinterpret_cast<uint4*>(sb + sw128_offset(tok, ch)) = load_x8(p, n0 + tok, kt * BK + ch * 8);
+                for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(sa + sw128_offset(row, half * 4 + j)) = wv[j];
+                fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&ab_full[s]);
             }
-            fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&full_bar[s]);
         }
         // ---- epilogue: TMEM -> registers -> activation -> token-major rows ----
         mbar_wait(&done_bar, 0, &abort_flag, p.status);
@@ -271,12 +281,12 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) matmul_umma_kernel(const Umma
                 }
             }
         }
-    } else {
+    } else if (warp == kMmaWarp) {
         // ---- MMA issuer ----
         const uint32_t idesc = f16_idesc(BM, p.n_tile);
         for (uint32_t kt = 0; kt < nk; ++kt) {
             const uint32_t s = kt % p.stages, use = kt / p.stages;
-            mbar_wait(&full_bar[s], use & 1, &abort_flag, p.status);
+            mbar_wait(&ab_full[s], use & 1, &abort_flag, p.status);
             tc_fence_after();
             if (lane == 0) {
                 const uint32_t sa = smem_addr(smem + (size_t)s * stage_bytes);
@@ -284,29 +294,89 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) matmul_umma_kernel(const Umma
 #pragma unroll
                 for (uint32_t kk = 0; kk < BK / 16; ++kk)  // 32 bytes of K per instruction: + 2 in the address field
                     umma_f16(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (kt | kk) != 0 ? 1u : 0u);
-                umma_commit(&empty_bar[s]);  // arrives when the MMAs above have read the stage
+                umma_commit(&ab_empty[s]);  // arrives when the MMAs above have read the stage
             }
             __syncwarp();
         }
         if (lane == 0) umma_commit(&done_bar);
         __syncwarp();
+    } else if (warp == kWeightTmaWarp) {
+        if (lane == 0) {
+            if (quantized) {
+                for (uint32_t kt = 0; kt < nk; ++kt) {
+                    const uint32_t r = kt % p.raw, ruse = kt / p.raw;
+                    if (ruse > 0) mbar_wait(&raw_empty[r], (ruse - 1) & 1, &abort_flag, p.status);
+                    mbar_expect_tx(&raw_full[r], raw_bytes);
+                    tma_load_2d(raw_base + (size_t)r * raw_bytes, &map_w, kt * raw_row, m0, &raw_full[r]);
+                }
+            } else {
+                for (uint32_t kt = 0; kt < nk; ++kt) {
+                    const uint32_t s = kt % p.stages, use = kt / p.stages;
+                    if (use > 0) mbar_wait(&ab_empty[s], (use - 1) & 1, &abort_flag, p.status);
+                    mbar_expect_tx(&ab_full[s], A_STAGE_BYTES);
+                    tma_load_2d(smem + (size_t)s * stage_bytes, &map_w, kt * BK, m0, &ab_full[s]);
+                }
+            }
+        }
+    } else {
+        if (lane == 0) {
+            for (uint32_t kt = 0; kt < nk; ++kt) {
+                const uint32_t s = kt % p.stages, use = kt / p.stages;
+                if (use > 0) mbar_wait(&ab_empty[s], (use - 1) & 1, &abort_flag, p.status);
+                mbar_expect_tx(&ab_full[s], b_bytes);
+                tma_load_2d(smem + (size_t)s * stage_bytes + A_STAGE_BYTES, &map_x, kt * BK, n0, &ab_full[s]);
+            }
+        }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == kProducerWarps) {
+    if (warp == kMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_d), "r"(p.tmem_cols) : "memory");
     }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry-point lookup (no link against libcuda).
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+bool make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t rows, uint64_t row_bytes,
+                 uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swz) {
+    EncodeTiledFn fn = encode_tiled();
+    if (fn == nullptr) return false;
+    const cuuint64_t gdim[2] = {inner, rows};
+    const cuuint64_t gstride[1] = {row_bytes};
+    const cuuint32_t box[2] = {box_inner, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, dt, 2, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace
 
 bool matmul_umma_supported(const MatmulArgs& a) {
     if (a.B != 1 || a.N < 16 || a.M == 0) return false;
-    if (a.K % BK != 0 || (a.kind == MAT_INT8 && a.K % 128 != 0)) return false;
+    if (a.K % BK != 0 || (a.kind != MAT_FP16 && a.K % 256 != 0)) return false;  // scale slots are fetched 8 bytes at a time
     if (reinterpret_cast<uintptr_t>(a.matrix) % 16 != 0) return false;
-    if (a.scale != nullptr && reinterpret_cast<uintptr_t>(a.scale) % 4 != 0) return false;
-    return true;
+    if (a.scale != nullptr && reinterpret_cast<uintptr_t>(a.scale) % 8 != 0) return false;
+    // activations go through a tensor map: fp16, rows 16-byte aligned
+    if (a.in.dtype != WRK_F16 || a.in.stride[0] % 8 != 0) return false;
+    const uintptr_t x0 = reinterpret_cast<uintptr_t>(a.in.base) + a.in.index(0, 0, 0) * 2;
+    if (x0 % 16 != 0) return false;
+    return encode_tiled() != nullptr;
 }
 
 cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t stream) {
@@ -318,19 +388,39 @@ cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t strea
     p.K = a.K;
     p.M = a.M;
     p.N = a.N;
-    p.in = a.in;
     p.out = a.out;
     p.act = a.act;
     p.status = status;
     p.n_tile = std::min<uint32_t>(256, (a.N + 15) / 16 * 16);
     p.tmem_cols = 32;
     while (p.tmem_cols < p.n_tile) p.tmem_cols *= 2;
+    const uint32_t nk = a.K / BK;
     const uint32_t stage_bytes = A_STAGE_BYTES + p.n_tile * BK * 2;
-    p.stages = std::min<uint32_t>(kMaxStages, std::max<uint32_t>(2, (200u * 1024) / stage_bytes));
-    p.stages = std::min<uint32_t>(p.stages, std::max<uint32_t>(2, a.K / BK));
-    const size_t esz = a.in.dtype == WRK_F16 ? 2 : 4;
-    p.vec_in = (a.in.stride[0] % 8 == 0) && (a.in.offset[0] % 8 == 0) && (reinterpret_cast<uintptr_t>(a.in.base) % (8 * esz) == 0);
-    const size_t smem = (size_t)p.stages * stage_bytes + 1024;
+    const uint32_t raw_bytes = a.kind == MAT_INT8 ? BM * 64 : a.kind == MAT_NF4 ? BM * 32 : 0;
+    const uint32_t budget = 200u * 1024;
+    p.raw = a.kind == MAT_FP16 ? 0 : std::min<uint32_t>(kMaxRaw, std::max<uint32_t>(2, nk));
+    p.stages = std::min<uint32_t>(kMaxStages, std::max<uint32_t>(2, nk));
+    while (p.stages * stage_bytes + p.raw * raw_bytes + 2 * SCALE_SLOT_BYTES > budget) {
+        if (p.raw > 4) --p.raw;
+        else if (p.stages > 2) --p.stages;
+        else if (p.raw > 2) --p.raw;
+        else break;
+    }
+    const size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.raw * raw_bytes + 2 * SCALE_SLOT_BYTES + 1024;
+
+    CUtensorMap map_w, map_x;
+    bool ok;
+    if (a.kind == MAT_FP16)
+        ok = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a.matrix, a.K, a.M, (uint64_t)a.K * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+    else if (a.kind == MAT_INT8)
+        ok = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.matrix, a.K, a.M, a.K, 64, BM, CU_TENSOR_MAP_SWIZZLE_NONE);
+    else
+        ok = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.matrix, a.K / 2, a.M, a.K / 2, 32, BM, CU_TENSOR_MAP_SWIZZLE_NONE);
+    const __half* x0 = static_cast<const __half*>(a.in.base) + a.in.index(0, 0, 0);
+    ok = ok && make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x0, a.K, a.N, (uint64_t)a.in.stride[0] * 2, BK, p.n_tile,
+                           CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!ok) return cudaErrorInvalidValue;
+
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(matmul_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024);
@@ -338,7 +428,7 @@ cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t strea
         configured = true;
     }
     const dim3 grid((a.M + BM - 1) / BM, (a.N + p.n_tile - 1) / p.n_tile);
-    matmul_umma_kernel<<<grid, kUmmaThreads, smem, stream>>>(p);
+    matmul_umma_kernel<<<grid, kUmmaThreads, smem, stream>>>(p, map_w, map_x);
     return cudaGetLastError();
 }
 
