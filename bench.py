@@ -174,6 +174,7 @@ def main():
     ap.add_argument("--decode", type=int, default=DECODE)
     ap.add_argument("--cpu-sample", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--strict", action="store_true", help="one launch per reference op (no fused kernels)")
     args = ap.parse_args()
 
@@ -316,6 +317,28 @@ def main():
         e2e_s = float(t.item())
     e2e_value = world * args.steps * args.decode / e2e_s
 
+    # ---- secondary: prefill of one 256-token chunk of the same model (tensor-memory GEMM path), rank 0 only ----
+    prefill = None
+    if rank == 0 and not args.no_prefill:
+        chunk = 256
+        p_tokens = rng.integers(0, V - 1, chunk).tolist()
+        p_logits = np.empty((1, bundle.vocab), dtype=np.float32)
+
+        def prefill_once():
+            p_inp = rt.RnnInput([(p_tokens, wrk.RNN_LAST)], chunk)
+            bundle.infer(p_inp, p_logits)
+
+        for _ in range(2):
+            prefill_once()
+        ctx.synchronize()
+        t0 = time.perf_counter()
+        reps = 5
+        for _ in range(reps):
+            prefill_once()
+        ctx.synchronize()
+        prefill = {"value": reps * chunk / (time.perf_counter() - t0), "unit": "tokens/s",
+                   "workload": f"{chunk}-token chunk of the same model, host tokens in, last-token logits out"}
+
     if rank != 0:
         return
 
@@ -345,6 +368,7 @@ def main():
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s",
                 "h2d_bytes_per_step": args.decode * (C * 2 + 12), "d2h_bytes_per_step": args.decode * bundle.vocab * 4},
+        "prefill": prefill,
         "gpu_launches": int(gpu_launches),
         "kernels_per_token": int(kernels_per_token),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
