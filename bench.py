@@ -43,6 +43,21 @@ SEED_WEIGHTS, SEED_TOKENS = 1002, 2002
 NCU_TRAFFIC_RATIO = 1.01
 
 
+def max_over_ranks(value, dist, device="cuda"):
+    """MAX of a per-rank scalar over the process group (identity without one)."""
+    if dist is None:
+        return value
+    import torch
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def whole_job_rate(world, steps, units_per_step, ms):
+    """Units all ranks processed divided by the slowest rank's time."""
+    return world * steps * units_per_step / (ms * 1e-3)
+
+
 def _peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -283,12 +298,8 @@ def main():
     barrier()
     gpu_launches = ctx.launch_count() - launches0
     clocks = sampler.stop()
-    if dist is not None:
-        import torch
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    value = world * args.steps * args.decode / (ms * 1e-3)
+    ms = max_over_ranks(ms, dist)
+    value = whole_job_rate(world, args.steps, args.decode, ms)
 
     # ---- end to end through the reference-facing call: host tokens in, host logits out ----
     import ctypes
@@ -310,12 +321,8 @@ def main():
         e2e_step(args.decode)
     ctx.synchronize()
     e2e_s = time.perf_counter() - t0
-    if dist is not None:
-        import torch
-        t = torch.tensor([e2e_s], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    e2e_value = world * args.steps * args.decode / e2e_s
+    e2e_s = max_over_ranks(e2e_s, dist)
+    e2e_value = whole_job_rate(world, args.steps, args.decode, e2e_s * 1e3)
 
     # ---- secondary: prefill of one 256-token chunk of the same model (tensor-memory GEMM path), rank 0 only ----
     prefill = None

@@ -1,18 +1,18 @@
-// Fused decode path for jobs of a few tokens (T <= 8): the whole v5/v6 layer in seven launches.
+// Fused decode path for jobs of a few tokens (T <= 8): the whole v6 layer in seven launches.
 //
 // The quantized matmuls of a decode step are pure weight streaming, and at model widths of 2048-4096
 // a single matrix is only a few microseconds of HBM time, so the structure of this file is built
 // around never letting the stream of weights stop:
 //   * fused_gemv_kernel is a grouped weight-streaming kernel.  A launch covers several matrices (e.g.
 //     key / value / receptance / gate + the decay adapter); the concatenated row space is cut into one
-//     contiguous row range per CTA (balanced by bytes, one CTA per SM slot), and each CTA pulls exactly its
-//     rows into shared memory with asynchronous 16-byte copies (cp.async, one commit group per tile part of
-//     16 rows x 1 KB + its block scales), four to six tile parts in flight.  Per-row bulk-TMA copies were
-//     measured first: the TMA unit serialises them (~50 ns each, 32 per tile part), which cost more than
-//     the copy itself; a 2-D tensor-map box would fetch whole 16-row boxes and over-read the 13.8-row
-//     shares a 2048-row matrix leaves per SM.
+//     contiguous row range per CTA (balanced by bytes, one CTA per SM; the SM's second CTA slot is left to
+//     the next launch).  A CTA walks its rows in MMA row tiles of 16; its 16 warps split a tile's 128-byte
+//     chunks and each streams its own items through a private ring in shared memory with cp.async.
+//     (A variant that re-laid the weights per CTA at load time and fetched 34 KB stages with one
+//     cp.async.bulk each was measured: faster alone, slower inside the model, twice the weight memory;
+//     it is not kept.)
 //   * every kernel here is launched with programmatic dependent launch: it signals its dependents at
-//     once, issues the copies of its first weight tiles, and only then executes griddepcontrol.wait.
+//     once, issues the copies of its first weight items, and only then executes griddepcontrol.wait.
 //     Weights are never written during a job, so the next kernel's weights are already landing in shared
 //     memory while the previous kernel is still finishing.
 //   * layer norm + token shift run as a per-CTA prologue (every CTA recomputes the few-KB vector instead
