@@ -346,6 +346,9 @@ def main():
         prefill = {"value": reps * chunk / (time.perf_counter() - t0), "unit": "tokens/s",
                    "workload": f"{chunk}-token chunk of the same model, host tokens in, last-token logits out"}
 
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
         return
 

@@ -50,6 +50,9 @@ struct UmmaParams {
     uint32_t tmem_cols; // power of two >= max(32, n_tile)
     uint32_t stages;    // operand stages
     uint32_t raw;       // raw weight stages (quantized kinds)
+    uint32_t splits;    // CTAs along K per output tile (grid.z)
+    float* ws;          // [tile][split][n_tile][128] partial accumulators (splits > 1)
+    uint32_t* counters; // [tile] arrivals
     int32_t* status;
 };
 
@@ -194,7 +197,11 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
     uint8_t* raw_base = smem + (size_t)p.stages * stage_bytes;              // raw weight stages
     uint8_t* scale_base = raw_base + (size_t)p.raw * raw_bytes;             // [2][BM][8 bytes]
     const uint32_t m0 = blockIdx.x * BM, n0 = blockIdx.y * p.n_tile;
-    const uint32_t nk = p.K / BK;
+    // this CTA's share of the K steps (split-K: grid.z CTAs per output tile)
+    const uint32_t nk_all = p.K / BK;
+    const uint32_t k_begin = (uint32_t)((uint64_t)nk_all * blockIdx.z / p.splits);
+    const uint32_t nk = (uint32_t)((uint64_t)nk_all * (blockIdx.z + 1) / p.splits) - k_begin;
+    __shared__ uint32_t is_last_split;
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.stages; ++s) {
@@ -225,8 +232,9 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
             // ---- dequantizers: thread (row, half) owns 32 weights of a row per step ----
             const uint32_t row = threadIdx.x >> 1, half = threadIdx.x & 1;
             const uint32_t m = m0 + row;
-            const uint32_t nsuper = (nk + 3) / 4;  // scale slots cover 256 columns = four steps
-            const uint8_t* srow = reinterpret_cast<const uint8_t*>(p.scale) + (size_t)m * (p.K / 256) * 8;
+            // scale slots cover 256 columns = four steps; the walk starts at a multiple of four steps
+            const uint32_t nsuper = (nk + 3) / 4;
+            const uint8_t* srow = reinterpret_cast<const uint8_t*>(p.scale) + ((size_t)m * (p.K / 256) + k_begin / 4) * 8;
             if (half == 0) cp_async8z(scale_base + row * 8, srow, m < p.M);
             asm volatile("cp.async.commit_group;\n" ::: "memory");
             for (uint32_t kt = 0; kt < nk; ++kt) {
@@ -269,11 +277,17 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
         const uint32_t quad = warp & 3, side = warp >> 2;  // lanes 32 quad .., half of the columns each
         const uint32_t m = m0 + quad * 32 + lane;
         const uint32_t c_begin = side * (p.n_tile / 2), c_end = c_begin + p.n_tile / 2;
+        const uint32_t tile = blockIdx.y * gridDim.x + blockIdx.x;
+        float* ws_mine = p.ws + ((size_t)tile * p.splits + blockIdx.z) * p.n_tile * BM;
         for (uint32_t c = c_begin; c < c_end; c += 8) {
             uint32_t v[8];
             tmem_ld8(tmem_d + ((quad * 32) << 16) + c, v);
             tmem_ld_wait();
-            if (m < p.M) {
+            if (p.splits > 1) {
+                // partial sums, column-major inside the tile so that a warp writes 128 contiguous bytes
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ws_mine[(size_t)(c + j) * BM + quad * 32 + lane] = __uint_as_float(v[j]);
+            } else if (m < p.M) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const uint32_t n = n0 + c + j;
@@ -281,6 +295,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
                 }
             }
         }
+        if (p.splits > 1) __threadfence();
     } else if (warp == kMmaWarp) {
         // ---- MMA issuer ----
         const uint32_t idesc = f16_idesc(BM, p.n_tile);
@@ -307,14 +322,14 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
                     const uint32_t r = kt % p.raw, ruse = kt / p.raw;
                     if (ruse > 0) mbar_wait(&raw_empty[r], (ruse - 1) & 1, &abort_flag, p.status);
                     mbar_expect_tx(&raw_full[r], raw_bytes);
-                    tma_load_2d(raw_base + (size_t)r * raw_bytes, &map_w, kt * raw_row, m0, &raw_full[r]);
+                    tma_load_2d(raw_base + (size_t)r * raw_bytes, &map_w, (k_begin + kt) * raw_row, m0, &raw_full[r]);
                 }
             } else {
                 for (uint32_t kt = 0; kt < nk; ++kt) {
                     const uint32_t s = kt % p.stages, use = kt / p.stages;
                     if (use > 0) mbar_wait(&ab_empty[s], (use - 1) & 1, &abort_flag, p.status);
                     mbar_expect_tx(&ab_full[s], A_STAGE_BYTES);
-                    tma_load_2d(smem + (size_t)s * stage_bytes, &map_w, kt * BK, m0, &ab_full[s]);
+                    tma_load_2d(smem + (size_t)s * stage_bytes, &map_w, (k_begin + kt) * BK, m0, &ab_full[s]);
                 }
             }
         }
@@ -324,7 +339,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
                 const uint32_t s = kt % p.stages, use = kt / p.stages;
                 if (use > 0) mbar_wait(&ab_empty[s], (use - 1) & 1, &abort_flag, p.status);
                 mbar_expect_tx(&ab_full[s], b_bytes);
-                tma_load_2d(smem + (size_t)s * stage_bytes + A_STAGE_BYTES, &map_x, kt * BK, n0, &ab_full[s]);
+                tma_load_2d(smem + (size_t)s * stage_bytes + A_STAGE_BYTES, &map_x, (k_begin + kt) * BK, n0, &ab_full[s]);
             }
         }
     }
@@ -333,6 +348,46 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
     if (warp == kMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_d), "r"(p.tmem_cols) : "memory");
+    }
+    if (p.splits > 1) {
+        // the CTA that arrives last at the tile's counter adds the partial tiles and finishes the outputs
+        const uint32_t tile = blockIdx.y * gridDim.x + blockIdx.x;
+        if (threadIdx.x == 0) {
+            const uint32_t prev = atomicAdd(&p.counters[tile], 1u);
+            is_last_split = prev == p.splits - 1 ? 1u : 0u;
+            if (is_last_split) p.counters[tile] = 0;  // ready for the next launch on the stream
+        }
+        __syncthreads();
+        if (is_last_split && warp < kDequantWarps) {
+            __threadfence();
+            const float* ws_tile = p.ws + (size_t)tile * p.splits * p.n_tile * BM;
+            // thread: four consecutive rows (one 16-byte load per partial tile) of every eighth column
+            const uint32_t row = (threadIdx.x & 31) * 4, m = m0 + row;
+            for (uint32_t c0 = threadIdx.x >> 5; c0 < p.n_tile; c0 += 32) {
+                float4 sum[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) sum[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (uint32_t z = 0; z < p.splits; ++z) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const uint32_t c = c0 + 8 * u;
+                        if (c < p.n_tile) {
+                            const float4 v = *reinterpret_cast<const float4*>(ws_tile + ((size_t)z * p.n_tile + c) * BM + row);
+                            sum[u].x += v.x, sum[u].y += v.y, sum[u].z += v.z, sum[u].w += v.w;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t n = n0 + c0 + 8 * u;
+                    if (c0 + 8 * u >= p.n_tile || n >= p.N) continue;
+                    const float r4[4] = {sum[u].x, sum[u].y, sum[u].z, sum[u].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (m + e < p.M) dstore(p.out.base, p.out.dtype, p.out.index(m + e, n, 0), activate_f(p.act, r4[e]));
+                }
+            }
+        }
     }
 }
 
@@ -427,7 +482,28 @@ cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t strea
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    const dim3 grid((a.M + BM - 1) / BM, (a.N + p.n_tile - 1) / p.n_tile);
+    dim3 grid((a.M + BM - 1) / BM, (a.N + p.n_tile - 1) / p.n_tile, 1);
+    // split K across CTAs while the output tiles alone leave SMs idle: each split keeps at least eight steps
+    // (a multiple of four, so scale slots stay aligned) and its partial tile must fit the scratch
+    p.splits = 1;
+    const uint32_t tiles = grid.x * grid.y;
+    if (a.ws != nullptr && a.counters != nullptr && tiles <= a.num_counters) {
+        int sms = 148, device = 0;
+        if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        uint32_t want = std::max<uint32_t>(1, (uint32_t)sms / tiles);
+        want = std::min<uint32_t>(want, std::max<uint32_t>(1, nk / 8));
+        want = std::min<uint32_t>(want, 16);
+        while (want > 1 && (nk % (4 * want) != 0 || (size_t)tiles * want * p.n_tile * BM * sizeof(float) > a.ws_bytes)) --want;
+        p.splits = want;
+    }
+    p.ws = a.ws;
+    p.counters = a.counters;
+    grid.z = p.splits;
+    if (p.splits > 1) {
+        const uint32_t nk_split = nk / p.splits;
+        p.stages = std::min<uint32_t>(p.stages, std::max<uint32_t>(2, nk_split));
+        if (p.raw) p.raw = std::min<uint32_t>(p.raw, std::max<uint32_t>(2, nk_split));
+    }
     matmul_umma_kernel<<<grid, kUmmaThreads, smem, stream>>>(p, map_w, map_x);
     return cudaGetLastError();
 }
