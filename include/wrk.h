@@ -231,6 +231,19 @@ int32_t wrk_matrix_matmul_op_sparse(wrk_matrix* m, const wrk_view* input, const 
 /* The default NF4 table of Float4Quant::new, matrix.rs:48-70. */
 int32_t wrk_nf4_table(float table[16]);
 
+/* ---- Tensor-parallel plumbing (the reference is single-GPU; no counterpart) ----
+ * One process per GPU.  Rank 0 makes an id, every rank (rank 0 included) creates its communicator from the
+ * same 128 bytes; the collectives are deferred ops on the context's stream like any other op. */
+typedef struct wrk_comm wrk_comm;
+int32_t wrk_comm_unique_id(uint8_t id[128]);
+int32_t wrk_comm_create(wrk_context* ctx, const uint8_t id[128], int32_t rank, int32_t world, wrk_comm** out);
+int32_t wrk_comm_release(wrk_comm* comm);
+int32_t wrk_comm_rank(const wrk_comm* comm, int32_t* rank, int32_t* world);
+/* x <- sum over ranks of x, in place (f16 or f32). */
+int32_t wrk_op_all_reduce(wrk_comm* comm, wrk_tensor* x, wrk_op** out);
+/* output (world x len(input) elements) <- every rank's input, in rank order. */
+int32_t wrk_op_all_gather(wrk_comm* comm, wrk_tensor* input, wrk_tensor* output, wrk_op** out);
+
 /* ---- No counterpart in the reference ----
  * y[t][m] = act(W[m][:] . x[t][:]) for an Int8 matrix (the layout quantize_mat_int8 produces: u8 W[m][k], f16
  * (min, max) per 128-weight block), f16 x[t][k], f32 y[t][m], all raw device pointers, launched on `cuda_stream`

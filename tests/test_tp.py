@@ -1,0 +1,57 @@
+"""Tensor-parallel sharding: shard plan (host logic), the sharding rules against the CPU oracle with two gloo
+ranks, and — where two GPUs are present — the sharded v6 job against the single-GPU runtime."""
+import importlib
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+WORKER = os.path.join(ROOT, "tests", "tp_worker.py")
+
+
+def _spawn(mode, world, port):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, WORKER, mode], env=dict(env, RANK=str(r), LOCAL_RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    outs = [p.communicate(timeout=600)[0] for p in procs]
+    for r, (p, out) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, out[-4000:]
+        assert f"ok {r}" in out, out[-4000:]
+    return outs
+
+
+def test_shard_ranges_and_plan():
+    tp = importlib.import_module("web-rwkv_b200.tp")
+    wrk = importlib.import_module("web-rwkv_b200")
+    assert tp.shard_ranges(10, 3) == [(0, 4), (4, 7), (7, 10)]
+    # 8960 FFN columns in NF4 blocks of 64 over 8 ranks: 140 blocks -> 18, 18, 18, 18, 17, 17, 17, 17
+    r = tp.shard_ranges(8960, 8, 64)
+    assert [(b - a) // 64 for a, b in r] == [18, 18, 18, 18, 17, 17, 17, 17] and r[0][0] == 0 and r[-1][1] == 8960
+    assert all(a % 64 == 0 for a, _ in r)
+    with pytest.raises(ValueError):
+        tp.shard_ranges(100, 2, 64)
+    # Int8: a rank's channels are whole 128-column blocks of `output`, i.e. pairs of heads
+    plan = tp.ShardPlan(2048, 7168, 65536, 8, wrk.QUANT_INT8)
+    assert all((b - a) % 128 == 0 for a, b in plan.channels) and plan.channels[-1][1] == 2048
+    assert all((b - a) % 128 == 0 for a, b in plan.ffn) and plan.ffn[-1][1] == 7168
+    assert plan.vocab[3] == (3 * 8192, 4 * 8192)
+    # 12 heads (C = 768) over 8 ranks cannot be cut into pairs of heads
+    with pytest.raises(ValueError):
+        tp.ShardPlan(768, 2688, 65536, 8, wrk.QUANT_INT8)
+    p4 = tp.ShardPlan(768, 2688, 65536, 4, wrk.QUANT_NF4)
+    assert [b - a for a, b in p4.heads] == [3, 3, 3, 3]
+
+
+def test_sharding_rules_two_gloo_ranks_cpu_oracle():
+    _spawn("cpu", 2, 29541)
+
+
+@pytest.mark.gpu
+def test_tensor_parallel_v6_matches_single_gpu():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    outs = _spawn("gpu", 2, 29542)
+    assert "tp logits match" in outs[0]

@@ -16,6 +16,7 @@ OBJ = os.path.join(HERE, "build")
 SOURCES = [
     "context.cpp",
     "ops.cpp",
+    "comm.cpp",
     "kernels/quant.cu",
     "kernels/matmul.cu",
     "kernels/gemm_umma.cu",
@@ -84,7 +85,7 @@ def build(force=False, verbose=False, extra_flags=()):
     if failed:
         raise RuntimeError("nvcc failed")
     if procs or force or not os.path.exists(LIB):
-        cmd = [nvcc, "-shared", "-ccbin", "/usr/bin/g++", "-o", LIB, *objects, "-lcuda"]
+        cmd = [nvcc, "-shared", "-ccbin", "/usr/bin/g++", "-o", LIB, *objects, "-lcuda", "-lnccl"]
         subprocess.run(cmd, check=True)
     return LIB
 

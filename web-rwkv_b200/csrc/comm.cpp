@@ -1,0 +1,125 @@
+// Tensor-parallel plumbing: an NCCL communicator bound to a context's stream and the all-reduce /
+// all-gather ops the sharded layers need.  The ops are deferred like every other op (they can sit in op
+// lists and be captured into CUDA graphs) and run on the context's stream, so they are ordered with the
+// kernels around them.  The reference is single-GPU: nothing here has a counterpart in it.
+#include <nccl.h>
+
+#include <cstring>
+
+#include "common.h"
+
+struct wrk_comm {
+    std::atomic<int> refs{1};
+    wrk_context* ctx = nullptr;
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 1;
+};
+
+namespace {
+
+int32_t nccl_fail(const char* what, ncclResult_t r) {
+    return wrk::set_error(WRK_ERR_NCCL, "%s failed: %s", what, ncclGetErrorString(r));
+}
+
+bool nccl_dtype(int dtype, ncclDataType_t* out) {
+    switch (dtype) {
+        case WRK_F32: *out = ncclFloat32; return true;
+        case WRK_F16: *out = ncclFloat16; return true;
+        case WRK_U8: *out = ncclUint8; return true;
+        case WRK_U32: *out = ncclUint32; return true;
+        default: return false;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t wrk_comm_unique_id(uint8_t id[128]) {
+    WRK_REQUIRE(id, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    static_assert(sizeof(ncclUniqueId) == 128, "the C ABI passes the id as 128 bytes");
+    ncclUniqueId uid;
+    const ncclResult_t r = ncclGetUniqueId(&uid);
+    if (r != ncclSuccess) return nccl_fail("ncclGetUniqueId", r);
+    std::memcpy(id, &uid, sizeof uid);
+    return WRK_OK;
+}
+
+int32_t wrk_comm_create(wrk_context* ctx, const uint8_t id[128], int32_t rank, int32_t world, wrk_comm** out) {
+    WRK_REQUIRE(ctx && id && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(world >= 1 && rank >= 0 && rank < world, WRK_ERR_INVALID_ARGUMENT, "rank %d of %d", rank, world);
+    WRK_CUDA(cudaSetDevice(ctx->device));
+    ncclUniqueId uid;
+    std::memcpy(&uid, id, sizeof uid);
+    ncclComm_t comm = nullptr;
+    const ncclResult_t r = ncclCommInitRank(&comm, world, uid, rank);
+    if (r != ncclSuccess) return nccl_fail("ncclCommInitRank", r);
+    auto c = new wrk_comm();
+    c->ctx = ctx;
+    c->comm = comm;
+    c->rank = rank;
+    c->world = world;
+    *out = c;
+    return WRK_OK;
+}
+
+int32_t wrk_comm_release(wrk_comm* comm) {
+    if (comm == nullptr) return WRK_OK;
+    if (comm->refs.fetch_sub(1) == 1) {
+        if (comm->comm) {
+            cudaSetDevice(comm->ctx->device);
+            cudaStreamSynchronize(comm->ctx->stream);
+            ncclCommDestroy(comm->comm);
+        }
+        delete comm;
+    }
+    return WRK_OK;
+}
+
+int32_t wrk_comm_rank(const wrk_comm* comm, int32_t* rank, int32_t* world) {
+    WRK_REQUIRE(comm && rank && world, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    *rank = comm->rank;
+    *world = comm->world;
+    return WRK_OK;
+}
+
+// x <- sum over ranks of x (in place).
+int32_t wrk_op_all_reduce(wrk_comm* comm, wrk_tensor* x, wrk_op** out) {
+    WRK_REQUIRE(comm && x && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(x->ctx == comm->ctx, WRK_ERR_INVALID_ARGUMENT, "tensor and communicator belong to different contexts");
+    ncclDataType_t dt;
+    WRK_REQUIRE(x->dtype != WRK_U8 && x->dtype != WRK_U32 && nccl_dtype(x->dtype, &dt), WRK_ERR_TYPE,
+                "data type mismatch: all_reduce sums f16 or f32");
+    void* ptr = x->ptr();
+    const size_t count = x->len();
+    ncclComm_t c = comm->comm;
+    *out = wrk::new_atom("all_reduce",
+                         [=](cudaStream_t s) {
+                             return ncclAllReduce(ptr, ptr, count, dt, ncclSum, c, s) == ncclSuccess ? cudaSuccess : cudaErrorUnknown;
+                         },
+                         {x});
+    return WRK_OK;
+}
+
+// output[rank r's slot] <- input of rank r, for every r: output holds world * len(input) elements.
+int32_t wrk_op_all_gather(wrk_comm* comm, wrk_tensor* input, wrk_tensor* output, wrk_op** out) {
+    WRK_REQUIRE(comm && input && output && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(input->ctx == comm->ctx && output->ctx == comm->ctx, WRK_ERR_INVALID_ARGUMENT,
+                "tensors and communicator belong to different contexts");
+    ncclDataType_t dt;
+    WRK_REQUIRE(nccl_dtype(input->dtype, &dt) && output->dtype == input->dtype, WRK_ERR_TYPE, "data type mismatch");
+    WRK_REQUIRE(output->len() == input->len() * (size_t)comm->world, WRK_ERR_SIZE, "all_gather output holds %zu elements, expected %zu",
+                output->len(), input->len() * (size_t)comm->world);
+    const void* src = input->ptr();
+    void* dst = output->ptr();
+    const size_t count = input->len();
+    ncclComm_t c = comm->comm;
+    *out = wrk::new_atom("all_gather",
+                         [=](cudaStream_t s) {
+                             return ncclAllGather(src, dst, count, dt, c, s) == ncclSuccess ? cudaSuccess : cudaErrorUnknown;
+                         },
+                         {input, output});
+    return WRK_OK;
+}
+
+}  // extern "C"
