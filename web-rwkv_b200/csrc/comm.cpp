@@ -2,11 +2,44 @@
 // all-gather ops the sharded layers need.  The ops are deferred like every other op (they can sit in op
 // lists and be captured into CUDA graphs) and run on the context's stream, so they are ordered with the
 // kernels around them.  The reference is single-GPU: nothing here has a counterpart in it.
+#include <dlfcn.h>
 #include <nccl.h>
 
 #include <cstring>
 
 #include "common.h"
+
+// NCCL is bound at first use, not at link time: a process that never shards does not load it, and one that
+// has already loaded an NCCL (e.g. through torch.distributed) keeps using that single copy.
+namespace {
+struct NcclApi {
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+    bool ok = false;
+};
+
+const NcclApi& nccl() {
+    static NcclApi api = [] {
+        NcclApi a;
+        void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (h == nullptr) return a;
+        a.GetUniqueId = reinterpret_cast<decltype(a.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
+        a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
+        a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
+        a.AllReduce = reinterpret_cast<decltype(a.AllReduce)>(dlsym(h, "ncclAllReduce"));
+        a.AllGather = reinterpret_cast<decltype(a.AllGather)>(dlsym(h, "ncclAllGather"));
+        a.GetErrorString = reinterpret_cast<decltype(a.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
+        a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllReduce && a.AllGather && a.GetErrorString;
+        return a;
+    }();
+    return api;
+}
+}  // namespace
+#define WRK_NEED_NCCL() WRK_REQUIRE(nccl().ok, WRK_ERR_NCCL, "libnccl.so.2 could not be loaded")
 
 struct wrk_comm {
     std::atomic<int> refs{1};
@@ -18,7 +51,7 @@ struct wrk_comm {
 namespace {
 
 int32_t nccl_fail(const char* what, ncclResult_t r) {
-    return wrk::set_error(WRK_ERR_NCCL, "%s failed: %s", what, ncclGetErrorString(r));
+    return wrk::set_error(WRK_ERR_NCCL, "%s failed: %s", what, nccl().GetErrorString(r));
 }
 
 bool nccl_dtype(int dtype, ncclDataType_t* out) {
@@ -38,8 +71,9 @@ extern "C" {
 int32_t wrk_comm_unique_id(uint8_t id[128]) {
     WRK_REQUIRE(id, WRK_ERR_INVALID_ARGUMENT, "null argument");
     static_assert(sizeof(ncclUniqueId) == 128, "the C ABI passes the id as 128 bytes");
+    WRK_NEED_NCCL();
     ncclUniqueId uid;
-    const ncclResult_t r = ncclGetUniqueId(&uid);
+    const ncclResult_t r = nccl().GetUniqueId(&uid);
     if (r != ncclSuccess) return nccl_fail("ncclGetUniqueId", r);
     std::memcpy(id, &uid, sizeof uid);
     return WRK_OK;
@@ -48,11 +82,12 @@ int32_t wrk_comm_unique_id(uint8_t id[128]) {
 int32_t wrk_comm_create(wrk_context* ctx, const uint8_t id[128], int32_t rank, int32_t world, wrk_comm** out) {
     WRK_REQUIRE(ctx && id && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
     WRK_REQUIRE(world >= 1 && rank >= 0 && rank < world, WRK_ERR_INVALID_ARGUMENT, "rank %d of %d", rank, world);
+    WRK_NEED_NCCL();
     WRK_CUDA(cudaSetDevice(ctx->device));
     ncclUniqueId uid;
     std::memcpy(&uid, id, sizeof uid);
     ncclComm_t comm = nullptr;
-    const ncclResult_t r = ncclCommInitRank(&comm, world, uid, rank);
+    const ncclResult_t r = nccl().CommInitRank(&comm, world, uid, rank);
     if (r != ncclSuccess) return nccl_fail("ncclCommInitRank", r);
     auto c = new wrk_comm();
     c->ctx = ctx;
@@ -69,7 +104,7 @@ int32_t wrk_comm_release(wrk_comm* comm) {
         if (comm->comm) {
             cudaSetDevice(comm->ctx->device);
             cudaStreamSynchronize(comm->ctx->stream);
-            ncclCommDestroy(comm->comm);
+            nccl().CommDestroy(comm->comm);
         }
         delete comm;
     }
@@ -95,7 +130,7 @@ int32_t wrk_op_all_reduce(wrk_comm* comm, wrk_tensor* x, wrk_op** out) {
     ncclComm_t c = comm->comm;
     *out = wrk::new_atom("all_reduce",
                          [=](cudaStream_t s) {
-                             return ncclAllReduce(ptr, ptr, count, dt, ncclSum, c, s) == ncclSuccess ? cudaSuccess : cudaErrorUnknown;
+                             return nccl().AllReduce(ptr, ptr, count, dt, ncclSum, c, s) == ncclSuccess ? cudaSuccess : cudaErrorUnknown;
                          },
                          {x});
     return WRK_OK;
@@ -116,7 +151,7 @@ int32_t wrk_op_all_gather(wrk_comm* comm, wrk_tensor* input, wrk_tensor* output,
     ncclComm_t c = comm->comm;
     *out = wrk::new_atom("all_gather",
                          [=](cudaStream_t s) {
-                             return ncclAllGather(src, dst, count, dt, c, s) == ncclSuccess ? cudaSuccess : cudaErrorUnknown;
+                             return nccl().AllGather(src, dst, count, dt, c, s) == ncclSuccess ? cudaSuccess : cudaErrorUnknown;
                          },
                          {input, output});
     return WRK_OK;

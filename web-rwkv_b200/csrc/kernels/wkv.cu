@@ -45,23 +45,26 @@ __device__ __forceinline__ bool find_run(const uint32_t* cursors, int wide, uint
     return count != 0;
 }
 
-template <int S>
-__global__ void __launch_bounds__(S) time_mix_v56_kernel(const WkvArgs a) {
-    __shared__ float sk[2][S], sr[2][S], sw[2][S], su[S];
+// One CTA of Q * S threads per (head, batch slot): thread (q, j) keeps rows [q S/Q, (q+1) S/Q) of state
+// column j in registers for the sequence's whole run of tokens and adds its part of output j; the Q parts
+// meet in shared memory (one barrier per token, buffers alternate).
+template <int S, int Q>
+__global__ void __launch_bounds__(S * Q) time_mix_v56_kernel(const WkvArgs a) {
+    constexpr int SI = S / Q;
+    __shared__ float sk[2][S], sr[2][S], sw[2][S], su[S], part[2][Q][S];
     __shared__ uint32_t s_start, s_count;
-    const uint32_t h = blockIdx.x, slot = blockIdx.y, j = threadIdx.x;
+    const uint32_t h = blockIdx.x, slot = blockIdx.y, j = threadIdx.x % S, q = threadIdx.x / S;
     const uint32_t C = a.S * a.H, c = h * S + j;
 
     uint32_t start, count;
     if (!find_run(a.cursors, a.wide, a.T, slot, &s_start, &s_count, start, count)) return;
 
-    float st[S];
+    float st[SI];
 #pragma unroll
-    for (int i = 0; i < S; ++i) st[i] = static_cast<const float*>(a.state.base)[a.state.index(c, 1 + i, slot)];
-    su[j] = a.time_first[c];
-    if (!a.per_token_decay) sw[0][j] = sw[1][j] = a.time_decay[c];
-
-    {
+    for (int i = 0; i < SI; ++i) st[i] = static_cast<const float*>(a.state.base)[a.state.index(c, 1 + q * SI + i, slot)];
+    if (q == 0) {
+        su[j] = a.time_first[c];
+        if (!a.per_token_decay) sw[0][j] = sw[1][j] = a.time_decay[c];
         const size_t ti = (size_t)start * C + c;
         sk[0][j] = dload(a.k, a.dtype, ti);
         sr[0][j] = dload(a.r, a.dtype, ti);
@@ -74,37 +77,44 @@ __global__ void __launch_bounds__(S) time_mix_v56_kernel(const WkvArgs a) {
         const int cur = n & 1, nxt = cur ^ 1;
         const size_t ti = (size_t)t * C + c;
         // next token's shared vectors: issue the loads before this token's math
-        float nk = 0.f, nr = 0.f, nw = 0.f;
+        float nk = 0.f, nr = 0.f, nw = 0.f, xin = 0.f;
         const bool more = n + 1 < count;
-        if (more) {
-            nk = dload(a.k, a.dtype, ti + C);
-            nr = dload(a.r, a.dtype, ti + C);
-            if (a.per_token_decay) nw = a.time_decay[ti + C];
+        if (q == 0) {
+            if (more) {
+                nk = dload(a.k, a.dtype, ti + C);
+                nr = dload(a.r, a.dtype, ti + C);
+                if (a.per_token_decay) nw = a.time_decay[ti + C];
+            }
+            xin = dload(a.x, a.dtype, ti);
         }
         const float vj = dload(a.v, a.dtype, ti);
-        const float xin = dload(a.x, a.dtype, ti);
-        float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+        float y0 = 0.f, y1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < S; i += 4) {
+        for (int ii = 0; ii < SI; ii += 2) {
+            const int i = q * SI + ii;
             float kv;
-            kv = sk[cur][i] * vj;     y0 += sr[cur][i] * fmaf(su[i], kv, st[i]);         st[i] = fmaf(sw[cur][i], st[i], kv);
-            kv = sk[cur][i + 1] * vj; y1 += sr[cur][i + 1] * fmaf(su[i + 1], kv, st[i + 1]); st[i + 1] = fmaf(sw[cur][i + 1], st[i + 1], kv);
-            kv = sk[cur][i + 2] * vj; y2 += sr[cur][i + 2] * fmaf(su[i + 2], kv, st[i + 2]); st[i + 2] = fmaf(sw[cur][i + 2], st[i + 2], kv);
-            kv = sk[cur][i + 3] * vj; y3 += sr[cur][i + 3] * fmaf(su[i + 3], kv, st[i + 3]); st[i + 3] = fmaf(sw[cur][i + 3], st[i + 3], kv);
+            kv = sk[cur][i] * vj;     y0 += sr[cur][i] * fmaf(su[i], kv, st[ii]);             st[ii] = fmaf(sw[cur][i], st[ii], kv);
+            kv = sk[cur][i + 1] * vj; y1 += sr[cur][i + 1] * fmaf(su[i + 1], kv, st[ii + 1]); st[ii + 1] = fmaf(sw[cur][i + 1], st[ii + 1], kv);
         }
-        const CursorD cu = cursor_at(a.cursors, a.wide, t);
-        if (t - cu.token + 1u == cu.len)  // last token of the run: token-shift carry takes the layer input
-            static_cast<float*>(a.state.base)[a.state.index(c, 0, slot)] = xin;
-        dstore(a.x, a.dtype, ti, (y0 + y1) + (y2 + y3));
-        if (more) {
+        part[cur][q][j] = y0 + y1;
+        if (q == 0 && more) {
             sk[nxt][j] = nk;
             sr[nxt][j] = nr;
             if (a.per_token_decay) sw[nxt][j] = nw;
         }
         __syncthreads();
+        if (q == 0) {
+            float y = part[cur][0][j];
+#pragma unroll
+            for (int p2 = 1; p2 < Q; ++p2) y += part[cur][p2][j];
+            const CursorD cu = cursor_at(a.cursors, a.wide, t);
+            if (t - cu.token + 1u == cu.len)  // last token of the run: token-shift carry takes the layer input
+                static_cast<float*>(a.state.base)[a.state.index(c, 0, slot)] = xin;
+            dstore(a.x, a.dtype, ti, y);
+        }
     }
 #pragma unroll
-    for (int i = 0; i < S; ++i) static_cast<float*>(a.state.base)[a.state.index(c, 1 + i, slot)] = st[i];
+    for (int i = 0; i < SI; ++i) static_cast<float*>(a.state.base)[a.state.index(c, 1 + q * SI + i, slot)] = st[i];
 }
 
 template <int S>
@@ -209,9 +219,9 @@ cudaError_t time_mix_v56(const WkvArgs& a, cudaStream_t stream) {
     if (a.T == 0 || a.B == 0) return cudaSuccess;
     dim3 grid(a.H, a.B);
     switch (a.S) {
-        case 32: time_mix_v56_kernel<32><<<grid, 32, 0, stream>>>(a); break;
-        case 64: time_mix_v56_kernel<64><<<grid, 64, 0, stream>>>(a); break;
-        case 128: time_mix_v56_kernel<128><<<grid, 128, 0, stream>>>(a); break;
+        case 32: time_mix_v56_kernel<32, 4><<<grid, 128, 0, stream>>>(a); break;
+        case 64: time_mix_v56_kernel<64, 4><<<grid, 256, 0, stream>>>(a); break;
+        case 128: time_mix_v56_kernel<128, 4><<<grid, 512, 0, stream>>>(a); break;
         default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();
