@@ -12,10 +12,21 @@ WORKER = os.path.join(ROOT, "tests", "tp_worker.py")
 
 
 def _spawn(mode, world, port):
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0")
+    # loopback for every rendezvous (the host name of a container need not resolve); no NVLS: a rank that
+    # dies must not leave peers' memory bound to a multicast object
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0",
+               GLOO_SOCKET_IFNAME="lo", NCCL_SOCKET_IFNAME="lo")
     procs = [subprocess.Popen([sys.executable, WORKER, mode], env=dict(env, RANK=str(r), LOCAL_RANK=str(r)),
                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
-    outs = [p.communicate(timeout=600)[0] for p in procs]
+    outs = []
+    for p in procs:
+        try:
+            outs.append(p.communicate(timeout=180)[0])
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            outs.append(p.communicate()[0])
+            raise AssertionError("rank timed out:\n" + "\n".join(outs)[-4000:])
     for r, (p, out) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, out[-4000:]
         assert f"ok {r}" in out, out[-4000:]

@@ -21,8 +21,11 @@ def main():
     import torch
     import torch.distributed as dist
 
-    dist.init_process_group("gloo")
+    import datetime
+    dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=120))
     rank, world = dist.get_rank(), dist.get_world_size()
+    say = lambda *a: print(f"[rank {rank}]", *a, flush=True)
+    say("process group up")
     wrk = importlib.import_module("web-rwkv_b200")
     tp = importlib.import_module("web-rwkv_b200.tp")
     synth = importlib.import_module("web-rwkv_b200.synth")
@@ -83,13 +86,19 @@ def main():
     ctx = wrk.Context(rank)
     uid = [tp.Comm.unique_id() if rank == 0 else None]
     dist.broadcast_object_list(uid, src=0)
+    say("unique id exchanged")
     comm = tp.Comm(ctx, uid[0], rank, world)
+    say("communicator up")
     model = tp.TpModelV6(ctx, comm, tensors, quant=quant, num_batch=2)
+    say("model sharded")
     rng = np.random.default_rng(5)
     V = tensors["emb.weight"].shape[0]
     steps = [[rng.integers(0, V - 1, 5).tolist(), rng.integers(0, V - 1, 3).tolist()]]      # prompt, two sequences
     steps += [[[int(rng.integers(0, V - 1))], [int(rng.integers(0, V - 1))]] for _ in range(3)]  # three decode steps
-    outs = [model.run(s) for s in steps]
+    outs = []
+    for s in steps:
+        outs.append(model.run(s))
+        say("job done", [len(t) for t in s])
     assert ctx.device_status() == 0
     if rank == 0:
         b = rt.ModelBuilder(ctx)
