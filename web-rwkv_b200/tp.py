@@ -110,6 +110,13 @@ class Comm:
         self.handle = ctypes.c_void_p()
         buf = (ctypes.c_uint8 * 128).from_buffer_copy(bytes(unique_id))
         check(lib().wrk_comm_create(ctx.handle, buf, rank, world, ctypes.byref(self.handle)))
+        # NCCL sets up its transports at the first collective of each kind (allocations, handle exchange): do
+        # that here, eagerly, so that no later collective has to do it inside a stream capture
+        a = ctx.tensor(F32, [1024], zeros=True)
+        g = ctx.tensor(F32, [1024, world], zeros=True)
+        ctx.run(self.all_reduce(a))
+        ctx.run(self.all_gather(a, g))
+        ctx.synchronize()
 
     @staticmethod
     def unique_id():
@@ -136,8 +143,9 @@ class Comm:
 class TpModelV6:
     """One rank of a tensor-parallel v6 model: sharded weights, state, and the op list of a job."""
 
-    def __init__(self, ctx, comm, tensors, quant=QUANT_NONE, num_batch=1, rescale=6):
+    def __init__(self, ctx, comm, tensors, quant=QUANT_NONE, num_batch=1, rescale=6, use_graph=False):
         self.ctx, self.comm, self.quant, self.num_batch, self.rescale = ctx, comm, quant, num_batch, rescale
+        self.use_graph = use_graph  # capture a job's launches (collectives included) into a CUDA graph
         V, C = tensors["emb.weight"].shape
         F = tensors["blocks.0.ffn.key.weight"].shape[0]
         self.plan = plan = ShardPlan(C, F, V, comm.world, quant)
@@ -256,7 +264,7 @@ class TpModelV6:
         ops += [layer_norm(*self.ln_out, B["head_x"], LN_EPS),
                 self.head.matmul_op(B["head_x"], B["logits"], ACT_NONE, len(last) % 32 == 0),
                 self.comm.all_gather(B["logits"], B["all_logits"])]
-        cmd = ctx.encode(op_list(ops), use_graph=True)
+        cmd = ctx.encode(op_list(ops), use_graph=self.use_graph)
         return cmd, B, last, ops
 
     def run(self, tokens):
