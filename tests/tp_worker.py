@@ -100,6 +100,13 @@ def main():
         outs.append(model.run(s))
         say("job done", [len(t) for t in s])
     assert ctx.device_status() == 0
+    # the same jobs captured into CUDA graphs (collectives included) must give the same logits
+    graphed = tp.TpModelV6(ctx, comm, tensors, quant=quant, num_batch=2, use_graph=True)
+    for s, want in zip(steps, outs):
+        got = graphed.run(s)
+        for bi in want:
+            assert np.allclose(got[bi], want[bi], rtol=1e-5, atol=1e-5), "graph-captured job differs"
+    say("graph-captured jobs match")
     if rank == 0:
         b = rt.ModelBuilder(ctx)
         b.add_tensors(tensors)
@@ -122,6 +129,13 @@ def main():
         print("tp logits match the single-GPU runtime, worst max-abs", worst, flush=True)
     dist.barrier()
     print("ok", rank, flush=True)
+    # orderly teardown: graphs and models before the communicator, the communicator before the context
+    del graphed, model, outs
+    import gc
+    gc.collect()
+    del comm
+    gc.collect()
+    dist.destroy_process_group()
 
 
 if __name__ == "__main__":

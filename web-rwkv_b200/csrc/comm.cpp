@@ -15,7 +15,7 @@ namespace {
 struct NcclApi {
     ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
-    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
     ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
@@ -29,11 +29,11 @@ const NcclApi& nccl() {
         if (h == nullptr) return a;
         a.GetUniqueId = reinterpret_cast<decltype(a.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
         a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
-        a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
+        a.CommAbort = reinterpret_cast<decltype(a.CommAbort)>(dlsym(h, "ncclCommAbort"));
         a.AllReduce = reinterpret_cast<decltype(a.AllReduce)>(dlsym(h, "ncclAllReduce"));
         a.AllGather = reinterpret_cast<decltype(a.AllGather)>(dlsym(h, "ncclAllGather"));
         a.GetErrorString = reinterpret_cast<decltype(a.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
-        a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllReduce && a.AllGather && a.GetErrorString;
+        a.ok = a.GetUniqueId && a.CommInitRank && a.CommAbort && a.AllReduce && a.AllGather && a.GetErrorString;
         return a;
     }();
     return api;
@@ -104,7 +104,9 @@ int32_t wrk_comm_release(wrk_comm* comm) {
         if (comm->comm) {
             cudaSetDevice(comm->ctx->device);
             cudaStreamSynchronize(comm->ctx->stream);
-            nccl().CommDestroy(comm->comm);
+            // local teardown: it does not wait for the other ranks (which may already be gone) nor for
+            // CUDA graphs that still hold this communicator's kernels
+            nccl().CommAbort(comm->comm);
         }
         delete comm;
     }
