@@ -5,16 +5,15 @@
 // around never letting the stream of weights stop:
 //   * fused_gemv_kernel is a grouped weight-streaming kernel.  A launch covers several matrices (e.g.
 //     key / value / receptance / gate + the decay adapter); the concatenated row space is cut into one
-//     contiguous row range per CTA (balanced by bytes, one CTA per SM; the SM's second CTA slot is left to
-//     the next launch).  A CTA walks its rows in MMA row tiles of 16; its 16 warps split a tile's 128-byte
+//     contiguous row range per CTA (balanced by bytes, one CTA per SM).  A CTA walks its rows in MMA row tiles of 16; its 16 warps split a tile's 128-byte
 //     chunks and each streams its own items through a private ring in shared memory with cp.async.
 //     (A variant that re-laid the weights per CTA at load time and fetched 34 KB stages with one
 //     cp.async.bulk each was measured: faster alone, slower inside the model, twice the weight memory;
 //     it is not kept.)
 //   * every kernel here is launched with programmatic dependent launch: it signals its dependents at
 //     once, issues the copies of its first weight items, and only then executes griddepcontrol.wait.
-//     Weights are never written during a job, so the next kernel's weights are already landing in shared
-//     memory while the previous kernel is still finishing.
+//     Weights are never written during a job, so a CTA that becomes resident while the previous kernel is
+//     still draining already has its first weights landing in shared memory.
 //   * layer norm + token shift run as a per-CTA prologue (every CTA recomputes the few-KB vector instead
 //     of a separate launch and a grid-wide dependency); residual add, squared ReLU, channel mix and the
 //     carry-row updates run as epilogues.
@@ -110,7 +109,7 @@ struct Segs {
 // lane copies exactly the 16-byte pieces it will later feed to the MMA into its own slots, so reading them
 // back is conflict free; the block scales of the item's 16 rows are copied once per row (by the lanes
 // t4 = 0 / 2 for Int8, all four for NF4) and read after a warp barrier.
-constexpr int kMinRing = 2, kMaxRing = 4;          // items in flight per warp (chosen per launch)
+constexpr int kMinRing = 2, kMaxRing = 5;          // items in flight per warp (chosen per launch)
 constexpr int CELL_DATA = 32 * 4 * 16;             // per lane: four 16-byte pieces
 constexpr int CELL_BYTES = CELL_DATA + 16 * 8;     // + 8 bytes of block scales per row
 
@@ -134,7 +133,9 @@ __device__ __forceinline__ void cp_async_wait_dyn(int n) {
     if (n <= 1) cp_async_wait<1>();
     else if (n == 2) cp_async_wait<2>();
     else if (n == 3) cp_async_wait<3>();
-    else cp_async_wait<4>();
+    else if (n == 4) cp_async_wait<4>();
+    else if (n == 5) cp_async_wait<5>();
+    else cp_async_wait<6>();
 }
 
 // Work mapping inside a CTA: its row ranges are walked in MMA row tiles of 16 rows; the 16 warps split a
@@ -511,8 +512,11 @@ __device__ __forceinline__ void consume_item(const GemvProblem& p, const Item& i
     }
 }
 
+// One CTA per SM: the kernel then has 128 registers per thread (under a 64-register cap it spills inside the
+// item loop) and room for a deep ring; measured, that is worth far more than letting the next launch's CTAs
+// become resident early to prefetch (727 -> 932 tokens/s on the 1.6B-shaped bench model).
 #ifndef WRK_GEMV_MIN_CTAS
-#define WRK_GEMV_MIN_CTAS 2
+#define WRK_GEMV_MIN_CTAS 1
 #endif
 template <int PRO, int EPI>
 __global__ void __launch_bounds__(kThreads, WRK_GEMV_MIN_CTAS) fused_gemv_kernel(const FusedGemvArgs a) {
@@ -1014,9 +1018,8 @@ size_t fused_gemv_smem(uint32_t T, uint32_t Kmax, uint32_t C, int prologue, int 
 
 namespace {
 
-// Two CTAs fit on an SM while each stays below this (228 KB per SM, 1 KB reserved per CTA): the next launch's
-// CTAs then start fetching weights beside the running ones.
-constexpr size_t kCoResidentSmem = 113 * 1024;
+// Dynamic shared memory a launch may ask for (the ring takes what the activations leave).
+constexpr size_t kMaxGemvSmem = 200 * 1024;
 
 // Fills the launch-derived fields (largest K, ring depth) and returns the dynamic shared memory size.
 size_t fused_gemv_prepare(FusedGemvArgs& a) {
@@ -1024,7 +1027,7 @@ size_t fused_gemv_prepare(FusedGemvArgs& a) {
     for (int i = 0; i < a.num_problems; ++i) kmax = std::max(kmax, a.p[i].K);
     a.kmax = kmax;
     int depth = kMaxRing;
-    while (depth > kMinRing && fused_gemv_smem(a.T, kmax, a.C, a.prologue, depth) > kCoResidentSmem) --depth;
+    while (depth > kMinRing && fused_gemv_smem(a.T, kmax, a.C, a.prologue, depth) > kMaxGemvSmem) --depth;
     a.ring_depth = depth;
     return fused_gemv_smem(a.T, kmax, a.C, a.prologue, depth);
 }
