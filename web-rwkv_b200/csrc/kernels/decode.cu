@@ -427,15 +427,15 @@ __device__ __forceinline__ void epilogue_one(const FusedGemvArgs& a, const GemvP
 }
 
 // Multiplies one work item with the staged activations: out[0..3] = rows g / g + 8 x tokens 2 t4 / 2 t4 + 1.
-// The k-steps of an item alternate between two independent accumulators.
+// The four k-steps of an Int8 item go to four independent accumulators (chains of two MMAs).
 __device__ __forceinline__ void consume_item(const GemvProblem& p, const Item& it, int c, const __half* xrow, bool xval,
                                              const float* sums, uint32_t T, int t4, const __half* lut, float out[4]) {
     if (p.kind == MAT_INT8) {
         const uint32_t wa[8] = {it.q[0].x, it.q[0].y, it.q[0].z, it.q[0].w, it.q[1].x, it.q[1].y, it.q[1].z, it.q[1].w};
         const uint32_t wb[8] = {it.q[2].x, it.q[2].y, it.q[2].z, it.q[2].w, it.q[3].x, it.q[3].y, it.q[3].z, it.q[3].w};
-        float d[2][4];
+        float d[4][4];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) d[i][0] = d[i][1] = d[i][2] = d[i][3] = 0.f;
+        for (int i = 0; i < 4; ++i) d[i][0] = d[i][1] = d[i][2] = d[i][3] = 0.f;
 #pragma unroll
         for (int s2 = 0; s2 < 4; ++s2) {
             const uint32_t kk = c * 128 + (s2 < 2 ? 16 * t4 + 8 * s2 : 64 + 16 * t4 + 8 * (s2 - 2));
@@ -445,7 +445,7 @@ __device__ __forceinline__ void consume_item(const GemvProblem& p, const Item& i
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const uint32_t ua = wa[2 * s2 + h], ub = wb[2 * s2 + h];
-                mma16816(d[s2 & 1], __byte_perm(ua, 0x64646464u, 0x4140), __byte_perm(ub, 0x64646464u, 0x4140),
+                mma16816(d[s2], __byte_perm(ua, 0x64646464u, 0x4140), __byte_perm(ub, 0x64646464u, 0x4140),
                          __byte_perm(ua, 0x64646464u, 0x4342), __byte_perm(ub, 0x64646464u, 0x4342), h == 0 ? xq.x : xq.z,
                          h == 0 ? xq.y : xq.w);
             }
@@ -457,10 +457,10 @@ __device__ __forceinline__ void consume_item(const GemvProblem& p, const Item& i
         const float s0 = tk0 < T ? sums[tk0 * nblk + c] : 0.f, s1 = tk1 < T ? sums[tk1 * nblk + c] : 0.f;
         const float sA = (mmA.y - mmA.x) * (1.0f / 255.0f), sB = (mmB.y - mmB.x) * (1.0f / 255.0f);
         const float oA = mmA.x - 1024.0f * sA, oB = mmB.x - 1024.0f * sB;
-        out[0] = sA * (d[0][0] + d[1][0]) + oA * s0;
-        out[1] = sA * (d[0][1] + d[1][1]) + oA * s1;
-        out[2] = sB * (d[0][2] + d[1][2]) + oB * s0;
-        out[3] = sB * (d[0][3] + d[1][3]) + oB * s1;
+        out[0] = sA * ((d[0][0] + d[1][0]) + (d[2][0] + d[3][0])) + oA * s0;
+        out[1] = sA * ((d[0][1] + d[1][1]) + (d[2][1] + d[3][1])) + oA * s1;
+        out[2] = sB * ((d[0][2] + d[1][2]) + (d[2][2] + d[3][2])) + oB * s0;
+        out[3] = sB * ((d[0][3] + d[1][3]) + (d[2][3] + d[3][3])) + oB * s1;
     } else if (p.kind == MAT_NF4) {
         const uint32_t qa[8] = {it.q[0].x, it.q[0].y, it.q[0].z, it.q[0].w, it.q[1].x, it.q[1].y, it.q[1].z, it.q[1].w};
         const uint32_t qb[8] = {it.q[2].x, it.q[2].y, it.q[2].z, it.q[2].w, it.q[3].x, it.q[3].y, it.q[3].z, it.q[3].w};
@@ -545,7 +545,27 @@ __global__ void __launch_bounds__(kThreads, WRK_GEMV_MIN_CTAS) fused_gemv_kernel
 
     // ---- everything up to the wait touches only weights: each warp fetches its first items ----
     Segs sg;
-    {
+    if (a.inline_partition) {
+        // this CTA's slice of the concatenated row space, cut at the matrices' boundaries
+        const uint32_t g0 = a.cta_row_start[blockIdx.x], g1 = a.cta_row_start[blockIdx.x + 1];
+#pragma unroll
+        for (int i = 0; i < kSegmentsPerCta; ++i) sg.prob[i] = 0, sg.r0[i] = 0, sg.r1[i] = 0;
+        uint32_t base = 0;
+        int n = 0;
+#pragma unroll
+        for (int pi = 0; pi < kMaxProblems; ++pi) {
+            if (pi < a.num_problems) {
+                const uint32_t lo = max(g0, base), hi = min(g1, base + a.p[pi].M);
+                if (lo < hi) {
+                    if (n == 0) sg.prob[0] = pi, sg.r0[0] = (int)(lo - base), sg.r1[0] = (int)(hi - base);
+                    else if (n == 1) sg.prob[1] = pi, sg.r0[1] = (int)(lo - base), sg.r1[1] = (int)(hi - base);
+                    else if (n == 2) sg.prob[2] = pi, sg.r0[2] = (int)(lo - base), sg.r1[2] = (int)(hi - base);
+                    ++n;
+                }
+                base += a.p[pi].M;
+            }
+        }
+    } else {
         const int4* tab = reinterpret_cast<const int4*>(a.segments + (size_t)blockIdx.x * kSegmentsPerCta);
 #pragma unroll
         for (int i = 0; i < kSegmentsPerCta; ++i) {
@@ -1003,6 +1023,21 @@ bool fused_gemv_partition(const FusedGemvArgs& a, int grid, std::vector<GemvSegm
         }
     }
     return prob == a.num_problems;
+}
+
+void fused_gemv_inline_partition(FusedGemvArgs& a, int grid, const std::vector<GemvSegment>& table) {
+    a.inline_partition = 0;
+    if (grid > kInlineCtas) return;
+    uint32_t cur = 0;
+    for (int c = 0; c < grid; ++c) {
+        a.cta_row_start[c] = cur;
+        for (int i = 0; i < kSegmentsPerCta; ++i) {
+            const GemvSegment& sg = table[(size_t)c * kSegmentsPerCta + i];
+            if (sg.row1 > sg.row0) cur += (uint32_t)(sg.row1 - sg.row0);
+        }
+    }
+    a.cta_row_start[grid] = cur;
+    a.inline_partition = 1;
 }
 
 size_t fused_gemv_smem(uint32_t T, uint32_t Kmax, uint32_t C, int prologue, int depth) {

@@ -32,6 +32,7 @@ struct GemvSegment {
     int32_t problem, row0, row1, pad;
 };
 constexpr int kSegmentsPerCta = 3;
+constexpr int kInlineCtas = 192;
 
 struct FusedGemvArgs {
     GemvProblem p[kMaxProblems];
@@ -40,6 +41,11 @@ struct FusedGemvArgs {
     uint32_t kmax;                // largest K of the launch (filled in by fused_gemv)
     uint32_t T;
     const GemvSegment* segments;  // [grid][kSegmentsPerCta], row0 == row1 marks an unused entry
+    // The same partition as boundaries in the concatenated row space of the launch's matrices (filled in by
+    // fused_gemv for grids of at most kInlineCtas): CTA c owns rows [cta_row_start[c], cta_row_start[c + 1]).
+    // Read from the kernel parameters, it spares every CTA a dependent global load before its first copy.
+    int32_t inline_partition;
+    uint32_t cta_row_start[kInlineCtas + 1];
     const float* table;           // NF4 code book (device)
     int32_t* status;
     // prologue: layer norm of `ln_x` (+ token shift against the carry row `state`)
@@ -67,6 +73,8 @@ struct FusedGemvArgs {
 
 cudaError_t fused_gemv(const FusedGemvArgs& a, int grid, cudaStream_t stream);
 bool fused_gemv_partition(const FusedGemvArgs& a, int grid, std::vector<GemvSegment>& table);
+// Copies the partition's boundaries into the launch arguments (grids of at most kInlineCtas).
+void fused_gemv_inline_partition(FusedGemvArgs& a, int grid, const std::vector<GemvSegment>& table);
 // Dynamic shared memory of a launch with `depth` staging cells per warp (clamped to the supported 2 .. 4).
 size_t fused_gemv_smem(uint32_t T, uint32_t Kmax, uint32_t C, int prologue, int depth);
 

@@ -121,6 +121,7 @@ int32_t matmul_common(const char* name, int kind, wrk_tensor* matrix, wrk_tensor
             WRK_TRY(wrk_tensor_from_data(matrix->ctx, WRK_U32, tshape, table.data(),
                                          table.size() * sizeof(k::GemvSegment), &tt));
             f.segments = static_cast<const k::GemvSegment*>(tt->ptr());
+            k::fused_gemv_inline_partition(f, sms, table);
             *out = new_atom(name, [f, sms](cudaStream_t s) { return k::fused_gemv(f, sms, s); },
                             {matrix, scale, quant, input->tensor, output->tensor, tt});
             wrk_tensor_release(tt);  // the atom keeps the buffer alive

@@ -429,6 +429,7 @@ int32_t make_partition(wrk_context* ctx, k::FusedGemvArgs& a, int grid, CachedJo
     WRK_TRY(wrk_tensor_from_data(ctx, WRK_U32, shape, table.data(), table.size() * sizeof(k::GemvSegment), &t));
     job->tables.emplace_back(t);
     a.segments = static_cast<const k::GemvSegment*>(t->ptr());
+    k::fused_gemv_inline_partition(a, grid, table);
     return WRK_OK;
 }
 
