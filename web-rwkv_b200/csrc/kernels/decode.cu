@@ -429,7 +429,7 @@ __device__ __forceinline__ void epilogue_one(const FusedGemvArgs& a, const GemvP
 // Multiplies one work item with the staged activations: out[0..3] = rows g / g + 8 x tokens 2 t4 / 2 t4 + 1.
 // The four k-steps of an Int8 item go to four independent accumulators (chains of two MMAs).
 __device__ __forceinline__ void consume_item(const GemvProblem& p, const Item& it, int c, const __half* xrow, bool xval,
-                                             const float* sums, uint32_t T, int t4, const __half* lut, float out[4]) {
+                                             const float* sums, uint32_t T, int t4, const uint32_t* lut2, float out[4]) {
     if (p.kind == MAT_INT8) {
         const uint32_t wa[8] = {it.q[0].x, it.q[0].y, it.q[0].z, it.q[0].w, it.q[1].x, it.q[1].y, it.q[1].z, it.q[1].w};
         const uint32_t wb[8] = {it.q[2].x, it.q[2].y, it.q[2].z, it.q[2].w, it.q[3].x, it.q[3].y, it.q[3].z, it.q[3].w};
@@ -479,13 +479,9 @@ __device__ __forceinline__ void consume_item(const GemvProblem& p, const Item& i
                     xq = *reinterpret_cast<const uint4*>(xrow + c * 256 + j * 64 + 16 * t4 + 8 * s2);
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
+                    // a byte holds two consecutive weights: one lookup gives both as a half2
                     const uint32_t ua = qa[2 * j + s2] >> (16 * h), ub = qb[2 * j + s2] >> (16 * h);
-                    const __half2 a0 = __halves2half2(lut[ua & 15u], lut[(ua >> 4) & 15u]);
-                    const __half2 a2 = __halves2half2(lut[(ua >> 8) & 15u], lut[(ua >> 12) & 15u]);
-                    const __half2 a1 = __halves2half2(lut[ub & 15u], lut[(ub >> 4) & 15u]);
-                    const __half2 a3 = __halves2half2(lut[(ub >> 8) & 15u], lut[(ub >> 12) & 15u]);
-                    mma16816(d, *reinterpret_cast<const uint32_t*>(&a0), *reinterpret_cast<const uint32_t*>(&a1),
-                             *reinterpret_cast<const uint32_t*>(&a2), *reinterpret_cast<const uint32_t*>(&a3),
+                    mma16816(d, lut2[ua & 0xffu], lut2[ub & 0xffu], lut2[(ua >> 8) & 0xffu], lut2[(ub >> 8) & 0xffu],
                              h == 0 ? xq.x : xq.z, h == 0 ? xq.y : xq.w);
                 }
             }
@@ -522,7 +518,7 @@ template <int PRO, int EPI>
 __global__ void __launch_bounds__(kThreads, WRK_GEMV_MIN_CTAS) fused_gemv_kernel(const FusedGemvArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float scratch[kWarps];
-    __shared__ __half lut[16];
+    __shared__ uint32_t lut2[256];  // NF4: byte -> half2(table[low nibble], table[high nibble])
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
     const uint32_t T = a.T;
@@ -539,7 +535,10 @@ __global__ void __launch_bounds__(kThreads, WRK_GEMV_MIN_CTAS) fused_gemv_kernel
     const uint32_t pro_rows = PRO == PRO_LN ? T : PRO == PRO_LN_SHIFT1 ? 2 * T : 3 * T;
     __half* pbias = xs + (size_t)pro_rows * xp;                          // layer-norm bias (prologues only)
 
-    if (threadIdx.x < 16 && a.table != nullptr) lut[threadIdx.x] = __float2half_rn(a.table[threadIdx.x]);
+    if (threadIdx.x < 256 && a.table != nullptr) {
+        const __half2 v = __floats2half2_rn(a.table[threadIdx.x & 15], a.table[threadIdx.x >> 4]);
+        lut2[threadIdx.x] = *reinterpret_cast<const uint32_t*>(&v);
+    }
     trace(100);
     pdl_launch_dependents();
 
@@ -699,7 +698,7 @@ __global__ void __launch_bounds__(kThreads, WRK_GEMV_MIN_CTAS) fused_gemv_kernel
                     if (++cs_slot == depth) cs_slot = 0;
                     WRK_CLK(3);
                     float out[4];
-                    consume_item(p, it, c, xrow, xval, sums, T, t4, lut, out);
+                    consume_item(p, it, c, xrow, xval, sums, T, t4, lut2, out);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) acc[e] += out[e];
                     WRK_CLK(4);
@@ -986,7 +985,8 @@ cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaSt
 }  // namespace
 
 // Cuts the concatenated rows of the launch's matrices into one contiguous range per CTA, balanced by
-// weight bytes.  Returns false when a CTA would need more than kSegmentsPerCta ranges.
+// weight bytes (a single matrix: a running byte count; several: whole CTAs per matrix).  Returns false when a
+// CTA would need more than kSegmentsPerCta ranges.
 bool fused_gemv_partition(const FusedGemvArgs& a, int grid, std::vector<GemvSegment>& table) {
     table.assign((size_t)grid * kSegmentsPerCta, GemvSegment{0, 0, 0, 0});
     double total = 0;
@@ -995,6 +995,52 @@ bool fused_gemv_partition(const FusedGemvArgs& a, int grid, std::vector<GemvSegm
         const GemvProblem& p = a.p[i];
         cost[i] = p.kind == MAT_FP16 ? p.K * 2.0 : p.kind == MAT_INT8 ? p.K * 1.03125 : p.K * 0.53125;
         total += cost[i] * p.M;
+    }
+    if (a.num_problems > 1 && a.num_problems <= grid) {
+        // Several matrices: every matrix gets a whole number of CTAs in proportion to its bytes (largest
+        // remainders first, at least one each) and splits its rows evenly among them.  No CTA then crosses a
+        // matrix boundary: a crossing CTA re-stages its activations mid-way and ends up with an extra partial
+        // tile, which made it finish microseconds after the others.
+        std::vector<int> n(a.num_problems, 1);
+        std::vector<double> share(a.num_problems);
+        int used = a.num_problems;
+        for (int i = 0; i < a.num_problems; ++i) {
+            share[i] = cost[i] * a.p[i].M / total * grid;
+            const int extra = std::max(0, (int)std::floor(share[i]) - 1);
+            n[i] += extra;
+            used += extra;
+        }
+        while (used < grid) {  // hand out the remaining CTAs by largest load per CTA
+            int best = 0;
+            double worst = -1;
+            for (int i = 0; i < a.num_problems; ++i) {
+                const double load = cost[i] * a.p[i].M / n[i];
+                if (load > worst && (uint32_t)n[i] < a.p[i].M) worst = load, best = i;
+            }
+            ++n[best];
+            ++used;
+        }
+        while (used > grid) {  // more minimum CTAs than the proportional split: take from the lightest loads
+            int best = -1;
+            double lightest = 1e300;
+            for (int i = 0; i < a.num_problems; ++i) {
+                const double load = cost[i] * a.p[i].M / n[i];
+                if (n[i] > 1 && load < lightest) lightest = load, best = i;
+            }
+            if (best < 0) break;
+            --n[best];
+            --used;
+        }
+        if (used == grid) {
+            int c = 0;
+            for (int i = 0; i < a.num_problems; ++i)
+                for (int j = 0; j < n[i]; ++j, ++c) {
+                    const int32_t r0 = (int32_t)((uint64_t)a.p[i].M * j / n[i]), r1 = (int32_t)((uint64_t)a.p[i].M * (j + 1) / n[i]);
+                    table[(size_t)c * kSegmentsPerCta] = GemvSegment{i, r0, r1, 0};
+                }
+            return true;
+        }
+        table.assign((size_t)grid * kSegmentsPerCta, GemvSegment{0, 0, 0, 0});
     }
     int prob = 0;
     uint32_t row = 0;
