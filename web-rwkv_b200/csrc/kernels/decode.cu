@@ -228,9 +228,10 @@ __device__ __forceinline__ Item read_item(const uint8_t* cell, int lane) {
     return it;
 }
 
+// Sum over the CTA.  One barrier: the caller alternates between two scratch arrays, so the readers of one
+// use are past a barrier before the array is written again.
 __device__ __forceinline__ float block_sum_256(float v, float* scratch) {
     v = warp_sum(v);
-    __syncthreads();
     if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
     __syncthreads();
     float s = 0.f;
@@ -302,7 +303,7 @@ __device__ void run_prologue(const FusedGemvArgs& a, __half* xgen, uint32_t xp, 
                         prev1[q][e] = static_cast<const float*>(a.state.base)[a.state.index(gi * 8 + e, 0, cu0.batch)];
             }
         }
-        const float mean = block_sum_256(s, scratch) / (float)C;
+        const float mean = block_sum_256(s, scratch) / (float)C;  // scratch: [2][kWarps]
         float m2 = 0.f;
 #pragma unroll
         for (int q = 0; q < kLnVec; ++q)
@@ -312,7 +313,7 @@ __device__ void run_prologue(const FusedGemvArgs& a, __half* xgen, uint32_t xp, 
                     const float d = v[q][e] - mean;
                     m2 += d * d;
                 }
-        const float dev = rsqrtf(block_sum_256(m2, scratch) / (float)C + a.ln_eps);
+        const float dev = rsqrtf(block_sum_256(m2, scratch + kWarps) / (float)C + a.ln_eps);
 #pragma unroll
         for (int q = 0; q < kLnVec; ++q) {
             const uint32_t gi = threadIdx.x + q * kThreads;
@@ -517,7 +518,7 @@ __device__ __forceinline__ void consume_item(const GemvProblem& p, const Item& i
 template <int PRO, int EPI>
 __global__ void __launch_bounds__(kThreads, WRK_GEMV_MIN_CTAS) fused_gemv_kernel(const FusedGemvArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ float scratch[kWarps];
+    __shared__ float scratch[2 * kWarps];
     __shared__ uint32_t lut2[256];  // NF4: byte -> half2(table[low nibble], table[high nibble])
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
@@ -628,26 +629,40 @@ __global__ void __launch_bounds__(kThreads, WRK_GEMV_MIN_CTAS) fused_gemv_kernel
             __syncthreads();
             if (p.x != nullptr) {
                 const uint32_t groups = p.K / 8, total = T * groups;
-                for (uint32_t i0 = 0; i0 < total; i0 += kThreads) {
-                    const uint32_t i = i0 + threadIdx.x;
-                    float sum = 0.f;
-                    uint32_t tok = 0, k8 = 0;
-                    if (i < total) {
-                        tok = i / groups;
-                        k8 = i - tok * groups;
-                        const uint4 raw = *reinterpret_cast<const uint4*>(p.x + (size_t)tok * p.x_stride + k8 * 8);
-                        *reinterpret_cast<uint4*>(xs + (size_t)tok * xp + k8 * 8) = raw;
-                        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+                // four 16-byte loads per thread go in flight before any of them is used
+                for (uint32_t i0 = 0; i0 < total; i0 += 4 * kThreads) {
+                    uint4 raw[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float2 f = __half22float2(h[e]);
-                            sum += f.x + f.y;
+                    for (int u = 0; u < 4; ++u) {
+                        const uint32_t i = i0 + u * kThreads + threadIdx.x;
+                        raw[u] = make_uint4(0, 0, 0, 0);
+                        if (i < total) {
+                            const uint32_t tok = i / groups, k8 = i - tok * groups;
+                            raw[u] = *reinterpret_cast<const uint4*>(p.x + (size_t)tok * p.x_stride + k8 * 8);
                         }
                     }
-                    if (p.kind == MAT_INT8) {
 #pragma unroll
-                        for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off, 16);
-                        if (i < total && (k8 & 15) == 0) sums[tok * (p.K / 128) + (k8 >> 4)] = sum;
+                    for (int u = 0; u < 4; ++u) {
+                        const uint32_t i = i0 + u * kThreads + threadIdx.x;
+                        if (i0 + u * kThreads >= total) break;  // uniform across the CTA
+                        float sum = 0.f;
+                        uint32_t tok = 0, k8 = 0;
+                        if (i < total) {
+                            tok = i / groups;
+                            k8 = i - tok * groups;
+                            *reinterpret_cast<uint4*>(xs + (size_t)tok * xp + k8 * 8) = raw[u];
+                            const __half2* h = reinterpret_cast<const __half2*>(&raw[u]);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 f = __half22float2(h[e]);
+                                sum += f.x + f.y;
+                            }
+                        }
+                        if (p.kind == MAT_INT8) {
+#pragma unroll
+                            for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off, 16);
+                            if (i < total && (k8 & 15) == 0) sums[tok * (p.K / 128) + (k8 >> 4)] = sum;
+                        }
                     }
                 }
             } else if (p.kind == MAT_INT8) {
