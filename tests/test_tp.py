@@ -13,7 +13,7 @@ WORKER = os.path.join(ROOT, "tests", "tp_worker.py")
 
 def _spawn(mode, world, port):
     # loopback for every rendezvous (the host name of a container need not resolve); no NVLS: a rank that
-    # dies must not leave peers' memory bound to a multicast object
+    # dies must not leave peers' memory bound to a switch-side reduction object
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0",
                GLOO_SOCKET_IFNAME="lo", NCCL_SOCKET_IFNAME="lo")
     procs = [subprocess.Popen([sys.executable, WORKER, mode], env=dict(env, RANK=str(r), LOCAL_RANK=str(r)),
