@@ -865,14 +865,14 @@ __global__ void __launch_bounds__(4 * S) wkv56_fused_kernel(const Wkv6Args a) {
     }
     if (q == 0) su[j] = a.time_first[c];
     const float gw = __half2float(a.gn_w[c]), gb = __half2float(a.gn_b[c]);
-    trace(141);
-    pdl_wait();  // ...the state does (the previous token's job wrote it), and so do the cursors
-    trace(142);
-
-    // the state rows are needed whatever the cursors say: get their loads in flight first
+    // ...nor do the WKV state rows: within a job only this kernel writes them, and every job begins with
+    // launches that are not programmatic dependents, i.e. after the previous job has completed
     float st[SI];
 #pragma unroll
     for (int i = 0; i < SI; ++i) st[i] = static_cast<const float*>(a.state.base)[a.state.index(c, 1 + q * SI + i, slot)];
+    trace(141);
+    pdl_wait();  // the token's k, v, r, g and adapter activations come from the kernels before this one
+    trace(142);
 
     // run of tokens of this batch slot
     uint32_t start, count;
