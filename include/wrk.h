@@ -180,6 +180,9 @@ int32_t wrk_op_time_first_v7(wrk_tensor* u, wrk_tensor* r, wrk_tensor* n, wrk_te
 int32_t wrk_op_layer_norm(wrk_tensor* w, wrk_tensor* b, wrk_tensor* x, float eps, wrk_op** out);
 /* TensorOp::group_norm(w, b, x, eps), src/tensor/ops.rs:454-508 */
 int32_t wrk_op_group_norm(wrk_tensor* w, wrk_tensor* b, wrk_tensor* x, float eps, wrk_op** out);
+/* TensorOp::softmax(x), src/tensor/ops.rs:299-352 (shader src/shaders/softmax.wgsl): in place over every row of
+ * x.shape[0] elements; the device-side half of the logits hand-off of src/runtime/softmax.rs. */
+int32_t wrk_op_softmax(wrk_tensor* x, wrk_op** out);
 /* TensorOp::l2_norm(x, eps), src/tensor/ops.rs:642-691 */
 int32_t wrk_op_l2_norm(wrk_tensor* x, float eps, wrk_op** out);
 /* TensorOp::token_shift(cursors, time_mix, state, input, output, reversed), src/tensor/ops.rs:1393-1461 */

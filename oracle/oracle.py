@@ -181,6 +181,11 @@ def group_norm(w, b, x, eps, H, fast=False):
     lib(fast).orc_layer_norm(_ptr(w), _ptr(b), _dt(x), _ptr(x), S, x.size // S, H, ctypes.c_float(eps))
 
 
+def softmax(x, fast=False):
+    C = x.shape[-1]
+    lib(fast).orc_softmax(_dt(x), _ptr(x), C, x.size // C)
+
+
 def l2_norm(x, eps, fast=False):
     C = x.shape[-1]
     lib(fast).orc_l2_norm(_dt(x), _ptr(x), C, x.size // C, ctypes.c_float(eps))

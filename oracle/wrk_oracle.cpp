@@ -439,6 +439,23 @@ int orc_layer_norm(const uint16_t* w, const uint16_t* b, int dtype, void* x, uin
     return 0;
 }
 
+// softmax: src/shaders/softmax.wgsl:52-106.  x <- exp(x - max) / sum exp(x - max) per row of C, f32 math.
+int orc_softmax(int dtype, void* x, uint32_t C, uint32_t rows) {
+    orc_view xv = {x, dtype, {C, rows, 1, 1}, {C, rows, 1, 1}, {0, 0, 0, 0}};
+#pragma omp parallel for schedule(static)
+    for (int64_t row = 0; row < (int64_t)rows; ++row) {
+        float mx = -1.0e30f;
+        for (uint32_t c = 0; c < C; ++c) mx = std::max(mx, vload(xv, (size_t)row * C + c));
+        float sum = 0.0f;
+        for (uint32_t c = 0; c < C; ++c) sum += std::exp(vload(xv, (size_t)row * C + c) - mx);
+        for (uint32_t c = 0; c < C; ++c) {
+            const size_t i = (size_t)row * C + c;
+            vstore(xv, i, std::exp(vload(xv, i) - mx) / sum);
+        }
+    }
+    return 0;
+}
+
 // l2_norm: src/shaders/normalize.wgsl:120-152.  x *= rsqrt(sum x^2 + eps) per row of C.
 int orc_l2_norm(int dtype, void* x, uint32_t C, uint32_t rows, float eps) {
     orc_view xv = {x, dtype, {C, rows, 1, 1}, {C, rows, 1, 1}, {0, 0, 0, 0}};

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 from oracle import oracle
-from tests.util import assert_close
+from tests.util import assert_close, is_approx_eps
 
 pytestmark = pytest.mark.gpu
 
@@ -41,6 +41,38 @@ def test_group_norm(wrk, ctx, dtype):
     ref = x.copy()
     oracle.group_norm(w, b, ref, 64e-5, H)
     assert_close(t_x.numpy().reshape(T, H, S), ref, "group_norm")
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float16])
+def test_softmax_reference_test_shape(wrk, ctx, dt):
+    # C, T, B of test_softmax (src/tensor/ops.rs:2632-2669): uniform(-5, 5) data, dense answer in f32
+    rng = np.random.default_rng(42)
+    x = (10.0 * (rng.random((2, 3, 1000), dtype=np.float32) - 0.5)).astype(dt)
+    t_x = ctx.from_numpy(x)
+    ctx.run(wrk.softmax(t_x))
+    got = t_x.numpy().reshape(x.shape).astype(np.float32)
+    ref = x.copy()
+    oracle.softmax(ref)
+    xf = x.astype(np.float32)  # the answer from the values the tensor holds (fp16-rounded in the fp16 case)
+    e = np.exp(xf - xf.max(axis=-1, keepdims=True))
+    dense = e / e.sum(axis=-1, keepdims=True)
+    assert is_approx_eps(got, dense, 1e-3 if dt == np.float16 else 1e-4).all()
+    assert_close(got, ref.astype(np.float32), "softmax vs oracle")
+    assert np.allclose(got.sum(axis=-1), 1.0, atol=2e-3 if dt == np.float16 else 1e-5)
+
+
+def test_softmax_vocabulary_row(wrk, ctx):
+    # one row of 65536 logits with a wide range: the maximum is subtracted first
+    rng = np.random.default_rng(7)
+    x = (rng.standard_normal((1, 65536)) * 8.0 + 50.0).astype(np.float32)
+    t_x = ctx.from_numpy(x)
+    ctx.run(wrk.softmax(t_x))
+    got = t_x.numpy().reshape(x.shape)
+    ref = x.copy()
+    oracle.softmax(ref)
+    assert np.isfinite(got).all() and abs(float(got.sum()) - 1.0) < 1e-4
+    assert np.allclose(got, ref, rtol=1e-4, atol=1e-9)
+    assert int(got.argmax()) == int(x.argmax())
 
 
 def test_l2_norm(wrk, ctx):

@@ -163,3 +163,19 @@ def test_packed_cursor_wraps_like_the_reference():
     assert packed.shape == (256,) and packed[0] == 3  # len 256 wraps to 0
     packed = oracle.pack_cursors([(1, 5, 7), (2, 12, 0), (4, 12, 2)])
     assert list(packed) == [1 | 5 << 8 | 7 << 24] * 7 + [4 | 12 << 8 | 2 << 24] * 2
+
+
+def test_softmax_against_dense_numpy():
+    # the arithmetic of src/shaders/softmax.wgsl against a float64 restatement, on the reference test's shape
+    rng = np.random.default_rng(42)
+    x = (10.0 * (rng.random((2, 3, 1000), dtype=np.float32) - 0.5)).astype(np.float32)
+    got = x.copy()
+    oracle.softmax(got)
+    x64 = x.astype(np.float64)
+    e = np.exp(x64 - x64.max(axis=-1, keepdims=True))
+    assert np.allclose(got, e / e.sum(axis=-1, keepdims=True), rtol=1e-5, atol=1e-9)
+    h = x.astype(np.float16)  # fp16 tensors: fp16 inputs, f32 math, fp16 outputs
+    h64 = h.astype(np.float64)
+    oracle.softmax(h)
+    eh = np.exp(h64 - h64.max(axis=-1, keepdims=True))
+    assert np.allclose(h.astype(np.float64), eh / eh.sum(axis=-1, keepdims=True), rtol=2e-3, atol=1e-7)

@@ -310,6 +310,10 @@ def group_norm(w, b, x, eps):
     return _mk("wrk_op_group_norm", _t(w), _t(b), _t(x), ctypes.c_float(eps), keep=(w, b, x))
 
 
+def softmax(x):
+    return _mk("wrk_op_softmax", _t(x), keep=(x,))
+
+
 def l2_norm(x, eps):
     return _mk("wrk_op_l2_norm", _t(x), ctypes.c_float(eps), keep=(x,))
 

@@ -63,6 +63,7 @@ cudaError_t time_first_v7(const __half* u, int dtype, const void* r, const void*
 cudaError_t layer_norm(const __half* w, const __half* b, int dtype, void* x, uint32_t C, uint32_t rows,
                        uint32_t wrows, float eps, cudaStream_t stream);
 cudaError_t l2_norm(int dtype, void* x, uint32_t C, uint32_t rows, float eps, cudaStream_t stream);
+cudaError_t softmax(int dtype, void* x, uint32_t C, uint32_t rows, cudaStream_t stream);
 cudaError_t token_shift(const uint32_t* cursors, int wide, DView time_mix, DView state, DView input, DView output,
                         int reversed, cudaStream_t stream);
 cudaError_t channel_mix(const uint32_t* cursors, int wide, DView state, int dtype, const void* r, const void* v,

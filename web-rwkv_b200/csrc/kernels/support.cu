@@ -71,6 +71,30 @@ __global__ void l2_norm_kernel(int dtype, void* x, uint32_t C, uint32_t rows, fl
     }
 }
 
+// softmax.wgsl: x <- exp(x - max) / sum exp(x - max) per row of C (two reductions, then the write).
+__global__ void softmax_kernel(int dtype, void* x, uint32_t C, uint32_t rows) {
+    __shared__ float scratch[32];
+    for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const size_t base = (size_t)row * C;
+        float m = -1.0e30f;
+        for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) m = fmaxf(m, dload(x, dtype, base + c));
+        // block maximum through the sum helper's scratch: warp maxima, then the first warp's maximum of those
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = m;
+        __syncthreads();
+        float mx = -1.0e30f;
+        for (uint32_t w = 0; w < (blockDim.x + 31) / 32; ++w) mx = fmaxf(mx, scratch[w]);
+        __syncthreads();
+        float s = 0.f;
+        for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) s += expf(dload(x, dtype, base + c) - mx);
+        const float sum = block_sum(s, scratch);
+        for (uint32_t c = threadIdx.x; c < C; c += blockDim.x)
+            dstore(x, dtype, base + c, expf(dload(x, dtype, base + c) - mx) / sum);
+    }
+}
+
 // token_shift.wgsl: out[c, t, z] = mix(x_t, prev, f) (reversed) or mix(prev, x_t, f); prev is the
 // previous token of the same sequence or, at the sequence's first token of the job, the carry row.
 __global__ void token_shift_kernel(const uint32_t* cursors, int wide, DView tm, DView state, DView in, DView out,
@@ -186,6 +210,14 @@ cudaError_t l2_norm(int dtype, void* x, uint32_t C, uint32_t rows, float eps, cu
     const int block = C <= 256 ? 32 : 256;
     const uint32_t grid = rows < 148u * 32u ? rows : 148u * 32u;
     l2_norm_kernel<<<grid, block, 0, stream>>>(dtype, x, C, rows, eps);
+    return cudaGetLastError();
+}
+
+cudaError_t softmax(int dtype, void* x, uint32_t C, uint32_t rows, cudaStream_t stream) {
+    if (rows == 0 || C == 0) return cudaSuccess;
+    const int block = C <= 256 ? 32 : C <= 4096 ? 256 : 1024;
+    const uint32_t grid = rows < 148u * 32u ? rows : 148u * 32u;
+    softmax_kernel<<<grid, block, 0, stream>>>(dtype, x, C, rows);
     return cudaGetLastError();
 }
 

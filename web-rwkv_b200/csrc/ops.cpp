@@ -389,6 +389,17 @@ int32_t wrk_op_group_norm(wrk_tensor* w, wrk_tensor* b, wrk_tensor* x, float eps
     return norm_common("group_norm", true, w, b, x, eps, out);
 }
 
+int32_t wrk_op_softmax(wrk_tensor* x, wrk_op** out) {
+    REQ_NN(x, out);
+    REQ_FLOAT(x, "x");
+    const Shape4 sh = x->shape;
+    void* xp = x->ptr();
+    const int dt = x->dtype;
+    const uint32_t C = sh[0], rows = sh[1] * sh[2] * sh[3];
+    *out = new_atom("softmax", [=](cudaStream_t s) { return k::softmax(dt, xp, C, rows, s); }, {x});
+    return WRK_OK;
+}
+
 int32_t wrk_op_l2_norm(wrk_tensor* x, float eps, wrk_op** out) {
     REQ_NN(x, out);
     REQ_FLOAT(x, "x");
