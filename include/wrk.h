@@ -233,6 +233,12 @@ int32_t wrk_matrix_matmul_op_sparse(wrk_matrix* m, const wrk_view* input, const 
                                     int32_t turbo, wrk_op** out);
 /* The default NF4 table of Float4Quant::new, matrix.rs:48-70. */
 int32_t wrk_nf4_table(float table[16]);
+/* Float4Quant::new_student(nu) / quantile_student, matrix.rs:29-44 and 72-77: the SF4 code book.  The Student-t
+ * quantile the reference takes from the statrs crate (0.18) is computed here from the regularized incomplete
+ * beta function. */
+int32_t wrk_sf4_table(double nu, float table[16]);
+/* Matrix::quant_sf4(matrix, nu), matrix.rs:202-222 */
+int32_t wrk_matrix_quant_sf4(wrk_tensor* matrix, double nu, wrk_matrix** out);
 
 /* ---- Tensor-parallel plumbing (the reference is single-GPU; no counterpart) ----
  * One process per GPU.  Rank 0 makes an id, every rank (rank 0 included) creates its communicator from the

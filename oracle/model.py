@@ -11,7 +11,7 @@ import numpy as np
 from . import oracle as o
 
 LN_EPS, GN_EPS, L2_EPS = 1.0e-5, 64.0e-5, 1.0e-12
-QUANT_NONE, QUANT_INT8, QUANT_NF4 = 0, 1, 2
+QUANT_NONE, QUANT_INT8, QUANT_NF4, QUANT_SF4 = 0, 1, 2, 3
 
 
 class Mat:
@@ -20,17 +20,20 @@ class Mat:
     def __init__(self, w_f16, quant, fast=False):
         w = np.ascontiguousarray(w_f16, dtype=np.float16)
         self.shape = w.shape  # (..., M, K)
+        self.table = o.NF4_TABLE
         if quant == QUANT_INT8:
             self.kind = o.MAT_INT8
             self.w, self.scale = o.quantize_mat_int8(w, fast=fast)
-        elif quant == QUANT_NF4:
+        elif quant in (QUANT_NF4, QUANT_SF4):
+            # Quant::SF4 is the Fp4 matrix with the Student-t code book, nu = 5 (src/runtime/model.rs:133-134)
             self.kind = o.MAT_NF4
-            self.w, self.scale = o.quantize_mat_nf4(w, fast=fast)
+            self.table = o.NF4_TABLE if quant == QUANT_NF4 else o.sf4_table(5.0)
+            self.w, self.scale = o.quantize_mat_nf4(w, table=self.table, fast=fast)
         else:
             self.kind, self.w, self.scale = o.MAT_FP16, w, None
 
     def matmul(self, x, out, act=o.ACT_NONE, turbo=False, fast=False):
-        o.matmul(self.kind, self.w, self.scale, x, out, act=act, mode=1 if turbo else 0, fast=fast)
+        o.matmul(self.kind, self.w, self.scale, x, out, act=act, mode=1 if turbo else 0, table=self.table, fast=fast)
 
 
 class OracleModel:

@@ -22,6 +22,18 @@ NF4_TABLE = np.array([
 ], dtype=np.float32)  # src/tensor/matrix.rs:50-67
 
 
+def sf4_table(nu=5.0):
+    """`quantile_student(nu)` of src/tensor/matrix.rs:29-44: Student-t quantiles at 7 probabilities from delta up to
+    1/2 and 9 from 1/2 up to 1 - delta, divided by the largest.  The reference takes the quantile from statrs 0.18
+    (`StudentsT::inverse_cdf`), which is not part of its tree; scipy's `t.ppf` computes the same function."""
+    from scipy import stats
+    delta = (1.0 / 32.0 + 1.0 / 30.0) / 2.0
+    lo, hi = (0.5 - delta) / 7.0, (1.0 - delta - 0.5) / 8.0
+    prob = [delta + lo * i for i in range(7)] + [0.5 + hi * i for i in range(9)]
+    q = stats.t.ppf(np.array(prob, dtype=np.float64), nu)
+    return (q / q.max()).astype(np.float32)
+
+
 class _CView(ctypes.Structure):
     _fields_ = [("data", ctypes.c_void_p), ("dtype", ctypes.c_int32), ("shape", ctypes.c_uint32 * 4),
                 ("stride", ctypes.c_uint32 * 4), ("offset", ctypes.c_uint32 * 4)]

@@ -37,3 +37,19 @@ def test_error_reporting_without_device():
     table = (ctypes.c_float * 16)()
     assert lib.wrk_nf4_table(table) == 0
     assert table[0] == -1.0 and table[15] == 1.0 and table[7] == 0.0
+
+
+def test_sf4_table_matches_student_quantiles():
+    # Float4Quant::new_student(5.0), src/tensor/matrix.rs:29-44 and 72-77: the library's own quantile (incomplete beta
+    # function + bisection) against scipy's, which the oracle uses; no device is touched.
+    import numpy as np
+    from oracle import oracle
+    lib = ctypes.CDLL(os.path.join(ROOT, "web-rwkv_b200", "libwrk.so"))
+    for nu in (1.0, 2.5, 5.0, 30.0):
+        table = (ctypes.c_float * 16)()
+        assert lib.wrk_sf4_table(ctypes.c_double(nu), table) == 0
+        got = np.array(list(table), dtype=np.float32)
+        assert np.array_equal(got, oracle.sf4_table(nu)), nu
+        assert got[0] == -1.0 and got[7] == 0.0 and got[15] == 1.0 and (np.diff(got) > 0).all()
+    assert lib.wrk_sf4_table(ctypes.c_double(0.0), table) != 0
+    assert lib.wrk_sf4_table(ctypes.c_double(5.0), None) != 0

@@ -23,6 +23,9 @@ def _make_matrix(wrk, ctx, kind, w):
     if kind == "int8":
         q, mm = oracle.quantize_mat_int8(w)
         return wrk.Matrix.quant_u8(t), (oracle.MAT_INT8, q, mm)
+    if kind == "sf4":
+        q, am = oracle.quantize_mat_nf4(w, oracle.sf4_table(5.0))
+        return wrk.Matrix.quant_sf4(t, 5.0), (oracle.MAT_NF4, q, am)
     q, am = oracle.quantize_mat_nf4(w)
     return wrk.Matrix.quant_nf4(t), (oracle.MAT_NF4, q, am)
 
@@ -42,8 +45,16 @@ def _run(wrk, ctx, kind, K, M, N, *, turbo, in_dt=np.float16, out_dt=np.float32,
     ctx.run(mat.matmul_op(t_x, t_y, act=act, turbo=turbo))
     got = t_y.numpy().reshape(N, M)
     want = np.zeros((N, M), dtype=out_dt)
-    oracle.matmul(okind, om, oscale, x, want, act=act, mode=1 if turbo else 0)
+    table = oracle.sf4_table(5.0) if kind == "sf4" else oracle.NF4_TABLE
+    oracle.matmul(okind, om, oscale, x, want, act=act, mode=1 if turbo else 0, table=table)
     return got, want
+
+
+@pytest.mark.parametrize("n,k,m", [(1, 2048, 2048), (5, 1024, 256), (64, 2048, 512)])
+def test_sf4_code_book(wrk, ctx, n, k, m):
+    # Matrix::quant_sf4 with nu = 5 (Quant::SF4): decode GEMV, small-batch and tensor-core GEMM paths
+    got, want = _run(wrk, ctx, "sf4", k, m, n, turbo=(n % 32 == 0), seed=n)
+    assert_close(got, want, f"sf4 n={n}")
 
 
 @pytest.mark.parametrize("kind", KINDS)

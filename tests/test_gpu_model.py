@@ -57,6 +57,7 @@ def _check(pairs, bundle, state):
     ("v6-tiny", {0: 1, 1: 2}),      # layer 0 Int8, layer 1 NF4, layer 2 fp16
     ("v5-tiny", {0: 1, 1: 2}),
     ("v7-tiny", {0: 1, 1: 2}),
+    ("v6-tiny", {0: 3, 1: 3, 2: 2}),  # Quant::SF4 (Student-t code book, nu = 5) on layers 0-1
 ])
 def test_mixed_batches_chunked_prefill_then_decode(ctx, config, quant):
     rng = np.random.default_rng(2001)

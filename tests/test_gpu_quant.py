@@ -109,6 +109,20 @@ def test_nf4_unsorted_table_uses_literal_scan(wrk, ctx):
     assert np.array_equal(am.view(np.uint16), am_ref.view(np.uint16))
 
 
+@pytest.mark.parametrize("nu", [5.0, 2.0])
+def test_sf4_matrix_bit_exact(wrk, ctx, nu):
+    # Matrix::quant_sf4 (src/tensor/matrix.rs:202-222): the Fp4 packing with the Student-t code book
+    rng = np.random.default_rng(int(nu * 10))
+    m = (rng.standard_t(5.0, size=(64, 512)) * 0.02).astype(np.float16)
+    table = wrk.sf4_table(nu)
+    assert np.array_equal(table, oracle.sf4_table(nu))
+    kind, w, am, q = wrk.Matrix.quant_sf4(ctx.from_numpy(m), nu).parts()
+    q_ref, am_ref = oracle.quantize_mat_nf4(m, table)
+    assert np.array_equal(q.numpy().reshape(-1), table)
+    assert np.array_equal(w.numpy().reshape(q_ref.shape), q_ref)
+    assert np.array_equal(am.numpy().reshape(-1).view(np.uint16), am_ref.view(np.uint16))
+
+
 def test_full_size_checksum(wrk, ctx):
     # 7B-shaped FFN matrix (4096 x 14336): compare every byte with the oracle
     rng = np.random.default_rng(2024)

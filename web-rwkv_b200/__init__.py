@@ -387,6 +387,12 @@ def nf4_table():
     return np.array(list(t), dtype=np.float32)
 
 
+def sf4_table(nu=5.0):
+    t = (ctypes.c_float * 16)()
+    check(lib().wrk_sf4_table(ctypes.c_double(nu), t))
+    return np.array(list(t), dtype=np.float32)
+
+
 class Matrix:
     """`Matrix` of src/tensor/matrix.rs: Fp16 / Int8 {w, m} / Fp4 {q, w, m}."""
 
@@ -414,6 +420,12 @@ class Matrix:
     def quant_nf4(tensor):
         h = ctypes.c_void_p()
         check(lib().wrk_matrix_quant_nf4(tensor.handle, ctypes.byref(h)))
+        return Matrix(tensor.ctx, h)
+
+    @staticmethod
+    def quant_sf4(tensor, nu=5.0):
+        h = ctypes.c_void_p()
+        check(lib().wrk_matrix_quant_sf4(tensor.handle, ctypes.c_double(nu), ctypes.byref(h)))
         return Matrix(tensor.ctx, h)
 
     def parts(self):

@@ -175,6 +175,65 @@ int32_t time_mix_v56(const char* name, int per_token, wrk_tensor* cursors, wrk_t
 
 }  // namespace
 
+namespace {
+
+// Regularized incomplete beta function I_x(a, b): continued fraction evaluated with the modified Lentz method.
+double beta_cf(double a, double b, double x) {
+    const double tiny = 1e-300, eps = 1e-16;
+    const double qab = a + b, qap = a + 1.0, qam = a - 1.0;
+    double c = 1.0, d = 1.0 - qab * x / qap;
+    if (std::fabs(d) < tiny) d = tiny;
+    d = 1.0 / d;
+    double h = d;
+    for (int m = 1; m <= 500; ++m) {
+        const int m2 = 2 * m;
+        double aa = m * (b - m) * x / ((qam + m2) * (a + m2));
+        d = 1.0 + aa * d;
+        if (std::fabs(d) < tiny) d = tiny;
+        c = 1.0 + aa / c;
+        if (std::fabs(c) < tiny) c = tiny;
+        d = 1.0 / d;
+        h *= d * c;
+        aa = -(a + m) * (qab + m) * x / ((a + m2) * (qap + m2));
+        d = 1.0 + aa * d;
+        if (std::fabs(d) < tiny) d = tiny;
+        c = 1.0 + aa / c;
+        if (std::fabs(c) < tiny) c = tiny;
+        d = 1.0 / d;
+        const double del = d * c;
+        h *= del;
+        if (std::fabs(del - 1.0) < eps) break;
+    }
+    return h;
+}
+double reg_inc_beta(double a, double b, double x) {
+    if (x <= 0.0) return 0.0;
+    if (x >= 1.0) return 1.0;
+    const double front = std::exp(std::lgamma(a + b) - std::lgamma(a) - std::lgamma(b) + a * std::log(x) + b * std::log1p(-x));
+    if (x < (a + 1.0) / (a + b + 2.0)) return front * beta_cf(a, b, x) / a;
+    return 1.0 - front * beta_cf(b, a, 1.0 - x) / b;
+}
+// Distribution function of Student's t with nu degrees of freedom, and its inverse by bisection (monotone, 200
+// halvings of a bracket that doubles until it contains the root: exact to the last bit of a double).
+double student_cdf(double t, double nu) {
+    const double tail = 0.5 * reg_inc_beta(0.5 * nu, 0.5, nu / (nu + t * t));
+    return t >= 0.0 ? 1.0 - tail : tail;
+}
+double student_quantile(double p, double nu) {
+    if (p == 0.5) return 0.0;
+    double lo = -1.0, hi = 1.0;
+    while (student_cdf(lo, nu) > p) lo *= 2.0;
+    while (student_cdf(hi, nu) < p) hi *= 2.0;
+    for (int i = 0; i < 200; ++i) {
+        const double mid = 0.5 * (lo + hi);
+        if (student_cdf(mid, nu) < p) lo = mid;
+        else hi = mid;
+    }
+    return 0.5 * (lo + hi);
+}
+
+}  // namespace
+
 extern "C" {
 
 int32_t wrk_nf4_table(float table[16]) {
@@ -185,6 +244,27 @@ int32_t wrk_nf4_table(float table[16]) {
                                 0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
     WRK_REQUIRE(table, WRK_ERR_INVALID_ARGUMENT, "null argument");
     for (int i = 0; i < 16; ++i) table[i] = q[i];
+    return WRK_OK;
+}
+
+int32_t wrk_sf4_table(double nu, float table[16]) {
+    // quantile_student, src/tensor/matrix.rs:29-44: 16 probabilities (7 steps from delta up to 1/2, 9 from 1/2 to
+    // 1 - delta), the Student-t quantile of each, divided by the largest.  The reference takes the quantile from
+    // the statrs crate (0.18, StudentsT::inverse_cdf); here it is the root of the distribution function, which
+    // is written with the regularized incomplete beta function (continued fraction, modified Lentz).
+    WRK_REQUIRE(table, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(nu > 0.0 && std::isfinite(nu), WRK_ERR_INVALID_ARGUMENT, "nu must be positive");
+    const double delta = (1.0 / 32.0 + 1.0 / 30.0) / 2.0;
+    double prob[16];
+    const double step_lo = (0.5 - delta) / 7.0, step_hi = (1.0 - delta - 0.5) / 8.0;
+    for (int i = 0; i < 7; ++i) prob[i] = delta + step_lo * i;
+    for (int i = 0; i < 9; ++i) prob[7 + i] = 0.5 + step_hi * i;
+    double q[16], largest = 0.0;
+    for (int i = 0; i < 16; ++i) {
+        q[i] = student_quantile(prob[i], nu);
+        largest = std::max(largest, q[i]);
+    }
+    for (int i = 0; i < 16; ++i) table[i] = (float)(q[i] / largest);
     return WRK_OK;
 }
 
@@ -644,6 +724,12 @@ int32_t wrk_matrix_quant_fp4(wrk_tensor* matrix, const float table[16], wrk_matr
 int32_t wrk_matrix_quant_nf4(wrk_tensor* matrix, wrk_matrix** out) {
     float table[16];
     wrk_nf4_table(table);
+    return wrk_matrix_quant_fp4(matrix, table, out);
+}
+
+int32_t wrk_matrix_quant_sf4(wrk_tensor* matrix, double nu, wrk_matrix** out) {
+    float table[16];
+    WRK_TRY(wrk_sf4_table(nu, table));
     return wrk_matrix_quant_fp4(matrix, table, out);
 }
 

@@ -126,10 +126,8 @@ struct Loader {
             case WRK_QUANT_NONE: WRK_TRY(wrk_matrix_fp16(t, &m)); break;
             case WRK_QUANT_INT8: WRK_TRY(wrk_matrix_quant_u8(t, &m)); break;
             case WRK_QUANT_NF4: WRK_TRY(wrk_matrix_quant_nf4(t, &m)); break;
-            default:
-                return set_error(WRK_ERR_UNSUPPORTED,
-                                 "Quant::SF4 needs the Student-t code book of a third-party crate; pass a table to "
-                                 "wrk_matrix_quant_fp4 instead");
+            case WRK_QUANT_SF4: WRK_TRY(wrk_matrix_quant_sf4(t, 5.0, &m)); break;  // Quant::SF4: nu = 5 (model.rs:133-134)
+            default: return set_error(WRK_ERR_INVALID_ARGUMENT, "unknown quant %d", quant);
         }
         *out = MatrixH(m);
         // the fp16 staging tensor is released here; the stream orders its reuse after the quantizer
