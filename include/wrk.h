@@ -183,6 +183,14 @@ int32_t wrk_op_group_norm(wrk_tensor* w, wrk_tensor* b, wrk_tensor* x, float eps
 /* TensorOp::softmax(x), src/tensor/ops.rs:299-352 (shader src/shaders/softmax.wgsl): in place over every row of
  * x.shape[0] elements; the device-side half of the logits hand-off of src/runtime/softmax.rs. */
 int32_t wrk_op_softmax(wrk_tensor* x, wrk_op** out);
+/* TensorOp::embed(tokens, input, output), src/tensor/ops.rs:346-400 (shader src/shaders/embed.wgsl): the device-side
+ * embedding gather.  tokens u32 [T, B], input f16 [C, V], output [C, T, B].  A token id >= V leaves its row
+ * untouched and records WRK_ERR_BATCH_OUT_OF_RANGE in the context's device status. */
+int32_t wrk_op_embed(wrk_tensor* tokens, wrk_tensor* input, wrk_tensor* output, wrk_op** out);
+/* TensorOp::recenter(x), src/tensor/ops.rs:511-560 (shader src/shaders/normalize.wgsl:46-80) */
+int32_t wrk_op_recenter(wrk_tensor* x, wrk_op** out);
+/* TensorOp::rms_norm(w, b, x, eps), src/tensor/ops.rs:566-640 (shader src/shaders/normalize.wgsl:82-118) */
+int32_t wrk_op_rms_norm(wrk_tensor* w, wrk_tensor* b, wrk_tensor* x, float eps, wrk_op** out);
 /* TensorOp::l2_norm(x, eps), src/tensor/ops.rs:642-691 */
 int32_t wrk_op_l2_norm(wrk_tensor* x, float eps, wrk_op** out);
 /* TensorOp::token_shift(cursors, time_mix, state, input, output, reversed), src/tensor/ops.rs:1393-1461 */
@@ -204,6 +212,15 @@ int32_t wrk_op_mul_activate(const wrk_view* input, const wrk_view* output, int32
 int32_t wrk_op_activate(const wrk_view* x, int32_t act, wrk_op** out);
 /* TensorOp::blit(input, output), src/tensor/ops.rs:2015-2068 */
 int32_t wrk_op_blit(const wrk_view* input, const wrk_view* output, wrk_op** out);
+/* TensorOp::broadcast(input, output), src/tensor/ops.rs:2069-2118: input repeats along the token and batch axes */
+int32_t wrk_op_broadcast(const wrk_view* input, const wrk_view* output, wrk_op** out);
+/* TensorOp::blend(factor, input, output), src/tensor/ops.rs:2171-2223: output = factor[0] * input + factor[1] * output;
+ * factor is an f32 tensor of 4 entries (the reference's uniform). */
+int32_t wrk_op_blend(wrk_tensor* factor, wrk_tensor* input, wrk_tensor* output, wrk_op** out);
+/* TensorOp::blend_lora(factor, xa, xb, output), src/tensor/ops.rs:2226-2282 (shader src/shaders/blend_lora.wgsl):
+ * output[m, n, b] = factor[0] * sum_k xa[k, m, b] * xb[k, n, b] + factor[1] * output[m, n, b]; all f16, f32 sum. */
+int32_t wrk_op_blend_lora(wrk_tensor* factor, const wrk_view* xa, const wrk_view* xb, const wrk_view* output,
+                          wrk_op** out);
 /* TensorOp::transpose(input, output), src/tensor/ops.rs:2121-2169 */
 int32_t wrk_op_transpose(const wrk_view* input, const wrk_view* output, wrk_op** out);
 /* TensorOp::lerp(input, output, factor, reversed), src/tensor/ops.rs:2284-2350 */

@@ -198,6 +198,40 @@ def softmax(x, fast=False):
     lib(fast).orc_softmax(_dt(x), _ptr(x), C, x.size // C)
 
 
+def recenter(x, fast=False):
+    C = x.shape[-1]
+    lib(fast).orc_recenter(_dt(x), _ptr(x), C, x.size // C)
+
+
+def rms_norm(w, b, x, eps, fast=False):
+    C = x.shape[-1]
+    lib(fast).orc_rms_norm(_ptr(w), _ptr(b), _dt(x), _ptr(x), C, x.size // C, ctypes.c_float(eps))
+
+
+def embed(tokens, input, output, fast=False):
+    """tokens: (B, T) u32; input: (V, C) f16; output: (B, T, C)."""
+    C = output.shape[-1]
+    tokens = np.ascontiguousarray(tokens, dtype=np.uint32)
+    lib(fast).orc_embed(_ptr(tokens), _ptr(input), _dt(output), _ptr(output), C, output.size // C)
+
+
+def broadcast(input, output, fast=False):
+    iv, ov = _view(input).c(), _view(output).c()
+    lib(fast).orc_broadcast(ctypes.byref(iv), ctypes.byref(ov))
+
+
+def blend(factor, input, output, fast=False):
+    factor = np.ascontiguousarray(factor, dtype=np.float32)
+    iv, ov = _view(input).c(), _view(output).c()
+    lib(fast).orc_blend(_ptr(factor), ctypes.byref(iv), ctypes.byref(ov))
+
+
+def blend_lora(factor, xa, xb, output, fast=False):
+    factor = np.ascontiguousarray(factor, dtype=np.float32)
+    av, bv, ov = _view(xa).c(), _view(xb).c(), _view(output).c()
+    lib(fast).orc_blend_lora(_ptr(factor), ctypes.byref(av), ctypes.byref(bv), ctypes.byref(ov))
+
+
 def l2_norm(x, eps, fast=False):
     C = x.shape[-1]
     lib(fast).orc_l2_norm(_dt(x), _ptr(x), C, x.size // C, ctypes.c_float(eps))

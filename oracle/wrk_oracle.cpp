@@ -456,6 +456,84 @@ int orc_softmax(int dtype, void* x, uint32_t C, uint32_t rows) {
     return 0;
 }
 
+// recenter: src/shaders/normalize.wgsl:46-80.  x -= mean(x) per row of C.
+int orc_recenter(int dtype, void* x, uint32_t C, uint32_t rows) {
+    orc_view xv = {x, dtype, {C, rows, 1, 1}, {C, rows, 1, 1}, {0, 0, 0, 0}};
+    for (uint32_t row = 0; row < rows; ++row) {
+        float s = 0.0f;
+        for (uint32_t c = 0; c < C; ++c) s += vload(xv, (size_t)row * C + c);
+        const float mean = s / (float)C;
+        for (uint32_t c = 0; c < C; ++c) {
+            const size_t i = (size_t)row * C + c;
+            vstore(xv, i, vload(xv, i) - mean);
+        }
+    }
+    return 0;
+}
+
+// rms_norm: src/shaders/normalize.wgsl:82-118.  x = fma(x * rsqrt(mean x^2 + eps), w, b) per row of C.
+int orc_rms_norm(const uint16_t* w, const uint16_t* b, int dtype, void* x, uint32_t C, uint32_t rows, float eps) {
+    orc_view xv = {x, dtype, {C, rows, 1, 1}, {C, rows, 1, 1}, {0, 0, 0, 0}};
+    for (uint32_t row = 0; row < rows; ++row) {
+        float s = 0.0f;
+        for (uint32_t c = 0; c < C; ++c) {
+            const float val = vload(xv, (size_t)row * C + c);
+            s += val * val;
+        }
+        const float norm = 1.0f / std::sqrt(s / (float)C + eps);
+        for (uint32_t c = 0; c < C; ++c) {
+            const size_t i = (size_t)row * C + c;
+            vstore(xv, i, std::fma(vload(xv, i) * norm, h2f(w[c]), h2f(b[c])));
+        }
+    }
+    return 0;
+}
+
+// embed: src/shaders/embed.wgsl:21-41.  output[:, row] = input[:, tokens[row]] for row = b * T + t.
+int orc_embed(const uint32_t* tokens, const uint16_t* input, int dtype, void* output, uint32_t C, uint32_t rows) {
+    orc_view ov = {output, dtype, {C, rows, 1, 1}, {C, rows, 1, 1}, {0, 0, 0, 0}};
+    for (uint32_t row = 0; row < rows; ++row)
+        for (uint32_t c = 0; c < C; ++c) vstore(ov, (size_t)row * C + c, h2f(input[(size_t)tokens[row] * C + c]));
+    return 0;
+}
+
+// broadcast: src/shaders/reshape.wgsl:35-57.  output[c, t, b] = input[c, t % in.T, b % in.B].
+int orc_broadcast(const orc_view* input, const orc_view* output) {
+    for (uint32_t b = 0; b < output->shape[2]; ++b)
+        for (uint32_t t = 0; t < output->shape[1]; ++t)
+            for (uint32_t c = 0; c < output->shape[0]; ++c)
+                vstore(*output, vindex(*output, c, t, b),
+                       vload(*input, vindex(*input, c, t % input->shape[1], b % input->shape[2])));
+    return 0;
+}
+
+// blend: src/shaders/blend.wgsl:38-60.  output = factor.x * input + factor.y * output.
+int orc_blend(const float* factor, const orc_view* input, const orc_view* output) {
+    for (uint32_t b = 0; b < output->shape[2]; ++b)
+        for (uint32_t t = 0; t < output->shape[1]; ++t)
+            for (uint32_t c = 0; c < output->shape[0]; ++c) {
+                const size_t o = vindex(*output, c, t, b);
+                vstore(*output, o, factor[0] * vload(*input, vindex(*input, c, t, b)) + factor[1] * vload(*output, o));
+            }
+    return 0;
+}
+
+// blend_lora: src/shaders/blend_lora.wgsl:44-108.  output[m, n, b] = factor.x * sum_k xa[k, m, b] * xb[k, n, b] +
+// factor.y * output[m, n, b]; the sum runs over min(K_a, K_b) / 4 groups of four, in f32.
+int orc_blend_lora(const float* factor, const orc_view* xa, const orc_view* xb, const orc_view* output) {
+    const uint32_t K = std::min(xa->shape[0] / 4, xb->shape[0] / 4) * 4;
+    for (uint32_t b = 0; b < output->shape[2]; ++b)
+        for (uint32_t n = 0; n < output->shape[1]; ++n)
+            for (uint32_t m = 0; m < output->shape[0]; ++m) {
+                float sum = 0.0f;
+                for (uint32_t k = 0; k < K; ++k)
+                    sum += vload(*xa, vindex(*xa, k, m, b)) * vload(*xb, vindex(*xb, k, n, b));
+                const size_t o = vindex(*output, m, n, b);
+                vstore(*output, o, factor[0] * sum + factor[1] * vload(*output, o));
+            }
+    return 0;
+}
+
 // l2_norm: src/shaders/normalize.wgsl:120-152.  x *= rsqrt(sum x^2 + eps) per row of C.
 int orc_l2_norm(int dtype, void* x, uint32_t C, uint32_t rows, float eps) {
     orc_view xv = {x, dtype, {C, rows, 1, 1}, {C, rows, 1, 1}, {0, 0, 0, 0}};

@@ -85,6 +85,87 @@ def test_l2_norm(wrk, ctx):
     assert_close(t_x.numpy().reshape(x.shape), ref, "l2_norm")
 
 
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+def test_recenter_and_rms_norm(wrk, ctx, dtype):
+    rng = np.random.default_rng(21)
+    C, T, B = 768, 5, 2
+    x = (rng.standard_normal((B, T, C)) + 0.5).astype(dtype)
+    w = (1 + 0.02 * rng.standard_normal(C)).astype(np.float16)
+    b = (0.02 * rng.standard_normal(C)).astype(np.float16)
+    t_x = ctx.from_numpy(x)
+    ctx.run(wrk.recenter(t_x))
+    ref = x.copy()
+    oracle.recenter(ref)
+    assert_close(t_x.numpy().reshape(x.shape), ref, "recenter")
+    t_y = ctx.from_numpy(x)
+    ctx.run(wrk.rms_norm(ctx.from_numpy(w), ctx.from_numpy(b), t_y, 1e-5))
+    ref = x.copy()
+    oracle.rms_norm(w, b, ref, 1e-5)
+    assert_close(t_y.numpy().reshape(x.shape), ref, "rms_norm")
+    with pytest.raises(wrk.WrkError) as e:
+        wrk.rms_norm(ctx.from_numpy(w[:-4]), ctx.from_numpy(b), t_y, 1e-5)
+    assert e.value.status == -5
+
+
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+def test_embed_gather(wrk, ctx, dtype):
+    # the device-side embedding gather: bit-exact rows of the fp16 matrix (widened exactly for f32 outputs)
+    rng = np.random.default_rng(22)
+    C, V, T, B = 512, 1000, 7, 3
+    emb = rng.standard_normal((V, C)).astype(np.float16)
+    tokens = rng.integers(0, V, (B, T)).astype(np.uint32)
+    t_out = ctx.tensor(wrk.F16 if dtype == np.float16 else wrk.F32, [C, T, B])
+    ctx.run(wrk.embed(ctx.from_numpy(tokens), ctx.from_numpy(emb), t_out))
+    ref = np.zeros((B, T, C), dtype=dtype)
+    oracle.embed(tokens, emb, ref)
+    assert np.array_equal(t_out.numpy().reshape(ref.shape), ref)
+    assert np.array_equal(ref, emb[tokens].astype(dtype))
+    with pytest.raises(wrk.WrkError) as e:
+        wrk.embed(ctx.from_numpy(tokens[:, :-1].copy()), ctx.from_numpy(emb), t_out)
+    assert e.value.status == -5
+
+
+def test_broadcast_and_blend(wrk, ctx):
+    rng = np.random.default_rng(23)
+    C, T, B = 128, 6, 4
+    src = rng.standard_normal((2, 3, C)).astype(np.float16)
+    t_dst = ctx.tensor(wrk.F32, [C, T, B], zeros=True)
+    ctx.run(wrk.broadcast(ctx.from_numpy(src), t_dst))
+    ref = np.zeros((B, T, C), dtype=np.float32)
+    oracle.broadcast(src, ref)
+    assert np.array_equal(t_dst.numpy().reshape(ref.shape), ref)
+    assert np.array_equal(ref[3, 4], src[1, 1].astype(np.float32))
+    # blend: output = f0 * input + f1 * output
+    factor = np.array([0.25, 0.75, 0, 0], dtype=np.float32)
+    a = rng.standard_normal((B, T, C)).astype(np.float16)
+    o = rng.standard_normal((B, T, C)).astype(np.float16)
+    t_o = ctx.from_numpy(o)
+    ctx.run(wrk.blend(ctx.from_numpy(factor), ctx.from_numpy(a), t_o))
+    ref = o.copy()
+    oracle.blend(factor, a, ref)
+    assert_close(t_o.numpy().reshape(ref.shape), ref, "blend")
+
+
+def test_blend_lora(wrk, ctx):
+    # LoRA merge W += alpha * B A on an fp16 matrix [K = 256 inputs, M = 192 rows]: xa [R, K], xb [R, M]
+    rng = np.random.default_rng(24)
+    R, K, M = 16, 256, 192
+    xa = (0.1 * rng.standard_normal((K, R))).astype(np.float16)
+    xb = (0.1 * rng.standard_normal((M, R))).astype(np.float16)
+    w = (0.02 * rng.standard_normal((M, K))).astype(np.float16)
+    factor = np.array([0.5, 1.0, 0, 0], dtype=np.float32)
+    t_w = ctx.from_numpy(w)
+    ctx.run(wrk.blend_lora(ctx.from_numpy(factor), ctx.from_numpy(xa), ctx.from_numpy(xb), t_w))
+    ref = w.copy()
+    oracle.blend_lora(factor, xa, xb, ref)
+    assert_close(t_w.numpy().reshape(ref.shape), ref, "blend_lora", max_abs=2e-3)
+    dense = 0.5 * xb.astype(np.float64) @ xa.astype(np.float64).T + w.astype(np.float64)
+    assert np.max(np.abs(ref.astype(np.float64) - dense)) < 1e-3
+    with pytest.raises(wrk.WrkError) as e:
+        wrk.blend_lora(ctx.from_numpy(factor), ctx.from_numpy(xa[:-1].copy()), ctx.from_numpy(xb), t_w)
+    assert e.value.status == -5
+
+
 @pytest.mark.parametrize("reversed_", [True, False])
 @pytest.mark.parametrize("per_token", [True, False])
 def test_token_shift(wrk, ctx, reversed_, per_token):

@@ -179,3 +179,38 @@ def test_softmax_against_dense_numpy():
     oracle.softmax(h)
     eh = np.exp(h64 - h64.max(axis=-1, keepdims=True))
     assert np.allclose(h.astype(np.float64), eh / eh.sum(axis=-1, keepdims=True), rtol=2e-3, atol=1e-7)
+
+
+def test_load_time_ops_against_dense_numpy():
+    # recenter / rms_norm (normalize.wgsl), embed (embed.wgsl), broadcast (reshape.wgsl), blend, blend_lora
+    rng = np.random.default_rng(9)
+    x = (rng.standard_normal((2, 3, 256)) + 0.5).astype(np.float32)
+    got = x.copy()
+    oracle.recenter(got)
+    assert np.allclose(got, x - x.mean(axis=-1, keepdims=True), atol=1e-5)
+    w = (1 + 0.02 * rng.standard_normal(256)).astype(np.float16)
+    b = (0.02 * rng.standard_normal(256)).astype(np.float16)
+    got = x.copy()
+    oracle.rms_norm(w, b, got, 1e-5)
+    x64 = x.astype(np.float64)
+    want = x64 / np.sqrt((x64 ** 2).mean(axis=-1, keepdims=True) + 1e-5) * w.astype(np.float64) + b.astype(np.float64)
+    assert np.allclose(got, want, atol=1e-5)
+    emb = rng.standard_normal((50, 64)).astype(np.float16)
+    tokens = rng.integers(0, 50, (2, 5)).astype(np.uint32)
+    out = np.zeros((2, 5, 64), dtype=np.float32)
+    oracle.embed(tokens, emb, out)
+    assert np.array_equal(out, emb[tokens].astype(np.float32))
+    src = rng.standard_normal((2, 3, 64)).astype(np.float16)
+    dst = np.zeros((4, 6, 64), dtype=np.float16)
+    oracle.broadcast(src, dst)
+    assert np.array_equal(dst, np.tile(src, (2, 2, 1)))
+    a, o = rng.standard_normal((3, 64)).astype(np.float32), rng.standard_normal((3, 64)).astype(np.float32)
+    want = np.float32(0.25) * a + np.float32(0.75) * o
+    oracle.blend([0.25, 0.75, 0, 0], a, o)
+    assert np.array_equal(o, want)
+    xa = (0.1 * rng.standard_normal((32, 8))).astype(np.float16)
+    xb = (0.1 * rng.standard_normal((24, 8))).astype(np.float16)
+    m = (0.02 * rng.standard_normal((24, 32))).astype(np.float16)
+    want = 2.0 * xb.astype(np.float64) @ xa.astype(np.float64).T + 0.5 * m.astype(np.float64)
+    oracle.blend_lora([2.0, 0.5, 0, 0], xa, xb, m)
+    assert np.allclose(m.astype(np.float64), want, atol=1e-3)

@@ -314,6 +314,18 @@ def softmax(x):
     return _mk("wrk_op_softmax", _t(x), keep=(x,))
 
 
+def embed(tokens, input, output):
+    return _mk("wrk_op_embed", _t(tokens), _t(input), _t(output), keep=(tokens, input, output))
+
+
+def recenter(x):
+    return _mk("wrk_op_recenter", _t(x), keep=(x,))
+
+
+def rms_norm(w, b, x, eps):
+    return _mk("wrk_op_rms_norm", _t(w), _t(b), _t(x), ctypes.c_float(eps), keep=(w, b, x))
+
+
 def l2_norm(x, eps):
     return _mk("wrk_op_l2_norm", _t(x), ctypes.c_float(eps), keep=(x,))
 
@@ -360,6 +372,20 @@ def activate(x, act):
 def blit(input, output):
     (pi, ki), (po, ko) = _v(input), _v(output)
     return _mk("wrk_op_blit", pi, po, keep=(ki, ko))
+
+
+def broadcast(input, output):
+    (pi, ki), (po, ko) = _v(input), _v(output)
+    return _mk("wrk_op_broadcast", pi, po, keep=(ki, ko))
+
+
+def blend(factor, input, output):
+    return _mk("wrk_op_blend", _t(factor), _t(input), _t(output), keep=(factor, input, output))
+
+
+def blend_lora(factor, xa, xb, output):
+    (pa, ka), (pb, kb), (po, ko) = _v(xa), _v(xb), _v(output)
+    return _mk("wrk_op_blend_lora", _t(factor), pa, pb, po, keep=(factor, ka, kb, ko))
 
 
 def transpose(input, output):

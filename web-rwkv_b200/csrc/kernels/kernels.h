@@ -64,6 +64,14 @@ cudaError_t layer_norm(const __half* w, const __half* b, int dtype, void* x, uin
                        uint32_t wrows, float eps, cudaStream_t stream);
 cudaError_t l2_norm(int dtype, void* x, uint32_t C, uint32_t rows, float eps, cudaStream_t stream);
 cudaError_t softmax(int dtype, void* x, uint32_t C, uint32_t rows, cudaStream_t stream);
+cudaError_t recenter(int dtype, void* x, uint32_t C, uint32_t rows, cudaStream_t stream);
+cudaError_t rms_norm(const __half* w, const __half* b, int dtype, void* x, uint32_t C, uint32_t rows, float eps,
+                     cudaStream_t stream);
+cudaError_t embed(const uint32_t* tokens, const __half* input, int dtype, void* output, uint32_t C, uint32_t rows,
+                  uint32_t vocab, int32_t* status, cudaStream_t stream);
+cudaError_t broadcast(DView input, DView output, cudaStream_t stream);
+cudaError_t blend(const float* factor, DView input, DView output, cudaStream_t stream);
+cudaError_t blend_lora(const float* factor, DView xa, DView xb, DView output, uint32_t K, cudaStream_t stream);
 cudaError_t token_shift(const uint32_t* cursors, int wide, DView time_mix, DView state, DView input, DView output,
                         int reversed, cudaStream_t stream);
 cudaError_t channel_mix(const uint32_t* cursors, int wide, DView state, int dtype, const void* r, const void* v,

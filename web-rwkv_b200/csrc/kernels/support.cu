@@ -71,6 +71,91 @@ __global__ void l2_norm_kernel(int dtype, void* x, uint32_t C, uint32_t rows, fl
     }
 }
 
+// normalize.wgsl recenter: x - mean(x) per row of C.
+__global__ void recenter_kernel(int dtype, void* x, uint32_t C, uint32_t rows) {
+    __shared__ float scratch[32];
+    for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const size_t base = (size_t)row * C;
+        float s = 0.f;
+        for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) s += dload(x, dtype, base + c);
+        const float mean = block_sum(s, scratch) / (float)C;
+        for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) dstore(x, dtype, base + c, dload(x, dtype, base + c) - mean);
+    }
+}
+
+// normalize.wgsl rms_norm: fma(x * rsqrt(mean x^2 + eps), w, b) per row of C.
+__global__ void rms_norm_kernel(const __half* w, const __half* b, int dtype, void* x, uint32_t C, uint32_t rows,
+                                float eps) {
+    __shared__ float scratch[32];
+    for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const size_t base = (size_t)row * C;
+        float s = 0.f;
+        for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) {
+            const float v = dload(x, dtype, base + c);
+            s += v * v;
+        }
+        const float norm = rsqrtf(block_sum(s, scratch) / (float)C + eps);
+        for (uint32_t c = threadIdx.x; c < C; c += blockDim.x)
+            dstore(x, dtype, base + c, fmaf(dload(x, dtype, base + c) * norm, __half2float(w[c]), __half2float(b[c])));
+    }
+}
+
+// embed.wgsl: output[:, t, b] = input[:, tokens[t, b]] (fp16 rows of the embedding matrix, widened if the output is f32).
+__global__ void embed_kernel(const uint32_t* tokens, const __half* input, int dtype, void* output, uint32_t C,
+                             uint32_t rows, uint32_t vocab, int32_t* status) {
+    for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const uint32_t tok = tokens[row];
+        if (tok >= vocab) {  // the reference reads out of bounds here; report instead
+            if (threadIdx.x == 0) atomicCAS(status, 0, WRK_ERR_BATCH_OUT_OF_RANGE);
+            continue;
+        }
+        const __half* src = input + (size_t)tok * C;
+        for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) dstore(output, dtype, (size_t)row * C + c, __half2float(src[c]));
+    }
+}
+
+// reshape.wgsl broadcast: output[c, t, b] = input[c, t % in.T, b % in.B].
+__global__ void broadcast_kernel(DView in, DView out) {
+    const uint32_t C = out.shape[0], T = out.shape[1], B = out.shape[2];
+    const size_t total = (size_t)C * T * B;
+    for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t c = o % C, t = (o / C) % T, b = o / ((size_t)C * T);
+        dstore(out.base, out.dtype, out.index(c, t, b),
+               dload(in.base, in.dtype, in.index(c, t % in.shape[1], b % in.shape[2])));
+    }
+}
+
+// blend.wgsl: output = factor[0] * input + factor[1] * output.
+__global__ void blend_kernel(const float* factor, DView in, DView out) {
+    const uint32_t C = out.shape[0], T = out.shape[1], B = out.shape[2];
+    const size_t total = (size_t)C * T * B;
+    const float fx = factor[0], fy = factor[1];
+    for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t c = o % C, t = (o / C) % T, b = o / ((size_t)C * T);
+        const size_t oi = out.index(c, t, b);
+        dstore(out.base, out.dtype, oi,
+               fx * dload(in.base, in.dtype, in.index(c, t, b)) + fy * dload(out.base, out.dtype, oi));
+    }
+}
+
+// blend_lora.wgsl: output[m, n, b] = factor[0] * sum_k xa[k, m, b] * xb[k, n, b] + factor[1] * output[m, n, b], all fp16
+// tensors, f32 sum over the common rank K.  One warp per 32 consecutive m of one n: lanes read xa rows, xb's row of K
+// is shared by the warp.
+__global__ void blend_lora_kernel(const float* factor, DView xa, DView xb, DView out, uint32_t K) {
+    const uint32_t M = out.shape[0], N = out.shape[1], B = out.shape[2];
+    const size_t total = (size_t)M * N * B;
+    const float fx = factor[0], fy = factor[1];
+    for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t m = o % M, n = (o / M) % N, b = o / ((size_t)M * N);
+        const __half* a = static_cast<const __half*>(xa.base) + xa.index(0, m, b);
+        const __half* bb = static_cast<const __half*>(xb.base) + xb.index(0, n, b);
+        float sum = 0.f;
+        for (uint32_t k = 0; k < K; ++k) sum = fmaf(__half2float(a[k]), __half2float(bb[k]), sum);
+        const size_t oi = out.index(m, n, b);
+        dstore(out.base, out.dtype, oi, fx * sum + fy * dload(out.base, out.dtype, oi));
+    }
+}
+
 // softmax.wgsl: x <- exp(x - max) / sum exp(x - max) per row of C (two reductions, then the write).
 __global__ void softmax_kernel(int dtype, void* x, uint32_t C, uint32_t rows) {
     __shared__ float scratch[32];
@@ -218,6 +303,52 @@ cudaError_t softmax(int dtype, void* x, uint32_t C, uint32_t rows, cudaStream_t 
     const int block = C <= 256 ? 32 : C <= 4096 ? 256 : 1024;
     const uint32_t grid = rows < 148u * 32u ? rows : 148u * 32u;
     softmax_kernel<<<grid, block, 0, stream>>>(dtype, x, C, rows);
+    return cudaGetLastError();
+}
+
+cudaError_t recenter(int dtype, void* x, uint32_t C, uint32_t rows, cudaStream_t stream) {
+    if (rows == 0 || C == 0) return cudaSuccess;
+    const int block = C <= 256 ? 32 : 256;
+    const uint32_t grid = rows < 148u * 32u ? rows : 148u * 32u;
+    recenter_kernel<<<grid, block, 0, stream>>>(dtype, x, C, rows);
+    return cudaGetLastError();
+}
+
+cudaError_t rms_norm(const __half* w, const __half* b, int dtype, void* x, uint32_t C, uint32_t rows, float eps,
+                     cudaStream_t stream) {
+    if (rows == 0 || C == 0) return cudaSuccess;
+    const int block = C <= 256 ? 32 : 256;
+    const uint32_t grid = rows < 148u * 32u ? rows : 148u * 32u;
+    rms_norm_kernel<<<grid, block, 0, stream>>>(w, b, dtype, x, C, rows, eps);
+    return cudaGetLastError();
+}
+
+cudaError_t embed(const uint32_t* tokens, const __half* input, int dtype, void* output, uint32_t C, uint32_t rows,
+                  uint32_t vocab, int32_t* status, cudaStream_t stream) {
+    if (rows == 0 || C == 0) return cudaSuccess;
+    const uint32_t grid = rows < 148u * 32u ? rows : 148u * 32u;
+    embed_kernel<<<grid, 256, 0, stream>>>(tokens, input, dtype, output, C, rows, vocab, status);
+    return cudaGetLastError();
+}
+
+cudaError_t broadcast(DView input, DView output, cudaStream_t stream) {
+    const size_t total = (size_t)output.shape[0] * output.shape[1] * output.shape[2];
+    if (total == 0) return cudaSuccess;
+    broadcast_kernel<<<ew_grid(total), kEw, 0, stream>>>(input, output);
+    return cudaGetLastError();
+}
+
+cudaError_t blend(const float* factor, DView input, DView output, cudaStream_t stream) {
+    const size_t total = (size_t)output.shape[0] * output.shape[1] * output.shape[2];
+    if (total == 0) return cudaSuccess;
+    blend_kernel<<<ew_grid(total), kEw, 0, stream>>>(factor, input, output);
+    return cudaGetLastError();
+}
+
+cudaError_t blend_lora(const float* factor, DView xa, DView xb, DView output, uint32_t K, cudaStream_t stream) {
+    const size_t total = (size_t)output.shape[0] * output.shape[1] * output.shape[2];
+    if (total == 0) return cudaSuccess;
+    blend_lora_kernel<<<ew_grid(total), kEw, 0, stream>>>(factor, xa, xb, output, K);
     return cudaGetLastError();
 }
 

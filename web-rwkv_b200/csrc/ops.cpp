@@ -480,6 +480,55 @@ int32_t wrk_op_softmax(wrk_tensor* x, wrk_op** out) {
     return WRK_OK;
 }
 
+int32_t wrk_op_recenter(wrk_tensor* x, wrk_op** out) {
+    REQ_NN(x, out);
+    REQ_FLOAT(x, "x");
+    const Shape4 sh = x->shape;
+    void* xp = x->ptr();
+    const int dt = x->dtype;
+    const uint32_t C = sh[0], rows = sh[1] * sh[2];
+    *out = new_atom("recenter", [=](cudaStream_t s) { return k::recenter(dt, xp, C, rows, s); }, {x});
+    return WRK_OK;
+}
+
+int32_t wrk_op_rms_norm(wrk_tensor* w, wrk_tensor* b, wrk_tensor* x, float eps, wrk_op** out) {
+    REQ_NN(w, b, x, out);
+    REQ_FLOAT(x, "x");
+    REQ_DTYPE(w, WRK_F16, "w");
+    REQ_DTYPE(b, WRK_F16, "b");
+    const Shape4 sh = x->shape;
+    WRK_TRY(check_shape("x", sh, sh[0], sh[1], sh[2], 1));
+    WRK_TRY(check_shape("w", w->shape, sh[0], 1, 1, 1));
+    WRK_TRY(check_shape("b", b->shape, sh[0], 1, 1, 1));
+    const __half* wp = static_cast<const __half*>(w->ptr());
+    const __half* bp = static_cast<const __half*>(b->ptr());
+    void* xp = x->ptr();
+    const int dt = x->dtype;
+    const uint32_t C = sh[0], rows = sh[1] * sh[2];
+    *out = new_atom("rms_norm", [=](cudaStream_t s) { return k::rms_norm(wp, bp, dt, xp, C, rows, eps, s); }, {w, b, x});
+    return WRK_OK;
+}
+
+int32_t wrk_op_embed(wrk_tensor* tokens, wrk_tensor* input, wrk_tensor* output, wrk_op** out) {
+    REQ_NN(tokens, input, output, out);
+    REQ_DTYPE(tokens, WRK_U32, "tokens");
+    REQ_DTYPE(input, WRK_F16, "input");
+    REQ_FLOAT(output, "output");
+    const Shape4 sh = output->shape;
+    WRK_TRY(check_shape("tokens", tokens->shape, sh[1], sh[2], 1, 1));
+    WRK_TRY(check_shape("input", input->shape, sh[0], input->shape[1], 1, 1));
+    WRK_TRY(check_shape("output", sh, sh[0], sh[1], sh[2], 1));
+    const uint32_t* tp = static_cast<const uint32_t*>(tokens->ptr());
+    const __half* ip = static_cast<const __half*>(input->ptr());
+    void* op = output->ptr();
+    const int dt = output->dtype;
+    const uint32_t C = sh[0], rows = sh[1] * sh[2], vocab = input->shape[1];
+    int32_t* status = output->ctx->device_status;
+    *out = new_atom("embed", [=](cudaStream_t s) { return k::embed(tp, ip, dt, op, C, rows, vocab, status, s); },
+                    {tokens, input, output});
+    return WRK_OK;
+}
+
 int32_t wrk_op_l2_norm(wrk_tensor* x, float eps, wrk_op** out) {
     REQ_NN(x, out);
     REQ_FLOAT(x, "x");
@@ -593,6 +642,53 @@ int32_t wrk_op_blit(const wrk_view* input, const wrk_view* output, wrk_op** out)
     WRK_TRY(check_view("input", input, output->shape[0], output->shape[1], output->shape[2], output->shape[3]));
     DView in = make_dview(*input), o = make_dview(*output);
     *out = new_atom("blit", [=](cudaStream_t s) { return k::blit(in, o, 0, s); }, {input->tensor, output->tensor});
+    return WRK_OK;
+}
+
+int32_t wrk_op_broadcast(const wrk_view* input, const wrk_view* output, wrk_op** out) {
+    REQ_NN(input, input->tensor, output, output->tensor, out);
+    REQ_FLOAT(input->tensor, "input");
+    REQ_FLOAT(output->tensor, "output");
+    WRK_TRY(check_view("input", input, output->shape[0], input->shape[1], input->shape[2], 1));
+    WRK_REQUIRE(input->shape[1] > 0 && input->shape[2] > 0, WRK_ERR_EMPTY, "input is empty");
+    DView in = make_dview(*input), o = make_dview(*output);
+    *out = new_atom("broadcast", [=](cudaStream_t s) { return k::broadcast(in, o, s); }, {input->tensor, output->tensor});
+    return WRK_OK;
+}
+
+int32_t wrk_op_blend(wrk_tensor* factor, wrk_tensor* input, wrk_tensor* output, wrk_op** out) {
+    REQ_NN(factor, input, output, out);
+    REQ_DTYPE(factor, WRK_F32, "factor");
+    REQ_FLOAT(input, "input");
+    REQ_FLOAT(output, "output");
+    const Shape4 sh = output->shape;
+    WRK_TRY(check_shape("input", input->shape, sh[0], sh[1], sh[2], sh[3]));
+    WRK_TRY(check_shape("factor", factor->shape, 4, 1, 1, 1));
+    wrk_view iv, ov;
+    WRK_TRY(wrk_tensor_as_view(input, &iv));
+    WRK_TRY(wrk_tensor_as_view(output, &ov));
+    DView in = make_dview(iv), o = make_dview(ov);
+    const float* fp = static_cast<const float*>(factor->ptr());
+    *out = new_atom("blend", [=](cudaStream_t s) { return k::blend(fp, in, o, s); }, {factor, input, output});
+    return WRK_OK;
+}
+
+int32_t wrk_op_blend_lora(wrk_tensor* factor, const wrk_view* xa, const wrk_view* xb, const wrk_view* output,
+                          wrk_op** out) {
+    REQ_NN(factor, xa, xa->tensor, xb, xb->tensor, output, output->tensor, out);
+    REQ_DTYPE(factor, WRK_F32, "factor");
+    REQ_DTYPE(xa->tensor, WRK_F16, "xa");
+    REQ_DTYPE(xb->tensor, WRK_F16, "xb");
+    REQ_DTYPE(output->tensor, WRK_F16, "output");
+    WRK_TRY(check_shape("factor", factor->shape, 4, 1, 1, 1));
+    WRK_TRY(check_view("xa", xa, xa->shape[0], output->shape[0], output->shape[2], 1));
+    WRK_TRY(check_view("xb", xb, xb->shape[0], output->shape[1], output->shape[2], 1));
+    // the shader sums over min(K_a, K_b) / 4 groups of four
+    const uint32_t K = std::min(xa->shape[0] / 4, xb->shape[0] / 4) * 4;
+    DView a = make_dview(*xa), b = make_dview(*xb), o = make_dview(*output);
+    const float* fp = static_cast<const float*>(factor->ptr());
+    *out = new_atom("blend_lora", [=](cudaStream_t s) { return k::blend_lora(fp, a, b, o, K, s); },
+                    {factor, xa->tensor, xb->tensor, output->tensor});
     return WRK_OK;
 }
 
