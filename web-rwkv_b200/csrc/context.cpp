@@ -532,4 +532,9 @@ extern "C" int32_t wrk_debug_trace_read(unsigned long long* host, unsigned int* 
     WRK_CUDA(wrk::k::debug_trace_read(host, n));
     return WRK_OK;
 }
+namespace wrk { namespace k { cudaError_t debug_utrace_read(unsigned long long* host, unsigned int* n); } }
+extern "C" int32_t wrk_debug_utrace_read(unsigned long long* host, unsigned int* n) {
+    WRK_CUDA(wrk::k::debug_utrace_read(host, n));
+    return WRK_OK;
+}
 #endif

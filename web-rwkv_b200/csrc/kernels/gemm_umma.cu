@@ -142,6 +142,27 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 
 __device__ __forceinline__ uint32_t pack_half2(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
 
+// Optional timeline (builds with -DWRK_TRACE only): CTA (0, 0, 0) appends (stamp id, globaltimer ns) pairs to a
+// global log that the host reads back.
+#ifdef WRK_TRACE
+__device__ unsigned long long g_utrace[1 << 14];
+__device__ unsigned int g_utrace_n;
+__device__ __forceinline__ void utrace(uint32_t id) {
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        const unsigned int i = atomicAdd(&g_utrace_n, 1u);
+        if (i < (1u << 13)) {
+            g_utrace[2 * i] = id;
+            g_utrace[2 * i + 1] = t;
+        }
+    }
+}
+#define UTRACE(id) utrace(id)
+#else
+#define UTRACE(id)
+#endif
+
 
 // 32 (Int8) weights of one row, raw bytes in `q0, q1`, block scale (min, max) -> four 16-byte groups of fp16.
 __device__ __forceinline__ void dequant_int8(uint4 q0, uint4 q1, uint32_t minmax, uint4 out[4]) {
@@ -203,6 +224,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
     const uint32_t nk = (uint32_t)((uint64_t)nk_all * (blockIdx.z + 1) / p.splits) - k_begin;
     __shared__ uint32_t is_last_split;
 
+    if (threadIdx.x == 0) UTRACE(1);
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.stages; ++s) {
             mbar_init(&ab_full[s], quantized ? kDequantWarps + 1 : 2);  // dequant warps (or the weight TMA) + activation TMA
@@ -226,6 +248,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_d = tmem_base_slot;
+    if (threadIdx.x == 0) UTRACE(2);
 
     if (warp < kDequantWarps) {
         if (quantized) {
@@ -249,6 +272,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
                 }
                 const uint32_t r = kt % p.raw, ruse = kt / p.raw;
                 mbar_wait(&raw_full[r], ruse & 1, &abort_flag, p.status);
+                if (threadIdx.x == 0) UTRACE(1000 + kt);
                 const uint8_t* rs = raw_base + (size_t)r * raw_bytes + row * raw_row + half * (raw_row / 2);
                 uint4 q0 = *reinterpret_cast<const uint4*>(rs), q1 = make_uint4(0, 0, 0, 0);
                 if (p.kind == MAT_INT8) q1 = *reinterpret_cast<const uint4*>(rs + 16);
@@ -269,11 +293,13 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
                 fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ab_full[s]);
+                if (threadIdx.x == 0) UTRACE(2000 + kt);
             }
         }
         // ---- epilogue: TMEM -> registers -> activation -> token-major rows ----
         mbar_wait(&done_bar, 0, &abort_flag, p.status);
         tc_fence_after();
+        if (threadIdx.x == 0) UTRACE(3);
         const uint32_t quad = warp & 3, side = warp >> 2;  // lanes 32 quad .., half of the columns each
         const uint32_t m = m0 + quad * 32 + lane;
         const uint32_t c_begin = side * (p.n_tile / 2), c_end = c_begin + p.n_tile / 2;
@@ -296,6 +322,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
             }
         }
         if (p.splits > 1) __threadfence();
+        if (threadIdx.x == 0) UTRACE(4);
     } else if (warp == kMmaWarp) {
         // ---- MMA issuer ----
         const uint32_t idesc = f16_idesc(BM, p.n_tile);
@@ -303,6 +330,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
             const uint32_t s = kt % p.stages, use = kt / p.stages;
             mbar_wait(&ab_full[s], use & 1, &abort_flag, p.status);
             tc_fence_after();
+            if (lane == 0) UTRACE(3000 + kt);
             if (lane == 0) {
                 const uint32_t sa = smem_addr(smem + (size_t)s * stage_bytes);
                 const uint64_t da = sw128_desc(sa), db = sw128_desc(sa + A_STAGE_BYTES);
@@ -349,6 +377,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_d), "r"(p.tmem_cols) : "memory");
     }
+    if (threadIdx.x == 0) UTRACE(5);
     if (p.splits > 1) {
         // the CTA that arrives last at the tile's counter adds the partial tiles and finishes the outputs
         const uint32_t tile = blockIdx.y * gridDim.x + blockIdx.x;
@@ -389,6 +418,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
             }
         }
     }
+    if (threadIdx.x == 0) UTRACE((p.splits > 1 && is_last_split) ? 7 : 6);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -421,6 +451,17 @@ bool make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uin
 }
 
 }  // namespace
+
+#ifdef WRK_TRACE
+cudaError_t debug_utrace_read(unsigned long long* host, unsigned int* n) {
+    cudaError_t e = cudaMemcpyFromSymbol(n, g_utrace_n, sizeof(unsigned int));
+    if (e != cudaSuccess) return e;
+    e = cudaMemcpyFromSymbol(host, g_utrace, sizeof(unsigned long long) * (1 << 14));
+    unsigned int zero = 0;
+    cudaMemcpyToSymbol(g_utrace_n, &zero, sizeof zero);
+    return e;
+}
+#endif
 
 bool matmul_umma_supported(const MatmulArgs& a) {
     if (a.B != 1 || a.N < 16 || a.M == 0) return false;
