@@ -50,9 +50,7 @@ struct UmmaParams {
     uint32_t tmem_cols; // power of two >= max(32, n_tile)
     uint32_t stages;    // operand stages
     uint32_t raw;       // raw weight stages (quantized kinds)
-    uint32_t splits;    // CTAs along K per output tile (grid.z)
-    float* ws;          // [tile][split][n_tile][128] partial accumulators (splits > 1)
-    uint32_t* counters; // [tile] arrivals
+    uint32_t splits;    // CTAs along K per output tile (grid.z = the cluster's size)
     int32_t* status;
 };
 
@@ -140,6 +138,28 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t v[8]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 
+// Thread-block cluster: hardware barrier over all threads of all CTAs of the cluster, and 16-byte loads from
+// a peer CTA's shared memory.
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ float4 ld_peer_smem(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];\n"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(remote)
+                 : "memory");
+    return v;
+}
+
 __device__ __forceinline__ uint32_t pack_half2(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
 
 // Optional timeline (builds with -DWRK_TRACE only): CTA (0, 0, 0) appends (stamp id, globaltimer ns) pairs to a
@@ -222,7 +242,6 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
     const uint32_t nk_all = p.K / BK;
     const uint32_t k_begin = (uint32_t)((uint64_t)nk_all * blockIdx.z / p.splits);
     const uint32_t nk = (uint32_t)((uint64_t)nk_all * (blockIdx.z + 1) / p.splits) - k_begin;
-    __shared__ uint32_t is_last_split;
 
     if (threadIdx.x == 0) UTRACE(1);
     if (threadIdx.x == 0) {
@@ -272,7 +291,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
                 }
                 const uint32_t r = kt % p.raw, ruse = kt / p.raw;
                 mbar_wait(&raw_full[r], ruse & 1, &abort_flag, p.status);
-                if (threadIdx.x == 0) UTRACE(1000 + kt);
+                if (threadIdx.x == 0 && (kt == 0 || kt + 1 == nk)) UTRACE(1000 + kt);
                 const uint8_t* rs = raw_base + (size_t)r * raw_bytes + row * raw_row + half * (raw_row / 2);
                 uint4 q0 = *reinterpret_cast<const uint4*>(rs), q1 = make_uint4(0, 0, 0, 0);
                 if (p.kind == MAT_INT8) q1 = *reinterpret_cast<const uint4*>(rs + 16);
@@ -293,7 +312,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
                 fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ab_full[s]);
-                if (threadIdx.x == 0) UTRACE(2000 + kt);
+                if (threadIdx.x == 0 && (kt == 0 || kt + 1 == nk)) UTRACE(2000 + kt);
             }
         }
         // ---- epilogue: TMEM -> registers -> activation -> token-major rows ----
@@ -303,25 +322,33 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
         const uint32_t quad = warp & 3, side = warp >> 2;  // lanes 32 quad .., half of the columns each
         const uint32_t m = m0 + quad * 32 + lane;
         const uint32_t c_begin = side * (p.n_tile / 2), c_end = c_begin + p.n_tile / 2;
-        const uint32_t tile = blockIdx.y * gridDim.x + blockIdx.x;
-        float* ws_mine = p.ws + ((size_t)tile * p.splits + blockIdx.z) * p.n_tile * BM;
-        for (uint32_t c = c_begin; c < c_end; c += 8) {
-            uint32_t v[8];
-            tmem_ld8(tmem_d + ((quad * 32) << 16) + c, v);
+        // split K: the partial tile goes to this CTA's own shared memory (the operand stages are free once every
+        // MMA has completed), column-major [n_tile][BM] floats, for the cluster-wide sum below
+        float* ws_mine = reinterpret_cast<float*>(smem);
+        // up to four 8-column accumulator loads are in flight before the single wait
+        for (uint32_t c0 = c_begin; c0 < c_end; c0 += 32) {
+            uint32_t v[4][8];
+#pragma unroll
+            for (uint32_t q = 0; q < 4; ++q)
+                if (c0 + 8 * q < c_end) tmem_ld8(tmem_d + ((quad * 32) << 16) + c0 + 8 * q, v[q]);
             tmem_ld_wait();
-            if (p.splits > 1) {
-                // partial sums, column-major inside the tile so that a warp writes 128 contiguous bytes
 #pragma unroll
-                for (int j = 0; j < 8; ++j) ws_mine[(size_t)(c + j) * BM + quad * 32 + lane] = __uint_as_float(v[j]);
-            } else if (m < p.M) {
+            for (uint32_t q = 0; q < 4; ++q) {
+                const uint32_t c = c0 + 8 * q;
+                if (c >= c_end) continue;
+                if (p.splits > 1) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const uint32_t n = n0 + c + j;
-                    if (n < p.N) dstore(p.out.base, p.out.dtype, p.out.index(m, n, 0), activate_f(p.act, __uint_as_float(v[j])));
+                    for (int j = 0; j < 8; ++j) ws_mine[(size_t)(c + j) * BM + quad * 32 + lane] = __uint_as_float(v[q][j]);
+                } else if (m < p.M) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint32_t n = n0 + c + j;
+                        if (n < p.N)
+                            dstore(p.out.base, p.out.dtype, p.out.index(m, n, 0), activate_f(p.act, __uint_as_float(v[q][j])));
+                    }
                 }
             }
         }
-        if (p.splits > 1) __threadfence();
         if (threadIdx.x == 0) UTRACE(4);
     } else if (warp == kMmaWarp) {
         // ---- MMA issuer ----
@@ -330,7 +357,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
             const uint32_t s = kt % p.stages, use = kt / p.stages;
             mbar_wait(&ab_full[s], use & 1, &abort_flag, p.status);
             tc_fence_after();
-            if (lane == 0) UTRACE(3000 + kt);
+            if (lane == 0 && (kt == 0 || kt + 1 == nk)) UTRACE(3000 + kt);
             if (lane == 0) {
                 const uint32_t sa = smem_addr(smem + (size_t)s * stage_bytes);
                 const uint64_t da = sw128_desc(sa), db = sw128_desc(sa + A_STAGE_BYTES);
@@ -379,37 +406,47 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
     }
     if (threadIdx.x == 0) UTRACE(5);
     if (p.splits > 1) {
-        // the CTA that arrives last at the tile's counter adds the partial tiles and finishes the outputs
-        const uint32_t tile = blockIdx.y * gridDim.x + blockIdx.x;
-        if (threadIdx.x == 0) {
-            const uint32_t prev = atomicAdd(&p.counters[tile], 1u);
-            is_last_split = prev == p.splits - 1 ? 1u : 0u;
-            if (is_last_split) p.counters[tile] = 0;  // ready for the next launch on the stream
-        }
-        __syncthreads();
-        if (is_last_split && warp < kDequantWarps) {
-            __threadfence();
-            const float* ws_tile = p.ws + (size_t)tile * p.splits * p.n_tile * BM;
-            // thread: four consecutive rows (one 16-byte load per partial tile) of every eighth column
-            const uint32_t row = (threadIdx.x & 31) * 4, m = m0 + row;
-            for (uint32_t c0 = threadIdx.x >> 5; c0 < p.n_tile; c0 += 32) {
-                float4 sum[4];
+        // The CTAs of a cluster hold the partial tiles of one output tile.  After the cluster barrier CTA r adds
+        // its share of the columns over all peers (in rank order: the sum does not depend on timing), through
+        // distributed shared memory, and finishes those outputs.  The second barrier keeps every CTA's shared
+        // memory alive until its peers have read it.  Both are hardware barriers that every thread reaches, also
+        // after a wait above has given up.
+        cluster_sync();
+        if (threadIdx.x == 0) UTRACE(8);
+        const uint32_t rank = cluster_rank();
+        if (warp < kDequantWarps) {
+            constexpr uint32_t kGroups = 4, kReduceThreads = kDequantWarps * 32;
+            const uint32_t c_lo = p.n_tile * rank / p.splits, c_hi = p.n_tile * (rank + 1) / p.splits;
+            const uint32_t v_lo = c_lo * (BM / 4), v_hi = c_hi * (BM / 4);  // groups of four rows
+            const uint32_t base_addr = smem_addr(smem);
+            for (uint32_t base = v_lo; base < v_hi; base += kGroups * kReduceThreads) {
+                float4 sum[kGroups];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) sum[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (uint32_t z = 0; z < p.splits; ++z) {
+                for (uint32_t u = 0; u < kGroups; ++u) sum[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (uint32_t z0 = 0; z0 < p.splits; z0 += 4) {
+                    float4 v[kGroups][4];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const uint32_t c = c0 + 8 * u;
-                        if (c < p.n_tile) {
-                            const float4 v = *reinterpret_cast<const float4*>(ws_tile + ((size_t)z * p.n_tile + c) * BM + row);
-                            sum[u].x += v.x, sum[u].y += v.y, sum[u].z += v.z, sum[u].w += v.w;
+                    for (uint32_t u = 0; u < kGroups; ++u) {
+                        const uint32_t pos = base + u * kReduceThreads + threadIdx.x;
+#pragma unroll
+                        for (uint32_t dz = 0; dz < 4; ++dz) {
+                            v[u][dz] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (pos < v_hi && z0 + dz < p.splits) v[u][dz] = ld_peer_smem(base_addr + pos * 16, z0 + dz);
                         }
                     }
+#pragma unroll
+                    for (uint32_t u = 0; u < kGroups; ++u)
+#pragma unroll
+                        for (uint32_t dz = 0; dz < 4; ++dz)
+                            sum[u].x += v[u][dz].x, sum[u].y += v[u][dz].y, sum[u].z += v[u][dz].z, sum[u].w += v[u][dz].w;
                 }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const uint32_t n = n0 + c0 + 8 * u;
-                    if (c0 + 8 * u >= p.n_tile || n >= p.N) continue;
+                for (uint32_t u = 0; u < kGroups; ++u) {
+                    const uint32_t pos = base + u * kReduceThreads + threadIdx.x;
+                    if (pos >= v_hi) continue;
+                    const uint32_t c = pos / (BM / 4), row = (pos % (BM / 4)) * 4;
+                    const uint32_t n = n0 + c, m = m0 + row;
+                    if (n >= p.N) continue;
                     const float r4[4] = {sum[u].x, sum[u].y, sum[u].z, sum[u].w};
 #pragma unroll
                     for (int e = 0; e < 4; ++e)
@@ -417,8 +454,9 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
                 }
             }
         }
+        cluster_sync();
     }
-    if (threadIdx.x == 0) UTRACE((p.splits > 1 && is_last_split) ? 7 : 6);
+    if (threadIdx.x == 0) UTRACE(7);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -502,7 +540,6 @@ cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t strea
         else if (p.raw > 2) --p.raw;
         else break;
     }
-    const size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.raw * raw_bytes + 2 * SCALE_SLOT_BYTES + 1024;
 
     CUtensorMap map_w, map_x;
     bool ok;
@@ -524,29 +561,40 @@ cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t strea
         configured = true;
     }
     dim3 grid((a.M + BM - 1) / BM, (a.N + p.n_tile - 1) / p.n_tile, 1);
-    // split K across CTAs while the output tiles alone leave SMs idle: each split keeps at least eight steps
-    // (a multiple of four, so scale slots stay aligned) and its partial tile must fit the scratch
+    // split K across the CTAs of a thread-block cluster while the output tiles alone leave SMs idle: each split
+    // keeps at least eight steps (a multiple of four, so scale slots stay aligned); at most 8 CTAs per cluster
     p.splits = 1;
     const uint32_t tiles = grid.x * grid.y;
-    if (a.ws != nullptr && a.counters != nullptr && tiles <= a.num_counters) {
+    {
         int sms = 148, device = 0;
         if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
         uint32_t want = std::max<uint32_t>(1, (uint32_t)sms / tiles);
         want = std::min<uint32_t>(want, std::max<uint32_t>(1, nk / 8));
-        want = std::min<uint32_t>(want, 16);
-        while (want > 1 && (nk % (4 * want) != 0 || (size_t)tiles * want * p.n_tile * BM * sizeof(float) > a.ws_bytes)) --want;
+        want = std::min<uint32_t>(want, 8);
+        while (want > 1 && nk % (4 * want) != 0) --want;
         p.splits = want;
     }
-    p.ws = a.ws;
-    p.counters = a.counters;
     grid.z = p.splits;
     if (p.splits > 1) {
         const uint32_t nk_split = nk / p.splits;
         p.stages = std::min<uint32_t>(p.stages, std::max<uint32_t>(2, nk_split));
         if (p.raw) p.raw = std::min<uint32_t>(p.raw, std::max<uint32_t>(2, nk_split));
     }
-    matmul_umma_kernel<<<grid, kUmmaThreads, smem, stream>>>(p, map_w, map_x);
-    return cudaGetLastError();
+    size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.raw * raw_bytes + 2 * SCALE_SLOT_BYTES + 1024;
+    if (p.splits > 1) smem = std::max<size_t>(smem, (size_t)p.n_tile * BM * sizeof(float) + 1024);  // the partial tile
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kUmmaThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = p.splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, matmul_umma_kernel, p, map_w, map_x);
 }
 
 }  // namespace k
