@@ -92,16 +92,7 @@ struct wrk_context {
     int32_t* host_status = nullptr;    // pinned mirror for reads
     std::atomic<uint64_t> launches{0};
     std::mutex mutex;
-    // scratch of the split-K GEMM (allocated on first use, shared by every GEMM of the stream)
-    float* gemm_ws = nullptr;
-    uint32_t* gemm_counters = nullptr;  // one arrival counter per output tile, zero between launches
 };
-namespace wrk {
-constexpr size_t kGemmWorkspaceBytes = (size_t)64 << 20;
-constexpr uint32_t kGemmCounters = 16384;
-// Allocates the context's GEMM scratch if it does not exist yet.
-int32_t ensure_gemm_workspace(wrk_context* ctx);
-}  // namespace wrk
 
 struct wrk_tensor {
     std::atomic<int> refs{1};

@@ -29,16 +29,6 @@ Buffer::~Buffer() {
     }
 }
 
-int32_t ensure_gemm_workspace(wrk_context* ctx) {
-    std::lock_guard<std::mutex> lock(ctx->mutex);
-    if (ctx->gemm_ws != nullptr) return WRK_OK;
-    WRK_CUDA(cudaSetDevice(ctx->device));
-    WRK_CUDA(cudaMalloc(&ctx->gemm_ws, kGemmWorkspaceBytes));
-    WRK_CUDA(cudaMalloc(&ctx->gemm_counters, kGemmCounters * sizeof(uint32_t)));
-    WRK_CUDA(cudaMemset(ctx->gemm_counters, 0, kGemmCounters * sizeof(uint32_t)));
-    return WRK_OK;
-}
-
 DView make_dview(const wrk_tensor* t) {
     DView d;
     d.base = t->ptr();
@@ -184,8 +174,6 @@ int32_t wrk_context_destroy(wrk_context* ctx) {
     cudaEventDestroy(ctx->ev_start);
     cudaEventDestroy(ctx->ev_stop);
     cudaFree(ctx->device_status);
-    if (ctx->gemm_ws) cudaFree(ctx->gemm_ws);
-    if (ctx->gemm_counters) cudaFree(ctx->gemm_counters);
     cudaFreeHost(ctx->host_status);
     cudaStreamDestroy(ctx->stream);
     delete ctx;

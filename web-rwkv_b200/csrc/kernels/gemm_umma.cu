@@ -279,7 +279,10 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
             const uint8_t* srow = reinterpret_cast<const uint8_t*>(p.scale) + ((size_t)m * (p.K / 256) + k_begin / 4) * 8;
             if (half == 0) cp_async8z(scale_base + row * 8, srow, m < p.M);
             asm volatile("cp.async.commit_group;\n" ::: "memory");
-            for (uint32_t kt = 0; kt < nk; ++kt) {
+            // two steps per turn: both raw tiles are read, dequantized and stored before the one proxy fence and
+            // the arrivals, which halves the synchronisation per weight and doubles the independent work in flight
+            for (uint32_t kt = 0; kt < nk; kt += 2) {
+                const bool two = kt + 1 < nk;
                 if ((kt & 3) == 0) {
                     const uint32_t j = kt >> 2;
                     __syncwarp();  // both threads of a row are done with the slot about to be refilled
@@ -289,30 +292,55 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
                     asm volatile("cp.async.wait_group 1;\n" ::: "memory");
                     __syncwarp();  // the sibling thread's copy is visible
                 }
-                const uint32_t r = kt % p.raw, ruse = kt / p.raw;
-                mbar_wait(&raw_full[r], ruse & 1, &abort_flag, p.status);
-                if (threadIdx.x == 0 && (kt == 0 || kt + 1 == nk)) UTRACE(1000 + kt);
-                const uint8_t* rs = raw_base + (size_t)r * raw_bytes + row * raw_row + half * (raw_row / 2);
-                uint4 q0 = *reinterpret_cast<const uint4*>(rs), q1 = make_uint4(0, 0, 0, 0);
-                if (p.kind == MAT_INT8) q1 = *reinterpret_cast<const uint4*>(rs + 16);
-                const uint8_t* ss = scale_base + ((kt >> 2) & 1) * SCALE_SLOT_BYTES + row * 8;
-                uint4 wv[4];
+                const uint32_t r0 = kt % p.raw, r1 = (kt + 1) % p.raw;
+                mbar_wait(&raw_full[r0], (kt / p.raw) & 1, &abort_flag, p.status);
+                if (two) mbar_wait(&raw_full[r1], ((kt + 1) / p.raw) & 1, &abort_flag, p.status);
+                if (threadIdx.x == 0 && (kt == 0 || kt + 2 >= nk)) UTRACE(1000 + kt);
+                const uint32_t roff = row * raw_row + half * (raw_row / 2);
+                const uint8_t* rs0 = raw_base + (size_t)r0 * raw_bytes + roff;
+                const uint8_t* rs1 = raw_base + (size_t)r1 * raw_bytes + roff;
+                uint4 qa0 = *reinterpret_cast<const uint4*>(rs0), qa1 = make_uint4(0, 0, 0, 0);
+                uint4 qb0 = make_uint4(0, 0, 0, 0), qb1 = make_uint4(0, 0, 0, 0);
+                if (two) qb0 = *reinterpret_cast<const uint4*>(rs1);
                 if (p.kind == MAT_INT8) {
-                    dequant_int8(q0, q1, *reinterpret_cast<const uint32_t*>(ss + ((kt >> 1) & 1) * 4), wv);
+                    qa1 = *reinterpret_cast<const uint4*>(rs0 + 16);
+                    if (two) qb1 = *reinterpret_cast<const uint4*>(rs1 + 16);
+                }
+                const uint8_t* ss = scale_base + ((kt >> 2) & 1) * SCALE_SLOT_BYTES + row * 8;
+                uint4 wa[4], wb[4];
+                if (p.kind == MAT_INT8) {
+                    // a 128-column block is two steps: kt (even) and kt + 1 share the block's (min, max)
+                    const uint32_t mm = *reinterpret_cast<const uint32_t*>(ss + ((kt >> 1) & 1) * 4);
+                    dequant_int8(qa0, qa1, mm, wa);
+                    dequant_int8(qb0, qb1, mm, wb);
                 } else {
-                    dequant_nf4(q0, __half2float(*reinterpret_cast<const __half*>(ss + (kt & 3) * 2)), lut2, wv);
+                    dequant_nf4(qa0, __half2float(*reinterpret_cast<const __half*>(ss + (kt & 3) * 2)), lut2, wa);
+                    dequant_nf4(qb0, __half2float(*reinterpret_cast<const __half*>(ss + ((kt + 1) & 3) * 2)), lut2, wb);
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&raw_empty[r]);  // the raw stage may be refilled
-                const uint32_t s = kt % p.stages, use = kt / p.stages;
-                if (use > 0) mbar_wait(&ab_empty[s], (use - 1) & 1, &abort_flag, p.status);
-                uint8_t* sa = smem + (size_t)s * stage_bytes;
+                if (lane == 0) {  // the raw stages may be refilled
+                    mbar_arrive(&raw_empty[r0]);
+                    if (two) mbar_arrive(&raw_empty[r1]);
+                }
+                const uint32_t s0 = kt % p.stages, use0 = kt / p.stages;
+                const uint32_t s1 = (kt + 1) % p.stages, use1 = (kt + 1) / p.stages;
+                if (use0 > 0) mbar_wait(&ab_empty[s0], (use0 - 1) & 1, &abort_flag, p.status);
+                if (two && use1 > 0) mbar_wait(&ab_empty[s1], (use1 - 1) & 1, &abort_flag, p.status);
+                uint8_t* sa0 = smem + (size_t)s0 * stage_bytes;
+                uint8_t* sa1 = smem + (size_t)s1 * stage_bytes;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(sa + sw128_offset(row, half * 4 + j)) = wv[j];
+                for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(sa0 + sw128_offset(row, half * 4 + j)) = wa[j];
+                if (two) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(sa1 + sw128_offset(row, half * 4 + j)) = wb[j];
+                }
                 fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&ab_full[s]);
-                if (threadIdx.x == 0 && (kt == 0 || kt + 1 == nk)) UTRACE(2000 + kt);
+                if (lane == 0) {
+                    mbar_arrive(&ab_full[s0]);
+                    if (two) mbar_arrive(&ab_full[s1]);
+                }
+                if (threadIdx.x == 0 && (kt == 0 || kt + 2 >= nk)) UTRACE(2000 + kt);
             }
         }
         // ---- epilogue: TMEM -> registers -> activation -> token-major rows ----
@@ -414,8 +442,8 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
         cluster_sync();
         if (threadIdx.x == 0) UTRACE(8);
         const uint32_t rank = cluster_rank();
-        if (warp < kDequantWarps) {
-            constexpr uint32_t kGroups = 4, kReduceThreads = kDequantWarps * 32;
+        {
+            constexpr uint32_t kGroups = 4, kReduceThreads = kUmmaThreads;
             const uint32_t c_lo = p.n_tile * rank / p.splits, c_hi = p.n_tile * (rank + 1) / p.splits;
             const uint32_t v_lo = c_lo * (BM / 4), v_hi = c_hi * (BM / 4);  // groups of four rows
             const uint32_t base_addr = smem_addr(smem);
@@ -525,10 +553,32 @@ cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t strea
     p.out = a.out;
     p.act = a.act;
     p.status = status;
+    const uint32_t nk = a.K / BK;
+    // Output tiles are 128 rows x n_tile tokens; K is split across the CTAs of a thread-block cluster while the
+    // tiles alone leave SMs idle: a split keeps at least eight steps (a multiple of four, so scale slots stay
+    // aligned), a cluster at most 8 CTAs.  Up to 512 tokens, 128-token tiles replace 256-token ones when that
+    // doubles the CTAs of the single wave without lengthening a CTA's K walk: smaller operand stages (a deeper
+    // ring) and smaller partial tiles.  (Measured: 2048x2048 Int8, 256 tokens: 22.8 -> 15.9 us; where the K walk
+    // would double instead, 31 -> 37 us, so those keep 256.)
+    int sms = 148, device = 0;
+    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const uint32_t row_tiles = (a.M + BM - 1) / BM;
+    auto splits_for = [&](uint32_t n_tile) {
+        const uint32_t tiles = row_tiles * ((a.N + n_tile - 1) / n_tile);
+        uint32_t want = std::max<uint32_t>(1, (uint32_t)sms / tiles);
+        want = std::min<uint32_t>(want, std::max<uint32_t>(1, nk / 8));
+        want = std::min<uint32_t>(want, 8);
+        while (want > 1 && nk % (4 * want) != 0) --want;
+        return want;
+    };
     p.n_tile = std::min<uint32_t>(256, (a.N + 15) / 16 * 16);
+    p.splits = splits_for(p.n_tile);
+    if (p.n_tile > 128 && a.N <= 512) {
+        const uint32_t s2 = splits_for(128);
+        if (s2 >= p.splits && row_tiles * ((a.N + 127) / 128) * s2 <= (uint32_t)sms) p.n_tile = 128, p.splits = s2;
+    }
     p.tmem_cols = 32;
     while (p.tmem_cols < p.n_tile) p.tmem_cols *= 2;
-    const uint32_t nk = a.K / BK;
     const uint32_t stage_bytes = A_STAGE_BYTES + p.n_tile * BK * 2;
     const uint32_t raw_bytes = a.kind == MAT_INT8 ? BM * 64 : a.kind == MAT_NF4 ? BM * 32 : 0;
     const uint32_t budget = 200u * 1024;
@@ -561,19 +611,6 @@ cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t strea
         configured = true;
     }
     dim3 grid((a.M + BM - 1) / BM, (a.N + p.n_tile - 1) / p.n_tile, 1);
-    // split K across the CTAs of a thread-block cluster while the output tiles alone leave SMs idle: each split
-    // keeps at least eight steps (a multiple of four, so scale slots stay aligned); at most 8 CTAs per cluster
-    p.splits = 1;
-    const uint32_t tiles = grid.x * grid.y;
-    {
-        int sms = 148, device = 0;
-        if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-        uint32_t want = std::max<uint32_t>(1, (uint32_t)sms / tiles);
-        want = std::min<uint32_t>(want, std::max<uint32_t>(1, nk / 8));
-        want = std::min<uint32_t>(want, 8);
-        while (want > 1 && nk % (4 * want) != 0) --want;
-        p.splits = want;
-    }
     grid.z = p.splits;
     if (p.splits > 1) {
         const uint32_t nk_split = nk / p.splits;

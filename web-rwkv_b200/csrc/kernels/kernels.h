@@ -26,10 +26,6 @@ struct MatmulArgs {
     DView out;             // [M, N, B]
     int act;
     int32_t* status;       // device status word (bounded waits report here); may be null
-    float* ws;             // split-K scratch of the tensor-memory GEMM (null: no split)
-    size_t ws_bytes;
-    uint32_t* counters;    // zeroed arrival counters, one per output tile
-    uint32_t num_counters;
 };
 cudaError_t matmul(const MatmulArgs& a, int num_sms, cudaStream_t stream);
 // Tensor-memory (tcgen05) GEMM for N >= 16 tokens (gemm_umma.cu).

@@ -77,13 +77,6 @@ int32_t matmul_common(const char* name, int kind, wrk_tensor* matrix, wrk_tensor
     a.out = make_dview(*output);
     a.act = act;
     a.status = matrix->ctx->device_status;
-    if (n >= 16 && b == 1) {
-        WRK_TRY(wrk::ensure_gemm_workspace(matrix->ctx));
-        a.ws = matrix->ctx->gemm_ws;
-        a.ws_bytes = wrk::kGemmWorkspaceBytes;
-        a.counters = matrix->ctx->gemm_counters;
-        a.num_counters = wrk::kGemmCounters;
-    }
     const int sms = matrix->ctx->num_sms;
     // few tokens, fp16 activations, whole rows: the weight-streaming kernel of the decode path
     const uint32_t need = kind == k::MAT_FP16 ? 32 : 128;
