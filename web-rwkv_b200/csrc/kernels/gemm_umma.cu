@@ -236,7 +236,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
     const uint32_t raw_row = p.kind == MAT_INT8 ? 64u : 32u;                // raw bytes per row and step
     const uint32_t raw_bytes = BM * raw_row;
     uint8_t* raw_base = smem + (size_t)p.stages * stage_bytes;              // raw weight stages
-    uint8_t* scale_base = raw_base + (size_t)p.raw * raw_bytes;             // [2][BM][8 bytes]
+    uint8_t* scale_base = raw_base + (size_t)p.raw * raw_bytes;             // [2 groups][2 slots][BM][8 bytes]
     const uint32_t m0 = blockIdx.x * BM, n0 = blockIdx.y * p.n_tile;
     // this CTA's share of the K steps (split-K: grid.z CTAs per output tile)
     const uint32_t nk_all = p.K / BK;
@@ -246,12 +246,12 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
     if (threadIdx.x == 0) UTRACE(1);
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.stages; ++s) {
-            mbar_init(&ab_full[s], quantized ? kDequantWarps + 1 : 2);  // dequant warps (or the weight TMA) + activation TMA
+            mbar_init(&ab_full[s], quantized ? kDequantWarps / 2 + 1 : 2);  // one dequant group (or the weight TMA) + activation TMA
             mbar_init(&ab_empty[s], 1);
         }
         for (uint32_t r = 0; r < p.raw; ++r) {
             mbar_init(&raw_full[r], 1);
-            mbar_init(&raw_empty[r], kDequantWarps);
+            mbar_init(&raw_empty[r], kDequantWarps / 2);
         }
         mbar_init(&done_bar, 1);
         abort_flag = 0;
@@ -271,76 +271,57 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
 
     if (warp < kDequantWarps) {
         if (quantized) {
-            // ---- dequantizers: thread (row, half) owns 32 weights of a row per step ----
-            const uint32_t row = threadIdx.x >> 1, half = threadIdx.x & 1;
+            // ---- dequantizers: two groups of four warps take alternate pairs of steps (group g: steps 4j + 2g and
+            // 4j + 2g + 1), so one group computes while the other sits in its fence and barriers; a thread owns a
+            // row: 64 weights per step, one proxy fence and one round of arrivals per pair ----
+            const uint32_t group = warp >> 2, row = threadIdx.x & (BM - 1);
             const uint32_t m = m0 + row;
             // scale slots cover 256 columns = four steps; the walk starts at a multiple of four steps
             const uint32_t nsuper = (nk + 3) / 4;
             const uint8_t* srow = reinterpret_cast<const uint8_t*>(p.scale) + ((size_t)m * (p.K / 256) + k_begin / 4) * 8;
-            if (half == 0) cp_async8z(scale_base + row * 8, srow, m < p.M);
+            uint8_t* my_scale = scale_base + group * 2 * SCALE_SLOT_BYTES + row * 8;  // [group][2 slots][BM][8 bytes]
+            cp_async8z(my_scale, srow, m < p.M);
             asm volatile("cp.async.commit_group;\n" ::: "memory");
-            // two steps per turn: both raw tiles are read, dequantized and stored before the one proxy fence and
-            // the arrivals, which halves the synchronisation per weight and doubles the independent work in flight
-            for (uint32_t kt = 0; kt < nk; kt += 2) {
-                const bool two = kt + 1 < nk;
-                if ((kt & 3) == 0) {
-                    const uint32_t j = kt >> 2;
-                    __syncwarp();  // both threads of a row are done with the slot about to be refilled
-                    if (half == 0 && j + 1 < nsuper)
-                        cp_async8z(scale_base + ((j + 1) & 1) * SCALE_SLOT_BYTES + row * 8, srow + (size_t)(j + 1) * 8, m < p.M);
-                    asm volatile("cp.async.commit_group;\n" ::: "memory");
-                    asm volatile("cp.async.wait_group 1;\n" ::: "memory");
-                    __syncwarp();  // the sibling thread's copy is visible
-                }
-                const uint32_t r0 = kt % p.raw, r1 = (kt + 1) % p.raw;
-                mbar_wait(&raw_full[r0], (kt / p.raw) & 1, &abort_flag, p.status);
-                if (two) mbar_wait(&raw_full[r1], ((kt + 1) / p.raw) & 1, &abort_flag, p.status);
-                if (threadIdx.x == 0 && (kt == 0 || kt + 2 >= nk)) UTRACE(1000 + kt);
-                const uint32_t roff = row * raw_row + half * (raw_row / 2);
-                const uint8_t* rs0 = raw_base + (size_t)r0 * raw_bytes + roff;
-                const uint8_t* rs1 = raw_base + (size_t)r1 * raw_bytes + roff;
-                uint4 qa0 = *reinterpret_cast<const uint4*>(rs0), qa1 = make_uint4(0, 0, 0, 0);
-                uint4 qb0 = make_uint4(0, 0, 0, 0), qb1 = make_uint4(0, 0, 0, 0);
-                if (two) qb0 = *reinterpret_cast<const uint4*>(rs1);
-                if (p.kind == MAT_INT8) {
-                    qa1 = *reinterpret_cast<const uint4*>(rs0 + 16);
-                    if (two) qb1 = *reinterpret_cast<const uint4*>(rs1 + 16);
-                }
-                const uint8_t* ss = scale_base + ((kt >> 2) & 1) * SCALE_SLOT_BYTES + row * 8;
-                uint4 wa[4], wb[4];
-                if (p.kind == MAT_INT8) {
-                    // a 128-column block is two steps: kt (even) and kt + 1 share the block's (min, max)
-                    const uint32_t mm = *reinterpret_cast<const uint32_t*>(ss + ((kt >> 1) & 1) * 4);
-                    dequant_int8(qa0, qa1, mm, wa);
-                    dequant_int8(qb0, qb1, mm, wb);
-                } else {
-                    dequant_nf4(qa0, __half2float(*reinterpret_cast<const __half*>(ss + (kt & 3) * 2)), lut2, wa);
-                    dequant_nf4(qb0, __half2float(*reinterpret_cast<const __half*>(ss + ((kt + 1) & 3) * 2)), lut2, wb);
-                }
-                __syncwarp();
-                if (lane == 0) {  // the raw stages may be refilled
-                    mbar_arrive(&raw_empty[r0]);
-                    if (two) mbar_arrive(&raw_empty[r1]);
-                }
-                const uint32_t s0 = kt % p.stages, use0 = kt / p.stages;
-                const uint32_t s1 = (kt + 1) % p.stages, use1 = (kt + 1) / p.stages;
-                if (use0 > 0) mbar_wait(&ab_empty[s0], (use0 - 1) & 1, &abort_flag, p.status);
-                if (two && use1 > 0) mbar_wait(&ab_empty[s1], (use1 - 1) & 1, &abort_flag, p.status);
-                uint8_t* sa0 = smem + (size_t)s0 * stage_bytes;
-                uint8_t* sa1 = smem + (size_t)s1 * stage_bytes;
+            for (uint32_t j = 0; j < nsuper; ++j) {
+                if (j + 1 < nsuper) cp_async8z(my_scale + ((j + 1) & 1) * SCALE_SLOT_BYTES, srow + (size_t)(j + 1) * 8, m < p.M);
+                asm volatile("cp.async.commit_group;\n" ::: "memory");
+                asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+                const uint8_t* ss = my_scale + (j & 1) * SCALE_SLOT_BYTES;
+                const uint32_t kt0 = 4 * j + 2 * group;
+                if (threadIdx.x == 0 && (j == 0 || j + 1 == nsuper)) UTRACE(1000 + kt0);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(sa0 + sw128_offset(row, half * 4 + j)) = wa[j];
-                if (two) {
+                for (uint32_t d = 0; d < 2; ++d) {
+                    const uint32_t kt = kt0 + d;
+                    if (kt >= nk) break;
+                    const uint32_t r = kt % p.raw;
+                    mbar_wait(&raw_full[r], (kt / p.raw) & 1, &abort_flag, p.status);
+                    const uint4* rs = reinterpret_cast<const uint4*>(raw_base + (size_t)r * raw_bytes + row * raw_row);
+                    uint4 q[4];
+                    q[0] = rs[0], q[1] = rs[1];
+                    if (p.kind == MAT_INT8) q[2] = rs[2], q[3] = rs[3];
+                    const uint32_t s = kt % p.stages, use = kt / p.stages;
+                    if (use > 0) mbar_wait(&ab_empty[s], (use - 1) & 1, &abort_flag, p.status);
+                    uint8_t* sa = smem + (size_t)s * stage_bytes;
+                    uint4 wv[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(sa1 + sw128_offset(row, half * 4 + j)) = wb[j];
+                    for (uint32_t h = 0; h < 2; ++h) {  // columns 32 h .. 32 h + 31 of the step
+                        if (p.kind == MAT_INT8)  // a 128-column block is two steps: this group's pair shares (min, max)
+                            dequant_int8(q[2 * h], q[2 * h + 1], *reinterpret_cast<const uint32_t*>(ss + group * 4), wv);
+                        else
+                            dequant_nf4(q[h], __half2float(*reinterpret_cast<const __half*>(ss + (kt & 3) * 2)), lut2, wv);
+#pragma unroll
+                        for (uint32_t c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(sa + sw128_offset(row, h * 4 + c)) = wv[c];
+                    }
+                    __syncwarp();  // every lane has consumed its raw bytes
+                    if (lane == 0) mbar_arrive(&raw_empty[r]);  // the raw stage may be refilled
                 }
                 fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(&ab_full[s0]);
-                    if (two) mbar_arrive(&ab_full[s1]);
+                    if (kt0 < nk) mbar_arrive(&ab_full[kt0 % p.stages]);
+                    if (kt0 + 1 < nk) mbar_arrive(&ab_full[(kt0 + 1) % p.stages]);
                 }
-                if (threadIdx.x == 0 && (kt == 0 || kt + 2 >= nk)) UTRACE(2000 + kt);
+                if (threadIdx.x == 0 && (j == 0 || j + 1 == nsuper)) UTRACE(2000 + kt0);
             }
         }
         // ---- epilogue: TMEM -> registers -> activation -> token-major rows ----
@@ -584,7 +565,7 @@ cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t strea
     const uint32_t budget = 200u * 1024;
     p.raw = a.kind == MAT_FP16 ? 0 : std::min<uint32_t>(kMaxRaw, std::max<uint32_t>(2, nk));
     p.stages = std::min<uint32_t>(kMaxStages, std::max<uint32_t>(2, nk));
-    while (p.stages * stage_bytes + p.raw * raw_bytes + 2 * SCALE_SLOT_BYTES > budget) {
+    while (p.stages * stage_bytes + p.raw * raw_bytes + 4 * SCALE_SLOT_BYTES > budget) {
         if (p.raw > 4) --p.raw;
         else if (p.stages > 2) --p.stages;
         else if (p.raw > 2) --p.raw;
@@ -617,7 +598,7 @@ cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t strea
         p.stages = std::min<uint32_t>(p.stages, std::max<uint32_t>(2, nk_split));
         if (p.raw) p.raw = std::min<uint32_t>(p.raw, std::max<uint32_t>(2, nk_split));
     }
-    size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.raw * raw_bytes + 2 * SCALE_SLOT_BYTES + 1024;
+    size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.raw * raw_bytes + 4 * SCALE_SLOT_BYTES + 1024;
     if (p.splits > 1) smem = std::max<size_t>(smem, (size_t)p.n_tile * BM * sizeof(float) + 1024);  // the partial tile
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
