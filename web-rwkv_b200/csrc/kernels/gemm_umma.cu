@@ -296,9 +296,6 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
                     const uint32_t r = kt % p.raw;
                     mbar_wait(&raw_full[r], (kt / p.raw) & 1, &abort_flag, p.status);
                     const uint4* rs = reinterpret_cast<const uint4*>(raw_base + (size_t)r * raw_bytes + row * raw_row);
-                    uint4 q[4];
-                    q[0] = rs[0], q[1] = rs[1];
-                    if (p.kind == MAT_INT8) q[2] = rs[2], q[3] = rs[3];
                     const uint32_t s = kt % p.stages, use = kt / p.stages;
                     if (use > 0) mbar_wait(&ab_empty[s], (use - 1) & 1, &abort_flag, p.status);
                     uint8_t* sa = smem + (size_t)s * stage_bytes;
@@ -306,9 +303,9 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
 #pragma unroll
                     for (uint32_t h = 0; h < 2; ++h) {  // columns 32 h .. 32 h + 31 of the step
                         if (p.kind == MAT_INT8)  // a 128-column block is two steps: this group's pair shares (min, max)
-                            dequant_int8(q[2 * h], q[2 * h + 1], *reinterpret_cast<const uint32_t*>(ss + group * 4), wv);
+                            dequant_int8(rs[2 * h], rs[2 * h + 1], *reinterpret_cast<const uint32_t*>(ss + group * 4), wv);
                         else
-                            dequant_nf4(q[h], __half2float(*reinterpret_cast<const __half*>(ss + (kt & 3) * 2)), lut2, wv);
+                            dequant_nf4(rs[h], __half2float(*reinterpret_cast<const __half*>(ss + (kt & 3) * 2)), lut2, wv);
 #pragma unroll
                         for (uint32_t c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(sa + sw128_offset(row, h * 4 + c)) = wv[c];
                     }
