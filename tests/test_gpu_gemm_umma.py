@@ -1,6 +1,6 @@
 """Tensor-memory GEMM (matmul_mat_* with 16 or more tokens) against the CPU oracle: token counts around the
-tile sizes, ragged row counts, split-K shapes, output types, activations, views, and repeated launches
-(the split-K scratch and its arrival counters must be left clean).  Tolerance: tests/util.py."""
+tile sizes, ragged row counts, split-K shapes (clusters of 4, 7 and 8 CTAs that add their partial tiles through
+distributed shared memory), output types, activations, views, and repeated launches.  Tolerance: tests/util.py."""
 import numpy as np
 import pytest
 
@@ -21,7 +21,8 @@ def test_token_counts_around_the_tiles(wrk, ctx, kind, n):
 @pytest.mark.parametrize("kind", KINDS)
 @pytest.mark.parametrize("k,m,n", [(2048, 256, 64), (4096, 128, 32), (2048, 2048, 256), (512, 4099, 48), (7168, 300, 128)])
 def test_split_k_and_ragged_rows(wrk, ctx, kind, k, m, n):
-    # few output tiles and a long K: the launch is split along K; 4099 / 300 rows: last tile ragged
+    # few output tiles and a long K: K is split over a cluster (4, 8, 4 with 128-token tiles, none, 7 CTAs);
+    # 4099 / 300 rows: last tile ragged
     got, want = _run(wrk, ctx, kind, k, m, n, turbo=True, seed=k + m + n)
     assert_close(got, want, f"{kind} {k}x{m} n={n}")
 
@@ -34,7 +35,7 @@ def test_fp16_output_and_activation(wrk, ctx, kind):
     assert_close(got, want, f"{kind} tanh")
 
 
-def test_repeated_launches_leave_the_scratch_clean(wrk, ctx):
+def test_repeated_split_k_launches(wrk, ctx):
     rng = np.random.default_rng(11)
     w = (rng.standard_normal((256, 2048), dtype=np.float32) * 0.02).astype(np.float16)
     mat, (okind, om, oscale) = _make_matrix(wrk, ctx, "int8", w)
