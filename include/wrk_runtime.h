@@ -40,6 +40,18 @@ int32_t wrk_model_builder_destroy(wrk_model_builder* b);
  * and K columns is {M, K}).  The bytes are copied. */
 int32_t wrk_model_builder_add_tensor(wrk_model_builder* b, const char* name, const uint64_t* shape, uint32_t ndim,
                                      const void* data_f16, size_t bytes);
+/* ModelBuilder::lora (src/runtime/model.rs:176-179) with a `Lora` (src/runtime/loader.rs:104-171) fed piece by piece:
+ * `_lora` opens one and returns its index, `_lora_tensor` adds a named fp16 tensor of the LoRA file (a vector or
+ * matrix named like the model's, or "<matrix name without .weight>.lora.0 / .lora.1"), `_lora_blend` appends a
+ * LoraBlendPattern (regex searched in the tensor name, factor alpha; the last matching pattern of a LoRA counts).
+ * LoraBlend::full(alpha) = blend(".+", 1.0) then
+ * blend("blocks\.([0-9]+)\.(att|ffn)\.(key|value|receptance|gate|output)\.weight", alpha).
+ * Applied at build time as in src/runtime/loader.rs:393-686: vectors alpha * lora + (1 - alpha) * model in f32,
+ * matrices += discount * alpha / rank * lora.0 x lora.1 (TensorOp::blend_lora) before quantization. */
+int32_t wrk_model_builder_lora(wrk_model_builder* b, uint32_t* index);
+int32_t wrk_model_builder_lora_tensor(wrk_model_builder* b, uint32_t index, const char* name, const uint64_t* shape,
+                                      uint32_t ndim, const void* data_f16, size_t bytes);
+int32_t wrk_model_builder_lora_blend(wrk_model_builder* b, uint32_t index, const char* pattern, float alpha);
 int32_t wrk_model_builder_quant(wrk_model_builder* b, uint32_t layer, int32_t quant); /* ModelBuilder::quant */
 int32_t wrk_model_builder_rescale(wrk_model_builder* b, uint32_t value);             /* ModelBuilder::rescale */
 int32_t wrk_model_builder_sep(wrk_model_builder* b, uint32_t value);                 /* ModelBuilder::sep */

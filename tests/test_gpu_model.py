@@ -173,3 +173,47 @@ def test_config1_v6_0p1b_int8_256_tokens_chunk_32(ctx):
     pairs, state = _drive(bundle, ref, [(prompt, LAST)], 32)
     assert len(pairs) == 8 and pairs[-1][1][0].shape == (1, 65536)
     _check(pairs, bundle, state)
+
+
+def test_lora_is_merged_before_quantization(ctx):
+    # ModelBuilder::lora with LoraBlend::full(0.5): vectors of the LoRA replace the model's, matrices get
+    # alpha / rank * lora.0 x lora.1 (TensorOp::blend_lora) before they are quantized (src/runtime/loader.rs:393-686)
+    rng = np.random.default_rng(77)
+    tensors = synth.make_model("v6-tiny", seed=1000)
+    R, alpha = 8, 0.5
+    lora, merged = {}, dict(tensors)
+    for name in ("blocks.0.ln1.weight", "blocks.1.att.time_first", "blocks.2.ffn.time_mix_k"):
+        lora[name] = (tensors[name].astype(np.float32) + 0.1 * rng.standard_normal(tensors[name].shape)).astype(np.float16)
+        merged[name] = lora[name]
+    for name in ("blocks.0.att.key.weight", "blocks.1.ffn.value.weight", "blocks.2.att.output.weight"):
+        M, K = tensors[name].shape
+        base = name.replace(".weight", "")
+        lora[base + ".lora.0"] = (0.05 * rng.standard_normal((K, R))).astype(np.float16)
+        lora[base + ".lora.1"] = (0.05 * rng.standard_normal((M, R))).astype(np.float16)
+        w = tensors[name].copy()
+        oracle.blend_lora([alpha / R, 1.0, 0, 0], lora[base + ".lora.0"], lora[base + ".lora.1"], w)
+        assert np.abs(w.astype(np.float32) - tensors[name].astype(np.float32)).max() > 1e-3  # the LoRA does something
+        merged[name] = w
+    # a tensor of a matrix's own name is added with factor (alpha, 1); one that no pattern matches is ignored
+    quant = {0: 1, 1: 2}
+    model = rt.ModelBuilder(ctx).add_tensors(tensors).lora(lora, alpha=alpha).quant(quant).build()
+    ref = omodel.OracleModel(merged, quant)
+    kind, w, m, q = model.matrix_parts(2, "att.w_o")  # layer 2 stays fp16: the merged weights themselves
+    want = merged["blocks.2.att.output.weight"]
+    assert np.abs(w.reshape(want.shape).astype(np.float32) - want.astype(np.float32)).max() <= 2.5e-4
+    bundle = rt.Bundle(model, 2)
+    V = model.info.num_vocab
+    batches = [(rng.integers(0, V - 1, 40).tolist(), LAST), (rng.integers(0, V - 1, 5).tolist(), FULL)]
+    pairs, state = _drive(bundle, ref, batches, 32)
+    _check(pairs, bundle, state)
+    # and the LoRA changed the logits: the plain model's differ
+    plain = rt.Bundle(rt.ModelBuilder(ctx).add_tensors(tensors).quant(quant).build(), 1)
+    inp = rt.RnnInput([(batches[1][0], LAST)], 32)
+    a = plain.infer(inp)[0].copy()
+    with_lora = rt.Bundle(model, 1)
+    inp = rt.RnnInput([(batches[1][0], LAST)], 32)
+    bb = with_lora.infer(inp)[0].copy()
+    assert np.abs(a - bb).max() > 1e-2
+    with pytest.raises(rt.WrkError) as e:  # a pattern that is not a regular expression
+        rt.ModelBuilder(ctx).add_tensors(tensors).lora({}, blend=[("(", 1.0)])
+    assert e.value.status == -103

@@ -6,6 +6,8 @@ import subprocess
 import sys
 import textwrap
 
+from tests.util import free_port
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 WORKER = textwrap.dedent(
@@ -33,7 +35,7 @@ WORKER = textwrap.dedent(
 def test_replica_aggregation_two_gloo_ranks(tmp_path):
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29533", WORLD_SIZE="2")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(free_port()), WORLD_SIZE="2")
     procs = []
     for rank in range(2):
         e = dict(env, RANK=str(rank), LOCAL_RANK=str(rank))

@@ -7,6 +7,8 @@ import sys
 
 import pytest
 
+from tests.util import free_port
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 WORKER = os.path.join(ROOT, "tests", "tp_worker.py")
 
@@ -56,7 +58,7 @@ def test_shard_ranges_and_plan():
 
 
 def test_sharding_rules_two_gloo_ranks_cpu_oracle():
-    _spawn("cpu", 2, 29541)
+    _spawn("cpu", 2, free_port())
 
 
 @pytest.mark.gpu
@@ -64,5 +66,5 @@ def test_tensor_parallel_v6_matches_single_gpu():
     listing = subprocess.run(["nvidia-smi", "-L"], capture_output=True, text=True).stdout
     if listing.count("GPU ") < 2:
         pytest.skip("needs two GPUs")
-    outs = _spawn("gpu", 2, 29542)
+    outs = _spawn("gpu", 2, free_port())
     assert "tp logits match" in outs[0]

@@ -32,3 +32,11 @@ def is_approx_eps(a, b, eps):
     a = np.asarray(a, dtype=np.float64)
     b = np.asarray(b, dtype=np.float64)
     return np.abs(a - b) <= np.maximum(eps, eps * np.maximum(np.abs(a), np.abs(b)))
+
+
+def free_port():
+    """A TCP port on the loopback interface that is free right now (for a torch.distributed rendezvous)."""
+    import socket
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sock:
+        sock.bind(("127.0.0.1", 0))
+        return sock.getsockname()[1]

@@ -39,12 +39,116 @@ struct Loader {
         return WRK_OK;
     }
 
-    // load_vector_f16, src/runtime/loader.rs:514-565: flattened to [n, 1, 1, 1]
+    // In each LoRA only the last pattern that matches the name counts (rfind, src/runtime/loader.rs:333-341).
+    static const float* lora_alpha(const wrk_model_builder::Lora& lora, const std::string& name) {
+        for (auto it = lora.blend.rbegin(); it != lora.blend.rend(); ++it)
+            if (std::regex_search(name, it->first)) return &it->second;
+        return nullptr;
+    }
+
+    int32_t upload_f16(const wrk_model_builder::Entry& e, TensorH* out) const {
+        uint32_t shape[4];
+        WRK_TRY(rev_shape(e.shape, shape));
+        wrk_tensor* t = nullptr;
+        WRK_TRY(wrk_tensor_from_data(ctx, WRK_F16, shape, e.data.data(), e.data.size() * 2, &t));
+        *out = TensorH(t);
+        return WRK_OK;
+    }
+
+    int32_t factor_tensor(float x, float y, TensorH* out) const {
+        const float f[4] = {x, y, 0.0f, 0.0f};
+        const uint32_t shape[4] = {4, 1, 1, 1};
+        wrk_tensor* t = nullptr;
+        WRK_TRY(wrk_tensor_from_data(ctx, WRK_F32, shape, f, sizeof f, &t));
+        *out = TensorH(t);
+        return WRK_OK;
+    }
+
+    int32_t run_and_release(wrk_op* op) const {
+        const int32_t s = wrk_run(ctx, op);
+        wrk_op_release(op);
+        return s;
+    }
+
+    // lora_vectors (src/runtime/loader.rs:326-352) applied as TensorOp::blend with factor (fx * alpha, keep): the
+    // LoRA holds a tensor of the same name; `target` is viewed with that tensor's shape.
+    int32_t blend_named(const std::string& name, wrk_tensor* target, float fx, bool replace) const {
+        for (const auto& lora : b->loras) {
+            const float* alpha = lora_alpha(lora, name);
+            if (!alpha) continue;
+            auto it = lora.tensors.find(name);
+            if (it == lora.tensors.end()) continue;
+            TensorH lt, factor;
+            WRK_TRY(upload_f16(it->second, &lt));
+            WRK_TRY(factor_tensor(fx * *alpha, replace ? 1.0f - *alpha : 1.0f, &factor));
+            wrk_tensor* shaped = nullptr;
+            WRK_TRY(wrk_tensor_reshape(target, lt.p->shape.v, &shaped));
+            TensorH sh(shaped);
+            wrk_op* op = nullptr;
+            WRK_TRY(wrk_op_blend(factor, lt, sh, &op));
+            WRK_TRY(run_and_release(op));
+        }
+        return WRK_OK;
+    }
+
+    bool has_named(const std::string& name) const {
+        for (const auto& lora : b->loras)
+            if (lora_alpha(lora, name) && lora.tensors.count(name)) return true;
+        return false;
+    }
+
+    // lora_matrices (src/runtime/loader.rs:354-385) applied as TensorOp::blend_lora with factor
+    // (discount * alpha / rank, 1): tensors "<name without its weight component>.lora.0" and ".lora.1".
+    int32_t blend_matrices(const std::string& name, wrk_tensor* target, float discount) const {
+        std::string base;
+        size_t pos = 0;
+        while (pos <= name.size()) {
+            const size_t dot = std::min(name.find('.', pos), name.size());
+            const std::string part = name.substr(pos, dot - pos);
+            if (part.find("weight") == std::string::npos) base += (base.empty() ? "" : ".") + part;
+            pos = dot + 1;
+        }
+        for (const auto& lora : b->loras) {
+            const float* alpha = lora_alpha(lora, name);
+            if (!alpha) continue;
+            auto ix = lora.tensors.find(base + ".lora.0"), iy = lora.tensors.find(base + ".lora.1");
+            if (ix == lora.tensors.end() || iy == lora.tensors.end()) continue;
+            WRK_REQUIRE(ix->second.shape.size() == 2, WRK_ERR_SHAPE, "tensor shape not match (%s.lora.0)", base.c_str());
+            const float rank = (float)ix->second.shape[1];
+            TensorH x, y, factor;
+            WRK_TRY(upload_f16(ix->second, &x));
+            WRK_TRY(upload_f16(iy->second, &y));
+            WRK_TRY(factor_tensor(discount * *alpha / rank, 1.0f, &factor));
+            wrk_view vx, vy, vo;
+            WRK_TRY(wrk_tensor_as_view(x, &vx));
+            WRK_TRY(wrk_tensor_as_view(y, &vy));
+            WRK_TRY(wrk_tensor_as_view(target, &vo));
+            wrk_op* op = nullptr;
+            WRK_TRY(wrk_op_blend_lora(factor, &vx, &vy, &vo, &op));
+            WRK_TRY(run_and_release(op));
+        }
+        return WRK_OK;
+    }
+
+    // load_vector_f16, src/runtime/loader.rs:514-565: flattened to [n, 1, 1, 1]; with a LoRA vector the blend runs
+    // in f32 and the result is rounded to fp16 once
     int32_t vector_f16(const std::string& name, TensorH* out) const {
         const wrk_model_builder::Entry* e;
         WRK_TRY(entry(name, &e));
         const uint32_t shape[4] = {(uint32_t)e->data.size(), 1, 1, 1};
         wrk_tensor* t = nullptr;
+        if (has_named(name)) {
+            TensorH f32;
+            WRK_TRY(vector_f32(name, &f32));
+            WRK_TRY(wrk_tensor_create(ctx, WRK_F16, shape, &t));
+            *out = TensorH(t);
+            wrk_view vi, vo;
+            WRK_TRY(wrk_tensor_as_view(f32, &vi));
+            WRK_TRY(wrk_tensor_as_view(t, &vo));
+            wrk_op* op = nullptr;
+            WRK_TRY(wrk_op_blit(&vi, &vo, &op));
+            return run_and_release(op);
+        }
         WRK_TRY(wrk_tensor_from_data(ctx, WRK_F16, shape, e->data.data(), e->data.size() * 2, &t));
         *out = TensorH(t);
         return WRK_OK;
@@ -60,7 +164,7 @@ struct Loader {
         wrk_tensor* t = nullptr;
         WRK_TRY(wrk_tensor_from_data(ctx, WRK_F32, shape, f.data(), f.size() * 4, &t));
         *out = TensorH(t);
-        return WRK_OK;
+        return blend_named(name, t, 1.0f, true);  // factor (alpha, 1 - alpha), src/runtime/loader.rs:410-425
     }
 
     // load_vector_exp_exp_f32, src/runtime/loader.rs:472-512: f32 vector, then StableExp on the device
@@ -105,7 +209,10 @@ struct Loader {
         wrk_tensor* t = nullptr;
         WRK_TRY(wrk_tensor_from_data(ctx, WRK_F16, shape, src, n * 2, &t));
         *out = TensorH(t);
-        return WRK_OK;
+        if (padded || b->loras.empty()) return WRK_OK;  // load_matrix_f16_padded_cpu takes no LoRA
+        // blend_lora, then blend of a same-named tensor, src/runtime/loader.rs:577-588 and 606-617
+        WRK_TRY(blend_matrices(name, t, discount));
+        return blend_named(name, t, discount, false);
     }
 
     int32_t matrix_fp16(const std::string& name, MatrixH* out) const {
@@ -400,6 +507,40 @@ int32_t wrk_model_builder_quant(wrk_model_builder* b, uint32_t layer, int32_t qu
     WRK_REQUIRE(b, WRK_ERR_INVALID_ARGUMENT, "null argument");
     WRK_REQUIRE(quant >= WRK_QUANT_NONE && quant <= WRK_QUANT_SF4, WRK_ERR_INVALID_ARGUMENT, "unknown quant %d", quant);
     b->quant[layer] = quant;
+    return WRK_OK;
+}
+
+int32_t wrk_model_builder_lora(wrk_model_builder* b, uint32_t* index) {
+    WRK_REQUIRE(b && index, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    b->loras.emplace_back();
+    *index = (uint32_t)b->loras.size() - 1;
+    return WRK_OK;
+}
+
+int32_t wrk_model_builder_lora_tensor(wrk_model_builder* b, uint32_t index, const char* name, const uint64_t* shape,
+                                      uint32_t ndim, const void* data_f16, size_t bytes) {
+    WRK_REQUIRE(b && name && shape && data_f16, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(index < b->loras.size(), WRK_ERR_INVALID_ARGUMENT, "no LoRA %u", index);
+    WRK_REQUIRE(ndim >= 1 && ndim <= 4, WRK_ERR_DEDUCE, "cannot deduce dimension");
+    size_t n = 1;
+    for (uint32_t i = 0; i < ndim; ++i) n *= shape[i];
+    WRK_REQUIRE(n * 2 == bytes, WRK_ERR_SIZE, "tensor %s: %zu bytes for %zu fp16 elements", name, bytes, n);
+    wrk_model_builder::Entry e;
+    e.shape.assign(shape, shape + ndim);
+    e.data.resize(n);
+    std::memcpy(e.data.data(), data_f16, bytes);
+    b->loras[index].tensors[name] = std::move(e);
+    return WRK_OK;
+}
+
+int32_t wrk_model_builder_lora_blend(wrk_model_builder* b, uint32_t index, const char* pattern, float alpha) {
+    WRK_REQUIRE(b && pattern, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(index < b->loras.size(), WRK_ERR_INVALID_ARGUMENT, "no LoRA %u", index);
+    try {
+        b->loras[index].blend.emplace_back(std::regex(pattern, std::regex::ECMAScript), alpha);
+    } catch (const std::regex_error& err) {
+        return set_error(WRK_ERR_INVALID_ARGUMENT, "bad blend pattern %s: %s", pattern, err.what());
+    }
     return WRK_OK;
 }
 

@@ -3,6 +3,7 @@
 
 #include <algorithm>
 #include <map>
+#include <regex>
 #include <string>
 #include <unordered_map>
 #include <utility>
@@ -110,8 +111,14 @@ struct wrk_model_builder {
         std::vector<uint64_t> shape;  // outermost first
         std::vector<uint16_t> data;   // fp16 bits
     };
+    // `Lora` of src/runtime/loader.rs:104-113: named fp16 tensors and an ordered list of (pattern, alpha)
+    struct Lora {
+        std::map<std::string, Entry> tensors;
+        std::vector<std::pair<std::regex, float>> blend;
+    };
     wrk_context* ctx = nullptr;
     std::map<std::string, Entry> tensors;
+    std::vector<Lora> loras;
     std::unordered_map<uint32_t, int32_t> quant;
     size_t rescale = 0;  // 0 = default of the version
     size_t sep = 0;

@@ -39,6 +39,22 @@ class ModelBuilder:
             self.add_tensor(name, arr)
         return self
 
+    LORA_MATRICES = r"blocks\.([0-9]+)\.(att|ffn)\.(key|value|receptance|gate|output)\.weight"
+
+    def lora(self, tensors, blend=None, alpha=1.0):
+        """`ModelBuilder::lora`: tensors {name: fp16 array} of one LoRA file; blend: [(regex, alpha), ...] in order,
+        default `LoraBlend::full(alpha)` (src/runtime/loader.rs:119-124)."""
+        index = ctypes.c_uint32()
+        check(lib().wrk_model_builder_lora(self.handle, ctypes.byref(index)))
+        for name, arr in tensors.items():
+            arr = np.ascontiguousarray(arr, dtype=np.float16)
+            shape = (ctypes.c_uint64 * arr.ndim)(*arr.shape)
+            check(lib().wrk_model_builder_lora_tensor(self.handle, index, name.encode(), shape, arr.ndim,
+                                                      arr.ctypes.data_as(ctypes.c_void_p), ctypes.c_size_t(arr.nbytes)))
+        for pattern, a in (blend if blend is not None else [(r".+", 1.0), (self.LORA_MATRICES, alpha)]):
+            check(lib().wrk_model_builder_lora_blend(self.handle, index, pattern.encode(), ctypes.c_float(a)))
+        return self
+
     def quant(self, mapping):
         for layer, q in mapping.items():
             check(lib().wrk_model_builder_quant(self.handle, layer, q))
