@@ -55,6 +55,9 @@ int32_t wrk_model_builder_lora_blend(wrk_model_builder* b, uint32_t index, const
 int32_t wrk_model_builder_quant(wrk_model_builder* b, uint32_t layer, int32_t quant); /* ModelBuilder::quant */
 int32_t wrk_model_builder_rescale(wrk_model_builder* b, uint32_t value);             /* ModelBuilder::rescale */
 int32_t wrk_model_builder_sep(wrk_model_builder* b, uint32_t value);                 /* ModelBuilder::sep */
+/* read_state (src/runtime/v6.rs:1175-1208, same in v5.rs / v7.rs): the pre-trained initial state stored in the file as
+ * blocks.N.att.time_state, as the f32 [C, S + 2, L] tensor that State::load (wrk_state_load) takes for a batch slot. */
+int32_t wrk_model_builder_read_state(wrk_model_builder* b, float* host, size_t bytes);
 /* Loader::info (src/runtime/loader.rs:208-324) on the tensors added so far. */
 int32_t wrk_model_builder_info(wrk_model_builder* b, wrk_model_info* info);
 /* ModelBuilder::build_v5 / build_v6 / build_v7 (src/runtime/v5.rs:922-1082, v6.rs:995-1172,

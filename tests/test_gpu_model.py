@@ -217,3 +217,29 @@ def test_lora_is_merged_before_quantization(ctx):
     with pytest.raises(rt.WrkError) as e:  # a pattern that is not a regular expression
         rt.ModelBuilder(ctx).add_tensors(tensors).lora({}, blend=[("(", 1.0)])
     assert e.value.status == -103
+
+
+def test_read_state_from_the_model_file(ctx):
+    # read_state (src/runtime/v6.rs:1175-1208): blocks.N.att.time_state (H, S, S) -> rows 1..S of the f32 [C, S + 2, L]
+    # state, column h * S + j of row 1 + i holding time_state[h][i][j]; State::load takes it for a batch slot
+    rng = np.random.default_rng(88)
+    tensors = dict(synth.make_model("v6-tiny", seed=1000))
+    info = rt.ModelBuilder(ctx).add_tensors(tensors).info()
+    L, C, H = info.num_layer, info.num_emb, info.num_head
+    S = C // H
+    for layer in range(L):
+        tensors[f"blocks.{layer}.att.time_state"] = rng.standard_normal((H, S, S)).astype(np.float16)
+    builder = rt.ModelBuilder(ctx).add_tensors(tensors)
+    got = builder.read_state()
+    want = np.zeros((L, S + 2, C), dtype=np.float32)
+    for layer in range(L):
+        ts = tensors[f"blocks.{layer}.att.time_state"].astype(np.float32)  # [h][i][j]
+        want[layer, 1:S + 1, :] = ts.transpose(1, 0, 2).reshape(S, C)
+    assert np.array_equal(got, want)
+    bundle = rt.Bundle(builder.build(), 2)
+    bundle.state_load(got, 1)
+    assert np.array_equal(bundle.state_back(1).reshape(got.shape), got)
+    assert not bundle.state_back(0).any()
+    with pytest.raises(rt.WrkError) as e:  # a file without the tensors
+        rt.ModelBuilder(ctx).add_tensors(synth.make_model("v6-tiny", seed=1000)).read_state()
+    assert e.value.status == -21

@@ -556,6 +556,48 @@ int32_t wrk_model_builder_sep(wrk_model_builder* b, uint32_t value) {
     return WRK_OK;
 }
 
+int32_t wrk_model_builder_read_state(wrk_model_builder* b, float* host, size_t bytes) {
+    // read_state, src/runtime/v5.rs / v6.rs:1175-1208 / v7.rs: per layer the matrix blocks.N.att.time_state
+    // (H x S x S in the file) is transposed to [S, H, S], viewed as [C, S] and copied into rows 1..S of an f32
+    // [C, S + 2, L] tensor of zeros, which State::load takes for one batch slot.
+    WRK_REQUIRE(b && host, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    wrk_model_info info{};
+    WRK_TRY(sniff_info(b, &info));
+    const uint32_t C = info.num_emb, H = info.num_head, L = info.num_layer;
+    WRK_REQUIRE(H > 0 && C % H == 0, WRK_ERR_SHAPE, "num_emb %u is not a multiple of num_head %u", C, H);
+    const uint32_t S = C / H;
+    WRK_REQUIRE(bytes == (size_t)C * (S + 2) * L * sizeof(float), WRK_ERR_SIZE, "state of %zu bytes expected",
+                (size_t)C * (S + 2) * L * sizeof(float));
+    Loader ld{b, b->ctx};
+    const uint32_t data_shape[4] = {C, S + 2, L, 1};
+    wrk_tensor* data_raw = nullptr;
+    WRK_TRY(wrk_tensor_zeros(b->ctx, WRK_F32, data_shape, &data_raw));
+    TensorH data(data_raw);
+    for (uint32_t layer = 0; layer < L; ++layer) {
+        TensorH matrix;
+        WRK_TRY(ld.matrix_f16("blocks." + std::to_string(layer) + ".att.time_state", false, 1.0f, &matrix));
+        WRK_TRY(check_shape("time_state", matrix.p->shape, S, S, H, 1));
+        const uint32_t state_shape[4] = {S, H, S, 1}, flat_shape[4] = {C, S, 1, WRK_DIM_AUTO};
+        wrk_tensor *state_raw = nullptr, *flat_raw = nullptr;
+        WRK_TRY(wrk_tensor_create(b->ctx, WRK_F16, state_shape, &state_raw));
+        TensorH state(state_raw);
+        WRK_TRY(wrk_tensor_reshape(state, flat_shape, &flat_raw));
+        TensorH flat(flat_raw);
+        wrk_view vm, vs, vf, vd;
+        WRK_TRY(wrk_tensor_as_view(matrix, &vm));
+        WRK_TRY(wrk_tensor_as_view(state, &vs));
+        WRK_TRY(wrk_tensor_as_view(flat, &vf));
+        const uint32_t start[4] = {0, 1, layer, 0}, end[4] = {C, S + 1, layer + 1, 1};
+        WRK_TRY(wrk_tensor_view(data, start, end, &vd));
+        wrk_op* op = nullptr;
+        WRK_TRY(wrk_op_transpose(&vm, &vs, &op));
+        WRK_TRY(ld.run_and_release(op));
+        WRK_TRY(wrk_op_blit(&vf, &vd, &op));
+        WRK_TRY(ld.run_and_release(op));
+    }
+    return wrk_tensor_back(data, host, bytes);
+}
+
 int32_t wrk_model_builder_info(wrk_model_builder* b, wrk_model_info* info) {
     WRK_REQUIRE(b && info, WRK_ERR_INVALID_ARGUMENT, "null argument");
     return sniff_info(b, info);

@@ -64,6 +64,15 @@ class ModelBuilder:
         check(lib().wrk_model_builder_rescale(self.handle, value))
         return self
 
+    def read_state(self):
+        """`read_state` (src/runtime/v6.rs:1175-1208): (L, S + 2, C) f32 from the blocks.N.att.time_state tensors."""
+        info = self.info()
+        S = info.num_emb // info.num_head
+        out = np.empty((info.num_layer, S + 2, info.num_emb), dtype=np.float32)
+        check(lib().wrk_model_builder_read_state(self.handle, out.ctypes.data_as(ctypes.c_void_p),
+                                                 ctypes.c_size_t(out.nbytes)))
+        return out
+
     def info(self):
         info = ModelInfo()
         check(lib().wrk_model_builder_info(self.handle, ctypes.byref(info)))
