@@ -161,6 +161,11 @@ int32_t wrk_op_matmul_mat_int8(const wrk_view* matrix, wrk_tensor* minmax, const
 /* TensorOp::matmul_mat_nf4(matrix, quant, absmax, input, output, act), src/tensor/ops.rs:1150-1221 */
 int32_t wrk_op_matmul_mat_nf4(const wrk_view* matrix, wrk_tensor* quant, wrk_tensor* absmax,
                               const wrk_view* input, const wrk_view* output, int32_t act, wrk_op** out);
+/* TensorOp::time_mix_v4(cursors, time_decay, time_first, state, k, v, r, x), src/tensor/ops.rs:1464-1528 (shader
+ * src/shaders/time_mix_v4.wgsl): k, v, r, x [C, T]; time_decay, time_first f32 [C]; state view f32 [C, 4, B] (rows: shift
+ * carry, aa, bb, pp). */
+int32_t wrk_op_time_mix_v4(wrk_tensor* cursors, wrk_tensor* time_decay, wrk_tensor* time_first, const wrk_view* state,
+                           wrk_tensor* k, wrk_tensor* v, wrk_tensor* r, wrk_tensor* x, wrk_op** out);
 /* TensorOp::time_mix_v5(cursors, time_decay, time_first, state, k, v, r, x), src/tensor/ops.rs:1530-1598 */
 int32_t wrk_op_time_mix_v5(wrk_tensor* cursors, wrk_tensor* time_decay, wrk_tensor* time_first,
                            const wrk_view* state, wrk_tensor* k, wrk_tensor* v, wrk_tensor* r, wrk_tensor* x,

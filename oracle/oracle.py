@@ -168,6 +168,16 @@ def time_mix_v56(per_token, cursors, time_decay, time_first, state, k, v, r, x, 
     assert s == 0
 
 
+def time_mix_v4(cursors, time_decay, time_first, state, k, v, r, x, fast=False):
+    """k, v, r, x: (T, C); time_decay, time_first: (C,) f32; state: (B, 4, C) f32 (or a View of it)."""
+    c, wide = _cursors(cursors)
+    C = x.shape[-1]
+    sv = _view(state).c()
+    s = lib(fast).orc_time_mix_v4(_ptr(c), wide, _ptr(time_decay), _ptr(time_first), ctypes.byref(sv), _dt(x), _ptr(k),
+                                  _ptr(v), _ptr(r), _ptr(x), C, x.size // C)
+    assert s == 0
+
+
 def time_mix_v7(cursors, state, r, w, n, x, S, H, fast=False):
     c, wide = _cursors(cursors)
     T = x.size // (S * H)

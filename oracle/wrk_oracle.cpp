@@ -439,6 +439,50 @@ int orc_layer_norm(const uint16_t* w, const uint16_t* b, int dtype, void* x, uin
     return 0;
 }
 
+// time_mix_v4: src/shaders/time_mix_v4.wgsl:62-124.  State view [C, 4, B]: row 0 = token-shift carry, rows 1..3 =
+// (aa, bb, pp).  Every token rewrites row 0 from the input x of its sequence's last token of the job (read before
+// that slot of x is overwritten), then x_t = sigmoid(r) (e1 aa + e2 v) / (e1 bb + e2) and the (aa, bb, pp) update.
+int orc_time_mix_v4(const uint32_t* cursors, int wide, const float* time_decay, const float* time_first,
+                    const orc_view* state, int dtype, const void* k, const void* v, const void* r, void* x, uint32_t C,
+                    uint32_t T) {
+    orc_view kv = {const_cast<void*>(k), dtype, {C, T, 1, 1}, {C, T, 1, 1}, {0, 0, 0, 0}};
+    orc_view vv_ = kv, rv = kv, xv = kv;
+    vv_.data = const_cast<void*>(v);
+    rv.data = const_cast<void*>(r);
+    xv.data = x;
+    float* st = (float*)state->data;
+    for (uint32_t c = 0; c < C; ++c) {
+        const float u = time_first[c], w = time_decay[c];
+        for (uint32_t t = 0; t < T; ++t) {
+            uint32_t batch, token, len;
+            if (wide) {
+                batch = cursors[3 * t], token = cursors[3 * t + 1], len = cursors[3 * t + 2];
+            } else {
+                batch = cursors[t] & 0xffu, token = (cursors[t] >> 8) & 0xffffu, len = (cursors[t] >> 24) & 0xffu;
+            }
+            const size_t ai = vindex(*state, c, 1, batch), bi = vindex(*state, c, 2, batch), pi = vindex(*state, c, 3, batch);
+            float aa = st[ai], bb = st[bi], pp = st[pi];
+            const uint32_t last = token + len - 1u;
+            if (last < T) st[vindex(*state, c, 0, batch)] = vload(xv, (size_t)last * C + c);
+            const size_t ti = (size_t)t * C + c;
+            const float kk = vload(kv, ti), vv = vload(vv_, ti);
+            const float rr = 1.0f / (1.0f + std::exp(-vload(rv, ti)));
+            float ww = u + kk;
+            float q = std::max(pp, ww);
+            float e1 = std::exp(pp - q), e2 = std::exp(ww - q);
+            vstore(xv, ti, rr * (e1 * aa + e2 * vv) / (e1 * bb + e2));
+            ww = w + pp;
+            q = std::max(ww, kk);
+            e1 = std::exp(ww - q);
+            e2 = std::exp(kk - q);
+            st[ai] = e1 * aa + e2 * vv;
+            st[bi] = e1 * bb + e2;
+            st[pi] = q;
+        }
+    }
+    return 0;
+}
+
 // softmax: src/shaders/softmax.wgsl:52-106.  x <- exp(x - max) / sum exp(x - max) per row of C, f32 math.
 int orc_softmax(int dtype, void* x, uint32_t C, uint32_t rows) {
     orc_view xv = {x, dtype, {C, rows, 1, 1}, {C, rows, 1, 1}, {0, 0, 0, 0}};

@@ -167,3 +167,31 @@ def test_shape_errors(wrk, ctx):
     with pytest.raises(wrk.WrkError) as e:  # state view must have S + 1 rows
         wrk.time_mix_v6(cursors, f(S, H, T), f(S, H), state, f(S, H, T), f(S, H, T), f(S, H, T), f(S, H, T))
     assert e.value.status == -5
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_time_mix_v4(wrk, ctx, dtype):
+    # TensorOp::time_mix_v4 (src/tensor/ops.rs:1464-1528): three sequences in three batch slots, one revisited slot
+    rng = np.random.default_rng(44)
+    C, B = 320, 3
+    seqs = [(2, 0, 7), (0, 7, 1), (1, 8, 12)]
+    T = 20
+    k, v, r, x = (rng.standard_normal((T, C)).astype(dtype) for _ in range(4))
+    w = (-np.exp(rng.uniform(-3, 0.5, C))).astype(np.float32)
+    u = rng.uniform(-1, 1, C).astype(np.float32)
+    state = rng.standard_normal((B, 4, C)).astype(np.float32)
+    state[:, 2] = np.abs(state[:, 2]) + 0.5
+    for wide in (True, False):
+        cursors = oracle.pack_cursors(seqs, wide=wide)
+        t_state, t_x = ctx.from_numpy(state), ctx.from_numpy(x)
+        ctx.run(wrk.time_mix_v4(ctx.from_numpy(cursors), ctx.from_numpy(w), ctx.from_numpy(u), t_state,
+                                ctx.from_numpy(k), ctx.from_numpy(v), ctx.from_numpy(r), t_x))
+        x_ref, st_ref = x.copy(), state.copy()
+        oracle.time_mix_v4(cursors, w, u, st_ref, k, v, r, x_ref)
+        assert_close(t_x.numpy().reshape(T, C), x_ref, f"v4 x wide={wide}")
+        assert_close(t_state.numpy().reshape(B, 4, C), st_ref, f"v4 state wide={wide}")
+        assert np.array_equal(t_state.numpy().reshape(B, 4, C)[:, 0], st_ref[:, 0])  # the carry rows are copies
+    with pytest.raises(wrk.WrkError) as e:
+        wrk.time_mix_v4(ctx.from_numpy(cursors), ctx.from_numpy(w[:-4]), ctx.from_numpy(u), t_state, ctx.from_numpy(k),
+                        ctx.from_numpy(v), ctx.from_numpy(r), t_x)
+    assert e.value.status == -5

@@ -214,3 +214,33 @@ def test_load_time_ops_against_dense_numpy():
     want = 2.0 * xb.astype(np.float64) @ xa.astype(np.float64).T + 0.5 * m.astype(np.float64)
     oracle.blend_lora([2.0, 0.5, 0, 0], xa, xb, m)
     assert np.allclose(m.astype(np.float64), want, atol=1e-3)
+
+
+def test_wkv4_against_dense_numpy():
+    # time_mix_v4.wgsl keeps (aa, bb, pp) = (numerator, denominator, running exponent) of
+    # wkv_t = (sum_{s<t} e^{(t-1-s) w + k_s} v_s + e^{u + k_t} v_t) / (sum_{s<t} e^{(t-1-s) w + k_s} + e^{u + k_t});
+    # the float64 restatement evaluates those sums directly (w <= 0 is the per-step log decay)
+    rng = np.random.default_rng(4)
+    C, T = 64, 9
+    k, v, r = (rng.standard_normal((T, C)).astype(np.float32) for _ in range(3))
+    x = rng.standard_normal((T, C)).astype(np.float32)
+    w = (-np.exp(rng.uniform(-3, 0.5, C))).astype(np.float32)
+    u = rng.uniform(-1, 1, C).astype(np.float32)
+    state = np.zeros((2, 4, C), dtype=np.float32)
+    state[:, 3] = -1e30  # the empty history: pp = -inf stand-in, aa = bb = 0
+    cursors = oracle.pack_cursors([(1, 0, 6), (0, 6, 3)], wide=True)
+    x_in, st = x.copy(), state.copy()
+    oracle.time_mix_v4(cursors, w, u, st, k, v, r, x)
+    for batch, t0, n in ((1, 0, 6), (0, 6, 3)):
+        k64, v64 = k[t0:t0 + n].astype(np.float64), v[t0:t0 + n].astype(np.float64)
+        for t in range(n):
+            decay = np.array([(t - 1 - s_) * w.astype(np.float64) + k64[s_] for s_ in range(t)]).reshape(t, C)
+            num = (np.exp(decay) * v64[:t]).sum(axis=0) + np.exp(u + k64[t]) * v64[t]
+            den = np.exp(decay).sum(axis=0) + np.exp(u + k64[t])
+            want = num / den / (1.0 + np.exp(-r[t0 + t].astype(np.float64)))
+            assert np.allclose(x[t0 + t], want, rtol=1e-4, atol=1e-5), (batch, t)
+        assert np.array_equal(st[batch, 0], x_in[t0 + n - 1])  # token-shift carry = the sequence's last input row
+        # state after n tokens: aa / bb = decayed averages, in the shader's scaled form aa e^{pp}, bb e^{pp}
+        decay = np.array([(n - 1 - s_) * w.astype(np.float64) + k64[s_] for s_ in range(n)])
+        assert np.allclose(st[batch, 1] * np.exp(st[batch, 3].astype(np.float64)), (np.exp(decay) * v64).sum(axis=0), rtol=1e-4)
+        assert np.allclose(st[batch, 2] * np.exp(st[batch, 3].astype(np.float64)), np.exp(decay).sum(axis=0), rtol=1e-4)

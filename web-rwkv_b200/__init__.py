@@ -281,6 +281,12 @@ def matmul_mat_nf4(matrix, quant, absmax, input, output, act=ACT_NONE):
     return _mk("wrk_op_matmul_mat_nf4", pm, _t(quant), _t(absmax), pi, po, act, keep=(km, quant, absmax, ki, ko))
 
 
+def time_mix_v4(cursors, time_decay, time_first, state, k, v, r, x):
+    ps, ks = _v(state)
+    return _mk("wrk_op_time_mix_v4", _t(cursors), _t(time_decay), _t(time_first), ps, _t(k), _t(v), _t(r), _t(x),
+               keep=(cursors, time_decay, time_first, ks, k, v, r, x))
+
+
 def time_mix_v5(cursors, time_decay, time_first, state, k, v, r, x):
     ps, ks = _v(state)
     return _mk("wrk_op_time_mix_v5", _t(cursors), _t(time_decay), _t(time_first), ps, _t(k), _t(v), _t(r), _t(x),

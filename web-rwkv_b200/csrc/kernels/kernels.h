@@ -52,6 +52,9 @@ struct WkvArgs {
 };
 cudaError_t time_mix_v56(const WkvArgs& a, cudaStream_t stream);
 cudaError_t time_mix_v7(const WkvArgs& a, cudaStream_t stream);
+cudaError_t time_mix_v4(const uint32_t* cursors, int wide, const float* time_decay, const float* time_first, DView state,
+                        int dtype, const void* k, const void* v, const void* r, void* x, uint32_t C, uint32_t T,
+                        cudaStream_t stream);
 cudaError_t time_first_v7(const __half* u, int dtype, const void* r, const void* n, void* x, uint32_t S,
                           uint32_t H, uint32_t T, cudaStream_t stream);
 

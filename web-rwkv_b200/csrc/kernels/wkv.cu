@@ -239,6 +239,68 @@ cudaError_t time_mix_v7(const WkvArgs& a, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
+// time_mix_v4.wgsl: per channel c and token t (batch from the cursor), with (aa, bb, pp) = state rows 1..3:
+//   x_t = sigmoid(r_t) * (e1 aa + e2 v_t) / (e1 bb + e2),   e1 = exp(pp - q), e2 = exp(u + k_t - q), q = max(pp, u + k_t)
+//   (aa, bb, pp) <- (e1' aa + e2' v_t, e1' bb + e2', q'),      e1' = exp(w + pp - q'), e2' = exp(k_t - q'), q' = max(w + pp, k_t)
+// and state row 0 <- the input x of the sequence's last token in the job.  One thread per channel walks the tokens in
+// order and keeps (aa, bb, pp) in registers while consecutive tokens belong to one batch slot.
+__global__ void time_mix_v4_kernel(const uint32_t* cursors, int wide, const float* time_decay, const float* time_first,
+                                   DView state, int dtype, const void* k, const void* v, const void* r, void* x,
+                                   uint32_t C, uint32_t T) {
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const float u = time_first[c], w = time_decay[c];
+    float* st = static_cast<float*>(state.base);
+    uint32_t held = 0xffffffffu;  // batch slot whose recurrence is in registers
+    float aa = 0.f, bb = 0.f, pp = 0.f;
+    for (uint32_t t = 0; t < T; ++t) {
+        const CursorD cu = cursor_at(cursors, wide, t);
+        if (cu.batch != held) {
+            if (held != 0xffffffffu) {
+                st[state.index(c, 1, held)] = aa;
+                st[state.index(c, 2, held)] = bb;
+                st[state.index(c, 3, held)] = pp;
+            }
+            held = cu.batch;
+            aa = st[state.index(c, 1, held)];
+            bb = st[state.index(c, 2, held)];
+            pp = st[state.index(c, 3, held)];
+        }
+        const size_t ti = (size_t)t * C + c;
+        // the token-shift carry: read before this token's slot of x is overwritten (the last token's slot is >= t)
+        const uint32_t last = cu.token + cu.len - 1u;
+        if ((t == last || t == cu.token) && last >= t && last < T)
+            st[state.index(c, 0, held)] = dload(x, dtype, (size_t)last * C + c);
+        const float kk = dload(k, dtype, ti), vv = dload(v, dtype, ti);
+        const float rr = 1.0f / (1.0f + expf(-dload(r, dtype, ti)));
+        float ww = u + kk;
+        float q = fmaxf(pp, ww);
+        float e1 = expf(pp - q), e2 = expf(ww - q);
+        dstore(x, dtype, ti, rr * (e1 * aa + e2 * vv) / (e1 * bb + e2));
+        ww = w + pp;
+        q = fmaxf(ww, kk);
+        e1 = expf(ww - q);
+        e2 = expf(kk - q);
+        aa = e1 * aa + e2 * vv;
+        bb = e1 * bb + e2;
+        pp = q;
+    }
+    if (held != 0xffffffffu) {
+        st[state.index(c, 1, held)] = aa;
+        st[state.index(c, 2, held)] = bb;
+        st[state.index(c, 3, held)] = pp;
+    }
+}
+
+cudaError_t time_mix_v4(const uint32_t* cursors, int wide, const float* time_decay, const float* time_first, DView state,
+                        int dtype, const void* k, const void* v, const void* r, void* x, uint32_t C, uint32_t T,
+                        cudaStream_t stream) {
+    if (T == 0 || C == 0) return cudaSuccess;
+    time_mix_v4_kernel<<<(C + 127) / 128, 128, 0, stream>>>(cursors, wide, time_decay, time_first, state, dtype, k, v, r, x,
+                                                            C, T);
+    return cudaGetLastError();
+}
+
 cudaError_t time_first_v7(const __half* u, int dtype, const void* r, const void* n, void* x, uint32_t S, uint32_t H,
                           uint32_t T, cudaStream_t stream) {
     if (T == 0) return cudaSuccess;

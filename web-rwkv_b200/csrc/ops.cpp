@@ -361,6 +361,40 @@ int32_t wrk_op_matmul_mat_nf4(const wrk_view* matrix, wrk_tensor* quant, wrk_ten
     return matmul_common("matmul_mat_nf4", k::MAT_NF4, m, absmax, quant, input, output, act, out);
 }
 
+int32_t wrk_op_time_mix_v4(wrk_tensor* cursors, wrk_tensor* time_decay, wrk_tensor* time_first, const wrk_view* state,
+                           wrk_tensor* k, wrk_tensor* v, wrk_tensor* r, wrk_tensor* x, wrk_op** out) {
+    REQ_NN(cursors, time_decay, time_first, state, state->tensor, k, v, r, x, out);
+    REQ_FLOAT(x, "x");
+    REQ_DTYPE(k, x->dtype, "k");
+    REQ_DTYPE(v, x->dtype, "v");
+    REQ_DTYPE(r, x->dtype, "r");
+    REQ_DTYPE(time_decay, WRK_F32, "time_decay");
+    REQ_DTYPE(time_first, WRK_F32, "time_first");
+    REQ_DTYPE(state->tensor, WRK_F32, "state");
+    const Shape4 sh = x->shape;
+    const uint32_t C = sh[0], T = sh[1];
+    WRK_TRY(check_shape("x", sh, C, T, 1, 1));
+    WRK_TRY(check_shape("k", k->shape, C, T, 1, 1));
+    WRK_TRY(check_shape("v", v->shape, C, T, 1, 1));
+    WRK_TRY(check_shape("r", r->shape, C, T, 1, 1));
+    WRK_TRY(check_shape("time_decay", time_decay->shape, C, 1, 1, 1));
+    WRK_TRY(check_shape("time_first", time_first->shape, C, 1, 1, 1));
+    WRK_TRY(check_view("state", state, C, 4, state->shape[2], 1));
+    WRK_TRY(check_cursors(cursors, T));
+    const uint32_t* cp = static_cast<const uint32_t*>(cursors->ptr());
+    const int wide = cursors_wide(cursors, T);
+    const float* td = static_cast<const float*>(time_decay->ptr());
+    const float* tf = static_cast<const float*>(time_first->ptr());
+    DView sv = make_dview(*state);
+    const int dt = x->dtype;
+    const void *kp = k->ptr(), *vp = v->ptr(), *rp = r->ptr();
+    void* xp = x->ptr();
+    *out = new_atom("time_mix_v4",
+                    [=](cudaStream_t s) { return k::time_mix_v4(cp, wide, td, tf, sv, dt, kp, vp, rp, xp, C, T, s); },
+                    {cursors, time_decay, time_first, state->tensor, k, v, r, x});
+    return WRK_OK;
+}
+
 int32_t wrk_op_time_mix_v5(wrk_tensor* cursors, wrk_tensor* time_decay, wrk_tensor* time_first, const wrk_view* state,
                            wrk_tensor* k, wrk_tensor* v, wrk_tensor* r, wrk_tensor* x, wrk_op** out) {
     return time_mix_v56("time_mix_v5", 0, cursors, time_decay, time_first, state, k, v, r, x, out);
