@@ -7,13 +7,17 @@
 //     weights go straight into the A operand stage through a 128-byte-swizzled tensor map;
 //   * warp 10 (one lane) streams the fp16 activations of the step, [tokens x 64] through a 128-byte-swizzled
 //     tensor map, into the B operand stage (rows past the last token are zero-filled by the TMA unit);
-//   * warps 0-7 dequantize: each thread turns 32 weights of one row into fp16 (f32 math, one rounding) and
-//     stores them in the K-major 128-byte-swizzled layout tcgen05 reads; the (min, max) / absmax values of
-//     the next 256 columns are fetched with cp.async while the current ones are in use;
+//   * warps 0-7 dequantize as two groups of four warps on alternate pairs of steps: a thread turns the 64
+//     weights of one row and step into fp16 (f32 math, one rounding) and stores them in the K-major
+//     128-byte-swizzled layout tcgen05 reads; the (min, max) / absmax values of the next 256 columns are
+//     fetched with cp.async while the current ones are in use;
 //   * warp 8 (one lane) issues tcgen05.mma.cta_group::1.kind::f16 (M = 128, N = token tile, K = 16, four per
 //     step) into a TMEM accumulator of 128 lanes x N fp32 columns and releases the stage with tcgen05.commit;
 //   * after the last step warps 0-7 read the accumulator back with tcgen05.ld (warp w reads lanes
 //     32 (w % 4) ..), apply the activation and store token-major rows.
+// Where the output tiles alone leave SMs idle, the CTAs of a thread-block cluster (up to 8, along grid.z) split the
+// K range of one tile: each writes its partial accumulator to its own shared memory and, after a cluster barrier,
+// adds its share of the columns over all peers through distributed shared memory.
 // Weights enter the MMA as fp16(fma(q, (max - min) / 255, min)) resp. fp16(table[nib] * absmax), computed in
 // f32 and rounded once; the accumulation is fp32.  Every wait on an mbarrier is bounded: on a timeout the
 // kernel records WRK_ERR_TIMEOUT in the context's status word, stops waiting and still frees its TMEM.
