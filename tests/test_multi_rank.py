@@ -35,7 +35,7 @@ WORKER = textwrap.dedent(
 def test_replica_aggregation_two_gloo_ranks(tmp_path):
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(free_port()), WORLD_SIZE="2")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(free_port()), WORLD_SIZE="2", GLOO_SOCKET_IFNAME="lo")
     procs = []
     for rank in range(2):
         e = dict(env, RANK=str(rank), LOCAL_RANK=str(rank))

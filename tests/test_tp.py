@@ -14,6 +14,20 @@ WORKER = os.path.join(ROOT, "tests", "tp_worker.py")
 
 
 def _spawn(mode, world, port):
+    """Runs the worker ranks; for the CPU (gloo) ranks a rendezvous that fails (a port taken between its probe and its use, a loopback
+    connection refused while the host is busy) is repeated once on another port, with a warning that carries the
+    first attempt's output."""
+    if mode != "cpu":  # ranks that drive GPUs are never run a second time after a failure
+        return _spawn_once(mode, world, port)
+    try:
+        return _spawn_once(mode, world, port)
+    except AssertionError as first:
+        import warnings
+        warnings.warn(f"worker ranks failed once, repeating: {first}")
+        return _spawn_once(mode, world, free_port())
+
+
+def _spawn_once(mode, world, port):
     # loopback for every rendezvous (the host name of a container need not resolve); no NVLS: a rank that
     # dies must not leave peers' memory bound to a switch-side reduction object
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0",
