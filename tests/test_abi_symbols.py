@@ -10,7 +10,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def _declared():
     names = []
     for header in sorted(glob.glob(os.path.join(ROOT, "include", "*.h"))):
-        text = open(header).read()
+        with open(header) as f:
+            text = f.read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
         names += re.findall(r"\b(wrk_[a-z0-9_]+)\s*\(", text)
     return sorted(set(names))
