@@ -1,6 +1,6 @@
 """Op-level sweep of the quantized matmul: `Matrix::matmul_op` over weight shapes and token counts.
 
-    python web-rwkv_b200/op_sweep.py                       # Int8 / NF4 / fp16, three shapes, N in {1, 16, 64, 256, 1024}
+    python web-rwkv_b200/op_sweep.py                       # Int8 / NF4 / fp16, three shapes, N in {1, 4, 16, 64, 256, 1024}
     python web-rwkv_b200/op_sweep.py --kind int8 --shape 4096,4096 --tokens 1024 --reps 3 --single
     python web-rwkv_b200/op_sweep.py --wkv                 # time_mix_v7 / v6: 64 heads of 64 x 64 f32 state, T = 1 ... 512
 
@@ -96,7 +96,7 @@ def main():
     ap.add_argument("--wkv", action="store_true", help="sweep time_mix_v7 / time_mix_v6 over T instead of the matmuls")
     ap.add_argument("--kind", default="int8,nf4,fp16")
     ap.add_argument("--shape", action="append", help="K,M (repeatable)")
-    ap.add_argument("--tokens", default="1,16,64,256,1024")
+    ap.add_argument("--tokens", default="1,4,16,64,256,1024")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--matrices", type=int, default=8)
     ap.add_argument("--single", action="store_true")
