@@ -1,24 +1,29 @@
 #!/usr/bin/env python
 """Benchmark of the B200-native web-rwkv hot path: Int8 batch-1 decode of an RWKV-v6-shaped model.
 
-Workload (the configuration the headline metric is quoted on): RWKV-v6 1.6B-shaped random-init
-model (n_embd 2048, 24 layers, FFN 7168, vocab 65536), every layer Int8 through the quantizer,
-a 64-token seeded prompt, then batch-1 decode.  One *step* = 512 decoded tokens.
+Workload (the configuration the target is quoted on): RWKV-v6 7B-shaped random-init model (n_embd 4096,
+32 layers, FFN 14336, vocab 65536), every layer Int8 through the quantizer, a 64-token seeded prompt, then
+batch-1 decode.  One *step* = `--decode` decoded tokens (default 256).
 
   value  tokens/s with the step's inputs (embedding rows) already resident in HBM and the logits left
-         on the device: one stream-ordered device copy + one CUDA-graph launch per token.
+         on the device: one stream-ordered device copy + the decode job per token.
   e2e    tokens/s through the reference-facing call (`SimpleRuntime::infer` = wrk_runtime_infer) with
          host token ids in and host logits out every token (pinned H2D of the embedding row and
          cursors, D2H of the [vocab] fp32 logits, greedy arg-max on the host feeding the next token).
-  roofline      the Int8 GEMV kernel (dominant: it streams ~84 % of a decode step's bytes), timed with
+  checked       before anything is timed, the logits of one decoded token from the fused job are compared
+                with the one-launch-per-reference-op job of the same model (max-abs difference reported).
+  roofline      the Int8 GEMV kernel (dominant: it streams ~91 % of a decode step's bytes), timed with
                 CUDA events over a loop that runs every quantized matmul of every layer at T = 1 in
-                model order (weights of all layers = 1.3 GB, larger than L2).
+                model order (weights of all layers = 7 GB, larger than L2).
+  decode_1p6b   secondary: the same measurement of `value` on the 1.6B-shaped model (BASELINE config 2).
+  prefill       secondary: one 256-token chunk of the headline model through wrk_runtime_infer.
   cpu_baseline  the CPU oracle (a port of the reference's shader arithmetic; the reference itself is
                 Rust + WGSL and cannot be built here) decoding a bounded sample on the host cores.
 
 `--impl reference` times that CPU port on the same workload (bounded sample per step).
-With N > 1 GPUs every rank decodes its own replica of the same model (the model is tiny compared with
-180 GB; data-parallel replicas, weak scaling, no data-path collective).
+`--sweep matmul|wkv` runs the op-level sweep (BASELINE config 5) instead and prints one line per point.
+With N > 1 GPUs every rank decodes its own replica of the same model (data-parallel replicas, weak
+scaling, no data-path collective).
 """
 import argparse
 import importlib
@@ -29,17 +34,31 @@ import sys
 import threading
 import time
 
-import numpy as np
-
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-CONFIG = "v6-1.6b"
+
+def host_threads():
+    """Cores this process may run on.  Launchers such as torch.distributed.run export OMP_NUM_THREADS=1 to
+    their children; the CPU arms state their own thread count instead, before the OpenMP runtime loads."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+os.environ["OMP_NUM_THREADS"] = str(host_threads())
+
+import numpy as np  # noqa: E402
+
+CONFIG = "v6-7b"
+SECONDARY = "v6-1.6b"
 PROMPT = 64
-DECODE = 512
+DECODE = 256
 SEED_WEIGHTS, SEED_TOKENS = 1002, 2002
 
-
+# dram read + write per launch over algorithmic bytes, from the ncu capture of the GEMV kernel summarised
+# under profiles/ (every Int8 launch of the captured token measured 1.01)
 NCU_TRAFFIC_RATIO = 1.01
 
 
@@ -137,7 +156,7 @@ def gemv_roofline(wrk, rt, ctx, model, dims, reps):
     version, C, L, F, V = dims
     lib = wrk.lib()
     import ctypes
-    ops, keep = [], []
+    ops = []
     x_c = ctx.from_numpy(np.random.default_rng(1).standard_normal((1, C)).astype(np.float16))
     x_f = ctx.from_numpy(np.random.default_rng(2).standard_normal((1, F)).astype(np.float16))
     y_c, y_f = ctx.tensor(wrk.F32, [C, 1]), ctx.tensor(wrk.F16, [F, 1])
@@ -162,7 +181,7 @@ def gemv_roofline(wrk, rt, ctx, model, dims, reps):
     return ms * 1e-3 / (reps * launches), gemv_bytes / launches, launches
 
 
-def cpu_decode(config, tensors, dims, sample_tokens, fast=True):
+def cpu_decode(tensors, dims, sample_tokens, fast=True):
     """The oracle port decoding `sample_tokens` tokens after a 1-token prompt; returns tokens/s."""
     from oracle import model as omodel
     from oracle import oracle
@@ -178,6 +197,173 @@ def cpu_decode(config, tensors, dims, sample_tokens, fast=True):
     return sample_tokens / dt, oracle.num_threads(fast)
 
 
+def workload_name(config, dims, decode):
+    version, C, L, F, V = dims
+    return (f"RWKV-v6-shaped {config} random-init (n_embd {C}, {L} layers, FFN {F}, vocab {V}), all layers "
+            f"Int8, {PROMPT}-token seeded prompt then batch-1 decode, {decode} tokens per step")
+
+
+def reference_arm(args, synth, dims, workload):
+    """The reference's own implementation of the path is Rust + WGSL on wgpu and cannot be built or run here;
+    its arithmetic restated in C++ (the oracle port) is timed on the host cores instead."""
+    from oracle import model as omodel
+    from oracle import oracle
+    L = dims[2]
+    tensors = synth.make_model(args.config, SEED_WEIGHTS, L)
+    ref = omodel.OracleModel(tensors, {i: 1 for i in range(L)}, fast=True)
+    state = ref.init_state(1)
+    out = ref.run(state, [[0]], [(1, 0)])[0]
+    sample = args.cpu_sample
+
+    def one_step():
+        nonlocal out
+        for _ in range(sample):
+            out = ref.run(state, [[int(np.argmax(out[-1]))]], [(1, 0)])[0]
+
+    for _ in range(min(args.warmup, 1)):
+        one_step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        one_step()
+    dt = time.perf_counter() - t0
+    value = args.steps * sample / dt
+    cores = oracle.num_threads(True)
+    print(json.dumps({
+        "impl": "reference", "metric": "int8 batch-1 decode throughput", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload, "sample": f"{sample} decoded tokens per step"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": f"{sample} decoded tokens per step, {args.steps} steps"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def device_decode(wrk, rt, ctx, bundle, embeds, decode, steps, warmup, sync):
+    """Times `steps` x `decode` tokens of the T = 1 job with device-resident embedding rows; returns
+    (milliseconds, kernels launched in the timed region, kernels per token)."""
+    job = bundle.dispatch([(1, wrk.RNN_LAST)])
+
+    def one_step():
+        for t in range(decode):
+            rt.job_load_embed(job, embeds, t)
+            job.submit()
+
+    for _ in range(warmup):
+        one_step()
+    sync()
+    launches0 = ctx.launch_count()
+    ctx.timer_start()
+    for _ in range(steps):
+        one_step()
+    ms = ctx.timer_stop()
+    sync()
+    return ms, ctx.launch_count() - launches0, job.num_kernels()
+
+
+def check_fused_against_strict(wrk, rt, model, prompt, vocab):
+    """One decoded token after the prompt through the fused job and through the op-by-op job."""
+    outs = []
+    for fused in (True, False):
+        bundle = rt.Bundle(model, 1)
+        bundle.set_fused(fused)
+        inp = rt.RnnInput([(prompt, wrk.RNN_LAST)], PROMPT)
+        logits = np.empty((PROMPT, vocab), dtype=np.float32)
+        first = bundle.infer(inp, logits)[0].copy()
+        inp.append(0, [int(np.argmax(first[-1]))])
+        outs.append(bundle.infer(inp, logits)[0][-1].copy())
+        del bundle
+    return float(np.max(np.abs(outs[0] - outs[1]))), float(np.max(np.abs(outs[1])))
+
+
+# ---- op-level sweep (BASELINE config 5) ---------------------------------------------------------------
+BYTES_PER_WEIGHT = {"int8": 1.0 + 4.0 / 128.0, "nf4": 0.5 + 2.0 / 64.0, "fp16": 2.0}
+
+
+def sweep_matmul(wrk, ctx, rng, kind, K, M, N, reps, matrices, single):
+    """CUDA-event time per launch of a graph holding `matrices` different weight matrices of the shape (so that
+    consecutive launches do not re-read one matrix from L2); `single` submits one op per launch without a graph
+    (the form used under a profiler)."""
+    def make():
+        w = ctx.from_numpy((rng.standard_normal((M, K), dtype=np.float32) * 0.02).astype(np.float16))
+        return wrk.Matrix.quant_u8(w) if kind == "int8" else wrk.Matrix.quant_nf4(w) if kind == "nf4" else wrk.Matrix.fp16(w)
+
+    mats = [make() for _ in range(1 if single else matrices)]
+    x = ctx.from_numpy(rng.standard_normal((N, K), dtype=np.float32).astype(np.float16))
+    y = ctx.tensor(wrk.F16, [M, N])
+    ops = [m.matmul_op(x, y, turbo=(N % 32 == 0)) for m in mats]
+    if single:
+        for _ in range(reps):
+            ctx.run(ops[0])
+        ctx.synchronize()
+        print(f"{kind} K={K} M={M} N={N}: {reps} single launches", flush=True)
+        return
+    cmd = ctx.encode(wrk.op_list(ops), use_graph=True)
+    for _ in range(3):
+        cmd.submit()
+    ctx.synchronize()
+    ctx.timer_start()
+    for _ in range(reps):
+        cmd.submit()
+    us = ctx.timer_stop() * 1e3 / (reps * len(mats))
+    nbytes = K * M * BYTES_PER_WEIGHT[kind] + 2.0 * N * (K + M)
+    print(f"{kind} K={K} M={M} N={N}: {us:8.1f} us  {nbytes / us / 1e3:8.1f} GB/s  {2.0 * K * M * N / us / 1e6:8.1f} TFLOP/s",
+          flush=True)
+
+
+def sweep_wkv(wrk, ctx, rng, version, H, T, reps):
+    """`time_mix_v7` (fp16 r, w, n, x) or `time_mix_v6` (f32 k, v, r, x) on one sequence of T tokens: H heads of
+    64 x 64 f32 state.  The state grows stale over the repetitions, which does not change the work."""
+    S = 64
+    C = S * H
+    cursors = ctx.from_numpy(np.array([[0, 0, T]] * T, dtype=np.uint32))  # wide cursors: (batch, token, len) per token
+    state = ctx.from_numpy((rng.standard_normal((1, S + 2, C)) * 0.1).astype(np.float32))
+    if version == 7:
+        f = np.float16
+        r = ctx.from_numpy(rng.standard_normal((T, H, S)).astype(f))
+        w = ctx.from_numpy(rng.standard_normal((T, H, S)).astype(f))
+        kk = rng.standard_normal((T, H, S)).astype(np.float32)
+        kk /= np.linalg.norm(kk, axis=-1, keepdims=True)  # the model L2-normalises kk per head
+        n = np.stack([rng.standard_normal((T, H, S)), rng.standard_normal((T, H, S)), rng.uniform(0, 1, (T, H, S)), kk])
+        x = ctx.from_numpy(rng.standard_normal((T, H, S)).astype(f))
+        op = wrk.time_mix_v7(cursors, state.view(y=(0, S + 1)), r, w, ctx.from_numpy(n.astype(f)), x)
+        nbytes = 2.0 * C * S * 4 + T * C * 2.0 * 8
+    else:
+        f = np.float32
+        k, v, r, x = (ctx.from_numpy(rng.standard_normal((T, H, S)).astype(f) * 0.5) for _ in range(4))
+        decay = ctx.from_numpy(np.exp(-np.exp(rng.uniform(-6, 1, (T, H, S)))).astype(f))
+        first = ctx.from_numpy(rng.uniform(-1, 1, (H, S)).astype(f))
+        op = wrk.time_mix_v6(cursors, decay, first, state.view(y=(0, S + 1)), k, v, r, x)
+        nbytes = 2.0 * C * S * 4 + T * C * 4.0 * 6
+    cmd = ctx.encode(wrk.op_list([op]), use_graph=True)
+    for _ in range(3):
+        cmd.submit()
+    ctx.synchronize()
+    ctx.timer_start()
+    for _ in range(reps):
+        cmd.submit()
+    us = ctx.timer_stop() * 1e3 / reps
+    flops = (10.0 if version == 7 else 7.0) * C * S * T
+    print(f"time_mix_v{version} H={H} T={T}: {us:8.1f} us  {us / T:6.2f} us/token  {nbytes / us / 1e3:8.1f} GB/s  "
+          f"{flops / us / 1e6:6.2f} TFLOP/s", flush=True)
+
+
+def sweep(args):
+    wrk = importlib.import_module("web-rwkv_b200")
+    ctx = wrk.Context(0)
+    rng = np.random.default_rng(4000)
+    if args.sweep == "wkv":
+        for version in (7, 6):
+            for T in (1, 2, 8, 32, 64, 128, 256, 512):
+                sweep_wkv(wrk, ctx, rng, version, 64, T, args.reps)
+        return
+    shapes = [tuple(int(v) for v in s.split(",")) for s in (args.shape or ["2048,2048", "2560,8960", "4096,4096"])]
+    for kind in args.kind.split(","):
+        for K, M in shapes:
+            for N in (int(v) for v in args.tokens.split(",")):
+                sweep_matmul(wrk, ctx, rng, kind, K, M, N, args.reps, args.matrices, args.single)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -187,11 +373,22 @@ def main():
     ap.add_argument("--config", default=CONFIG)
     ap.add_argument("--layers", type=int, default=None, help="debug: truncate the model")
     ap.add_argument("--decode", type=int, default=DECODE)
-    ap.add_argument("--cpu-sample", type=int, default=8)
+    ap.add_argument("--cpu-sample", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true")
     ap.add_argument("--strict", action="store_true", help="one launch per reference op (no fused kernels)")
+    ap.add_argument("--sweep", choices=["matmul", "wkv"], help="op-level sweep instead of the model benchmark")
+    ap.add_argument("--kind", default="int8,nf4,fp16")
+    ap.add_argument("--shape", action="append", help="sweep: K,M (repeatable)")
+    ap.add_argument("--tokens", default="1,4,16,64,256,1024")
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--matrices", type=int, default=8)
+    ap.add_argument("--single", action="store_true")
     args = ap.parse_args()
+
+    if args.sweep:
+        return sweep(args)
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -200,44 +397,11 @@ def main():
     version, C, L, F, V = synth.CONFIGS[args.config]
     L = args.layers or L
     dims = (version, C, L, F, V)
-    workload = (f"RWKV-v6-shaped {args.config} random-init (n_embd {C}, {L} layers, FFN {F}, vocab {V}), all layers "
-                f"Int8, {PROMPT}-token seeded prompt then batch-1 decode, {args.decode} tokens per step")
+    workload = workload_name(args.config, dims, args.decode)
 
     if args.impl == "reference":
-        # The reference's own CPU implementation of the path does not exist (it is Rust + WGSL on wgpu and
-        # cannot be built or run here); its arithmetic restated in C++ (the oracle port) is timed instead.
-        if rank != 0:
-            return
-        tensors = synth.make_model(args.config, SEED_WEIGHTS, L)
-        from oracle import model as omodel
-        from oracle import oracle
-        ref = omodel.OracleModel(tensors, {i: 1 for i in range(L)}, fast=True)
-        state = ref.init_state(1)
-        out = ref.run(state, [[0]], [(1, 0)])[0]
-        sample = args.cpu_sample
-
-        def one_step():
-            nonlocal out
-            for _ in range(sample):
-                out = ref.run(state, [[int(np.argmax(out[-1]))]], [(1, 0)])[0]
-
-        for _ in range(min(args.warmup, 1)):
-            one_step()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            one_step()
-        dt = time.perf_counter() - t0
-        value = args.steps * sample / dt
-        cores = oracle.num_threads(True)
-        print(json.dumps({
-            "impl": "reference", "metric": "int8 batch-1 decode throughput", "value": value, "unit": "tokens/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": workload, "sample": f"{sample} decoded tokens per step"},
-            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
-                             "sample": f"{sample} decoded tokens per step, {args.steps} steps"},
-            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        }))
+        if rank == 0:
+            reference_arm(args, synth, dims, workload)
         return
 
     wrk = importlib.import_module("web-rwkv_b200")
@@ -251,31 +415,29 @@ def main():
 
     ctx = wrk.Context(local_rank)
     keep = rank == 0 and not args.no_cpu_baseline
+    t_build = time.perf_counter()
     model, tensors, _ = build_model(wrk, rt, synth, ctx, args.config, L, keep=keep)
-    bundle = rt.Bundle(model, 1)
-    bundle.set_fused(not args.strict)
+    ctx.synchronize()
+    t_build = time.perf_counter() - t_build
     rng = np.random.default_rng(SEED_TOKENS + rank)
     prompt = rng.integers(0, V - 1, PROMPT).tolist()
-    total_tokens = args.decode * (args.steps + args.warmup)
-    tokens = rng.integers(0, V - 1, total_tokens).astype(np.uint32)
+    tokens = rng.integers(0, V - 1, args.decode).astype(np.uint32)
+
+    # ---- parity of what is timed: the fused job against the op-by-op job, one decoded token ----
+    checked = None
+    if not args.strict:
+        diff, scale = check_fused_against_strict(wrk, rt, model, prompt, (V + 7) // 8 * 8)
+        checked = {"checked": bool(diff <= 2e-2 * max(1.0, scale)), "max_abs": diff, "logit_scale": scale,
+                   "against": "one-launch-per-reference-op job, same model, prompt and token"}
+
+    bundle = rt.Bundle(model, 1)
+    bundle.set_fused(not args.strict)
 
     # prompt (GEMM path), untimed
     inp = rt.RnnInput([(prompt, wrk.RNN_LAST)], PROMPT)
     logits = np.empty((PROMPT, bundle.vocab), dtype=np.float32)
     out = bundle.infer(inp, logits)[0]
     next_token = int(np.argmax(out[-1]))
-
-    # ---- device-resident decode: embedding rows of the step's tokens live in HBM ----
-    emb = synth.make_globals(version, C, V, SEED_WEIGHTS)["emb.weight"]
-    embeds = ctx.from_numpy(emb[tokens[: args.decode]])  # [C, decode] fp16, reused by every step
-    del emb
-    job = bundle.dispatch([(1, wrk.RNN_LAST)])
-    kernels_per_token = job.num_kernels()
-
-    def device_step():
-        for t in range(args.decode):
-            rt.job_load_embed(job, embeds, t)
-            job.submit()
 
     def barrier():
         ctx.synchronize()
@@ -285,24 +447,19 @@ def main():
             torch.cuda.synchronize()
         ctx.synchronize()
 
-    for _ in range(args.warmup):
-        device_step()
+    # ---- device-resident decode: embedding rows of the step's tokens live in HBM ----
+    emb = synth.make_globals(version, C, V, SEED_WEIGHTS)["emb.weight"]
+    embeds = ctx.from_numpy(emb[tokens])  # [C, decode] fp16, reused by every step
     barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
-    launches0 = ctx.launch_count()
-    ctx.timer_start()
-    for _ in range(args.steps):
-        device_step()
-    ms = ctx.timer_stop()
-    barrier()
-    gpu_launches = ctx.launch_count() - launches0
+    ms, gpu_launches, kernels_per_token = device_decode(wrk, rt, ctx, bundle, embeds, args.decode, args.steps,
+                                                        args.warmup, barrier)
     clocks = sampler.stop()
     ms = max_over_ranks(ms, dist)
     value = whole_job_rate(world, args.steps, args.decode, ms)
 
     # ---- end to end through the reference-facing call: host tokens in, host logits out ----
-    import ctypes
     host_logits = np.empty((1, bundle.vocab), dtype=np.float32)
     inp = rt.RnnInput([([next_token], wrk.RNN_LAST)], 32)
 
@@ -354,16 +511,33 @@ def main():
 
     # ---- roofline of the dominant kernel ----
     peak, peak_kind = _peaks()
-    sec_per_launch, bytes_per_launch, launches = gemv_roofline(wrk, rt, ctx, model, dims, reps=20)
+    sec_per_launch, bytes_per_launch, launches = gemv_roofline(wrk, rt, ctx, model, dims, reps=10)
     achieved = bytes_per_launch / sec_per_launch / 1e9
     total_bytes, gemv_bytes, _ = step_bytes(C, L, F, V)
-    # dram read + write per launch: the ncu capture of the same kernel on this model's matrices (summary under
-    # profiles/, fused_gemv_kernel) measured 1.01 x the algorithmic bytes for every Int8 launch
     traffic = NCU_TRAFFIC_RATIO * bytes_per_launch
+    del bundle, embeds
+
+    # ---- secondary: the 1.6B-shaped model (BASELINE config 2), device-resident decode only ----
+    secondary = None
+    if not args.no_secondary and args.config != SECONDARY and not args.layers:
+        model2, _, dims2 = build_model(wrk, rt, synth, ctx, SECONDARY)
+        _, C2, L2, F2, V2 = dims2
+        bundle2 = rt.Bundle(model2, 1)
+        bundle2.set_fused(not args.strict)
+        bundle2.infer(rt.RnnInput([(prompt, wrk.RNN_LAST)], PROMPT), logits)
+        emb2 = synth.make_globals(6, C2, V2, SEED_WEIGHTS)["emb.weight"]
+        embeds2 = ctx.from_numpy(emb2[tokens])
+        ms2, _, k2 = device_decode(wrk, rt, ctx, bundle2, embeds2, args.decode, 3, 3, ctx.synchronize)
+        bytes2, _, _ = step_bytes(C2, L2, F2, V2)
+        rate2 = 3 * args.decode / (ms2 * 1e-3)
+        secondary = {"value": rate2, "unit": "tokens/s", "workload": workload_name(SECONDARY, dims2, args.decode),
+                     "kernels_per_token": int(k2), "algorithmic_bytes_per_token": bytes2,
+                     "frac_of_roofline": rate2 / (peak * 1e9 / bytes2)}
+        del bundle2, embeds2, model2
 
     cpu = None
     if not args.no_cpu_baseline:
-        cpu_tps, cores = cpu_decode(args.config, tensors, dims, args.cpu_sample)
+        cpu_tps, cores = cpu_decode(tensors, dims, args.cpu_sample)
         cpu = {"value": cpu_tps, "unit": "tokens/s", "cores": cores, "kind": "port",
                "sample": f"{args.cpu_sample} greedy decode tokens of the same model after a 1-token prompt"}
 
@@ -373,18 +547,21 @@ def main():
         "scaling": "weak", "vs_baseline": None, "dtype": "f16 activations, f32 accumulate, u8 weights",
         "data": "synthetic",
         "config": {"workload": workload, "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
-                   "l2": "weights of one token (1.4 GB) exceed L2 (126 MB); no flush needed",
-                   "mode": "strict" if args.strict else "fused"},
+                   "l2": f"weights of one token ({total_bytes / 1e9:.1f} GB) exceed L2 (126 MB); no flush needed",
+                   "mode": "strict" if args.strict else "fused", "model_build_s": t_build},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s",
-                "h2d_bytes_per_step": args.decode * (C * 2 + 12), "d2h_bytes_per_step": args.decode * bundle.vocab * 4},
+                "h2d_bytes_per_step": args.decode * (C * 2 + 12), "d2h_bytes_per_step": args.decode * ((V + 7) // 8 * 8) * 4},
+        "parity": checked,
         "prefill": prefill,
+        "decode_1p6b": secondary,
         "gpu_launches": int(gpu_launches),
         "kernels_per_token": int(kernels_per_token),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": peak_kind, "traffic": traffic, "kernel": "fused_gemv_kernel (Int8 weights, T = 1, standalone launches)",
+                     "peak_kind": peak_kind, "traffic": traffic,
+                     "kernel": "Int8 weight-streaming GEMV (T = 1, standalone launches over the model's matrices)",
                      "algorithmic_bytes_per_launch": bytes_per_launch, "us_per_launch": sec_per_launch * 1e6,
-                     "launches_timed": launches * 20},
+                     "launches_timed": launches * 10},
         "decode_step": {"algorithmic_bytes_per_token": total_bytes, "gemv_share": gemv_bytes / total_bytes,
                         "hbm_roofline_tokens_per_s": peak * 1e9 / total_bytes,
                         "frac_of_roofline": value / world / (peak * 1e9 / total_bytes)},

@@ -4,6 +4,7 @@ import numpy as np
 import pytest
 
 from oracle import oracle
+from tests.golden import reference_answers as ra
 from tests.util import is_approx_eps
 
 
@@ -244,3 +245,36 @@ def test_wkv4_against_dense_numpy():
         decay = np.array([(n - 1 - s_) * w.astype(np.float64) + k64[s_] for s_ in range(n)])
         assert np.allclose(st[batch, 1] * np.exp(st[batch, 3].astype(np.float64)), (np.exp(decay) * v64).sum(axis=0), rtol=1e-4)
         assert np.allclose(st[batch, 2] * np.exp(st[batch, 3].astype(np.float64)), np.exp(decay).sum(axis=0), rtol=1e-4)
+
+
+@pytest.mark.parametrize("c,r,t", [(2560, 2048, 8), (320, 64, 320)])
+def test_int8_against_the_reference_tests_own_answer_code(c, r, t):
+    # tests/golden/reference_answers.py restates the host code of test_matmul_int8; the oracle stands where the
+    # shaders stand in that test and must pass the same three comparisons
+    m, x = ra.int8_inputs(c, r, t)
+    q_ans, mn, mx = ra.int8_quantize(m)
+    q, mm = oracle.quantize_mat_int8(m)
+    assert ra.is_approx_eps(mm.reshape(-1, 2)[:, 0], mn, 0.01).all() and ra.is_approx_eps(mm.reshape(-1, 2)[:, 1], mx, 0.01).all()
+    assert (np.abs(q.astype(np.int32) - q_ans.astype(np.int32)) < 2).all()
+    # the test feeds the *shader's* bytes to its answer loop
+    ans = ra.int8_answer(q, mn, mx, x)
+    for mode in (0, 1):
+        if mode == 1 and c % 128:
+            continue
+        y = np.zeros((t, r), dtype=np.float32)
+        oracle.matmul(oracle.MAT_INT8, q, mm, x, y, mode=mode)
+        assert ra.is_approx_eps(y, ans, 0.01).all(), f"mode {mode}"
+
+
+@pytest.mark.parametrize("c,r,t", [(2560, 2048, 8), (320, 64, 320)])
+def test_nf4_against_the_reference_tests_own_answer_code(c, r, t):
+    m, x = ra.nf4_inputs(c, r, t)
+    idx, packed, absmax = ra.nf4_quantize(m)
+    q, am = oracle.quantize_mat_nf4(m)
+    assert ra.is_approx_eps(am, absmax, 0.01).all()
+    assert np.array_equal(q.reshape(packed.shape), packed)  # the test asserts the packed nibbles equal
+    ans = ra.nf4_answer(idx, absmax, x)
+    for mode in (0, 1):
+        y = np.zeros((t, r), dtype=np.float32)
+        oracle.matmul(oracle.MAT_NF4, q, am, x, y, mode=mode)
+        assert ra.is_approx_eps(y, ans, 0.01).all(), f"mode {mode}"

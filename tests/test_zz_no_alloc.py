@@ -1,8 +1,12 @@
 """`wrk_gemv_int8_static`: the Int8 GEMV entry point that allocates nothing (its row-range table is a static
 device array).  Collected last so that it also runs after every other test has used the device; it passes on
-its own as well.  Checked against the existing entry point (`Matrix::matmul_op` -> matmul_vec_int8)."""
+its own as well.  Checked against the existing entry point (`Matrix::matmul_op` -> matmul_vec_int8), bit for bit,
+and against the CPU oracle within the path's tolerance."""
 import numpy as np
 import pytest
+
+from oracle import oracle
+from tests.util import assert_close
 
 pytestmark = pytest.mark.gpu
 
@@ -24,20 +28,22 @@ def _case(wrk, ctx, rng, K, M, T, act):
         wrk.gemv_int8_static(ctx, wq, mm, x, y_new, act)
         ctx.synchronize()
         got = y_new.numpy().copy()
-        outs.append((ref, got))
+        want = np.zeros((T, M), dtype=np.float32)
+        oracle.matmul(oracle.MAT_INT8, wq.numpy().reshape(M, K), mm.numpy().reshape(-1), x.numpy().reshape(T, K), want,
+                      act=act)
+        outs.append((ref.reshape(T, M), got.reshape(T, M), want))
     return outs
 
 
 @pytest.mark.parametrize("K,M,T,act", [(2048, 2048, 1, 0), (1024, 4099, 3, 1), (7168, 2048, 1, 0), (256, 65536, 2, 2)])
 def test_static_gemv_matches_matmul_vec_int8(wrk, ctx, K, M, T, act):
     rng = np.random.default_rng(K + M + T)
-    for ref, got in _case(wrk, ctx, rng, K, M, T, act):
+    for ref, got, want in _case(wrk, ctx, rng, K, M, T, act):
         assert np.isfinite(got).all()
-        # same kernel and row split as the existing entry point; the warps' partial sums meet in shared-memory
-        # atomics whose order is free, so the last bits of the f32 results may differ between any two launches
-        scale = max(1.0, float(np.abs(ref).max()))
-        err = float(np.abs(got - ref).max())
-        assert err <= 2e-5 * scale, f"max |diff| {err} at scale {scale}"
+        # same kernel and the same row split as the existing entry point, and the warps' partial sums are added
+        # in warp order: the two launches give the same bits
+        assert np.array_equal(got, ref), f"max |diff| {float(np.abs(got - ref).max())}"
+        assert_close(got, want, f"static gemv {K}x{M} T={T} act={act}")
 
 
 def test_static_gemv_rejects_what_does_not_fit(wrk, ctx):

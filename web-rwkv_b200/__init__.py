@@ -480,7 +480,7 @@ class Matrix:
         return _mk(fn, self.handle, pi, po, act, int(turbo), keep=(self, ki, ko))
 
 
-def gemv_int8_static(ctx, matrix, minmax, x, y, act=ACT_NONE, num_ctas=0, device=0):
+def gemv_int8_static(ctx, matrix, minmax, x, y, act=ACT_NONE, num_ctas=0, device=None):
     """`wrk_gemv_int8_static` (no counterpart in the reference): y[t][m] = act(W[m][:] . x[t][:]) on the context's
     stream without any allocation; the kernel's row-range table sits in a static device array (512 CTAs at most).
     `matrix` u8 [k, m], `minmax` f16 pairs, `x` f16 [k, t], `y` f32 [m, t]."""
@@ -493,6 +493,10 @@ def gemv_int8_static(ctx, matrix, minmax, x, y, act=ACT_NONE, num_ctas=0, device
     check(lib().wrk_context_stream(ctx.handle, ctypes.byref(stream)))
     k, m = matrix.shape[0], matrix.shape[1]
     t = x.shape[1]
+    if device is None:  # the context's own device
+        dev = ctypes.c_int32()
+        check(lib().wrk_context_device(ctx.handle, ctypes.byref(dev)))
+        device = dev.value
     check(lib().wrk_gemv_int8_static(ctypes.c_int32(device), stream, ptrs[0], ptrs[1], ptrs[2], ptrs[3],
                                      ctypes.c_uint32(k), ctypes.c_uint32(m), ctypes.c_uint32(t), ctypes.c_int32(act),
                                      ctypes.c_uint32(num_ctas)))

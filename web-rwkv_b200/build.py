@@ -85,7 +85,7 @@ def build(force=False, verbose=False, extra_flags=()):
     if failed:
         raise RuntimeError("nvcc failed")
     if procs or force or not os.path.exists(LIB):
-        cmd = [nvcc, "-shared", "-ccbin", "/usr/bin/g++", "-o", LIB, *objects, "-lcuda", "-ldl"]
+        cmd = [nvcc, "-shared", "-ccbin", "/usr/bin/g++", "-o", LIB, *objects, "-ldl"]
         subprocess.run(cmd, check=True)
     return LIB
 

@@ -5,6 +5,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "common.h"
@@ -54,6 +55,16 @@ int32_t nccl_fail(const char* what, ncclResult_t r) {
     return wrk::set_error(WRK_ERR_NCCL, "%s failed: %s", what, nccl().GetErrorString(r));
 }
 
+// Shared by every op built on a communicator: the communicator is torn down only after the last op (and
+// with it the last op list or command buffer) that may still launch on it is gone.
+struct CommHold {
+    wrk_comm* comm;
+    explicit CommHold(wrk_comm* c) : comm(c) { c->refs.fetch_add(1); }
+    CommHold(const CommHold&) = delete;
+    CommHold& operator=(const CommHold&) = delete;
+    ~CommHold() { wrk_comm_release(comm); }
+};
+
 bool nccl_dtype(int dtype, ncclDataType_t* out) {
     switch (dtype) {
         case WRK_F32: *out = ncclFloat32; return true;
@@ -84,6 +95,10 @@ int32_t wrk_comm_create(wrk_context* ctx, const uint8_t id[128], int32_t rank, i
     WRK_REQUIRE(world >= 1 && rank >= 0 && rank < world, WRK_ERR_INVALID_ARGUMENT, "rank %d of %d", rank, world);
     WRK_NEED_NCCL();
     WRK_CUDA(cudaSetDevice(ctx->device));
+    // In-switch reduction binds every rank's buffers to one NVLink multicast object; a rank that dies while
+    // bound faults its peers' GPUs.  Ranks of this library may leave (teardown is a local abort), so the
+    // multicast path stays off unless the embedder has set the variable itself.
+    setenv("NCCL_NVLS_ENABLE", "0", 0);
     ncclUniqueId uid;
     std::memcpy(&uid, id, sizeof uid);
     ncclComm_t comm = nullptr;
@@ -130,8 +145,10 @@ int32_t wrk_op_all_reduce(wrk_comm* comm, wrk_tensor* x, wrk_op** out) {
     void* ptr = x->ptr();
     const size_t count = x->len();
     ncclComm_t c = comm->comm;
+    auto hold = std::make_shared<CommHold>(comm);
     *out = wrk::new_atom("all_reduce",
                          [=](cudaStream_t s) {
+                             (void)hold;
                              return nccl().AllReduce(ptr, ptr, count, dt, ncclSum, c, s) == ncclSuccess ? cudaSuccess : cudaErrorUnknown;
                          },
                          {x});
@@ -151,8 +168,10 @@ int32_t wrk_op_all_gather(wrk_comm* comm, wrk_tensor* input, wrk_tensor* output,
     void* dst = output->ptr();
     const size_t count = input->len();
     ncclComm_t c = comm->comm;
+    auto hold = std::make_shared<CommHold>(comm);
     *out = wrk::new_atom("all_gather",
                          [=](cudaStream_t s) {
+                             (void)hold;
                              return nccl().AllGather(src, dst, count, dt, c, s) == ncclSuccess ? cudaSuccess : cudaErrorUnknown;
                          },
                          {input, output});

@@ -69,6 +69,9 @@ struct Buffer {
     wrk_context* ctx = nullptr;
     void* ptr = nullptr;
     size_t bytes = 0;
+    explicit Buffer(wrk_context* owner);
+    Buffer(const Buffer&) = delete;
+    Buffer& operator=(const Buffer&) = delete;
     ~Buffer();
 };
 
@@ -84,6 +87,9 @@ using Launch = std::function<cudaError_t(cudaStream_t)>;
 }  // namespace wrk
 
 struct wrk_context {
+    // One reference for the owner (dropped by wrk_context_destroy) and one per live device buffer: the stream
+    // and the device outlive every tensor, op and command buffer that still holds memory of this context.
+    std::atomic<int> refs{1};
     int device = 0;
     cudaStream_t stream = nullptr;
     cudaEvent_t ev_start = nullptr, ev_stop = nullptr;

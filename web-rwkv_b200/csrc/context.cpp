@@ -22,11 +22,27 @@ int32_t set_error(int32_t code, const char* fmt, ...) {
     return code;
 }
 
+// Tears the context down when its last reference (owner or buffer) goes.
+static void context_unref(wrk_context* ctx) {
+    if (ctx->refs.fetch_sub(1) != 1) return;
+    cudaSetDevice(ctx->device);
+    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
+    if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
+    if (ctx->device_status) cudaFree(ctx->device_status);
+    if (ctx->host_status) cudaFreeHost(ctx->host_status);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+Buffer::Buffer(wrk_context* owner) : ctx(owner) { ctx->refs.fetch_add(1); }
+
 Buffer::~Buffer() {
     if (ptr) {
         cudaSetDevice(ctx->device);
         cudaFreeAsync(ptr, ctx->stream);
     }
+    context_unref(ctx);
 }
 
 DView make_dview(const wrk_tensor* t) {
@@ -78,8 +94,7 @@ int32_t tensor_alloc(wrk_context* ctx, int dtype, const uint32_t shape[4], bool 
     t->ctx = ctx;
     t->dtype = dtype;
     for (int i = 0; i < 4; ++i) t->shape.v[i] = shape[i];
-    auto buf = std::make_shared<Buffer>();
-    buf->ctx = ctx;
+    auto buf = std::make_shared<Buffer>(ctx);
     buf->bytes = t->bytes();
     const size_t alloc = buf->bytes ? (buf->bytes + 255) / 256 * 256 : 256;
     cudaError_t e = cudaMallocAsync(&buf->ptr, alloc, ctx->stream);
@@ -152,31 +167,35 @@ int32_t wrk_context_create(int32_t device, wrk_context** out) {
     auto ctx = new wrk_context();
     ctx->device = device;
     ctx->num_sms = prop.multiProcessorCount;
-    WRK_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
-    WRK_CUDA(cudaEventCreate(&ctx->ev_start));
-    WRK_CUDA(cudaEventCreate(&ctx->ev_stop));
-    WRK_CUDA(cudaMalloc(&ctx->device_status, sizeof(int32_t)));
-    WRK_CUDA(cudaMemset(ctx->device_status, 0, sizeof(int32_t)));
-    WRK_CUDA(cudaMallocHost(&ctx->host_status, sizeof(int32_t)));
-    // keep freed device memory in the pool instead of returning it to the driver on every sync
-    cudaMemPool_t pool;
-    WRK_CUDA(cudaDeviceGetDefaultMemPool(&pool, device));
-    uint64_t threshold = UINT64_MAX;
-    WRK_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &threshold));
+    const int32_t status = [&]() -> int32_t {
+        WRK_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+        WRK_CUDA(cudaEventCreate(&ctx->ev_start));
+        WRK_CUDA(cudaEventCreate(&ctx->ev_stop));
+        WRK_CUDA(cudaMalloc(&ctx->device_status, sizeof(int32_t)));
+        WRK_CUDA(cudaMemset(ctx->device_status, 0, sizeof(int32_t)));
+        WRK_CUDA(cudaMallocHost(&ctx->host_status, sizeof(int32_t)));
+        // keep freed device memory in the pool instead of returning it to the driver on every sync
+        cudaMemPool_t pool;
+        WRK_CUDA(cudaDeviceGetDefaultMemPool(&pool, device));
+        uint64_t threshold = UINT64_MAX;
+        WRK_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &threshold));
+        return WRK_OK;
+    }();
+    if (status != WRK_OK) {
+        context_unref(ctx);  // frees whatever was created before the failure
+        return status;
+    }
     *out = ctx;
     return WRK_OK;
 }
 
+// Drops the owner's reference.  Tensors, ops and command buffers released later still find the stream: the
+// context is torn down when the last device buffer that belongs to it has been freed.
 int32_t wrk_context_destroy(wrk_context* ctx) {
     if (!ctx) return WRK_OK;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
-    cudaEventDestroy(ctx->ev_start);
-    cudaEventDestroy(ctx->ev_stop);
-    cudaFree(ctx->device_status);
-    cudaFreeHost(ctx->host_status);
-    cudaStreamDestroy(ctx->stream);
-    delete ctx;
+    context_unref(ctx);
     return WRK_OK;
 }
 
@@ -513,16 +532,3 @@ int32_t wrk_run(wrk_context* ctx, wrk_op* op) {
 }
 
 }  // extern "C"
-
-#ifdef WRK_TRACE
-namespace wrk { namespace k { cudaError_t debug_trace_read(unsigned long long* host, unsigned int* n); } }
-extern "C" int32_t wrk_debug_trace_read(unsigned long long* host, unsigned int* n) {
-    WRK_CUDA(wrk::k::debug_trace_read(host, n));
-    return WRK_OK;
-}
-namespace wrk { namespace k { cudaError_t debug_utrace_read(unsigned long long* host, unsigned int* n); } }
-extern "C" int32_t wrk_debug_utrace_read(unsigned long long* host, unsigned int* n) {
-    WRK_CUDA(wrk::k::debug_utrace_read(host, n));
-    return WRK_OK;
-}
-#endif

@@ -39,36 +39,6 @@ __host__ __device__ inline uint32_t sums_floats(uint32_t T, uint32_t kmax) {
     return (T * ((kmax + 127) / 128) + 3) / 4 * 4 + 4;
 }
 
-// Optional stage timestamps (builds with -DWRK_TRACE only): CTA 0 records (stage, globaltimer ns) in
-// shared memory and appends them to a global log when the kernel ends.
-#ifdef WRK_TRACE
-__device__ unsigned long long g_trace[1 << 16];
-__device__ unsigned int g_trace_n;
-__shared__ unsigned long long s_trace[128];
-__shared__ unsigned int s_trace_n;
-__device__ __forceinline__ void trace(int stage) {
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        if (stage % 20 == 0) s_trace_n = 0;
-        if (s_trace_n < 64) {
-            s_trace[2 * s_trace_n] = (unsigned long long)stage;
-            s_trace[2 * s_trace_n + 1] = t;
-            ++s_trace_n;
-        }
-        if (stage % 20 == 7) {
-            const unsigned int base = atomicAdd(&g_trace_n, s_trace_n);
-            for (unsigned int i = 0; i < s_trace_n && base + i < (1u << 15); ++i) {
-                g_trace[2 * (base + i)] = s_trace[2 * i];
-                g_trace[2 * (base + i) + 1] = s_trace[2 * i + 1];
-            }
-        }
-    }
-}
-#else
-__device__ __forceinline__ void trace(int) {}
-#endif
-
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
@@ -540,7 +510,6 @@ __global__ void __launch_bounds__(kThreads, WRK_GEMV_MIN_CTAS) fused_gemv_kernel
         const __half2 v = __floats2half2_rn(a.table[threadIdx.x & 15], a.table[threadIdx.x >> 4]);
         lut2[threadIdx.x] = *reinterpret_cast<const uint32_t*>(&v);
     }
-    trace(100);
     pdl_launch_dependents();
 
     // ---- everything up to the wait touches only weights: each warp fetches its first items ----
@@ -585,34 +554,17 @@ __global__ void __launch_bounds__(kThreads, WRK_GEMV_MIN_CTAS) fused_gemv_kernel
     ld.seg = 0;
     ld.enter(a, sg, warp, lane);
     int cs_slot = 0;
-#ifdef WRK_TRACE
-    // cycle accounting of warps 0 and 7 of CTA 0: clk_acc[i] = cycles between stamps i - 1 and i
-    long long clk_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}, clk_last = 0;
-#define WRK_CLK(i)                                                             \
-    do {                                                                       \
-        long long now_;                                                        \
-        asm volatile("mov.u64 %0, %%clock64;" : "=l"(now_)::"memory");          \
-        if (i == 0) clk_acc[0] += 1;                                           \
-        else clk_acc[i] += now_ - clk_last;                                    \
-        clk_last = now_;                                                       \
-    } while (0)
-#else
-#define WRK_CLK(i)
-#endif
 #pragma unroll 1
     for (int d = 0; d < depth; ++d) {
         ld.issue(a, sg, ring + d * CELL_BYTES, warp, lane);
         cp_async_commit();  // one group per cell, empty or not
     }
-    trace(101);
     pdl_wait();
-    trace(102);
 
     if (PRO != PRO_NONE && pro) {
         cp_async_wait_dyn(depth);  // this thread's parameter copies (it is their only reader)
         run_prologue<PRO>(a, xgen, xp, lnrow, pbias, scratch);
     }
-    trace(103);
 
     int staged_problem = -1;
     const int last_seg = sg.r0[2] < sg.r1[2] ? 2 : sg.r0[1] < sg.r1[1] ? 1 : 0;
@@ -677,13 +629,11 @@ __global__ void __launch_bounds__(kThreads, WRK_GEMV_MIN_CTAS) fused_gemv_kernel
                 }
             }
             __syncthreads();
-            trace(110);
             staged_problem = problem;
         }
         const bool xval = (uint32_t)g < T;
         const __half* xrow = xv + (size_t)(xval ? g : 0) * xp;
         const int nchunk = (int)((row_bytes(p) + CHUNK_BYTES - 1) / CHUNK_BYTES);
-        trace(104);
 
 #pragma unroll 1
         for (int group0 = r0; group0 < r1; group0 += GROUP_ROWS) {
@@ -700,23 +650,18 @@ __global__ void __launch_bounds__(kThreads, WRK_GEMV_MIN_CTAS) fused_gemv_kernel
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
                 for (int c = warp; c < nchunk; c += kWarps) {
-                    WRK_CLK(0);
                     cp_async_wait_dyn(depth - 1);  // this lane's copies of the oldest item in flight have landed
                     __syncwarp();                  // ... and so have the other lanes' (the rows' block scales)
-                    WRK_CLK(1);
                     uint8_t* cell = ring + cs_slot * CELL_BYTES;
                     const Item it = read_item(cell, lane);
                     __syncwarp();  // every lane has read the cell: refill it with the item `depth` steps ahead
-                    WRK_CLK(2);
                     ld.issue(a, sg, cell, warp, lane);
                     cp_async_commit();
                     if (++cs_slot == depth) cs_slot = 0;
-                    WRK_CLK(3);
                     float out[4];
                     consume_item(p, it, c, xrow, xval, sums, T, t4, lut2, out);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) acc[e] += out[e];
-                    WRK_CLK(4);
                 }
                 // this warp's partial results of the tile's 16 rows
                 const uint32_t tk0 = 2 * t4, tk1 = tk0 + 1;
@@ -730,11 +675,7 @@ __global__ void __launch_bounds__(kThreads, WRK_GEMV_MIN_CTAS) fused_gemv_kernel
                     dst[(g + 8) * T + tk1] = acc[3];
                 }
             }
-            WRK_CLK(5);
-            trace(108);
             __syncthreads();
-            trace(109);
-            WRK_CLK(6);
             // the 16 warps' partial results are summed in warp order (deterministic)
             if (has_out) {
                 const float* src = part + threadIdx.x;
@@ -744,41 +685,15 @@ __global__ void __launch_bounds__(kThreads, WRK_GEMV_MIN_CTAS) fused_gemv_kernel
                 epilogue_one<EPI>(a, p, (uint32_t)(group0 + orow), otok, s, eo);
             }
             if (group0 + GROUP_ROWS < r1 || seg < last_seg) __syncthreads();  // the slabs are written again
-            WRK_CLK(7);
-        }
-        trace(105);
-    }
-#ifdef WRK_TRACE
-    if (blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 7)) {
-        const unsigned int base = atomicAdd(&g_trace_n, 8u);
-        for (int k2 = 0; k2 < 8; ++k2) {
-            g_trace[2 * (base + k2)] = 200 + warp * 8 + k2;
-            g_trace[2 * (base + k2) + 1] = (unsigned long long)clk_acc[k2];
         }
     }
-#endif
-    trace(107);
 }
-
-#ifdef WRK_TRACE
-}  // namespace
-cudaError_t debug_trace_read(unsigned long long* host, unsigned int* n) {
-    cudaError_t e = cudaMemcpyFromSymbol(n, g_trace_n, sizeof(unsigned int));
-    if (e != cudaSuccess) return e;
-    e = cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * (1 << 16));
-    unsigned int zero = 0;
-    cudaMemcpyToSymbol(g_trace_n, &zero, sizeof zero);
-    return e;
-}
-namespace {
-#endif
 
 
 // ---- v6 data-dependent token shift ---------------------------------------------------------------
 // sx[i][t][c] = mix(att_x[t][c], prev[t][c], f16(f16(W2[i][c][:] . tmx[t][i*D:(i+1)*D]) + mix[i][c]))
 __global__ void __launch_bounds__(256) tmix_shift_kernel(const TmixArgs a) {
     extern __shared__ __half s_tmx[];  // [T][5 * D]
-    trace(120);
     pdl_launch_dependents();
     const uint32_t C = a.C, D = a.D, T = a.T;
     // the adapter weights of this thread do not depend on earlier kernels
@@ -794,16 +709,13 @@ __global__ void __launch_bounds__(256) tmix_shift_kernel(const TmixArgs a) {
             if (j < D / 8) wreg[j] = wp[j];
         mu = __half2float(a.mix[(size_t)i * C + c]);
     }
-    trace(121);
     pdl_wait();
-    trace(122);
     // every input of token 0 goes in flight before the first barrier: one memory round trip, not four
     for (uint32_t j = threadIdx.x; j < T * 5 * D; j += blockDim.x) s_tmx[j] = a.tmx[j];
     const CursorD cu0 = cursor_at(a.cursors, a.wide, 0);
     const float cur0 = active ? __half2float(a.att_x[c]) : 0.f;
     const float prev0 = (active && cu0.token == 0) ? static_cast<const float*>(a.state.base)[a.state.index(c, 0, cu0.batch)] : 0.f;
     __syncthreads();
-    trace(123);
     if (!active) return;
     for (uint32_t t = 0; t < T; ++t) {
         float acc = 0.f;
@@ -833,7 +745,6 @@ __global__ void __launch_bounds__(256) tmix_shift_kernel(const TmixArgs a) {
         }
         a.sx[((size_t)i * T + t) * C + c] = __float2half_rn(cur * (1.0f - f) + prev * f);
     }
-    trace(127);
 }
 
 // ---- v5 / v6 time-mix block: decay adapter, WKV, group norm, gate --------------------------------
@@ -845,7 +756,6 @@ __global__ void __launch_bounds__(4 * S) wkv56_fused_kernel(const Wkv6Args a) {
     __shared__ float sk[S], sr[S], sw[S], su[S], part[Q][S], red[Q * S / 32];
     __shared__ __half s_tdw[128];
     __shared__ uint32_t s_start, s_count;
-    trace(140);
     pdl_launch_dependents();
     const uint32_t h = blockIdx.x, slot = blockIdx.y, j = threadIdx.x % S, q = threadIdx.x / S;
     const uint32_t C = S * a.H, c = h * S + j;
@@ -870,9 +780,7 @@ __global__ void __launch_bounds__(4 * S) wkv56_fused_kernel(const Wkv6Args a) {
     float st[SI];
 #pragma unroll
     for (int i = 0; i < SI; ++i) st[i] = static_cast<const float*>(a.state.base)[a.state.index(c, 1 + q * SI + i, slot)];
-    trace(141);
     pdl_wait();  // the token's k, v, r, g and adapter activations come from the kernels before this one
-    trace(142);
 
     // run of tokens of this batch slot
     uint32_t start, count;
@@ -913,7 +821,6 @@ __global__ void __launch_bounds__(4 * S) wkv56_fused_kernel(const Wkv6Args a) {
         if (a.per_token_decay && threadIdx.x < a.D) tdh = a.tdw[(size_t)t * a.D + threadIdx.x];
         const CursorD cu = cursor_at(a.cursors, a.wide, t);
         __syncthreads();  // the previous token's readers are done
-        trace(143);
         if (q == 0) {
             sk[j] = kj;
             sr[j] = rj;
@@ -950,7 +857,6 @@ __global__ void __launch_bounds__(4 * S) wkv56_fused_kernel(const Wkv6Args a) {
             kv = sk[i] * vj;     y0 += sr[i] * fmaf(su[i], kv, st[ii]);             st[ii] = fmaf(sw[i], st[ii], kv);
             kv = sk[i + 1] * vj; y1 += sr[i + 1] * fmaf(su[i + 1], kv, st[ii + 1]); st[ii + 1] = fmaf(sw[i + 1], st[ii + 1], kv);
         }
-        trace(144);
         part[q][j] = y0 + y1;
         if (q == 0 && t - cu.token + 1u == cu.len) static_cast<float*>(a.state.base)[a.state.index(c, 0, slot)] = ax;
         __syncthreads();
@@ -975,11 +881,9 @@ __global__ void __launch_bounds__(4 * S) wkv56_fused_kernel(const Wkv6Args a) {
         const float gn16 = __half2float(__float2half_rn(fmaf(dlt * dev, gw, gb)));
         const float silu = gg / (1.0f + expf(-gg));
         if (q == 0) a.out[ti] = __float2half_rn(silu * gn16);
-        trace(145);
     }
 #pragma unroll
     for (int i = 0; i < SI; ++i) static_cast<float*>(a.state.base)[a.state.index(c, 1 + q * SI + i, slot)] = st[i];
-    trace(147);
 }
 
 template <typename Kernel, typename Args>
@@ -1130,15 +1034,8 @@ size_t fused_gemv_prepare(FusedGemvArgs& a) {
 
 template <int PRO, int EPI>
 cudaError_t launch_fused_gemv(const FusedGemvArgs& a, int grid, size_t smem, cudaStream_t stream, bool pdl) {
-    static bool configured[kStaticGemvMaxDevices] = {};
-    int device = 0;
-    cudaError_t e = cudaGetDevice(&device);
-    if (e != cudaSuccess) return e;
-    if (device < kStaticGemvMaxDevices && !configured[device]) {
-        e = cudaFuncSetAttribute(fused_gemv_kernel<PRO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e != cudaSuccess) return e;
-        configured[device] = true;
-    }
+    static SmemOptIn opt_in;  // one per instantiation
+    if (cudaError_t e = opt_in.ensure(fused_gemv_kernel<PRO, EPI>, 200 * 1024); e != cudaSuccess) return e;
     if (pdl) return launch_pdl(fused_gemv_kernel<PRO, EPI>, dim3(grid), dim3(kThreads), smem, stream, a);
     fused_gemv_kernel<PRO, EPI><<<grid, kThreads, smem, stream>>>(a);
     return cudaGetLastError();
@@ -1213,7 +1110,7 @@ __global__ void static_partition_kernel(GemvSegment* table, uint32_t K, uint32_t
 struct StaticSetup {
     GemvSegment* table = nullptr;
     int sms = 0;
-    bool ready = false;
+    std::atomic<bool> ready{false};
 };
 StaticSetup g_static_setup[kStaticGemvMaxDevices];
 std::mutex g_static_mutex;
@@ -1228,16 +1125,16 @@ int gemv_int8_static(int device, cudaStream_t stream, const uint8_t* w, const __
     if ((*cuda_error = cudaGetDevice(&current)) != cudaSuccess) return SG_CUDA;
     if (current != device) return SG_BAD_DEVICE;
     StaticSetup& su = g_static_setup[device];
-    {
-        // first call on this device: the array's address and the SM count
+    if (!su.ready.load(std::memory_order_acquire)) {
+        // first call on this device: the array's address and the SM count (later calls take no lock)
         std::lock_guard<std::mutex> lock(g_static_mutex);
-        if (!su.ready) {
+        if (!su.ready.load(std::memory_order_relaxed)) {
             void* ptr = nullptr;
             if ((*cuda_error = cudaGetSymbolAddress(&ptr, g_static_segments)) != cudaSuccess) return SG_CUDA;
             if ((*cuda_error = cudaDeviceGetAttribute(&su.sms, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess)
                 return SG_CUDA;
             su.table = static_cast<GemvSegment*>(ptr);
-            su.ready = true;
+            su.ready.store(true, std::memory_order_release);
         }
     }
     if (K == 0 || M == 0 || K % 128 != 0 || T == 0 || T > (uint32_t)kDecodeMaxTokens || M > 0x7fffffffu) return SG_BAD_SHAPE;

@@ -166,28 +166,6 @@ __device__ __forceinline__ float4 ld_peer_smem(uint32_t local_addr, uint32_t ran
 
 __device__ __forceinline__ uint32_t pack_half2(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
 
-// Optional timeline (builds with -DWRK_TRACE only): CTA (0, 0, 0) appends (stamp id, globaltimer ns) pairs to a
-// global log that the host reads back.
-#ifdef WRK_TRACE
-__device__ unsigned long long g_utrace[1 << 14];
-__device__ unsigned int g_utrace_n;
-__device__ __forceinline__ void utrace(uint32_t id) {
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        const unsigned int i = atomicAdd(&g_utrace_n, 1u);
-        if (i < (1u << 13)) {
-            g_utrace[2 * i] = id;
-            g_utrace[2 * i + 1] = t;
-        }
-    }
-}
-#define UTRACE(id) utrace(id)
-#else
-#define UTRACE(id)
-#endif
-
-
 // 32 (Int8) weights of one row, raw bytes in `q0, q1`, block scale (min, max) -> four 16-byte groups of fp16.
 __device__ __forceinline__ void dequant_int8(uint4 q0, uint4 q1, uint32_t minmax, uint4 out[4]) {
     // f32 dequantization, one rounding to fp16 per weight: the errors of a row are independent, none is
@@ -247,7 +225,6 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
     const uint32_t k_begin = (uint32_t)((uint64_t)nk_all * blockIdx.z / p.splits);
     const uint32_t nk = (uint32_t)((uint64_t)nk_all * (blockIdx.z + 1) / p.splits) - k_begin;
 
-    if (threadIdx.x == 0) UTRACE(1);
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.stages; ++s) {
             mbar_init(&ab_full[s], quantized ? kDequantWarps / 2 + 1 : 2);  // one dequant group (or the weight TMA) + activation TMA
@@ -271,7 +248,6 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_d = tmem_base_slot;
-    if (threadIdx.x == 0) UTRACE(2);
 
     if (warp < kDequantWarps) {
         if (quantized) {
@@ -292,7 +268,6 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
                 asm volatile("cp.async.wait_group 1;\n" ::: "memory");
                 const uint8_t* ss = my_scale + (j & 1) * SCALE_SLOT_BYTES;
                 const uint32_t kt0 = 4 * j + 2 * group;
-                if (threadIdx.x == 0 && (j == 0 || j + 1 == nsuper)) UTRACE(1000 + kt0);
 #pragma unroll
                 for (uint32_t d = 0; d < 2; ++d) {
                     const uint32_t kt = kt0 + d;
@@ -322,13 +297,11 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
                     if (kt0 < nk) mbar_arrive(&ab_full[kt0 % p.stages]);
                     if (kt0 + 1 < nk) mbar_arrive(&ab_full[(kt0 + 1) % p.stages]);
                 }
-                if (threadIdx.x == 0 && (j == 0 || j + 1 == nsuper)) UTRACE(2000 + kt0);
             }
         }
         // ---- epilogue: TMEM -> registers -> activation -> token-major rows ----
         mbar_wait(&done_bar, 0, &abort_flag, p.status);
         tc_fence_after();
-        if (threadIdx.x == 0) UTRACE(3);
         const uint32_t quad = warp & 3, side = warp >> 2;  // lanes 32 quad .., half of the columns each
         const uint32_t m = m0 + quad * 32 + lane;
         const uint32_t c_begin = side * (p.n_tile / 2), c_end = c_begin + p.n_tile / 2;
@@ -359,7 +332,6 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
                 }
             }
         }
-        if (threadIdx.x == 0) UTRACE(4);
     } else if (warp == kMmaWarp) {
         // ---- MMA issuer ----
         const uint32_t idesc = f16_idesc(BM, p.n_tile);
@@ -367,7 +339,6 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
             const uint32_t s = kt % p.stages, use = kt / p.stages;
             mbar_wait(&ab_full[s], use & 1, &abort_flag, p.status);
             tc_fence_after();
-            if (lane == 0 && (kt == 0 || kt + 1 == nk)) UTRACE(3000 + kt);
             if (lane == 0) {
                 const uint32_t sa = smem_addr(smem + (size_t)s * stage_bytes);
                 const uint64_t da = sw128_desc(sa), db = sw128_desc(sa + A_STAGE_BYTES);
@@ -414,7 +385,6 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_d), "r"(p.tmem_cols) : "memory");
     }
-    if (threadIdx.x == 0) UTRACE(5);
     if (p.splits > 1) {
         // The CTAs of a cluster hold the partial tiles of one output tile.  After the cluster barrier CTA r adds
         // its share of the columns over all peers (in rank order: the sum does not depend on timing), through
@@ -422,7 +392,6 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
         // memory alive until its peers have read it.  Both are hardware barriers that every thread reaches, also
         // after a wait above has given up.
         cluster_sync();
-        if (threadIdx.x == 0) UTRACE(8);
         const uint32_t rank = cluster_rank();
         {
             constexpr uint32_t kGroups = 4, kReduceThreads = kUmmaThreads;
@@ -466,14 +435,13 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
         }
         cluster_sync();
     }
-    if (threadIdx.x == 0) UTRACE(7);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// cuTensorMapEncodeTiled through the runtime's driver entry-point lookup (no link against libcuda).
+// cuTensorMapEncodeTiled through the runtime's driver entry-point lookup: the library does not link libcuda.
 EncodeTiledFn encode_tiled() {
     static EncodeTiledFn fn = nullptr;
     if (fn == nullptr) {
@@ -499,17 +467,6 @@ bool make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uin
 }
 
 }  // namespace
-
-#ifdef WRK_TRACE
-cudaError_t debug_utrace_read(unsigned long long* host, unsigned int* n) {
-    cudaError_t e = cudaMemcpyFromSymbol(n, g_utrace_n, sizeof(unsigned int));
-    if (e != cudaSuccess) return e;
-    e = cudaMemcpyFromSymbol(host, g_utrace, sizeof(unsigned long long) * (1 << 14));
-    unsigned int zero = 0;
-    cudaMemcpyToSymbol(g_utrace_n, &zero, sizeof zero);
-    return e;
-}
-#endif
 
 bool matmul_umma_supported(const MatmulArgs& a) {
     if (a.B != 1 || a.N < 16 || a.M == 0) return false;
@@ -586,12 +543,8 @@ cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t strea
                            CU_TENSOR_MAP_SWIZZLE_128B);
     if (!ok) return cudaErrorInvalidValue;
 
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(matmul_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static SmemOptIn opt_in;
+    if (cudaError_t e = opt_in.ensure(matmul_umma_kernel, 208 * 1024); e != cudaSuccess) return e;
     dim3 grid((a.M + BM - 1) / BM, (a.N + p.n_tile - 1) / p.n_tile, 1);
     grid.z = p.splits;
     if (p.splits > 1) {

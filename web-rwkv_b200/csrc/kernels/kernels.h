@@ -8,6 +8,24 @@ namespace k {
 
 enum MatKind { MAT_FP16 = 0, MAT_INT8 = 1, MAT_NF4 = 2 };
 
+// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to a (kernel, device) pair: one of these per kernel,
+// asked before every launch, opts the current device in the first time it is seen there.  Devices past the
+// mask's width are opted in on every launch (the call is idempotent).
+struct SmemOptIn {
+    std::atomic<uint64_t> devices{0};
+    template <typename Kernel>
+    cudaError_t ensure(Kernel kernel, int bytes) {
+        int device = 0;
+        cudaError_t e = cudaGetDevice(&device);
+        if (e != cudaSuccess) return e;
+        const uint64_t bit = device >= 0 && device < 64 ? 1ull << device : 0;
+        if (bit != 0 && (devices.load(std::memory_order_acquire) & bit) != 0) return cudaSuccess;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e == cudaSuccess && bit != 0) devices.fetch_or(bit, std::memory_order_release);
+        return e;
+    }
+};
+
 // ---- quantizers (quant.cu) -------------------------------------------------------------
 cudaError_t quantize_int8(const __half* input, size_t len, __half* minmax, uint8_t* output, int num_sms,
                           cudaStream_t stream);

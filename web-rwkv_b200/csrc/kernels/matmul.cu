@@ -338,13 +338,8 @@ template <int KIND, int NT>
 cudaError_t launch_mma(const MmParams& p, uint32_t B, cudaStream_t stream) {
     const size_t smem = (size_t)p.ntok * p.xstride * sizeof(__half) + (size_t)p.ntok * (p.KS / 128) * sizeof(float) +
                         (size_t)kWarps * kRows * 8 * NT * sizeof(float);
-    static bool configured = false;  // per instantiation; benign race (idempotent call)
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(matmul_mma_kernel<KIND, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             160 * 1024);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static SmemOptIn opt_in;  // one per instantiation
+    if (cudaError_t e = opt_in.ensure(matmul_mma_kernel<KIND, NT>, 160 * 1024); e != cudaSuccess) return e;
     dim3 grid((p.M + kRows - 1) / kRows, (p.N + 8 * NT - 1) / (8 * NT), B);
     matmul_mma_kernel<KIND, NT><<<grid, kThreads, smem, stream>>>(p);
     return cudaGetLastError();

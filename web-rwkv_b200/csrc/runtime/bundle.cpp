@@ -67,6 +67,7 @@ struct wrk_job {
     wrk_bundle* bundle = nullptr;
     std::shared_ptr<CachedJob> job;
     RnnInfo info;
+    RnnRedirect redirect;  // this dispatch's per-batch output ranges (jobs of one structure share a CachedJob)
 };
 
 namespace {
@@ -873,7 +874,7 @@ int32_t wrk_bundle_dispatch(wrk_bundle* b, const uint32_t* lens, const int32_t* 
         b->jobs[key] = cj;
     }
     cj->tick = ++b->tick;
-    cj->redirect = rd;  // per-batch ranges differ between jobs that share a structure
+    job->redirect = std::move(rd);  // per-batch ranges differ between jobs that share a structure
     job->job = cj;
     *out = job;
     return WRK_OK;
@@ -980,8 +981,8 @@ int32_t wrk_job_back(wrk_job* job, float* logits, size_t capacity, uint32_t* out
     if (num_headers) *num_headers = cj.num_header;
     if (outputs)
         for (uint32_t i = 0; i < b->num_batch; ++i) {
-            outputs[2 * i] = cj.redirect.outputs[i].first;
-            outputs[2 * i + 1] = cj.redirect.outputs[i].second;
+            outputs[2 * i] = job->redirect.outputs[i].first;
+            outputs[2 * i + 1] = job->redirect.outputs[i].second;
         }
     if (cj.num_token == 0 || cj.num_header == 0) {
         WRK_CUDA(cudaStreamSynchronize(ctx->stream));

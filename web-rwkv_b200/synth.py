@@ -109,15 +109,28 @@ def make_globals(version, C, V, seed):
     }
 
 
-def iter_tensors(config, seed=1000, num_layer=None):
-    """Yields (name, fp16 array) for a whole model, one block at a time (bounded host memory)."""
+def iter_tensors(config, seed=1000, num_layer=None, workers=None):
+    """Yields (name, fp16 array) for a whole model, one block at a time (bounded host memory).  Blocks are
+    generated by a few threads ahead of the consumer (each has its own seeded generator, so the result does not
+    depend on the thread count)."""
+    import os
+    from concurrent.futures import ThreadPoolExecutor
     version, C, L, F, V = CONFIGS[config] if isinstance(config, str) else config
     L = num_layer or L
-    for name, arr in make_globals(version, C, V, seed).items():
-        yield name, arr
-    for layer in range(L):
-        for name, arr in make_layer(version, layer, C, F, seed).items():
+    if workers is None:
+        workers = max(1, min(16, len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else 4))
+    with ThreadPoolExecutor(workers) as pool:
+        head = pool.submit(make_globals, version, C, V, seed)
+        pending = [pool.submit(make_layer, version, layer, C, F, seed) for layer in range(min(L, workers))]
+        for name, arr in head.result().items():
             yield name, arr
+        for layer in range(L):
+            block = pending.pop(0).result()
+            nxt = layer + workers
+            if nxt < L:
+                pending.append(pool.submit(make_layer, version, nxt, C, F, seed))
+            for name, arr in block.items():
+                yield name, arr
 
 
 def make_model(config, seed=1000, num_layer=None):
