@@ -8,6 +8,7 @@ import numpy as np
 import pytest
 
 from oracle import oracle
+from tests.golden import reference_answers as ra
 from tests.util import assert_close, is_approx_eps
 
 pytestmark = pytest.mark.gpu
@@ -77,6 +78,44 @@ def test_reference_test_shapes(wrk, ctx, kind, c, r, t):
             # near-zero outputs of this +-5 data does not admit (an fp16 output of this size has a spacing of
             # 0.25 itself); instead the error is bounded at 0.5% of the output rms.
             assert np.max(np.abs(got - want)) <= 5e-3 * scale, f"{kind} turbo={turbo}"
+
+
+# Share of outputs that must pass the reference tests' own comparison, is_approx_eps(computed, answer, 0.01), with
+# the answer computed by the restated host code of those tests (tests/golden/reference_answers.py).  The Int8
+# decode kernel keeps the bytes exact (1024 + q in fp16, affine term applied in f32) and passes it outright.  The
+# token-batched Int8 kernel and both NF4 kernels hand the tensor cores weights rounded to fp16 (relative error
+# 2^-11 each); on this +-5 data that leaves the outputs that happen to land within 0.01..0.4 of zero outside the
+# absolute half of the criterion: 1.3 % of them for Int8 at K = 2560, 0.3 % for NF4 (measured on a B200).
+REFERENCE_CRITERION = {("int8", "vec"): 1.0, ("int8", "mat"): 0.98, ("nf4", "vec"): 0.995, ("nf4", "mat"): 0.995}
+
+
+@pytest.mark.parametrize("kind", ["int8", "nf4"])
+@pytest.mark.parametrize("c,r,t", [(2560, 2048, 64), (320, 64, 320)])
+def test_reference_tests_own_criterion_per_kernel(wrk, ctx, kind, c, r, t):
+    if kind == "int8":
+        m, x = ra.int8_inputs(c, r, t)
+        mat = wrk.Matrix.quant_u8(ctx.from_numpy(m))
+        _, wq, mm, _ = mat.parts()
+        q_ans, mn, mx = ra.int8_quantize(m)
+        got_q, got_mm = wq.numpy().reshape(r, c), mm.numpy().reshape(-1, 2)
+        assert (np.abs(got_q.astype(np.int32) - q_ans.astype(np.int32)) < 2).all()
+        assert ra.is_approx_eps(got_mm[:, 0], mn, 0.01).all() and ra.is_approx_eps(got_mm[:, 1], mx, 0.01).all()
+        ans = ra.int8_answer(got_q, mn, mx, x)  # the test multiplies the bytes the shader produced
+    else:
+        m, x = ra.nf4_inputs(c, r, t)
+        mat = wrk.Matrix.quant_nf4(ctx.from_numpy(m))
+        _, wq, am, _ = mat.parts()
+        idx, packed, absmax = ra.nf4_quantize(m)
+        assert np.array_equal(wq.numpy().reshape(packed.shape), packed)
+        assert ra.is_approx_eps(am.numpy().reshape(-1), absmax, 0.01).all()
+        ans = ra.nf4_answer(idx, absmax, x)
+    cases = [("vec", 1, False), ("vec", 8, False), ("mat", t, True)]
+    for form, n, turbo in cases:
+        y = ctx.tensor(wrk.F32, [r, n])
+        ctx.run(mat.matmul_op(ctx.from_numpy(x[:n]), y, turbo=turbo))
+        ok = ra.is_approx_eps(y.numpy().reshape(n, r), ans[:n], 0.01)
+        need = REFERENCE_CRITERION[(kind, form)]
+        assert ok.mean() >= need, f"{kind} {form} n={n}: {ok.mean():.5f} of the outputs pass, {need} required"
 
 
 @pytest.mark.parametrize("kind", KINDS)

@@ -14,7 +14,7 @@ import numpy as np
 import pytest
 
 from oracle import model as omodel
-from tests.util import assert_close
+from tests.util import assert_close, assert_state_close
 
 pytestmark = pytest.mark.gpu
 
@@ -78,8 +78,9 @@ def test_fused_decode_matches_oracle_and_strict_job(ctx, config, seed):
     want = job(rng.integers(0, V - 1, 2).tolist(), FULL, "job of 2 tokens")
     want = job(rng.integers(0, V - 1, 8).tolist(), FULL, "job of 8 tokens")
     got_f, want_s = _state(fused, state)
-    assert_close(got_f, want_s, f"{config} fused state")
-    assert_close(_state(strict, state)[0], want_s, f"{config} strict state")
+    assert_state_close(got_f, want_s, f"{config} fused state")
+    assert_state_close(_state(strict, state)[0], want_s, f"{config} strict state")
+    assert_state_close(got_f, _state(strict, state)[0], f"{config} fused vs strict state")
     assert ctx.device_status() == 0
 
 
@@ -108,7 +109,7 @@ def test_nf4_prefill_chunk_of_256(ctx, packed):
         jobs += 1
     assert jobs == 2
     got_s, want_s = _state(bundle, state)
-    assert_close(got_s, want_s, f"v6-3b NF4 state packed={packed}")
+    assert_state_close(got_s, want_s, f"v6-3b NF4 state packed={packed}")
     assert ctx.device_status() == 0
 
 
@@ -152,5 +153,5 @@ def test_v7_batched_decode_of_64_sequences(ctx):
         assert drain(f"decode {step}") == 1
     for b in (0, 17, 63):
         got_s, want_s = _state(bundle, state, b)
-        assert_close(got_s, want_s, f"v7 state batch {b}")
+        assert_state_close(got_s, want_s, f"v7 state batch {b}")
     assert ctx.device_status() == 0
