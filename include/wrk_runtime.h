@@ -79,9 +79,18 @@ int32_t wrk_bundle_release(wrk_bundle* b);
 int32_t wrk_bundle_set_packed_cursors(wrk_bundle* b, int32_t packed);
 /* Build jobs as CUDA graphs (default 1) or as plain launch lists (0). */
 int32_t wrk_bundle_set_use_graph(wrk_bundle* b, int32_t use_graph);
-/* 1 (default): jobs may use fused kernels in place of runs of reference ops; 0: one launch per
- * reference op, every intermediate tensor materialised with the reference's dtypes. */
+/* 1 (default): jobs may use fused kernels in place of runs of reference ops, and a v6 job of at most 8 tokens
+ * runs as one persistent kernel (all layers and the head; the CTAs meet at a grid barrier between phases);
+ * 2: the same fused kernels, one launch per phase; 0: one launch per reference op, every intermediate tensor
+ * materialised with the reference's dtypes. */
 int32_t wrk_bundle_set_fused(wrk_bundle* b, int32_t fused);
+/* No counterpart in the reference (its profiler hooks are wgpu timestamp queries, commented out in
+ * src/tensor/ops.rs:2600).  Makes the persistent decode kernel record the device's nanosecond timer when each CTA
+ * starts (after the grid barrier) and ends every phase; max_phases = 0 switches it off.  Jobs built afterwards with
+ * at most max_phases phases record; wrk_job_phase_timeline copies the stamps of the job's last run to the host
+ * as [2 * num_phases][num_ctas] u64 (phase start rows even, phase end rows odd). */
+int32_t wrk_bundle_set_phase_timeline(wrk_bundle* b, uint32_t max_phases);
+int32_t wrk_job_phase_timeline(wrk_job* job, uint64_t* stamps, size_t capacity, uint32_t* num_phases, uint32_t* num_ctas);
 int32_t wrk_state_num_batch(wrk_bundle* b, uint32_t* num_batch);                 /* State::num_batch */
 int32_t wrk_state_init_shape(wrk_bundle* b, uint32_t shape[4]);                  /* State::init_shape */
 int32_t wrk_state_load(wrk_bundle* b, const float* host, size_t bytes, uint32_t batch); /* State::load */

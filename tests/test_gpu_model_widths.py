@@ -49,31 +49,35 @@ def test_fused_decode_matches_oracle_and_strict_job(ctx, config, seed):
     model, ref = _models(ctx, cfg, INT8, seed)
     rng = np.random.default_rng(seed + 1000)
     prompt = rng.integers(0, V - 1, 64).tolist()
-    fused, strict = rt.Bundle(model, 1), rt.Bundle(model, 1)
-    strict.set_fused(False)
+    fused, phased, strict = rt.Bundle(model, 1), rt.Bundle(model, 1), rt.Bundle(model, 1)
+    phased.set_fused(2)  # the same fused kernels, one launch per phase
+    strict.set_fused(0)
+    bundles = (fused, phased, strict)
     state = ref.init_state(1)
 
     def job(tokens, option, what):
         rows = len(tokens) if option == FULL else 1
         want = ref.run(state, [tokens], [(len(tokens), option)])[0]
         got = []
-        for bundle in (fused, strict):
+        for bundle in bundles:
             inp = bundle.pending
             inp.append(0, tokens)
             got.append(bundle.infer(inp)[0].copy())
             assert inp.num_token() == 0
         assert got[0].shape == want.shape == (rows, V)
         assert_close(got[0], want, f"{config} fused {what}")
-        assert_close(got[1], want, f"{config} strict {what}")
-        assert_close(got[0], got[1], f"{config} fused vs strict {what}")
+        assert_close(got[1], want, f"{config} fused, launch per phase, {what}")
+        assert_close(got[2], want, f"{config} strict {what}")
+        assert_close(got[0], got[2], f"{config} fused vs strict {what}")
+        assert_close(got[0], got[1], f"{config} one kernel vs launch per phase {what}")
         return want
 
-    for bundle in (fused, strict):
+    for bundle in bundles:
         bundle.pending = rt.RnnInput([([], LAST)], 64)
     want = job(prompt, LAST, "prompt")
     for step in range(8):
         want = job([int(np.argmax(want[-1]))], LAST, f"decode {step}")
-    for bundle in (fused, strict):  # Full: one head row per token of the job
+    for bundle in bundles:  # Full: one head row per token of the job
         bundle.pending = rt.RnnInput([([], FULL)], 32)
     want = job(rng.integers(0, V - 1, 2).tolist(), FULL, "job of 2 tokens")
     want = job(rng.integers(0, V - 1, 8).tolist(), FULL, "job of 8 tokens")
@@ -81,6 +85,7 @@ def test_fused_decode_matches_oracle_and_strict_job(ctx, config, seed):
     assert_state_close(got_f, want_s, f"{config} fused state")
     assert_state_close(_state(strict, state)[0], want_s, f"{config} strict state")
     assert_state_close(got_f, _state(strict, state)[0], f"{config} fused vs strict state")
+    assert_state_close(_state(phased, state)[0], want_s, f"{config} fused, launch per phase, state")
     assert ctx.device_status() == 0
 
 

@@ -23,6 +23,7 @@ SOURCES = [
     "kernels/wkv.cu",
     "kernels/support.cu",
     "kernels/decode.cu",
+    "kernels/decode_step.cu",
     "runtime/rnn.cpp",
     "runtime/model.cpp",
     "runtime/bundle.cpp",

@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(kThreads, WRK_GEMV_MIN_CTAS) fused_gemv_kernel
                     cp_async_commit();
                     if (++cs_slot == depth) cs_slot = 0;
                     float out[4];
-                    consume_item(p, it, c, xrow, xval, sums, T, t4, lut2, out);
+                    consume_item(p.kind, p.K, it, c, xrow, xval, sums, T, t4, lut2, out);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) acc[e] += out[e];
                 }

@@ -34,23 +34,18 @@ struct GemvSegment {
 constexpr int kSegmentsPerCta = 3;
 constexpr int kInlineCtas = 192;
 
-struct FusedGemvArgs {
+// What the device math of a weight-streaming launch (or phase) needs: the matrices, the prologue and the epilogue.
+struct GemvCore {
     GemvProblem p[kMaxProblems];
     int32_t num_problems;
-    int32_t ring_depth;           // staging cells per warp (filled in by fused_gemv)
     uint32_t kmax;                // largest K of the launch (filled in by fused_gemv)
     uint32_t T;
-    const GemvSegment* segments;  // [grid][kSegmentsPerCta], row0 == row1 marks an unused entry
-    // The same partition as boundaries in the concatenated row space of the launch's matrices (filled in by
-    // fused_gemv for grids of at most kInlineCtas): CTA c owns rows [cta_row_start[c], cta_row_start[c + 1]).
-    // Read from the kernel parameters, it spares every CTA a dependent global load before its first copy.
-    int32_t inline_partition;
-    uint32_t cta_row_start[kInlineCtas + 1];
     const float* table;           // NF4 code book (device)
     int32_t* status;
     // prologue: layer norm of `ln_x` (+ token shift against the carry row `state`)
     int32_t prologue;
-    const __half* ln_x;           // [T][C] residual stream
+    const __half* ln_x;           // rows of C fp16; prologue row t reads row t + ln_row_off[t]
+    int32_t ln_row_off[kDecodeMaxTokens];
     const __half* ln_w;
     const __half* ln_b;
     float ln_eps;
@@ -69,6 +64,16 @@ struct FusedGemvArgs {
     const __half* cm_x;           // channel mix: normalised ffn input [T][M] (becomes the carry row)
     DView cm_state;
     float rescale;                // 1.0 or 0.5 applied to the residual stream after the add
+};
+
+struct FusedGemvArgs : GemvCore {
+    int32_t ring_depth;           // staging cells per warp (filled in by fused_gemv)
+    const GemvSegment* segments;  // [grid][kSegmentsPerCta], row0 == row1 marks an unused entry
+    // The same partition as boundaries in the concatenated row space of the launch's matrices (filled in by
+    // fused_gemv for grids of at most kInlineCtas): CTA c owns rows [cta_row_start[c], cta_row_start[c + 1]).
+    // Read from the kernel parameters, it spares every CTA a dependent global load before its first copy.
+    int32_t inline_partition;
+    uint32_t cta_row_start[kInlineCtas + 1];
 };
 
 cudaError_t fused_gemv(const FusedGemvArgs& a, int grid, cudaStream_t stream);
@@ -125,6 +130,53 @@ constexpr int kStaticGemvMaxDevices = 64;
 enum StaticGemvError { SG_OK = 0, SG_TOO_MANY_CTAS = 1, SG_BAD_SHAPE = 2, SG_BAD_DEVICE = 3, SG_CUDA = 4 };
 int gemv_int8_static(int device, cudaStream_t stream, const uint8_t* w, const __half* minmax, const __half* x, float* y,
                      uint32_t K, uint32_t M, uint32_t T, int act, uint32_t num_ctas, cudaError_t* cuda_error);
+
+// ---- the whole decode step in one persistent kernel (decode_step.cu) -----------------------------------
+// A job of a few tokens runs as a list of phases inside one cooperative launch of one CTA per SM; the CTAs meet
+// at a grid-wide barrier between phases.  A CTA's copies of weights run ahead of its math across phase
+// boundaries (weights never change during a job), so the stream of weights does not stop while a barrier, a
+// layer norm or the WKV recurrence is in progress.
+enum StepPhaseType { PH_GEMV = 0, PH_TMIX = 1, PH_WKV = 2 };
+
+struct alignas(16) StepPhase {
+    int32_t type;
+    int32_t gemv_index;  // PH_GEMV: index into the CTA's work list, -1 for a phase without matrices
+    union {
+        GemvCore gemv;
+        TmixArgs tmix;
+        Wkv6Args wkv;
+    };
+};
+static_assert(sizeof(StepPhase) % 16 == 0, "phases are fetched with 16-byte bulk copies");
+
+// One CTA's share of one weight-streaming phase: rows [r0, r1) of one matrix (r0 == r1: none).
+struct StepWork {
+    const uint8_t* w;
+    const __half* scale;
+    int32_t r0, r1;
+    uint32_t K;
+    int16_t kind, problem;
+};
+static_assert(sizeof(StepWork) == 32, "work lists are fetched with 16-byte bulk copies");
+
+struct StepArgs {
+    const StepPhase* phases;
+    int32_t num_phases;
+    const StepWork* work;     // [grid][num_gemv]
+    int32_t num_gemv;
+    uint32_t T;               // tokens of the job (the largest T of any phase)
+    uint32_t kmax;            // largest K of any matrix
+    uint32_t C;
+    int32_t ring_depth;
+    uint32_t x_halfs;         // fp16 elements reserved for staged activations / prologue rows
+    const float* table;       // NF4 code book or null
+    uint32_t* barrier;        // grid barrier counter; the launcher zeroes it on the stream before the kernel
+    int32_t* status;          // device status word: a wait that gives up writes WRK_ERR_TIMEOUT here
+    unsigned long long* timeline;  // optional [2 * num_phases][grid] globaltimer stamps (phase start / end)
+};
+// Shared memory of the step kernel for a job shape, or 0 when it does not fit; fills ring_depth and x_halfs.
+size_t decode_step_prepare(StepArgs& s, bool any_prologue);
+cudaError_t decode_step(const StepArgs& s, int grid, cudaStream_t stream);
 
 }  // namespace k
 }  // namespace wrk

@@ -94,36 +94,30 @@ __device__ __forceinline__ void cp_async_wait_dyn(int n) {
 // shared memory once per tile.  The copy side of a warp walks the same (range, tile, chunk) sequence as its
 // compute side, `depth` items ahead.  Tiles are taken in groups of four: one barrier and one pass of sums
 // and epilogues per 64 rows.
-struct Loader {
-    int seg, row0, r1, c, nchunk;  // seg == kSegmentsPerCta: the CTA's work is exhausted
+struct LoaderCore {
+    int row0, r1, c, nchunk;
     int kind;
     uint32_t rb, srow;             // bytes per weight row / per row of the scale table
     const uint8_t* wbase;          // matrix + this lane's byte offset inside a chunk
     const uint8_t* sbase;          // scale table
 
-    __device__ __forceinline__ bool valid() const { return seg < kSegmentsPerCta; }
-
-    // first range at or after `seg` in which this warp has chunks
-    __device__ __forceinline__ void enter(const FusedGemvArgs& a, const Segs& sg, int warp, int lane) {
-        for (; seg < kSegmentsPerCta; ++seg) {
-            if (sg.R0(seg) >= sg.R1(seg)) continue;
-            const GemvProblem& p = a.p[sg.P(seg)];
-            rb = row_bytes(p);
-            nchunk = (int)((rb + CHUNK_BYTES - 1) / CHUNK_BYTES);
-            if (warp >= nchunk) continue;
-            kind = p.kind;
-            srow = kind == MAT_INT8 ? (p.K / 128) * 4 : kind == MAT_NF4 ? (p.K / 64) * 2 : 0;
-            wbase = p.w + (kind == MAT_NF4 ? 8 : 16) * (lane & 3);
-            sbase = reinterpret_cast<const uint8_t*>(p.scale);
-            row0 = sg.R0(seg);
-            r1 = sg.R1(seg);
-            c = warp;
-            return;
-        }
+    // Points the loader at rows [first, last) of a matrix; false when this warp has no chunk of its rows.
+    __device__ __forceinline__ bool open(int mat_kind, uint32_t K, const uint8_t* w, const __half* scale, int first, int last,
+                                         int warp, int lane) {
+        rb = mat_kind == MAT_FP16 ? K * 2 : mat_kind == MAT_INT8 ? K : K / 2;
+        nchunk = (int)((rb + CHUNK_BYTES - 1) / CHUNK_BYTES);
+        if (warp >= nchunk) return false;
+        kind = mat_kind;
+        srow = kind == MAT_INT8 ? (K / 128) * 4 : kind == MAT_NF4 ? (K / 64) * 2 : 0;
+        wbase = w + (kind == MAT_NF4 ? 8 : 16) * (lane & 3);
+        sbase = reinterpret_cast<const uint8_t*>(scale);
+        row0 = first;
+        r1 = last;
+        c = warp;
+        return true;
     }
-    // Issues the copies of the current item into `cell` (nothing when exhausted) and steps to the next one.
-    __device__ __forceinline__ void issue(const FusedGemvArgs& a, const Segs& sg, uint8_t* cell, int warp, int lane) {
-        if (!valid()) return;
+    // Issues the copies of the current item into `cell` and steps to the next one; true when the range is done.
+    __device__ __forceinline__ bool copy_and_step(uint8_t* cell, int warp, int lane) {
         const int g = lane >> 2, t4 = lane & 3;
         const bool vA = row0 + g < r1, vB = row0 + g + 8 < r1;
         const uint32_t off = (uint32_t)c * CHUNK_BYTES;
@@ -156,10 +150,55 @@ struct Loader {
         if (c >= nchunk) {
             c = warp;
             row0 += 16;
-            if (row0 >= r1) {
-                ++seg;
-                enter(a, sg, warp, lane);
-            }
+            if (row0 >= r1) return true;
+        }
+        return false;
+    }
+};
+
+// The loader of a single launch: walks the CTA's (at most kSegmentsPerCta) row ranges.
+struct Loader : LoaderCore {
+    int seg;  // seg == kSegmentsPerCta: the CTA's work is exhausted
+
+    __device__ __forceinline__ bool valid() const { return seg < kSegmentsPerCta; }
+
+    // first range at or after `seg` in which this warp has chunks
+    __device__ __forceinline__ void enter(const GemvCore& a, const Segs& sg, int warp, int lane) {
+        for (; seg < kSegmentsPerCta; ++seg) {
+            if (sg.R0(seg) >= sg.R1(seg)) continue;
+            const GemvProblem& p = a.p[sg.P(seg)];
+            if (open(p.kind, p.K, p.w, p.scale, sg.R0(seg), sg.R1(seg), warp, lane)) return;
+        }
+    }
+    // Issues the copies of the current item into `cell` (nothing when exhausted) and steps to the next one.
+    __device__ __forceinline__ void issue(const GemvCore& a, const Segs& sg, uint8_t* cell, int warp, int lane) {
+        if (!valid()) return;
+        if (copy_and_step(cell, warp, lane)) {
+            ++seg;
+            enter(a, sg, warp, lane);
+        }
+    }
+};
+
+// The loader of the step kernel: walks the CTA's work list (one row range per weight-streaming phase, in
+// shared memory) from the first phase to the last, regardless of which phase the math is in.
+struct StepLoader : LoaderCore {
+    int entry, count;
+    const StepWork* work;
+
+    __device__ __forceinline__ bool valid() const { return entry < count; }
+    __device__ __forceinline__ void enter(int warp, int lane) {
+        for (; entry < count; ++entry) {
+            const StepWork wk = work[entry];
+            if (wk.r0 >= wk.r1) continue;
+            if (open(wk.kind, wk.K, wk.w, wk.scale, wk.r0, wk.r1, warp, lane)) return;
+        }
+    }
+    __device__ __forceinline__ void issue(uint8_t* cell, int warp, int lane) {
+        if (!valid()) return;
+        if (copy_and_step(cell, warp, lane)) {
+            ++entry;
+            enter(warp, lane);
         }
     }
 };
@@ -199,7 +238,7 @@ __device__ __forceinline__ float block_sum_256(float v, float* scratch) {
 // owner thread before that thread overwrites it with row 0's result.
 constexpr int kLnVec = 2;  // groups of 8 channels per thread: C <= 8192
 template <int PRO>
-__device__ __forceinline__ void stage_prologue_params(const FusedGemvArgs& a, __half* xgen, uint32_t xp, __half* lnrow,
+__device__ __forceinline__ void stage_prologue_params(const GemvCore& a, __half* xgen, uint32_t xp, __half* lnrow,
                                                       __half* pbias) {
     const uint32_t ngrp = a.C / 8;
     constexpr int nv = PRO == PRO_LN ? 0 : PRO == PRO_LN_SHIFT2 ? 2 : 1;
@@ -216,7 +255,7 @@ __device__ __forceinline__ void stage_prologue_params(const FusedGemvArgs& a, __
 }
 
 template <int PRO>
-__device__ void run_prologue(const FusedGemvArgs& a, __half* xgen, uint32_t xp, __half* lnrow, const __half* pbias,
+__device__ void run_prologue(const GemvCore& a, __half* xgen, uint32_t xp, __half* lnrow, const __half* pbias,
                              float* scratch) {
     const uint32_t C = a.C, T = a.T;
     const uint32_t ngrp = C / 8;  // 16-byte groups per row
@@ -233,7 +272,7 @@ __device__ void run_prologue(const FusedGemvArgs& a, __half* xgen, uint32_t xp, 
         for (int q = 0; q < kLnVec; ++q) {
             const uint32_t gi = threadIdx.x + q * kThreads;
             if (gi < ngrp) {
-                const uint4 raw = *reinterpret_cast<const uint4*>(a.ln_x + (size_t)t * C + gi * 8);
+                const uint4 raw = *reinterpret_cast<const uint4*>(a.ln_x + (size_t)(t + a.ln_row_off[t]) * C + gi * 8);
                 const __half2* h = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -334,7 +373,7 @@ struct EpiOperands {
     CursorD cu;
 };
 template <int EPI>
-__device__ __forceinline__ EpiOperands epilogue_fetch(const FusedGemvArgs& a, const GemvProblem& p, uint32_t m, int tok) {
+__device__ __forceinline__ EpiOperands epilogue_fetch(const GemvCore& a, const GemvProblem& p, uint32_t m, int tok) {
     EpiOperands e;
     e.xres = e.r = e.cmx = 0.f;
     e.cu = CursorD{0, 0, 1};
@@ -351,7 +390,7 @@ __device__ __forceinline__ EpiOperands epilogue_fetch(const FusedGemvArgs& a, co
 
 // Activation + the launch's epilogue for output (token tok, row m) of problem p.
 template <int EPI>
-__device__ __forceinline__ void epilogue_one(const FusedGemvArgs& a, const GemvProblem& p, uint32_t m, int tok, float s,
+__device__ __forceinline__ void epilogue_one(const GemvCore& a, const GemvProblem& p, uint32_t m, int tok, float s,
                                              const EpiOperands& e) {
     s = activate_f(p.act, s);
     const size_t oi = (size_t)tok * p.M + m;
@@ -380,9 +419,9 @@ __device__ __forceinline__ void epilogue_one(const FusedGemvArgs& a, const GemvP
 
 // Multiplies one work item with the staged activations: out[0..3] = rows g / g + 8 x tokens 2 t4 / 2 t4 + 1.
 // The four k-steps of an Int8 item go to four independent accumulators (chains of two MMAs).
-__device__ __forceinline__ void consume_item(const GemvProblem& p, const Item& it, int c, const __half* xrow, bool xval,
+__device__ __forceinline__ void consume_item(int kind, uint32_t K, const Item& it, int c, const __half* xrow, bool xval,
                                              const float* sums, uint32_t T, int t4, const uint32_t* lut2, float out[4]) {
-    if (p.kind == MAT_INT8) {
+    if (kind == MAT_INT8) {
         const uint32_t wa[8] = {it.q[0].x, it.q[0].y, it.q[0].z, it.q[0].w, it.q[1].x, it.q[1].y, it.q[1].z, it.q[1].w};
         const uint32_t wb[8] = {it.q[2].x, it.q[2].y, it.q[2].z, it.q[2].w, it.q[3].x, it.q[3].y, it.q[3].z, it.q[3].w};
         float d[4][4];
@@ -404,7 +443,7 @@ __device__ __forceinline__ void consume_item(const GemvProblem& p, const Item& i
         }
         const float2 mmA = __half22float2(*reinterpret_cast<const __half2*>(&it.s[0]));
         const float2 mmB = __half22float2(*reinterpret_cast<const __half2*>(&it.s[2]));
-        const uint32_t nblk = p.K / 128;
+        const uint32_t nblk = K / 128;
         const uint32_t tk0 = 2 * t4, tk1 = tk0 + 1;
         const float s0 = tk0 < T ? sums[tk0 * nblk + c] : 0.f, s1 = tk1 < T ? sums[tk1 * nblk + c] : 0.f;
         const float sA = (mmA.y - mmA.x) * (1.0f / 255.0f), sB = (mmB.y - mmB.x) * (1.0f / 255.0f);
@@ -413,7 +452,7 @@ __device__ __forceinline__ void consume_item(const GemvProblem& p, const Item& i
         out[1] = sA * ((d[0][1] + d[1][1]) + (d[2][1] + d[3][1])) + oA * s1;
         out[2] = sB * ((d[0][2] + d[1][2]) + (d[2][2] + d[3][2])) + oB * s0;
         out[3] = sB * ((d[0][3] + d[1][3]) + (d[2][3] + d[3][3])) + oB * s1;
-    } else if (p.kind == MAT_NF4) {
+    } else if (kind == MAT_NF4) {
         const uint32_t qa[8] = {it.q[0].x, it.q[0].y, it.q[0].z, it.q[0].w, it.q[1].x, it.q[1].y, it.q[1].z, it.q[1].w};
         const uint32_t qb[8] = {it.q[2].x, it.q[2].y, it.q[2].z, it.q[2].w, it.q[3].x, it.q[3].y, it.q[3].z, it.q[3].w};
         out[0] = out[1] = out[2] = out[3] = 0.f;
@@ -427,7 +466,7 @@ __device__ __forceinline__ void consume_item(const GemvProblem& p, const Item& i
 #pragma unroll
             for (int s2 = 0; s2 < 2; ++s2) {
                 uint4 xq = make_uint4(0, 0, 0, 0);
-                if (xval && (uint32_t)(c * 256 + j * 64) < p.K)
+                if (xval && (uint32_t)(c * 256 + j * 64) < K)
                     xq = *reinterpret_cast<const uint4*>(xrow + c * 256 + j * 64 + 16 * t4 + 8 * s2);
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
@@ -450,7 +489,7 @@ __device__ __forceinline__ void consume_item(const GemvProblem& p, const Item& i
             d[hlf][0] = d[hlf][1] = d[hlf][2] = d[hlf][3] = 0.f;
             const uint4 wa = it.q[hlf], wb = it.q[2 + hlf];
             uint4 xq = make_uint4(0, 0, 0, 0);
-            if (xval && (uint32_t)(c * 64 + hlf * 32) < p.K)
+            if (xval && (uint32_t)(c * 64 + hlf * 32) < K)
                 xq = *reinterpret_cast<const uint4*>(xrow + c * 64 + hlf * 32 + 8 * t4);
             mma16816(d[hlf], wa.x, wb.x, wa.y, wb.y, xq.x, xq.y);
             mma16816(d[hlf], wa.z, wb.z, wa.w, wb.w, xq.z, xq.w);

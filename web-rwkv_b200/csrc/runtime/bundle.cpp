@@ -32,7 +32,8 @@ struct CachedJob {
     wrk_commands* commands = nullptr;
     uint32_t num_token = 0, num_header = 0;
     uint64_t tick = 0;
-    std::vector<TensorH> tables;  // per-launch row partitions of the fused path
+    std::vector<TensorH> tables;  // row partitions, phase lists and work lists of the fused paths
+    uint32_t num_phases = 0;      // phases of the step kernel (0: the job runs as a list of launches)
     ~CachedJob() {
         if (commands) wrk_commands_release(commands);
     }
@@ -46,6 +47,9 @@ struct wrk_bundle {
     uint32_t num_batch = 0;
     std::vector<TensorH> state;  // per layer f32 [C, S + 2, num_batch]
     bool packed_cursors = false, use_graph = true, fused = true;
+    bool step_kernel = true;  // fused jobs run as one persistent kernel where the job shape allows it
+    TensorH timeline;         // optional globaltimer stamps of the step kernel: [2 * timeline_phases][num_sms] u64
+    size_t timeline_phases = 0;
     std::map<uint32_t, std::shared_ptr<Buffers>> buffers, headers;
     std::map<std::vector<uint32_t>, std::shared_ptr<CachedJob>> jobs;
     uint64_t tick = 0;
@@ -465,9 +469,78 @@ bool fused_v6_supported(wrk_bundle* bd, uint32_t T) {
            k::fused_gemv_smem(T, info.num_emb, info.num_emb, k::PRO_LN_SHIFT2, 2) <= 200 * 1024 && info.num_emb <= 8192;
 }
 
-int32_t layer_v6_fused(wrk_bundle* bd, OpList& ops, CachedJob* job, const Buffers& B, uint32_t index, uint32_t T) {
+// The phases of a job that runs as one persistent kernel (kernels/decode_step.cu), collected while the
+// fused layers are emitted.
+struct StepBuilder {
+    std::vector<k::StepPhase> phases;
+    std::vector<std::vector<k::StepWork>> work;  // [gemv phase][cta]
+    uint32_t kmax = 0;
+    bool any_prologue = false;
+    const float* table = nullptr;
+};
+
+// Where the fused layers go: a list of launches (one per phase, chained with programmatic dependent launch) or
+// the phase list of the step kernel.
+struct FusedSink {
+    wrk_context* ctx;
+    OpList* ops;
+    CachedJob* job;
+    StepBuilder* step;  // null: one launch per phase
+};
+
+int32_t emit_gemv(FusedSink& sink, k::FusedGemvArgs a, const char* name, std::initializer_list<const wrk_tensor*> keep) {
+    if (sink.step == nullptr) return add_fused_gemv(sink.ctx, *sink.ops, sink.job, a, name, keep);
+    StepBuilder& sb = *sink.step;
+    const int grid = sink.ctx->num_sms;
+    a.status = sink.ctx->device_status;
+    uint32_t kmax = 0;
+    for (int i = 0; i < a.num_problems; ++i) {
+        kmax = std::max(kmax, a.p[i].K);
+        if (a.p[i].kind == k::MAT_NF4 && a.table == nullptr)
+            return set_error(WRK_ERR_INVALID_ARGUMENT, "NF4 problem without a code book");
+    }
+    a.kmax = kmax;
+    sb.kmax = std::max(sb.kmax, kmax);
+    if (a.table) sb.table = a.table;
+    if (a.prologue != k::PRO_NONE) sb.any_prologue = true;
+    k::StepPhase ph{};
+    ph.type = k::PH_GEMV;
+    ph.gemv_index = -1;
+    if (a.num_problems > 0) {
+        std::vector<k::GemvSegment> table;
+        WRK_REQUIRE(k::fused_gemv_partition(a, grid, table), WRK_ERR_UNSUPPORTED,
+                    "row partition overflow: too many small matrices per CTA");
+        std::vector<k::StepWork> work(grid);
+        for (int c = 0; c < grid; ++c) {
+            k::StepWork wk{};
+            int used = 0;
+            for (int i = 0; i < k::kSegmentsPerCta; ++i) {
+                const k::GemvSegment& sg = table[(size_t)c * k::kSegmentsPerCta + i];
+                if (sg.row1 <= sg.row0) continue;
+                const k::GemvProblem& p = a.p[sg.problem];
+                wk.w = p.w;
+                wk.scale = p.scale;
+                wk.r0 = sg.row0;
+                wk.r1 = sg.row1;
+                wk.K = p.K;
+                wk.kind = (int16_t)p.kind;
+                wk.problem = (int16_t)sg.problem;
+                ++used;
+            }
+            WRK_REQUIRE(used <= 1, WRK_ERR_UNSUPPORTED, "a CTA of the step kernel takes one row range per phase");
+            work[c] = wk;
+        }
+        ph.gemv_index = (int32_t)sb.work.size();
+        sb.work.push_back(std::move(work));
+    }
+    ph.gemv = static_cast<const k::GemvCore&>(a);
+    sb.phases.push_back(ph);
+    return WRK_OK;
+}
+
+int32_t layer_v6_fused(wrk_bundle* bd, FusedSink& sink, const Buffers& B, uint32_t index, uint32_t T) {
     const wrk_model_info& info = bd->model->info;
-    wrk_context* ctx = bd->model->ctx;
+    OpList& ops = *sink.ops;
     const Layer& L = bd->model->layers[index];
     const uint32_t C = info.num_emb, S = 64, F = info.num_hidden;
     const uint32_t* cursors = static_cast<const uint32_t*>(B["cursors"]->ptr());
@@ -497,7 +570,7 @@ int32_t layer_v6_fused(wrk_bundle* bd, OpList& ops, CachedJob* job, const Buffer
         a.p[0] = problem(mat_info(L.time_mix_w1), nullptr, 0, B["time_mix_x"]->ptr(), WRK_F16, WRK_ACT_TANH);
         a.epilogue = k::EPI_STORE;
         a.rescale = 1.0f;
-        WRK_TRY(add_fused_gemv(ctx, ops, job, a, "fused_ln_shift_adapter", {B["x"], B["att_x"], B["time_mix_x"], L.time_mix_w1.p->w}));
+        WRK_TRY(emit_gemv(sink, a, "fused_ln_shift_adapter", {B["x"], B["att_x"], B["time_mix_x"], L.time_mix_w1.p->w}));
     }
     // B: adapter W2 + static mixes + five-way token shift
     {
@@ -513,8 +586,16 @@ int32_t layer_v6_fused(wrk_bundle* bd, OpList& ops, CachedJob* job, const Buffer
         a.C = C;
         a.D = info.custom[0];
         a.T = T;
-        ops.ops.push_back(new_atom("fused_tmix_shift", [a](cudaStream_t s) { return k::tmix_shift_v6(a, s); },
-                                   {B["time_mix_x"], B["att_x"], B["att_sx"], L.time_mix_w2.p->w, L.time_mix.p}));
+        if (sink.step) {
+            k::StepPhase ph{};
+            ph.type = k::PH_TMIX;
+            ph.gemv_index = -1;
+            ph.tmix = a;
+            sink.step->phases.push_back(ph);
+        } else {
+            ops.ops.push_back(new_atom("fused_tmix_shift", [a](cudaStream_t s) { return k::tmix_shift_v6(a, s); },
+                                       {B["time_mix_x"], B["att_x"], B["att_sx"], L.time_mix_w2.p->w, L.time_mix.p}));
+        }
     }
     // C: key / value / receptance / gate + decay adapter W1 in one launch
     {
@@ -533,7 +614,7 @@ int32_t layer_v6_fused(wrk_bundle* bd, OpList& ops, CachedJob* job, const Buffer
         a.p[4] = problem(mat_info(L.time_decay_w1), sx, 0, B["att_w"]->ptr(), WRK_F16, WRK_ACT_TANH);
         a.epilogue = k::EPI_STORE;
         a.rescale = 1.0f;
-        WRK_TRY(add_fused_gemv(ctx, ops, job, a, "fused_att_linear",
+        WRK_TRY(emit_gemv(sink, a, "fused_att_linear",
                                {B["att_sx"], B["att_k"], B["att_v"], B["att_r"], B["att_g"], B["att_w"]}));
     }
     // D: decay adapter W2 + WKV + group norm + gate
@@ -560,9 +641,17 @@ int32_t layer_v6_fused(wrk_bundle* bd, OpList& ops, CachedJob* job, const Buffer
         a.gn_b = H(L.gn.b);
         a.gn_eps = GN_EPS;
         a.out = Hm(B["att_xx"]);
-        ops.ops.push_back(new_atom("fused_wkv6", [a](cudaStream_t s) { return k::wkv56_fused(a, s); },
-                                   {B["att_w"], B["att_k"], B["att_v"], B["att_r"], B["att_g"], B["att_x"], B["att_xx"],
-                                    bd->state[index].p}));
+        if (sink.step) {
+            k::StepPhase ph{};
+            ph.type = k::PH_WKV;
+            ph.gemv_index = -1;
+            ph.wkv = a;
+            sink.step->phases.push_back(ph);
+        } else {
+            ops.ops.push_back(new_atom("fused_wkv6", [a](cudaStream_t s) { return k::wkv56_fused(a, s); },
+                                       {B["att_w"], B["att_k"], B["att_v"], B["att_r"], B["att_g"], B["att_x"], B["att_xx"],
+                                        bd->state[index].p}));
+        }
     }
     // E: output projection + residual
     {
@@ -576,7 +665,7 @@ int32_t layer_v6_fused(wrk_bundle* bd, OpList& ops, CachedJob* job, const Buffer
         a.epilogue = k::EPI_RESIDUAL;
         a.xres = Hm(B["x"]);
         a.rescale = 1.0f;
-        WRK_TRY(add_fused_gemv(ctx, ops, job, a, "fused_att_out", {B["att_xx"], B["x"]}));
+        WRK_TRY(emit_gemv(sink, a, "fused_att_out", {B["att_xx"], B["x"]}));
     }
     // F: layer norm + two shifts -> ffn key (squared ReLU) and receptance
     {
@@ -601,7 +690,7 @@ int32_t layer_v6_fused(wrk_bundle* bd, OpList& ops, CachedJob* job, const Buffer
         a.p[1] = problem(mat_info(L.ffn_w_r), nullptr, 1, B["ffn_r"]->ptr(), WRK_F16, WRK_ACT_NONE);
         a.epilogue = k::EPI_STORE;
         a.rescale = 1.0f;
-        WRK_TRY(add_fused_gemv(ctx, ops, job, a, "fused_ffn_in", {B["x"], B["ffn_x"], B["ffn_k"], B["ffn_r"]}));
+        WRK_TRY(emit_gemv(sink, a, "fused_ffn_in", {B["x"], B["ffn_x"], B["ffn_k"], B["ffn_r"]}));
     }
     // G: ffn value + channel mix + residual (+ rescale)
     {
@@ -620,9 +709,92 @@ int32_t layer_v6_fused(wrk_bundle* bd, OpList& ops, CachedJob* job, const Buffer
         a.cm_x = H(B["ffn_x"]);
         a.cm_state = st_ffn;
         a.rescale = (index + 1) % bd->model->rescale == 0 ? 0.5f : 1.0f;
-        WRK_TRY(add_fused_gemv(ctx, ops, job, a, "fused_ffn_out", {B["ffn_k"], B["ffn_r"], B["ffn_x"], B["x"], bd->state[index].p}));
+        WRK_TRY(emit_gemv(sink, a, "fused_ffn_out", {B["ffn_k"], B["ffn_r"], B["ffn_x"], B["x"], bd->state[index].p}));
     }
     (void)F;
+    return WRK_OK;
+}
+
+// The job as one persistent kernel: embedding layer norm, the fused layers and (when rows need logits) the head.
+// Returns WRK_ERR_UNSUPPORTED when the job shape does not fit the kernel (the caller then builds launches).
+int32_t build_step_job(wrk_bundle* bd, CachedJob* job, OpList& ops) {
+    wrk_model* m = bd->model;
+    wrk_context* ctx = m->ctx;
+    const uint32_t T = job->num_token, NH = job->num_header, C = m->info.num_emb;
+    const Buffers& B = *job->buffer;
+    const Buffers& Hd = *job->header;
+    const int grid = ctx->num_sms;
+    WRK_REQUIRE((5 * C + grid - 1) / grid <= 512, WRK_ERR_UNSUPPORTED, "token-shift phase wider than a CTA");
+    StepBuilder sb;
+    OpList unused;
+    FusedSink sink{ctx, &unused, job, &sb};
+    // embed: layer norm of the uploaded rows into x (a phase without matrices; CTA 0 writes the rows)
+    {
+        k::FusedGemvArgs a{};
+        a.T = T;
+        a.C = C;
+        a.prologue = k::PRO_LN;
+        a.ln_x = H(B["input"]);
+        a.ln_w = H(m->embed_ln.w);
+        a.ln_b = H(m->embed_ln.b);
+        a.ln_eps = LN_EPS;
+        a.ln_out = Hm(B["x"]);
+        a.num_problems = 0;
+        a.epilogue = k::EPI_STORE;
+        a.rescale = 1.0f;
+        WRK_TRY(emit_gemv(sink, a, "step_embed", {}));
+    }
+    for (uint32_t i = 0; i < m->info.num_layer; ++i) WRK_TRY(layer_v6_fused(bd, sink, B, i, T));
+    if (NH > 0) {
+        k::FusedGemvArgs a{};
+        a.T = NH;
+        a.C = C;
+        a.prologue = k::PRO_LN;
+        a.ln_x = H(B["x"]);
+        // RnnRedirect::op (rnn.rs:102-133): head row h normalises row headers[h] of x
+        for (uint32_t h = 0; h < NH; ++h) a.ln_row_off[h] = (int32_t)job->redirect.headers[h] - (int32_t)h;
+        a.ln_w = H(m->head_ln.w);
+        a.ln_b = H(m->head_ln.b);
+        a.ln_eps = LN_EPS;
+        a.num_problems = 1;
+        a.p[0] = problem(mat_info(m->head_w), nullptr, 0, Hd["head_o"]->ptr(), WRK_F32, WRK_ACT_NONE);
+        a.epilogue = k::EPI_STORE;
+        a.rescale = 1.0f;
+        WRK_TRY(emit_gemv(sink, a, "step_head", {}));
+    }
+    k::StepArgs s{};
+    s.num_phases = (int32_t)sb.phases.size();
+    s.num_gemv = (int32_t)sb.work.size();
+    s.T = T;
+    s.kmax = std::max(sb.kmax, C);
+    s.C = C;
+    s.table = sb.table;
+    s.status = ctx->device_status;
+    WRK_REQUIRE(k::decode_step_prepare(s, sb.any_prologue) != 0, WRK_ERR_UNSUPPORTED,
+                "job of %u tokens does not fit the step kernel's shared memory", T);
+    // phase list, work lists ([cta][phase]) and the barrier word live as long as the job
+    std::vector<k::StepWork> flat((size_t)grid * sb.work.size());
+    for (size_t g = 0; g < sb.work.size(); ++g)
+        for (int c = 0; c < grid; ++c) flat[(size_t)c * sb.work.size() + g] = sb.work[g][c];
+    auto upload = [&](const void* data, size_t bytes, wrk_tensor** out) -> int32_t {
+        const uint32_t shape[4] = {(uint32_t)((bytes + 3) / 4), 1, 1, 1};
+        WRK_TRY(wrk_tensor_from_data(ctx, WRK_U32, shape, data, bytes, out));
+        job->tables.emplace_back(*out);
+        return WRK_OK;
+    };
+    wrk_tensor *t_phases = nullptr, *t_work = nullptr, *t_bar = nullptr;
+    WRK_TRY(upload(sb.phases.data(), sb.phases.size() * sizeof(k::StepPhase), &t_phases));
+    WRK_TRY(upload(flat.data(), flat.size() * sizeof(k::StepWork), &t_work));
+    const uint32_t zero[4] = {0, 0, 0, 0};
+    WRK_TRY(upload(zero, sizeof zero, &t_bar));
+    s.phases = static_cast<const k::StepPhase*>(t_phases->ptr());
+    s.work = static_cast<const k::StepWork*>(t_work->ptr());
+    s.barrier = static_cast<uint32_t*>(t_bar->ptr());
+    if (bd->timeline_phases >= sb.phases.size() && bd->timeline.p != nullptr)
+        s.timeline = static_cast<unsigned long long*>(bd->timeline.p->ptr());
+    job->num_phases = (uint32_t)sb.phases.size();
+    ops.ops.push_back(new_atom("decode_step", [s, grid](cudaStream_t st) { return k::decode_step(s, grid, st); },
+                               {B["input"], B["x"], t_phases, t_work, t_bar}));
     return WRK_OK;
 }
 
@@ -633,13 +805,30 @@ int32_t build_job(wrk_bundle* bd, const RnnInfo& info, CachedJob* job) {
     const Buffers& B = *job->buffer;
     const Buffers& Hd = *job->header;
     OpList ops;
+    const bool fused = fused_v6_supported(bd, T);
+
+    // the whole job as one persistent kernel (launched eagerly: a memset of the barrier word and one cooperative
+    // launch per job need no graph)
+    if (fused && bd->step_kernel && NH <= (uint32_t)k::kDecodeMaxTokens) {
+        const int32_t st = build_step_job(bd, job, ops);
+        if (st == WRK_OK) {
+            wrk_op* list = nullptr;
+            WRK_TRY(wrk_op_list(ops.ops.data(), ops.ops.size(), &list));
+            const int32_t s = wrk_encode(m->ctx, list, 0, &job->commands);
+            wrk_op_release(list);
+            return s;
+        }
+        if (st != WRK_ERR_UNSUPPORTED) return st;
+        job->tables.clear();
+        job->num_phases = 0;
+    }
 
     // embed: layer norm on the uploaded rows, then copy into x
     ADD(wrk_op_layer_norm(m->embed_ln.w, m->embed_ln.b, B["input"], LN_EPS, &_o));
     WRK_TRY(blit(ops, V(B["input"]), V(B["x"])));
-    const bool fused = fused_v6_supported(bd, T);
+    FusedSink sink{m->ctx, &ops, job, nullptr};
     for (uint32_t i = 0; i < m->info.num_layer; ++i) {
-        if (fused) WRK_TRY(layer_v6_fused(bd, ops, job, B, i, T));
+        if (fused) WRK_TRY(layer_v6_fused(bd, sink, B, i, T));
         else if (m->info.version == 7) WRK_TRY(layer_v7(bd, ops, B, i, T));
         else WRK_TRY(layer_v56(bd, ops, B, i, T));
         if ((i + 1) % m->sep == 0) ADD(wrk_op_sep(&_o));
@@ -762,8 +951,40 @@ int32_t wrk_bundle_set_use_graph(wrk_bundle* b, int32_t use_graph) {
 
 int32_t wrk_bundle_set_fused(wrk_bundle* b, int32_t fused) {
     WRK_REQUIRE(b, WRK_ERR_INVALID_ARGUMENT, "null argument");
-    if (b->fused != (fused != 0)) drop_caches(b);
+    WRK_REQUIRE(fused >= 0 && fused <= 2, WRK_ERR_INVALID_ARGUMENT, "fused mode %d: 0, 1 or 2", fused);
+    if (b->fused != (fused != 0) || b->step_kernel != (fused == 1)) drop_caches(b);
     b->fused = fused != 0;
+    b->step_kernel = fused == 1;
+    return WRK_OK;
+}
+
+int32_t wrk_bundle_set_phase_timeline(wrk_bundle* b, uint32_t max_phases) {
+    WRK_REQUIRE(b, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    drop_caches(b);
+    b->timeline = TensorH();
+    b->timeline_phases = 0;
+    if (max_phases == 0) return WRK_OK;
+    wrk_context* ctx = b->model->ctx;
+    const uint32_t shape[4] = {2u * (uint32_t)ctx->num_sms * 2u, max_phases, 1, 1};  // u64 as pairs of u32
+    wrk_tensor* t = nullptr;
+    WRK_TRY(wrk_tensor_zeros(ctx, WRK_U32, shape, &t));
+    b->timeline = TensorH(t);
+    b->timeline_phases = max_phases;
+    return WRK_OK;
+}
+
+int32_t wrk_job_phase_timeline(wrk_job* job, uint64_t* stamps, size_t capacity, uint32_t* num_phases, uint32_t* num_ctas) {
+    WRK_REQUIRE(job && num_phases && num_ctas, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    wrk_bundle* b = job->bundle;
+    wrk_context* ctx = b->model->ctx;
+    *num_phases = job->job->num_phases;
+    *num_ctas = (uint32_t)ctx->num_sms;
+    WRK_REQUIRE(b->timeline.p != nullptr && job->job->num_phases > 0 && job->job->num_phases <= b->timeline_phases,
+                WRK_ERR_EMPTY, "list must not be empty: the job records no phase timeline");
+    const size_t need = (size_t)2 * job->job->num_phases * ctx->num_sms;
+    WRK_REQUIRE(stamps && capacity >= need, WRK_ERR_SIZE, "data size not match: %zu vs. %zu", capacity, need);
+    WRK_CUDA(cudaMemcpyAsync(stamps, b->timeline.p->ptr(), need * sizeof(uint64_t), cudaMemcpyDeviceToHost, ctx->stream));
+    WRK_CUDA(cudaStreamSynchronize(ctx->stream));
     return WRK_OK;
 }
 

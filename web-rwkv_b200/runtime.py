@@ -215,7 +215,12 @@ class Bundle:
         check(lib().wrk_bundle_set_use_graph(self.handle, int(use)))
 
     def set_fused(self, fused):
+        """0 / False: one launch per reference op; 1 / True: fused kernels, small v6 jobs as one persistent kernel;
+        2: fused kernels, one launch per phase."""
         check(lib().wrk_bundle_set_fused(self.handle, int(fused)))
+
+    def set_phase_timeline(self, max_phases):
+        check(lib().wrk_bundle_set_phase_timeline(self.handle, int(max_phases)))
 
     def state_shape(self):
         s = (ctypes.c_uint32 * 4)()
@@ -275,6 +280,15 @@ class Job:
         check(lib().wrk_job_back(self.handle, logits.ctypes.data_as(ctypes.c_void_p), ctypes.c_size_t(logits.size),
                                  outs, ctypes.byref(nh)))
         return [logits[outs[2 * i]: outs[2 * i + 1]] for i in range(nb)]
+
+    def phase_timeline(self):
+        """(num_phases, 2, num_ctas) uint64 device-timer stamps (ns) of the job's last run: [:, 0] phase starts,
+        [:, 1] phase ends."""
+        nph, ncta = ctypes.c_uint32(), ctypes.c_uint32()
+        buf = np.zeros(2 * 4096 * 256, dtype=np.uint64)
+        check(lib().wrk_job_phase_timeline(self.handle, buf.ctypes.data_as(ctypes.c_void_p), ctypes.c_size_t(buf.size),
+                                           ctypes.byref(nph), ctypes.byref(ncta)))
+        return buf[: 2 * nph.value * ncta.value].reshape(nph.value, 2, ncta.value)
 
     def num_kernels(self):
         n = ctypes.c_uint64()
