@@ -140,6 +140,32 @@ def build_model(wrk, rt, synth, ctx, config, num_layer=None, keep=False):
     return model, kept, (version, C, L, F, V)
 
 
+def serialize_round_trip(rt, ctx, model):
+    """Writes the quantized model to a file and restores it (what a server does on every start after the first);
+    returns the times next to which `model_build_s` (quantizing from fp16) is read."""
+    import shutil
+    import tempfile
+    folder = tempfile.mkdtemp(prefix="wrk_model_")
+    try:
+        if shutil.disk_usage(folder).free < 24 << 30:
+            return {"skipped": "less than 24 GB free for the model file"}
+        path = os.path.join(folder, "model.cbor")
+        t0 = time.perf_counter()
+        model.save(path)
+        t1 = time.perf_counter()
+        loaded = rt.Model.load(ctx, path)
+        ctx.synchronize()
+        t2 = time.perf_counter()
+        same = all(np.array_equal(a, b) for name in ("att.w_k", "ffn.w_v")
+                   for a, b in zip(model.matrix_parts(0, name)[1:3], loaded.matrix_parts(0, name)[1:3]))
+        del loaded
+        return {"save_s": t1 - t0, "load_s": t2 - t1, "file_gb": os.path.getsize(path) / 1e9, "layer0_bytes_identical": bool(same)}
+    except Exception as e:  # a full disk must not cost the benchmark
+        return {"failed": str(e)[:200]}
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+
+
 def step_bytes(C, L, F, V, S=64):
     """Algorithmic HBM bytes of one batch-1 v6 Int8 decode token and of its quantized GEMVs."""
     int8 = lambda k, m: k * m * (1 + 4 / 128) + 2 * k + 4 * m  # weights + scales + fp16 x + <=fp32 y
@@ -261,10 +287,10 @@ def device_decode(wrk, rt, ctx, bundle, embeds, decode, steps, warmup, sync):
     return ms, ctx.launch_count() - launches0, job.num_kernels()
 
 
-def check_fused_against_strict(wrk, rt, model, prompt, vocab):
+def check_fused_against_strict(wrk, rt, model, prompt, vocab, mode):
     """One decoded token after the prompt through the fused job and through the op-by-op job."""
     outs = []
-    for fused in (True, False):
+    for fused in (mode, 0):
         bundle = rt.Bundle(model, 1)
         bundle.set_fused(fused)
         inp = rt.RnnInput([(prompt, wrk.RNN_LAST)], PROMPT)
@@ -378,6 +404,9 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-secondary", action="store_true")
     ap.add_argument("--strict", action="store_true", help="one launch per reference op (no fused kernels)")
+    ap.add_argument("--fused", type=int, default=2, choices=[1, 2, 3],
+                    help="decode job: 2 = one launch per fused phase (default), 1 = one persistent kernel, 3 = persistent, mma.sync only")
+    ap.add_argument("--no-serialize", action="store_true", help="skip the save / load timing of the quantized model")
     ap.add_argument("--sweep", choices=["matmul", "wkv"], help="op-level sweep instead of the model benchmark")
     ap.add_argument("--kind", default="int8,nf4,fp16")
     ap.add_argument("--shape", action="append", help="sweep: K,M (repeatable)")
@@ -419,6 +448,7 @@ def main():
     model, tensors, _ = build_model(wrk, rt, synth, ctx, args.config, L, keep=keep)
     ctx.synchronize()
     t_build = time.perf_counter() - t_build
+    serialized = serialize_round_trip(rt, ctx, model) if rank == 0 and world == 1 and not args.no_serialize else None
     rng = np.random.default_rng(SEED_TOKENS + rank)
     prompt = rng.integers(0, V - 1, PROMPT).tolist()
     tokens = rng.integers(0, V - 1, args.decode).astype(np.uint32)
@@ -426,12 +456,12 @@ def main():
     # ---- parity of what is timed: the fused job against the op-by-op job, one decoded token ----
     checked = None
     if not args.strict:
-        diff, scale = check_fused_against_strict(wrk, rt, model, prompt, (V + 7) // 8 * 8)
+        diff, scale = check_fused_against_strict(wrk, rt, model, prompt, (V + 7) // 8 * 8, args.fused)
         checked = {"checked": bool(diff <= 2e-2 * max(1.0, scale)), "max_abs": diff, "logit_scale": scale,
                    "against": "one-launch-per-reference-op job, same model, prompt and token"}
 
     bundle = rt.Bundle(model, 1)
-    bundle.set_fused(not args.strict)
+    bundle.set_fused(0 if args.strict else args.fused)
 
     # prompt (GEMM path), untimed
     inp = rt.RnnInput([(prompt, wrk.RNN_LAST)], PROMPT)
@@ -523,7 +553,7 @@ def main():
         model2, _, dims2 = build_model(wrk, rt, synth, ctx, SECONDARY)
         _, C2, L2, F2, V2 = dims2
         bundle2 = rt.Bundle(model2, 1)
-        bundle2.set_fused(not args.strict)
+        bundle2.set_fused(0 if args.strict else args.fused)
         bundle2.infer(rt.RnnInput([(prompt, wrk.RNN_LAST)], PROMPT), logits)
         emb2 = synth.make_globals(6, C2, V2, SEED_WEIGHTS)["emb.weight"]
         embeds2 = ctx.from_numpy(emb2[tokens])
@@ -548,7 +578,7 @@ def main():
         "data": "synthetic",
         "config": {"workload": workload, "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
                    "l2": f"weights of one token ({total_bytes / 1e9:.1f} GB) exceed L2 (126 MB); no flush needed",
-                   "mode": "strict" if args.strict else "fused", "model_build_s": t_build},
+                   "mode": "strict" if args.strict else {1: "fused, one persistent kernel", 2: "fused, launch per phase", 3: "fused, persistent mma.sync kernel"}[args.fused], "model_build_s": t_build, "model_file": serialized},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s",
                 "h2d_bytes_per_step": args.decode * (C * 2 + 12), "d2h_bytes_per_step": args.decode * ((V + 7) // 8 * 8) * 4},

@@ -64,6 +64,14 @@ int32_t wrk_model_builder_info(wrk_model_builder* b, wrk_model_info* info);
  * v7.rs:1038-1226), chosen by the version Loader::info finds. */
 int32_t wrk_model_builder_build(wrk_model_builder* b, wrk_model** out);
 
+/* The built model (packed weights, block scales, code tables; no fp16 originals of quantized matrices) written to
+ * one file and restored from it: the reference derives Serialize for its `Model` (every `TensorGpu` is read back as a
+ * `TensorBlob {shape, data}`, src/tensor/serialization.rs:11-75), restores through `Seed<Context, Model>`
+ * (src/tensor/serialization.rs:96-159) and round-trips through CBOR in examples/serde.rs:218-268.  The file is that
+ * CBOR tree: maps keyed by the reference's field names, `Matrix` as `Fp16` / `Int8 {w, m}` / `Fp4 {q, w, m}`. */
+int32_t wrk_model_save(wrk_model* m, const char* path);
+int32_t wrk_model_load(wrk_context* ctx, const char* path, wrk_model** out);
+
 int32_t wrk_model_info_get(const wrk_model* m, wrk_model_info* info);
 int32_t wrk_model_retain(wrk_model* m);
 int32_t wrk_model_release(wrk_model* m);
@@ -79,10 +87,13 @@ int32_t wrk_bundle_release(wrk_bundle* b);
 int32_t wrk_bundle_set_packed_cursors(wrk_bundle* b, int32_t packed);
 /* Build jobs as CUDA graphs (default 1) or as plain launch lists (0). */
 int32_t wrk_bundle_set_use_graph(wrk_bundle* b, int32_t use_graph);
-/* 1 (default): jobs may use fused kernels in place of runs of reference ops, and a v6 job of at most 8 tokens
- * runs as one persistent kernel (all layers and the head; the CTAs meet at a grid barrier between phases);
- * 2: the same fused kernels, one launch per phase; 0: one launch per reference op, every intermediate tensor
- * materialised with the reference's dtypes. */
+/* 2 (default): jobs may use fused kernels in place of runs of reference ops, one launch per phase (seven per v6
+ * layer, chained by programmatic dependent launch inside a CUDA graph); 1: a v6 job of at most 8 tokens runs as
+ * one persistent kernel instead (all layers and the head; the CTAs meet at a grid barrier between phases; Int8 and
+ * fp16 matrices with one or two tokens are multiplied by tcgen05.mma from shared memory, anything else by cp.async
+ * rings and mma.sync); 3: as 1 but always the mma.sync kernel; 0: one launch per reference op, every intermediate
+ * tensor materialised with the reference's dtypes.  No counterpart in the reference, whose jobs are always one
+ * pass per op (src/runtime/v6.rs:560-900). */
 int32_t wrk_bundle_set_fused(wrk_bundle* b, int32_t fused);
 /* No counterpart in the reference (its profiler hooks are wgpu timestamp queries, commented out in
  * src/tensor/ops.rs:2600).  Makes the persistent decode kernel record the device's nanosecond timer when each CTA

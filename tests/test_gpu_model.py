@@ -72,7 +72,7 @@ def test_mixed_batches_chunked_prefill_then_decode(ctx, config, quant):
 
 
 @pytest.mark.parametrize("config", ["v6-tiny", "v5-tiny", "v7-tiny"])
-@pytest.mark.parametrize("fused", [0, 1, 2])  # op by op / one persistent kernel per job / one launch per phase
+@pytest.mark.parametrize("fused", [0, 1, 2, 3])  # op by op / one persistent kernel per job (tensor-core, where the matrices allow) / one launch per phase / persistent mma.sync kernel
 def test_decode_loop(ctx, config, fused):
     rng = np.random.default_rng(2002)
     tensors, model, ref = _build(ctx, config, {0: 1, 1: 1, 2: 1})

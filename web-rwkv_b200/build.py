@@ -24,9 +24,11 @@ SOURCES = [
     "kernels/support.cu",
     "kernels/decode.cu",
     "kernels/decode_step.cu",
+    "kernels/decode_step_umma.cu",
     "runtime/rnn.cpp",
     "runtime/model.cpp",
     "runtime/bundle.cpp",
+    "runtime/serialize.cpp",
 ]
 
 NVCC_FLAGS = [

@@ -178,5 +178,74 @@ struct StepArgs {
 size_t decode_step_prepare(StepArgs& s, bool any_prologue);
 cudaError_t decode_step(const StepArgs& s, int grid, cudaStream_t stream);
 
+// ---- the same job with the matrices on the 5th-generation tensor cores (decode_step_umma.cu) ----------------
+// Int8 and fp16 matrices, jobs of one or two tokens.  A CTA's rows of a matrix arrive as blocks of
+// [rows][128 bytes] in a ring of 16 KB stages (cp.async by four loader warps, into the 128-byte-swizzled operand
+// layout) and are multiplied straight from shared memory by tcgen05.mma (kind::i8 against the activations as three
+// signed-byte digits per value, kind::f16 against fp16 activations); the accumulators live in tensor memory.
+struct UmmaWork {
+    const uint8_t* w;       // the matrix: rows of K bytes (Int8) or 2 K bytes (fp16)
+    const __half* scale;    // Int8: (min, max) per 128 weights
+    int32_t r0, r1;         // rows [r0, r1) of the matrix (r0 == r1: none)
+    uint32_t K;
+    int16_t kind, problem;
+    int32_t direct;         // 1: a few rows of an fp16 matrix fed by a one-token prologue: multiplied from registers,
+                            // never staged (the loaders and issuers skip the entry)
+    uint8_t pad_[28];
+};
+static_assert(sizeof(UmmaWork) == 64, "work lists are fetched with 16-byte bulk copies");
+
+// Geometry of one 128-row tile of a CTA's row range: P stage rows per k-block, Q k-blocks per stage; a stage's
+// activation operand is one 8-row atom (Q == 1) or two.
+struct UmmaTile {
+    int rows, P, Q, nkb, nslots;
+    uint32_t xstep;  // elements of the tensor map per k-block (128 bytes)
+    uint32_t atom;   // bytes of the activation operand per stage
+};
+__host__ __device__ inline UmmaTile umma_tile(int total_rows, int tile, int kind, uint32_t K, uint32_t T) {
+    UmmaTile t;
+    const bool i8 = kind == MAT_INT8;
+    const int left = total_rows - tile * 128;
+    t.rows = left < 128 ? left : 128;
+    // the blocks of a stage share one MMA: block i's activations take columns [i * c, (i + 1) * c) of its 16
+    const int cols = i8 ? 3 * (int)T : (int)T;
+    int q = t.rows <= 32 ? 4 : t.rows <= 64 ? 2 : 1;
+    if (total_rows > 128) q = 1;  // the operand has one layout per range: ranges of several tiles do not pack their last one
+    while (q * cols > 16) q >>= 1;
+    t.Q = q;
+    t.P = 128 / q;
+    // activation rows of a stage: up to eight fit one 8-row atom (1 KB; the MMA's columns 8-15 then alias 0-7)
+    t.atom = q * cols > 8 ? 2048u : 1024u;
+    t.nkb = i8 ? (int)(K / 128) : (int)(K / 64);
+    t.nslots = (t.nkb + t.Q - 1) / t.Q;
+    t.xstep = i8 ? 128u : 64u;
+    return t;
+}
+__host__ __device__ inline uint32_t umma_operand_bytes(int total_rows, int kind, uint32_t K, uint32_t T) {
+    if (total_rows <= 0) return 0;
+    const UmmaTile t = umma_tile(total_rows, 0, kind, K, T);
+    return (uint32_t)t.nslots * t.atom;
+}
+
+struct UmmaStepArgs {
+    const StepPhase* phases;
+    int32_t num_phases;
+    const UmmaWork* work;   // [grid][num_gemv]
+    int32_t num_gemv;
+    uint32_t T, C;
+    int32_t num_slots;      // 16 KB stages (filled in by decode_step_umma_prepare)
+    uint32_t b_bytes;       // activation operand region: 1 KB per k-block of the longest row (+ the prologue rows)
+    uint32_t x_bytes;       // prologue rows at the end of that region
+    uint32_t nkb_max;       // most 128-weight blocks of any Int8 row
+    uint32_t* barrier;
+    int32_t* status;
+    unsigned long long* timeline;
+};
+// Shared memory of the kernel for a job shape (0: does not fit); fills num_slots, b_bytes, x_bytes.
+// `operand_bytes`: the largest activation operand of any CTA and phase, plus the prologue rows where the phase
+// has a prologue (b_bytes); x_bytes: the prologue rows alone.
+size_t decode_step_umma_prepare(UmmaStepArgs& s, uint32_t operand_bytes, uint32_t x_bytes, uint32_t kmax_int8);
+cudaError_t decode_step_umma(const UmmaStepArgs& s, int grid, cudaStream_t stream);
+
 }  // namespace k
 }  // namespace wrk

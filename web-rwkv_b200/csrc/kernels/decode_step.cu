@@ -18,135 +18,142 @@
 // Phase descriptors are fetched two phases ahead into shared memory with one bulk copy each (completion on an
 // mbarrier); what a phase needs from memory that no earlier phase of the job writes (layer-norm parameters,
 // adapter rows, the WKV state) is requested before the barrier wait, so that it is in flight while the CTA waits.
-#include "gemv_device.cuh"
+#include "decode_step_common.cuh"
+
+#include <cstdlib>
 
 namespace wrk {
 namespace k {
 
 namespace {
 
-constexpr uint32_t kStepSpinLimit = 1u << 21;  // polls before a wait gives up (about a second)
-
-__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ unsigned long long global_timer() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completing on `bar`.
-__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void bar_sync_256() { asm volatile("bar.sync 1, 256;\n" ::: "memory"); }
-
-// What a CTA carries from phase to phase.
-struct Step {
-    const StepArgs& s;
-    int phase;
-    volatile int* abort_flag;
-    // shared memory
-    StepWork* work;
+// The CTA's shared memory as the weight-streaming phases use it.
+struct GemvShared {
     uint8_t* ring;   // this warp's cells
     float* part;
     float* sums;
     __half* xs;
     float* scratch;  // [2 * kWarps]
     const uint32_t* lut2;
-    StepLoader ld;
-    int cs_slot;
-    int warp, lane;
-
-    __device__ __forceinline__ Step(const StepArgs& args) : s(args) {}
-
-    __device__ __forceinline__ void stamp(int which) {
-        if (s.timeline != nullptr && threadIdx.x == 0)
-            s.timeline[(size_t)(2 * phase + which) * gridDim.x + blockIdx.x] = global_timer();
-    }
-    // Every CTA has finished the previous phase and its results are visible.  False: the wait gave up.
-    __device__ __forceinline__ bool wait_grid() {
-        if (phase > 0) {
-            if (threadIdx.x == 0) {
-                const uint32_t target = (uint32_t)phase * gridDim.x;
-                uint32_t polls = 0;
-                while (ld_acquire_gpu(s.barrier) < target) {
-                    if (++polls >= kStepSpinLimit) {
-                        *abort_flag = 1;
-                        atomicExch(s.status, (int32_t)WRK_ERR_TIMEOUT);
-                        break;
-                    }
-                }
-                __threadfence();
-            }
-            __syncthreads();
-        }
-        stamp(0);
-        return *abort_flag == 0;
-    }
-    // This CTA's results of the phase are written: arrive at the barrier.
-    __device__ __forceinline__ void arrive_grid() {
-        __syncthreads();
-        stamp(1);
-        if (threadIdx.x == 0) {
-            __threadfence();
-            atomicAdd(s.barrier, 1u);
-        }
-    }
+    int depth;
 };
 
 // ---- weight-streaming phase ------------------------------------------------------------------------
-// The body of fused_gemv_kernel for one row range, with the loader running over the whole job.
-template <int PRO, int EPI>
-__device__ __noinline__ bool gemv_phase(Step& st, const GemvCore& a, const StepWork wk) {
-    const int warp = st.warp, lane = st.lane, g = lane >> 2, t4 = lane & 3;
+// The body of fused_gemv_kernel for one row range, with the loader running over the whole job.  Prologue and
+// epilogue are chosen at run time and the row loop exists once per weight format: every phase of every layer
+// runs the same few KB of loop code, which therefore stays in the instruction caches from phase to phase (six
+// template copies of the loop, one per prologue / epilogue pair, starved the warps of instructions: each phase
+// began with a cold loop fetched through a memory system that is busy streaming weights).
+// Rows [r0, r1) of one matrix of format KIND against the staged activations: the item loop and, per group of 64
+// rows, the sum over the warps and the epilogue.
+template <int KIND>
+__device__ __noinline__ void stream_rows(const GemvShared sm, const GemvCore& a, const GemvProblem& p, int epi, uint32_t K, int r0,
+                                         int r1, const __half* xv, uint32_t xp, StepLoader& ld_io, int& cs_slot_io, int warp, int lane) {
+    const int g = lane >> 2, t4 = lane & 3;
     const uint32_t T = a.T;
-    const int depth = st.s.ring_depth;
-    const uint32_t xp = (PRO != PRO_NONE ? a.C : a.kmax) + 8;  // halfs per activation row
-    __half* xs = st.xs;
+    const int depth = sm.depth;
+    float* part = sm.part;
+    const float* sums = sm.sums;
+    const bool xval = (uint32_t)g < T;
+    const __half* xrow = xv + (size_t)(xval ? g : 0) * xp;
+    const uint32_t rb = KIND == MAT_FP16 ? K * 2 : KIND == MAT_INT8 ? K : K / 2;
+    const int nchunk = (int)((rb + CHUNK_BYTES - 1) / CHUNK_BYTES);
+    uint8_t* ring = sm.ring;
+    const uint32_t* lut2 = sm.lut2;
+    int cs_slot = cs_slot_io;
+    StepLoader ld = ld_io;  // the loader and the ring cursor live in registers through the loop
+
+#pragma unroll 1
+    for (int group0 = r0; group0 < r1; group0 += GROUP_ROWS) {
+        const int gn = min(GROUP_ROWS, r1 - group0);
+        // the group's outputs belong to the first gn * T threads; their epilogue operands go in flight now
+        const int orow = (int)threadIdx.x / (int)T, otok = (int)threadIdx.x - orow * (int)T;
+        const bool has_out = (int)threadIdx.x < gn * (int)T;
+        EpiOperands eo;
+        if (has_out) eo = epilogue_fetch_rt(epi, a, p, (uint32_t)(group0 + orow), otok);
+
+        float* mine = part + (size_t)warp * GROUP_ROWS * T;
+#pragma unroll 1
+        for (int row0 = group0; row0 < group0 + gn; row0 += 16) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+            for (int c = warp; c < nchunk; c += kWarps) {
+                cp_async_wait_dyn(depth - 1);  // this lane's copies of the oldest item in flight have landed
+                __syncwarp();                  // ... and so have the other lanes' (the rows' block scales)
+                uint8_t* cell = ring + cs_slot * CELL_BYTES;
+                const Item it = read_item(cell, lane);
+                __syncwarp();  // every lane has read the cell: refill it with the item `depth` steps ahead
+                ld.issue(cell, warp, lane);
+                cp_async_commit();
+                if (++cs_slot == depth) cs_slot = 0;
+                float out[4];
+                consume_item(KIND, K, it, c, xrow, xval, sums, T, t4, lut2, out);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[e] += out[e];
+            }
+            const uint32_t tk0 = 2 * t4, tk1 = tk0 + 1;
+            float* dst = mine + (size_t)(row0 - group0) * T;
+            if (tk0 < T) {
+                dst[g * T + tk0] = acc[0];
+                dst[(g + 8) * T + tk0] = acc[2];
+            }
+            if (tk1 < T) {
+                dst[g * T + tk1] = acc[1];
+                dst[(g + 8) * T + tk1] = acc[3];
+            }
+        }
+        __syncthreads();
+        // the 16 warps' partial results are summed in warp order (deterministic)
+        if (has_out) {
+            const float* src = part + threadIdx.x;
+            float total = 0.f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) total += src[(size_t)w * GROUP_ROWS * T];
+            epilogue_one_rt(epi, a, p, (uint32_t)(group0 + orow), otok, total, eo);
+        }
+        if (group0 + GROUP_ROWS < r1) __syncthreads();  // the slabs are written again
+    }
+    cs_slot_io = cs_slot;
+    ld_io = ld;
+}
+
+// Stages the phase's activations: the layer-norm / token-shift prologue or the explicit input rows, and the
+// per-128-block sums of the values an Int8 matrix will be multiplied with.  Returns the rows the matrix reads.
+__device__ __noinline__ const __half* stage_activations(const GridSync gs, const GemvShared sm, const GemvCore& a, const StepWork wk,
+                                                       bool* alive) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pro_kind = a.prologue;
+    const uint32_t T = a.T;
+    const uint32_t xp = (pro_kind != PRO_NONE ? a.C : a.kmax) + 8;  // halfs per activation row
+    __half* xs = sm.xs;
     __half* lnrow = xs;
-    __half* xgen = PRO == PRO_LN ? xs : xs + (size_t)T * xp;
-    const uint32_t pro_rows = PRO == PRO_LN ? T : PRO == PRO_LN_SHIFT1 ? 2 * T : 3 * T;
+    __half* xgen = pro_kind == PRO_LN || pro_kind == PRO_NONE ? xs : xs + (size_t)T * xp;
+    const uint32_t pro_rows = pro_kind == PRO_LN ? T : pro_kind == PRO_LN_SHIFT1 ? 2 * T : 3 * T;
     __half* pbias = xs + (size_t)pro_rows * xp;
-    float* part = st.part;
-    float* sums = st.sums;
+    float* sums = sm.sums;
 
     const bool any_work = wk.r0 < wk.r1;
-    const bool pro = PRO != PRO_NONE && (any_work || blockIdx.x == 0);
-    if (PRO != PRO_NONE) {
+    const bool pro = pro_kind != PRO_NONE && (any_work || blockIdx.x == 0);
+    if (pro_kind != PRO_NONE) {
         // parameters of the prologue: in flight while the CTA waits for the previous phase
-        if (pro) stage_prologue_params<PRO>(a, xgen, xp, lnrow, pbias);
+        if (pro) {
+            if (pro_kind == PRO_LN) stage_prologue_params<PRO_LN>(a, xgen, xp, lnrow, pbias);
+            else if (pro_kind == PRO_LN_SHIFT1) stage_prologue_params<PRO_LN_SHIFT1>(a, xgen, xp, lnrow, pbias);
+            else stage_prologue_params<PRO_LN_SHIFT2>(a, xgen, xp, lnrow, pbias);
+        }
         cp_async_commit();
     }
-    if (!st.wait_grid()) return false;
-    if (PRO != PRO_NONE && pro) {
+    *alive = gs.wait();
+    if (!*alive) return nullptr;
+    if (pro) {
         // the parameter group is the newest of this thread: waiting for it waits for the ring's groups too,
         // which were issued before the barrier and have had its whole wait to land
         cp_async_wait<0>();
-        run_prologue<PRO>(a, xgen, xp, lnrow, pbias, st.scratch);
+        if (pro_kind == PRO_LN) run_prologue<PRO_LN>(a, xgen, xp, lnrow, pbias, sm.scratch);
+        else if (pro_kind == PRO_LN_SHIFT1) run_prologue<PRO_LN_SHIFT1>(a, xgen, xp, lnrow, pbias, sm.scratch);
+        else run_prologue<PRO_LN_SHIFT2>(a, xgen, xp, lnrow, pbias, sm.scratch);
     }
-    if (!any_work) return true;
+    if (!any_work) return nullptr;
 
     const GemvProblem& p = a.p[wk.problem];
     const int kind = wk.kind;
@@ -199,301 +206,12 @@ __device__ __noinline__ bool gemv_phase(Step& st, const GemvCore& a, const StepW
             const uint2 raw = *reinterpret_cast<const uint2*>(xv + (size_t)tok * xp + blk * 128 + lane * 4);
             const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
             const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-            const float sm = warp_sum((lo.x + lo.y) + (hi.x + hi.y));
-            if (lane == 0) sums[tok * nblk + blk] = sm;
+            const float total = warp_sum((lo.x + lo.y) + (hi.x + hi.y));
+            if (lane == 0) sums[tok * nblk + blk] = total;
         }
     }
     __syncthreads();
-
-    const bool xval = (uint32_t)g < T;
-    const __half* xrow = xv + (size_t)(xval ? g : 0) * xp;
-    const uint32_t rb = kind == MAT_FP16 ? K * 2 : kind == MAT_INT8 ? K : K / 2;
-    const int nchunk = (int)((rb + CHUNK_BYTES - 1) / CHUNK_BYTES);
-    const int r0 = wk.r0, r1 = wk.r1;
-    uint8_t* ring = st.ring;
-    const uint32_t* lut2 = st.lut2;
-    int cs_slot = st.cs_slot;
-    StepLoader ld = st.ld;  // the loader and the ring cursor live in registers through the loop
-
-#pragma unroll 1
-    for (int group0 = r0; group0 < r1; group0 += GROUP_ROWS) {
-        const int gn = min(GROUP_ROWS, r1 - group0);
-        // the group's outputs belong to the first gn * T threads; their epilogue operands go in flight now
-        const int orow = (int)threadIdx.x / (int)T, otok = (int)threadIdx.x - orow * (int)T;
-        const bool has_out = (int)threadIdx.x < gn * (int)T;
-        EpiOperands eo;
-        if (has_out) eo = epilogue_fetch<EPI>(a, p, (uint32_t)(group0 + orow), otok);
-
-        float* mine = part + (size_t)warp * GROUP_ROWS * T;
-#pragma unroll 1
-        for (int row0 = group0; row0 < group0 + gn; row0 += 16) {
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
-            for (int c = warp; c < nchunk; c += kWarps) {
-                cp_async_wait_dyn(depth - 1);  // this lane's copies of the oldest item in flight have landed
-                __syncwarp();                  // ... and so have the other lanes' (the rows' block scales)
-                uint8_t* cell = ring + cs_slot * CELL_BYTES;
-                const Item it = read_item(cell, lane);
-                __syncwarp();  // every lane has read the cell: refill it with the item `depth` steps ahead
-                ld.issue(cell, warp, lane);
-                cp_async_commit();
-                if (++cs_slot == depth) cs_slot = 0;
-                float out[4];
-                consume_item(kind, K, it, c, xrow, xval, sums, T, t4, lut2, out);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) acc[e] += out[e];
-            }
-            const uint32_t tk0 = 2 * t4, tk1 = tk0 + 1;
-            float* dst = mine + (size_t)(row0 - group0) * T;
-            if (tk0 < T) {
-                dst[g * T + tk0] = acc[0];
-                dst[(g + 8) * T + tk0] = acc[2];
-            }
-            if (tk1 < T) {
-                dst[g * T + tk1] = acc[1];
-                dst[(g + 8) * T + tk1] = acc[3];
-            }
-        }
-        __syncthreads();
-        // the 16 warps' partial results are summed in warp order (deterministic)
-        if (has_out) {
-            const float* src = part + threadIdx.x;
-            float sm = 0.f;
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) sm += src[(size_t)w * GROUP_ROWS * T];
-            epilogue_one<EPI>(a, p, (uint32_t)(group0 + orow), otok, sm, eo);
-        }
-        if (group0 + GROUP_ROWS < r1) __syncthreads();  // the slabs are written again
-    }
-    st.cs_slot = cs_slot;
-    st.ld = ld;
-    return true;
-}
-
-// ---- v6 data-dependent token shift -------------------------------------------------------------------
-// sx[i][t][c] = mix(att_x[t][c], prev[t][c], f16(f16(W2[i][c][:] . tmx[t][i*D:(i+1)*D]) + mix[i][c])); the 5 C
-// outputs are spread evenly over the CTAs, one per thread.
-__device__ __noinline__ bool tmix_phase(Step& st, const TmixArgs& a) {
-    __half* s_tmx = st.xs;  // [T][5 * D]
-    const uint32_t C = a.C, D = a.D, T = a.T;
-    const uint32_t per = (5 * C + gridDim.x - 1) / gridDim.x;  // at most kThreads (checked by the host)
-    const uint32_t o = blockIdx.x * per + threadIdx.x;
-    const bool active = threadIdx.x < per && o < 5 * C;
-    const uint32_t i = active ? o / C : 0, c = active ? o % C : 0;
-    // the adapter weights of this thread do not depend on earlier phases
-    uint4 wreg[8];  // D <= 64 halfs
-    float mu = 0.f;
-    if (active) {
-        const uint4* wp = reinterpret_cast<const uint4*>(a.w2 + ((size_t)i * C + c) * D);
-#pragma unroll
-        for (uint32_t j = 0; j < 8; ++j)
-            if (j < D / 8) wreg[j] = wp[j];
-        mu = __half2float(a.mix[(size_t)i * C + c]);
-    }
-    if (!st.wait_grid()) return false;
-    for (uint32_t j = threadIdx.x; j < T * 5 * D; j += kThreads) s_tmx[j] = a.tmx[j];
-    const CursorD cu0 = cursor_at(a.cursors, a.wide, 0);
-    const float cur0 = active ? __half2float(a.att_x[c]) : 0.f;
-    const float prev0 = (active && cu0.token == 0) ? static_cast<const float*>(a.state.base)[a.state.index(c, 0, cu0.batch)] : 0.f;
-    __syncthreads();
-    if (!active) return true;
-    for (uint32_t t = 0; t < T; ++t) {
-        float acc = 0.f;
-        const __half* xv = s_tmx + (size_t)t * 5 * D + i * D;
-#pragma unroll
-        for (uint32_t j = 0; j < 8; ++j) {
-            if (j >= D / 8) break;
-            const __half2* w2 = reinterpret_cast<const __half2*>(&wreg[j]);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 wf = __half22float2(w2[e]);
-                acc = fmaf(wf.x, __half2float(xv[j * 8 + 2 * e]), acc);
-                acc = fmaf(wf.y, __half2float(xv[j * 8 + 2 * e + 1]), acc);
-            }
-        }
-        // time_mix buffer is fp16: matmul result rounded, then the static mix added and rounded again
-        const float f = __half2float(__float2half_rn(__half2float(__float2half_rn(acc)) + mu));
-        float cur, prev;
-        if (t == 0) {
-            cur = cur0;
-            prev = prev0;
-        } else {
-            const CursorD cu = cursor_at(a.cursors, a.wide, t);
-            cur = __half2float(a.att_x[(size_t)t * C + c]);
-            prev = (t == cu.token) ? static_cast<const float*>(a.state.base)[a.state.index(c, 0, cu.batch)]
-                                   : __half2float(a.att_x[(size_t)(t - 1) * C + c]);
-        }
-        a.sx[((size_t)i * T + t) * C + c] = __float2half_rn(cur * (1.0f - f) + prev * f);
-    }
-    return true;
-}
-
-// ---- v5 / v6 time-mix block: decay adapter, WKV, group norm, gate ------------------------------------------
-// A (head, sequence) pair is worked by 4 * S = 256 threads of a CTA: thread (q, j) owns rows [q S/4, (q+1) S/4) of
-// state column j, a quarter of the decay-adapter dot product of channel j and a quarter of output j's sum.  Pairs
-// are spread over the CTAs (every fourth SM or so at 64 heads), so each state column is fetched by its own SM.
-struct WkvStatic {
-    uint4 w2reg[4];
-    float td_static, td5, u, gw, gb;
-    float st[16];
-};
-__device__ __forceinline__ void wkv_load(const Wkv6Args& a, uint32_t h, uint32_t slot, uint32_t j, uint32_t q, WkvStatic& r) {
-    constexpr int S = 64, SI = 16;
-    const uint32_t c = h * S + j;
-    const uint32_t dq = a.D / 4;
-    r.td_static = r.td5 = 0.f;
-    if (a.per_token_decay) {
-        const uint4* wp = reinterpret_cast<const uint4*>(a.td_w2 + (size_t)c * a.D + q * dq);
-#pragma unroll
-        for (uint32_t e = 0; e < 4; ++e)
-            if (e < dq / 8) r.w2reg[e] = wp[e];
-        r.td_static = __half2float(a.td0[c]);
-    } else {
-        r.td5 = a.td5[c];
-    }
-    r.u = a.time_first[c];
-    r.gw = __half2float(a.gn_w[c]);
-    r.gb = __half2float(a.gn_b[c]);
-    // within a job only this phase writes the WKV rows of its layer
-#pragma unroll
-    for (int i = 0; i < SI; ++i) r.st[i] = static_cast<const float*>(a.state.base)[a.state.index(c, 1 + q * SI + i, slot)];
-}
-
-__device__ __forceinline__ void wkv_pair(const Wkv6Args& a, uint32_t h, uint32_t slot, uint32_t start, uint32_t count, WkvStatic& r, float* fs,
-                         __half* s_tdw) {
-    constexpr int S = 64, Q = 4, SI = S / Q;
-    float* sk = fs;
-    float* sr = fs + S;
-    float* sw = fs + 2 * S;
-    float* su = fs + 3 * S;
-    float* part = fs + 4 * S;     // [Q][S]
-    float* red = fs + 8 * S;      // [Q * S / 32]
-    const uint32_t j = threadIdx.x % S, q = threadIdx.x / S;
-    const uint32_t C = S * a.H, c = h * S + j;
-    const uint32_t dq = a.D / Q;
-    if (q == 0) su[j] = r.u;
-    for (uint32_t n = 0; n < count; ++n) {
-        const uint32_t t = start + n;
-        const size_t ti = (size_t)t * C + c;
-        // all of the token's inputs go in flight together
-        const float kj = a.k[ti], rj = a.r[ti], vj = a.v[ti];
-        const float gg = __half2float(a.g[ti]), ax = __half2float(a.att_x[ti]);
-        __half tdh = __float2half_rn(0.f);
-        if (a.per_token_decay && threadIdx.x < a.D) tdh = a.tdw[(size_t)t * a.D + threadIdx.x];
-        const CursorD cu = cursor_at(a.cursors, a.wide, t);
-        bar_sync_256();  // the previous token's readers are done
-        if (q == 0) {
-            sk[j] = kj;
-            sr[j] = rj;
-        }
-        if (a.per_token_decay && threadIdx.x < a.D) s_tdw[threadIdx.x] = tdh;
-        bar_sync_256();
-        if (a.per_token_decay) {
-            float acc = 0.f;
-            const __half* xv = s_tdw + q * dq;
-#pragma unroll
-            for (uint32_t e = 0; e < 4; ++e) {
-                if (e >= dq / 8) break;
-                const __half2* w2 = reinterpret_cast<const __half2*>(&r.w2reg[e]);
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const float2 wf = __half22float2(w2[u]);
-                    acc = fmaf(wf.x, __half2float(xv[e * 8 + 2 * u]), acc);
-                    acc = fmaf(wf.y, __half2float(xv[e * 8 + 2 * u + 1]), acc);
-                }
-            }
-            part[q * S + j] = acc;
-            bar_sync_256();
-            // time_decay buffer is f32: no rounding before the activation
-            if (q == 0)
-                sw[j] = expf(-expf(((part[j] + part[S + j]) + (part[2 * S + j] + part[3 * S + j])) + r.td_static));
-        } else if (q == 0) {
-            sw[j] = r.td5;
-        }
-        bar_sync_256();
-        float y0 = 0.f, y1 = 0.f;
-#pragma unroll
-        for (int ii = 0; ii < SI; ii += 2) {
-            const int i = q * SI + ii;
-            float kv;
-            kv = sk[i] * vj;     y0 += sr[i] * fmaf(su[i], kv, r.st[ii]);             r.st[ii] = fmaf(sw[i], r.st[ii], kv);
-            kv = sk[i + 1] * vj; y1 += sr[i + 1] * fmaf(su[i + 1], kv, r.st[ii + 1]); r.st[ii + 1] = fmaf(sw[i + 1], r.st[ii + 1], kv);
-        }
-        bar_sync_256();  // the adapter sums in part[] have been read
-        part[q * S + j] = y0 + y1;
-        if (q == 0 && t - cu.token + 1u == cu.len) static_cast<float*>(a.state.base)[a.state.index(c, 0, slot)] = ax;
-        bar_sync_256();
-        const float y = (part[j] + part[S + j]) + (part[2 * S + j] + part[3 * S + j]);
-        // group norm over the head's S outputs (f32 buffer in the reference), then fp16, then the gate;
-        // every quarter repeats it on the same values, quarter 0 stores
-        const uint32_t wbase = q * (S / 32);
-        float sm = warp_sum(y);
-        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sm;
-        bar_sync_256();
-        float tot = 0.f;
-        for (int w = 0; w < S / 32; ++w) tot += red[wbase + w];
-        const float mean = tot / (float)S;
-        const float dlt = y - mean;
-        bar_sync_256();
-        sm = warp_sum(dlt * dlt);
-        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sm;
-        bar_sync_256();
-        tot = 0.f;
-        for (int w = 0; w < S / 32; ++w) tot += red[wbase + w];
-        const float dev = rsqrtf(tot / (float)S + a.gn_eps);
-        const float gn16 = __half2float(__float2half_rn(fmaf(dlt * dev, r.gw, r.gb)));
-        const float silu = gg / (1.0f + expf(-gg));
-        if (q == 0) a.out[ti] = __float2half_rn(silu * gn16);
-    }
-#pragma unroll
-    for (int i = 0; i < SI; ++i) static_cast<float*>(a.state.base)[a.state.index(c, 1 + q * SI + i, slot)] = r.st[i];
-    bar_sync_256();  // the arrays are reused by the CTA's next pair
-}
-
-__device__ __noinline__ bool wkv_phase(Step& st, const Wkv6Args& a) {
-    constexpr int S = 64;
-    // the sequences of the job's tokens: (slot, first token, count), in token order (cursors are uploaded before
-    // the launch; no phase writes them)
-    uint32_t* runs = reinterpret_cast<uint32_t*>(st.xs);           // [3 * kDecodeMaxTokens + 1]
-    float* fs = reinterpret_cast<float*>(st.xs) + 32;               // 8 * S + 8 floats
-    __half* s_tdw = reinterpret_cast<__half*>(fs + 8 * S + 8);      // 128 halfs
-    if (threadIdx.x == 0) {
-        uint32_t n = 0;
-        for (uint32_t t = 0; t < a.T;) {
-            const CursorD cu = cursor_at(a.cursors, a.wide, t);
-            uint32_t e = t + 1;
-            while (e < a.T && cursor_at(a.cursors, a.wide, e).batch == cu.batch) ++e;
-            runs[3 * n] = cu.batch;
-            runs[3 * n + 1] = t;
-            runs[3 * n + 2] = e - t;
-            ++n;
-            t = e;
-        }
-        runs[3 * kDecodeMaxTokens] = n;
-    }
-    __syncthreads();
-    const uint32_t npairs = runs[3 * kDecodeMaxTokens] * a.H;
-    // pairs are spread over the grid: with fewer pairs than CTAs, pair p sits on CTA floor(p * grid / npairs)
-    uint32_t first = 0xffffffffu, stride = gridDim.x;
-    if (npairs <= gridDim.x) {
-        const uint32_t p = (blockIdx.x * npairs + gridDim.x - 1) / gridDim.x;
-        if (p < npairs && p * gridDim.x / npairs == blockIdx.x) first = p;
-        stride = npairs;  // one pair at most
-    } else {
-        first = blockIdx.x;
-    }
-    const bool worker = threadIdx.x < 4 * S;
-    const uint32_t j = threadIdx.x % S, q = (threadIdx.x / S) & 3;
-    WkvStatic regs;
-    if (worker && first < npairs) wkv_load(a, first % a.H, runs[3 * (first / a.H)], j, q, regs);
-    if (!st.wait_grid()) return false;
-    if (!worker) return true;
-    for (uint32_t p = first; p < npairs; p += stride) {
-        const uint32_t run = p / a.H, h = p % a.H;
-        if (p != first) wkv_load(a, h, runs[3 * run], j, q, regs);
-        wkv_pair(a, h, runs[3 * run], runs[3 * run + 1], runs[3 * run + 2], regs, fs, s_tdw);
-    }
-    return true;
+    return xv;
 }
 
 __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const StepArgs s) {
@@ -505,22 +223,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const StepArgs
     __shared__ __align__(8) uint64_t work_bar;
     __shared__ int abort_flag;
 
-    Step st(s);
-    st.warp = threadIdx.x >> 5;
-    st.lane = threadIdx.x & 31;
-    st.abort_flag = &abort_flag;
-    st.phase = 0;
-    st.scratch = scratch;
-    st.lut2 = lut2;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t T = s.T;
     const int depth = s.ring_depth;
     const uint32_t work_bytes = ((uint32_t)s.num_gemv * (uint32_t)sizeof(StepWork) + 127u) / 128u * 128u;
-    st.work = reinterpret_cast<StepWork*>(smem);
+    StepWork* work = reinterpret_cast<StepWork*>(smem);
     uint8_t* ring0 = smem + work_bytes;
-    st.ring = ring0 + (size_t)st.warp * depth * CELL_BYTES;
-    st.part = reinterpret_cast<float*>(ring0 + (size_t)kWarps * depth * CELL_BYTES);
-    st.sums = st.part + kWarps * GROUP_ROWS * T;
-    st.xs = reinterpret_cast<__half*>(st.sums + sums_floats(T, s.kmax));
+    GemvShared sm;
+    sm.ring = ring0 + (size_t)warp * depth * CELL_BYTES;
+    sm.part = reinterpret_cast<float*>(ring0 + (size_t)kWarps * depth * CELL_BYTES);
+    sm.sums = sm.part + kWarps * GROUP_ROWS * T;
+    sm.xs = reinterpret_cast<__half*>(sm.sums + sums_floats(T, s.kmax));
+    sm.scratch = scratch;
+    sm.lut2 = lut2;
+    sm.depth = depth;
+    GridSync gs{s.barrier, s.status, s.timeline, &abort_flag, 0};
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -531,7 +248,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const StepArgs
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         if (s.num_gemv > 0) {
             mbar_expect_tx(&work_bar, (uint32_t)s.num_gemv * (uint32_t)sizeof(StepWork));
-            bulk_load(st.work, s.work + (size_t)blockIdx.x * s.num_gemv, (uint32_t)s.num_gemv * (uint32_t)sizeof(StepWork), &work_bar);
+            bulk_load(work, s.work + (size_t)blockIdx.x * s.num_gemv, (uint32_t)s.num_gemv * (uint32_t)sizeof(StepWork), &work_bar);
         }
         for (int i = 0; i < 2 && i < s.num_phases; ++i) {
             mbar_expect_tx(&desc_bar[i], (uint32_t)sizeof(StepPhase));
@@ -560,20 +277,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const StepArgs
     alive = abort_flag == 0;
     if (alive && s.num_gemv > 0)
         for (uint32_t polls = 0; polls < 1024 && !mbar_try_wait(&work_bar, 0); ++polls) {}
-    st.ld.entry = 0;
-    st.ld.count = alive ? s.num_gemv : 0;
-    st.ld.work = st.work;
-    st.ld.enter(st.warp, st.lane);
-    st.cs_slot = 0;
+    StepLoader ld;
+    ld.entry = 0;
+    ld.count = alive ? s.num_gemv : 0;
+    ld.work = work;
+    ld.enter(warp, lane);
+    int cs_slot = 0;
 #pragma unroll 1
     for (int d = 0; d < depth; ++d) {
-        st.ld.issue(st.ring + d * CELL_BYTES, st.warp, st.lane);
+        ld.issue(sm.ring + d * CELL_BYTES, warp, lane);
         cp_async_commit();  // one group per cell, empty or not
     }
 
 #pragma unroll 1
     for (int ph = 0; alive && ph < s.num_phases; ++ph) {
-        st.phase = ph;
+        gs.phase = ph;
         // the phase's descriptor has landed: one thread waits (bounded), the others follow it through a barrier
         // and then observe the completed phase of the mbarrier themselves
         if (threadIdx.x == 0) {
@@ -593,22 +311,23 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const StepArgs
         if (d.type == PH_GEMV) {
             const GemvCore& a = d.gemv;
             StepWork wk{};
-            if (d.gemv_index >= 0) wk = st.work[d.gemv_index];
-            const int pe = a.prologue * 4 + a.epilogue;
-            if (pe == PRO_NONE * 4 + EPI_STORE) alive = gemv_phase<PRO_NONE, EPI_STORE>(st, a, wk);
-            else if (pe == PRO_NONE * 4 + EPI_RESIDUAL) alive = gemv_phase<PRO_NONE, EPI_RESIDUAL>(st, a, wk);
-            else if (pe == PRO_NONE * 4 + EPI_CHANNEL_MIX) alive = gemv_phase<PRO_NONE, EPI_CHANNEL_MIX>(st, a, wk);
-            else if (pe == PRO_LN * 4 + EPI_STORE) alive = gemv_phase<PRO_LN, EPI_STORE>(st, a, wk);
-            else if (pe == PRO_LN_SHIFT1 * 4 + EPI_STORE) alive = gemv_phase<PRO_LN_SHIFT1, EPI_STORE>(st, a, wk);
-            else alive = gemv_phase<PRO_LN_SHIFT2, EPI_STORE>(st, a, wk);
+            if (d.gemv_index >= 0) wk = work[d.gemv_index];
+            const __half* xv = stage_activations(gs, sm, a, wk, &alive);
+            if (alive && xv != nullptr) {
+                const GemvProblem& p = a.p[wk.problem];
+                const uint32_t xp = (a.prologue != PRO_NONE ? a.C : a.kmax) + 8;
+                if (wk.kind == MAT_INT8) stream_rows<MAT_INT8>(sm, a, p, a.epilogue, wk.K, wk.r0, wk.r1, xv, xp, ld, cs_slot, warp, lane);
+                else if (wk.kind == MAT_NF4) stream_rows<MAT_NF4>(sm, a, p, a.epilogue, wk.K, wk.r0, wk.r1, xv, xp, ld, cs_slot, warp, lane);
+                else stream_rows<MAT_FP16>(sm, a, p, a.epilogue, wk.K, wk.r0, wk.r1, xv, xp, ld, cs_slot, warp, lane);
+            }
         } else if (d.type == PH_TMIX) {
-            alive = tmix_phase(st, d.tmix);
+            alive = tmix_phase(gs, d.tmix, sm.xs);
         } else {
-            alive = wkv_phase(st, d.wkv);
+            alive = wkv_phase(gs, d.wkv, sm.xs);
         }
         if (!alive) break;
         if (ph + 1 < s.num_phases) {
-            st.arrive_grid();
+            gs.arrive();
             // desc[ph & 1] is free (every thread is past the phase): fetch the descriptor two phases ahead
             if (threadIdx.x == 0 && ph + 2 < s.num_phases) {
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -616,7 +335,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const StepArgs
                 bulk_load(&desc[ph & 1], s.phases + ph + 2, (uint32_t)sizeof(StepPhase), &desc_bar[ph & 1]);
             }
         } else {
-            st.stamp(1);
+            gs.stamp(1);
         }
     }
     cp_async_wait<0>();  // nothing of this CTA is in flight when it leaves

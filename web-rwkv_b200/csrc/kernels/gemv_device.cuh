@@ -6,6 +6,12 @@
 #include "decode.cuh"
 #include "device.cuh"
 
+// Barrier over the kThreads compute threads of a CTA.  A kernel that carries extra warps outside the compute
+// group (a producer warp that never joins) defines it as a named barrier of kThreads threads before including this.
+#ifndef WRK_CTA_SYNC
+#define WRK_CTA_SYNC() __syncthreads()
+#endif
+
 namespace wrk {
 namespace k {
 namespace {
@@ -223,7 +229,7 @@ __device__ __forceinline__ Item read_item(const uint8_t* cell, int lane) {
 __device__ __forceinline__ float block_sum_256(float v, float* scratch) {
     v = warp_sum(v);
     if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-    __syncthreads();
+    WRK_CTA_SYNC();
     float s = 0.f;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) s += scratch[w];
@@ -363,7 +369,7 @@ __device__ void run_prologue(const GemvCore& a, __half* xgen, uint32_t xp, __hal
             }
         }
     }
-    __syncthreads();
+    WRK_CTA_SYNC();
 }
 
 // Operands of the launch's epilogue for one output, fetched before the weights are multiplied so that

@@ -47,7 +47,8 @@ struct wrk_bundle {
     uint32_t num_batch = 0;
     std::vector<TensorH> state;  // per layer f32 [C, S + 2, num_batch]
     bool packed_cursors = false, use_graph = true, fused = true;
-    bool step_kernel = true;  // fused jobs run as one persistent kernel where the job shape allows it
+    bool step_kernel = false;  // fused jobs of at most 8 tokens run as one persistent kernel where the job shape allows it
+    int step_engine = 1;      // 1: tensor-core kernel where the matrices allow it; 3: always the mma.sync kernel
     TensorH timeline;         // optional globaltimer stamps of the step kernel: [2 * timeline_phases][num_sms] u64
     size_t timeline_phases = 0;
     std::map<uint32_t, std::shared_ptr<Buffers>> buffers, headers;
@@ -471,11 +472,18 @@ bool fused_v6_supported(wrk_bundle* bd, uint32_t T) {
 
 // The phases of a job that runs as one persistent kernel (kernels/decode_step.cu), collected while the
 // fused layers are emitted.
+struct StepRange {
+    const uint8_t* w;
+    const __half* scale;
+    int32_t r0, r1;
+    uint32_t K, M;
+    int16_t kind, problem;
+};
 struct StepBuilder {
     std::vector<k::StepPhase> phases;
-    std::vector<std::vector<k::StepWork>> work;  // [gemv phase][cta]
-    uint32_t kmax = 0;
-    bool any_prologue = false;
+    std::vector<std::vector<StepRange>> work;  // [gemv phase][cta]
+    uint32_t kmax = 0, kmax_int8 = 0, kmax_fp16 = 0;
+    bool any_prologue = false, has_nf4 = false, umma_shapes = true;
     const float* table = nullptr;
 };
 
@@ -510,9 +518,9 @@ int32_t emit_gemv(FusedSink& sink, k::FusedGemvArgs a, const char* name, std::in
         std::vector<k::GemvSegment> table;
         WRK_REQUIRE(k::fused_gemv_partition(a, grid, table), WRK_ERR_UNSUPPORTED,
                     "row partition overflow: too many small matrices per CTA");
-        std::vector<k::StepWork> work(grid);
+        std::vector<StepRange> work(grid);
         for (int c = 0; c < grid; ++c) {
-            k::StepWork wk{};
+            StepRange wk{};
             int used = 0;
             for (int i = 0; i < k::kSegmentsPerCta; ++i) {
                 const k::GemvSegment& sg = table[(size_t)c * k::kSegmentsPerCta + i];
@@ -523,12 +531,24 @@ int32_t emit_gemv(FusedSink& sink, k::FusedGemvArgs a, const char* name, std::in
                 wk.r0 = sg.row0;
                 wk.r1 = sg.row1;
                 wk.K = p.K;
+                wk.M = p.M;
                 wk.kind = (int16_t)p.kind;
                 wk.problem = (int16_t)sg.problem;
                 ++used;
             }
             WRK_REQUIRE(used <= 1, WRK_ERR_UNSUPPORTED, "a CTA of the step kernel takes one row range per phase");
             work[c] = wk;
+        }
+        for (int i = 0; i < a.num_problems; ++i) {
+            const k::GemvProblem& p = a.p[i];
+            if (p.kind == k::MAT_NF4) sb.has_nf4 = true;
+            if (p.kind == k::MAT_INT8) sb.kmax_int8 = std::max(sb.kmax_int8, p.K);
+            if (p.kind == k::MAT_FP16) sb.kmax_fp16 = std::max(sb.kmax_fp16, p.K);
+            // tensor-core path: whole 128-byte blocks per row (fp16: four per stage of a packed tile), 16-byte
+            // aligned rows and inputs
+            const uint32_t unit = p.kind == k::MAT_INT8 ? 128 : 256;
+            if (p.K % unit != 0 || reinterpret_cast<uintptr_t>(p.w) % 16 != 0 || (p.x != nullptr && (p.x_stride % 8 != 0 || reinterpret_cast<uintptr_t>(p.x) % 16 != 0)))
+                sb.umma_shapes = false;
         }
         ph.gemv_index = (int32_t)sb.work.size();
         sb.work.push_back(std::move(work));
@@ -762,20 +782,6 @@ int32_t build_step_job(wrk_bundle* bd, CachedJob* job, OpList& ops) {
         a.rescale = 1.0f;
         WRK_TRY(emit_gemv(sink, a, "step_head", {}));
     }
-    k::StepArgs s{};
-    s.num_phases = (int32_t)sb.phases.size();
-    s.num_gemv = (int32_t)sb.work.size();
-    s.T = T;
-    s.kmax = std::max(sb.kmax, C);
-    s.C = C;
-    s.table = sb.table;
-    s.status = ctx->device_status;
-    WRK_REQUIRE(k::decode_step_prepare(s, sb.any_prologue) != 0, WRK_ERR_UNSUPPORTED,
-                "job of %u tokens does not fit the step kernel's shared memory", T);
-    // phase list, work lists ([cta][phase]) and the barrier word live as long as the job
-    std::vector<k::StepWork> flat((size_t)grid * sb.work.size());
-    for (size_t g = 0; g < sb.work.size(); ++g)
-        for (int c = 0; c < grid; ++c) flat[(size_t)c * sb.work.size() + g] = sb.work[g][c];
     auto upload = [&](const void* data, size_t bytes, wrk_tensor** out) -> int32_t {
         const uint32_t shape[4] = {(uint32_t)((bytes + 3) / 4), 1, 1, 1};
         WRK_TRY(wrk_tensor_from_data(ctx, WRK_U32, shape, data, bytes, out));
@@ -784,15 +790,97 @@ int32_t build_step_job(wrk_bundle* bd, CachedJob* job, OpList& ops) {
     };
     wrk_tensor *t_phases = nullptr, *t_work = nullptr, *t_bar = nullptr;
     WRK_TRY(upload(sb.phases.data(), sb.phases.size() * sizeof(k::StepPhase), &t_phases));
-    WRK_TRY(upload(flat.data(), flat.size() * sizeof(k::StepWork), &t_work));
     const uint32_t zero[4] = {0, 0, 0, 0};
     WRK_TRY(upload(zero, sizeof zero, &t_bar));
+    unsigned long long* timeline = nullptr;
+    if (bd->timeline_phases >= sb.phases.size() && bd->timeline.p != nullptr)
+        timeline = static_cast<unsigned long long*>(bd->timeline.p->ptr());
+    job->num_phases = (uint32_t)sb.phases.size();
+    const size_t ng = sb.work.size();
+
+    // Int8 / fp16 matrices and at most two tokens: the tensor-core kernel (TMA boxes + tcgen05)
+    if (bd->step_engine != 3 && !sb.has_nf4 && sb.umma_shapes && T <= 2) {
+        k::UmmaStepArgs u{};
+        u.num_phases = (int32_t)sb.phases.size();
+        u.num_gemv = (int32_t)ng;
+        u.T = T;
+        u.C = C;
+        u.status = ctx->device_status;
+        // the activation operand of a phase sits in front of the prologue's rows (T normalised, up to 2 T shifted,
+        // one of bias; pitch C + 8), which only phases with a prologue use
+        const uint32_t x_bytes = sb.any_prologue ? (uint32_t)(((size_t)(3 * T + 1) * (C + 8) * 2 + 127) / 128 * 128) : 0;
+        uint32_t operand = 0;
+        for (const auto& ph : sb.phases) {
+            if (ph.type != k::PH_GEMV || ph.gemv_index < 0) continue;
+            const uint32_t tail = ph.gemv.prologue != k::PRO_NONE ? x_bytes : 0;
+            for (int c = 0; c < grid; ++c) {
+                const StepRange& r = sb.work[ph.gemv_index][c];
+                operand = std::max(operand, k::umma_operand_bytes(r.r1 - r.r0, r.kind, r.K, ph.gemv.T) + tail);
+            }
+        }
+        operand = std::max(operand, x_bytes);
+        if (k::decode_step_umma_prepare(u, operand, x_bytes, sb.kmax_int8) != 0) {
+            // phases whose prologue the kernel runs in registers (one token, a row of at most 4096 values): ranges of
+            // one or two rows of an fp16 matrix are multiplied there as well and never staged
+            std::vector<bool> direct_phase(ng, false);
+            for (const auto& ph : sb.phases)
+                if (ph.type == k::PH_GEMV && ph.gemv_index >= 0 && ph.gemv.prologue != k::PRO_NONE && ph.gemv.T == 1 && C % 128 == 0 && C <= 4096)
+                    direct_phase[ph.gemv_index] = true;
+            std::vector<k::UmmaWork> flat((size_t)grid * ng);
+            for (size_t g = 0; g < ng; ++g)
+                for (int c = 0; c < grid; ++c) {
+                    const StepRange& r = sb.work[g][c];
+                    k::UmmaWork& wk = flat[(size_t)c * ng + g];
+                    std::memset(&wk, 0, sizeof wk);
+                    wk.direct = direct_phase[g] && r.kind == k::MAT_FP16 && r.K == C && r.r1 - r.r0 >= 1 && r.r1 - r.r0 <= 2 ? 1 : 0;
+                    wk.w = r.w;
+                    wk.scale = r.scale;
+                    wk.r0 = r.r0;
+                    wk.r1 = r.r1;
+                    wk.K = r.K;
+                    wk.kind = r.kind;
+                    wk.problem = r.problem;
+                }
+            WRK_TRY(upload(flat.data(), std::max<size_t>(flat.size(), 1) * sizeof(k::UmmaWork), &t_work));
+            u.phases = static_cast<const k::StepPhase*>(t_phases->ptr());
+            u.work = static_cast<const k::UmmaWork*>(t_work->ptr());
+            u.barrier = static_cast<uint32_t*>(t_bar->ptr());
+            u.timeline = timeline;
+            ops.ops.push_back(new_atom("decode_step_umma", [u, grid](cudaStream_t st) { return k::decode_step_umma(u, grid, st); },
+                                       {B["input"], B["x"], t_phases, t_work, t_bar}));
+            return WRK_OK;
+        }
+    }
+
+    k::StepArgs s{};
+    s.num_phases = (int32_t)sb.phases.size();
+    s.num_gemv = (int32_t)ng;
+    s.T = T;
+    s.kmax = std::max(sb.kmax, C);
+    s.C = C;
+    s.table = sb.table;
+    s.status = ctx->device_status;
+    WRK_REQUIRE(k::decode_step_prepare(s, sb.any_prologue) != 0, WRK_ERR_UNSUPPORTED,
+                "job of %u tokens does not fit the step kernel's shared memory", T);
+    // work lists ([cta][phase]) live as long as the job
+    std::vector<k::StepWork> flat((size_t)grid * ng);
+    for (size_t g = 0; g < ng; ++g)
+        for (int c = 0; c < grid; ++c) {
+            const StepRange& r = sb.work[g][c];
+            k::StepWork& wk = flat[(size_t)c * ng + g];
+            wk.w = r.w;
+            wk.scale = r.scale;
+            wk.r0 = r.r0;
+            wk.r1 = r.r1;
+            wk.K = r.K;
+            wk.kind = r.kind;
+            wk.problem = r.problem;
+        }
+    WRK_TRY(upload(flat.data(), std::max<size_t>(flat.size(), 1) * sizeof(k::StepWork), &t_work));
     s.phases = static_cast<const k::StepPhase*>(t_phases->ptr());
     s.work = static_cast<const k::StepWork*>(t_work->ptr());
     s.barrier = static_cast<uint32_t*>(t_bar->ptr());
-    if (bd->timeline_phases >= sb.phases.size() && bd->timeline.p != nullptr)
-        s.timeline = static_cast<unsigned long long*>(bd->timeline.p->ptr());
-    job->num_phases = (uint32_t)sb.phases.size();
+    s.timeline = timeline;
     ops.ops.push_back(new_atom("decode_step", [s, grid](cudaStream_t st) { return k::decode_step(s, grid, st); },
                                {B["input"], B["x"], t_phases, t_work, t_bar}));
     return WRK_OK;
@@ -951,10 +1039,11 @@ int32_t wrk_bundle_set_use_graph(wrk_bundle* b, int32_t use_graph) {
 
 int32_t wrk_bundle_set_fused(wrk_bundle* b, int32_t fused) {
     WRK_REQUIRE(b, WRK_ERR_INVALID_ARGUMENT, "null argument");
-    WRK_REQUIRE(fused >= 0 && fused <= 2, WRK_ERR_INVALID_ARGUMENT, "fused mode %d: 0, 1 or 2", fused);
-    if (b->fused != (fused != 0) || b->step_kernel != (fused == 1)) drop_caches(b);
+    WRK_REQUIRE(fused >= 0 && fused <= 3, WRK_ERR_INVALID_ARGUMENT, "fused mode %d: 0, 1, 2 or 3", fused);
+    drop_caches(b);
     b->fused = fused != 0;
-    b->step_kernel = fused == 1;
+    b->step_kernel = fused == 1 || fused == 3;
+    b->step_engine = fused == 3 ? 3 : 1;
     return WRK_OK;
 }
 

@@ -93,6 +93,17 @@ class Model:
             lib().wrk_model_release(self.handle)
             self.handle = None
 
+    def save(self, path):
+        """Serialize for Model (src/tensor/serialization.rs:11-75; examples/serde.rs:218-268): one CBOR file."""
+        check(lib().wrk_model_save(self.handle, str(path).encode()))
+
+    @classmethod
+    def load(cls, ctx, path):
+        """Seed::<Context, Model>::deserialize (src/tensor/serialization.rs:96-159)."""
+        h = ctypes.c_void_p()
+        check(lib().wrk_model_load(ctx.handle, str(path).encode(), ctypes.byref(h)))
+        return cls(ctx, h)
+
     @property
     def info(self):
         info = ModelInfo()
@@ -215,8 +226,8 @@ class Bundle:
         check(lib().wrk_bundle_set_use_graph(self.handle, int(use)))
 
     def set_fused(self, fused):
-        """0 / False: one launch per reference op; 1 / True: fused kernels, small v6 jobs as one persistent kernel;
-        2: fused kernels, one launch per phase."""
+        """0: one launch per reference op; 2 (the default of a new bundle): fused kernels, one launch per phase;
+        1: fused kernels, v6 jobs of at most 8 tokens as one persistent kernel; 3: as 1, mma.sync engine only."""
         check(lib().wrk_bundle_set_fused(self.handle, int(fused)))
 
     def set_phase_timeline(self, max_phases):
