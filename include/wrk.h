@@ -268,7 +268,15 @@ int32_t wrk_matrix_quant_sf4(wrk_tensor* matrix, double nu, wrk_matrix** out);
 typedef struct wrk_comm wrk_comm;
 int32_t wrk_comm_unique_id(uint8_t id[128]);
 int32_t wrk_comm_create(wrk_context* ctx, const uint8_t id[128], int32_t rank, int32_t world, wrk_comm** out);
+int32_t wrk_comm_retain(wrk_comm* comm);
 int32_t wrk_comm_release(wrk_comm* comm);
+/* The host-side wait of a rank of a split job: waits for everything submitted to the communicator's context, polling
+ * ncclCommGetAsyncError; after timeout_ms, or on an asynchronous NCCL error, aborts the communicator (its kernels leave
+ * the device, the context stays usable) and returns WRK_ERR_TIMEOUT / WRK_ERR_NCCL. */
+int32_t wrk_comm_wait(wrk_comm* comm, uint32_t timeout_ms);
+/* The loop under wrk_comm_wait with its two questions passed in: ends WRK_OK when done(user) is non-zero, WRK_ERR_NCCL
+ * when failure(user) is (may be null), WRK_ERR_TIMEOUT after timeout_ms; polls every poll_us microseconds. */
+int32_t wrk_watchdog_wait(int32_t (*done)(void*), int32_t (*failure)(void*), void* user, uint32_t timeout_ms, uint32_t poll_us);
 int32_t wrk_comm_rank(const wrk_comm* comm, int32_t* rank, int32_t* world);
 /* x <- sum over ranks of x, in place (f16 or f32). */
 int32_t wrk_op_all_reduce(wrk_comm* comm, wrk_tensor* x, wrk_op** out);

@@ -52,6 +52,15 @@ int32_t wrk_model_builder_lora(wrk_model_builder* b, uint32_t* index);
 int32_t wrk_model_builder_lora_tensor(wrk_model_builder* b, uint32_t index, const char* name, const uint64_t* shape,
                                       uint32_t ndim, const void* data_f16, size_t bytes);
 int32_t wrk_model_builder_lora_blend(wrk_model_builder* b, uint32_t index, const char* pattern, float alpha);
+/* No counterpart in the reference (one GPU).  Makes the builder keep one rank's part of a model split `world` ways:
+ * call before the first tensor; every tensor is cut as it is added.  Time-mix channels are split by whole heads
+ * (key / value / receptance / gate and the per-channel adapters' second matrices keep the rank's rows, `output` the
+ * matching columns), ffn `key` by rows and `value` by the matching columns, the head by vocabulary rows; everything
+ * else is held whole.  Splits of a K dimension fall on multiples of `block` (128 when any layer is Int8, 64 for
+ * NF4 / SF4, 1 for fp16), so a rank's packed bytes and scales equal the matching slice of the whole model's.
+ * wrk_shard_range is the rule: `world` contiguous ranges of whole `align` units, sizes within one unit, larger first. */
+int32_t wrk_model_builder_shard(wrk_model_builder* b, uint32_t rank, uint32_t world, uint32_t head_size, uint32_t block);
+int32_t wrk_shard_range(uint32_t total, uint32_t align, uint32_t world, uint32_t rank, uint32_t* begin, uint32_t* end);
 int32_t wrk_model_builder_quant(wrk_model_builder* b, uint32_t layer, int32_t quant); /* ModelBuilder::quant */
 int32_t wrk_model_builder_rescale(wrk_model_builder* b, uint32_t value);             /* ModelBuilder::rescale */
 int32_t wrk_model_builder_sep(wrk_model_builder* b, uint32_t value);                 /* ModelBuilder::sep */
@@ -81,6 +90,12 @@ int32_t wrk_model_matrix(wrk_model* m, uint32_t layer, const char* name, wrk_mat
 
 /* ---- Bundle + State (src/runtime/model.rs:78-120, src/runtime/v6.rs:142-266, 499-521) ---- */
 int32_t wrk_bundle_create(wrk_model* model, uint32_t num_batch, wrk_bundle** out); /* Bundle::<f16>::new */
+/* The bundle of one rank of a split model (wrk_model_builder_shard): the op list of the reference's dispatch_layer
+ * (src/runtime/v5.rs:656-885, v6.rs:701-958, v7.rs:716-1007) with the time-mix ops on the rank's heads, `output` and
+ * ffn `value` producing f32 partial sums that one all-reduce per sub-block adds across the ranks, and the rank's
+ * vocabulary rows gathered into full logits.  Every rank submits the same jobs in the same order.  State rows of
+ * heads the rank does not own stay zero (wrk_state_back returns them so). */
+int32_t wrk_bundle_create_sharded(wrk_model* model, uint32_t num_batch, wrk_comm* comm, wrk_bundle** out);
 int32_t wrk_bundle_release(wrk_bundle* b);
 /* Cursor format uploaded with every job: 0 (default) = three u32 per token, exact for any run length;
  * 1 = the reference's packed u32 (8-bit batch, 16-bit token, 8-bit len: src/tensor/mod.rs:53-60). */

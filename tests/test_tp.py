@@ -1,5 +1,6 @@
-"""Tensor-parallel sharding: shard plan (host logic), the sharding rules against the CPU oracle with two gloo
-ranks, and — where two GPUs are present — the sharded v6 job against the single-GPU runtime."""
+"""A model split across GPUs: shard plan (host logic), the sharding rules against the CPU oracle with two gloo
+ranks, the host-side wait that gives up on a missing peer, and — where two GPUs are present — the sharded v5 / v6 /
+v7 bundles of the C library against the whole model on one GPU."""
 import importlib
 import os
 import subprocess
@@ -75,8 +76,29 @@ def test_sharding_rules_two_gloo_ranks_cpu_oracle():
     _spawn("cpu", 2, free_port())
 
 
+def test_wait_gives_up_when_a_peer_skips_a_collective():
+    # failure injected on the host: gloo ranks on CPU, no GPU involved
+    outs = _spawn("watchdog", 2, free_port())
+    assert "peer skipped a collective" in outs[0]
+
+
+def test_watchdog_loop_answers():
+    import ctypes
+    wrk = importlib.import_module("web-rwkv_b200")
+    lib = wrk.lib()
+    CB = ctypes.CFUNCTYPE(ctypes.c_int32, ctypes.c_void_p)
+    calls = []
+    done = CB(lambda _: calls.append(1) or (1 if len(calls) >= 3 else 0))
+    assert lib.wrk_watchdog_wait(done, None, None, 5000, 100) == 0 and len(calls) == 3
+    never = CB(lambda _: 0)
+    assert lib.wrk_watchdog_wait(never, None, None, 50, 100) == wrk.ERR_TIMEOUT
+    assert lib.wrk_watchdog_wait(never, CB(lambda _: 3), None, 5000, 100) == wrk.ERR_NCCL
+    assert b"code 3" in lib.wrk_last_error_message()
+    assert lib.wrk_watchdog_wait(None, None, None, 50, 100) == wrk.ERR_INVALID_ARGUMENT
+
+
 @pytest.mark.gpu
-def test_tensor_parallel_v6_matches_single_gpu():
+def test_sharded_bundles_match_the_whole_model():
     listing = subprocess.run(["nvidia-smi", "-L"], capture_output=True, text=True).stdout
     if listing.count("GPU ") < 2:
         pytest.skip("needs two GPUs")

@@ -26,6 +26,9 @@ _NP = {F32: np.float32, F16: np.float16, U8: np.uint8, U16: np.uint16, U32: np.u
 _DT = {np.dtype(v): k for k, v in _NP.items()}
 
 
+ERR_NCCL, ERR_TIMEOUT, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED = -101, -102, -103, -104  # wrk_status, include/wrk.h
+
+
 class WrkError(RuntimeError):
     def __init__(self, status, message):
         super().__init__(f"wrk status {status}: {message}")

@@ -5,8 +5,12 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <chrono>
 #include <cstdlib>
 #include <cstring>
+#include <thread>
+
+#include <string>
 
 #include "common.h"
 
@@ -17,6 +21,7 @@ struct NcclApi {
     ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
     ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
@@ -31,10 +36,11 @@ const NcclApi& nccl() {
         a.GetUniqueId = reinterpret_cast<decltype(a.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
         a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
         a.CommAbort = reinterpret_cast<decltype(a.CommAbort)>(dlsym(h, "ncclCommAbort"));
+        a.CommGetAsyncError = reinterpret_cast<decltype(a.CommGetAsyncError)>(dlsym(h, "ncclCommGetAsyncError"));
         a.AllReduce = reinterpret_cast<decltype(a.AllReduce)>(dlsym(h, "ncclAllReduce"));
         a.AllGather = reinterpret_cast<decltype(a.AllGather)>(dlsym(h, "ncclAllGather"));
         a.GetErrorString = reinterpret_cast<decltype(a.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
-        a.ok = a.GetUniqueId && a.CommInitRank && a.CommAbort && a.AllReduce && a.AllGather && a.GetErrorString;
+        a.ok = a.GetUniqueId && a.CommInitRank && a.CommAbort && a.CommGetAsyncError && a.AllReduce && a.AllGather && a.GetErrorString;
         return a;
     }();
     return api;
@@ -128,6 +134,73 @@ int32_t wrk_comm_release(wrk_comm* comm) {
     return WRK_OK;
 }
 
+int32_t wrk_comm_retain(wrk_comm* comm) {
+    WRK_REQUIRE(comm, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    comm->refs.fetch_add(1);
+    return WRK_OK;
+}
+
+// The wait every rank of a split job makes in place of a plain stream synchronize: a peer that never enters a
+// collective leaves this rank's kernel spinning on the device, which no CUDA call reports.  `done` and `failure`
+// are polled every `poll_us` microseconds; the wait ends with WRK_OK when done() is non-zero, with WRK_ERR_NCCL
+// when failure() is (its value is put in the message), with WRK_ERR_TIMEOUT after `timeout_ms`.
+int32_t wrk_watchdog_wait(int32_t (*done)(void*), int32_t (*failure)(void*), void* user, uint32_t timeout_ms, uint32_t poll_us) {
+    WRK_REQUIRE(done, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    const auto start = std::chrono::steady_clock::now();
+    const auto limit = std::chrono::milliseconds(timeout_ms);
+    for (;;) {
+        if (done(user) != 0) return WRK_OK;
+        if (failure) {
+            const int32_t f = failure(user);
+            if (f != 0) return wrk::set_error(WRK_ERR_NCCL, "a collective failed asynchronously (code %d)", f);
+        }
+        if (std::chrono::steady_clock::now() - start >= limit)
+            return wrk::set_error(WRK_ERR_TIMEOUT, "work on the stream did not finish within %u ms: a peer may have left", timeout_ms);
+        if (poll_us) std::this_thread::sleep_for(std::chrono::microseconds(poll_us));
+    }
+}
+
+namespace {
+struct CommWait {
+    wrk_comm* comm;
+    cudaEvent_t event;
+};
+int32_t comm_done(void* user) {
+    const cudaError_t e = cudaEventQuery(static_cast<CommWait*>(user)->event);
+    return e == cudaErrorNotReady ? 0 : 1;  // an error ends the wait too; the synchronize that follows reports it
+}
+int32_t comm_failure(void* user) {
+    ncclResult_t async = ncclSuccess;
+    const ncclResult_t r = nccl().CommGetAsyncError(static_cast<CommWait*>(user)->comm->comm, &async);
+    if (r != ncclSuccess) return (int32_t)r;
+    return async == ncclSuccess || async == ncclInProgress ? 0 : (int32_t)async;
+}
+}  // namespace
+
+// Waits for everything submitted to the communicator's context so far, polling ncclCommGetAsyncError; on a failure
+// or after timeout_ms the communicator is aborted (its kernels leave the device) and the error is returned: the
+// context stays usable, the communicator does not.
+int32_t wrk_comm_wait(wrk_comm* comm, uint32_t timeout_ms) {
+    WRK_REQUIRE(comm, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(comm->comm, WRK_ERR_NCCL, "the communicator was aborted by an earlier failure");
+    WRK_CUDA(cudaSetDevice(comm->ctx->device));
+    CommWait w{comm, nullptr};
+    WRK_CUDA(cudaEventCreateWithFlags(&w.event, cudaEventDisableTiming));
+    cudaError_t e = cudaEventRecord(w.event, comm->ctx->stream);
+    int32_t status = e == cudaSuccess ? wrk_watchdog_wait(comm_done, comm_failure, &w, timeout_ms, 50)
+                                      : wrk::set_error(WRK_ERR_CUDA, "cudaEventRecord failed: %s", cudaGetErrorString(e));
+    if (status == WRK_ERR_TIMEOUT || status == WRK_ERR_NCCL) {
+        const std::string message = wrk_last_error_message();
+        nccl().CommAbort(comm->comm);
+        comm->comm = nullptr;
+        cudaStreamSynchronize(comm->ctx->stream);
+        wrk::set_error(status, "%s; the communicator was aborted", message.c_str());
+    }
+    cudaEventDestroy(w.event);
+    if (status == WRK_OK) WRK_CUDA(cudaStreamSynchronize(comm->ctx->stream));
+    return status;
+}
+
 int32_t wrk_comm_rank(const wrk_comm* comm, int32_t* rank, int32_t* world) {
     WRK_REQUIRE(comm && rank && world, WRK_ERR_INVALID_ARGUMENT, "null argument");
     *rank = comm->rank;
@@ -144,11 +217,11 @@ int32_t wrk_op_all_reduce(wrk_comm* comm, wrk_tensor* x, wrk_op** out) {
                 "data type mismatch: all_reduce sums f16 or f32");
     void* ptr = x->ptr();
     const size_t count = x->len();
-    ncclComm_t c = comm->comm;
     auto hold = std::make_shared<CommHold>(comm);
     *out = wrk::new_atom("all_reduce",
                          [=](cudaStream_t s) {
-                             (void)hold;
+                             ncclComm_t c = hold->comm->comm;  // null once a failed wait has aborted it
+                             if (c == nullptr) return cudaErrorUnknown;
                              return nccl().AllReduce(ptr, ptr, count, dt, ncclSum, c, s) == ncclSuccess ? cudaSuccess : cudaErrorUnknown;
                          },
                          {x});
@@ -167,11 +240,11 @@ int32_t wrk_op_all_gather(wrk_comm* comm, wrk_tensor* input, wrk_tensor* output,
     const void* src = input->ptr();
     void* dst = output->ptr();
     const size_t count = input->len();
-    ncclComm_t c = comm->comm;
     auto hold = std::make_shared<CommHold>(comm);
     *out = wrk::new_atom("all_gather",
                          [=](cudaStream_t s) {
-                             (void)hold;
+                             ncclComm_t c = hold->comm->comm;
+                             if (c == nullptr) return cudaErrorUnknown;
                              return nccl().AllGather(src, dst, count, dt, c, s) == ncclSuccess ? cudaSuccess : cudaErrorUnknown;
                          },
                          {input, output});

@@ -46,6 +46,8 @@ struct wrk_bundle {
     wrk_model* model = nullptr;
     uint32_t num_batch = 0;
     std::vector<TensorH> state;  // per layer f32 [C, S + 2, num_batch]
+    wrk_comm* comm = nullptr;  // a rank of a split model: sums of partial products cross this communicator
+    std::vector<std::pair<uint32_t, uint32_t>> building_last;  // (batch, its last token's row) of the job being built
     bool packed_cursors = false, use_graph = true, fused = true;
     bool step_kernel = false;  // fused jobs of at most 8 tokens run as one persistent kernel where the job shape allows it
     int step_engine = 1;      // 1: tensor-core kernel where the matrices allow it; 3: always the mma.sync kernel
@@ -65,6 +67,7 @@ struct wrk_bundle {
         if (stage_cursors) cudaFreeHost(stage_cursors);
         state.clear();
         if (model) wrk_model_release(model);
+        if (comm) wrk_comm_release(comm);
     }
 };
 
@@ -109,6 +112,13 @@ wrk_view Vy(wrk_tensor* t, uint32_t y0, uint32_t y1) {  // t.view(.., y0..y1, ..
     return v;
 }
 
+wrk_view Vx(wrk_tensor* t, uint32_t x0, uint32_t x1) {  // t.view(x0..x1, .., .., ..)
+    wrk_view v = V(t);
+    v.shape[0] = x1 - x0;
+    v.offset[0] = x0;
+    return v;
+}
+
 int32_t reshape(wrk_tensor* t, uint32_t x, uint32_t y, uint32_t z, uint32_t w, TensorH* out) {
     const uint32_t s[4] = {x, y, z, w};
     wrk_tensor* r = nullptr;
@@ -130,26 +140,36 @@ int32_t make_runtime(wrk_bundle* bd, uint32_t T, std::shared_ptr<Buffers>* out) 
     const wrk_model_info& info = bd->model->info;
     wrk_context* ctx = bd->model->ctx;
     auto b = std::make_shared<Buffers>();
-    const uint32_t C = info.num_emb, F = info.num_hidden;
+    const uint32_t C = info.num_emb;
+    // a rank of a split model keeps its own time-mix channels (Cl of C) and FFN columns (F of num_hidden); the
+    // residual stream, the token shifts and the sums after `output` / ffn `value` span all C channels
+    const Shard& sh = bd->model->shard;
+    const uint32_t Cl = sh.on() ? sh.c1 - sh.c0 : C, F = sh.on() ? sh.f1 - sh.f0 : info.num_hidden;
     const int H16 = WRK_F16, F32 = WRK_F32;
     WRK_TRY(alloc(ctx, *b, "cursors", WRK_U32, bd->packed_cursors ? T : 3 * T, 1));
     WRK_TRY(alloc(ctx, *b, "input", H16, C, T));
     WRK_TRY(alloc(ctx, *b, "x", H16, C, T));
+    if (sh.on()) {
+        WRK_TRY(alloc(ctx, *b, "att_xl", H16, Cl, T));
+        WRK_TRY(alloc(ctx, *b, "partial", F32, C, T));
+    }
     if (info.version == 7) {
-        for (auto n : {"att_x", "att_v0", "att_rx", "att_wx", "att_kx", "att_vx", "att_ax", "att_gx", "att_r", "att_w",
-                       "att_k", "att_v", "att_a", "att_g", "att_o", "att_kk", "att_vv", "ffn_x", "ffn_kx", "ffn_v"})
+        for (auto n : {"att_x", "att_rx", "att_wx", "att_kx", "att_vx", "att_ax", "att_gx", "att_o", "ffn_x", "ffn_kx", "ffn_v"})
             WRK_TRY(alloc(ctx, *b, n, H16, C, T));
-        WRK_TRY(alloc(ctx, *b, "att_n", H16, C, T, 4));
+        for (auto n : {"att_v0", "att_r", "att_w", "att_k", "att_v", "att_a", "att_g", "att_kk", "att_vv"})
+            WRK_TRY(alloc(ctx, *b, n, H16, Cl, T));
+        WRK_TRY(alloc(ctx, *b, "att_n", H16, Cl, T, 4));
         WRK_TRY(alloc(ctx, *b, "aux_w", H16, info.custom[0], T));
         WRK_TRY(alloc(ctx, *b, "aux_a", H16, info.custom[1], T));
         WRK_TRY(alloc(ctx, *b, "aux_g", H16, info.custom[2], T));
         WRK_TRY(alloc(ctx, *b, "aux_v", H16, info.custom[3], T));
         WRK_TRY(alloc(ctx, *b, "ffn_k", H16, F, T));
     } else {
-        WRK_TRY(alloc(ctx, *b, "aux_x", F32, C, T));
-        for (auto n : {"att_x", "att_g", "att_o", "ffn_x", "ffn_kx", "ffn_rx", "ffn_v", "ffn_r"})
+        WRK_TRY(alloc(ctx, *b, "aux_x", F32, Cl, T));
+        for (auto n : {"att_x", "att_o", "ffn_x", "ffn_kx", "ffn_rx", "ffn_v", "ffn_r"})
             WRK_TRY(alloc(ctx, *b, n, H16, C, T));
-        for (auto n : {"att_k", "att_v", "att_r"}) WRK_TRY(alloc(ctx, *b, n, F32, C, T));
+        WRK_TRY(alloc(ctx, *b, "att_g", H16, Cl, T));
+        for (auto n : {"att_k", "att_v", "att_r"}) WRK_TRY(alloc(ctx, *b, n, F32, Cl, T));
         WRK_TRY(alloc(ctx, *b, "ffn_k", H16, F, T));
         if (info.version == 6) {
             WRK_TRY(alloc(ctx, *b, "att_xx", H16, C, T));
@@ -158,7 +178,7 @@ int32_t make_runtime(wrk_bundle* bd, uint32_t T, std::shared_ptr<Buffers>* out) 
             WRK_TRY(alloc(ctx, *b, "time_mix_x", H16, info.custom[0], 5, T));
             WRK_TRY(alloc(ctx, *b, "time_mix_t", H16, info.custom[0], T, 5));
             WRK_TRY(alloc(ctx, *b, "time_mix", H16, C, T, 5));
-            WRK_TRY(alloc(ctx, *b, "time_decay", F32, C, T));
+            WRK_TRY(alloc(ctx, *b, "time_decay", F32, Cl, T));
         } else {
             for (auto n : {"att_kx", "att_vx", "att_rx", "att_gx"}) WRK_TRY(alloc(ctx, *b, n, H16, C, T));
         }
@@ -178,6 +198,13 @@ int32_t make_header(wrk_bundle* bd, uint32_t num_header, std::shared_ptr<Buffers
         wrk_matrix_parts(bd->model->head_w, nullptr, &w, nullptr, nullptr);
         wrk_tensor_shape(w, s);
         vocab = s[1];
+    }
+    const Shard& sh = bd->model->shard;
+    if (sh.on()) {
+        // the rank's slice of the vocabulary, every rank's slice (gathered), and the rows put in order
+        WRK_TRY(alloc(bd->model->ctx, *b, "head_l", WRK_F32, vocab, num_header));
+        WRK_TRY(alloc(bd->model->ctx, *b, "head_all", WRK_F32, vocab, num_header, sh.world));
+        vocab *= sh.world;
     }
     WRK_TRY(alloc(bd->model->ctx, *b, "head_o", WRK_F32, vocab, num_header));
     *out = b;
@@ -212,6 +239,47 @@ int32_t add(OpList& ops, wrk_view in, wrk_view out, int32_t act_out = WRK_ACT_NO
 wrk_view state_att(wrk_bundle* bd, uint32_t layer, uint32_t S) { return Vy(bd->state[layer], 0, S + 1); }
 wrk_view state_ffn(wrk_bundle* bd, uint32_t layer, uint32_t S) { return Vy(bd->state[layer], S + 1, S + 2); }
 
+// ---- a rank of a split model (no counterpart in the reference, which runs on one GPU) ----
+// The layer functions below serve both: with the whole model on this GPU the local channel range is all of C and
+// they emit the reference's op list; on a rank of a split model the time-mix ops between the token shifts and
+// `output` run on the rank's channels, `output` and ffn `value` multiply the rank's slice of K into an f32 partial
+// sum over all C channels, and one all-reduce per sub-block turns it into the sum the residual needs.
+struct Split {
+    bool on;
+    uint32_t c0, Cl;
+};
+Split split_of(const wrk_bundle* bd) {
+    const Shard& sh = bd->model->shard;
+    return {sh.on(), sh.on() ? sh.c0 : 0u, sh.on() ? sh.c1 - sh.c0 : bd->model->info.num_emb};
+}
+// The state rows a time-mix op touches (the shift row and the S rows of the recurrence), for the rank's channels.
+wrk_view state_wkv(wrk_bundle* bd, uint32_t layer, uint32_t S, const Split& sp) {
+    wrk_view v = state_att(bd, layer, S);
+    if (sp.on) {
+        v.shape[0] = sp.Cl;
+        v.offset[0] = sp.c0;
+    }
+    return v;
+}
+// `partial` holds this rank's share of a product over all C channels: sum over the ranks, round to fp16 once.
+int32_t reduce_partial(wrk_bundle* bd, OpList& ops, const Buffers& B, wrk_tensor* out) {
+    ADD(wrk_op_all_reduce(bd->comm, B["partial"], &_o));
+    return blit(ops, V(B["partial"]), V(out));
+}
+// The time-mix op has written the shift row (the normalised input of every sequence's last token) for the rank's
+// channels only; the next job's token shifts read all of them.
+int32_t carry_all_channels(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, uint32_t S) {
+    (void)S;
+    for (const auto& bt : bd->building_last) {
+        wrk_view in = Vy(B["att_x"], bt.second, bt.second + 1);
+        wrk_view out = Vy(bd->state[index], 0, 1);
+        out.shape[2] = 1;
+        out.offset[2] = bt.first;
+        WRK_TRY(blit(ops, in, out));
+    }
+    return WRK_OK;
+}
+
 // dispatch_layer of v5 (v5.rs:656-885) and v6 (v6.rs:701-958)
 int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, uint32_t T) {
     const wrk_model_info& info = bd->model->info;
@@ -220,6 +288,8 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
     const bool turbo = T % WRK_MIN_TOKEN_CHUNK_SIZE == 0;
     const bool v6 = info.version == 6;
     wrk_tensor* cursors = B["cursors"];
+    const Split sp = split_of(bd);
+    wrk_tensor* att_loc = sp.on ? B["att_xl"] : B["att_x"];  // the gated WKV output, `output`'s input
 
     TensorH time_first, time_decay, aux_x, att_k, att_v, att_r;
     WRK_TRY(reshape(L.time_first, S, WRK_DIM_AUTO, 1, 1, &time_first));
@@ -265,19 +335,23 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
         WRK_TRY(matmul(ops, L.att_w_r, V(B["att_rx"]), V(B["att_r"]), WRK_ACT_NONE, turbo));
         WRK_TRY(matmul(ops, L.att_w_g, V(B["att_gx"]), V(B["att_g"]), WRK_ACT_NONE, turbo));
     }
-    WRK_TRY(blit(ops, V(B["att_x"]), V(B["aux_x"])));
+    WRK_TRY(blit(ops, Vx(B["att_x"], sp.c0, sp.c0 + sp.Cl), V(B["aux_x"])));
     {
-        const wrk_view st = state_att(bd, index, S);
+        const wrk_view st = state_wkv(bd, index, S, sp);
         if (v6) ADD(wrk_op_time_mix_v6(cursors, time_decay, time_first, &st, att_k, att_v, att_r, aux_x, &_o));
         else ADD(wrk_op_time_mix_v5(cursors, time_decay, time_first, &st, att_k, att_v, att_r, aux_x, &_o));
     }
     ADD(wrk_op_group_norm(L.gn.w, L.gn.b, aux_x, GN_EPS, &_o));
-    WRK_TRY(blit(ops, V(B["aux_x"]), V(B["att_x"])));
+    WRK_TRY(blit(ops, V(B["aux_x"]), V(att_loc)));
     {
-        const wrk_view g = V(B["att_g"]), x = V(B["att_x"]);
+        const wrk_view g = V(B["att_g"]), x = V(att_loc);
         ADD(wrk_op_mul_activate(&g, &x, WRK_ACT_SILU, WRK_ACT_NONE, WRK_ACT_NONE, &_o));
     }
-    WRK_TRY(matmul(ops, L.att_w_o, V(B["att_x"]), V(B["att_o"]), WRK_ACT_NONE, turbo));
+    WRK_TRY(matmul(ops, L.att_w_o, V(att_loc), V(sp.on ? B["partial"] : B["att_o"]), WRK_ACT_NONE, turbo));
+    if (sp.on) {
+        WRK_TRY(reduce_partial(bd, ops, B, B["att_o"]));
+        WRK_TRY(carry_all_channels(bd, ops, B, index, S));
+    }
     WRK_TRY(add(ops, V(B["att_o"]), V(B["x"])));
 
     WRK_TRY(blit(ops, V(B["x"]), V(B["ffn_x"])));
@@ -285,7 +359,8 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
     WRK_TRY(token_shift(ops, cursors, V(L.ffn_time_mix_k), state_ffn(bd, index, S), B["ffn_x"], B["ffn_kx"], v6));
     WRK_TRY(token_shift(ops, cursors, V(L.ffn_time_mix_r), state_ffn(bd, index, S), B["ffn_x"], B["ffn_rx"], v6));
     WRK_TRY(matmul(ops, L.ffn_w_k, V(B["ffn_kx"]), V(B["ffn_k"]), WRK_ACT_SQUARED_RELU, turbo));
-    WRK_TRY(matmul(ops, L.ffn_w_v, V(B["ffn_k"]), V(B["ffn_v"]), WRK_ACT_NONE, turbo, true));
+    WRK_TRY(matmul(ops, L.ffn_w_v, V(B["ffn_k"]), V(sp.on ? B["partial"] : B["ffn_v"]), WRK_ACT_NONE, turbo, true));
+    if (sp.on) WRK_TRY(reduce_partial(bd, ops, B, B["ffn_v"]));
     WRK_TRY(matmul(ops, L.ffn_w_r, V(B["ffn_rx"]), V(B["ffn_r"]), WRK_ACT_NONE, turbo));
     {
         const wrk_view st = state_ffn(bd, index, S);
@@ -303,10 +378,12 @@ int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, 
     const uint32_t C = info.num_emb, S = C / info.num_head;
     const bool turbo = T % WRK_MIN_TOKEN_CHUNK_SIZE == 0;
     wrk_tensor* cursors = B["cursors"];
+    const Split sp = split_of(bd);
+    wrk_tensor* att_loc = sp.on ? B["att_xl"] : B["att_x"];  // the time-mix op's input (shift source) and output
 
     TensorH att_kk, att_x, att_r, att_w, att_n;
     WRK_TRY(reshape(B["att_kk"], S, WRK_DIM_AUTO, T, 1, &att_kk));
-    WRK_TRY(reshape(B["att_x"], S, WRK_DIM_AUTO, T, 1, &att_x));
+    WRK_TRY(reshape(att_loc, S, WRK_DIM_AUTO, T, 1, &att_x));
     WRK_TRY(reshape(B["att_r"], S, WRK_DIM_AUTO, T, 1, &att_r));
     WRK_TRY(reshape(B["att_w"], S, WRK_DIM_AUTO, T, 1, &att_w));
     WRK_TRY(reshape(B["att_n"], S, WRK_DIM_AUTO, T, 4, &att_n));
@@ -354,21 +431,30 @@ int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, 
     WRK_TRY(blit(ops, V(B["att_v"]), Vz(B["att_n"], 1)));
     WRK_TRY(blit(ops, V(B["att_a"]), Vz(B["att_n"], 2)));
     WRK_TRY(blit(ops, V(B["att_kk"]), Vz(B["att_n"], 3)));
-    ADD(wrk_op_time_mix_v7(cursors, &sa, att_r, att_w, att_n, att_x, &_o));
+    if (sp.on) WRK_TRY(blit(ops, Vx(B["att_x"], sp.c0, sp.c0 + sp.Cl), V(att_loc)));
+    {
+        const wrk_view st = state_wkv(bd, index, S, sp);
+        ADD(wrk_op_time_mix_v7(cursors, &st, att_r, att_w, att_n, att_x, &_o));
+    }
     ADD(wrk_op_group_norm(L.gn.w, L.gn.b, att_x, GN_EPS, &_o));
     ADD(wrk_op_time_first_v7(L.r_k, att_r, att_n, att_x, &_o));
     {
-        const wrk_view g = V(B["att_g"]), x = V(B["att_x"]);
+        const wrk_view g = V(B["att_g"]), x = V(att_loc);
         ADD(wrk_op_mul_activate(&g, &x, WRK_ACT_NONE, WRK_ACT_NONE, WRK_ACT_NONE, &_o));
     }
-    WRK_TRY(matmul(ops, L.att_w_o, V(B["att_x"]), V(B["att_o"]), WRK_ACT_NONE, turbo));
+    WRK_TRY(matmul(ops, L.att_w_o, V(att_loc), V(sp.on ? B["partial"] : B["att_o"]), WRK_ACT_NONE, turbo));
+    if (sp.on) {
+        WRK_TRY(reduce_partial(bd, ops, B, B["att_o"]));
+        WRK_TRY(carry_all_channels(bd, ops, B, index, S));
+    }
     WRK_TRY(add(ops, V(B["att_o"]), V(B["x"])));
 
     WRK_TRY(blit(ops, V(B["x"]), V(B["ffn_x"])));
     ADD(wrk_op_layer_norm(L.ffn_ln.w, L.ffn_ln.b, B["ffn_x"], LN_EPS, &_o));
     WRK_TRY(token_shift(ops, cursors, V(L.ffn_x_k), state_ffn(bd, index, S), B["ffn_x"], B["ffn_kx"], true));
     WRK_TRY(matmul(ops, L.ffn_w_k, V(B["ffn_kx"]), V(B["ffn_k"]), WRK_ACT_SQUARED_RELU, turbo));
-    WRK_TRY(matmul(ops, L.ffn_w_v, V(B["ffn_k"]), V(B["ffn_v"]), WRK_ACT_NONE, turbo, true));
+    WRK_TRY(matmul(ops, L.ffn_w_v, V(B["ffn_k"]), V(sp.on ? B["partial"] : B["ffn_v"]), WRK_ACT_NONE, turbo, true));
+    if (sp.on) WRK_TRY(reduce_partial(bd, ops, B, B["ffn_v"]));
     {
         const wrk_view st = state_ffn(bd, index, S);
         ADD(wrk_op_channel_mix_v7(cursors, &st, B["ffn_v"], B["ffn_x"], &_o));
@@ -457,6 +543,7 @@ __half* Hm(wrk_tensor* t) { return static_cast<__half*>(t->ptr()); }
 bool fused_v6_supported(wrk_bundle* bd, uint32_t T) {
     const wrk_model_info& info = bd->model->info;
     if (!bd->fused || info.version != 6 || T == 0 || T > (uint32_t)k::kDecodeMaxTokens) return false;
+    if (bd->model->shard.on()) return false;  // the fused phases end in residual adds; a split model sums across ranks first
     if (info.num_emb / info.num_head != 64 || info.num_emb % 128 || info.custom[0] % 8 || info.custom[0] > 64 ||
         info.custom[1] % 32 || info.custom[1] > 128)
         return false;
@@ -894,6 +981,14 @@ int32_t build_job(wrk_bundle* bd, const RnnInfo& info, CachedJob* job) {
     const Buffers& Hd = *job->header;
     OpList ops;
     const bool fused = fused_v6_supported(bd, T);
+    bd->building_last.clear();
+    {
+        uint32_t row = 0;
+        for (uint32_t batch = 0; batch < info.lens.size(); ++batch) {
+            if (info.lens[batch] > 0) bd->building_last.emplace_back(batch, row + info.lens[batch] - 1);
+            row += info.lens[batch];
+        }
+    }
 
     // the whole job as one persistent kernel (launched eagerly: a memset of the barrier word and one cooperative
     // launch per job need no graph)
@@ -953,6 +1048,13 @@ int32_t build_job(wrk_bundle* bd, const RnnInfo& info, CachedJob* job) {
         a.epilogue = k::EPI_STORE;
         a.rescale = 1.0f;
         WRK_TRY(add_fused_gemv(m->ctx, ops, job, a, "fused_head", {head_x, Hd["head_o"]}));
+    } else if (NH > 0 && m->shard.on()) {
+        // every rank multiplies its slice of the vocabulary; the slices are gathered and put in order
+        ADD(wrk_op_layer_norm(m->head_ln.w, m->head_ln.b, head_x, LN_EPS, &_o));
+        WRK_TRY(matmul(ops, m->head_w, V(head_x), V(Hd["head_l"]), WRK_ACT_NONE, NH % WRK_MIN_TOKEN_CHUNK_SIZE == 0));
+        ADD(wrk_op_all_gather(bd->comm, Hd["head_l"], Hd["head_all"], &_o));
+        const uint32_t Vl = m->shard.v1 - m->shard.v0;
+        for (uint32_t r = 0; r < m->shard.world; ++r) WRK_TRY(blit(ops, Vz(Hd["head_all"], r), Vx(Hd["head_o"], r * Vl, (r + 1) * Vl)));
     } else if (NH > 0) {
         ADD(wrk_op_layer_norm(m->head_ln.w, m->head_ln.b, head_x, LN_EPS, &_o));
         WRK_TRY(matmul(ops, m->head_w, V(head_x), V(Hd["head_o"]), WRK_ACT_NONE, NH % WRK_MIN_TOKEN_CHUNK_SIZE == 0));
@@ -984,10 +1086,32 @@ int32_t ensure_staging(wrk_bundle* bd, size_t tokens) {
 
 extern "C" {
 
+static int32_t bundle_create(wrk_model* model, uint32_t num_batch, wrk_comm* comm, wrk_bundle** out);
+
 int32_t wrk_bundle_create(wrk_model* model, uint32_t num_batch, wrk_bundle** out) {
     WRK_REQUIRE(model && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(!model->shard.on(), WRK_ERR_INVALID_ARGUMENT, "rank %u of a model split %u ways needs wrk_bundle_create_sharded", model->shard.rank,
+                model->shard.world);
+    return bundle_create(model, num_batch, nullptr, out);
+}
+
+int32_t wrk_bundle_create_sharded(wrk_model* model, uint32_t num_batch, wrk_comm* comm, wrk_bundle** out) {
+    WRK_REQUIRE(model && comm && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    int32_t rank = 0, world = 1;
+    WRK_TRY(wrk_comm_rank(comm, &rank, &world));
+    WRK_REQUIRE((uint32_t)world == model->shard.world && (uint32_t)rank == model->shard.rank, WRK_ERR_INVALID_ARGUMENT,
+                "the model is rank %u of %u, the communicator rank %d of %d", model->shard.rank, model->shard.world, rank, world);
+    if (world == 1) return bundle_create(model, num_batch, nullptr, out);
+    return bundle_create(model, num_batch, comm, out);
+}
+
+static int32_t bundle_create(wrk_model* model, uint32_t num_batch, wrk_comm* comm, wrk_bundle** out) {
     WRK_REQUIRE(num_batch >= 1, WRK_ERR_INVALID_ARGUMENT, "num_batch must be at least 1");
     auto b = new wrk_bundle();
+    if (comm) {
+        wrk_comm_retain(comm);
+        b->comm = comm;
+    }
     wrk_model_retain(model);
     b->model = model;
     b->num_batch = num_batch;

@@ -13,6 +13,22 @@ wrk_model::~wrk_model() {
     if (embed_host) cudaFreeHost(embed_host);
 }
 
+namespace wrk {
+namespace rt {
+int32_t shard_range(const char* what, uint32_t total, uint32_t align, uint32_t world, uint32_t rank, uint32_t* begin, uint32_t* end) {
+    WRK_REQUIRE(align >= 1 && world >= 1 && rank < world, WRK_ERR_INVALID_ARGUMENT, "%s: unit %u, rank %u of %u", what, align, rank, world);
+    WRK_REQUIRE(total % align == 0, WRK_ERR_SHAPE, "%s: %u is not a multiple of the unit %u", what, total, align);
+    const uint32_t units = total / align;
+    WRK_REQUIRE(units >= world, WRK_ERR_SHAPE, "%s: %u units of %u cannot be split %u ways", what, units, align, world);
+    const uint32_t base = units / world, extra = units % world;
+    const uint32_t first = rank * base + std::min(rank, extra);
+    *begin = first * align;
+    *end = (first + base + (rank < extra ? 1u : 0u)) * align;
+    return WRK_OK;
+}
+}  // namespace rt
+}  // namespace wrk
+
 namespace {
 
 struct Loader {
@@ -261,6 +277,77 @@ struct Loader {
     }
 };
 
+// A dimension of the tensor as the file holds it (a sharded builder keeps the rank's slice and this record).
+uint32_t file_dim(const wrk_model_builder::Entry* e, size_t i) { return (uint32_t)(e->full.empty() ? e->shape[i] : e->full[i]); }
+
+// Which slice of a tensor a rank of a sharded model keeps, by the tensor's name.  Time-mix channels go by whole
+// heads: key / value / receptance / gate and the second matrices of the per-channel adapters keep the rows of the
+// rank's channels, `output` the matching columns (a split of its K), per-channel vectors their slice; ffn `key` keeps
+// a slice of rows, `value` the matching columns; the head keeps a slice of the vocabulary.  Everything else (layer
+// norms, token-shift mixes, the adapters' first matrices, ffn `receptance`, the embedding) is held whole by every rank.
+enum class Cut { None, RowsC, ColsC, FlatC, RowsF, ColsF, RowsV };
+Cut cut_of(const std::string& name) {
+    if (name == "head.weight") return Cut::RowsV;
+    if (name.rfind("blocks.", 0) != 0) return Cut::None;
+    const size_t dot = name.find('.', 7);
+    if (dot == std::string::npos) return Cut::None;
+    const std::string leaf = name.substr(dot + 1);
+    for (auto n : {"att.key.weight", "att.value.weight", "att.receptance.weight", "att.gate.weight", "att.time_decay_w2", "att.w2",
+                   "att.a2", "att.g2", "att.v2"})
+        if (leaf == n) return Cut::RowsC;
+    if (leaf == "att.output.weight") return Cut::ColsC;
+    for (auto n : {"att.time_decay", "att.time_first", "att.ln_x.weight", "att.ln_x.bias", "att.w0", "att.a0", "att.v0", "att.k_k",
+                   "att.k_a", "att.r_k"})
+        if (leaf == n) return Cut::FlatC;
+    if (leaf == "ffn.key.weight") return Cut::RowsF;
+    if (leaf == "ffn.value.weight") return Cut::ColsF;
+    return Cut::None;
+}
+
+int32_t cut_entry(const wrk_model_builder* b, const std::string& name, wrk_model_builder::Entry& e) {
+    const Cut cut = cut_of(name);
+    if (cut == Cut::None) return WRK_OK;
+    const uint32_t S = b->shard_head_size, blk = b->shard_block;
+    const uint32_t align_c = std::max(S, blk), align_f = std::max(blk, 8u);
+    size_t n = 1;
+    for (auto d : e.shape) n *= d;
+    uint32_t b0 = 0, b1 = 0;
+    const std::vector<uint64_t> full = e.shape;
+    if (cut == Cut::FlatC) {
+        WRK_TRY(shard_range(name.c_str(), (uint32_t)n, align_c, b->shard_world, b->shard_rank, &b0, &b1));
+        std::memmove(e.data.data(), e.data.data() + b0, (size_t)(b1 - b0) * 2);
+        e.data.resize(b1 - b0);
+        // (heads, head size) stays two-dimensional; everything else becomes a vector
+        if (full.size() == 2 && full[1] == S && full[0] * S == n) e.shape = {(b1 - b0) / S, S};
+        else e.shape = {b1 - b0};
+        e.full = full;
+        return WRK_OK;
+    }
+    WRK_REQUIRE(e.shape.size() == 2, WRK_ERR_SHAPE, "tensor shape not match: %s is not a matrix", name.c_str());
+    const uint32_t M = (uint32_t)e.shape[0], K = (uint32_t)e.shape[1];
+    const bool rows = cut == Cut::RowsC || cut == Cut::RowsF || cut == Cut::RowsV;
+    uint32_t align = cut == Cut::RowsC || cut == Cut::ColsC ? align_c : align_f;
+    if (cut == Cut::RowsV) {
+        WRK_REQUIRE(M % (8 * b->shard_world) == 0, WRK_ERR_SHAPE, "a vocabulary of %u rows does not split into %u slices of whole 8-row groups",
+                    M, b->shard_world);
+        align = M / b->shard_world;
+    }
+    WRK_TRY(shard_range(name.c_str(), rows ? M : K, align, b->shard_world, b->shard_rank, &b0, &b1));
+    if (rows) {
+        std::memmove(e.data.data(), e.data.data() + (size_t)b0 * K, (size_t)(b1 - b0) * K * 2);
+        e.data.resize((size_t)(b1 - b0) * K);
+        e.shape = {b1 - b0, K};
+    } else {
+        const uint32_t Kl = b1 - b0;
+        for (uint32_t m = 0; m < M; ++m) std::memmove(e.data.data() + (size_t)m * Kl, e.data.data() + (size_t)m * K + b0, (size_t)Kl * 2);
+        e.data.resize((size_t)M * Kl);
+        e.shape = {M, Kl};
+    }
+    e.data.shrink_to_fit();
+    e.full = full;
+    return WRK_OK;
+}
+
 // Loader::info, src/runtime/loader.rs:208-324.
 int32_t sniff_info(const wrk_model_builder* b, wrk_model_info* info) {
     Loader ld{const_cast<wrk_model_builder*>(b), b->ctx};
@@ -307,13 +394,13 @@ int32_t sniff_info(const wrk_model_builder* b, wrk_model_info* info) {
     std::memset(info, 0, sizeof *info);
     info->version = version;
     info->num_layer = num_layer;
-    info->num_emb = (uint32_t)embed->shape[1];
-    info->num_hidden = (uint32_t)ffn->shape[0];
-    info->num_vocab = (uint32_t)embed->shape[0];
+    info->num_emb = file_dim(embed, 1);
+    info->num_hidden = file_dim(ffn, 0);
+    info->num_vocab = file_dim(embed, 0);
     const wrk_model_builder::Entry* e;
     if (version == 7) {
         WRK_TRY(ld.entry("blocks.0.att.r_k", &e));
-        info->num_head = (uint32_t)e->shape[0];
+        info->num_head = file_dim(e, 0);
         WRK_TRY(ld.entry("blocks.0.att.w1", &e));
         info->custom[0] = (uint32_t)e->shape[0];
         WRK_TRY(ld.entry("blocks.0.att.a1", &e));
@@ -324,7 +411,7 @@ int32_t sniff_info(const wrk_model_builder* b, wrk_model_info* info) {
         info->custom[3] = (uint32_t)e->shape[0];
     } else {
         WRK_TRY(ld.entry("blocks.0.att.time_first", &e));
-        info->num_head = (uint32_t)e->shape[0];
+        info->num_head = file_dim(e, 0);
         if (version == 6) {
             WRK_TRY(ld.entry("blocks.0.att.time_mix_w1", &e));
             info->custom[0] = (uint32_t)e->shape[0] / 5;
@@ -354,6 +441,36 @@ int32_t build_common(const Loader& ld, wrk_model* m) {
     WRK_TRY(wrk_matrix_fp16(head, &hm));
     m->head_w = MatrixH(hm);
     return WRK_OK;
+}
+
+// The rank's ranges, from the whole model's dimensions with the rules cut_entry applied tensor by tensor.
+int32_t plan_shard(const wrk_model_builder* b, wrk_model* m) {
+    const wrk_model_info& info = m->info;
+    const uint32_t S = info.num_emb / info.num_head;
+    WRK_REQUIRE(S == b->shard_head_size, WRK_ERR_SHAPE, "the model's heads have %u channels, the split was set up for %u", S,
+                b->shard_head_size);
+    uint32_t blk = 1;
+    for (uint32_t layer = 0; layer < info.num_layer; ++layer) {
+        auto it = b->quant.find(layer);
+        const int32_t q = it == b->quant.end() ? WRK_QUANT_NONE : it->second;
+        blk = std::max(blk, q == WRK_QUANT_INT8 ? 128u : q == WRK_QUANT_NONE ? 1u : 64u);
+    }
+    WRK_REQUIRE(b->shard_block % blk == 0, WRK_ERR_INVALID_ARGUMENT,
+                "the split was set up for quantization blocks of %u values, the layers' quantization needs %u", b->shard_block, blk);
+    Shard& sh = m->shard;
+    sh.rank = b->shard_rank;
+    sh.world = b->shard_world;
+    WRK_TRY(shard_range("channels", info.num_emb, std::max(S, b->shard_block), sh.world, sh.rank, &sh.c0, &sh.c1));
+    WRK_TRY(shard_range("ffn columns", info.num_hidden, std::max(b->shard_block, 8u), sh.world, sh.rank, &sh.f0, &sh.f1));
+    WRK_REQUIRE(info.num_vocab % (8 * sh.world) == 0, WRK_ERR_SHAPE, "a vocabulary of %u rows does not split into %u slices of whole 8-row groups",
+                info.num_vocab, sh.world);
+    WRK_TRY(shard_range("vocabulary", info.num_vocab, info.num_vocab / sh.world, sh.world, sh.rank, &sh.v0, &sh.v1));
+    return WRK_OK;
+}
+
+uint32_t local_heads(const wrk_model* m) {
+    const uint32_t S = m->info.num_emb / m->info.num_head;
+    return m->shard.on() ? (m->shard.c1 - m->shard.c0) / S : m->info.num_head;
 }
 
 int32_t quant_of(const wrk_model_builder* b, uint32_t layer) {
@@ -403,7 +520,7 @@ int32_t build_v56(const Loader& ld, wrk_model* m) {
             WRK_TRY(ld.matrix_fp16(att + ".time_mix_w1", &L.time_mix_w1));
             WRK_TRY(ld.matrix_fp16(att + ".time_mix_w2", &L.time_mix_w2));
         }
-        WRK_TRY(ld.group_norm(att + ".ln_x", info.num_head, &L.gn));
+        WRK_TRY(ld.group_norm(att + ".ln_x", local_heads(m), &L.gn));
         WRK_TRY(ld.matrix(att + ".key.weight", quant, 1.0f, &L.att_w_k));
         WRK_TRY(ld.matrix(att + ".value.weight", quant, 1.0f, &L.att_w_v));
         WRK_TRY(ld.matrix(att + ".receptance.weight", quant, 1.0f, &L.att_w_r));
@@ -458,7 +575,7 @@ int32_t build_v7(const Loader& ld, wrk_model* m) {
         WRK_TRY(ld.matrix_f16(att + ".r_k", false, 1.0f, &L.r_k));
         WRK_TRY(ld.vector_f16(att + ".k_k", &L.k_k));
         WRK_TRY(ld.vector_f16(att + ".k_a", &L.k_a));
-        WRK_TRY(ld.group_norm(att + ".ln_x", info.num_head, &L.gn));
+        WRK_TRY(ld.group_norm(att + ".ln_x", local_heads(m), &L.gn));
         WRK_TRY(ld.matrix(att + ".key.weight", quant, 1.0f, &L.att_w_k));
         WRK_TRY(ld.matrix(att + ".value.weight", quant, 1.0f, &L.att_w_v));
         WRK_TRY(ld.matrix(att + ".receptance.weight", quant, 1.0f, &L.att_w_r));
@@ -498,9 +615,33 @@ int32_t wrk_model_builder_add_tensor(wrk_model_builder* b, const char* name, con
     WRK_REQUIRE(n * 2 == bytes, WRK_ERR_SIZE, "data size not match: %zu vs. %zu", n * 2, bytes);
     auto& e = b->tensors[name];
     e.shape.assign(shape, shape + ndim);
+    e.full.clear();
     e.data.resize(n);
     std::memcpy(e.data.data(), data_f16, bytes);
+    if (b->shard_world > 1) {
+        const int32_t s = cut_entry(b, name, e);
+        if (s != WRK_OK) b->tensors.erase(name);
+        return s;
+    }
     return WRK_OK;
+}
+
+int32_t wrk_model_builder_shard(wrk_model_builder* b, uint32_t rank, uint32_t world, uint32_t head_size, uint32_t block) {
+    WRK_REQUIRE(b, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(world >= 1 && rank < world, WRK_ERR_INVALID_ARGUMENT, "rank %u of %u", rank, world);
+    WRK_REQUIRE(head_size >= 1 && block >= 1, WRK_ERR_INVALID_ARGUMENT, "head size %u, block %u", head_size, block);
+    WRK_REQUIRE(b->tensors.empty() && b->loras.empty(), WRK_ERR_INVALID_ARGUMENT,
+                "the split is chosen before the first tensor is added (tensors are cut as they arrive)");
+    b->shard_rank = rank;
+    b->shard_world = world;
+    b->shard_head_size = head_size;
+    b->shard_block = block;
+    return WRK_OK;
+}
+
+int32_t wrk_shard_range(uint32_t total, uint32_t align, uint32_t world, uint32_t rank, uint32_t* begin, uint32_t* end) {
+    WRK_REQUIRE(begin && end, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    return shard_range("range", total, align, world, rank, begin, end);
 }
 
 int32_t wrk_model_builder_quant(wrk_model_builder* b, uint32_t layer, int32_t quant) {
@@ -512,6 +653,7 @@ int32_t wrk_model_builder_quant(wrk_model_builder* b, uint32_t layer, int32_t qu
 
 int32_t wrk_model_builder_lora(wrk_model_builder* b, uint32_t* index) {
     WRK_REQUIRE(b && index, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(b->shard_world == 1, WRK_ERR_UNSUPPORTED, "LoRA blending is not built for split models: merge first, then split");
     b->loras.emplace_back();
     *index = (uint32_t)b->loras.size() - 1;
     return WRK_OK;
@@ -612,10 +754,11 @@ int32_t wrk_model_builder_build(wrk_model_builder* b, wrk_model** out) {
         const size_t def_rescale = m->info.version == 7 ? 1024 : 6;  // Model::DEFAULT_RESCALE
         m->rescale = b->rescale ? b->rescale : def_rescale;
         m->sep = b->sep ? b->sep : 1024;
-        WRK_REQUIRE(m->info.num_emb % m->info.num_head == 0, WRK_ERR_SHAPE, "num_emb %u not divisible by num_head %u",
-                    m->info.num_emb, m->info.num_head);
+        if (m->info.num_emb % m->info.num_head != 0)
+            s = set_error(WRK_ERR_SHAPE, "num_emb %u not divisible by num_head %u", m->info.num_emb, m->info.num_head);
+        if (s == WRK_OK && b->shard_world > 1) s = plan_shard(b, m);
         Loader ld{b, b->ctx};
-        s = build_common(ld, m);
+        if (s == WRK_OK) s = build_common(ld, m);
         if (s == WRK_OK) s = m->info.version == 7 ? build_v7(ld, m) : build_v56(ld, m);
     }
     if (s != WRK_OK) {

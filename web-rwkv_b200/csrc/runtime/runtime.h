@@ -106,11 +106,29 @@ RnnIter make_iter(const wrk_rnn_input& in);
 }
 }  // namespace wrk
 
+namespace wrk {
+namespace rt {
+// One rank's part of a model split across GPUs: time-mix channels [c0, c1) (whole heads), FFN columns [f0, f1)
+// and vocabulary rows [v0, v1); world == 1 means the whole model.
+struct Shard {
+    uint32_t rank = 0, world = 1;
+    uint32_t c0 = 0, c1 = 0, f0 = 0, f1 = 0, v0 = 0, v1 = 0;
+    bool on() const { return world > 1; }
+};
+// `world` contiguous ranges over `total`, each a whole number of `align`-sized units, sizes differing by at most
+// one unit (larger ranges first).
+int32_t shard_range(const char* what, uint32_t total, uint32_t align, uint32_t world, uint32_t rank, uint32_t* begin, uint32_t* end);
+}  // namespace rt
+}  // namespace wrk
+
 struct wrk_model_builder {
     struct Entry {
         std::vector<uint64_t> shape;  // outermost first
         std::vector<uint16_t> data;   // fp16 bits
+        std::vector<uint64_t> full;   // shape before the rank's slice was cut (empty: not sliced)
     };
+    // sharded build: set before the first tensor is added; every tensor is cut to the rank's slice as it arrives
+    uint32_t shard_rank = 0, shard_world = 1, shard_head_size = 64, shard_block = 1;
     // `Lora` of src/runtime/loader.rs:104-113: named fp16 tensors and an ordered list of (pattern, alpha)
     struct Lora {
         std::map<std::string, Entry> tensors;
@@ -132,6 +150,7 @@ struct wrk_model {
     size_t rescale = 6;
     size_t sep = 1024;
     uint32_t num_vocab_padded = 0;
+    wrk::rt::Shard shard;  // info keeps the dimensions of the whole model
     wrk::rt::LayerNorm embed_ln, head_ln;
     uint16_t* embed_host = nullptr;  // pinned [num_vocab_padded][num_emb] fp16 (the reference keeps it on the CPU)
     wrk::rt::MatrixH head_w;

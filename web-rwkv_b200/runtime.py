@@ -55,6 +55,12 @@ class ModelBuilder:
             check(lib().wrk_model_builder_lora_blend(self.handle, index, pattern.encode(), ctypes.c_float(a)))
         return self
 
+    def shard(self, rank, world, head_size=64, block=1):
+        """Keep rank `rank`'s part of a model split `world` ways (`wrk_model_builder_shard`): before any tensor.
+        block: 128 when any layer is Int8, 64 for NF4 / SF4, 1 for fp16."""
+        check(lib().wrk_model_builder_shard(self.handle, rank, world, head_size, block))
+        return self
+
     def quant(self, mapping):
         for layer, q in mapping.items():
             check(lib().wrk_model_builder_quant(self.handle, layer, q))
@@ -207,10 +213,14 @@ def redirect(info):
 class Bundle:
     """`Bundle<f16>` + `State` (src/runtime/v6.rs:489-521, src/runtime/model.rs:78-120)."""
 
-    def __init__(self, model, num_batch):
-        self.model, self.num_batch = model, num_batch
+    def __init__(self, model, num_batch, comm=None):
+        """comm: the communicator of a split model's rank (`wrk_bundle_create_sharded`)."""
+        self.model, self.num_batch, self.comm = model, num_batch, comm
         self.handle = ctypes.c_void_p()
-        check(lib().wrk_bundle_create(model.handle, num_batch, ctypes.byref(self.handle)))
+        if comm is None:
+            check(lib().wrk_bundle_create(model.handle, num_batch, ctypes.byref(self.handle)))
+        else:
+            check(lib().wrk_bundle_create_sharded(model.handle, num_batch, comm.handle, ctypes.byref(self.handle)))
         info = model.info
         self.vocab = (info.num_vocab + 7) // 8 * 8 if info.version != 5 else info.num_vocab
 
