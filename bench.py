@@ -287,6 +287,115 @@ def device_decode(wrk, rt, ctx, bundle, embeds, decode, steps, warmup, sync):
     return ms, ctx.launch_count() - launches0, job.num_kernels()
 
 
+TP_CONFIG, TP_BATCH = "v7-7b", 64
+
+
+def tp_only(args):
+    """The split-model leg alone, for profiling: `python bench.py --tp-only [--tp-layers 2] --steps K` (one GPU) or under
+    torch.distributed.run."""
+    rank, local_rank, world = (int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("LOCAL_RANK", "0"), ("WORLD_SIZE", "1")))
+    host_threads()
+    wrk = importlib.import_module("web-rwkv_b200")
+    rt = importlib.import_module("web-rwkv_b200.runtime")
+    synth = importlib.import_module("web-rwkv_b200.synth")
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = wrk.Context(local_rank)
+    out = tp_leg(wrk, rt, synth, ctx, rank, world, dist, args.steps, args.tp_layers or None)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps({"tp": out, "n_gpus": world}))
+
+
+def tp_leg(wrk, rt, synth, ctx, rank, world, dist, steps, layers=None):
+    """BASELINE config 4 (v7 7B-shaped, all layers Int8, 64 sequences decoding in step) as ONE model split over
+    the ranks: time-mix heads and FFN columns sharded, one all-reduce after `output` and one after ffn `value`
+    per layer, vocabulary slices gathered.  Strong scaling: the work is fixed, the ranks divide it.  At one
+    GPU the same jobs run unsharded."""
+    import ctypes
+    version, C, L, F, V = synth.CONFIGS[TP_CONFIG]
+    L = layers or L
+    comm = None
+    builder = rt.ModelBuilder(ctx)
+    if world > 1:
+        tp = importlib.import_module("web-rwkv_b200.tp")
+        uid = [tp.Comm.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        comm = tp.Comm(ctx, uid[0], rank, world)
+        builder.shard(rank, world, 64, 128)
+    t0 = time.perf_counter()
+    for name, arr in synth.iter_tensors(TP_CONFIG, SEED_WEIGHTS + 4, L):
+        builder.add_tensor(name, arr)
+    builder.quant({i: wrk.QUANT_INT8 for i in range(L)})
+    model = builder.build()
+    del builder
+    ctx.synchronize()
+    build_s = time.perf_counter() - t0
+    bundle = rt.Bundle(model, TP_BATCH, comm)
+    rng = np.random.default_rng(SEED_TOKENS + 4)  # the same tokens on every rank
+    first = rng.integers(0, V - 1, TP_BATCH).tolist()
+    inp = rt.RnnInput([([t], wrk.RNN_LAST) for t in first], TP_BATCH)
+    logits = np.empty((TP_BATCH, bundle.vocab), dtype=np.float32)
+    out = bundle.infer(inp, logits)
+    checksum = float(np.abs(np.concatenate([o for o in out if o.size])).sum())
+    job = bundle.dispatch([(1, wrk.RNN_LAST)] * TP_BATCH)
+    tokens = rng.integers(0, V - 1, (16, TP_BATCH)).astype(np.uint32)
+
+    def sync():
+        ctx.synchronize()
+        if dist is not None:
+            import torch
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def run(n):
+        for i in range(n):
+            job.load(tokens[i % 16])
+            job.submit()
+
+    run(3)
+    sync()
+    ctx.timer_start()
+    run(steps)
+    ms = ctx.timer_stop()
+    sync()
+    ms = max_over_ranks(ms, dist)
+    result = {"workload": f"RWKV-v7-shaped {TP_CONFIG} random-init (n_embd {C}, {L} layers, FFN {F}, vocab {V}), all layers Int8, "
+                          f"{TP_BATCH} sequences, one token each per step, host tokens in; one model split over the ranks",
+              "value": steps * TP_BATCH / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms / steps, "steps": steps,
+              "scaling": "strong", "parallelism": f"tp{world}" if world > 1 else "single GPU", "model_build_s": build_s,
+              "kernels_per_step": job.num_kernels(), "logit_abs_sum_first_job": checksum}
+    if comm is not None:
+        # the collectives of one step alone, on the same communicator and sizes: 2 per layer of [C, 64] f32, plus the gather
+        part = ctx.tensor(wrk.F32, [C, TP_BATCH], zeros=True)
+        op = wrk.op_list([comm.all_reduce(part) for _ in range(2 * L)])
+        cmd = ctx.encode(op, use_graph=True)
+        for _ in range(3):
+            cmd.submit()
+        sync()
+        ctx.timer_start()
+        for _ in range(steps):
+            cmd.submit()
+        ar_ms = max_over_ranks(ctx.timer_stop(), dist)
+        sync()
+        result["all_reduce"] = {"per_step_ms": ar_ms / steps, "share_of_step": ar_ms / ms, "count_per_step": 2 * L,
+                                "bytes_each": C * TP_BATCH * 4, "kind": "NCCL all-reduce on the job's stream, NVLS off"}
+        del cmd, op, part
+    del job, bundle, model
+    if comm is not None:
+        import gc
+        gc.collect()
+        del comm
+        gc.collect()
+    return result
+
+
 def check_fused_against_strict(wrk, rt, model, prompt, vocab, mode):
     """One decoded token after the prompt through the fused job and through the op-by-op job."""
     outs = []
@@ -406,6 +515,9 @@ def main():
     ap.add_argument("--strict", action="store_true", help="one launch per reference op (no fused kernels)")
     ap.add_argument("--fused", type=int, default=2, choices=[1, 2, 3],
                     help="decode job: 2 = one launch per fused phase (default), 1 = one persistent kernel, 3 = persistent, mma.sync only")
+    ap.add_argument("--tp-only", action="store_true", help="only the split-model leg (for profiles); --tp-layers cuts the model")
+    ap.add_argument("--tp-layers", type=int, default=0)
+    ap.add_argument("--no-tp", action="store_true", help="skip the split-model leg (v7 7B-shaped, 64 sequences)")
     ap.add_argument("--no-serialize", action="store_true", help="skip the save / load timing of the quantized model")
     ap.add_argument("--sweep", choices=["matmul", "wkv"], help="op-level sweep instead of the model benchmark")
     ap.add_argument("--kind", default="int8,nf4,fp16")
@@ -418,6 +530,8 @@ def main():
 
     if args.sweep:
         return sweep(args)
+    if args.tp_only:
+        return tp_only(args)
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -533,6 +647,14 @@ def main():
         prefill = {"value": reps * chunk / (time.perf_counter() - t0), "unit": "tokens/s",
                    "workload": f"{chunk}-token chunk of the same model, host tokens in, last-token logits out"}
 
+    # ---- one model split over the ranks (BASELINE config 4), at every N ----
+    tp = None
+    if not args.no_tp:
+        try:
+            tp = tp_leg(wrk, rt, synth, ctx, rank, world, dist, max(args.steps, 3) * 8)
+        except Exception as e:  # the headline stands on its own
+            tp = {"failed": str(e)[:300]}
+
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -584,6 +706,7 @@ def main():
                 "h2d_bytes_per_step": args.decode * (C * 2 + 12), "d2h_bytes_per_step": args.decode * ((V + 7) // 8 * 8) * 4},
         "parity": checked,
         "prefill": prefill,
+        "tp": tp,
         "decode_1p6b": secondary,
         "gpu_launches": int(gpu_launches),
         "kernels_per_token": int(kernels_per_token),

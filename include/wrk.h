@@ -201,6 +201,10 @@ int32_t wrk_op_l2_norm(wrk_tensor* x, float eps, wrk_op** out);
 /* TensorOp::token_shift(cursors, time_mix, state, input, output, reversed), src/tensor/ops.rs:1393-1461 */
 int32_t wrk_op_token_shift(wrk_tensor* cursors, const wrk_view* time_mix, const wrk_view* state,
                            wrk_tensor* input, wrk_tensor* output, int32_t reversed, wrk_op** out);
+/* No counterpart in the reference, where the time-mix and channel-mix shaders store this row themselves
+ * (src/shaders/time_mix_v6.wgsl:100, channel_mix.wgsl:98): state row 0 of every sequence with tokens in the job <- x at
+ * that sequence's last token.  A rank of a split model uses it for the channels its time-mix op does not own. */
+int32_t wrk_op_shift_carry(wrk_tensor* cursors, const wrk_view* state, wrk_tensor* x, wrk_op** out);
 /* TensorOp::channel_mix(cursors, state, r, v, x), src/tensor/ops.rs:1860-1915 */
 int32_t wrk_op_channel_mix(wrk_tensor* cursors, const wrk_view* state, wrk_tensor* r, wrk_tensor* v,
                            wrk_tensor* x, wrk_op** out);

@@ -121,6 +121,13 @@ int32_t wrk_state_num_batch(wrk_bundle* b, uint32_t* num_batch);                
 int32_t wrk_state_init_shape(wrk_bundle* b, uint32_t shape[4]);                  /* State::init_shape */
 int32_t wrk_state_load(wrk_bundle* b, const float* host, size_t bytes, uint32_t batch); /* State::load */
 int32_t wrk_state_back(wrk_bundle* b, uint32_t batch, float* host, size_t bytes);       /* State::back */
+/* State::write / State::read (src/runtime/model.rs:98-100; v6: src/runtime/v6.rs:223-258): a batch slot from / to a
+ * device tensor f32 [C, S + 2, L], ordered on the context's stream (no host wait); `read` returns a new tensor. */
+int32_t wrk_state_write(wrk_bundle* b, wrk_tensor* tensor, uint32_t batch);
+int32_t wrk_state_read(wrk_bundle* b, uint32_t batch, wrk_tensor** out);
+/* State::embed (src/runtime/model.rs:102; v6: src/runtime/v6.rs:260-262): row 0 of layer `layer` of a state read back
+ * with wrk_state_back, C floats. */
+int32_t wrk_state_embed(wrk_bundle* b, uint32_t layer, const float* backed, size_t bytes, float* embed, size_t embed_bytes);
 /* The per-layer state tensor [C, S + 2, num_batch] (borrowed), as State::att / State::ffn slice it. */
 int32_t wrk_state_layer(wrk_bundle* b, uint32_t layer, wrk_tensor** out);
 

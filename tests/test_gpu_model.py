@@ -162,6 +162,86 @@ def test_state_load_back_and_errors(ctx):
     assert e.value.status in (-20, -21)
 
 
+def test_state_write_read_embed(ctx):
+    # State::write / read / embed (src/runtime/model.rs:98-102, src/runtime/v6.rs:223-262): device-to-device hand-off
+    tensors, model, ref = _build(ctx, "v6-tiny", {})
+    bundle = rt.Bundle(model, 3)
+    V = model.info.num_vocab
+    rng = np.random.default_rng(11)
+    bundle.infer(rt.RnnInput([(rng.integers(0, V - 1, 9).tolist(), LAST), ([], LAST), ([], LAST)], 32))
+    want = bundle.state_back(0)
+    assert np.abs(want).max() > 0
+    moved = bundle.state_read(0)                       # slot 0 as a device tensor [C, S + 2, L]
+    assert moved.shape[:3] == [256, 66, 3]
+    assert np.array_equal(moved.numpy().reshape(3, 66, 256), want)
+    bundle.state_write(moved, 2)                       # ... into slot 2, no host copy
+    assert np.array_equal(bundle.state_back(2), want)
+    assert (bundle.state_back(1) == 0).all()
+    for layer in range(3):
+        assert np.array_equal(bundle.state_embed(layer, want), want[layer, 0])
+    # the copied slot continues exactly like the original
+    tok = int(rng.integers(0, V - 1))
+    out = bundle.infer(rt.RnnInput([([tok], LAST), ([], LAST), ([tok], LAST)], 32))
+    assert np.array_equal(out[0], out[2])
+    wrk = importlib.import_module("web-rwkv_b200")
+    with pytest.raises(wrk.WrkError) as e:
+        bundle.state_write(moved, 3)
+    assert e.value.status == -7
+    with pytest.raises(wrk.WrkError) as e:
+        bundle.state_write(ctx.tensor(wrk.F32, [256, 66, 2], zeros=True), 0)
+    assert e.value.status == -5
+    with pytest.raises(wrk.WrkError) as e:
+        bundle.state_embed(3, want)
+    assert e.value.status == -8
+    assert ctx.device_status() == 0
+
+
+def test_two_jobs_of_one_shape_dispatched_before_back(ctx):
+    # the reference dispatches the next job while the current one runs (src/runtime/mod.rs:215-260): two live jobs of
+    # the same (tokens, header rows) but different per-batch lengths keep their own output ranges
+    tensors, model, ref = _build(ctx, "v6-tiny", {0: 1})
+    bundle = rt.Bundle(model, 2)
+    V = model.info.num_vocab
+    first = bundle.dispatch([(2, FULL), (0, FULL)])
+    second = bundle.dispatch([(1, FULL), (1, FULL)])
+    first.load([5, 6])
+    first.submit()
+    got_first = [g.copy() for g in first.back()]
+    second.load([7, 8])
+    second.submit()
+    got_second = [g.copy() for g in second.back()]
+    assert [g.shape[0] for g in got_first] == [2, 0]
+    assert [g.shape[0] for g in got_second] == [1, 1]
+    state = ref.init_state(2)
+    want_first = ref.run(state, [[5, 6], []], [(2, FULL), (0, FULL)])
+    want_second = ref.run(state, [[7], [8]], [(1, FULL), (1, FULL)])
+    assert_close(got_first[0], want_first[0], "first job")
+    assert_close(got_second[0], want_second[0], "second job, batch 0")
+    assert_close(got_second[1], want_second[1], "second job, batch 1")
+
+
+def test_second_context_on_another_device(ctx):
+    # shared-memory opt-ins are per device: the first launches of every kernel family on a second GPU
+    import subprocess
+    if subprocess.run(["nvidia-smi", "-L"], capture_output=True, text=True).stdout.count("GPU ") < 2:
+        pytest.skip("needs two GPUs")
+    wrk = importlib.import_module("web-rwkv_b200")
+    other = wrk.Context(1)
+    tensors = synth.make_model("v6-tiny", seed=1000)
+    outs = []
+    for c in (ctx, other):
+        model = rt.ModelBuilder(c).add_tensors(tensors).quant({0: 1, 1: 2}).build()
+        bundle = rt.Bundle(model, 1)
+        prompt = rt.RnnInput([(list(range(1, 41)), LAST)], 64)   # GEMM path
+        while prompt.num_token():
+            out = bundle.infer(prompt)[0].copy()
+        prompt.append(0, [3])
+        outs.append((out, bundle.infer(prompt)[0].copy()))      # fused decode path
+        assert c.device_status() == 0
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+    other.synchronize()
+
+
 def test_config1_v6_0p1b_int8_256_tokens_chunk_32(ctx):
     # BASELINE config 1: n_embd 768, 12 layers, FFN 2688, vocab 65536, all layers Int8, one sequence of
     # 256 uniform-random tokens, token_chunk_size 32, num_batch 1

@@ -91,6 +91,8 @@ cudaError_t blend(const float* factor, DView input, DView output, cudaStream_t s
 cudaError_t blend_lora(const float* factor, DView xa, DView xb, DView output, uint32_t K, cudaStream_t stream);
 cudaError_t token_shift(const uint32_t* cursors, int wide, DView time_mix, DView state, DView input, DView output,
                         int reversed, cudaStream_t stream);
+cudaError_t shift_carry(const uint32_t* cursors, int wide, DView state, int dtype, const void* x, uint32_t C, uint32_t T,
+                        cudaStream_t stream);
 cudaError_t channel_mix(const uint32_t* cursors, int wide, DView state, int dtype, const void* r, const void* v,
                         void* x, uint32_t C, uint32_t T, int v7, cudaStream_t stream);
 cudaError_t binary(int is_mul, DView input, DView output, int act_x, int act_y, int act_out, cudaStream_t stream);

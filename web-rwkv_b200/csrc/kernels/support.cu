@@ -216,6 +216,17 @@ __global__ void channel_mix_kernel(const uint32_t* cursors, int wide, DView stat
     }
 }
 
+// The shift row of every sequence that has tokens in the job <- x at the sequence's last token (what the time-mix
+// and channel-mix ops do for their own channels, as an op of its own).
+__global__ void shift_carry_kernel(const uint32_t* cursors, int wide, DView state, int dtype, const void* x, uint32_t C, uint32_t T) {
+    const size_t total = (size_t)C * T;
+    for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t c = o % C, t = o / C;
+        const CursorD cu = cursor_at(cursors, wide, t);
+        if (t - cu.token + 1u == cu.len) static_cast<float*>(state.base)[state.index(c, 0, cu.batch)] = dload(x, dtype, o);
+    }
+}
+
 __global__ void binary_kernel(int is_mul, DView in, DView out, int act_x, int act_y, int act_out) {
     const uint32_t C = out.shape[0], T = out.shape[1], B = out.shape[2];
     const size_t total = (size_t)C * T * B;
@@ -357,6 +368,14 @@ cudaError_t token_shift(const uint32_t* cursors, int wide, DView time_mix, DView
     const size_t total = (size_t)output.shape[0] * output.shape[1] * output.shape[2];
     if (total == 0) return cudaSuccess;
     token_shift_kernel<<<ew_grid(total), kEw, 0, stream>>>(cursors, wide, time_mix, state, input, output, reversed);
+    return cudaGetLastError();
+}
+
+cudaError_t shift_carry(const uint32_t* cursors, int wide, DView state, int dtype, const void* x, uint32_t C, uint32_t T,
+                        cudaStream_t stream) {
+    const size_t total = (size_t)C * T;
+    if (total == 0) return cudaSuccess;
+    shift_carry_kernel<<<ew_grid(total), kEw, 0, stream>>>(cursors, wide, state, dtype, x, C, T);
     return cudaGetLastError();
 }
 

@@ -619,6 +619,25 @@ static int32_t channel_mix_common(const char* name, int v7, wrk_tensor* cursors,
     return WRK_OK;
 }
 
+int32_t wrk_op_shift_carry(wrk_tensor* cursors, const wrk_view* state, wrk_tensor* x, wrk_op** out) {
+    REQ_NN(cursors, state, state->tensor, x, out);
+    REQ_FLOAT(x, "x");
+    REQ_DTYPE(state->tensor, WRK_F32, "state");
+    const Shape4 sh = x->shape;
+    WRK_TRY(check_shape("x", sh, sh[0], sh[1], 1, 1));
+    WRK_TRY(check_view("state", state, sh[0], 1, state->shape[2], 1));
+    WRK_TRY(check_cursors(cursors, sh[1]));
+    const uint32_t* cp = static_cast<const uint32_t*>(cursors->ptr());
+    const int wide = cursors_wide(cursors, sh[1]);
+    DView st = make_dview(*state);
+    const void* xp = x->ptr();
+    const int dt = x->dtype;
+    const uint32_t C = sh[0], T = sh[1];
+    *out = new_atom("shift_carry", [=](cudaStream_t s) { return k::shift_carry(cp, wide, st, dt, xp, C, T, s); },
+                    {cursors, state->tensor, x});
+    return WRK_OK;
+}
+
 int32_t wrk_op_channel_mix(wrk_tensor* cursors, const wrk_view* state, wrk_tensor* r, wrk_tensor* v, wrk_tensor* x,
                            wrk_op** out) {
     return channel_mix_common("channel_mix", 0, cursors, state, r, v, x, out);

@@ -47,7 +47,6 @@ struct wrk_bundle {
     uint32_t num_batch = 0;
     std::vector<TensorH> state;  // per layer f32 [C, S + 2, num_batch]
     wrk_comm* comm = nullptr;  // a rank of a split model: sums of partial products cross this communicator
-    std::vector<std::pair<uint32_t, uint32_t>> building_last;  // (batch, its last token's row) of the job being built
     bool packed_cursors = false, use_graph = true, fused = true;
     bool step_kernel = false;  // fused jobs of at most 8 tokens run as one persistent kernel where the job shape allows it
     int step_engine = 1;      // 1: tensor-core kernel where the matrices allow it; 3: always the mma.sync kernel
@@ -270,13 +269,8 @@ int32_t reduce_partial(wrk_bundle* bd, OpList& ops, const Buffers& B, wrk_tensor
 // channels only; the next job's token shifts read all of them.
 int32_t carry_all_channels(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, uint32_t S) {
     (void)S;
-    for (const auto& bt : bd->building_last) {
-        wrk_view in = Vy(B["att_x"], bt.second, bt.second + 1);
-        wrk_view out = Vy(bd->state[index], 0, 1);
-        out.shape[2] = 1;
-        out.offset[2] = bt.first;
-        WRK_TRY(blit(ops, in, out));
-    }
+    const wrk_view row0 = Vy(bd->state[index], 0, 1);
+    ADD(wrk_op_shift_carry(B["cursors"], &row0, B["att_x"], &_o));
     return WRK_OK;
 }
 
@@ -981,15 +975,6 @@ int32_t build_job(wrk_bundle* bd, const RnnInfo& info, CachedJob* job) {
     const Buffers& Hd = *job->header;
     OpList ops;
     const bool fused = fused_v6_supported(bd, T);
-    bd->building_last.clear();
-    {
-        uint32_t row = 0;
-        for (uint32_t batch = 0; batch < info.lens.size(); ++batch) {
-            if (info.lens[batch] > 0) bd->building_last.emplace_back(batch, row + info.lens[batch] - 1);
-            row += info.lens[batch];
-        }
-    }
-
     // the whole job as one persistent kernel (launched eagerly: a memset of the barrier word and one cooperative
     // launch per job need no graph)
     if (fused && bd->step_kernel && NH <= (uint32_t)k::kDecodeMaxTokens) {
@@ -1248,6 +1233,64 @@ int32_t wrk_state_back(wrk_bundle* b, uint32_t batch, float* host, size_t bytes)
         WRK_CUDA(cudaMemcpyAsync(host + l * per_layer, static_cast<float*>(b->state[l].p->ptr()) + batch * per_layer,
                                  per_layer * 4, cudaMemcpyDeviceToHost, ctx->stream));
     WRK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return WRK_OK;
+}
+
+// State::write, v6.rs:223-239: a device tensor [C, S + 2, L] into one batch slot, stream-ordered (no host wait)
+int32_t wrk_state_write(wrk_bundle* b, wrk_tensor* tensor, uint32_t batch) {
+    WRK_REQUIRE(b && tensor, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    const wrk_model_info& info = b->model->info;
+    const uint32_t S = info.num_emb / info.num_head;
+    WRK_REQUIRE(tensor->dtype == WRK_F32, WRK_ERR_TYPE, "data type mismatch: the state is f32");
+    WRK_TRY(check_shape("state", tensor->shape, info.num_emb, S + 2, info.num_layer, 1));
+    WRK_REQUIRE(tensor->ctx == b->model->ctx, WRK_ERR_INVALID_ARGUMENT, "tensor and bundle belong to different contexts");
+    if (batch >= b->num_batch)
+        return set_error(WRK_ERR_BATCH_OUT_OF_RANGE, "batch %u out of range of max %u", batch, b->num_batch);
+    const size_t per_layer = (size_t)info.num_emb * (S + 2);
+    wrk_context* ctx = b->model->ctx;
+    for (uint32_t l = 0; l < info.num_layer; ++l)
+        WRK_CUDA(cudaMemcpyAsync(static_cast<float*>(b->state[l].p->ptr()) + batch * per_layer,
+                                 static_cast<const float*>(tensor->ptr()) + l * per_layer, per_layer * 4, cudaMemcpyDeviceToDevice,
+                                 ctx->stream));
+    return WRK_OK;
+}
+
+// State::read, v6.rs:241-258: one batch slot as a new device tensor [C, S + 2, L]
+int32_t wrk_state_read(wrk_bundle* b, uint32_t batch, wrk_tensor** out) {
+    WRK_REQUIRE(b && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    const wrk_model_info& info = b->model->info;
+    const uint32_t S = info.num_emb / info.num_head;
+    if (batch >= b->num_batch)
+        return set_error(WRK_ERR_BATCH_OUT_OF_RANGE, "batch %u out of range of max %u", batch, b->num_batch);
+    const uint32_t shape[4] = {info.num_emb, S + 2, info.num_layer, 1};
+    wrk_tensor* t = nullptr;
+    WRK_TRY(wrk_tensor_create(b->model->ctx, WRK_F32, shape, &t));
+    const size_t per_layer = (size_t)info.num_emb * (S + 2);
+    wrk_context* ctx = b->model->ctx;
+    for (uint32_t l = 0; l < info.num_layer; ++l) {
+        const cudaError_t e = cudaMemcpyAsync(static_cast<float*>(t->ptr()) + l * per_layer,
+                                              static_cast<const float*>(b->state[l].p->ptr()) + batch * per_layer, per_layer * 4,
+                                              cudaMemcpyDeviceToDevice, ctx->stream);
+        if (e != cudaSuccess) {
+            wrk_tensor_release(t);
+            return set_error(WRK_ERR_CUDA, "cudaMemcpyAsync failed: %s", cudaGetErrorString(e));
+        }
+    }
+    *out = t;
+    return WRK_OK;
+}
+
+// State::embed, v6.rs:260-262: row 0 (the time-mix shift row) of one layer of a backed state
+int32_t wrk_state_embed(wrk_bundle* b, uint32_t layer, const float* backed, size_t bytes, float* embed, size_t embed_bytes) {
+    WRK_REQUIRE(b && backed && embed, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    const wrk_model_info& info = b->model->info;
+    const size_t per_layer = (size_t)info.num_emb * (info.num_emb / info.num_head + 2);
+    WRK_REQUIRE(bytes == per_layer * info.num_layer * 4, WRK_ERR_SIZE, "data size not match: %zu vs. %zu", bytes,
+                per_layer * info.num_layer * 4);
+    WRK_REQUIRE(embed_bytes == (size_t)info.num_emb * 4, WRK_ERR_SIZE, "data size not match: %zu vs. %zu", embed_bytes,
+                (size_t)info.num_emb * 4);
+    if (layer >= info.num_layer) return set_error(WRK_ERR_SLICE_OUT_OF_RANGE, "layer %u out of range of %u", layer, info.num_layer);
+    std::memcpy(embed, backed + layer * per_layer, embed_bytes);
     return WRK_OK;
 }
 

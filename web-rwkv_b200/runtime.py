@@ -254,6 +254,24 @@ class Bundle:
         check(lib().wrk_state_back(self.handle, batch, arr.ctypes.data_as(ctypes.c_void_p), ctypes.c_size_t(arr.nbytes)))
         return arr
 
+    def state_read(self, batch):
+        """State::read: the slot as a device tensor [C, S + 2, L]."""
+        h = ctypes.c_void_p()
+        check(lib().wrk_state_read(self.handle, batch, ctypes.byref(h)))
+        return Tensor(self.model.ctx, h)
+
+    def state_write(self, tensor, batch):
+        """State::write: a device tensor [C, S + 2, L] into the slot."""
+        check(lib().wrk_state_write(self.handle, tensor.handle, batch))
+
+    def state_embed(self, layer, backed):
+        """State::embed: the shift row of one layer of a backed state."""
+        backed = np.ascontiguousarray(backed, dtype=np.float32)
+        out = np.empty(backed.shape[-1], dtype=np.float32)
+        check(lib().wrk_state_embed(self.handle, layer, backed.ctypes.data_as(ctypes.c_void_p), ctypes.c_size_t(backed.nbytes),
+                                    out.ctypes.data_as(ctypes.c_void_p), ctypes.c_size_t(out.nbytes)))
+        return out
+
     def state_load(self, arr, batch):
         arr = np.ascontiguousarray(arr, dtype=np.float32)
         check(lib().wrk_state_load(self.handle, arr.ctypes.data_as(ctypes.c_void_p), ctypes.c_size_t(arr.nbytes), batch))
