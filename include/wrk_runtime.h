@@ -22,7 +22,7 @@ typedef struct wrk_rnn_iter wrk_rnn_iter;           /* `RnnIter`, src/runtime/in
 typedef struct wrk_job wrk_job;                     /* `RnnJob`, src/runtime/v6.rs:408-477 */
 
 /* `ModelInfo`, src/runtime/model.rs:24-76 (+ `ModelCustomInfo`: v6 {time_mix, time_decay},
- * v7 {w, a, g, v}). version is 5, 6 or 7. */
+ * v7 {w, a, g, v}). version is 4, 5, 6 or 7 (v4 counts one head: src/runtime/loader.rs:290-294). */
 typedef struct {
     uint32_t version;
     uint32_t num_layer;
@@ -69,7 +69,7 @@ int32_t wrk_model_builder_sep(wrk_model_builder* b, uint32_t value);            
 int32_t wrk_model_builder_read_state(wrk_model_builder* b, float* host, size_t bytes);
 /* Loader::info (src/runtime/loader.rs:208-324) on the tensors added so far. */
 int32_t wrk_model_builder_info(wrk_model_builder* b, wrk_model_info* info);
-/* ModelBuilder::build_v5 / build_v6 / build_v7 (src/runtime/v5.rs:922-1082, v6.rs:995-1172,
+/* ModelBuilder::build_v4 / build_v5 / build_v6 / build_v7 (src/runtime/v4.rs:829-960, v5.rs:922-1082, v6.rs:995-1172,
  * v7.rs:1038-1226), chosen by the version Loader::info finds. */
 int32_t wrk_model_builder_build(wrk_model_builder* b, wrk_model** out);
 
@@ -110,6 +110,41 @@ int32_t wrk_bundle_set_use_graph(wrk_bundle* b, int32_t use_graph);
  * tensor materialised with the reference's dtypes.  No counterpart in the reference, whose jobs are always one
  * pass per op (src/runtime/v6.rs:560-900). */
 int32_t wrk_bundle_set_fused(wrk_bundle* b, int32_t fused);
+
+/* ---- Hooks (`Hook` and `HookMap` of each version: src/runtime/v4.rs:304-330, v5.rs:330-358, v6.rs:366-406,
+ * v7.rs:385-425; called through `hook_op`, src/runtime/v6.rs:572-581) ----
+ * A hook is a callback that, while a job is being built, may return one op to insert at its point of the layer's op
+ * list (or leave *op null: TensorOp::empty()).  It sees the job's `Frame` (src/runtime/v6.rs:479-487): runtime buffers
+ * by the reference's field name ("x", "att_x", "att_k", "ffn_k", ... of `Runtime`, src/runtime/v6.rs:305-345; "head_x",
+ * "head_o" of `Header`), and the state through wrk_state_layer.  The enum is the union of the four versions' hooks; a
+ * point a version does not have is never reached.  `layer` is ignored for the embed / head hooks.  While a bundle
+ * has any hook, its jobs are built one launch per reference op (the fused kernels have no such points); setting or
+ * clearing a hook drops the cached jobs.  fn == NULL clears the hook. */
+typedef enum {
+    WRK_HOOK_POST_EMBED_LOADED = 0, WRK_HOOK_POST_EMBED_LAYER_NORM,
+    WRK_HOOK_PRE_ATT, WRK_HOOK_POST_ATT_LAYER_NORM, WRK_HOOK_PRE_ATT_TOKEN_SHIFT, WRK_HOOK_POST_ATT_TOKEN_SHIFT,
+    WRK_HOOK_PRE_ATT_TOKEN_SHIFT_ADAPT, WRK_HOOK_POST_ATT_TOKEN_SHIFT_ADAPT_ACTIVATE, WRK_HOOK_POST_ATT_TOKEN_SHIFT_ADAPT,
+    WRK_HOOK_PRE_ATT_GATED_TOKEN_SHIFT, WRK_HOOK_POST_ATT_GATED_TOKEN_SHIFT,
+    WRK_HOOK_PRE_ATT_LINEAR, WRK_HOOK_POST_ATT_LINEAR,
+    WRK_HOOK_PRE_ATT_TIME_DECAY_ADAPT, WRK_HOOK_POST_ATT_TIME_DECAY_ADAPT_ACTIVATE, WRK_HOOK_POST_ATT_TIME_DECAY_ADAPT,
+    WRK_HOOK_PRE_ATT_TIME_DECAY_ACTIVATE, WRK_HOOK_POST_ATT_TIME_DECAY_ACTIVATE,
+    WRK_HOOK_PRE_ATT_ADAPT, WRK_HOOK_POST_ATT_ADAPT, WRK_HOOK_PRE_ATT_CONTROL, WRK_HOOK_POST_ATT_CONTROL,
+    WRK_HOOK_PRE_ATT_VALUE_RESIDUAL, WRK_HOOK_POST_ATT_VALUE_RESIDUAL,
+    WRK_HOOK_PRE_ATT_TIME_MIX, WRK_HOOK_POST_ATT_TIME_MIX, WRK_HOOK_PRE_ATT_GATE, WRK_HOOK_POST_ATT_GATE,
+    WRK_HOOK_PRE_ATT_OUT, WRK_HOOK_POST_ATT_OUT, WRK_HOOK_POST_ATT,
+    WRK_HOOK_PRE_FFN, WRK_HOOK_POST_FFN_LAYER_NORM, WRK_HOOK_PRE_FFN_TOKEN_SHIFT, WRK_HOOK_POST_FFN_TOKEN_SHIFT,
+    WRK_HOOK_PRE_FFN_LINEAR, WRK_HOOK_POST_FFN_ACTIVATE, WRK_HOOK_POST_FFN_LINEAR,
+    WRK_HOOK_PRE_FFN_CHANNEL_MIX, WRK_HOOK_POST_FFN_CHANNEL_MIX, WRK_HOOK_POST_FFN,
+    WRK_HOOK_PRE_HEAD, WRK_HOOK_POST_HEAD_LAYER_NORM, WRK_HOOK_POST_HEAD,
+    WRK_HOOK_COUNT
+} wrk_hook;
+typedef struct wrk_frame wrk_frame; /* `Frame`, src/runtime/v6.rs:479-487: valid only inside the callback */
+typedef int32_t (*wrk_hook_fn)(void* user, const wrk_frame* frame, wrk_op** op);
+int32_t wrk_bundle_set_hook(wrk_bundle* b, int32_t hook, uint32_t layer, wrk_hook_fn fn, void* user);
+int32_t wrk_frame_bundle(const wrk_frame* frame, wrk_bundle** bundle);               /* Frame::state lives in the bundle */
+int32_t wrk_frame_num_token(const wrk_frame* frame, uint32_t* num_token, uint32_t* num_header);
+/* A buffer of the frame by field name; borrowed: valid while the job lives (ops built on it keep it alive). */
+int32_t wrk_frame_buffer(const wrk_frame* frame, const char* name, wrk_tensor** out);
 /* No counterpart in the reference (its profiler hooks are wgpu timestamp queries, commented out in
  * src/tensor/ops.rs:2600).  Makes the persistent decode kernel record the device's nanosecond timer when each CTA
  * starts (after the grid barrier) and ends every phase; max_phases = 0 switches it off.  Jobs built afterwards with
@@ -118,7 +153,10 @@ int32_t wrk_bundle_set_fused(wrk_bundle* b, int32_t fused);
 int32_t wrk_bundle_set_phase_timeline(wrk_bundle* b, uint32_t max_phases);
 int32_t wrk_job_phase_timeline(wrk_job* job, uint64_t* stamps, size_t capacity, uint32_t* num_phases, uint32_t* num_ctas);
 int32_t wrk_state_num_batch(wrk_bundle* b, uint32_t* num_batch);                 /* State::num_batch */
-int32_t wrk_state_init_shape(wrk_bundle* b, uint32_t shape[4]);                  /* State::init_shape */
+/* State::init_shape as [C, rows, L, 1] with rows = S + 2 (v5 / v6 / v7: src/runtime/v6.rs:163-168) or 5 (v4, whose
+ * reference shape [C, 5 L] is the same memory: src/runtime/v4.rs:158-161).  A new v4 bundle holds State::init's f32::MIN
+ * in the running-maximum row (src/runtime/v4.rs:163-180). */
+int32_t wrk_state_init_shape(wrk_bundle* b, uint32_t shape[4]);
 int32_t wrk_state_load(wrk_bundle* b, const float* host, size_t bytes, uint32_t batch); /* State::load */
 int32_t wrk_state_back(wrk_bundle* b, uint32_t batch, float* host, size_t bytes);       /* State::back */
 /* State::write / State::read (src/runtime/model.rs:98-100; v6: src/runtime/v6.rs:223-258): a batch slot from / to a

@@ -1,7 +1,7 @@
-"""Full-model CPU oracle: the v5 / v6 / v7 `run()` job of the reference, op by op.
+"""Full-model CPU oracle: the v4 / v5 / v6 / v7 `run()` job of the reference, op by op.
 
 TEST INFRASTRUCTURE ONLY (see oracle/wrk_oracle.cpp).  The op order, buffer dtypes (Bundle<f16>)
-and load-time transforms follow src/runtime/v5.rs:656-920, v6.rs:701-992, v7.rs:716-1036 and
+and load-time transforms follow src/runtime/v4.rs:630-829, v5.rs:656-920, v6.rs:701-992, v7.rs:716-1036 and
 src/runtime/loader.rs; every tensor the reference stores as fp16 is an fp16 numpy array here, so
 every rounding point of the reference is a rounding point of this oracle.  The reference has no
 model-level test: end-to-end logits parity is unpinned beyond this restatement.
@@ -43,11 +43,13 @@ class OracleModel:
         self.fast = fast
         quant = quant or {}
         names = set(t)
-        self.version = 7 if "blocks.0.att.x_r" in names else 6 if "blocks.0.att.time_mix_x" in names else 5
+        self.version = (7 if "blocks.0.att.x_r" in names else 6 if "blocks.0.att.time_mix_x" in names else
+                        5 if "blocks.0.att.gate.weight" in names else 4)
         self.L = 1 + max(int(n.split(".")[1]) for n in names if n.startswith("blocks."))
         self.V, self.C = t["emb.weight"].shape
         self.F = t["blocks.0.ffn.key.weight"].shape[0]
-        self.H = (t["blocks.0.att.r_k"] if self.version == 7 else t["blocks.0.att.time_first"]).shape[0]
+        # Loader::info: v4 counts one head (src/runtime/loader.rs:290-294)
+        self.H = 1 if self.version == 4 else (t["blocks.0.att.r_k"] if self.version == 7 else t["blocks.0.att.time_first"]).shape[0]
         self.S = self.C // self.H
         self.rescale = rescale if rescale is not None else (1024 if self.version == 7 else 6)
         f16 = lambda n: np.ascontiguousarray(t[n], dtype=np.float16).reshape(-1)
@@ -64,7 +66,8 @@ class OracleModel:
             L = {
                 "ln1": (f16(f"{blk}.ln1.weight"), f16(f"{blk}.ln1.bias")),
                 "ln2": (f16(f"{blk}.ln2.weight"), f16(f"{blk}.ln2.bias")),
-                "gn": (f16(f"{att}.ln_x.weight").reshape(self.H, self.S), f16(f"{att}.ln_x.bias").reshape(self.H, self.S)),
+                "gn": None if self.version == 4 else
+                      (f16(f"{att}.ln_x.weight").reshape(self.H, self.S), f16(f"{att}.ln_x.bias").reshape(self.H, self.S)),
                 "w_k": mat(f"{att}.key.weight"), "w_v": mat(f"{att}.value.weight"),
                 "w_r": mat(f"{att}.receptance.weight"),
                 "w_o": mat(f"{att}.output.weight", discount if discount != 1 else None),
@@ -75,6 +78,15 @@ class OracleModel:
                 L["w_g"] = mat(f"{att}.gate.weight")
                 L["ffn_r"] = mat(f"{ffn}.receptance.weight")
                 L["time_first"] = f16(f"{att}.time_first").astype(np.float32)
+                L["ffn_mix_k"], L["ffn_mix_r"] = f16(f"{ffn}.time_mix_k"), f16(f"{ffn}.time_mix_r")
+            if self.version == 4:
+                L["ffn_r"] = mat(f"{ffn}.receptance.weight")
+                L["time_first"] = f16(f"{att}.time_first").astype(np.float32)
+                td = f16(f"{att}.time_decay").astype(np.float32)
+                o.activate(td, o.ACT_OPPOSITE_EXP)  # load_vector_exp_f32: -exp(x), src/runtime/loader.rs:431-470
+                L["time_decay"] = td
+                for n in "kvr":
+                    L[f"mix_{n}"] = f16(f"{att}.time_mix_{n}")
                 L["ffn_mix_k"], L["ffn_mix_r"] = f16(f"{ffn}.time_mix_k"), f16(f"{ffn}.time_mix_r")
             if self.version == 5:
                 td = f16(f"{att}.time_decay").astype(np.float32)
@@ -101,7 +113,13 @@ class OracleModel:
             self.layers.append(L)
 
     def init_state(self, num_batch):
-        """per layer f32 (B, S + 2, C), zeros (State::init)."""
+        """per layer f32 (B, S + 2, C), zeros (State::init); v4: (B, 5, C) with the running-maximum row at f32::MIN
+        (src/runtime/v4.rs:163-180)."""
+        if self.version == 4:
+            st = [np.zeros((num_batch, 5, self.C), dtype=np.float32) for _ in range(self.L)]
+            for s in st:
+                s[:, 3, :] = np.finfo(np.float32).min
+            return st
         return [np.zeros((num_batch, self.S + 2, self.C), dtype=np.float32) for _ in range(self.L)]
 
     # -------------------------------------------------------------------------------------
@@ -130,9 +148,13 @@ class OracleModel:
         for i, L in enumerate(self.layers):
             st = state[i]
             st_att, st_ffn = o.View(st, y=(0, S + 1)), o.View(st, y=(S + 1, S + 2))
+            if self.version == 4:
+                st_att, st_ffn = o.View(st, y=(0, 4)), o.View(st, y=(4, 5))
             att_x = x.copy()
             o.layer_norm(*L["ln1"], att_x, LN_EPS, fast=fast)
-            if self.version == 7:
+            if self.version == 4:
+                self._att_v4(L, st_att, cursors, att_x, T, turbo)
+            elif self.version == 7:
                 self._att_v7(i, L, st_att, cursors, att_x, T, turbo)
             else:
                 self._att_v56(L, st_att, cursors, att_x, T, turbo)
@@ -150,7 +172,7 @@ class OracleModel:
                 L["ffn_v"].matmul(ffn_k, ffn_v, turbo=turbo, fast=fast)
                 o.channel_mix(cursors, st_ffn, None, ffn_v, ffn_x, v7=True)
             else:
-                rev = self.version == 6
+                rev = self.version == 6  # v4 and v5 mix in the other direction
                 ffn_kx, ffn_rx, ffn_r = f16z(1, T, C), f16z(1, T, C), f16z(T, C)
                 o.token_shift(cursors, L["ffn_mix_k"], st_ffn, ffn_x, ffn_kx, rev)
                 o.token_shift(cursors, L["ffn_mix_r"], st_ffn, ffn_x, ffn_rx, rev)
@@ -186,6 +208,23 @@ class OracleModel:
         return [logits[a:b] for a, b in outs]
 
     # -------------------------------------------------------------------------------------
+    def _att_v4(self, L, st_att, cursors, att_x, T, turbo):
+        """src/runtime/v4.rs:652-730.  att_x: LN'd input (T, C) f16; on return holds the WKV output (receptance applied)."""
+        fast, C = self.fast, self.C
+        f16z = lambda *s: np.zeros(s, dtype=np.float16)
+        kx, vx, rx = f16z(1, T, C), f16z(1, T, C), f16z(1, T, C)
+        o.token_shift(cursors, L["mix_k"], st_att, att_x, kx, False)
+        o.token_shift(cursors, L["mix_v"], st_att, att_x, vx, False)
+        o.token_shift(cursors, L["mix_r"], st_att, att_x, rx, False)
+        f32z = lambda *s: np.zeros(s, dtype=np.float32)
+        att_k, att_v, att_r = f32z(T, C), f32z(T, C), f32z(T, C)  # f32 buffers (src/runtime/v4.rs:234-256)
+        L["w_k"].matmul(kx[0], att_k, turbo=turbo, fast=fast)
+        L["w_v"].matmul(vx[0], att_v, turbo=turbo, fast=fast)
+        L["w_r"].matmul(rx[0], att_r, turbo=turbo, fast=fast)
+        aux = att_x.astype(np.float32)  # blit att_x -> aux_x (f32)
+        o.time_mix_v4(cursors, L["time_decay"], L["time_first"], st_att, att_k, att_v, att_r, aux, fast=fast)
+        att_x[...] = aux.astype(np.float16)  # blit aux_x -> att_x
+
     def _att_v56(self, L, st_att, cursors, att_x, T, turbo):
         """att_x: LN'd input (T, C) f16; on return holds the gated group-normed WKV output."""
         fast, C, S, H = self.fast, self.C, self.S, self.H

@@ -173,6 +173,35 @@ def test_batched_fp16(wrk, ctx):
     assert_close(t_y.numpy().reshape(B, T, M), want, "batched fp16")
 
 
+@pytest.mark.parametrize("k,m", [(4096, 64), (4096, 160), (2560, 128), (64, 4096), (128, 2560), (32, 256), (48, 1000), (256, 33)])
+@pytest.mark.parametrize("n", [9, 64, 100, 256])
+def test_low_rank_adapter_shapes(wrk, ctx, k, m, n):
+    # fp16 matrices with one small dimension at more tokens than the weight-streaming kernel takes: v6 time_mix_w1
+    # (C -> 160, tanh), time_decay_w1 / w2, v7 w1 / w2 (64), a, g (128), v (32); ragged rows and tokens.  A short K
+    # takes the small-tile kernel, a long K the tensor-memory kernel.
+    for act, out_dt in ((0, np.float32), (2, np.float16)):  # none; tanh
+        got, want = _run(wrk, ctx, "fp16", k, m, n, turbo=(n % 32 == 0), act=act, out_dt=out_dt, wscale=0.05, seed=k + m + n)
+        assert_close(got, want, f"fp16 {k}x{m} n={n} act={act}")
+    # two runs agree bit for bit
+    a, _ = _run(wrk, ctx, "fp16", k, m, n, turbo=False, seed=3)
+    b, _ = _run(wrk, ctx, "fp16", k, m, n, turbo=False, seed=3)
+    assert np.array_equal(a, b)
+
+
+def test_batched_low_rank_adapter_at_64_tokens(wrk, ctx):
+    # the v6 token-shift adapter's second matrix [32, C, 5] at a prefill chunk, on views of a larger buffer
+    K, M, T, B = 32, 2048, 64, 5
+    rng = np.random.default_rng(16)
+    w = (rng.standard_normal((B, M, K), dtype=np.float32) * 0.1).astype(np.float16)
+    x = rng.standard_normal((B, T, K), dtype=np.float32).astype(np.float16)
+    mat = wrk.Matrix.fp16(ctx.from_numpy(w))
+    t_x, t_y = ctx.from_numpy(x), ctx.tensor(wrk.F16, [M, T, B])
+    ctx.run(mat.matmul_op(t_x, t_y, turbo=True))
+    want = np.zeros((B, T, M), dtype=np.float16)
+    oracle.matmul(oracle.MAT_FP16, w, None, x, want, mode=1)
+    assert_close(t_y.numpy().reshape(B, T, M), want, "batched fp16, 64 tokens")
+
+
 def test_odd_k_falls_back(wrk, ctx):
     # K not a multiple of the quantization block: the shape-agnostic kernel takes over
     got, want = _run(wrk, ctx, "int8", 320, 64, 3, turbo=False, seed=1)

@@ -9,7 +9,7 @@ import pytest
 
 from oracle import model as omodel
 from oracle import oracle
-from tests.util import assert_close
+from tests.util import assert_close, assert_state_close
 
 pytestmark = pytest.mark.gpu
 
@@ -50,13 +50,14 @@ def _check(pairs, bundle, state):
     for b in range(bundle.num_batch):
         got_state = bundle.state_back(b)
         want_state = np.stack([s[b] for s in state])
-        assert_close(got_state, want_state, f"state batch {b}")
+        assert_state_close(got_state, want_state, f"state batch {b}")  # relative to each layer's scale
 
 
 @pytest.mark.parametrize("config,quant", [
     ("v6-tiny", {0: 1, 1: 2}),      # layer 0 Int8, layer 1 NF4, layer 2 fp16
     ("v5-tiny", {0: 1, 1: 2}),
     ("v7-tiny", {0: 1, 1: 2}),
+    ("v4-tiny", {0: 1, 1: 2}),      # src/runtime/v4.rs: per-channel WKV with a running maximum, state [C, 5, B]
     ("v6-tiny", {0: 3, 1: 3, 2: 2}),  # Quant::SF4 (Student-t code book, nu = 5) on layers 0-1
 ])
 def test_mixed_batches_chunked_prefill_then_decode(ctx, config, quant):
@@ -71,7 +72,7 @@ def test_mixed_batches_chunked_prefill_then_decode(ctx, config, quant):
     _check(pairs, bundle, state)
 
 
-@pytest.mark.parametrize("config", ["v6-tiny", "v5-tiny", "v7-tiny"])
+@pytest.mark.parametrize("config", ["v6-tiny", "v5-tiny", "v7-tiny", "v4-tiny"])
 @pytest.mark.parametrize("fused", [0, 1, 2, 3])  # op by op / one persistent kernel per job (tensor-core, where the matrices allow) / one launch per phase / persistent mma.sync kernel
 def test_decode_loop(ctx, config, fused):
     rng = np.random.default_rng(2002)
@@ -193,6 +194,54 @@ def test_state_write_read_embed(ctx):
     with pytest.raises(wrk.WrkError) as e:
         bundle.state_embed(3, want)
     assert e.value.status == -8
+    assert ctx.device_status() == 0
+
+
+def test_hooks_insert_ops_at_their_points(ctx):
+    # HookMap (src/runtime/v6.rs:366-406, 572-581): a callback per (hook, layer) returns an op for the job's op list
+    wrk = importlib.import_module("web-rwkv_b200")
+    tensors, model, ref = _build(ctx, "v6-tiny", {0: 1})
+    info = model.info
+    V, C, L = info.num_vocab, info.num_emb, info.num_layer
+    tokens = [5, 9, 2]
+    plain = rt.Bundle(model, 1)
+    want_plain = plain.infer(rt.RnnInput([(tokens, FULL)], 32))[0].copy()
+
+    # (1) capture: the embedding after its layer norm
+    bundle = rt.Bundle(model, 1)
+    saved = ctx.tensor(wrk.F16, [C, len(tokens)])
+    seen = []
+
+    def capture(frame):
+        seen.append(frame.num_token())
+        return wrk.blit(frame.buffer("x"), saved)
+
+    bundle.set_hook(rt.HOOK["POST_EMBED_LAYER_NORM"], 0, capture)
+    got = bundle.infer(rt.RnnInput([(tokens, FULL)], 32))[0].copy()
+    assert seen == [(3, 3)]
+    assert np.array_equal(got, want_plain)  # a copy changes nothing ...
+    emb = np.ascontiguousarray(tensors["emb.weight"][tokens])
+    oracle.layer_norm(tensors["blocks.0.ln0.weight"].reshape(-1), tensors["blocks.0.ln0.bias"].reshape(-1), emb, 1e-5)
+    assert_close(saved.numpy().reshape(len(tokens), C), emb, "captured embedding")
+
+    # (2) an op that changes the result: the residual stream zeroed after the last layer -> logits = head . ln_out.bias
+    bundle.set_hook(rt.HOOK["POST_EMBED_LAYER_NORM"], 0, None)
+    bundle.set_hook(rt.HOOK["POST_FFN"], L - 1, lambda frame: wrk.affine(frame.buffer("x"), 0.0, 0.0))
+    got = bundle.infer(rt.RnnInput([(tokens, LAST)], 32))[0].copy()
+    bias = np.ascontiguousarray(tensors["ln_out.bias"].reshape(1, C))
+    want = np.zeros((1, V), dtype=np.float32)
+    oracle.matmul(oracle.MAT_FP16, np.ascontiguousarray(tensors["head.weight"]), None, bias, want)
+    assert_close(got, want, "zeroed residual")
+
+    # (3) hooks switch the fused kernels off (they have no such points); clearing brings them back
+    hooked = bundle.dispatch([(1, LAST)]).num_kernels()
+    bundle.set_hook(rt.HOOK["POST_FFN"], L - 1, None)
+    fused = bundle.dispatch([(1, LAST)]).num_kernels()
+    strict = rt.Bundle(model, 1)
+    strict.set_fused(0)
+    assert fused < hooked and hooked == strict.dispatch([(1, LAST)]).num_kernels() + 1
+    with pytest.raises(wrk.WrkError):
+        bundle.set_hook(rt.HOOK["PRE_ATT"], L, lambda frame: None)
     assert ctx.device_status() == 0
 
 

@@ -67,7 +67,7 @@ def _logits(model, tokens):
     return out, bundle.infer(inp)[0].copy(), bundle.state_back(0)
 
 
-@pytest.mark.parametrize("config", ["v6-tiny", "v5-tiny", "v7-tiny"])
+@pytest.mark.parametrize("config", ["v6-tiny", "v5-tiny", "v7-tiny", "v4-tiny"])
 def test_save_load_round_trip(ctx, tmp_path, config):
     tensors = synth.make_model(config, seed=1234)
     model = rt.ModelBuilder(ctx).add_tensors(tensors).quant(QUANT).build()
@@ -79,7 +79,7 @@ def test_save_load_round_trip(ctx, tmp_path, config):
         assert getattr(a, field) == getattr(b, field)
     assert list(a.custom) == list(b.custom)
     # every packed byte, scale and table entry
-    names = MATRICES + (["att.w_g", "ffn.w_r"] if a.version != 7 else [])
+    names = MATRICES + (["att.w_g", "ffn.w_r"] if a.version in (5, 6) else ["ffn.w_r"] if a.version == 4 else [])
     for layer in range(a.num_layer):
         for name in names:
             ka, wa, ma, qa = model.matrix_parts(layer, name)

@@ -20,6 +20,7 @@ SOURCES = [
     "kernels/quant.cu",
     "kernels/matmul.cu",
     "kernels/gemm_umma.cu",
+    "kernels/gemm_small.cu",
     "kernels/wkv.cu",
     "kernels/support.cu",
     "kernels/decode.cu",

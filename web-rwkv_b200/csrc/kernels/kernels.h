@@ -46,6 +46,9 @@ struct MatmulArgs {
     int32_t* status;       // device status word (bounded waits report here); may be null
 };
 cudaError_t matmul(const MatmulArgs& a, int num_sms, cudaStream_t stream);
+// fp16 matrices with K <= 256 (the low-rank adapters' second matrices) at any token count (gemm_small.cu).
+bool matmul_small_supported(const MatmulArgs& a);
+cudaError_t matmul_small(const MatmulArgs& a, int num_sms, cudaStream_t stream);
 // Tensor-memory (tcgen05) GEMM for N >= 16 tokens (gemm_umma.cu).
 bool matmul_umma_supported(const MatmulArgs& a);
 cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t stream);

@@ -366,6 +366,8 @@ cudaError_t dispatch_nt(MmParams& p, uint32_t B, cudaStream_t stream) {
 
 cudaError_t matmul(const MatmulArgs& a, int num_sms, cudaStream_t stream) {
     if (a.M == 0 || a.N == 0 || a.B == 0) return cudaSuccess;
+    // more tokens than the weight-streaming kernel takes (8) and a short K: the adapters' second matrices
+    if (a.N > 8 && matmul_small_supported(a)) return matmul_small(a, num_sms, stream);
     if (matmul_umma_supported(a)) return matmul_umma(a, a.status, stream);
     const uint32_t ck = a.kind == MAT_INT8 ? 128 : a.kind == MAT_NF4 ? 64 : 32;
     const bool aligned = (reinterpret_cast<uintptr_t>(a.matrix) % 16 == 0) && a.K % ck == 0 &&

@@ -32,11 +32,41 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 // layer_norm.wgsl: per row of C, (x - mean) * rsqrt(var + eps) * w + b; var = E[(x - mean)^2].
+// Rows of up to kLnRegs * blockDim values are read once and kept in registers (one round of loads in flight instead
+// of three dependent passes over global memory); longer rows take the three passes.
+constexpr int kLnRegs = 32;
 __global__ void layer_norm_kernel(const __half* w, const __half* b, int dtype, void* x, uint32_t C, uint32_t rows,
                                   uint32_t wrows, float eps) {
     __shared__ float scratch[32];
+    const bool cached = C <= (uint32_t)kLnRegs * blockDim.x;
     for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const size_t base = (size_t)row * C;
+        const size_t wb = (size_t)(row % wrows) * C;
+        if (cached) {
+            float v[kLnRegs];
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < kLnRegs; ++i) {
+                const uint32_t c = threadIdx.x + (uint32_t)i * blockDim.x;
+                v[i] = c < C ? dload(x, dtype, base + c) : 0.f;
+                s += v[i];
+            }
+            const float mean = block_sum(s, scratch) / (float)C;
+            float m2 = 0.f;
+#pragma unroll
+            for (int i = 0; i < kLnRegs; ++i) {
+                const uint32_t c = threadIdx.x + (uint32_t)i * blockDim.x;
+                const float d = v[i] - mean;
+                if (c < C) m2 += d * d;
+            }
+            const float dev = rsqrtf(block_sum(m2, scratch) / (float)C + eps);
+#pragma unroll
+            for (int i = 0; i < kLnRegs; ++i) {
+                const uint32_t c = threadIdx.x + (uint32_t)i * blockDim.x;
+                if (c < C) dstore(x, dtype, base + c, fmaf((v[i] - mean) * dev, __half2float(w[wb + c]), __half2float(b[wb + c])));
+            }
+            continue;
+        }
         float s = 0.f;
         for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) s += dload(x, dtype, base + c);
         const float mean = block_sum(s, scratch) / (float)C;
@@ -47,7 +77,6 @@ __global__ void layer_norm_kernel(const __half* w, const __half* b, int dtype, v
         }
         const float var = block_sum(m2, scratch) / (float)C + eps;
         const float dev = rsqrtf(var);
-        const size_t wb = (size_t)(row % wrows) * C;
         for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) {
             const float v = (dload(x, dtype, base + c) - mean) * dev;
             dstore(x, dtype, base + c, fmaf(v, __half2float(w[wb + c]), __half2float(b[wb + c])));

@@ -8,6 +8,7 @@
 // with the cursors; back() reads the [vocab, num_header] fp32 logits into the caller's buffer.
 // Hooks (v6.rs:366-406) are not built.
 #include <cstring>
+#include <limits>
 #include <list>
 
 #include "../kernels/decode.cuh"
@@ -46,6 +47,13 @@ struct wrk_bundle {
     wrk_model* model = nullptr;
     uint32_t num_batch = 0;
     std::vector<TensorH> state;  // per layer f32 [C, S + 2, num_batch]
+    struct HookEntry {
+        wrk_hook_fn fn;
+        void* user;
+    };
+    std::map<std::pair<int32_t, uint32_t>, HookEntry> hooks;  // (hook, layer; 0 for the embed / head hooks)
+    const Buffers* building_header = nullptr;  // of the job being built (for the hooks' frame)
+    uint32_t building_tokens = 0, building_headers = 0;
     wrk_comm* comm = nullptr;  // a rank of a split model: sums of partial products cross this communicator
     bool packed_cursors = false, use_graph = true, fused = true;
     bool step_kernel = false;  // fused jobs of at most 8 tokens run as one persistent kernel where the job shape allows it
@@ -134,6 +142,9 @@ int32_t alloc(wrk_context* ctx, Buffers& b, const char* name, int dtype, uint32_
     return WRK_OK;
 }
 
+// Rows of a layer's state per batch slot: S + 2 (v5 / v6 / v7: v6.rs:163-168), 5 for v4 (v4.rs:158-161).
+uint32_t state_rows(const wrk_model_info& info) { return info.version == 4 ? 5u : info.num_emb / info.num_head + 2; }
+
 // Runtime<f16>::new of each version (v5.rs:258-315, v6.rs:268-345, v7.rs:279-363)
 int32_t make_runtime(wrk_bundle* bd, uint32_t T, std::shared_ptr<Buffers>* out) {
     const wrk_model_info& info = bd->model->info;
@@ -162,6 +173,13 @@ int32_t make_runtime(wrk_bundle* bd, uint32_t T, std::shared_ptr<Buffers>* out) 
         WRK_TRY(alloc(ctx, *b, "aux_a", H16, info.custom[1], T));
         WRK_TRY(alloc(ctx, *b, "aux_g", H16, info.custom[2], T));
         WRK_TRY(alloc(ctx, *b, "aux_v", H16, info.custom[3], T));
+        WRK_TRY(alloc(ctx, *b, "ffn_k", H16, F, T));
+    } else if (info.version == 4) {
+        // Runtime<f16>::new, v4.rs:258-282
+        WRK_TRY(alloc(ctx, *b, "aux_x", F32, C, T));
+        for (auto n : {"att_x", "att_kx", "att_vx", "att_rx", "att_o", "ffn_x", "ffn_kx", "ffn_rx", "ffn_v", "ffn_r"})
+            WRK_TRY(alloc(ctx, *b, n, H16, C, T));
+        for (auto n : {"att_k", "att_v", "att_r"}) WRK_TRY(alloc(ctx, *b, n, F32, C, T));
         WRK_TRY(alloc(ctx, *b, "ffn_k", H16, F, T));
     } else {
         WRK_TRY(alloc(ctx, *b, "aux_x", F32, Cl, T));
@@ -234,9 +252,93 @@ int32_t add(OpList& ops, wrk_view in, wrk_view out, int32_t act_out = WRK_ACT_NO
     return WRK_OK;
 }
 
+}  // namespace
+
+struct wrk_frame {
+    wrk_bundle* bundle;
+    const Buffers* buffer;
+    const Buffers* header;
+    uint32_t num_token, num_header;
+};
+
+namespace {
+
+// hook_op, v6.rs:572-581: the op a registered callback returns for this point of the job, if any
+int32_t hook(wrk_bundle* bd, OpList& ops, const Buffers& B, int32_t kind, uint32_t layer) {
+    if (bd->hooks.empty()) return WRK_OK;
+    const bool global = kind <= WRK_HOOK_POST_EMBED_LAYER_NORM || kind >= WRK_HOOK_PRE_HEAD;
+    auto it = bd->hooks.find({kind, global ? 0u : layer});
+    if (it == bd->hooks.end()) return WRK_OK;
+    wrk_frame frame{bd, &B, bd->building_header, bd->building_tokens, bd->building_headers};
+    wrk_op* op = nullptr;
+    const int32_t s = it->second.fn(it->second.user, &frame, &op);
+    if (s != WRK_OK) {
+        if (op) wrk_op_release(op);
+        return s;
+    }
+    if (op) ops.ops.push_back(op);
+    return WRK_OK;
+}
+#define HOOK(kind) WRK_TRY(hook(bd, ops, B, WRK_HOOK_##kind, index))
+
 // State::att / State::ffn, v6.rs:187-197
 wrk_view state_att(wrk_bundle* bd, uint32_t layer, uint32_t S) { return Vy(bd->state[layer], 0, S + 1); }
 wrk_view state_ffn(wrk_bundle* bd, uint32_t layer, uint32_t S) { return Vy(bd->state[layer], S + 1, S + 2); }
+
+// dispatch_layer of v4 (v4.rs:630-795); the layer's state is [C, 5, B]: rows 0-3 for the time mix (shift row, the two
+// running sums and the running maximum), row 4 the ffn shift row (v4.rs:182-192)
+int32_t layer_v4(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, uint32_t T) {
+    const Layer& L = bd->model->layers[index];
+    const bool turbo = T % WRK_MIN_TOKEN_CHUNK_SIZE == 0;
+    wrk_tensor* cursors = B["cursors"];
+    const wrk_view sa = Vy(bd->state[index], 0, 4), sf = Vy(bd->state[index], 4, 5);
+    WRK_TRY(blit(ops, V(B["x"]), V(B["att_x"])));
+    HOOK(PRE_ATT);
+    ADD(wrk_op_layer_norm(L.att_ln.w, L.att_ln.b, B["att_x"], LN_EPS, &_o));
+    HOOK(POST_ATT_LAYER_NORM);
+    HOOK(PRE_ATT_TOKEN_SHIFT);
+    WRK_TRY(token_shift(ops, cursors, V(L.time_mix_k), sa, B["att_x"], B["att_kx"], false));
+    WRK_TRY(token_shift(ops, cursors, V(L.time_mix_v), sa, B["att_x"], B["att_vx"], false));
+    WRK_TRY(token_shift(ops, cursors, V(L.time_mix_r), sa, B["att_x"], B["att_rx"], false));
+    HOOK(POST_ATT_TOKEN_SHIFT);
+    HOOK(PRE_ATT_LINEAR);
+    WRK_TRY(matmul(ops, L.att_w_k, V(B["att_kx"]), V(B["att_k"]), WRK_ACT_NONE, turbo));
+    WRK_TRY(matmul(ops, L.att_w_v, V(B["att_vx"]), V(B["att_v"]), WRK_ACT_NONE, turbo));
+    WRK_TRY(matmul(ops, L.att_w_r, V(B["att_rx"]), V(B["att_r"]), WRK_ACT_NONE, turbo));
+    HOOK(POST_ATT_LINEAR);
+    HOOK(PRE_ATT_TIME_MIX);
+    WRK_TRY(blit(ops, V(B["att_x"]), V(B["aux_x"])));
+    ADD(wrk_op_time_mix_v4(cursors, L.time_decay, L.time_first, &sa, B["att_k"], B["att_v"], B["att_r"], B["aux_x"], &_o));
+    WRK_TRY(blit(ops, V(B["aux_x"]), V(B["att_x"])));
+    HOOK(POST_ATT_TIME_MIX);
+    HOOK(PRE_ATT_OUT);
+    WRK_TRY(matmul(ops, L.att_w_o, V(B["att_x"]), V(B["att_o"]), WRK_ACT_NONE, turbo));
+    HOOK(POST_ATT_OUT);
+    WRK_TRY(add(ops, V(B["att_o"]), V(B["x"])));
+    HOOK(POST_ATT);
+
+    WRK_TRY(blit(ops, V(B["x"]), V(B["ffn_x"])));
+    HOOK(PRE_FFN);
+    ADD(wrk_op_layer_norm(L.ffn_ln.w, L.ffn_ln.b, B["ffn_x"], LN_EPS, &_o));
+    HOOK(POST_FFN_LAYER_NORM);
+    HOOK(PRE_FFN_TOKEN_SHIFT);
+    WRK_TRY(token_shift(ops, cursors, V(L.ffn_time_mix_k), sf, B["ffn_x"], B["ffn_kx"], false));
+    WRK_TRY(token_shift(ops, cursors, V(L.ffn_time_mix_r), sf, B["ffn_x"], B["ffn_rx"], false));
+    HOOK(POST_FFN_TOKEN_SHIFT);
+    HOOK(PRE_FFN_LINEAR);
+    WRK_TRY(matmul(ops, L.ffn_w_k, V(B["ffn_kx"]), V(B["ffn_k"]), WRK_ACT_SQUARED_RELU, turbo));
+    HOOK(POST_FFN_ACTIVATE);
+    WRK_TRY(matmul(ops, L.ffn_w_v, V(B["ffn_k"]), V(B["ffn_v"]), WRK_ACT_NONE, turbo, true));
+    WRK_TRY(matmul(ops, L.ffn_w_r, V(B["ffn_rx"]), V(B["ffn_r"]), WRK_ACT_NONE, turbo));
+    HOOK(POST_FFN_LINEAR);
+    HOOK(PRE_FFN_CHANNEL_MIX);
+    ADD(wrk_op_channel_mix(cursors, &sf, B["ffn_r"], B["ffn_v"], B["ffn_x"], &_o));
+    HOOK(POST_FFN_CHANNEL_MIX);
+    WRK_TRY(add(ops, V(B["ffn_x"]), V(B["x"])));
+    HOOK(POST_FFN);
+    if ((index + 1) % bd->model->rescale == 0) ADD(wrk_op_affine(B["x"], 0.5f, 0.0f, &_o));
+    return WRK_OK;
+}
 
 // ---- a rank of a split model (no counterpart in the reference, which runs on one GPU) ----
 // The layer functions below serve both: with the whole model on this GPU the local channel range is all of C and
@@ -295,40 +397,60 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
     WRK_TRY(reshape(B["att_r"], S, WRK_DIM_AUTO, T, 1, &att_r));
 
     WRK_TRY(blit(ops, V(B["x"]), V(B["att_x"])));
+    HOOK(PRE_ATT);
     ADD(wrk_op_layer_norm(L.att_ln.w, L.att_ln.b, B["att_x"], LN_EPS, &_o));
+    HOOK(POST_ATT_LAYER_NORM);
+    HOOK(PRE_ATT_TOKEN_SHIFT);
     if (v6) {
         TensorH time_mix_x;
         WRK_TRY(reshape(B["time_mix_x"], WRK_DIM_AUTO, T, 1, 1, &time_mix_x));
         WRK_TRY(token_shift(ops, cursors, V(L.time_mix_x), state_att(bd, index, S), B["att_x"], B["att_xx"], true));
+        HOOK(POST_ATT_TOKEN_SHIFT);
+        HOOK(PRE_ATT_TOKEN_SHIFT_ADAPT);
         WRK_TRY(matmul(ops, L.time_mix_w1, V(B["att_xx"]), V(time_mix_x), WRK_ACT_TANH, turbo));
         {
             const wrk_view in = V(B["time_mix_x"]), out = V(B["time_mix_t"]);
             ADD(wrk_op_transpose(&in, &out, &_o));
         }
+        HOOK(POST_ATT_TOKEN_SHIFT_ADAPT_ACTIVATE);
         WRK_TRY(matmul(ops, L.time_mix_w2, V(B["time_mix_t"]), V(B["time_mix"]), WRK_ACT_NONE, turbo));
+        HOOK(POST_ATT_TOKEN_SHIFT_ADAPT);
         WRK_TRY(add(ops, V(L.time_mix), V(B["time_mix"])));
+        HOOK(PRE_ATT_GATED_TOKEN_SHIFT);
         WRK_TRY(token_shift(ops, cursors, V(B["time_mix"]), state_att(bd, index, S), B["att_x"], B["att_sx"], true));
+        HOOK(POST_ATT_GATED_TOKEN_SHIFT);
+        HOOK(PRE_ATT_LINEAR);
         WRK_TRY(matmul(ops, L.att_w_k, Vz(B["att_sx"], 1), V(B["att_k"]), WRK_ACT_NONE, turbo));
         WRK_TRY(matmul(ops, L.att_w_v, Vz(B["att_sx"], 2), V(B["att_v"]), WRK_ACT_NONE, turbo));
         WRK_TRY(matmul(ops, L.att_w_r, Vz(B["att_sx"], 3), V(B["att_r"]), WRK_ACT_NONE, turbo));
         WRK_TRY(matmul(ops, L.att_w_g, Vz(B["att_sx"], 4), V(B["att_g"]), WRK_ACT_NONE, turbo));
+        HOOK(POST_ATT_LINEAR);
+        HOOK(PRE_ATT_TIME_DECAY_ADAPT);
         WRK_TRY(matmul(ops, L.time_decay_w1, Vz(B["att_sx"], 0), V(B["att_w"]), WRK_ACT_TANH, turbo));
+        HOOK(POST_ATT_TIME_DECAY_ADAPT_ACTIVATE);
         WRK_TRY(matmul(ops, L.time_decay_w2, V(B["att_w"]), V(B["time_decay"]), WRK_ACT_NONE, turbo));
+        HOOK(POST_ATT_TIME_DECAY_ADAPT);
         WRK_TRY(add(ops, V(L.time_decay), V(B["time_decay"])));
+        HOOK(PRE_ATT_TIME_DECAY_ACTIVATE);
         {
             const wrk_view td = V(B["time_decay"]);
             ADD(wrk_op_activate(&td, WRK_ACT_STABLE_EXP, &_o));
         }
+        HOOK(POST_ATT_TIME_DECAY_ACTIVATE);
     } else {
         WRK_TRY(token_shift(ops, cursors, V(L.time_mix_k), state_att(bd, index, S), B["att_x"], B["att_kx"], false));
         WRK_TRY(token_shift(ops, cursors, V(L.time_mix_v), state_att(bd, index, S), B["att_x"], B["att_vx"], false));
         WRK_TRY(token_shift(ops, cursors, V(L.time_mix_r), state_att(bd, index, S), B["att_x"], B["att_rx"], false));
         WRK_TRY(token_shift(ops, cursors, V(L.time_mix_g), state_att(bd, index, S), B["att_x"], B["att_gx"], false));
+        HOOK(POST_ATT_TOKEN_SHIFT);
+        HOOK(PRE_ATT_LINEAR);
         WRK_TRY(matmul(ops, L.att_w_k, V(B["att_kx"]), V(B["att_k"]), WRK_ACT_NONE, turbo));
         WRK_TRY(matmul(ops, L.att_w_v, V(B["att_vx"]), V(B["att_v"]), WRK_ACT_NONE, turbo));
         WRK_TRY(matmul(ops, L.att_w_r, V(B["att_rx"]), V(B["att_r"]), WRK_ACT_NONE, turbo));
         WRK_TRY(matmul(ops, L.att_w_g, V(B["att_gx"]), V(B["att_g"]), WRK_ACT_NONE, turbo));
+        HOOK(POST_ATT_LINEAR);
     }
+    HOOK(PRE_ATT_TIME_MIX);
     WRK_TRY(blit(ops, Vx(B["att_x"], sp.c0, sp.c0 + sp.Cl), V(B["aux_x"])));
     {
         const wrk_view st = state_wkv(bd, index, S, sp);
@@ -337,30 +459,46 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
     }
     ADD(wrk_op_group_norm(L.gn.w, L.gn.b, aux_x, GN_EPS, &_o));
     WRK_TRY(blit(ops, V(B["aux_x"]), V(att_loc)));
+    HOOK(POST_ATT_TIME_MIX);
+    HOOK(PRE_ATT_GATE);
     {
         const wrk_view g = V(B["att_g"]), x = V(att_loc);
         ADD(wrk_op_mul_activate(&g, &x, WRK_ACT_SILU, WRK_ACT_NONE, WRK_ACT_NONE, &_o));
     }
+    HOOK(POST_ATT_GATE);
+    HOOK(PRE_ATT_OUT);
     WRK_TRY(matmul(ops, L.att_w_o, V(att_loc), V(sp.on ? B["partial"] : B["att_o"]), WRK_ACT_NONE, turbo));
     if (sp.on) {
         WRK_TRY(reduce_partial(bd, ops, B, B["att_o"]));
         WRK_TRY(carry_all_channels(bd, ops, B, index, S));
     }
+    HOOK(POST_ATT_OUT);
     WRK_TRY(add(ops, V(B["att_o"]), V(B["x"])));
+    HOOK(POST_ATT);
 
     WRK_TRY(blit(ops, V(B["x"]), V(B["ffn_x"])));
+    HOOK(PRE_FFN);
     ADD(wrk_op_layer_norm(L.ffn_ln.w, L.ffn_ln.b, B["ffn_x"], LN_EPS, &_o));
+    HOOK(POST_FFN_LAYER_NORM);
+    HOOK(PRE_FFN_TOKEN_SHIFT);
     WRK_TRY(token_shift(ops, cursors, V(L.ffn_time_mix_k), state_ffn(bd, index, S), B["ffn_x"], B["ffn_kx"], v6));
     WRK_TRY(token_shift(ops, cursors, V(L.ffn_time_mix_r), state_ffn(bd, index, S), B["ffn_x"], B["ffn_rx"], v6));
+    HOOK(POST_FFN_TOKEN_SHIFT);
+    HOOK(PRE_FFN_LINEAR);
     WRK_TRY(matmul(ops, L.ffn_w_k, V(B["ffn_kx"]), V(B["ffn_k"]), WRK_ACT_SQUARED_RELU, turbo));
+    HOOK(POST_FFN_ACTIVATE);
     WRK_TRY(matmul(ops, L.ffn_w_v, V(B["ffn_k"]), V(sp.on ? B["partial"] : B["ffn_v"]), WRK_ACT_NONE, turbo, true));
     if (sp.on) WRK_TRY(reduce_partial(bd, ops, B, B["ffn_v"]));
     WRK_TRY(matmul(ops, L.ffn_w_r, V(B["ffn_rx"]), V(B["ffn_r"]), WRK_ACT_NONE, turbo));
+    HOOK(POST_FFN_LINEAR);
+    HOOK(PRE_FFN_CHANNEL_MIX);
     {
         const wrk_view st = state_ffn(bd, index, S);
         ADD(wrk_op_channel_mix(cursors, &st, B["ffn_r"], B["ffn_v"], B["ffn_x"], &_o));
     }
+    HOOK(POST_FFN_CHANNEL_MIX);
     WRK_TRY(add(ops, V(B["ffn_x"]), V(B["x"])));
+    HOOK(POST_FFN);
     if ((index + 1) % bd->model->rescale == 0) ADD(wrk_op_affine(B["x"], 0.5f, 0.0f, &_o));
     return WRK_OK;
 }
@@ -383,7 +521,10 @@ int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, 
     WRK_TRY(reshape(B["att_n"], S, WRK_DIM_AUTO, T, 4, &att_n));
 
     WRK_TRY(blit(ops, V(B["x"]), V(B["att_x"])));
+    HOOK(PRE_ATT);
     ADD(wrk_op_layer_norm(L.att_ln.w, L.att_ln.b, B["att_x"], LN_EPS, &_o));
+    HOOK(POST_ATT_LAYER_NORM);
+    HOOK(PRE_ATT_TOKEN_SHIFT);
     const wrk_view sa = state_att(bd, index, S);
     WRK_TRY(token_shift(ops, cursors, V(L.x_r), sa, B["att_x"], B["att_rx"], true));
     WRK_TRY(token_shift(ops, cursors, V(L.x_w), sa, B["att_x"], B["att_wx"], true));
@@ -391,9 +532,13 @@ int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, 
     WRK_TRY(token_shift(ops, cursors, V(L.x_v), sa, B["att_x"], B["att_vx"], true));
     WRK_TRY(token_shift(ops, cursors, V(L.x_a), sa, B["att_x"], B["att_ax"], true));
     WRK_TRY(token_shift(ops, cursors, V(L.x_g), sa, B["att_x"], B["att_gx"], true));
+    HOOK(POST_ATT_TOKEN_SHIFT);
+    HOOK(PRE_ATT_LINEAR);
     WRK_TRY(matmul(ops, L.att_w_r, V(B["att_rx"]), V(B["att_r"]), WRK_ACT_NONE, turbo));
     WRK_TRY(matmul(ops, L.att_w_k, V(B["att_kx"]), V(B["att_k"]), WRK_ACT_NONE, turbo));
     WRK_TRY(matmul(ops, L.att_w_v, V(B["att_vx"]), V(B["att_v"]), WRK_ACT_NONE, turbo));
+    HOOK(POST_ATT_LINEAR);
+    HOOK(PRE_ATT_ADAPT);
     WRK_TRY(matmul(ops, L.w1, V(B["att_wx"]), V(B["aux_w"]), WRK_ACT_TANH, turbo));
     WRK_TRY(matmul(ops, L.w2, V(B["aux_w"]), V(B["att_w"]), WRK_ACT_NONE, turbo));
     WRK_TRY(add(ops, V(L.w0), V(B["att_w"])));
@@ -402,6 +547,8 @@ int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, 
     WRK_TRY(add(ops, V(L.a0), V(B["att_a"]), WRK_ACT_SIGMOID));
     WRK_TRY(matmul(ops, L.g1, V(B["att_gx"]), V(B["aux_g"]), WRK_ACT_SIGMOID, turbo));
     WRK_TRY(matmul(ops, L.g2, V(B["aux_g"]), V(B["att_g"]), WRK_ACT_NONE, turbo));
+    HOOK(POST_ATT_ADAPT);
+    HOOK(PRE_ATT_CONTROL);
     WRK_TRY(blit(ops, V(B["att_k"]), V(B["att_kk"])));
     {
         const wrk_view kk = V(L.k_k), o = V(B["att_kk"]);
@@ -412,6 +559,8 @@ int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, 
         const wrk_view a = V(B["att_a"]), k = V(B["att_k"]);
         ADD(wrk_op_control_k_v7(L.k_a, &a, &k, &_o));
     }
+    HOOK(POST_ATT_CONTROL);
+    HOOK(PRE_ATT_VALUE_RESIDUAL);
     if (index == 0) {
         WRK_TRY(blit(ops, V(B["att_v"]), V(B["att_v0"])));
     } else {
@@ -421,6 +570,8 @@ int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, 
         const wrk_view in = V(B["att_v0"]), out = V(B["att_v"]), f = V(B["att_vv"]);
         ADD(wrk_op_lerp(&in, &out, &f, 1, &_o));
     }
+    HOOK(POST_ATT_VALUE_RESIDUAL);
+    HOOK(PRE_ATT_TIME_MIX);
     WRK_TRY(blit(ops, V(B["att_k"]), Vz(B["att_n"], 0)));
     WRK_TRY(blit(ops, V(B["att_v"]), Vz(B["att_n"], 1)));
     WRK_TRY(blit(ops, V(B["att_a"]), Vz(B["att_n"], 2)));
@@ -432,28 +583,44 @@ int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, 
     }
     ADD(wrk_op_group_norm(L.gn.w, L.gn.b, att_x, GN_EPS, &_o));
     ADD(wrk_op_time_first_v7(L.r_k, att_r, att_n, att_x, &_o));
+    HOOK(POST_ATT_TIME_MIX);
+    HOOK(PRE_ATT_GATE);
     {
         const wrk_view g = V(B["att_g"]), x = V(att_loc);
         ADD(wrk_op_mul_activate(&g, &x, WRK_ACT_NONE, WRK_ACT_NONE, WRK_ACT_NONE, &_o));
     }
+    HOOK(POST_ATT_GATE);
+    HOOK(PRE_ATT_OUT);
     WRK_TRY(matmul(ops, L.att_w_o, V(att_loc), V(sp.on ? B["partial"] : B["att_o"]), WRK_ACT_NONE, turbo));
     if (sp.on) {
         WRK_TRY(reduce_partial(bd, ops, B, B["att_o"]));
         WRK_TRY(carry_all_channels(bd, ops, B, index, S));
     }
+    HOOK(POST_ATT_OUT);
     WRK_TRY(add(ops, V(B["att_o"]), V(B["x"])));
+    HOOK(POST_ATT);
 
     WRK_TRY(blit(ops, V(B["x"]), V(B["ffn_x"])));
+    HOOK(PRE_FFN);
     ADD(wrk_op_layer_norm(L.ffn_ln.w, L.ffn_ln.b, B["ffn_x"], LN_EPS, &_o));
+    HOOK(POST_FFN_LAYER_NORM);
+    HOOK(PRE_FFN_TOKEN_SHIFT);
     WRK_TRY(token_shift(ops, cursors, V(L.ffn_x_k), state_ffn(bd, index, S), B["ffn_x"], B["ffn_kx"], true));
+    HOOK(POST_FFN_TOKEN_SHIFT);
+    HOOK(PRE_FFN_LINEAR);
     WRK_TRY(matmul(ops, L.ffn_w_k, V(B["ffn_kx"]), V(B["ffn_k"]), WRK_ACT_SQUARED_RELU, turbo));
+    HOOK(POST_FFN_ACTIVATE);
     WRK_TRY(matmul(ops, L.ffn_w_v, V(B["ffn_k"]), V(sp.on ? B["partial"] : B["ffn_v"]), WRK_ACT_NONE, turbo, true));
     if (sp.on) WRK_TRY(reduce_partial(bd, ops, B, B["ffn_v"]));
+    HOOK(POST_FFN_LINEAR);
+    HOOK(PRE_FFN_CHANNEL_MIX);
     {
         const wrk_view st = state_ffn(bd, index, S);
         ADD(wrk_op_channel_mix_v7(cursors, &st, B["ffn_v"], B["ffn_x"], &_o));
     }
+    HOOK(POST_FFN_CHANNEL_MIX);
     WRK_TRY(add(ops, V(B["ffn_x"]), V(B["x"])));
+    HOOK(POST_FFN);
     if ((index + 1) % bd->model->rescale == 0) ADD(wrk_op_affine(B["x"], 0.5f, 0.0f, &_o));
     return WRK_OK;
 }
@@ -537,6 +704,7 @@ __half* Hm(wrk_tensor* t) { return static_cast<__half*>(t->ptr()); }
 bool fused_v6_supported(wrk_bundle* bd, uint32_t T) {
     const wrk_model_info& info = bd->model->info;
     if (!bd->fused || info.version != 6 || T == 0 || T > (uint32_t)k::kDecodeMaxTokens) return false;
+    if (!bd->hooks.empty()) return false;     // hooks sit between reference ops
     if (bd->model->shard.on()) return false;  // the fused phases end in residual adds; a split model sums across ranks first
     if (info.num_emb / info.num_head != 64 || info.num_emb % 128 || info.custom[0] % 8 || info.custom[0] > 64 ||
         info.custom[1] % 32 || info.custom[1] > 128)
@@ -975,6 +1143,10 @@ int32_t build_job(wrk_bundle* bd, const RnnInfo& info, CachedJob* job) {
     const Buffers& Hd = *job->header;
     OpList ops;
     const bool fused = fused_v6_supported(bd, T);
+    bd->building_header = &Hd;
+    bd->building_tokens = T;
+    bd->building_headers = NH;
+    const uint32_t index = 0;  // the embed / head hooks take no layer
     // the whole job as one persistent kernel (launched eagerly: a memset of the barrier word and one cooperative
     // launch per job need no graph)
     if (fused && bd->step_kernel && NH <= (uint32_t)k::kDecodeMaxTokens) {
@@ -992,12 +1164,15 @@ int32_t build_job(wrk_bundle* bd, const RnnInfo& info, CachedJob* job) {
     }
 
     // embed: layer norm on the uploaded rows, then copy into x
+    HOOK(POST_EMBED_LOADED);
     ADD(wrk_op_layer_norm(m->embed_ln.w, m->embed_ln.b, B["input"], LN_EPS, &_o));
     WRK_TRY(blit(ops, V(B["input"]), V(B["x"])));
+    HOOK(POST_EMBED_LAYER_NORM);
     FusedSink sink{m->ctx, &ops, job, nullptr};
     for (uint32_t i = 0; i < m->info.num_layer; ++i) {
         if (fused) WRK_TRY(layer_v6_fused(bd, sink, B, i, T));
         else if (m->info.version == 7) WRK_TRY(layer_v7(bd, ops, B, i, T));
+        else if (m->info.version == 4) WRK_TRY(layer_v4(bd, ops, B, i, T));
         else WRK_TRY(layer_v56(bd, ops, B, i, T));
         if ((i + 1) % m->sep == 0) ADD(wrk_op_sep(&_o));
     }
@@ -1035,14 +1210,20 @@ int32_t build_job(wrk_bundle* bd, const RnnInfo& info, CachedJob* job) {
         WRK_TRY(add_fused_gemv(m->ctx, ops, job, a, "fused_head", {head_x, Hd["head_o"]}));
     } else if (NH > 0 && m->shard.on()) {
         // every rank multiplies its slice of the vocabulary; the slices are gathered and put in order
+        HOOK(PRE_HEAD);
         ADD(wrk_op_layer_norm(m->head_ln.w, m->head_ln.b, head_x, LN_EPS, &_o));
+        HOOK(POST_HEAD_LAYER_NORM);
         WRK_TRY(matmul(ops, m->head_w, V(head_x), V(Hd["head_l"]), WRK_ACT_NONE, NH % WRK_MIN_TOKEN_CHUNK_SIZE == 0));
         ADD(wrk_op_all_gather(bd->comm, Hd["head_l"], Hd["head_all"], &_o));
         const uint32_t Vl = m->shard.v1 - m->shard.v0;
         for (uint32_t r = 0; r < m->shard.world; ++r) WRK_TRY(blit(ops, Vz(Hd["head_all"], r), Vx(Hd["head_o"], r * Vl, (r + 1) * Vl)));
+        HOOK(POST_HEAD);
     } else if (NH > 0) {
+        HOOK(PRE_HEAD);
         ADD(wrk_op_layer_norm(m->head_ln.w, m->head_ln.b, head_x, LN_EPS, &_o));
+        HOOK(POST_HEAD_LAYER_NORM);
         WRK_TRY(matmul(ops, m->head_w, V(head_x), V(Hd["head_o"]), WRK_ACT_NONE, NH % WRK_MIN_TOKEN_CHUNK_SIZE == 0));
+        HOOK(POST_HEAD);
     }
     wrk_op* list = nullptr;
     WRK_TRY(wrk_op_list(ops.ops.data(), ops.ops.size(), &list));
@@ -1101,12 +1282,20 @@ static int32_t bundle_create(wrk_model* model, uint32_t num_batch, wrk_comm* com
     b->model = model;
     b->num_batch = num_batch;
     const wrk_model_info& info = model->info;
-    const uint32_t S = info.num_emb / info.num_head;
-    const uint32_t shape[4] = {info.num_emb, S + 2, num_batch, 1};
+    const uint32_t shape[4] = {info.num_emb, state_rows(info), num_batch, 1};
+    // v4: State::init puts f32::MIN in the running-maximum row (v4.rs:163-180)
+    std::vector<float> init;
+    if (info.version == 4) {
+        init.assign((size_t)shape[0] * shape[1] * num_batch, 0.0f);
+        for (uint32_t batch = 0; batch < num_batch; ++batch)
+            std::fill_n(init.begin() + ((size_t)batch * 5 + 3) * info.num_emb, info.num_emb, std::numeric_limits<float>::lowest());
+    }
     for (uint32_t l = 0; l < info.num_layer; ++l) {
         wrk_tensor* t = nullptr;
         int32_t s = wrk_tensor_zeros(model->ctx, WRK_F32, shape, &t);
+        if (s == WRK_OK && !init.empty()) s = wrk_tensor_load(t, init.data(), init.size() * sizeof(float));
         if (s != WRK_OK) {
+            if (t) wrk_tensor_release(t);
             delete b;
             return s;
         }
@@ -1156,6 +1345,44 @@ int32_t wrk_bundle_set_fused(wrk_bundle* b, int32_t fused) {
     return WRK_OK;
 }
 
+int32_t wrk_bundle_set_hook(wrk_bundle* b, int32_t hook, uint32_t layer, wrk_hook_fn fn, void* user) {
+    WRK_REQUIRE(b, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(hook >= 0 && hook < WRK_HOOK_COUNT, WRK_ERR_INVALID_ARGUMENT, "unknown hook %d", hook);
+    const bool global = hook <= WRK_HOOK_POST_EMBED_LAYER_NORM || hook >= WRK_HOOK_PRE_HEAD;
+    WRK_REQUIRE(global || layer < b->model->info.num_layer, WRK_ERR_INVALID_ARGUMENT, "layer %u out of range", layer);
+    drop_caches(b);
+    const std::pair<int32_t, uint32_t> key{hook, global ? 0u : layer};
+    if (fn) b->hooks[key] = {fn, user};
+    else b->hooks.erase(key);
+    return WRK_OK;
+}
+
+int32_t wrk_frame_bundle(const wrk_frame* frame, wrk_bundle** bundle) {
+    WRK_REQUIRE(frame && bundle, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    *bundle = frame->bundle;
+    return WRK_OK;
+}
+
+int32_t wrk_frame_num_token(const wrk_frame* frame, uint32_t* num_token, uint32_t* num_header) {
+    WRK_REQUIRE(frame && num_token && num_header, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    *num_token = frame->num_token;
+    *num_header = frame->num_header;
+    return WRK_OK;
+}
+
+int32_t wrk_frame_buffer(const wrk_frame* frame, const char* name, wrk_tensor** out) {
+    WRK_REQUIRE(frame && name && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    for (const Buffers* b : {frame->buffer, frame->header}) {
+        if (!b) continue;
+        auto it = b->t.find(name);
+        if (it != b->t.end()) {
+            *out = it->second;
+            return WRK_OK;
+        }
+    }
+    return set_error(WRK_ERR_INVALID_ARGUMENT, "the job has no buffer named %s", name);
+}
+
 int32_t wrk_bundle_set_phase_timeline(wrk_bundle* b, uint32_t max_phases) {
     WRK_REQUIRE(b, WRK_ERR_INVALID_ARGUMENT, "null argument");
     drop_caches(b);
@@ -1196,7 +1423,7 @@ int32_t wrk_state_init_shape(wrk_bundle* b, uint32_t shape[4]) {
     WRK_REQUIRE(b && shape, WRK_ERR_INVALID_ARGUMENT, "null argument");
     const wrk_model_info& info = b->model->info;
     shape[0] = info.num_emb;
-    shape[1] = info.num_emb / info.num_head + 2;
+    shape[1] = state_rows(info);
     shape[2] = info.num_layer;
     shape[3] = 1;
     return WRK_OK;
@@ -1206,7 +1433,7 @@ int32_t wrk_state_init_shape(wrk_bundle* b, uint32_t shape[4]) {
 int32_t wrk_state_load(wrk_bundle* b, const float* host, size_t bytes, uint32_t batch) {
     WRK_REQUIRE(b && host, WRK_ERR_INVALID_ARGUMENT, "null argument");
     const wrk_model_info& info = b->model->info;
-    const size_t per_layer = (size_t)info.num_emb * (info.num_emb / info.num_head + 2);
+    const size_t per_layer = (size_t)info.num_emb * state_rows(info);
     WRK_REQUIRE(bytes == per_layer * info.num_layer * 4, WRK_ERR_SIZE, "data size not match: %zu vs. %zu", bytes,
                 per_layer * info.num_layer * 4);
     if (batch >= b->num_batch)
@@ -1223,7 +1450,7 @@ int32_t wrk_state_load(wrk_bundle* b, const float* host, size_t bytes, uint32_t 
 int32_t wrk_state_back(wrk_bundle* b, uint32_t batch, float* host, size_t bytes) {
     WRK_REQUIRE(b && host, WRK_ERR_INVALID_ARGUMENT, "null argument");
     const wrk_model_info& info = b->model->info;
-    const size_t per_layer = (size_t)info.num_emb * (info.num_emb / info.num_head + 2);
+    const size_t per_layer = (size_t)info.num_emb * state_rows(info);
     WRK_REQUIRE(bytes == per_layer * info.num_layer * 4, WRK_ERR_SIZE, "data size not match: %zu vs. %zu", bytes,
                 per_layer * info.num_layer * 4);
     if (batch >= b->num_batch)
@@ -1240,13 +1467,13 @@ int32_t wrk_state_back(wrk_bundle* b, uint32_t batch, float* host, size_t bytes)
 int32_t wrk_state_write(wrk_bundle* b, wrk_tensor* tensor, uint32_t batch) {
     WRK_REQUIRE(b && tensor, WRK_ERR_INVALID_ARGUMENT, "null argument");
     const wrk_model_info& info = b->model->info;
-    const uint32_t S = info.num_emb / info.num_head;
+    const uint32_t rows = state_rows(info);
     WRK_REQUIRE(tensor->dtype == WRK_F32, WRK_ERR_TYPE, "data type mismatch: the state is f32");
-    WRK_TRY(check_shape("state", tensor->shape, info.num_emb, S + 2, info.num_layer, 1));
+    WRK_TRY(check_shape("state", tensor->shape, info.num_emb, rows, info.num_layer, 1));
     WRK_REQUIRE(tensor->ctx == b->model->ctx, WRK_ERR_INVALID_ARGUMENT, "tensor and bundle belong to different contexts");
     if (batch >= b->num_batch)
         return set_error(WRK_ERR_BATCH_OUT_OF_RANGE, "batch %u out of range of max %u", batch, b->num_batch);
-    const size_t per_layer = (size_t)info.num_emb * (S + 2);
+    const size_t per_layer = (size_t)info.num_emb * rows;
     wrk_context* ctx = b->model->ctx;
     for (uint32_t l = 0; l < info.num_layer; ++l)
         WRK_CUDA(cudaMemcpyAsync(static_cast<float*>(b->state[l].p->ptr()) + batch * per_layer,
@@ -1259,13 +1486,13 @@ int32_t wrk_state_write(wrk_bundle* b, wrk_tensor* tensor, uint32_t batch) {
 int32_t wrk_state_read(wrk_bundle* b, uint32_t batch, wrk_tensor** out) {
     WRK_REQUIRE(b && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
     const wrk_model_info& info = b->model->info;
-    const uint32_t S = info.num_emb / info.num_head;
+    const uint32_t rows = state_rows(info);
     if (batch >= b->num_batch)
         return set_error(WRK_ERR_BATCH_OUT_OF_RANGE, "batch %u out of range of max %u", batch, b->num_batch);
-    const uint32_t shape[4] = {info.num_emb, S + 2, info.num_layer, 1};
+    const uint32_t shape[4] = {info.num_emb, rows, info.num_layer, 1};
     wrk_tensor* t = nullptr;
     WRK_TRY(wrk_tensor_create(b->model->ctx, WRK_F32, shape, &t));
-    const size_t per_layer = (size_t)info.num_emb * (S + 2);
+    const size_t per_layer = (size_t)info.num_emb * rows;
     wrk_context* ctx = b->model->ctx;
     for (uint32_t l = 0; l < info.num_layer; ++l) {
         const cudaError_t e = cudaMemcpyAsync(static_cast<float*>(t->ptr()) + l * per_layer,
@@ -1284,7 +1511,7 @@ int32_t wrk_state_read(wrk_bundle* b, uint32_t batch, wrk_tensor** out) {
 int32_t wrk_state_embed(wrk_bundle* b, uint32_t layer, const float* backed, size_t bytes, float* embed, size_t embed_bytes) {
     WRK_REQUIRE(b && backed && embed, WRK_ERR_INVALID_ARGUMENT, "null argument");
     const wrk_model_info& info = b->model->info;
-    const size_t per_layer = (size_t)info.num_emb * (info.num_emb / info.num_head + 2);
+    const size_t per_layer = (size_t)info.num_emb * state_rows(info);
     WRK_REQUIRE(bytes == per_layer * info.num_layer * 4, WRK_ERR_SIZE, "data size not match: %zu vs. %zu", bytes,
                 per_layer * info.num_layer * 4);
     WRK_REQUIRE(embed_bytes == (size_t)info.num_emb * 4, WRK_ERR_SIZE, "data size not match: %zu vs. %zu", embed_bytes,

@@ -195,6 +195,16 @@ struct Loader {
         return s;
     }
 
+    // load_vector_exp_f32, src/runtime/loader.rs:431-470: f32 vector, then OppositeExp (-exp(x)) on the device
+    int32_t vector_exp_f32(const std::string& name, TensorH* out) const {
+        WRK_TRY(vector_f32(name, out));
+        wrk_view v;
+        WRK_TRY(wrk_tensor_as_view(*out, &v));
+        wrk_op* op = nullptr;
+        WRK_TRY(wrk_op_activate(&v, WRK_ACT_OPPOSITE_EXP, &op));
+        return run_and_release(op);
+    }
+
     // load_matrix_f16, src/runtime/loader.rs:567-592 (optionally padded to multiples of 8: :688-707)
     int32_t matrix_f16(const std::string& name, bool padded, float discount, TensorH* out) const {
         const wrk_model_builder::Entry* e;
@@ -382,8 +392,7 @@ int32_t sniff_info(const wrk_model_builder* b, wrk_model_info* info) {
     if (v7) version = 7;
     else if (v6) version = 6;
     else if (v5) version = 5;
-    else if (v4)
-        return set_error(WRK_ERR_UNSUPPORTED, "RWKV v4 models are outside this library's path (v5, v6, v7 only)");
+    else if (v4) version = 4;
     else
         return set_error(WRK_ERR_INVALID_VERSION, "invalid model version");
 
@@ -409,6 +418,8 @@ int32_t sniff_info(const wrk_model_builder* b, wrk_model_info* info) {
         info->custom[2] = (uint32_t)e->shape[0];
         WRK_TRY(ld.entry("blocks.1.att.v1", &e));
         info->custom[3] = (uint32_t)e->shape[0];
+    } else if (version == 4) {
+        info->num_head = 1;  // src/runtime/loader.rs:290-294
     } else {
         WRK_TRY(ld.entry("blocks.0.att.time_first", &e));
         info->num_head = file_dim(e, 0);
@@ -436,7 +447,7 @@ int32_t build_common(const Loader& ld, wrk_model* m) {
     std::memcpy(m->embed_host, e->data.data(), e->data.size() * 2);
     // head: never quantized; v6 / v7 pad it, v5 does not (v5.rs:956, v6.rs:1029, v7.rs:1073)
     TensorH head;
-    WRK_TRY(ld.matrix_f16("head.weight", info.version != 5, 1.0f, &head));
+    WRK_TRY(ld.matrix_f16("head.weight", info.version >= 6, 1.0f, &head));  // v4: src/runtime/v4.rs:861
     wrk_matrix* hm = nullptr;
     WRK_TRY(wrk_matrix_fp16(head, &hm));
     m->head_w = MatrixH(hm);
@@ -533,6 +544,38 @@ int32_t build_v56(const Loader& ld, wrk_model* m) {
         WRK_TRY(ld.matrix(ffn + ".key.weight", quant, 1.0f, &L.ffn_w_k));
         WRK_TRY(ld.matrix(ffn + ".value.weight", quant, discount, &L.ffn_w_v));
         WRK_CUDA(cudaStreamSynchronize(ctx->stream));  // frees the fp16 staging of this layer (v6.rs:1135-1139)
+    }
+    return WRK_OK;
+}
+
+// ModelBuilder::build_v4, src/runtime/v4.rs:829-960
+int32_t build_v4(const Loader& ld, wrk_model* m) {
+    const wrk_model_info& info = m->info;
+    wrk_context* ctx = m->ctx;
+    m->layers.resize(info.num_layer);
+    for (uint32_t layer = 0; layer < info.num_layer; ++layer) {
+        Layer& L = m->layers[layer];
+        const int32_t quant = quant_of(ld.b, layer);
+        const float discount = std::ldexp(1.0f, -(int)(layer / m->rescale));
+        const std::string blk = "blocks." + std::to_string(layer);
+        const std::string att = blk + ".att", ffn = blk + ".ffn";
+        WRK_TRY(ld.layer_norm(blk + ".ln1", &L.att_ln));
+        WRK_TRY(ld.vector_exp_f32(att + ".time_decay", &L.time_decay));
+        WRK_TRY(ld.vector_f32(att + ".time_first", &L.time_first));
+        WRK_TRY(ld.vector_f16(att + ".time_mix_k", &L.time_mix_k));
+        WRK_TRY(ld.vector_f16(att + ".time_mix_v", &L.time_mix_v));
+        WRK_TRY(ld.vector_f16(att + ".time_mix_r", &L.time_mix_r));
+        WRK_TRY(ld.matrix(att + ".key.weight", quant, 1.0f, &L.att_w_k));
+        WRK_TRY(ld.matrix(att + ".value.weight", quant, 1.0f, &L.att_w_v));
+        WRK_TRY(ld.matrix(att + ".receptance.weight", quant, 1.0f, &L.att_w_r));
+        WRK_TRY(ld.matrix(att + ".output.weight", quant, discount, &L.att_w_o));
+        WRK_TRY(ld.layer_norm(blk + ".ln2", &L.ffn_ln));
+        WRK_TRY(ld.vector_f16(ffn + ".time_mix_k", &L.ffn_time_mix_k));
+        WRK_TRY(ld.vector_f16(ffn + ".time_mix_r", &L.ffn_time_mix_r));
+        WRK_TRY(ld.matrix(ffn + ".receptance.weight", quant, 1.0f, &L.ffn_w_r));
+        WRK_TRY(ld.matrix(ffn + ".key.weight", quant, 1.0f, &L.ffn_w_k));
+        WRK_TRY(ld.matrix(ffn + ".value.weight", quant, discount, &L.ffn_w_v));
+        WRK_CUDA(cudaStreamSynchronize(ctx->stream));
     }
     return WRK_OK;
 }
@@ -759,7 +802,9 @@ int32_t wrk_model_builder_build(wrk_model_builder* b, wrk_model** out) {
         if (s == WRK_OK && b->shard_world > 1) s = plan_shard(b, m);
         Loader ld{b, b->ctx};
         if (s == WRK_OK) s = build_common(ld, m);
-        if (s == WRK_OK) s = m->info.version == 7 ? build_v7(ld, m) : build_v56(ld, m);
+        if (s == WRK_OK && m->info.version == 4 && b->shard_world > 1)
+            s = set_error(WRK_ERR_UNSUPPORTED, "v4 models are not split across GPUs (their time-mix has no heads)");
+        if (s == WRK_OK) s = m->info.version == 7 ? build_v7(ld, m) : m->info.version == 4 ? build_v4(ld, m) : build_v56(ld, m);
     }
     if (s != WRK_OK) {
         delete m;

@@ -398,6 +398,33 @@ int32_t walk_layer_norm(V& v, const char* key, LayerNorm& ln) {
     return v.end();
 }
 
+// `Layer` of v4 (src/runtime/v4.rs:67-103)
+template <class V>
+int32_t walk_layer_v4(V& v, Layer& L) {
+    WRK_TRY(v.map(nullptr, 4));
+    WRK_TRY(walk_layer_norm(v, "att_layer_norm", L.att_ln));
+    WRK_TRY(walk_layer_norm(v, "ffn_layer_norm", L.ffn_ln));
+    WRK_TRY(v.map("att", 9));
+    WRK_TRY(v.tensor("time_decay", L.time_decay, WRK_F32));
+    WRK_TRY(v.tensor("time_first", L.time_first, WRK_F32));
+    WRK_TRY(v.tensor("time_mix_k", L.time_mix_k));
+    WRK_TRY(v.tensor("time_mix_v", L.time_mix_v));
+    WRK_TRY(v.tensor("time_mix_r", L.time_mix_r));
+    WRK_TRY(v.matrix("w_k", L.att_w_k));
+    WRK_TRY(v.matrix("w_v", L.att_w_v));
+    WRK_TRY(v.matrix("w_r", L.att_w_r));
+    WRK_TRY(v.matrix("w_o", L.att_w_o));
+    WRK_TRY(v.end());
+    WRK_TRY(v.map("ffn", 5));
+    WRK_TRY(v.tensor("time_mix_k", L.ffn_time_mix_k));
+    WRK_TRY(v.tensor("time_mix_r", L.ffn_time_mix_r));
+    WRK_TRY(v.matrix("w_k", L.ffn_w_k));
+    WRK_TRY(v.matrix("w_v", L.ffn_w_v));
+    WRK_TRY(v.matrix("w_r", L.ffn_w_r));
+    WRK_TRY(v.end());
+    return v.end();
+}
+
 // `Layer` of v5 (src/runtime/v5.rs:68-118) and v6 (src/runtime/v6.rs:77-118)
 template <class V>
 int32_t walk_layer_v56(V& v, uint32_t version, Layer& L) {
@@ -491,7 +518,6 @@ int32_t walk_model(V& v, wrk_model* m, bool restoring) {
     uint32_t version = info.version - 4;
     WRK_TRY(v.variant("version", versions, 4, version));
     info.version = version + 4;
-    WRK_REQUIRE(info.version >= 5, WRK_ERR_UNSUPPORTED, "serialized model: version %u has no runtime here", info.version);
     uint64_t fields[5] = {info.num_layer, info.num_emb, info.num_hidden, info.num_vocab, info.num_head};
     static const char* names[5] = {"num_layer", "num_emb", "num_hidden", "num_vocab", "num_head"};
     for (int i = 0; i < 5; ++i) {
@@ -515,7 +541,7 @@ int32_t walk_model(V& v, wrk_model* m, bool restoring) {
     WRK_TRY(v.map("tensor", 3));
     WRK_TRY(v.map("embed", 2));
     WRK_TRY(walk_layer_norm(v, v7 ? "ln" : "layer_norm", m->embed_ln));
-    m->num_vocab_padded = (info.num_vocab + 7) / 8 * 8;
+    m->num_vocab_padded = (info.num_vocab + 7) / 8 * 8;  // load_matrix_f16_padded_cpu in every version
     WRK_TRY(v.host_f16("w", m->embed_host, info.num_emb, m->num_vocab_padded));
     WRK_TRY(v.end());
     WRK_TRY(v.map("head", 2));
@@ -528,7 +554,7 @@ int32_t walk_model(V& v, wrk_model* m, bool restoring) {
         WRK_REQUIRE(count == info.num_layer, WRK_ERR_INVALID_ARGUMENT, "serialized model: %zu layers, info says %u", count, info.num_layer);
         m->layers.resize(count);
     }
-    for (auto& L : m->layers) WRK_TRY(v7 ? walk_layer_v7(v, L) : walk_layer_v56(v, info.version, L));
+    for (auto& L : m->layers) WRK_TRY(v7 ? walk_layer_v7(v, L) : info.version == 4 ? walk_layer_v4(v, L) : walk_layer_v56(v, info.version, L));
     if (restoring) WRK_TRY(v.end());
     WRK_TRY(v.end());
     return v.end();

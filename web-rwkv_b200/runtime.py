@@ -210,6 +210,37 @@ def redirect(info):
             [(outputs[2 * i], outputs[2 * i + 1]) for i in range(n)])
 
 
+HOOK_FN = ctypes.CFUNCTYPE(ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p))
+HOOKS = ["POST_EMBED_LOADED", "POST_EMBED_LAYER_NORM", "PRE_ATT", "POST_ATT_LAYER_NORM", "PRE_ATT_TOKEN_SHIFT",
+         "POST_ATT_TOKEN_SHIFT", "PRE_ATT_TOKEN_SHIFT_ADAPT", "POST_ATT_TOKEN_SHIFT_ADAPT_ACTIVATE", "POST_ATT_TOKEN_SHIFT_ADAPT",
+         "PRE_ATT_GATED_TOKEN_SHIFT", "POST_ATT_GATED_TOKEN_SHIFT", "PRE_ATT_LINEAR", "POST_ATT_LINEAR",
+         "PRE_ATT_TIME_DECAY_ADAPT", "POST_ATT_TIME_DECAY_ADAPT_ACTIVATE", "POST_ATT_TIME_DECAY_ADAPT",
+         "PRE_ATT_TIME_DECAY_ACTIVATE", "POST_ATT_TIME_DECAY_ACTIVATE", "PRE_ATT_ADAPT", "POST_ATT_ADAPT", "PRE_ATT_CONTROL",
+         "POST_ATT_CONTROL", "PRE_ATT_VALUE_RESIDUAL", "POST_ATT_VALUE_RESIDUAL", "PRE_ATT_TIME_MIX", "POST_ATT_TIME_MIX",
+         "PRE_ATT_GATE", "POST_ATT_GATE", "PRE_ATT_OUT", "POST_ATT_OUT", "POST_ATT", "PRE_FFN", "POST_FFN_LAYER_NORM",
+         "PRE_FFN_TOKEN_SHIFT", "POST_FFN_TOKEN_SHIFT", "PRE_FFN_LINEAR", "POST_FFN_ACTIVATE", "POST_FFN_LINEAR",
+         "PRE_FFN_CHANNEL_MIX", "POST_FFN_CHANNEL_MIX", "POST_FFN", "PRE_HEAD", "POST_HEAD_LAYER_NORM", "POST_HEAD"]
+HOOK = {name: i for i, name in enumerate(HOOKS)}  # wrk_hook, include/wrk_runtime.h
+
+
+class Frame:
+    """`Frame` (src/runtime/v6.rs:479-487) as a hook sees it: valid only during the callback."""
+
+    def __init__(self, bundle, handle):
+        self.bundle, self.handle = bundle, ctypes.c_void_p(handle)  # the callback receives the pointer as an int
+
+    def buffer(self, name):
+        h = ctypes.c_void_p()
+        check(lib().wrk_frame_buffer(self.handle, name.encode(), ctypes.byref(h)))
+        check(lib().wrk_tensor_retain(h))
+        return Tensor(self.bundle.model.ctx, h)
+
+    def num_token(self):
+        t, n = ctypes.c_uint32(), ctypes.c_uint32()
+        check(lib().wrk_frame_num_token(self.handle, ctypes.byref(t), ctypes.byref(n)))
+        return t.value, n.value
+
+
 class Bundle:
     """`Bundle<f16>` + `State` (src/runtime/v6.rs:489-521, src/runtime/model.rs:78-120)."""
 
@@ -222,7 +253,7 @@ class Bundle:
         else:
             check(lib().wrk_bundle_create_sharded(model.handle, num_batch, comm.handle, ctypes.byref(self.handle)))
         info = model.info
-        self.vocab = (info.num_vocab + 7) // 8 * 8 if info.version != 5 else info.num_vocab
+        self.vocab = (info.num_vocab + 7) // 8 * 8 if info.version >= 6 else info.num_vocab  # v4 / v5 heads are not padded
 
     def __del__(self):
         if getattr(self, "handle", None):
@@ -239,6 +270,34 @@ class Bundle:
         """0: one launch per reference op; 2 (the default of a new bundle): fused kernels, one launch per phase;
         1: fused kernels, v6 jobs of at most 8 tokens as one persistent kernel; 3: as 1, mma.sync engine only."""
         check(lib().wrk_bundle_set_fused(self.handle, int(fused)))
+
+    def set_hook(self, hook, layer, fn):
+        """`HookMap` entry (src/runtime/v6.rs:366-406, 572-581): fn(frame) -> Op or None is called while a job is built,
+        at `hook` (a HOOK_* index) of layer `layer`; None clears it."""
+        if not hasattr(self, "_hooks"):
+            self._hooks = {}
+        key = (int(hook), int(layer))
+        if fn is None:
+            check(lib().wrk_bundle_set_hook(self.handle, key[0], key[1], None, None))
+            self._hooks.pop(key, None)
+            return
+        bundle = self
+
+        def trampoline(_user, frame, out):
+            try:
+                op = fn(Frame(bundle, frame))
+                if op is not None:
+                    out[0] = op.handle.value if hasattr(op.handle, "value") else op.handle
+                    op.handle = None  # the job's op list owns the reference now (the op keeps its buffers alive)
+                return 0
+            except Exception:  # reported as an invalid argument: exceptions cannot cross the C frames
+                import traceback
+                traceback.print_exc()
+                return -103
+
+        cb = HOOK_FN(trampoline)
+        self._hooks[key] = cb
+        check(lib().wrk_bundle_set_hook(self.handle, key[0], key[1], cb, None))
 
     def set_phase_timeline(self, max_phases):
         check(lib().wrk_bundle_set_phase_timeline(self.handle, int(max_phases)))

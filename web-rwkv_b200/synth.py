@@ -23,6 +23,7 @@ CONFIGS = {
     "v6-tiny": (6, 256, 3, 896, 512),
     "v5-tiny": (5, 256, 3, 896, 512),
     "v7-tiny": (7, 256, 3, 1024, 512),
+    "v4-tiny": (4, 256, 3, 1024, 512),
 }
 HEAD_SIZE = 64
 V6_TIME_MIX, V6_TIME_DECAY = 32, 64
@@ -53,14 +54,24 @@ def make_layer(version, layer, C, F, seed):
     if layer == 0:
         t[f"{blk}.ln0.weight"] = _normal(rng, (C,), mean=1.0)
         t[f"{blk}.ln0.bias"] = _normal(rng, (C,))
-    t[f"{att}.ln_x.weight"] = _normal(rng, (C,), mean=1.0)
-    t[f"{att}.ln_x.bias"] = _normal(rng, (C,))
+    if version != 4:
+        t[f"{att}.ln_x.weight"] = _normal(rng, (C,), mean=1.0)
+        t[f"{att}.ln_x.bias"] = _normal(rng, (C,))
     t[f"{att}.key.weight"] = _normal(rng, (C, C))
     t[f"{att}.value.weight"] = _normal(rng, (C, C))
     t[f"{att}.receptance.weight"] = _normal(rng, (C, C))
     t[f"{att}.output.weight"] = _normal(rng, (C, C))
     t[f"{ffn}.key.weight"] = _normal(rng, (F, C))
     t[f"{ffn}.value.weight"] = _normal(rng, (C, F))
+    if version == 4:
+        # per-channel decay (before -exp(.)) and bonus, three static token-shift mixes, receptance-gated FFN
+        t[f"{ffn}.receptance.weight"] = _normal(rng, (C, C))
+        t[f"{att}.time_decay"] = _uniform(rng, (C,), -6.0, 1.0)
+        t[f"{att}.time_first"] = _uniform(rng, (C,), -1.0, 1.0)
+        for n in ("k", "v", "r"):
+            t[f"{att}.time_mix_{n}"] = _uniform(rng, (1, 1, C), 0.0, 1.0)
+        t[f"{ffn}.time_mix_k"] = _uniform(rng, (1, 1, C), 0.0, 1.0)
+        t[f"{ffn}.time_mix_r"] = _uniform(rng, (1, 1, C), 0.0, 1.0)
     if version in (5, 6):
         t[f"{att}.gate.weight"] = _normal(rng, (C, C))
         t[f"{ffn}.receptance.weight"] = _normal(rng, (C, C))
