@@ -372,21 +372,45 @@ def tp_leg(wrk, rt, synth, ctx, rank, world, dist, steps, layers=None):
               "scaling": "strong", "parallelism": f"tp{world}" if world > 1 else "single GPU", "model_build_s": build_s,
               "kernels_per_step": job.num_kernels(), "logit_abs_sum_first_job": checksum}
     if comm is not None:
-        # the collectives of one step alone, on the same communicator and sizes: 2 per layer of [C, 64] f32, plus the gather
+        # the collectives of one step alone, on the same communicator and sizes: 2 per layer of [C, 64] f32
+        def time_ops(make):
+            cmd = ctx.encode(wrk.op_list([make(i) for i in range(2 * L)]), use_graph=True)
+            for _ in range(3):
+                cmd.submit()
+            sync()
+            ctx.timer_start()
+            for _ in range(steps):
+                cmd.submit()
+            t = max_over_ranks(ctx.timer_stop(), dist)
+            sync()
+            return t / steps
+
         part = ctx.tensor(wrk.F32, [C, TP_BATCH], zeros=True)
-        op = wrk.op_list([comm.all_reduce(part) for _ in range(2 * L)])
-        cmd = ctx.encode(op, use_graph=True)
-        for _ in range(3):
-            cmd.submit()
-        sync()
-        ctx.timer_start()
-        for _ in range(steps):
-            cmd.submit()
-        ar_ms = max_over_ranks(ctx.timer_stop(), dist)
-        sync()
-        result["all_reduce"] = {"per_step_ms": ar_ms / steps, "share_of_step": ar_ms / ms, "count_per_step": 2 * L,
-                                "bytes_each": C * TP_BATCH * 4, "kind": "NCCL all-reduce on the job's stream, NVLS off"}
-        del cmd, op, part
+        nccl_ms = time_ops(lambda i: comm.all_reduce(part))
+        result["all_reduce"] = {"count_per_step": 2 * L, "bytes_each": C * TP_BATCH * 4, "nccl_per_step_ms": nccl_ms,
+                                "nccl": "NCCL all-reduce on the job's stream, NVLS off"}
+        if bundle.peer_reduce():
+            dst = ctx.tensor(wrk.F16, [C, TP_BATCH], zeros=True)
+            peer_ms = time_ops(lambda i: comm.peer_all_reduce(i & 1, C * TP_BATCH, dst))
+            # the same jobs with NCCL in place of the peer-memory reduce
+            bundle.set_peer_reduce(0)
+            job_nccl = bundle.dispatch([(1, wrk.RNN_LAST)] * TP_BATCH)
+            for i in range(3):
+                job_nccl.load(tokens[i % 16])
+                job_nccl.submit()
+            sync()
+            ctx.timer_start()
+            for i in range(steps):
+                job_nccl.load(tokens[i % 16])
+                job_nccl.submit()
+            ms_nccl = max_over_ranks(ctx.timer_stop(), dist)
+            sync()
+            del job_nccl
+            result["all_reduce"].update({"used": "one-shot reduce over peer memory (plain loads over NVLink, sums in rank order)",
+                                         "per_step_ms": peer_ms, "share_of_step": peer_ms * steps / ms,
+                                         "value_with_nccl": steps * TP_BATCH / (ms_nccl * 1e-3)})
+        else:
+            result["all_reduce"].update({"used": "NCCL", "per_step_ms": nccl_ms, "share_of_step": nccl_ms * steps / ms})
     del job, bundle, model
     if comm is not None:
         import gc

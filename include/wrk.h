@@ -282,6 +282,17 @@ int32_t wrk_comm_wait(wrk_comm* comm, uint32_t timeout_ms);
  * when failure(user) is (may be null), WRK_ERR_TIMEOUT after timeout_ms; polls every poll_us microseconds. */
 int32_t wrk_watchdog_wait(int32_t (*done)(void*), int32_t (*failure)(void*), void* user, uint32_t timeout_ms, uint32_t poll_us);
 int32_t wrk_comm_rank(const wrk_comm* comm, int32_t* rank, int32_t* world);
+/* One-shot all-reduce over peer memory.  wrk_comm_enable_peer_reduce is itself a collective (every rank calls it at the
+ * same point, outside any graph capture): each rank allocates two slots of `slot_bytes` and a flag word per rank, the CUDA
+ * IPC handles travel through an NCCL all-gather, every rank maps every other rank's region.  wrk_comm_peer_slot returns a
+ * tensor over one of this rank's slots (a matmul's f32 output goes there directly); wrk_op_peer_all_reduce makes every
+ * rank signal its slot, wait (bounded; WRK_ERR_TIMEOUT in the device status word on expiry) for all ranks' signals and
+ * add the ranks' slots in rank order with plain loads over NVLink into `dst` (f16 or f32).  Consecutive reduces on a
+ * communicator alternate between slot 0 and slot 1. */
+int32_t wrk_comm_enable_peer_reduce(wrk_comm* comm, size_t slot_bytes);
+int32_t wrk_comm_peer_slot_bytes(const wrk_comm* comm, size_t* slot_bytes); /* 0 before wrk_comm_enable_peer_reduce */
+int32_t wrk_comm_peer_slot(wrk_comm* comm, uint32_t slot, int32_t dtype, const uint32_t shape[4], wrk_tensor** out);
+int32_t wrk_op_peer_all_reduce(wrk_comm* comm, uint32_t slot, size_t count, wrk_tensor* dst, wrk_op** out);
 /* x <- sum over ranks of x, in place (f16 or f32). */
 int32_t wrk_op_all_reduce(wrk_comm* comm, wrk_tensor* x, wrk_op** out);
 /* output (world x len(input) elements) <- every rank's input, in rank order. */

@@ -96,6 +96,11 @@ int32_t wrk_bundle_create(wrk_model* model, uint32_t num_batch, wrk_bundle** out
  * vocabulary rows gathered into full logits.  Every rank submits the same jobs in the same order.  State rows of
  * heads the rank does not own stay zero (wrk_state_back returns them so). */
 int32_t wrk_bundle_create_sharded(wrk_model* model, uint32_t num_batch, wrk_comm* comm, wrk_bundle** out);
+/* How the partial sums of a sharded bundle meet: 1 = the one-shot reduce over peer memory (wrk_op_peer_all_reduce; the
+ * matmuls write into the exchange slots, no copy), the default where wrk_bundle_create_sharded could set the exchange
+ * region up (jobs of up to 256 tokens; larger ones use NCCL); 0 = NCCL all-reduce.  Every rank sets the same value. */
+int32_t wrk_bundle_set_peer_reduce(wrk_bundle* b, int32_t on);
+int32_t wrk_bundle_peer_reduce(const wrk_bundle* b, int32_t* on);
 int32_t wrk_bundle_release(wrk_bundle* b);
 /* Cursor format uploaded with every job: 0 (default) = three u32 per token, exact for any run length;
  * 1 = the reference's packed u32 (8-bit batch, 16-bit token, 8-bit len: src/tensor/mod.rs:53-60). */

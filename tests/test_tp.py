@@ -104,3 +104,6 @@ def test_sharded_bundles_match_the_whole_model():
         pytest.skip("needs two GPUs")
     outs = _spawn("gpu", 2, free_port())
     assert "tp logits match" in outs[0]
+    # where the two GPUs can map each other's memory the one-shot reduce is what ran, and it agrees with NCCL
+    if "peer reduce True" in outs[0]:
+        assert outs[0].count("peer reduce matches nccl") == 4

@@ -154,6 +154,22 @@ def main():
         got = drive(bundle)
         comm.wait(20000)
         assert ctx.device_status() == 0
+        # the same jobs with the partial sums through NCCL instead of peer memory
+        say(config, "peer reduce", bundle.peer_reduce())
+        if bundle.peer_reduce():
+            nccl_bundle = rt.Bundle(model, 3, comm)
+            nccl_bundle.set_peer_reduce(0)
+            got_nccl = drive(nccl_bundle)
+            comm.wait(20000)
+            for g, w in zip(got, got_nccl):
+                for bi in range(3):
+                    assert g[bi].shape == w[bi].shape
+                    if w[bi].size:
+                        err = float(np.max(np.abs(g[bi] - w[bi]) / np.maximum(1.0, np.abs(w[bi]))))
+                        assert err <= 2e-2, (config, "peer vs nccl", err)
+            del nccl_bundle
+            if rank == 0:
+                print("peer reduce matches nccl", config, flush=True)
         # packed bytes of a rank's slice are the slice of the whole model's packing
         if rank == 0:
             whole = rt.ModelBuilder(ctx).add_tensors(tensors).quant(qmap).build()

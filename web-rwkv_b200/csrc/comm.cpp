@@ -13,6 +13,7 @@
 #include <string>
 
 #include "common.h"
+#include "kernels/kernels.h"
 
 // NCCL is bound at first use, not at link time: a process that never shards does not load it, and one that
 // has already loaded an NCCL (e.g. through torch.distributed) keeps using that single copy.
@@ -48,11 +49,29 @@ const NcclApi& nccl() {
 }  // namespace
 #define WRK_NEED_NCCL() WRK_REQUIRE(nccl().ok, WRK_ERR_NCCL, "libnccl.so.2 could not be loaded")
 
+// The exchange region of the one-shot all-reduce over peer memory: this rank's two slots and flag words (plain
+// cudaMalloc memory, exported with CUDA IPC) and the mappings of every other rank's region.
+struct Exchange {
+    int device = 0, rank = 0, world = 1;
+    size_t slot_bytes = 0;
+    void* local = nullptr;
+    void* regions[wrk::k::kMaxPeers] = {};
+    uint32_t* counters = nullptr;  // [0] sequence number of the last finished call, [1] CTAs done in the running call
+    ~Exchange() {
+        cudaSetDevice(device);
+        for (int r = 0; r < world; ++r)
+            if (r != rank && regions[r]) cudaIpcCloseMemHandle(regions[r]);
+        if (local) cudaFree(local);
+        if (counters) cudaFree(counters);
+    }
+};
+
 struct wrk_comm {
     std::atomic<int> refs{1};
     wrk_context* ctx = nullptr;
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1;
+    std::shared_ptr<Exchange> exchange;
 };
 
 namespace {
@@ -205,6 +224,128 @@ int32_t wrk_comm_rank(const wrk_comm* comm, int32_t* rank, int32_t* world) {
     WRK_REQUIRE(comm && rank && world, WRK_ERR_INVALID_ARGUMENT, "null argument");
     *rank = comm->rank;
     *world = comm->world;
+    return WRK_OK;
+}
+
+// Collective over the ranks (every rank calls it at the same point): allocates this rank's exchange region, passes its IPC
+// handle around with an NCCL all-gather and maps the peers' regions.
+int32_t wrk_comm_enable_peer_reduce(wrk_comm* comm, size_t slot_bytes) {
+    WRK_REQUIRE(comm, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(comm->comm, WRK_ERR_NCCL, "the communicator was aborted by an earlier failure");
+    WRK_REQUIRE(comm->world <= wrk::k::kMaxPeers, WRK_ERR_UNSUPPORTED, "peer reduce is built for up to %d ranks", wrk::k::kMaxPeers);
+    WRK_REQUIRE(slot_bytes >= 16 && slot_bytes % 256 == 0, WRK_ERR_INVALID_ARGUMENT, "slot of %zu bytes: a multiple of 256", slot_bytes);
+    if (comm->exchange && comm->exchange->slot_bytes >= slot_bytes) return WRK_OK;
+    WRK_REQUIRE(!comm->exchange, WRK_ERR_UNSUPPORTED, "the exchange region holds slots of %zu bytes; it is sized once", comm->exchange->slot_bytes);
+    wrk_context* ctx = comm->ctx;
+    WRK_CUDA(cudaSetDevice(ctx->device));
+    auto ex = std::make_shared<Exchange>();
+    ex->device = ctx->device;
+    ex->rank = comm->rank;
+    ex->world = comm->world;
+    ex->slot_bytes = slot_bytes;
+    const size_t region = 2 * slot_bytes + 256;
+    WRK_CUDA(cudaMalloc(&ex->local, region));
+    WRK_CUDA(cudaMemset(ex->local, 0, region));  // flags at zero before any peer can reach them
+    WRK_CUDA(cudaMalloc(reinterpret_cast<void**>(&ex->counters), 256));
+    WRK_CUDA(cudaMemset(ex->counters, 0, 256));
+    cudaIpcMemHandle_t mine;
+    WRK_CUDA(cudaIpcGetMemHandle(&mine, ex->local));
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handles travel as 64 bytes");
+    uint8_t* dev = nullptr;  // [world + 1][64]: this rank's handle, then every rank's
+    WRK_CUDA(cudaMalloc(reinterpret_cast<void**>(&dev), (size_t)(comm->world + 1) * 64));
+    std::vector<cudaIpcMemHandle_t> all(comm->world);
+    cudaError_t e = cudaMemcpyAsync(dev, &mine, 64, cudaMemcpyHostToDevice, ctx->stream);
+    ncclResult_t r = ncclSuccess;
+    if (e == cudaSuccess) r = nccl().AllGather(dev, dev + 64, 64, ncclUint8, comm->comm, ctx->stream);
+    if (e == cudaSuccess && r == ncclSuccess) e = cudaMemcpyAsync(all.data(), dev + 64, (size_t)comm->world * 64, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess && r == ncclSuccess) e = cudaStreamSynchronize(ctx->stream);
+    cudaFree(dev);
+    if (r != ncclSuccess) return nccl_fail("ncclAllGather (IPC handles)", r);
+    if (e != cudaSuccess) return wrk::set_error(WRK_ERR_CUDA, "exchanging IPC handles failed: %s", cudaGetErrorString(e));
+    for (int p = 0; p < comm->world; ++p) {
+        if (p == comm->rank) {
+            ex->regions[p] = ex->local;
+            continue;
+        }
+        e = cudaIpcOpenMemHandle(&ex->regions[p], all[p], cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            ex->regions[p] = nullptr;
+            return wrk::set_error(WRK_ERR_CUDA, "mapping rank %d's exchange region failed: %s", p, cudaGetErrorString(e));
+        }
+    }
+    // nobody proceeds (and starts writing flags) before every rank has mapped every region
+    float* token = nullptr;
+    WRK_CUDA(cudaMalloc(reinterpret_cast<void**>(&token), 256));
+    WRK_CUDA(cudaMemsetAsync(token, 0, 256, ctx->stream));
+    r = nccl().AllReduce(token, token, 1, ncclFloat32, ncclSum, comm->comm, ctx->stream);
+    e = cudaStreamSynchronize(ctx->stream);
+    cudaFree(token);
+    if (r != ncclSuccess) return nccl_fail("ncclAllReduce (barrier)", r);
+    if (e != cudaSuccess) return wrk::set_error(WRK_ERR_CUDA, "barrier after mapping failed: %s", cudaGetErrorString(e));
+    comm->exchange = ex;
+    return WRK_OK;
+}
+
+int32_t wrk_comm_peer_slot_bytes(const wrk_comm* comm, size_t* slot_bytes) {
+    WRK_REQUIRE(comm && slot_bytes, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    *slot_bytes = comm->exchange ? comm->exchange->slot_bytes : 0;
+    return WRK_OK;
+}
+
+// A tensor over slot `slot` (0 or 1) of this rank's exchange region: what a matmul writes its partial sums into.
+int32_t wrk_comm_peer_slot(wrk_comm* comm, uint32_t slot, int32_t dtype, const uint32_t shape[4], wrk_tensor** out) {
+    WRK_REQUIRE(comm && shape && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(comm->exchange, WRK_ERR_INVALID_ARGUMENT, "wrk_comm_enable_peer_reduce has not run on this communicator");
+    WRK_REQUIRE(slot < 2, WRK_ERR_INVALID_ARGUMENT, "slot %u: 0 or 1", slot);
+    auto t = new wrk_tensor();
+    t->ctx = comm->ctx;
+    t->dtype = dtype;
+    for (int i = 0; i < 4; ++i) t->shape.v[i] = shape[i];
+    if (wrk::dtype_size(dtype) == 0 || t->bytes() > comm->exchange->slot_bytes) {
+        const size_t need = t->bytes();
+        delete t;
+        return wrk::set_error(WRK_ERR_SIZE, "a slot holds %zu bytes, the tensor needs %zu", comm->exchange->slot_bytes, need);
+    }
+    auto buf = std::make_shared<wrk::Buffer>(comm->ctx);
+    buf->ptr = static_cast<uint8_t*>(comm->exchange->local) + (size_t)slot * comm->exchange->slot_bytes;
+    buf->bytes = t->bytes();
+    buf->external = comm->exchange;  // the region outlives the tensor
+    t->buf = buf;
+    *out = t;
+    return WRK_OK;
+}
+
+// dst <- sum over the ranks of the first `count` f32 of slot `slot`, added in rank order by every rank from peer memory.
+int32_t wrk_op_peer_all_reduce(wrk_comm* comm, uint32_t slot, size_t count, wrk_tensor* dst, wrk_op** out) {
+    WRK_REQUIRE(comm && dst && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    WRK_REQUIRE(comm->exchange, WRK_ERR_INVALID_ARGUMENT, "wrk_comm_enable_peer_reduce has not run on this communicator");
+    WRK_REQUIRE(dst->ctx == comm->ctx, WRK_ERR_INVALID_ARGUMENT, "tensor and communicator belong to different contexts");
+    WRK_REQUIRE(slot < 2 && count % 4 == 0 && count * 4 <= comm->exchange->slot_bytes, WRK_ERR_SIZE,
+                "slot %u, %zu elements: slots are 0 or 1, counts multiples of 4 within %zu bytes", slot, count, comm->exchange->slot_bytes);
+    WRK_REQUIRE((dst->dtype == WRK_F16 || dst->dtype == WRK_F32) && dst->len() == count, WRK_ERR_SIZE,
+                "the destination holds %zu elements, the sum %zu", dst->len(), count);
+    wrk::k::PeerReduceArgs a{};
+    auto ex = comm->exchange;
+    for (int r = 0; r < comm->world; ++r) a.regions[r] = ex->regions[r];
+    a.world = (uint32_t)comm->world;
+    a.rank = (uint32_t)comm->rank;
+    a.slot = slot;
+    a.slot_bytes = ex->slot_bytes;
+    a.count = count;
+    a.dst = dst->ptr();
+    a.dst_dtype = dst->dtype;
+    a.epoch = ex->counters;
+    a.done = ex->counters + 1;
+    a.status = comm->ctx->device_status;
+    const int sms = comm->ctx->num_sms;
+    auto hold = std::make_shared<CommHold>(comm);
+    *out = wrk::new_atom("peer_all_reduce",
+                         [=](cudaStream_t s) {
+                             (void)hold;
+                             (void)ex;
+                             return wrk::k::peer_all_reduce(a, sms, s);
+                         },
+                         {dst});
     return WRK_OK;
 }
 

@@ -69,6 +69,7 @@ struct Buffer {
     wrk_context* ctx = nullptr;
     void* ptr = nullptr;
     size_t bytes = 0;
+    std::shared_ptr<void> external;  // set: `ptr` lies in memory this object keeps alive and is not freed with the buffer
     explicit Buffer(wrk_context* owner);
     Buffer(const Buffer&) = delete;
     Buffer& operator=(const Buffer&) = delete;

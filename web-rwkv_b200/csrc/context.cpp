@@ -38,7 +38,7 @@ static void context_unref(wrk_context* ctx) {
 Buffer::Buffer(wrk_context* owner) : ctx(owner) { ctx->refs.fetch_add(1); }
 
 Buffer::~Buffer() {
-    if (ptr) {
+    if (ptr && !external) {
         cudaSetDevice(ctx->device);
         cudaFreeAsync(ptr, ctx->stream);
     }

@@ -166,8 +166,11 @@ __device__ __forceinline__ float4 ld_peer_smem(uint32_t local_addr, uint32_t ran
 
 __device__ __forceinline__ uint32_t pack_half2(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
 
-// (Sixteen dequantizing warps, each taking half of a step's columns, measured the same as eight: Int8 4096 x 4096 at
-// 64 / 1024 tokens 19.3 / 72.5 us against 19.1 / 74.4 us.  The convert chain's latency is not what paces the kernel.)
+// Two variations measured the same as this arrangement and were dropped: sixteen dequantizing warps, each taking half of
+// a step's columns (Int8 4096 x 4096 at 64 / 1024 tokens: 19.3 / 72.5 us against 19.1 / 74.4 us), and four MMA issuer
+// warps with an accumulator each (19.2 us at 64 tokens, slower at 256).  Neither the convert chain's latency nor the
+// single issuing thread paces the kernel at few tokens; its fixed work per launch does (set-up, pipeline fill,
+// epilogue, cluster reduction: about 10 of the 19 us).
 // 32 (Int8) weights of one row, raw bytes in `q0, q1`, block scale (min, max) -> four 16-byte groups of fp16.
 __device__ __forceinline__ void dequant_int8(uint4 q0, uint4 q1, uint32_t minmax, uint4 out[4]) {
     // f32 dequantization, one rounding to fp16 per weight: the errors of a row are independent, none is

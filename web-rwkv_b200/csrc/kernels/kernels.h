@@ -53,6 +53,21 @@ cudaError_t matmul_small(const MatmulArgs& a, int num_sms, cudaStream_t stream);
 bool matmul_umma_supported(const MatmulArgs& a);
 cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t stream);
 
+// ---- one-shot all-reduce over peer memory (peer_reduce.cu) --------------------------------------------
+constexpr int kMaxPeers = 8;
+struct PeerReduceArgs {
+    void* regions[kMaxPeers];  // every rank's exchange region ([slot 0][slot 1][flags: one u32 per rank]); [rank] is local
+    uint32_t world, rank, slot;
+    size_t slot_bytes;
+    size_t count;              // f32 elements to add, a multiple of 4
+    void* dst;                 // local destination, f16 or f32
+    int dst_dtype;
+    uint32_t* epoch;           // local: sequence number of the last finished call
+    uint32_t* done;            // local: CTAs of the running call that have finished
+    int32_t* status;
+};
+cudaError_t peer_all_reduce(const PeerReduceArgs& a, int num_sms, cudaStream_t stream);
+
 // ---- WKV recurrences (wkv.cu) ------------------------------------------------------------
 struct WkvArgs {
     const uint32_t* cursors;  // packed [T] or wide [3 * T]

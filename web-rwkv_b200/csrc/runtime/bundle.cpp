@@ -54,6 +54,7 @@ struct wrk_bundle {
     std::map<std::pair<int32_t, uint32_t>, HookEntry> hooks;  // (hook, layer; 0 for the embed / head hooks)
     const Buffers* building_header = nullptr;  // of the job being built (for the hooks' frame)
     uint32_t building_tokens = 0, building_headers = 0;
+    bool peer_reduce = false;  // partial sums meet through the communicator's exchange region instead of NCCL
     wrk_comm* comm = nullptr;  // a rank of a split model: sums of partial products cross this communicator
     bool packed_cursors = false, use_graph = true, fused = true;
     bool step_kernel = false;  // fused jobs of at most 8 tokens run as one persistent kernel where the job shape allows it
@@ -161,7 +162,19 @@ int32_t make_runtime(wrk_bundle* bd, uint32_t T, std::shared_ptr<Buffers>* out) 
     WRK_TRY(alloc(ctx, *b, "x", H16, C, T));
     if (sh.on()) {
         WRK_TRY(alloc(ctx, *b, "att_xl", H16, Cl, T));
-        WRK_TRY(alloc(ctx, *b, "partial", F32, C, T));
+        size_t slot_bytes = 0;
+        if (bd->peer_reduce) WRK_TRY(wrk_comm_peer_slot_bytes(bd->comm, &slot_bytes));
+        if ((size_t)C * T * 4 <= slot_bytes) {
+            // the partial sums of `output` (slot 0) and ffn `value` (slot 1) are written where the peers read them
+            const uint32_t shape[4] = {C, T, 1, 1};
+            for (uint32_t slot = 0; slot < 2; ++slot) {
+                wrk_tensor* t = nullptr;
+                WRK_TRY(wrk_comm_peer_slot(bd->comm, slot, WRK_F32, shape, &t));
+                b->t[slot == 0 ? "partial0" : "partial1"] = TensorH(t);
+            }
+        } else {
+            WRK_TRY(alloc(ctx, *b, "partial", F32, C, T));
+        }
     }
     if (info.version == 7) {
         for (auto n : {"att_x", "att_rx", "att_wx", "att_kx", "att_vx", "att_ax", "att_gx", "att_o", "ffn_x", "ffn_kx", "ffn_v"})
@@ -362,10 +375,20 @@ wrk_view state_wkv(wrk_bundle* bd, uint32_t layer, uint32_t S, const Split& sp) 
     }
     return v;
 }
-// `partial` holds this rank's share of a product over all C channels: sum over the ranks, round to fp16 once.
-int32_t reduce_partial(wrk_bundle* bd, OpList& ops, const Buffers& B, wrk_tensor* out) {
-    ADD(wrk_op_all_reduce(bd->comm, B["partial"], &_o));
-    return blit(ops, V(B["partial"]), V(out));
+// Where `output` (which = 0) / ffn `value` (which = 1) write this rank's share of their product over all C channels.
+wrk_tensor* partial_of(const Buffers& B, uint32_t which) {
+    if (B.t.count("partial")) return B["partial"];
+    return B[which == 0 ? "partial0" : "partial1"];
+}
+// Sum over the ranks, round to fp16 once: NCCL all-reduce in place + a copy, or the one-shot reduce over peer memory,
+// whose two slots the two reduces of a layer use in turn.
+int32_t reduce_partial(wrk_bundle* bd, OpList& ops, const Buffers& B, wrk_tensor* out, uint32_t which) {
+    if (B.t.count("partial")) {
+        ADD(wrk_op_all_reduce(bd->comm, B["partial"], &_o));
+        return blit(ops, V(B["partial"]), V(out));
+    }
+    ADD(wrk_op_peer_all_reduce(bd->comm, which, out->len(), out, &_o));
+    return WRK_OK;
 }
 // The time-mix op has written the shift row (the normalised input of every sequence's last token) for the rank's
 // channels only; the next job's token shifts read all of them.
@@ -467,9 +490,9 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
     }
     HOOK(POST_ATT_GATE);
     HOOK(PRE_ATT_OUT);
-    WRK_TRY(matmul(ops, L.att_w_o, V(att_loc), V(sp.on ? B["partial"] : B["att_o"]), WRK_ACT_NONE, turbo));
+    WRK_TRY(matmul(ops, L.att_w_o, V(att_loc), V(sp.on ? partial_of(B, 0) : B["att_o"]), WRK_ACT_NONE, turbo));
     if (sp.on) {
-        WRK_TRY(reduce_partial(bd, ops, B, B["att_o"]));
+        WRK_TRY(reduce_partial(bd, ops, B, B["att_o"], 0));
         WRK_TRY(carry_all_channels(bd, ops, B, index, S));
     }
     HOOK(POST_ATT_OUT);
@@ -487,8 +510,8 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
     HOOK(PRE_FFN_LINEAR);
     WRK_TRY(matmul(ops, L.ffn_w_k, V(B["ffn_kx"]), V(B["ffn_k"]), WRK_ACT_SQUARED_RELU, turbo));
     HOOK(POST_FFN_ACTIVATE);
-    WRK_TRY(matmul(ops, L.ffn_w_v, V(B["ffn_k"]), V(sp.on ? B["partial"] : B["ffn_v"]), WRK_ACT_NONE, turbo, true));
-    if (sp.on) WRK_TRY(reduce_partial(bd, ops, B, B["ffn_v"]));
+    WRK_TRY(matmul(ops, L.ffn_w_v, V(B["ffn_k"]), V(sp.on ? partial_of(B, 1) : B["ffn_v"]), WRK_ACT_NONE, turbo, true));
+    if (sp.on) WRK_TRY(reduce_partial(bd, ops, B, B["ffn_v"], 1));
     WRK_TRY(matmul(ops, L.ffn_w_r, V(B["ffn_rx"]), V(B["ffn_r"]), WRK_ACT_NONE, turbo));
     HOOK(POST_FFN_LINEAR);
     HOOK(PRE_FFN_CHANNEL_MIX);
@@ -591,9 +614,9 @@ int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, 
     }
     HOOK(POST_ATT_GATE);
     HOOK(PRE_ATT_OUT);
-    WRK_TRY(matmul(ops, L.att_w_o, V(att_loc), V(sp.on ? B["partial"] : B["att_o"]), WRK_ACT_NONE, turbo));
+    WRK_TRY(matmul(ops, L.att_w_o, V(att_loc), V(sp.on ? partial_of(B, 0) : B["att_o"]), WRK_ACT_NONE, turbo));
     if (sp.on) {
-        WRK_TRY(reduce_partial(bd, ops, B, B["att_o"]));
+        WRK_TRY(reduce_partial(bd, ops, B, B["att_o"], 0));
         WRK_TRY(carry_all_channels(bd, ops, B, index, S));
     }
     HOOK(POST_ATT_OUT);
@@ -610,8 +633,8 @@ int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, 
     HOOK(PRE_FFN_LINEAR);
     WRK_TRY(matmul(ops, L.ffn_w_k, V(B["ffn_kx"]), V(B["ffn_k"]), WRK_ACT_SQUARED_RELU, turbo));
     HOOK(POST_FFN_ACTIVATE);
-    WRK_TRY(matmul(ops, L.ffn_w_v, V(B["ffn_k"]), V(sp.on ? B["partial"] : B["ffn_v"]), WRK_ACT_NONE, turbo, true));
-    if (sp.on) WRK_TRY(reduce_partial(bd, ops, B, B["ffn_v"]));
+    WRK_TRY(matmul(ops, L.ffn_w_v, V(B["ffn_k"]), V(sp.on ? partial_of(B, 1) : B["ffn_v"]), WRK_ACT_NONE, turbo, true));
+    if (sp.on) WRK_TRY(reduce_partial(bd, ops, B, B["ffn_v"], 1));
     HOOK(POST_FFN_LINEAR);
     HOOK(PRE_FFN_CHANNEL_MIX);
     {
@@ -1253,6 +1276,7 @@ int32_t ensure_staging(wrk_bundle* bd, size_t tokens) {
 extern "C" {
 
 static int32_t bundle_create(wrk_model* model, uint32_t num_batch, wrk_comm* comm, wrk_bundle** out);
+static void drop_caches(wrk_bundle* b);
 
 int32_t wrk_bundle_create(wrk_model* model, uint32_t num_batch, wrk_bundle** out) {
     WRK_REQUIRE(model && out, WRK_ERR_INVALID_ARGUMENT, "null argument");
@@ -1268,7 +1292,30 @@ int32_t wrk_bundle_create_sharded(wrk_model* model, uint32_t num_batch, wrk_comm
     WRK_REQUIRE((uint32_t)world == model->shard.world && (uint32_t)rank == model->shard.rank, WRK_ERR_INVALID_ARGUMENT,
                 "the model is rank %u of %u, the communicator rank %d of %d", model->shard.rank, model->shard.world, rank, world);
     if (world == 1) return bundle_create(model, num_batch, nullptr, out);
-    return bundle_create(model, num_batch, comm, out);
+    WRK_TRY(bundle_create(model, num_batch, comm, out));
+    // slots for jobs of up to 256 tokens; larger jobs, or a node without peer access, use NCCL
+    const size_t slot = ((size_t)model->info.num_emb * 256 * 4 + 255) / 256 * 256;
+    (*out)->peer_reduce = wrk_comm_enable_peer_reduce(comm, slot) == WRK_OK;
+    return WRK_OK;
+}
+
+int32_t wrk_bundle_set_peer_reduce(wrk_bundle* b, int32_t on) {
+    WRK_REQUIRE(b, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    if (on) {
+        size_t bytes = 0;
+        WRK_REQUIRE(b->comm, WRK_ERR_INVALID_ARGUMENT, "the bundle is not a rank of a split model");
+        WRK_TRY(wrk_comm_peer_slot_bytes(b->comm, &bytes));
+        WRK_REQUIRE(bytes != 0, WRK_ERR_UNSUPPORTED, "the communicator has no exchange region (peer access unavailable)");
+    }
+    drop_caches(b);
+    b->peer_reduce = on != 0;
+    return WRK_OK;
+}
+
+int32_t wrk_bundle_peer_reduce(const wrk_bundle* b, int32_t* on) {
+    WRK_REQUIRE(b && on, WRK_ERR_INVALID_ARGUMENT, "null argument");
+    *on = b->peer_reduce ? 1 : 0;
+    return WRK_OK;
 }
 
 static int32_t bundle_create(wrk_model* model, uint32_t num_batch, wrk_comm* comm, wrk_bundle** out) {

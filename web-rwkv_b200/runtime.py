@@ -271,6 +271,15 @@ class Bundle:
         1: fused kernels, v6 jobs of at most 8 tokens as one persistent kernel; 3: as 1, mma.sync engine only."""
         check(lib().wrk_bundle_set_fused(self.handle, int(fused)))
 
+    def set_peer_reduce(self, on):
+        """A sharded bundle's partial sums through peer memory (1, the default where available) or NCCL (0)."""
+        check(lib().wrk_bundle_set_peer_reduce(self.handle, int(on)))
+
+    def peer_reduce(self):
+        on = ctypes.c_int32()
+        check(lib().wrk_bundle_peer_reduce(self.handle, ctypes.byref(on)))
+        return bool(on.value)
+
     def set_hook(self, hook, layer, fn):
         """`HookMap` entry (src/runtime/v6.rs:366-406, 572-581): fn(frame) -> Op or None is called while a job is built,
         at `hook` (a HOOK_* index) of layer `layer`; None clears it."""

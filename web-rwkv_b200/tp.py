@@ -92,6 +92,21 @@ class Comm:
         """Host wait for everything submitted so far, with the async-error poll and the time limit (`wrk_comm_wait`)."""
         check(lib().wrk_comm_wait(self.handle, int(timeout_ms)))
 
+    def enable_peer_reduce(self, slot_bytes):
+        """Collective: sets up the exchange region of the one-shot all-reduce over peer memory."""
+        check(lib().wrk_comm_enable_peer_reduce(self.handle, ctypes.c_size_t(slot_bytes)))
+
+    def peer_slot(self, slot, dtype, shape):
+        from . import Tensor, _shape4
+        h = ctypes.c_void_p()
+        check(lib().wrk_comm_peer_slot(self.handle, slot, dtype, _shape4(list(shape)), ctypes.byref(h)))
+        return Tensor(self.ctx, h)
+
+    def peer_all_reduce(self, slot, count, dst):
+        h = ctypes.c_void_p()
+        check(lib().wrk_op_peer_all_reduce(self.handle, slot, ctypes.c_size_t(count), dst.handle, ctypes.byref(h)))
+        return Op(h, keep=(self, dst))
+
     def all_reduce(self, x):
         h = ctypes.c_void_p()
         check(lib().wrk_op_all_reduce(self.handle, x.handle, ctypes.byref(h)))
