@@ -207,6 +207,8 @@ __device__ __forceinline__ void dequant_nf4(uint4 q, float am, const float2* lut
     for (int j = 0; j < 4; ++j) out[j] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
 }
 
+// One instantiation per weight format: the dequantizing loop holds only its own format's code.
+template <int KIND>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x) {
     extern __shared__ uint8_t smem_raw[];
@@ -216,11 +218,11 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
     __shared__ int abort_flag;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool quantized = p.kind != MAT_FP16;
+    constexpr bool quantized = KIND != MAT_FP16;
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t b_bytes = p.n_tile * BK * 2;
     const uint32_t stage_bytes = A_STAGE_BYTES + b_bytes;                   // [A | B], both 1024-byte aligned
-    const uint32_t raw_row = p.kind == MAT_INT8 ? 64u : 32u;                // raw bytes per row and step
+    constexpr uint32_t raw_row = KIND == MAT_INT8 ? 64u : 32u;              // raw bytes per row and step
     const uint32_t raw_bytes = BM * raw_row;
     uint8_t* raw_base = smem + (size_t)p.stages * stage_bytes;              // raw weight stages
     uint8_t* scale_base = raw_base + (size_t)p.raw * raw_bytes;             // [2 groups][2 slots][BM][8 bytes]
@@ -243,7 +245,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (p.kind == MAT_NF4 && threadIdx.x < 256) lut2[threadIdx.x] = make_float2(p.table[threadIdx.x & 15], p.table[threadIdx.x >> 4]);
+    if (KIND == MAT_NF4 && threadIdx.x < 256) lut2[threadIdx.x] = make_float2(p.table[threadIdx.x & 15], p.table[threadIdx.x >> 4]);
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(&tmem_base_slot)), "r"(p.tmem_cols)
                      : "memory");
@@ -273,7 +275,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
                 asm volatile("cp.async.wait_group 1;\n" ::: "memory");
                 const uint8_t* ss = my_scale + (j & 1) * SCALE_SLOT_BYTES;
                 const uint32_t kt0 = 4 * j + 2 * group;
-#pragma unroll
+#pragma unroll 1
                 for (uint32_t d = 0; d < 2; ++d) {
                     const uint32_t kt = kt0 + d;
                     if (kt >= nk) break;
@@ -286,7 +288,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
                     uint4 wv[4];
 #pragma unroll
                     for (uint32_t h = 0; h < 2; ++h) {  // columns 32 h .. 32 h + 31 of the step
-                        if (p.kind == MAT_INT8)  // a 128-column block is two steps: this group's pair shares (min, max)
+                        if (KIND == MAT_INT8)  // a 128-column block is two steps: this group's pair shares (min, max)
                             dequant_int8(rs[2 * h], rs[2 * h + 1], *reinterpret_cast<const uint32_t*>(ss + group * 4), wv);
                         else
                             dequant_nf4(rs[h], __half2float(*reinterpret_cast<const __half*>(ss + (kt & 3) * 2)), lut2, wv);
@@ -548,8 +550,9 @@ cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t strea
                            CU_TENSOR_MAP_SWIZZLE_128B);
     if (!ok) return cudaErrorInvalidValue;
 
-    static SmemOptIn opt_in;
-    if (cudaError_t e = opt_in.ensure(matmul_umma_kernel, 208 * 1024); e != cudaSuccess) return e;
+    static SmemOptIn opt_in[3];
+    auto kernel = a.kind == MAT_INT8 ? matmul_umma_kernel<MAT_INT8> : a.kind == MAT_NF4 ? matmul_umma_kernel<MAT_NF4> : matmul_umma_kernel<MAT_FP16>;
+    if (cudaError_t e = opt_in[a.kind == MAT_INT8 ? 0 : a.kind == MAT_NF4 ? 1 : 2].ensure(kernel, 208 * 1024); e != cudaSuccess) return e;
     dim3 grid((a.M + BM - 1) / BM, (a.N + p.n_tile - 1) / p.n_tile, 1);
     grid.z = p.splits;
     if (p.splits > 1) {
@@ -571,7 +574,7 @@ cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t strea
     attr[0].val.clusterDim.z = p.splits;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, matmul_umma_kernel, p, map_w, map_x);
+    return cudaLaunchKernelEx(&cfg, kernel, p, map_w, map_x);
 }
 
 }  // namespace k
