@@ -201,6 +201,23 @@ int32_t wrk_op_l2_norm(wrk_tensor* x, float eps, wrk_op** out);
 /* TensorOp::token_shift(cursors, time_mix, state, input, output, reversed), src/tensor/ops.rs:1393-1461 */
 int32_t wrk_op_token_shift(wrk_tensor* cursors, const wrk_view* time_mix, const wrk_view* state,
                            wrk_tensor* input, wrk_tensor* output, int32_t reversed, wrk_op** out);
+/* No counterpart in the reference: runs of its ops as one launch each, with the same arithmetic and the same roundings
+ * per element, so that results are bit-identical to the separate ops.  The runtime uses them where no hook sits between
+ * the ops they replace.
+ *   layer_norm_copy: src <- src + delta when delta is not NULL (TensorOp::add, src/tensor/ops.rs:1656); dst <-
+ *     layer_norm(src) (TensorOp::blit + TensorOp::layer_norm, src/tensor/ops.rs:2015, 407).  Three distinct tensors of
+ *     one shape [C, T, B] and data type.
+ *   token_shift_multi: up to six TensorOp::token_shift (src/tensor/ops.rs:1393-1462) of one f16 input [C, T] with f16
+ *     mixes [C] into f16 outputs [C, T].
+ *   pack_v7: on f16 tensors [S, H, T] of one layer of v7: kk <- l2_norm(k * k_k) per head (blit + mul + l2_norm,
+ *     src/runtime/v7.rs:888-890), k <- control_k(k_a, a, k) (TensorOp::control_k_v7), n[S, H, T, 4] <- k, v, a, kk
+ *     (the four blits of src/runtime/v7.rs:925-928). */
+int32_t wrk_op_layer_norm_copy(wrk_tensor* w, wrk_tensor* b, wrk_tensor* delta, wrk_tensor* src, wrk_tensor* dst, float eps,
+                               wrk_op** out);
+int32_t wrk_op_token_shift_multi(wrk_tensor* cursors, const wrk_view* state, wrk_tensor* input, uint32_t count,
+                                 wrk_tensor* const* time_mix, wrk_tensor* const* outputs, int32_t reversed, wrk_op** out);
+int32_t wrk_op_pack_v7(wrk_tensor* k_k, wrk_tensor* k_a, wrk_tensor* k, wrk_tensor* v, wrk_tensor* a, wrk_tensor* kk, wrk_tensor* n,
+                       float eps, wrk_op** out);
 /* No counterpart in the reference, where the time-mix and channel-mix shaders store this row themselves
  * (src/shaders/time_mix_v6.wgsl:100, channel_mix.wgsl:98): state row 0 of every sequence with tokens in the job <- x at
  * that sequence's last token.  A rank of a split model uses it for the channels its time-mix op does not own. */

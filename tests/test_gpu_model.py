@@ -95,6 +95,41 @@ def test_decode_loop(ctx, config, fused):
     assert_close(bundle.state_back(0), np.stack([s[0] for s in state]), "state")
 
 
+@pytest.mark.parametrize("config,quant,saved", [("v7-tiny", {0: 1, 1: 2}, 15), ("v7-tiny", {}, 15), ("v5-tiny", {0: 1}, 7),
+                                                ("v6-tiny", {0: 2}, 4)])
+def test_merged_elementwise_launches_are_bit_identical_to_the_op_list(ctx, config, quant, saved):
+    """layer_norm_copy, token_shift_multi and pack_v7 stand for runs of the reference's elementwise ops
+    (src/runtime/v7.rs:762-928, v6.rs:771-1010, v5.rs:686-870); the strict mode runs those ops one by one."""
+    rng = np.random.default_rng(2003)
+    tensors, model, ref = _build(ctx, config, quant)
+    V = model.info.num_vocab
+    batches = [(rng.integers(0, V - 1, 45).tolist(), FULL), (rng.integers(0, V - 1, 3).tolist(), LAST)]
+    results = []
+    for fused in (2, 0):
+        bundle = rt.Bundle(model, 2)
+        bundle.set_fused(fused)
+        inp = rt.RnnInput(batches, 32)
+        outs = []
+        while inp.num_token():
+            outs += [g.copy() for g in bundle.infer(inp)]
+        for _ in range(0 if config == "v6-tiny" else 3):  # single-token jobs (v6 has fused kernels of its own for those)
+            inp.append(0, [5])
+            inp.append(1, [7])
+            outs += [g.copy() for g in bundle.infer(inp)]
+        before = ctx.launch_count()
+        inp.append(0, list(range(9, 20)))
+        inp.append(1, [11])
+        outs += [g.copy() for g in bundle.infer(inp)]
+        results.append((outs, [bundle.state_back(b) for b in range(2)], ctx.launch_count() - before))
+    (a, sa, la), (b, sb, lb) = results
+    assert len(a) == len(b)
+    for i, (x, y) in enumerate(zip(a, b)):
+        assert np.array_equal(x, y), (i, float(np.abs(x - y).max()) if x.size else None)
+    for x, y in zip(sa, sb):
+        assert np.array_equal(x, y), float(np.abs(x - y).max())
+    assert lb - la == saved * model.info.num_layer, (la, lb)
+
+
 def test_packed_bytes_and_scales_match_the_oracle(ctx):
     tensors, model, ref = _build(ctx, "v6-tiny", {0: 1, 1: 2})
     names = {"att.w_k": "w_k", "att.w_v": "w_v", "att.w_r": "w_r", "att.w_g": "w_g", "att.w_o": "w_o",

@@ -283,3 +283,75 @@ def test_op_list_encode_and_graph(wrk, ctx):
     assert np.array_equal(t_x.numpy().reshape(x.shape), (((x * 2 + 1) * 3) * 2 + 1) * 3)
     assert ctx.launch_count() - before == 4
     assert ctx.device_status() == 0
+
+
+# ---- merged elementwise launches: bit-identical to the runs of single ops they stand for ----------------
+
+@pytest.mark.parametrize("reversed_", [False, True])
+@pytest.mark.parametrize("count", [1, 2, 6])
+def test_token_shift_multi_equals_the_single_shifts(wrk, ctx, reversed_, count):
+    rng = np.random.default_rng(31)
+    C, B, T = 256, 3, 11
+    cursors = ctx.from_numpy(oracle.pack_cursors([(0, 0, 4), (2, 4, 1), (1, 5, 6)]))
+    state = ctx.from_numpy(rng.standard_normal((B, 66, C)).astype(np.float32))
+    x = ctx.from_numpy(rng.standard_normal((T, C)).astype(np.float16))
+    mixes = [ctx.from_numpy(rng.uniform(0, 1, (C,)).astype(np.float16)) for _ in range(count)]
+    single = [ctx.tensor(wrk.F16, [C, T, 1]) for _ in range(count)]
+    multi = [ctx.tensor(wrk.F16, [C, T, 1]) for _ in range(count)]
+    for m, o in zip(mixes, single):
+        ctx.run(wrk.token_shift(cursors, m, state.view(y=(0, 1)), x, o, reversed_))
+    ctx.run(wrk.token_shift_multi(cursors, state.view(y=(0, 1)), x, mixes, multi, reversed_))
+    for a, b in zip(single, multi):
+        assert np.array_equal(a.numpy(), b.numpy())
+    with pytest.raises(wrk.WrkError):
+        wrk.token_shift_multi(cursors, state.view(y=(0, 1)), x, mixes * 7, multi * 7, reversed_)
+
+
+@pytest.mark.parametrize("C,T", [(256, 9), (4096, 5), (12288, 3)])  # one warp per row / rows kept in registers / three passes
+@pytest.mark.parametrize("with_delta", [False, True])
+def test_layer_norm_copy_equals_add_blit_layer_norm(wrk, ctx, C, T, with_delta):
+    rng = np.random.default_rng(32)
+    w = ctx.from_numpy(rng.standard_normal(C).astype(np.float16))
+    b = ctx.from_numpy(rng.standard_normal(C).astype(np.float16))
+    x0 = rng.standard_normal((T, C)).astype(np.float16)
+    d0 = rng.standard_normal((T, C)).astype(np.float16)
+    x_a, x_b, delta = ctx.from_numpy(x0), ctx.from_numpy(x0), ctx.from_numpy(d0)
+    out_a, out_b = ctx.tensor(wrk.F16, [C, T, 1]), ctx.tensor(wrk.F16, [C, T, 1])
+    if with_delta:
+        ctx.run(wrk.add(delta, x_a))
+    ctx.run(wrk.blit(x_a, out_a))
+    ctx.run(wrk.layer_norm(w, b, out_a, 1e-5))
+    ctx.run(wrk.layer_norm_copy(w, b, delta if with_delta else None, x_b, out_b, 1e-5))
+    assert np.array_equal(x_a.numpy(), x_b.numpy())
+    assert np.array_equal(out_a.numpy(), out_b.numpy())
+    if with_delta:
+        with pytest.raises(wrk.WrkError):
+            wrk.layer_norm_copy(w, b, x_b, x_b, out_b, 1e-5)
+
+
+def test_pack_v7_equals_the_eight_ops(wrk, ctx):
+    rng = np.random.default_rng(33)
+    S, H, T = 64, 6, 7
+    C = S * H
+    k0 = rng.standard_normal((T, C)).astype(np.float16)
+    v0 = rng.standard_normal((T, C)).astype(np.float16)
+    a0 = rng.uniform(0, 1, (T, C)).astype(np.float16)
+    k_k = ctx.from_numpy(rng.uniform(0.5, 1.5, C).astype(np.float16))
+    k_a = ctx.from_numpy(rng.uniform(0.5, 1.5, C).astype(np.float16))
+    # the reference's op list (src/runtime/v7.rs:888-891, 925-928)
+    k, v, a = ctx.from_numpy(k0), ctx.from_numpy(v0), ctx.from_numpy(a0)
+    kk, n = ctx.tensor(wrk.F16, [C, T, 1]), ctx.tensor(wrk.F16, [C, T, 4])
+    ctx.run(wrk.blit(k, kk))
+    ctx.run(wrk.mul(k_k, kk))
+    ctx.run(wrk.l2_norm(kk.reshape(S, H, T), 1e-12))
+    ctx.run(wrk.control_k_v7(k_a, a, k))
+    for z, t in enumerate((k, v, a, kk)):
+        ctx.run(wrk.blit(t, n.view(z=z)))
+    # one launch
+    k2, v2, a2 = ctx.from_numpy(k0), ctx.from_numpy(v0), ctx.from_numpy(a0)
+    kk2, n2 = ctx.tensor(wrk.F16, [S, H, T]), ctx.tensor(wrk.F16, [S, H, T, 4])
+    ctx.run(wrk.pack_v7(k_k, k_a, k2.reshape(S, H, T), v2.reshape(S, H, T), a2.reshape(S, H, T), kk2, n2, 1e-12))
+    assert np.array_equal(k.numpy().ravel(), k2.numpy().ravel())
+    assert np.array_equal(kk.numpy().ravel(), kk2.numpy().ravel())
+    assert np.array_equal(n.numpy().ravel(), n2.numpy().ravel())
+    assert float(np.abs(kk2.numpy()).max()) > 0

@@ -416,6 +416,28 @@ def control_k_v7(p, a, k):
     return _mk("wrk_op_control_k_v7", _t(p), pa, pk, keep=(p, ka, kk))
 
 
+def layer_norm_copy(w, b, delta, src, dst, eps):
+    """dst <- layer_norm(src), after src <- src + delta when delta is not None: blit + layer_norm (+ add) in one launch."""
+    return _mk("wrk_op_layer_norm_copy", _t(w), _t(b), _t(delta) if delta is not None else None, _t(src), _t(dst),
+               ctypes.c_float(eps), keep=(w, b, delta, src, dst))
+
+
+def token_shift_multi(cursors, state, input, time_mixes, outputs, reversed):
+    """Up to six token shifts of one f16 input in one launch."""
+    ps, ks = _v(state)
+    n = len(time_mixes)
+    mixes = (ctypes.c_void_p * n)(*[_t(t) for t in time_mixes])
+    outs = (ctypes.c_void_p * n)(*[_t(t) for t in outputs])
+    return _mk("wrk_op_token_shift_multi", _t(cursors), ps, _t(input), ctypes.c_uint32(n), mixes, outs, int(reversed),
+               keep=(cursors, ks, input, *time_mixes, *outputs))
+
+
+def pack_v7(k_k, k_a, k, v, a, kk, n, eps):
+    """kk <- l2_norm(k * k_k), k <- control_k(k_a, a, k), n <- (k, v, a, kk) on f16 [S, H, T] tensors in one launch."""
+    return _mk("wrk_op_pack_v7", _t(k_k), _t(k_a), _t(k), _t(v), _t(a), _t(kk), _t(n), ctypes.c_float(eps),
+               keep=(k_k, k_a, k, v, a, kk, n))
+
+
 def nf4_table():
     t = (ctypes.c_float * 16)()
     check(lib().wrk_nf4_table(t))

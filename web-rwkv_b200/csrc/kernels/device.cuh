@@ -29,6 +29,15 @@ __device__ __forceinline__ float activate_f(int act, float x) {
     }
 }
 
+// Roundings fixed by hand (no contraction left to the compiler), so that every kernel that evaluates one of these
+// gives the same bits: the merged elementwise kernels are compared bit for bit with the single-op kernels.
+// a (1 - f) + b f: the token shift and lerp of the reference (token_shift.wgsl, lerp.wgsl: mix(a, b, f))
+__device__ __forceinline__ float mix_f(float a, float b, float f) { return __fmaf_rn(b, f, __fmul_rn(a, __fsub_rn(1.0f, f))); }
+// k (1 + (a - 1) p): control_k_v7.wgsl
+__device__ __forceinline__ float control_k_f(float k, float a, float p) {
+    return __fmul_rn(k, __fmaf_rn(__fsub_rn(a, 1.0f), p, 1.0f));
+}
+
 struct CursorD { uint32_t batch, token, len; };
 // Packed cursor: batch | token << 8 | len << 24 (src/tensor/mod.rs:53-60); wide: three u32 per token.
 __device__ __forceinline__ CursorD cursor_at(const uint32_t* cursors, int wide, uint32_t t) {

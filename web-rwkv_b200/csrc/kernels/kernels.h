@@ -97,6 +97,8 @@ cudaError_t time_first_v7(const __half* u, int dtype, const void* r, const void*
 // ---- supporting ops (support.cu) -----------------------------------------------------------
 cudaError_t layer_norm(const __half* w, const __half* b, int dtype, void* x, uint32_t C, uint32_t rows,
                        uint32_t wrows, float eps, cudaStream_t stream);
+cudaError_t layer_norm_copy(const __half* w, const __half* b, int dtype, const void* delta, void* src, void* x, uint32_t C,
+                            uint32_t rows, uint32_t wrows, float eps, cudaStream_t stream);
 cudaError_t l2_norm(int dtype, void* x, uint32_t C, uint32_t rows, float eps, cudaStream_t stream);
 cudaError_t softmax(int dtype, void* x, uint32_t C, uint32_t rows, cudaStream_t stream);
 cudaError_t recenter(int dtype, void* x, uint32_t C, uint32_t rows, cudaStream_t stream);
@@ -109,6 +111,26 @@ cudaError_t blend(const float* factor, DView input, DView output, cudaStream_t s
 cudaError_t blend_lora(const float* factor, DView xa, DView xb, DView output, uint32_t K, cudaStream_t stream);
 cudaError_t token_shift(const uint32_t* cursors, int wide, DView time_mix, DView state, DView input, DView output,
                         int reversed, cudaStream_t stream);
+constexpr uint32_t kShiftMultiMax = 6;
+struct ShiftMultiArgs {
+    const uint32_t* cursors;
+    int wide;
+    DView state;          // f32, row 0 = the shift row
+    const __half* in;     // [C, T]
+    uint32_t C, T, count;
+    const __half* mix[kShiftMultiMax];  // [C] each
+    __half* out[kShiftMultiMax];        // [C, T] each
+    int reversed;
+};
+cudaError_t token_shift_multi(const ShiftMultiArgs& a, cudaStream_t stream);
+struct PackV7Args {
+    const __half *k_k, *k_a;  // [H * S]
+    __half *k, *kk, *n;       // [S, H, T] (k updated in place), [S, H, T], [S, H, T, 4]
+    const __half *v, *a;      // [S, H, T]
+    uint32_t S, H, rows;      // rows = H * T
+    float eps;
+};
+cudaError_t pack_v7(const PackV7Args& p, cudaStream_t stream);
 cudaError_t shift_carry(const uint32_t* cursors, int wide, DView state, int dtype, const void* x, uint32_t C, uint32_t T,
                         cudaStream_t stream);
 cudaError_t channel_mix(const uint32_t* cursors, int wide, DView state, int dtype, const void* r, const void* v,

@@ -35,8 +35,9 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // Rows of up to kLnRegs * blockDim values are read once and kept in registers (one round of loads in flight instead
 // of three dependent passes over global memory); longer rows take the three passes.
 constexpr int kLnRegs = 32;
-__global__ void layer_norm_kernel(const __half* w, const __half* b, int dtype, void* x, uint32_t C, uint32_t rows,
-                                  uint32_t wrows, float eps) {
+// With `delta`, src <- src + delta first (rounded to the data type, as the separate add stores it).
+__global__ void layer_norm_kernel(const __half* w, const __half* b, int dtype, const void* delta, void* src, void* x, uint32_t C,
+                                  uint32_t rows, uint32_t wrows, float eps) {
     __shared__ float scratch[32];
     const bool cached = C <= (uint32_t)kLnRegs * blockDim.x;
     for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -48,7 +49,12 @@ __global__ void layer_norm_kernel(const __half* w, const __half* b, int dtype, v
 #pragma unroll
             for (int i = 0; i < kLnRegs; ++i) {
                 const uint32_t c = threadIdx.x + (uint32_t)i * blockDim.x;
-                v[i] = c < C ? dload(x, dtype, base + c) : 0.f;
+                v[i] = c < C ? dload(src, dtype, base + c) : 0.f;
+                if (delta && c < C) {
+                    v[i] = dtype == WRK_F16 ? __half2float(__float2half_rn(dload(delta, dtype, base + c) + v[i]))
+                                            : dload(delta, dtype, base + c) + v[i];
+                    dstore(src, dtype, base + c, v[i]);
+                }
                 s += v[i];
             }
             const float mean = block_sum(s, scratch) / (float)C;
@@ -67,18 +73,21 @@ __global__ void layer_norm_kernel(const __half* w, const __half* b, int dtype, v
             }
             continue;
         }
+        if (delta)  // each thread reads back only what it wrote
+            for (uint32_t c = threadIdx.x; c < C; c += blockDim.x)
+                dstore(src, dtype, base + c, dload(delta, dtype, base + c) + dload(src, dtype, base + c));
         float s = 0.f;
-        for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) s += dload(x, dtype, base + c);
+        for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) s += dload(src, dtype, base + c);
         const float mean = block_sum(s, scratch) / (float)C;
         float m2 = 0.f;
         for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) {
-            const float d = dload(x, dtype, base + c) - mean;
+            const float d = dload(src, dtype, base + c) - mean;
             m2 += d * d;
         }
         const float var = block_sum(m2, scratch) / (float)C + eps;
         const float dev = rsqrtf(var);
         for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) {
-            const float v = (dload(x, dtype, base + c) - mean) * dev;
+            const float v = (dload(src, dtype, base + c) - mean) * dev;
             dstore(x, dtype, base + c, fmaf(v, __half2float(w[wb + c]), __half2float(b[wb + c])));
         }
     }
@@ -92,7 +101,7 @@ __global__ void l2_norm_kernel(int dtype, void* x, uint32_t C, uint32_t rows, fl
         float s = 0.f;
         for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) {
             const float v = dload(x, dtype, base + c);
-            s += v * v;
+            s = __fmaf_rn(v, v, s);
         }
         const float norm = rsqrtf(block_sum(s, scratch) + eps);
         for (uint32_t c = threadIdx.x; c < C; c += blockDim.x)
@@ -223,7 +232,59 @@ __global__ void token_shift_kernel(const uint32_t* cursors, int wide, DView tm, 
         const float prev = (t == cu.token) ? static_cast<const float*>(state.base)[state.index(c, 0, cu.batch)]
                                            : dload(in.base, in.dtype, in.index(c, t - 1, 0));
         const float a = reversed ? cur : prev, b = reversed ? prev : cur;
-        dstore(out.base, out.dtype, out.index(c, t, z), a * (1.0f - f) + b * f);
+        dstore(out.base, out.dtype, out.index(c, t, z), mix_f(a, b, f));
+    }
+}
+
+// Several token shifts of one input in one launch: out_i[c, t] = mix(x_t, prev, f_i[c]) as token_shift_kernel computes it,
+// with the input and the previous row read once.
+__global__ void token_shift_multi_kernel(const ShiftMultiArgs a) {
+    const size_t total = (size_t)a.C * a.T;
+    for (size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t c = o % a.C, t = o / a.C;
+        const CursorD cu = cursor_at(a.cursors, a.wide, t);
+        const float cur = __half2float(a.in[o]);
+        const float prev = (t == cu.token) ? static_cast<const float*>(a.state.base)[a.state.index(c, 0, cu.batch)]
+                                           : __half2float(a.in[o - a.C]);
+        const float x = a.reversed ? cur : prev, y = a.reversed ? prev : cur;
+#pragma unroll
+        for (uint32_t i = 0; i < kShiftMultiMax; ++i) {
+            if (i >= a.count) break;
+            const float f = __half2float(a.mix[i][c]);
+            a.out[i][o] = __float2half_rn(mix_f(x, y, f));
+        }
+    }
+}
+
+// The v7 time-mix operand in one launch, one warp per head and token (a row of S channels of [S, H, T]):
+//   kk <- l2_norm(k * k_k)  (blit + mul + l2_norm, each rounding to f16 where the separate ops store f16),
+//   k  <- k * (1 + (a - 1) * k_a)  (control_k_kernel),  n[.., 0..3] <- k, v, a, kk  (four blits).
+// Sums run in l2_norm_kernel's order for a block of 32 threads, so the results are bit-identical to the separate ops.
+__global__ void pack_v7_kernel(const PackV7Args p) {
+    const uint32_t lane = threadIdx.x;
+    const size_t plane = (size_t)p.rows * p.S;
+    for (uint32_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+        const size_t base = (size_t)row * p.S;
+        const uint32_t c0 = (row % p.H) * p.S;
+        float s = 0.f;
+        for (uint32_t c = lane; c < p.S; c += 32) {
+            const float v = __half2float(__float2half_rn(__half2float(p.k_k[c0 + c]) * __half2float(p.k[base + c])));
+            s = __fmaf_rn(v, v, s);
+        }
+        const float norm = rsqrtf(warp_sum(s) + p.eps);
+        for (uint32_t c = lane; c < p.S; c += 32) {
+            const size_t i = base + c;
+            const float kv = __half2float(p.k[i]), av = __half2float(p.a[i]);
+            const float v = __half2float(__float2half_rn(__half2float(p.k_k[c0 + c]) * kv));
+            const __half kk = __float2half_rn(v * norm);
+            const __half kn = __float2half_rn(control_k_f(kv, av, __half2float(p.k_a[c0 + c])));
+            p.kk[i] = kk;
+            p.k[i] = kn;
+            p.n[i] = kn;
+            p.n[plane + i] = p.v[i];
+            p.n[2 * plane + i] = p.a[i];
+            p.n[3 * plane + i] = kk;
+        }
     }
 }
 
@@ -298,7 +359,7 @@ __global__ void lerp_kernel(DView in, DView out, DView f, int reversed) {
         const size_t oi = out.index(c, t, b);
         const float yo = dload(out.base, out.dtype, oi);
         const float a = reversed ? yo : xi, bb = reversed ? xi : yo;
-        dstore(out.base, out.dtype, oi, a * (1.0f - ff) + bb * ff);
+        dstore(out.base, out.dtype, oi, mix_f(a, bb, ff));
     }
 }
 
@@ -315,7 +376,7 @@ __global__ void control_k_kernel(const __half* p, DView a, DView k) {
         const float pp = __half2float(p[c]);
         const float av = dload(a.base, a.dtype, a.index(c, t, b));
         const size_t ki = k.index(c, t, b);
-        dstore(k.base, k.dtype, ki, dload(k.base, k.dtype, ki) * (1.0f + (av - 1.0f) * pp));
+        dstore(k.base, k.dtype, ki, control_k_f(dload(k.base, k.dtype, ki), av, pp));
     }
 }
 
@@ -323,10 +384,16 @@ __global__ void control_k_kernel(const __half* p, DView a, DView k) {
 
 cudaError_t layer_norm(const __half* w, const __half* b, int dtype, void* x, uint32_t C, uint32_t rows, uint32_t wrows,
                        float eps, cudaStream_t stream) {
+    return layer_norm_copy(w, b, dtype, nullptr, x, x, C, rows, wrows, eps, stream);
+}
+
+// src <- src + delta when `delta` is given; x <- layer norm of `src` (the same dtype and shape; src == x: in place)
+cudaError_t layer_norm_copy(const __half* w, const __half* b, int dtype, const void* delta, void* src, void* x, uint32_t C,
+                            uint32_t rows, uint32_t wrows, float eps, cudaStream_t stream) {
     if (rows == 0 || C == 0) return cudaSuccess;
     const int block = C <= 256 ? 32 : 256;
     const uint32_t grid = rows < 148u * 32u ? rows : 148u * 32u;
-    layer_norm_kernel<<<grid, block, 0, stream>>>(w, b, dtype, x, C, rows, wrows, eps);
+    layer_norm_kernel<<<grid, block, 0, stream>>>(w, b, dtype, delta, src, x, C, rows, wrows, eps);
     return cudaGetLastError();
 }
 
@@ -397,6 +464,20 @@ cudaError_t token_shift(const uint32_t* cursors, int wide, DView time_mix, DView
     const size_t total = (size_t)output.shape[0] * output.shape[1] * output.shape[2];
     if (total == 0) return cudaSuccess;
     token_shift_kernel<<<ew_grid(total), kEw, 0, stream>>>(cursors, wide, time_mix, state, input, output, reversed);
+    return cudaGetLastError();
+}
+
+cudaError_t token_shift_multi(const ShiftMultiArgs& a, cudaStream_t stream) {
+    const size_t total = (size_t)a.C * a.T;
+    if (total == 0 || a.count == 0) return cudaSuccess;
+    token_shift_multi_kernel<<<ew_grid(total), kEw, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t pack_v7(const PackV7Args& p, cudaStream_t stream) {
+    if (p.rows == 0 || p.S == 0) return cudaSuccess;
+    const uint32_t grid = p.rows < 148u * 32u ? p.rows : 148u * 32u;
+    pack_v7_kernel<<<grid, 32, 0, stream>>>(p);
     return cudaGetLastError();
 }
 

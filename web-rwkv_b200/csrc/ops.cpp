@@ -492,6 +492,106 @@ int32_t wrk_op_layer_norm(wrk_tensor* w, wrk_tensor* b, wrk_tensor* x, float eps
     return norm_common("layer_norm", false, w, b, x, eps, out);
 }
 
+int32_t wrk_op_layer_norm_copy(wrk_tensor* w, wrk_tensor* b, wrk_tensor* delta, wrk_tensor* src, wrk_tensor* dst, float eps,
+                               wrk_op** out) {
+    REQ_NN(w, b, src, dst, out);
+    REQ_FLOAT(dst, "dst");
+    REQ_DTYPE(src, dst->dtype, "src");
+    REQ_DTYPE(w, WRK_F16, "w");
+    REQ_DTYPE(b, WRK_F16, "b");
+    const Shape4 sh = dst->shape;
+    WRK_TRY(check_shape("dst", sh, sh[0], sh[1], sh[2], 1));
+    WRK_TRY(check_shape("src", src->shape, sh[0], sh[1], sh[2], 1));
+    WRK_TRY(check_shape("w", w->shape, sh[0], 1, 1, 1));
+    WRK_TRY(check_shape("b", b->shape, sh[0], 1, 1, 1));
+    if (delta) {
+        REQ_DTYPE(delta, dst->dtype, "delta");
+        WRK_TRY(check_shape("delta", delta->shape, sh[0], sh[1], sh[2], 1));
+        WRK_REQUIRE(delta->ptr() != src->ptr() && src->ptr() != dst->ptr(), WRK_ERR_INVALID_ARGUMENT,
+                    "delta, src and dst must be three tensors");
+    }
+    const __half* wp = static_cast<const __half*>(w->ptr());
+    const __half* bp = static_cast<const __half*>(b->ptr());
+    const void* ap = delta ? delta->ptr() : nullptr;
+    void* sp = src->ptr();
+    void* dp = dst->ptr();
+    const int dt = dst->dtype;
+    const uint32_t C = sh[0], rows = sh[1] * sh[2];
+    *out = new_atom("layer_norm_copy", [=](cudaStream_t s) { return k::layer_norm_copy(wp, bp, dt, ap, sp, dp, C, rows, 1, eps, s); },
+                    {w, b, src, dst});
+    if (delta) (*out)->keep.push_back(delta->buf);
+    return WRK_OK;
+}
+
+int32_t wrk_op_token_shift_multi(wrk_tensor* cursors, const wrk_view* state, wrk_tensor* input, uint32_t count,
+                                 wrk_tensor* const* time_mix, wrk_tensor* const* outputs, int32_t reversed, wrk_op** out) {
+    REQ_NN(cursors, state, state->tensor, input, time_mix, outputs, out);
+    WRK_REQUIRE(count >= 1 && count <= k::kShiftMultiMax, WRK_ERR_INVALID_ARGUMENT, "%u shifts: 1 to %u", count, k::kShiftMultiMax);
+    REQ_DTYPE(input, WRK_F16, "input");
+    REQ_DTYPE(state->tensor, WRK_F32, "state");
+    const Shape4 sh = input->shape;
+    const uint32_t C = sh[0], T = sh[1];
+    WRK_TRY(check_shape("input", sh, C, T, 1, 1));
+    WRK_TRY(check_view("state", state, C, state->shape[1], state->shape[2], 1));
+    WRK_TRY(check_cursors(cursors, T));
+    k::ShiftMultiArgs a{};
+    a.cursors = static_cast<const uint32_t*>(cursors->ptr());
+    a.wide = cursors_wide(cursors, T);
+    a.state = make_dview(*state);
+    a.in = static_cast<const __half*>(input->ptr());
+    a.C = C;
+    a.T = T;
+    a.count = count;
+    a.reversed = reversed;
+    wrk_op* op = new_atom("token_shift_multi", nullptr, {cursors, state->tensor, input});
+    for (uint32_t i = 0; i < count; ++i) {
+        const int32_t s1 = time_mix[i] && outputs[i] ? WRK_OK : set_error(WRK_ERR_INVALID_ARGUMENT, "null argument");
+        int32_t s2 = s1;
+        if (s2 == WRK_OK && (time_mix[i]->dtype != WRK_F16 || outputs[i]->dtype != WRK_F16)) s2 = set_error(WRK_ERR_TYPE, "data type mismatch: f16 mixes and outputs");
+        if (s2 == WRK_OK) s2 = check_shape("time_mix", time_mix[i]->shape, C, 1, 1, 1);
+        if (s2 == WRK_OK) s2 = check_shape("output", outputs[i]->shape, C, T, 1, 1);
+        if (s2 != WRK_OK) {
+            wrk_op_release(op);
+            return s2;
+        }
+        a.mix[i] = static_cast<const __half*>(time_mix[i]->ptr());
+        a.out[i] = static_cast<__half*>(outputs[i]->ptr());
+        op->keep.push_back(time_mix[i]->buf);
+        op->keep.push_back(outputs[i]->buf);
+    }
+    op->launch = [a](cudaStream_t s) { return k::token_shift_multi(a, s); };
+    *out = op;
+    return WRK_OK;
+}
+
+int32_t wrk_op_pack_v7(wrk_tensor* k_k, wrk_tensor* k_a, wrk_tensor* k, wrk_tensor* v, wrk_tensor* a, wrk_tensor* kk, wrk_tensor* n,
+                       float eps, wrk_op** out) {
+    REQ_NN(k_k, k_a, k, v, a, kk, n, out);
+    const Shape4 sh = k->shape;  // [S, H, T]
+    const uint32_t S = sh[0], H = sh[1], T = sh[2];
+    for (wrk_tensor* t : {k_k, k_a, k, v, a, kk, n}) REQ_DTYPE(t, WRK_F16, "tensor");
+    WRK_TRY(check_shape("k", sh, S, H, T, 1));
+    WRK_TRY(check_shape("v", v->shape, S, H, T, 1));
+    WRK_TRY(check_shape("a", a->shape, S, H, T, 1));
+    WRK_TRY(check_shape("kk", kk->shape, S, H, T, 1));
+    WRK_TRY(check_shape("n", n->shape, S, H, T, 4));
+    WRK_REQUIRE(k_k->len() == (size_t)S * H && k_a->len() == (size_t)S * H, WRK_ERR_SHAPE, "k_k and k_a hold %u values", S * H);
+    k::PackV7Args p{};
+    p.k_k = static_cast<const __half*>(k_k->ptr());
+    p.k_a = static_cast<const __half*>(k_a->ptr());
+    p.k = static_cast<__half*>(k->ptr());
+    p.kk = static_cast<__half*>(kk->ptr());
+    p.n = static_cast<__half*>(n->ptr());
+    p.v = static_cast<const __half*>(v->ptr());
+    p.a = static_cast<const __half*>(a->ptr());
+    p.S = S;
+    p.H = H;
+    p.rows = H * T;
+    p.eps = eps;
+    *out = new_atom("pack_v7", [p](cudaStream_t s) { return k::pack_v7(p, s); }, {k_k, k_a, k, v, a, kk, n});
+    return WRK_OK;
+}
+
 int32_t wrk_op_group_norm(wrk_tensor* w, wrk_tensor* b, wrk_tensor* x, float eps, wrk_op** out) {
     return norm_common("group_norm", true, w, b, x, eps, out);
 }

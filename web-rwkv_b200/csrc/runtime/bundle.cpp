@@ -419,9 +419,16 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
     WRK_TRY(reshape(B["att_v"], S, WRK_DIM_AUTO, T, 1, &att_v));
     WRK_TRY(reshape(B["att_r"], S, WRK_DIM_AUTO, T, 1, &att_r));
 
-    WRK_TRY(blit(ops, V(B["x"]), V(B["att_x"])));
-    HOOK(PRE_ATT);
-    ADD(wrk_op_layer_norm(L.att_ln.w, L.att_ln.b, B["att_x"], LN_EPS, &_o));
+    // Runs of elementwise ops as one launch each (bit-identical results) unless the op list is to be the reference's,
+    // op for op: with hooks, which sit between those ops, or in strict mode.
+    const bool merged = bd->fused && bd->hooks.empty();
+    if (merged) {
+        ADD(wrk_op_layer_norm_copy(L.att_ln.w, L.att_ln.b, nullptr, B["x"], B["att_x"], LN_EPS, &_o));
+    } else {
+        WRK_TRY(blit(ops, V(B["x"]), V(B["att_x"])));
+        HOOK(PRE_ATT);
+        ADD(wrk_op_layer_norm(L.att_ln.w, L.att_ln.b, B["att_x"], LN_EPS, &_o));
+    }
     HOOK(POST_ATT_LAYER_NORM);
     HOOK(PRE_ATT_TOKEN_SHIFT);
     if (v6) {
@@ -460,6 +467,15 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
             ADD(wrk_op_activate(&td, WRK_ACT_STABLE_EXP, &_o));
         }
         HOOK(POST_ATT_TIME_DECAY_ACTIVATE);
+    } else if (merged) {
+        const wrk_view sa = state_att(bd, index, S);
+        wrk_tensor* const mixes[4] = {L.time_mix_k, L.time_mix_v, L.time_mix_r, L.time_mix_g};
+        wrk_tensor* const outs[4] = {B["att_kx"], B["att_vx"], B["att_rx"], B["att_gx"]};
+        ADD(wrk_op_token_shift_multi(cursors, &sa, B["att_x"], 4, mixes, outs, false, &_o));
+        WRK_TRY(matmul(ops, L.att_w_k, V(B["att_kx"]), V(B["att_k"]), WRK_ACT_NONE, turbo));
+        WRK_TRY(matmul(ops, L.att_w_v, V(B["att_vx"]), V(B["att_v"]), WRK_ACT_NONE, turbo));
+        WRK_TRY(matmul(ops, L.att_w_r, V(B["att_rx"]), V(B["att_r"]), WRK_ACT_NONE, turbo));
+        WRK_TRY(matmul(ops, L.att_w_g, V(B["att_gx"]), V(B["att_g"]), WRK_ACT_NONE, turbo));
     } else {
         WRK_TRY(token_shift(ops, cursors, V(L.time_mix_k), state_att(bd, index, S), B["att_x"], B["att_kx"], false));
         WRK_TRY(token_shift(ops, cursors, V(L.time_mix_v), state_att(bd, index, S), B["att_x"], B["att_vx"], false));
@@ -496,16 +512,23 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
         WRK_TRY(carry_all_channels(bd, ops, B, index, S));
     }
     HOOK(POST_ATT_OUT);
-    WRK_TRY(add(ops, V(B["att_o"]), V(B["x"])));
-    HOOK(POST_ATT);
-
-    WRK_TRY(blit(ops, V(B["x"]), V(B["ffn_x"])));
-    HOOK(PRE_FFN);
-    ADD(wrk_op_layer_norm(L.ffn_ln.w, L.ffn_ln.b, B["ffn_x"], LN_EPS, &_o));
-    HOOK(POST_FFN_LAYER_NORM);
-    HOOK(PRE_FFN_TOKEN_SHIFT);
-    WRK_TRY(token_shift(ops, cursors, V(L.ffn_time_mix_k), state_ffn(bd, index, S), B["ffn_x"], B["ffn_kx"], v6));
-    WRK_TRY(token_shift(ops, cursors, V(L.ffn_time_mix_r), state_ffn(bd, index, S), B["ffn_x"], B["ffn_rx"], v6));
+    if (merged) {
+        ADD(wrk_op_layer_norm_copy(L.ffn_ln.w, L.ffn_ln.b, B["att_o"], B["x"], B["ffn_x"], LN_EPS, &_o));
+        const wrk_view sf = state_ffn(bd, index, S);
+        wrk_tensor* const mixes[2] = {L.ffn_time_mix_k, L.ffn_time_mix_r};
+        wrk_tensor* const outs[2] = {B["ffn_kx"], B["ffn_rx"]};
+        ADD(wrk_op_token_shift_multi(cursors, &sf, B["ffn_x"], 2, mixes, outs, v6, &_o));
+    } else {
+        WRK_TRY(add(ops, V(B["att_o"]), V(B["x"])));
+        HOOK(POST_ATT);
+        WRK_TRY(blit(ops, V(B["x"]), V(B["ffn_x"])));
+        HOOK(PRE_FFN);
+        ADD(wrk_op_layer_norm(L.ffn_ln.w, L.ffn_ln.b, B["ffn_x"], LN_EPS, &_o));
+        HOOK(POST_FFN_LAYER_NORM);
+        HOOK(PRE_FFN_TOKEN_SHIFT);
+        WRK_TRY(token_shift(ops, cursors, V(L.ffn_time_mix_k), state_ffn(bd, index, S), B["ffn_x"], B["ffn_kx"], v6));
+        WRK_TRY(token_shift(ops, cursors, V(L.ffn_time_mix_r), state_ffn(bd, index, S), B["ffn_x"], B["ffn_rx"], v6));
+    }
     HOOK(POST_FFN_TOKEN_SHIFT);
     HOOK(PRE_FFN_LINEAR);
     WRK_TRY(matmul(ops, L.ffn_w_k, V(B["ffn_kx"]), V(B["ffn_k"]), WRK_ACT_SQUARED_RELU, turbo));
@@ -543,18 +566,28 @@ int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, 
     WRK_TRY(reshape(B["att_w"], S, WRK_DIM_AUTO, T, 1, &att_w));
     WRK_TRY(reshape(B["att_n"], S, WRK_DIM_AUTO, T, 4, &att_n));
 
-    WRK_TRY(blit(ops, V(B["x"]), V(B["att_x"])));
-    HOOK(PRE_ATT);
-    ADD(wrk_op_layer_norm(L.att_ln.w, L.att_ln.b, B["att_x"], LN_EPS, &_o));
-    HOOK(POST_ATT_LAYER_NORM);
-    HOOK(PRE_ATT_TOKEN_SHIFT);
+    // Runs of elementwise ops as one launch each (bit-identical results) unless the op list is to be the reference's,
+    // op for op: with hooks, which sit between those ops, or in strict mode.
+    const bool merged = bd->fused && bd->hooks.empty();
     const wrk_view sa = state_att(bd, index, S);
-    WRK_TRY(token_shift(ops, cursors, V(L.x_r), sa, B["att_x"], B["att_rx"], true));
-    WRK_TRY(token_shift(ops, cursors, V(L.x_w), sa, B["att_x"], B["att_wx"], true));
-    WRK_TRY(token_shift(ops, cursors, V(L.x_k), sa, B["att_x"], B["att_kx"], true));
-    WRK_TRY(token_shift(ops, cursors, V(L.x_v), sa, B["att_x"], B["att_vx"], true));
-    WRK_TRY(token_shift(ops, cursors, V(L.x_a), sa, B["att_x"], B["att_ax"], true));
-    WRK_TRY(token_shift(ops, cursors, V(L.x_g), sa, B["att_x"], B["att_gx"], true));
+    if (merged) {
+        ADD(wrk_op_layer_norm_copy(L.att_ln.w, L.att_ln.b, nullptr, B["x"], B["att_x"], LN_EPS, &_o));
+        wrk_tensor* const mixes[6] = {L.x_r, L.x_w, L.x_k, L.x_v, L.x_a, L.x_g};
+        wrk_tensor* const outs[6] = {B["att_rx"], B["att_wx"], B["att_kx"], B["att_vx"], B["att_ax"], B["att_gx"]};
+        ADD(wrk_op_token_shift_multi(cursors, &sa, B["att_x"], 6, mixes, outs, true, &_o));
+    } else {
+        WRK_TRY(blit(ops, V(B["x"]), V(B["att_x"])));
+        HOOK(PRE_ATT);
+        ADD(wrk_op_layer_norm(L.att_ln.w, L.att_ln.b, B["att_x"], LN_EPS, &_o));
+        HOOK(POST_ATT_LAYER_NORM);
+        HOOK(PRE_ATT_TOKEN_SHIFT);
+        WRK_TRY(token_shift(ops, cursors, V(L.x_r), sa, B["att_x"], B["att_rx"], true));
+        WRK_TRY(token_shift(ops, cursors, V(L.x_w), sa, B["att_x"], B["att_wx"], true));
+        WRK_TRY(token_shift(ops, cursors, V(L.x_k), sa, B["att_x"], B["att_kx"], true));
+        WRK_TRY(token_shift(ops, cursors, V(L.x_v), sa, B["att_x"], B["att_vx"], true));
+        WRK_TRY(token_shift(ops, cursors, V(L.x_a), sa, B["att_x"], B["att_ax"], true));
+        WRK_TRY(token_shift(ops, cursors, V(L.x_g), sa, B["att_x"], B["att_gx"], true));
+    }
     HOOK(POST_ATT_TOKEN_SHIFT);
     HOOK(PRE_ATT_LINEAR);
     WRK_TRY(matmul(ops, L.att_w_r, V(B["att_rx"]), V(B["att_r"]), WRK_ACT_NONE, turbo));
@@ -572,15 +605,17 @@ int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, 
     WRK_TRY(matmul(ops, L.g2, V(B["aux_g"]), V(B["att_g"]), WRK_ACT_NONE, turbo));
     HOOK(POST_ATT_ADAPT);
     HOOK(PRE_ATT_CONTROL);
-    WRK_TRY(blit(ops, V(B["att_k"]), V(B["att_kk"])));
-    {
-        const wrk_view kk = V(L.k_k), o = V(B["att_kk"]);
-        ADD(wrk_op_mul_activate(&kk, &o, WRK_ACT_NONE, WRK_ACT_NONE, WRK_ACT_NONE, &_o));
-    }
-    ADD(wrk_op_l2_norm(att_kk, L2_EPS, &_o));
-    {
-        const wrk_view a = V(B["att_a"]), k = V(B["att_k"]);
-        ADD(wrk_op_control_k_v7(L.k_a, &a, &k, &_o));
+    if (!merged) {
+        WRK_TRY(blit(ops, V(B["att_k"]), V(B["att_kk"])));
+        {
+            const wrk_view kk = V(L.k_k), o = V(B["att_kk"]);
+            ADD(wrk_op_mul_activate(&kk, &o, WRK_ACT_NONE, WRK_ACT_NONE, WRK_ACT_NONE, &_o));
+        }
+        ADD(wrk_op_l2_norm(att_kk, L2_EPS, &_o));
+        {
+            const wrk_view a = V(B["att_a"]), k = V(B["att_k"]);
+            ADD(wrk_op_control_k_v7(L.k_a, &a, &k, &_o));
+        }
     }
     HOOK(POST_ATT_CONTROL);
     HOOK(PRE_ATT_VALUE_RESIDUAL);
@@ -595,10 +630,18 @@ int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, 
     }
     HOOK(POST_ATT_VALUE_RESIDUAL);
     HOOK(PRE_ATT_TIME_MIX);
-    WRK_TRY(blit(ops, V(B["att_k"]), Vz(B["att_n"], 0)));
-    WRK_TRY(blit(ops, V(B["att_v"]), Vz(B["att_n"], 1)));
-    WRK_TRY(blit(ops, V(B["att_a"]), Vz(B["att_n"], 2)));
-    WRK_TRY(blit(ops, V(B["att_kk"]), Vz(B["att_n"], 3)));
+    if (merged) {  // kk, the controlled k and the four planes of the time-mix operand (k and kk do not depend on v)
+        TensorH k3, v3, a3;
+        WRK_TRY(reshape(B["att_k"], S, WRK_DIM_AUTO, T, 1, &k3));
+        WRK_TRY(reshape(B["att_v"], S, WRK_DIM_AUTO, T, 1, &v3));
+        WRK_TRY(reshape(B["att_a"], S, WRK_DIM_AUTO, T, 1, &a3));
+        ADD(wrk_op_pack_v7(L.k_k, L.k_a, k3, v3, a3, att_kk, att_n, L2_EPS, &_o));
+    } else {
+        WRK_TRY(blit(ops, V(B["att_k"]), Vz(B["att_n"], 0)));
+        WRK_TRY(blit(ops, V(B["att_v"]), Vz(B["att_n"], 1)));
+        WRK_TRY(blit(ops, V(B["att_a"]), Vz(B["att_n"], 2)));
+        WRK_TRY(blit(ops, V(B["att_kk"]), Vz(B["att_n"], 3)));
+    }
     if (sp.on) WRK_TRY(blit(ops, Vx(B["att_x"], sp.c0, sp.c0 + sp.Cl), V(att_loc)));
     {
         const wrk_view st = state_wkv(bd, index, S, sp);
@@ -620,12 +663,15 @@ int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, 
         WRK_TRY(carry_all_channels(bd, ops, B, index, S));
     }
     HOOK(POST_ATT_OUT);
-    WRK_TRY(add(ops, V(B["att_o"]), V(B["x"])));
-    HOOK(POST_ATT);
-
-    WRK_TRY(blit(ops, V(B["x"]), V(B["ffn_x"])));
-    HOOK(PRE_FFN);
-    ADD(wrk_op_layer_norm(L.ffn_ln.w, L.ffn_ln.b, B["ffn_x"], LN_EPS, &_o));
+    if (merged) {
+        ADD(wrk_op_layer_norm_copy(L.ffn_ln.w, L.ffn_ln.b, B["att_o"], B["x"], B["ffn_x"], LN_EPS, &_o));
+    } else {
+        WRK_TRY(add(ops, V(B["att_o"]), V(B["x"])));
+        HOOK(POST_ATT);
+        WRK_TRY(blit(ops, V(B["x"]), V(B["ffn_x"])));
+        HOOK(PRE_FFN);
+        ADD(wrk_op_layer_norm(L.ffn_ln.w, L.ffn_ln.b, B["ffn_x"], LN_EPS, &_o));
+    }
     HOOK(POST_FFN_LAYER_NORM);
     HOOK(PRE_FFN_TOKEN_SHIFT);
     WRK_TRY(token_shift(ops, cursors, V(L.ffn_x_k), state_ffn(bd, index, S), B["ffn_x"], B["ffn_kx"], true));
