@@ -45,13 +45,19 @@ __device__ __forceinline__ bool find_run(const uint32_t* cursors, int wide, uint
     return count != 0;
 }
 
-// One CTA of Q * S threads per (head, batch slot): thread (q, j) keeps rows [q S/Q, (q+1) S/Q) of state
-// column j in registers for the sequence's whole run of tokens and adds its part of output j; the Q parts
-// meet in shared memory (one barrier per token, buffers alternate).
+// One CTA of 4 * S threads per (head, batch slot): thread (q, j) keeps rows [q S/4, (q+1) S/4) of state column j in
+// registers for the sequence's whole run of tokens and adds its part of output j; the four parts meet in shared
+// memory (one barrier per token, buffers alternate).  The tokens' k, r, w and v rows reach shared memory a chunk of
+// 1024 / S tokens at a time: thread group q loads one of the four tensors, a chunk ahead, into registers while the
+// current chunk is computed, so a token's step never waits for global memory.
 template <int S, int Q>
 __global__ void __launch_bounds__(S * Q) time_mix_v56_kernel(const WkvArgs a) {
-    constexpr int SI = S / Q;
-    __shared__ float sk[2][S], sr[2][S], sw[2][S], su[S], part[2][Q][S];
+    static_assert(Q == 4, "one loader group per staged tensor");
+    constexpr int SI = S / Q, TC = 1024 / S;
+    enum { IN_K = 0, IN_R = 1, IN_W = 2, IN_V = 3 };
+    __shared__ __align__(16) float sin[2][4][TC][S];
+    __shared__ __align__(16) float su[S];
+    __shared__ float part[2][Q][S];
     __shared__ uint32_t s_start, s_count;
     const uint32_t h = blockIdx.x, slot = blockIdx.y, j = threadIdx.x % S, q = threadIdx.x / S;
     const uint32_t C = a.S * a.H, c = h * S + j;
@@ -62,66 +68,91 @@ __global__ void __launch_bounds__(S * Q) time_mix_v56_kernel(const WkvArgs a) {
     float st[SI];
 #pragma unroll
     for (int i = 0; i < SI; ++i) st[i] = static_cast<const float*>(a.state.base)[a.state.index(c, 1 + q * SI + i, slot)];
-    if (q == 0) {
-        su[j] = a.time_first[c];
-        if (!a.per_token_decay) sw[0][j] = sw[1][j] = a.time_decay[c];
-        const size_t ti = (size_t)start * C + c;
-        sk[0][j] = dload(a.k, a.dtype, ti);
-        sr[0][j] = dload(a.r, a.dtype, ti);
-        if (a.per_token_decay) sw[0][j] = a.time_decay[ti];
-    }
+    if (q == 0) su[j] = a.time_first[c];
+
+    // group q's tensor: element (token, channel j) of chunk `chunk` (zero past the run's end)
+    float stage[TC];
+    auto load_chunk = [&](uint32_t chunk) {
+#pragma unroll
+        for (int n = 0; n < TC; ++n) {
+            const uint32_t m = chunk * TC + n;
+            const size_t ti = (size_t)(start + m) * C + c;
+            float v = 0.f;
+            if (m < count) {
+                if (q == IN_K) v = dload(a.k, a.dtype, ti);
+                else if (q == IN_R) v = dload(a.r, a.dtype, ti);
+                else if (q == IN_W) v = a.per_token_decay ? a.time_decay[ti] : a.time_decay[c];
+                else v = dload(a.v, a.dtype, ti);
+            }
+            stage[n] = v;
+        }
+    };
+    auto store_chunk = [&](int buf) {
+#pragma unroll
+        for (int n = 0; n < TC; ++n) sin[buf][q][n][j] = stage[n];
+    };
+    const uint32_t chunks = (count + TC - 1) / TC;
+    load_chunk(0);
+    store_chunk(0);
     __syncthreads();
 
-    for (uint32_t n = 0; n < count; ++n) {
-        const uint32_t t = start + n;
-        const int cur = n & 1, nxt = cur ^ 1;
-        const size_t ti = (size_t)t * C + c;
-        // next token's shared vectors: issue the loads before this token's math
-        float nk = 0.f, nr = 0.f, nw = 0.f, xin = 0.f;
-        const bool more = n + 1 < count;
-        if (q == 0) {
-            if (more) {
-                nk = dload(a.k, a.dtype, ti + C);
-                nr = dload(a.r, a.dtype, ti + C);
-                if (a.per_token_decay) nw = a.time_decay[ti + C];
+    for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
+        const int buf = chunk & 1;
+        const bool more = chunk + 1 < chunks;
+        if (more) load_chunk(chunk + 1);  // in flight while this chunk's tokens are computed
+        const uint32_t len = min((uint32_t)TC, count - chunk * TC);
+        for (uint32_t n = 0; n < len; ++n) {
+            const uint32_t t = start + chunk * TC + n;
+            const int cur = n & 1;  // TC is even: the parity runs on across chunks
+            const size_t ti = (size_t)t * C + c;
+            CursorD cu{};
+            if (q == 0) cu = cursor_at(a.cursors, a.wide, t);
+            const float vj = sin[buf][IN_V][n][j];
+            const float4* k4 = reinterpret_cast<const float4*>(&sin[buf][IN_K][n][q * SI]);
+            const float4* r4 = reinterpret_cast<const float4*>(&sin[buf][IN_R][n][q * SI]);
+            const float4* w4 = reinterpret_cast<const float4*>(&sin[buf][IN_W][n][q * SI]);
+            const float4* u4 = reinterpret_cast<const float4*>(&su[q * SI]);
+            float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+            for (int ii = 0; ii < SI; ii += 4) {
+                const float4 kq = k4[ii / 4], rq = r4[ii / 4], wq = w4[ii / 4], uq = u4[ii / 4];
+                float kv;
+                kv = kq.x * vj; y0 += rq.x * fmaf(uq.x, kv, st[ii]);     st[ii] = fmaf(wq.x, st[ii], kv);
+                kv = kq.y * vj; y1 += rq.y * fmaf(uq.y, kv, st[ii + 1]); st[ii + 1] = fmaf(wq.y, st[ii + 1], kv);
+                kv = kq.z * vj; y0 += rq.z * fmaf(uq.z, kv, st[ii + 2]); st[ii + 2] = fmaf(wq.z, st[ii + 2], kv);
+                kv = kq.w * vj; y1 += rq.w * fmaf(uq.w, kv, st[ii + 3]); st[ii + 3] = fmaf(wq.w, st[ii + 3], kv);
             }
-            xin = dload(a.x, a.dtype, ti);
-        }
-        const float vj = dload(a.v, a.dtype, ti);
-        float y0 = 0.f, y1 = 0.f;
+            part[cur][q][j] = y0 + y1;
+            __syncthreads();
+            if (q == 0) {
+                float y = part[cur][0][j];
 #pragma unroll
-        for (int ii = 0; ii < SI; ii += 2) {
-            const int i = q * SI + ii;
-            float kv;
-            kv = sk[cur][i] * vj;     y0 += sr[cur][i] * fmaf(su[i], kv, st[ii]);             st[ii] = fmaf(sw[cur][i], st[ii], kv);
-            kv = sk[cur][i + 1] * vj; y1 += sr[cur][i + 1] * fmaf(su[i + 1], kv, st[ii + 1]); st[ii + 1] = fmaf(sw[cur][i + 1], st[ii + 1], kv);
+                for (int p2 = 1; p2 < Q; ++p2) y += part[cur][p2][j];
+                if (t - cu.token + 1u == cu.len)  // last token of the run: token-shift carry takes the layer input
+                    static_cast<float*>(a.state.base)[a.state.index(c, 0, slot)] = dload(a.x, a.dtype, ti);
+                dstore(a.x, a.dtype, ti, y);
+            }
         }
-        part[cur][q][j] = y0 + y1;
-        if (q == 0 && more) {
-            sk[nxt][j] = nk;
-            sr[nxt][j] = nr;
-            if (a.per_token_decay) sw[nxt][j] = nw;
-        }
+        if (more) store_chunk(buf ^ 1);  // last read two chunks ago, before that chunk's closing barrier
         __syncthreads();
-        if (q == 0) {
-            float y = part[cur][0][j];
-#pragma unroll
-            for (int p2 = 1; p2 < Q; ++p2) y += part[cur][p2][j];
-            const CursorD cu = cursor_at(a.cursors, a.wide, t);
-            if (t - cu.token + 1u == cu.len)  // last token of the run: token-shift carry takes the layer input
-                static_cast<float*>(a.state.base)[a.state.index(c, 0, slot)] = xin;
-            dstore(a.x, a.dtype, ti, y);
-        }
     }
 #pragma unroll
     for (int i = 0; i < SI; ++i) static_cast<float*>(a.state.base)[a.state.index(c, 1 + q * SI + i, slot)] = st[i];
 }
 
-template <int S>
-__global__ void __launch_bounds__(S) time_mix_v7_kernel(const WkvArgs a) {
-    __shared__ float sr[2][S], sw[2][S], sk[2][S], sa[2][S], sb[2][S];
+// v7: one CTA of (1 + G) * S threads per (head, batch slot).  Thread j of the first S keeps the whole column j of the
+// state in registers, so a token needs no exchange between threads; the other G groups of S threads fetch the tokens'
+// rows a chunk of 768 / S tokens ahead (three pairs: r and the decay; k and v; a and kk, 3 / G pairs per group), apply
+// the per-token transforms (w -> exp(-0.606531 sigmoid(w)), -kk, kk a) and hand them over through shared memory, one
+// barrier per chunk.
+template <int S, int G>
+__global__ void __launch_bounds__((1 + G) * S) time_mix_v7_kernel(const WkvArgs a) {
+    static_assert(G == 1 || G == 3, "three pairs of rows over the loader groups");
+    constexpr int TC = 768 / S, P = 3 / G;
+    enum { IN_R = 0, IN_W = 1, IN_K = 2, IN_V = 3, IN_A = 4, IN_B = 5 };
+    __shared__ __align__(16) float sin[2][6][TC][S];
     __shared__ uint32_t s_start, s_count;
-    const uint32_t h = blockIdx.x, slot = blockIdx.y, j = threadIdx.x;
+    const uint32_t h = blockIdx.x, slot = blockIdx.y, j = threadIdx.x % S, q = threadIdx.x / S;
     const uint32_t C = a.S * a.H, c = h * S + j;
     const size_t plane = (size_t)a.T * C;
 
@@ -129,72 +160,107 @@ __global__ void __launch_bounds__(S) time_mix_v7_kernel(const WkvArgs a) {
     if (!find_run(a.cursors, a.wide, a.T, slot, &s_start, &s_count, start, count)) return;
 
     float st[S];
+    if (q == 0) {
 #pragma unroll
-    for (int i = 0; i < S; ++i) st[i] = static_cast<const float*>(a.state.base)[a.state.index(c, 1 + i, slot)];
+        for (int i = 0; i < S; ++i) st[i] = static_cast<const float*>(a.state.base)[a.state.index(c, 1 + i, slot)];
+    }
 
     auto decay = [](float w) { return expf(-0.606531f * (1.0f / (1.0f + expf(-w)))); };
-    {
-        const size_t ti = (size_t)start * C + c;
-        sr[0][j] = dload(a.r, a.dtype, ti);
-        sw[0][j] = decay(dload(a.w, a.dtype, ti));
-        sk[0][j] = dload(a.n, a.dtype, ti);
-        const float av = dload(a.n, a.dtype, ti + 2 * plane), kk = dload(a.n, a.dtype, ti + 3 * plane);
-        sa[0][j] = -kk;
-        sb[0][j] = kk * av;
+    // loader group q (1..G): the pairs of staged rows it owns, element (token, channel j) of chunk `chunk` (zero past
+    // the run's end)
+    float s0[P][TC], s1[P][TC];
+    auto load_chunk = [&](uint32_t chunk) {
+#pragma unroll
+        for (int pi = 0; pi < P; ++pi) {
+            const uint32_t pair = G == 1 ? (uint32_t)pi : q - 1;
+#pragma unroll
+            for (int n = 0; n < TC; ++n) {
+                const uint32_t m = chunk * TC + n;
+                const size_t ti = (size_t)(start + m) * C + c;
+                float x0 = 0.f, x1 = 0.f;
+                if (m < count) {
+                    if (pair == 0) x0 = dload(a.r, a.dtype, ti), x1 = dload(a.w, a.dtype, ti);
+                    else if (pair == 1) x0 = dload(a.n, a.dtype, ti), x1 = dload(a.n, a.dtype, ti + plane);
+                    else x0 = dload(a.n, a.dtype, ti + 2 * plane), x1 = dload(a.n, a.dtype, ti + 3 * plane);
+                }
+                s0[pi][n] = x0;
+                s1[pi][n] = x1;
+            }
+        }
+    };
+    auto store_chunk = [&](int buf) {
+#pragma unroll
+        for (int pi = 0; pi < P; ++pi) {
+            const uint32_t pair = G == 1 ? (uint32_t)pi : q - 1;
+#pragma unroll
+            for (int n = 0; n < TC; ++n) {
+                if (pair == 0) sin[buf][IN_R][n][j] = s0[pi][n], sin[buf][IN_W][n][j] = decay(s1[pi][n]);
+                else if (pair == 1) sin[buf][IN_K][n][j] = s0[pi][n], sin[buf][IN_V][n][j] = s1[pi][n];
+                else sin[buf][IN_A][n][j] = -s1[pi][n], sin[buf][IN_B][n][j] = s1[pi][n] * s0[pi][n];
+            }
+        }
+    };
+    const uint32_t chunks = (count + TC - 1) / TC;
+    if (q != 0) {
+        load_chunk(0);
+        store_chunk(0);
     }
     __syncthreads();
 
-    for (uint32_t n = 0; n < count; ++n) {
-        const uint32_t t = start + n;
-        const int cur = n & 1, nxt = cur ^ 1;
-        const size_t ti = (size_t)t * C + c;
-        const bool more = n + 1 < count;
-        float nr = 0.f, nw = 0.f, nk = 0.f, na = 0.f, nkk = 0.f;
-        if (more) {
-            nr = dload(a.r, a.dtype, ti + C);
-            nw = dload(a.w, a.dtype, ti + C);
-            nk = dload(a.n, a.dtype, ti + C);
-            na = dload(a.n, a.dtype, ti + C + 2 * plane);
-            nkk = dload(a.n, a.dtype, ti + C + 3 * plane);
-        }
-        const float vj = dload(a.n, a.dtype, ti + plane);
-        const float xin = dload(a.x, a.dtype, ti);
-        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
+        const int buf = chunk & 1;
+        const bool more = chunk + 1 < chunks;
+        if (q != 0) {
+            if (more) {
+                load_chunk(chunk + 1);
+                store_chunk(buf ^ 1);  // last read two chunks ago, before that chunk's closing barrier
+            }
+        } else {
+            const uint32_t len = min((uint32_t)TC, count - chunk * TC);
+            for (uint32_t n = 0; n < len; ++n) {
+                const uint32_t t = start + chunk * TC + n;
+                const size_t ti = (size_t)t * C + c;
+                const CursorD cu = cursor_at(a.cursors, a.wide, t);
+                const float vj = sin[buf][IN_V][n][j];
+                const float4* r4 = reinterpret_cast<const float4*>(sin[buf][IN_R][n]);
+                const float4* w4 = reinterpret_cast<const float4*>(sin[buf][IN_W][n]);
+                const float4* k4 = reinterpret_cast<const float4*>(sin[buf][IN_K][n]);
+                const float4* a4 = reinterpret_cast<const float4*>(sin[buf][IN_A][n]);
+                const float4* b4 = reinterpret_cast<const float4*>(sin[buf][IN_B][n]);
+                float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;
 #pragma unroll
-        for (int i = 0; i < S; i += 4) {
-            s0 = fmaf(st[i], sa[cur][i], s0);
-            s1 = fmaf(st[i + 1], sa[cur][i + 1], s1);
-            s2 = fmaf(st[i + 2], sa[cur][i + 2], s2);
-            s3 = fmaf(st[i + 3], sa[cur][i + 3], s3);
-        }
-        const float sav = (s0 + s1) + (s2 + s3);
-        float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+                for (int i = 0; i < S; i += 4) {
+                    const float4 av = a4[i / 4];
+                    z0 = fmaf(st[i], av.x, z0);
+                    z1 = fmaf(st[i + 1], av.y, z1);
+                    z2 = fmaf(st[i + 2], av.z, z2);
+                    z3 = fmaf(st[i + 3], av.w, z3);
+                }
+                const float sav = (z0 + z1) + (z2 + z3);
+                float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
 #pragma unroll
-        for (int i = 0; i < S; i += 4) {
-            st[i] = st[i] * sw[cur][i] + sk[cur][i] * vj + sav * sb[cur][i];
-            y0 = fmaf(sr[cur][i], st[i], y0);
-            st[i + 1] = st[i + 1] * sw[cur][i + 1] + sk[cur][i + 1] * vj + sav * sb[cur][i + 1];
-            y1 = fmaf(sr[cur][i + 1], st[i + 1], y1);
-            st[i + 2] = st[i + 2] * sw[cur][i + 2] + sk[cur][i + 2] * vj + sav * sb[cur][i + 2];
-            y2 = fmaf(sr[cur][i + 2], st[i + 2], y2);
-            st[i + 3] = st[i + 3] * sw[cur][i + 3] + sk[cur][i + 3] * vj + sav * sb[cur][i + 3];
-            y3 = fmaf(sr[cur][i + 3], st[i + 3], y3);
-        }
-        const CursorD cu = cursor_at(a.cursors, a.wide, t);
-        if (t - cu.token + 1u == cu.len)
-            static_cast<float*>(a.state.base)[a.state.index(c, 0, slot)] = xin;
-        dstore(a.x, a.dtype, ti, (y0 + y1) + (y2 + y3));
-        if (more) {
-            sr[nxt][j] = nr;
-            sw[nxt][j] = decay(nw);
-            sk[nxt][j] = nk;
-            sa[nxt][j] = -nkk;
-            sb[nxt][j] = nkk * na;
+                for (int i = 0; i < S; i += 4) {
+                    const float4 wv = w4[i / 4], kv = k4[i / 4], bv = b4[i / 4], rv = r4[i / 4];
+                    st[i] = st[i] * wv.x + kv.x * vj + sav * bv.x;
+                    y0 = fmaf(rv.x, st[i], y0);
+                    st[i + 1] = st[i + 1] * wv.y + kv.y * vj + sav * bv.y;
+                    y1 = fmaf(rv.y, st[i + 1], y1);
+                    st[i + 2] = st[i + 2] * wv.z + kv.z * vj + sav * bv.z;
+                    y2 = fmaf(rv.z, st[i + 2], y2);
+                    st[i + 3] = st[i + 3] * wv.w + kv.w * vj + sav * bv.w;
+                    y3 = fmaf(rv.w, st[i + 3], y3);
+                }
+                if (t - cu.token + 1u == cu.len)
+                    static_cast<float*>(a.state.base)[a.state.index(c, 0, slot)] = dload(a.x, a.dtype, ti);
+                dstore(a.x, a.dtype, ti, (y0 + y1) + (y2 + y3));
+            }
         }
         __syncthreads();
     }
+    if (q == 0) {
 #pragma unroll
-    for (int i = 0; i < S; ++i) static_cast<float*>(a.state.base)[a.state.index(c, 1 + i, slot)] = st[i];
+        for (int i = 0; i < S; ++i) static_cast<float*>(a.state.base)[a.state.index(c, 1 + i, slot)] = st[i];
+    }
 }
 
 // x_j += (sum_i u_i k_i r_i) * v_j per (token, head): one warp per (token, head).
@@ -231,9 +297,9 @@ cudaError_t time_mix_v7(const WkvArgs& a, cudaStream_t stream) {
     if (a.T == 0 || a.B == 0) return cudaSuccess;
     dim3 grid(a.H, a.B);
     switch (a.S) {
-        case 32: time_mix_v7_kernel<32><<<grid, 32, 0, stream>>>(a); break;
-        case 64: time_mix_v7_kernel<64><<<grid, 64, 0, stream>>>(a); break;
-        case 128: time_mix_v7_kernel<128><<<grid, 128, 0, stream>>>(a); break;
+        case 32: time_mix_v7_kernel<32, 3><<<grid, 128, 0, stream>>>(a); break;
+        case 64: time_mix_v7_kernel<64, 3><<<grid, 256, 0, stream>>>(a); break;
+        case 128: time_mix_v7_kernel<128, 1><<<grid, 256, 0, stream>>>(a); break;
         default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();
