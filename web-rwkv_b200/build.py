@@ -23,6 +23,7 @@ SOURCES = [
     "kernels/gemm_small.cu",
     "kernels/wkv.cu",
     "kernels/support.cu",
+    "kernels/elementwise.cu",
     "kernels/peer_reduce.cu",
     "kernels/decode.cu",
     "kernels/decode_step.cu",

@@ -123,6 +123,17 @@ struct ShiftMultiArgs {
     int reversed;
 };
 cudaError_t token_shift_multi(const ShiftMultiArgs& a, cudaStream_t stream);
+// Vector forms for dense operands (elementwise.cu); false: the operands do not fit, nothing was launched.
+bool layer_norm_vec(const __half* w, const __half* b, int dtype, const void* delta, void* src, void* x, uint32_t C, uint32_t rows,
+                    uint32_t wrows, float eps, cudaStream_t stream);
+bool binary_vec(int is_mul, const DView& input, const DView& output, int act_x, int act_y, int act_out, cudaStream_t stream);
+bool activate_vec(const DView& x, int act, cudaStream_t stream);
+bool blit_vec(const DView& input, const DView& output, cudaStream_t stream);
+bool token_shift_vec(const uint32_t* cursors, int wide, const DView& time_mix, const DView& state, const DView& input,
+                     const DView& output, int reversed, cudaStream_t stream);
+bool token_shift_multi_vec(const ShiftMultiArgs& a, cudaStream_t stream);
+bool channel_mix_vec(const uint32_t* cursors, int wide, const DView& state, int dtype, const void* r, const void* v, void* x,
+                     uint32_t C, uint32_t T, int v7, cudaStream_t stream);
 struct PackV7Args {
     const __half *k_k, *k_a;  // [H * S]
     __half *k, *kk, *n;       // [S, H, T] (k updated in place), [S, H, T], [S, H, T, 4]

@@ -391,6 +391,7 @@ cudaError_t layer_norm(const __half* w, const __half* b, int dtype, void* x, uin
 cudaError_t layer_norm_copy(const __half* w, const __half* b, int dtype, const void* delta, void* src, void* x, uint32_t C,
                             uint32_t rows, uint32_t wrows, float eps, cudaStream_t stream) {
     if (rows == 0 || C == 0) return cudaSuccess;
+    if (layer_norm_vec(w, b, dtype, delta, src, x, C, rows, wrows, eps, stream)) return cudaGetLastError();
     const int block = C <= 256 ? 32 : 256;
     const uint32_t grid = rows < 148u * 32u ? rows : 148u * 32u;
     layer_norm_kernel<<<grid, block, 0, stream>>>(w, b, dtype, delta, src, x, C, rows, wrows, eps);
@@ -463,6 +464,7 @@ cudaError_t token_shift(const uint32_t* cursors, int wide, DView time_mix, DView
                         int reversed, cudaStream_t stream) {
     const size_t total = (size_t)output.shape[0] * output.shape[1] * output.shape[2];
     if (total == 0) return cudaSuccess;
+    if (token_shift_vec(cursors, wide, time_mix, state, input, output, reversed, stream)) return cudaGetLastError();
     token_shift_kernel<<<ew_grid(total), kEw, 0, stream>>>(cursors, wide, time_mix, state, input, output, reversed);
     return cudaGetLastError();
 }
@@ -470,6 +472,7 @@ cudaError_t token_shift(const uint32_t* cursors, int wide, DView time_mix, DView
 cudaError_t token_shift_multi(const ShiftMultiArgs& a, cudaStream_t stream) {
     const size_t total = (size_t)a.C * a.T;
     if (total == 0 || a.count == 0) return cudaSuccess;
+    if (token_shift_multi_vec(a, stream)) return cudaGetLastError();
     token_shift_multi_kernel<<<ew_grid(total), kEw, 0, stream>>>(a);
     return cudaGetLastError();
 }
@@ -493,6 +496,7 @@ cudaError_t channel_mix(const uint32_t* cursors, int wide, DView state, int dtyp
                         void* x, uint32_t C, uint32_t T, int v7, cudaStream_t stream) {
     const size_t total = (size_t)C * T;
     if (total == 0) return cudaSuccess;
+    if (channel_mix_vec(cursors, wide, state, dtype, r, v, x, C, T, v7, stream)) return cudaGetLastError();
     channel_mix_kernel<<<ew_grid(total), kEw, 0, stream>>>(cursors, wide, state, dtype, r, v, x, C, T, v7);
     return cudaGetLastError();
 }
@@ -500,6 +504,7 @@ cudaError_t channel_mix(const uint32_t* cursors, int wide, DView state, int dtyp
 cudaError_t binary(int is_mul, DView input, DView output, int act_x, int act_y, int act_out, cudaStream_t stream) {
     const size_t total = (size_t)output.shape[0] * output.shape[1] * output.shape[2];
     if (total == 0) return cudaSuccess;
+    if (binary_vec(is_mul, input, output, act_x, act_y, act_out, stream)) return cudaGetLastError();
     binary_kernel<<<ew_grid(total), kEw, 0, stream>>>(is_mul, input, output, act_x, act_y, act_out);
     return cudaGetLastError();
 }
@@ -507,6 +512,7 @@ cudaError_t binary(int is_mul, DView input, DView output, int act_x, int act_y, 
 cudaError_t activate(DView x, int act, cudaStream_t stream) {
     const size_t total = (size_t)x.shape[0] * x.shape[1] * x.shape[2];
     if (total == 0) return cudaSuccess;
+    if (activate_vec(x, act, stream)) return cudaGetLastError();
     activate_kernel<<<ew_grid(total), kEw, 0, stream>>>(x, act);
     return cudaGetLastError();
 }
@@ -514,6 +520,7 @@ cudaError_t activate(DView x, int act, cudaStream_t stream) {
 cudaError_t blit(DView input, DView output, int transpose, cudaStream_t stream) {
     const size_t total = (size_t)input.shape[0] * input.shape[1] * input.shape[2];
     if (total == 0) return cudaSuccess;
+    if (!transpose && blit_vec(input, output, stream)) return cudaGetLastError();
     blit_kernel<<<ew_grid(total), kEw, 0, stream>>>(input, output, transpose);
     return cudaGetLastError();
 }
