@@ -24,7 +24,7 @@ def _cursors(seqs, wide):
     return oracle.pack_cursors(cur, wide=wide), tok
 
 
-def _v56_case(wrk, ctx, version, H, seqs, B, wide, dtype=np.float32, seed=0):
+def _v56_case(wrk, ctx, version, H, seqs, B, wide, dtype=np.float32, seed=0, S=S):
     rng = np.random.default_rng(seed)
     C = S * H
     cursors, T = _cursors(seqs, wide)
@@ -91,7 +91,22 @@ def test_v6_packed_cursor_len_wraps_at_256(wrk, ctx):
     assert not np.array_equal(gs[0, 0], gsw[0, 0])  # carry row differs between the two forms
 
 
-def _v7_case(wrk, ctx, H, seqs, B, wide, dtype=np.float16, seed=0):
+@pytest.mark.parametrize("head_size", [32, 128])
+@pytest.mark.parametrize("version", [5, 6])
+def test_v56_other_head_sizes(wrk, ctx, version, head_size):
+    # runs that end inside, at the end of and past a staged chunk of tokens
+    gx, gs, rx, rs = _v56_case(wrk, ctx, version, 3, [(0, 37), (1, 16), (2, 1)], 3, True, seed=40 + head_size, S=head_size)
+    assert_close(gx, rx, "x")
+    assert_close(gs, rs, "state")
+
+
+def test_v6_long_runs_cross_chunks(wrk, ctx):
+    gx, gs, rx, rs = _v56_case(wrk, ctx, 6, 5, [(1, 130), (0, 33), (2, 48)], 3, True, seed=44)
+    assert_close(gx, rx, "x")
+    assert_close(gs, rs, "state")
+
+
+def _v7_case(wrk, ctx, H, seqs, B, wide, dtype=np.float16, seed=0, S=S):
     rng = np.random.default_rng(seed)
     C = S * H
     cursors, T = _cursors(seqs, wide)
@@ -123,6 +138,13 @@ def test_v7_multi_sequence(wrk, ctx, wide, dtype):
     assert_close(gx, rx, "x")
     assert_close(gs, rs, "state")
     assert np.array_equal(gs[0], rs[0])
+
+
+@pytest.mark.parametrize("head_size", [32, 128])
+def test_v7_other_head_sizes(wrk, ctx, head_size):
+    gx, gs, rx, rs = _v7_case(wrk, ctx, 3, [(0, 29), (1, 24), (2, 1)], 3, True, seed=50 + head_size, S=head_size)
+    assert_close(gx, rx, "x")
+    assert_close(gs, rs, "state")
 
 
 @pytest.mark.parametrize("T", [1, 2, 64, 512])

@@ -19,77 +19,144 @@ namespace k {
 namespace {
 
 // Finds the contiguous run of tokens that belongs to batch slot `slot`.  Returns false when the
-// slot has no token in this job.
-__device__ __forceinline__ bool find_run(const uint32_t* cursors, int wide, uint32_t T, uint32_t slot,
-                                         uint32_t* s_start, uint32_t* s_count, uint32_t& start, uint32_t& count) {
+// slot has no token in this job.  `carry` (when given) receives 1 + the last token of the run whose cursor says it
+// ends its sequence's part of the job (t - token + 1 == len), or 0 when there is none: the token whose layer input
+// becomes the token-shift carry row.
+struct RunScratch {
+    uint32_t start, count, carry;
+};
+__device__ __forceinline__ bool find_run(const uint32_t* cursors, int wide, uint32_t T, uint32_t slot, RunScratch* sh,
+                                         uint32_t& start, uint32_t& count, uint32_t* carry = nullptr) {
     if (threadIdx.x == 0) {
-        *s_start = 0xffffffffu;
-        *s_count = 0;
+        sh->start = 0xffffffffu;
+        sh->count = 0;
+        sh->carry = 0;
     }
     __syncthreads();
-    uint32_t my_min = 0xffffffffu, my_cnt = 0;
+    uint32_t my_min = 0xffffffffu, my_cnt = 0, my_carry = 0;
     for (uint32_t t = threadIdx.x; t < T; t += blockDim.x) {
         const CursorD c = cursor_at(cursors, wide, t);
         if (c.batch == slot) {
             my_min = min(my_min, t);
             ++my_cnt;
+            if (t - c.token + 1u == c.len) my_carry = t + 1;
         }
     }
     if (my_cnt) {
-        atomicMin(s_start, my_min);
-        atomicAdd(s_count, my_cnt);
+        atomicMin(&sh->start, my_min);
+        atomicAdd(&sh->count, my_cnt);
+        if (my_carry) atomicMax(&sh->carry, my_carry);
     }
     __syncthreads();
-    start = *s_start;
-    count = *s_count;
+    start = sh->start;
+    count = sh->count;
+    if (carry) *carry = sh->carry;
     return count != 0;
 }
 
-// One CTA of 4 * S threads per (head, batch slot): thread (q, j) keeps rows [q S/4, (q+1) S/4) of state column j in
-// registers for the sequence's whole run of tokens and adds its part of output j; the four parts meet in shared
-// memory (one barrier per token, buffers alternate).  The tokens' k, r, w and v rows reach shared memory a chunk of
-// 1024 / S tokens at a time: thread group q loads one of the four tensors, a chunk ahead, into registers while the
-// current chunk is computed, so a token's step never waits for global memory.
-template <int S, int Q>
-__global__ void __launch_bounds__(S * Q) time_mix_v56_kernel(const WkvArgs a) {
-    static_assert(Q == 4, "one loader group per staged tensor");
-    constexpr int SI = S / Q, TC = 1024 / S;
+// One CTA of (S / 4) (S / CW) threads per (head, batch slot): a thread keeps a 4 x CW tile of the head's S x S state
+// in registers for the sequence's whole run of tokens (rows = key index, columns = value index), so every k, r, w
+// value it fetches from shared memory feeds CW columns and every v value four rows.  (Measured at S = 64, 64 heads:
+// CW = 4, 8 warps: 0.34 us per token; CW = 2, 16 warps: 0.40 us.)  The S / 4 row groups of a column
+// group are lanes of ONE warp: a token's output column is summed by shuffles alone, and nothing but the state's own
+// recurrence (one fma deep per token) ties a token to the one before it - no barrier, no shared-memory partials.  The
+// tokens' k, r, w and v rows reach shared memory a chunk of TC tokens at a time, loaded a chunk ahead into registers
+// while the current chunk is computed (one barrier per chunk), so a token's step never waits for global memory.
+template <int S, int CW>
+__global__ void __launch_bounds__((S / 4) * (S / CW)) time_mix_v56_kernel(const WkvArgs a) {
+    constexpr int RG = S / 4, NT = RG * (S / CW), CGW = 32 / RG, TC = S <= 64 ? 16 : 4, PI = (4 * S + NT - 1) / NT;
+    static_assert(CW == 2 || CW == 4, "columns per thread");
+    static_assert(RG == 8 || RG == 16 || RG == 32, "the row groups of a column group are lanes of one warp");
     enum { IN_K = 0, IN_R = 1, IN_W = 2, IN_V = 3 };
     __shared__ __align__(16) float sin[2][4][TC][S];
-    __shared__ __align__(16) float su[S];
-    __shared__ float part[2][Q][S];
-    __shared__ uint32_t s_start, s_count;
-    const uint32_t h = blockIdx.x, slot = blockIdx.y, j = threadIdx.x % S, q = threadIdx.x / S;
-    const uint32_t C = a.S * a.H, c = h * S + j;
+    __shared__ RunScratch run;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rg = lane % RG, cg = warp * CGW + lane / RG;  // rows 4 rg .. 4 rg + 3, columns CW cg .. CW cg + CW - 1
+    const uint32_t h = blockIdx.x, slot = blockIdx.y, C = a.S * a.H, c0 = h * S;
 
-    uint32_t start, count;
-    if (!find_run(a.cursors, a.wide, a.T, slot, &s_start, &s_count, start, count)) return;
+    uint32_t start, count, carry;
+    if (!find_run(a.cursors, a.wide, a.T, slot, &run, start, count, &carry)) return;
+    // The token-shift carry row takes the layer input of the run's closing token.  Nothing in this kernel reads that
+    // row, so it is written now, before the token's input is overwritten with its output; the token loop below then
+    // has no cursor to look at and no branch.
+    if (carry != 0) {
+        for (uint32_t j = tid; j < S; j += NT)
+            static_cast<float*>(a.state.base)[a.state.index(c0 + j, 0, slot)] = dload(a.x, a.dtype, (size_t)(carry - 1) * C + c0 + j);
+    }
 
-    float st[SI];
+    float st[4][CW], u[4];  // st[row][column]
 #pragma unroll
-    for (int i = 0; i < SI; ++i) st[i] = static_cast<const float*>(a.state.base)[a.state.index(c, 1 + q * SI + i, slot)];
-    if (q == 0) su[j] = a.time_first[c];
+    for (int r = 0; r < 4; ++r) {
+        u[r] = a.time_first[c0 + 4 * rg + r];
+#pragma unroll
+        for (int cc = 0; cc < CW; ++cc)
+            st[r][cc] = static_cast<const float*>(a.state.base)[a.state.index(c0 + CW * cg + cc, 1 + 4 * rg + r, slot)];
+    }
 
-    // group q's tensor: element (token, channel j) of chunk `chunk` (zero past the run's end)
-    float stage[TC];
+    // staging: (tensor, channel) pairs tid, tid + NT, ... of the 4 S pairs; element (token, channel) of chunk `chunk`
+    // (zero past the run's end)
+    float stage[PI][TC];
     auto load_chunk = [&](uint32_t chunk) {
 #pragma unroll
-        for (int n = 0; n < TC; ++n) {
-            const uint32_t m = chunk * TC + n;
-            const size_t ti = (size_t)(start + m) * C + c;
-            float v = 0.f;
-            if (m < count) {
-                if (q == IN_K) v = dload(a.k, a.dtype, ti);
-                else if (q == IN_R) v = dload(a.r, a.dtype, ti);
-                else if (q == IN_W) v = a.per_token_decay ? a.time_decay[ti] : a.time_decay[c];
-                else v = dload(a.v, a.dtype, ti);
+        for (int pi = 0; pi < PI; ++pi) {
+            const uint32_t pair = tid + pi * NT, tensor = pair / S, c = c0 + pair % S;
+#pragma unroll
+            for (int n = 0; n < TC; ++n) {
+                const uint32_t m = chunk * TC + n;
+                const size_t ti = (size_t)(start + m) * C + c;
+                float v = 0.f;
+                if (pair < 4 * S && m < count) {
+                    if (tensor == IN_K) v = dload(a.k, a.dtype, ti);
+                    else if (tensor == IN_R) v = dload(a.r, a.dtype, ti);
+                    else if (tensor == IN_W) v = a.per_token_decay ? a.time_decay[ti] : a.time_decay[c];
+                    else v = dload(a.v, a.dtype, ti);
+                }
+                stage[pi][n] = v;
             }
-            stage[n] = v;
         }
     };
     auto store_chunk = [&](int buf) {
 #pragma unroll
-        for (int n = 0; n < TC; ++n) sin[buf][q][n][j] = stage[n];
+        for (int pi = 0; pi < PI; ++pi) {
+            const uint32_t pair = tid + pi * NT;
+            if (pair < 4 * S) {
+#pragma unroll
+                for (int n = 0; n < TC; ++n) sin[buf][pair / S][n][pair % S] = stage[pi][n];
+            }
+        }
+    };
+    // one token: the tile's share of the four output columns, summed over the row groups; lane rg == 0 stores them
+    auto token = [&](int buf, uint32_t n, uint32_t t) {
+        const float4 kq = *reinterpret_cast<const float4*>(&sin[buf][IN_K][n][4 * rg]);
+        const float4 rq = *reinterpret_cast<const float4*>(&sin[buf][IN_R][n][4 * rg]);
+        const float4 wq = *reinterpret_cast<const float4*>(&sin[buf][IN_W][n][4 * rg]);
+        const float kr[4] = {kq.x, kq.y, kq.z, kq.w}, rr[4] = {rq.x, rq.y, rq.z, rq.w}, wr[4] = {wq.x, wq.y, wq.z, wq.w};
+        float vc[CW], y[CW];
+#pragma unroll
+        for (int cc = 0; cc < CW; cc += 2) {
+            const float2 vq = *reinterpret_cast<const float2*>(&sin[buf][IN_V][n][CW * cg + cc]);
+            vc[cc] = vq.x, vc[cc + 1] = vq.y;
+            y[cc] = y[cc + 1] = 0.f;
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+#pragma unroll
+            for (int cc = 0; cc < CW; ++cc) {
+                const float kv = kr[r] * vc[cc];
+                y[cc] = fmaf(rr[r], fmaf(u[r], kv, st[r][cc]), y[cc]);
+                st[r][cc] = fmaf(wr[r], st[r][cc], kv);
+            }
+        }
+#pragma unroll
+        for (int off = 1; off < RG; off <<= 1) {
+#pragma unroll
+            for (int cc = 0; cc < CW; ++cc) y[cc] += __shfl_xor_sync(0xffffffffu, y[cc], off);
+        }
+        if (rg == 0) {
+            const size_t ti = (size_t)t * C + c0 + CW * cg;
+#pragma unroll
+            for (int cc = 0; cc < CW; ++cc) dstore(a.x, a.dtype, ti + cc, y[cc]);
+        }
     };
     const uint32_t chunks = (count + TC - 1) / TC;
     load_chunk(0);
@@ -100,44 +167,21 @@ __global__ void __launch_bounds__(S * Q) time_mix_v56_kernel(const WkvArgs a) {
         const int buf = chunk & 1;
         const bool more = chunk + 1 < chunks;
         if (more) load_chunk(chunk + 1);  // in flight while this chunk's tokens are computed
-        const uint32_t len = min((uint32_t)TC, count - chunk * TC);
-        for (uint32_t n = 0; n < len; ++n) {
-            const uint32_t t = start + chunk * TC + n;
-            const int cur = n & 1;  // TC is even: the parity runs on across chunks
-            const size_t ti = (size_t)t * C + c;
-            CursorD cu{};
-            if (q == 0) cu = cursor_at(a.cursors, a.wide, t);
-            const float vj = sin[buf][IN_V][n][j];
-            const float4* k4 = reinterpret_cast<const float4*>(&sin[buf][IN_K][n][q * SI]);
-            const float4* r4 = reinterpret_cast<const float4*>(&sin[buf][IN_R][n][q * SI]);
-            const float4* w4 = reinterpret_cast<const float4*>(&sin[buf][IN_W][n][q * SI]);
-            const float4* u4 = reinterpret_cast<const float4*>(&su[q * SI]);
-            float y0 = 0.f, y1 = 0.f;
-#pragma unroll
-            for (int ii = 0; ii < SI; ii += 4) {
-                const float4 kq = k4[ii / 4], rq = r4[ii / 4], wq = w4[ii / 4], uq = u4[ii / 4];
-                float kv;
-                kv = kq.x * vj; y0 += rq.x * fmaf(uq.x, kv, st[ii]);     st[ii] = fmaf(wq.x, st[ii], kv);
-                kv = kq.y * vj; y1 += rq.y * fmaf(uq.y, kv, st[ii + 1]); st[ii + 1] = fmaf(wq.y, st[ii + 1], kv);
-                kv = kq.z * vj; y0 += rq.z * fmaf(uq.z, kv, st[ii + 2]); st[ii + 2] = fmaf(wq.z, st[ii + 2], kv);
-                kv = kq.w * vj; y1 += rq.w * fmaf(uq.w, kv, st[ii + 3]); st[ii + 3] = fmaf(wq.w, st[ii + 3], kv);
-            }
-            part[cur][q][j] = y0 + y1;
-            __syncthreads();
-            if (q == 0) {
-                float y = part[cur][0][j];
-#pragma unroll
-                for (int p2 = 1; p2 < Q; ++p2) y += part[cur][p2][j];
-                if (t - cu.token + 1u == cu.len)  // last token of the run: token-shift carry takes the layer input
-                    static_cast<float*>(a.state.base)[a.state.index(c, 0, slot)] = dload(a.x, a.dtype, ti);
-                dstore(a.x, a.dtype, ti, y);
-            }
+        const uint32_t len = min((uint32_t)TC, count - chunk * TC), t0 = start + chunk * TC;
+        if (len == TC) {
+#pragma unroll 4
+            for (uint32_t n = 0; n < TC; ++n) token(buf, n, t0 + n);
+        } else {
+            for (uint32_t n = 0; n < len; ++n) token(buf, n, t0 + n);
         }
-        if (more) store_chunk(buf ^ 1);  // last read two chunks ago, before that chunk's closing barrier
+        if (more) store_chunk(buf ^ 1);  // last read during the previous chunk, before its closing barrier
         __syncthreads();
     }
 #pragma unroll
-    for (int i = 0; i < SI; ++i) static_cast<float*>(a.state.base)[a.state.index(c, 1 + q * SI + i, slot)] = st[i];
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int cc = 0; cc < CW; ++cc)
+            static_cast<float*>(a.state.base)[a.state.index(c0 + CW * cg + cc, 1 + 4 * rg + r, slot)] = st[r][cc];
 }
 
 // v7: one CTA of (1 + G) * S threads per (head, batch slot).  Thread j of the first S keeps the whole column j of the
@@ -151,13 +195,17 @@ __global__ void __launch_bounds__((1 + G) * S) time_mix_v7_kernel(const WkvArgs 
     constexpr int TC = 768 / S, P = 3 / G;
     enum { IN_R = 0, IN_W = 1, IN_K = 2, IN_V = 3, IN_A = 4, IN_B = 5 };
     __shared__ __align__(16) float sin[2][6][TC][S];
-    __shared__ uint32_t s_start, s_count;
+    __shared__ RunScratch run;
     const uint32_t h = blockIdx.x, slot = blockIdx.y, j = threadIdx.x % S, q = threadIdx.x / S;
     const uint32_t C = a.S * a.H, c = h * S + j;
     const size_t plane = (size_t)a.T * C;
 
-    uint32_t start, count;
-    if (!find_run(a.cursors, a.wide, a.T, slot, &s_start, &s_count, start, count)) return;
+    uint32_t start, count, carry;
+    if (!find_run(a.cursors, a.wide, a.T, slot, &run, start, count, &carry)) return;
+    // the carry row takes the layer input of the run's closing token: written now (nothing here reads the row), before
+    // the token's input is overwritten with its output
+    if (carry != 0 && q == 0)
+        static_cast<float*>(a.state.base)[a.state.index(c, 0, slot)] = dload(a.x, a.dtype, (size_t)(carry - 1) * C + c);
 
     float st[S];
     if (q == 0) {
@@ -220,7 +268,6 @@ __global__ void __launch_bounds__((1 + G) * S) time_mix_v7_kernel(const WkvArgs 
             for (uint32_t n = 0; n < len; ++n) {
                 const uint32_t t = start + chunk * TC + n;
                 const size_t ti = (size_t)t * C + c;
-                const CursorD cu = cursor_at(a.cursors, a.wide, t);
                 const float vj = sin[buf][IN_V][n][j];
                 const float4* r4 = reinterpret_cast<const float4*>(sin[buf][IN_R][n]);
                 const float4* w4 = reinterpret_cast<const float4*>(sin[buf][IN_W][n]);
@@ -250,8 +297,6 @@ __global__ void __launch_bounds__((1 + G) * S) time_mix_v7_kernel(const WkvArgs 
                     st[i + 3] = st[i + 3] * wv.w + kv.w * vj + sav * bv.w;
                     y3 = fmaf(rv.w, st[i + 3], y3);
                 }
-                if (t - cu.token + 1u == cu.len)
-                    static_cast<float*>(a.state.base)[a.state.index(c, 0, slot)] = dload(a.x, a.dtype, ti);
                 dstore(a.x, a.dtype, ti, (y0 + y1) + (y2 + y3));
             }
         }
@@ -285,9 +330,9 @@ cudaError_t time_mix_v56(const WkvArgs& a, cudaStream_t stream) {
     if (a.T == 0 || a.B == 0) return cudaSuccess;
     dim3 grid(a.H, a.B);
     switch (a.S) {
-        case 32: time_mix_v56_kernel<32, 4><<<grid, 128, 0, stream>>>(a); break;
+        case 32: time_mix_v56_kernel<32, 4><<<grid, 64, 0, stream>>>(a); break;
         case 64: time_mix_v56_kernel<64, 4><<<grid, 256, 0, stream>>>(a); break;
-        case 128: time_mix_v56_kernel<128, 4><<<grid, 512, 0, stream>>>(a); break;
+        case 128: time_mix_v56_kernel<128, 4><<<grid, 1024, 0, stream>>>(a); break;
         default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();
