@@ -211,9 +211,22 @@ int32_t wrk_op_token_shift(wrk_tensor* cursors, const wrk_view* time_mix, const 
  *     mixes [C] into f16 outputs [C, T].
  *   pack_v7: on f16 tensors [S, H, T] of one layer of v7: kk <- l2_norm(k * k_k) per head (blit + mul + l2_norm,
  *     src/runtime/v7.rs:888-890), k <- control_k(k_a, a, k) (TensorOp::control_k_v7), n[S, H, T, 4] <- k, v, a, kk
- *     (the four blits of src/runtime/v7.rs:925-928). */
+ *     (the four blits of src/runtime/v7.rs:925-928).
+ *   token_shift_lora: TensorOp::add of the static factors [C, 1, Z] to the adapter's output [C, T, Z] (the sum rounded
+ *     to f16) + the TensorOp::token_shift that uses it (src/runtime/v6.rs:794-804); the adapter's output is left as
+ *     it was.  Dense f16 tensors, C a multiple of 8, Z <= 6.
+ *   group_norm_gate: TensorOp::group_norm of x [S, H, T] + TensorOp::blit into an f16 tensor + TensorOp::mul_activate
+ *     with act(gate) (src/runtime/v6.rs:862-879): output <- act(gate) * f16(group_norm(x)); x is left as it was.
+ *   channel_mix_add: TensorOp::channel_mix (v7 != 0: channel_mix_v7, r may be NULL) + TensorOp::add of its result to
+ *     the residual stream (src/runtime/v6.rs:941-949). */
 int32_t wrk_op_layer_norm_copy(wrk_tensor* w, wrk_tensor* b, wrk_tensor* delta, wrk_tensor* src, wrk_tensor* dst, float eps,
                                wrk_op** out);
+int32_t wrk_op_token_shift_lora(wrk_tensor* cursors, const wrk_view* time_mix, const wrk_view* bias, const wrk_view* state,
+                                wrk_tensor* input, wrk_tensor* output, int32_t reversed, wrk_op** out);
+int32_t wrk_op_group_norm_gate(wrk_tensor* w, wrk_tensor* b, wrk_tensor* x, wrk_tensor* gate, wrk_tensor* output, float eps,
+                               int32_t gate_act, wrk_op** out);
+int32_t wrk_op_channel_mix_add(wrk_tensor* cursors, const wrk_view* state, wrk_tensor* r, wrk_tensor* v, wrk_tensor* x,
+                               wrk_tensor* residual, int32_t v7, wrk_op** out);
 int32_t wrk_op_token_shift_multi(wrk_tensor* cursors, const wrk_view* state, wrk_tensor* input, uint32_t count,
                                  wrk_tensor* const* time_mix, wrk_tensor* const* outputs, int32_t reversed, wrk_op** out);
 int32_t wrk_op_pack_v7(wrk_tensor* k_k, wrk_tensor* k_a, wrk_tensor* k, wrk_tensor* v, wrk_tensor* a, wrk_tensor* kk, wrk_tensor* n,

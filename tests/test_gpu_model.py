@@ -95,11 +95,12 @@ def test_decode_loop(ctx, config, fused):
     assert_close(bundle.state_back(0), np.stack([s[0] for s in state]), "state")
 
 
-@pytest.mark.parametrize("config,quant,saved", [("v7-tiny", {0: 1, 1: 2}, 15), ("v7-tiny", {}, 15), ("v5-tiny", {0: 1}, 7),
-                                                ("v6-tiny", {0: 2}, 4)])
+@pytest.mark.parametrize("config,quant,saved", [("v7-tiny", {0: 1, 1: 2}, 16), ("v7-tiny", {}, 16), ("v5-tiny", {0: 1}, 10),
+                                                ("v6-tiny", {0: 2}, 9)])
 def test_merged_elementwise_launches_are_bit_identical_to_the_op_list(ctx, config, quant, saved):
-    """layer_norm_copy, token_shift_multi and pack_v7 stand for runs of the reference's elementwise ops
-    (src/runtime/v7.rs:762-928, v6.rs:771-1010, v5.rs:686-870); the strict mode runs those ops one by one."""
+    """layer_norm_copy, token_shift_multi / _lora, pack_v7, group_norm_gate and channel_mix_add stand for runs of the
+    reference's elementwise ops (src/runtime/v7.rs:762-928, v6.rs:759-949, v5.rs:686-870); the strict mode runs those
+    ops one by one."""
     rng = np.random.default_rng(2003)
     tensors, model, ref = _build(ctx, config, quant)
     V = model.info.num_vocab

@@ -355,3 +355,65 @@ def test_pack_v7_equals_the_eight_ops(wrk, ctx):
     assert np.array_equal(kk.numpy().ravel(), kk2.numpy().ravel())
     assert np.array_equal(n.numpy().ravel(), n2.numpy().ravel())
     assert float(np.abs(kk2.numpy()).max()) > 0
+
+
+def test_token_shift_lora_equals_add_then_shift(wrk, ctx):
+    rng = np.random.default_rng(34)
+    C, B, T, Z = 256, 3, 11, 5
+    cursors = ctx.from_numpy(oracle.pack_cursors([(0, 0, 4), (2, 4, 1), (1, 5, 6)]))
+    state = ctx.from_numpy(rng.standard_normal((B, 66, C)).astype(np.float32))
+    x = ctx.from_numpy(rng.standard_normal((T, C)).astype(np.float16))
+    lora0 = rng.uniform(-0.3, 0.3, (Z, T, C)).astype(np.float16)
+    bias = ctx.from_numpy(rng.uniform(0.2, 0.8, (Z, 1, C)).astype(np.float16))
+    lora_a, lora_b = ctx.from_numpy(lora0), ctx.from_numpy(lora0)
+    out_a, out_b = ctx.tensor(wrk.F16, [C, T, Z]), ctx.tensor(wrk.F16, [C, T, Z])
+    ctx.run(wrk.add(bias, lora_a))
+    ctx.run(wrk.token_shift(cursors, lora_a, state.view(y=(0, 1)), x, out_a, True))
+    ctx.run(wrk.token_shift_lora(cursors, lora_b, bias, state.view(y=(0, 1)), x, out_b, True))
+    assert np.array_equal(out_a.numpy(), out_b.numpy())
+    assert np.array_equal(lora_b.numpy().ravel(), lora0.ravel())  # the adapter's output is left alone
+    want = np.zeros((Z, T, C), dtype=np.float16)
+    oracle.token_shift(oracle.pack_cursors([(0, 0, 4), (2, 4, 1), (1, 5, 6)]), lora_a.numpy().reshape(Z, T, C),
+                       oracle.View(state.numpy().reshape(B, 66, C), y=(0, 1)), x.numpy().reshape(T, C), want, True)
+    assert_close(out_b.numpy().reshape(Z, T, C), want, "token_shift_lora")
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_group_norm_gate_equals_norm_copy_gate(wrk, ctx, dtype):
+    rng = np.random.default_rng(35)
+    S, H, T = 64, 5, 9
+    x0 = rng.standard_normal((T, H, S)).astype(dtype)
+    w = ctx.from_numpy(rng.standard_normal((H, S)).astype(np.float16))
+    b = ctx.from_numpy(rng.standard_normal((H, S)).astype(np.float16))
+    gate = ctx.from_numpy(rng.standard_normal((T, H * S)).astype(np.float16))
+    x_a, x_b = ctx.from_numpy(x0), ctx.from_numpy(x0)
+    out_a, out_b = ctx.tensor(wrk.F16, [H * S, T, 1]), ctx.tensor(wrk.F16, [H * S, T, 1])
+    ctx.run(wrk.group_norm(w, b, x_a, 64e-5))
+    ctx.run(wrk.blit(x_a.reshape(H * S, T), out_a))
+    ctx.run(wrk.mul_activate(gate, out_a, wrk.ACT_SILU, wrk.ACT_NONE, wrk.ACT_NONE))
+    ctx.run(wrk.group_norm_gate(w, b, x_b, gate, out_b, 64e-5, wrk.ACT_SILU))
+    assert np.array_equal(out_a.numpy(), out_b.numpy())
+    assert np.array_equal(x_b.numpy().ravel(), x0.ravel())
+
+
+@pytest.mark.parametrize("v7", [False, True])
+def test_channel_mix_add_equals_mix_then_add(wrk, ctx, v7):
+    rng = np.random.default_rng(36)
+    C, B, T = 256, 3, 11
+    cursors = ctx.from_numpy(oracle.pack_cursors([(0, 0, 4), (2, 4, 1), (1, 5, 6)]))
+    state0 = rng.standard_normal((B, 66, C)).astype(np.float32)
+    r = ctx.from_numpy(rng.standard_normal((T, C)).astype(np.float16))
+    v = ctx.from_numpy(rng.standard_normal((T, C)).astype(np.float16))
+    x0 = rng.standard_normal((T, C)).astype(np.float16)
+    res0 = rng.standard_normal((T, C)).astype(np.float16)
+    st_a, st_b = ctx.from_numpy(state0), ctx.from_numpy(state0)
+    x_a, x_b, res_a, res_b = ctx.from_numpy(x0), ctx.from_numpy(x0), ctx.from_numpy(res0), ctx.from_numpy(res0)
+    if v7:
+        ctx.run(wrk.channel_mix_v7(cursors, st_a.view(y=65), v, x_a))
+    else:
+        ctx.run(wrk.channel_mix(cursors, st_a.view(y=65), r, v, x_a))
+    ctx.run(wrk.add(x_a, res_a))
+    ctx.run(wrk.channel_mix_add(cursors, st_b.view(y=65), None if v7 else r, v, x_b, res_b, v7))
+    assert np.array_equal(x_a.numpy(), x_b.numpy())
+    assert np.array_equal(res_a.numpy(), res_b.numpy())
+    assert np.array_equal(st_a.numpy(), st_b.numpy())

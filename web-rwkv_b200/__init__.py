@@ -438,6 +438,26 @@ def pack_v7(k_k, k_a, k, v, a, kk, n, eps):
                keep=(k_k, k_a, k, v, a, kk, n))
 
 
+def token_shift_lora(cursors, time_mix, bias, state, input, output, reversed):
+    """token_shift with factors f16(time_mix + bias): the add of the static factors and the shift in one launch."""
+    (pt, kt), (pb, kb), (ps, ks) = _v(time_mix), _v(bias), _v(state)
+    return _mk("wrk_op_token_shift_lora", _t(cursors), pt, pb, ps, _t(input), _t(output), int(reversed),
+               keep=(cursors, kt, kb, ks, input, output))
+
+
+def group_norm_gate(w, b, x, gate, output, eps, gate_act):
+    """output <- act(gate) * f16(group_norm(x)): group norm + copy + gate in one launch; x is left as it was."""
+    return _mk("wrk_op_group_norm_gate", _t(w), _t(b), _t(x), _t(gate), _t(output), ctypes.c_float(eps), int(gate_act),
+               keep=(w, b, x, gate, output))
+
+
+def channel_mix_add(cursors, state, r, v, x, residual, v7=False):
+    """channel_mix (or channel_mix_v7) and the add of its result to the residual stream in one launch."""
+    ps, ks = _v(state)
+    return _mk("wrk_op_channel_mix_add", _t(cursors), ps, _t(r) if r is not None else None, _t(v), _t(x), _t(residual), int(v7),
+               keep=(cursors, ks, r, v, x, residual))
+
+
 def nf4_table():
     t = (ctypes.c_float * 16)()
     check(lib().wrk_nf4_table(t))

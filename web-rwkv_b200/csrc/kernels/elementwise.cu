@@ -6,7 +6,8 @@
 // fit; the caller then launches the general kernel.
 //
 // Same reference shaders as support.cu: token_shift.wgsl, binary.wgsl (add / mul with activations), activation.wgsl,
-// blit.wgsl, channel_mix.wgsl / channel_mix_v7.wgsl (src/tensor/ops.rs:1393-1462, 1656-1795, 1566-1650, 2015-2060).
+// blit.wgsl, channel_mix.wgsl / channel_mix_v7.wgsl, layer_norm.wgsl (src/tensor/ops.rs:1393-1462, 1656-1795, 1566-1650,
+// 2015-2060, 407-470).
 #include "device.cuh"
 
 namespace wrk {
@@ -72,13 +73,14 @@ bool dense_as(const DView& v, T** p) {
 }
 bool fits32(size_t elements) { return elements / 8 < 0x7fffffffull; }
 
-// ---- binary.wgsl: out <- act_out(act_x(in) (+|*) act_y(out)); `in` has out's shape or is one row [C] -------------
+// ---- binary.wgsl: out <- act_out(act_x(in) (+|*) act_y(out)); `in` has out's shape, or one row [C] for the whole of
+// out (plane8 = 0), or one row per plane [C, 1, Z] (plane8 = vectors per plane of out) ------------------------------
 template <typename In, typename Out>
-__global__ void binary_vec_kernel(int is_mul, const In* in, Out* out, uint32_t c8, uint32_t total8, int in_row, int act_x,
-                                  int act_y, int act_out) {
+__global__ void binary_vec_kernel(int is_mul, const In* in, Out* out, uint32_t c8, uint32_t total8, int in_row, uint32_t plane8,
+                                  int act_x, int act_y, int act_out) {
     for (uint32_t o = blockIdx.x * blockDim.x + threadIdx.x; o < total8; o += gridDim.x * blockDim.x) {
         float x[8], y[8];
-        load8(in + (size_t)(in_row ? o % c8 : o) * 8, x);
+        load8(in + (size_t)(in_row ? (plane8 ? o / plane8 * c8 : 0u) + o % c8 : o) * 8, x);
         load8(out + (size_t)o * 8, y);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -96,12 +98,13 @@ bool binary_typed(int is_mul, const DView& input, const DView& output, int act_x
     if (!dense_as<In>(input, &in) || !dense_as<Out>(output, &out)) return false;
     const bool same = input.shape[1] == output.shape[1] && input.shape[2] == output.shape[2];
     const bool row = input.shape[1] == 1 && input.shape[2] == 1;
-    if (input.shape[0] != output.shape[0] || !(same || row)) return false;
+    const bool plane_rows = input.shape[1] == 1 && input.shape[2] == output.shape[2];
+    if (input.shape[0] != output.shape[0] || !(same || row || plane_rows)) return false;
     const size_t total = (size_t)output.shape[0] * output.shape[1] * output.shape[2];
     if (!fits32(total)) return false;
-    binary_vec_kernel<In, Out><<<vec_grid(total / 8), kVecThreads, 0, stream>>>(is_mul, in, out, output.shape[0] / 8,
-                                                                              (uint32_t)(total / 8), same ? 0 : 1, act_x, act_y,
-                                                                              act_out);
+    const uint32_t c8 = output.shape[0] / 8;
+    binary_vec_kernel<In, Out><<<vec_grid(total / 8), kVecThreads, 0, stream>>>(
+        is_mul, in, out, c8, (uint32_t)(total / 8), same ? 0 : 1, same || row ? 0u : c8 * output.shape[1], act_x, act_y, act_out);
     return true;
 }
 
@@ -146,6 +149,7 @@ struct ShiftVecArgs {
     const __half* in;  // [C, T]
     uint32_t c8, T, count;
     const __half* mix[kShiftMultiMax];  // factors of output i: one row [C] (mix_rows == 1) or one row per token
+    const __half* bias[kShiftMultiMax]; // null, or one row [C] added to the factors first (the sum rounded to f16)
     __half* out[kShiftMultiMax];        // [C, T] each
     uint32_t mix_rows;
     int reversed;
@@ -169,6 +173,12 @@ __global__ void token_shift_vec_kernel(const ShiftVecArgs a) {
             if (k >= a.count) break;
             float f[8], y[8];
             load8(a.mix[k] + (size_t)(a.mix_rows == 1 ? o % a.c8 : o) * 8, f);
+            if (a.bias[k] != nullptr) {
+                float b[8];
+                load8(a.bias[k] + (size_t)(o % a.c8) * 8, b);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = __half2float(__float2half_rn(b[i] + f[i]));
+            }
 #pragma unroll
             for (int i = 0; i < 8; ++i) y[i] = a.reversed ? mix_f(cur[i], prev[i], f[i]) : mix_f(prev[i], cur[i], f[i]);
             store8(a.out[k] + (size_t)o * 8, y);
@@ -177,9 +187,10 @@ __global__ void token_shift_vec_kernel(const ShiftVecArgs a) {
 }
 
 // ---- channel_mix.wgsl / channel_mix_v7.wgsl ----------------------------------------------------------------------
+// With `xres`, the residual stream takes the result as well: xres <- xres + x (x as stored, i.e. rounded to its type).
 template <typename T>
-__global__ void channel_mix_vec_kernel(const uint32_t* cursors, int wide, DView state, const T* r, const T* v, T* x, uint32_t c8,
-                                       uint32_t total8, int v7) {
+__global__ void channel_mix_vec_kernel(const uint32_t* cursors, int wide, DView state, const T* r, const T* v, T* x, T* xres,
+                                       uint32_t c8, uint32_t total8, int v7) {
     for (uint32_t o = blockIdx.x * blockDim.x + threadIdx.x; o < total8; o += gridDim.x * blockDim.x) {
         const uint32_t c = (o % c8) * 8, t = o / c8;
         const CursorD cu = cursor_at(cursors, wide, t);
@@ -200,6 +211,13 @@ __global__ void channel_mix_vec_kernel(const uint32_t* cursors, int wide, DView 
             }
         }
         store8(x + (size_t)o * 8, vv);
+        if (xres != nullptr) {
+            float res[8];
+            load8(xres + (size_t)o * 8, res);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) res[i] = (sizeof(T) == 2 ? __half2float(__float2half_rn(vv[i])) : vv[i]) + res[i];
+            store8(xres + (size_t)o * 8, res);
+        }
     }
 }
 
@@ -228,9 +246,11 @@ __device__ __forceinline__ void norm_store(const __half* w, const __half* b, siz
 }
 
 // Rows of up to 256 values: C / 8 lanes per row (a power of two), several rows per warp, sums by shuffles.
+// With `gated`, the normalised row is not stored in x but rounded to f16 (the copy into an f16 tensor), multiplied by
+// act(gate) and stored, rounded again, in `gated` (token-major [rows C] like x): group norm + blit + mul in one pass.
 template <typename T>
 __global__ void layer_norm_rows_kernel(const __half* w, const __half* b, const T* delta, T* src, T* x, uint32_t C, uint32_t rows,
-                                       uint32_t wrows, float eps) {
+                                       uint32_t wrows, float eps, const __half* gate, __half* gated, int gate_act) {
     const uint32_t lanes = C / 8;
     const uint32_t per_block = blockDim.x / lanes;
     for (uint32_t row0 = blockIdx.x * per_block; row0 < rows; row0 += gridDim.x * per_block) {  // uniform trip count per warp
@@ -249,7 +269,15 @@ __global__ void layer_norm_rows_kernel(const __half* w, const __half* b, const T
         const float dev = rsqrtf(m2 / (float)C + eps);
         if (live) {
             norm_store(w, b, (size_t)(row % wrows) * C + l * 8, mean, dev, v);
-            store8(x + at, v);
+            if (gated == nullptr) {
+                store8(x + at, v);
+            } else {
+                float g[8];
+                load8(gate + at, g);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = activate_f(gate_act, g[i]) * __half2float(__float2half_rn(v[i]));
+                store8(gated + at, v);
+            }
         }
     }
 }
@@ -312,7 +340,8 @@ bool layer_norm_typed(const __half* w, const __half* b, const void* delta, void*
     const uint32_t lanes = C / 8;
     if (C <= 256 && (lanes & (lanes - 1)) == 0) {
         const uint32_t per_block = 256 / lanes, blocks = (rows + per_block - 1) / per_block;
-        layer_norm_rows_kernel<T><<<blocks < 148u * 16u ? blocks : 148u * 16u, 256, 0, stream>>>(w, b, dp, sp, xp, C, rows, wrows, eps);
+        layer_norm_rows_kernel<T><<<blocks < 148u * 16u ? blocks : 148u * 16u, 256, 0, stream>>>(w, b, dp, sp, xp, C, rows, wrows, eps,
+                                                                                                   nullptr, nullptr, 0);
         return true;
     }
     if (lanes <= (uint32_t)kNormIters * 256) {
@@ -323,6 +352,27 @@ bool layer_norm_typed(const __half* w, const __half* b, const void* delta, void*
 }
 
 }  // namespace
+
+bool group_norm_gate_supported(const __half* w, const __half* b, const void* x, const __half* gate, const __half* out, uint32_t C) {
+    const uint32_t lanes = C / 8;
+    return C % 8 == 0 && C <= 256 && (lanes & (lanes - 1)) == 0 && aligned16(w) && aligned16(b) && aligned16(x) && aligned16(gate) &&
+           aligned16(out);
+}
+
+cudaError_t group_norm_gate(const __half* w, const __half* b, int dtype, void* x, uint32_t C, uint32_t rows, uint32_t wrows, float eps,
+                            const __half* gate, __half* out, int gate_act, cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    if (!group_norm_gate_supported(w, b, x, gate, out, C)) return cudaErrorInvalidValue;
+    const uint32_t per_block = 256 / (C / 8), blocks = (rows + per_block - 1) / per_block;
+    const uint32_t grid = blocks < 148u * 16u ? blocks : 148u * 16u;
+    if (dtype == WRK_F16)
+        layer_norm_rows_kernel<__half><<<grid, 256, 0, stream>>>(w, b, nullptr, static_cast<__half*>(x), static_cast<__half*>(x), C, rows,
+                                                                 wrows, eps, gate, out, gate_act);
+    else
+        layer_norm_rows_kernel<float><<<grid, 256, 0, stream>>>(w, b, nullptr, static_cast<float*>(x), static_cast<float*>(x), C, rows,
+                                                                wrows, eps, gate, out, gate_act);
+    return cudaGetLastError();
+}
 
 bool layer_norm_vec(const __half* w, const __half* b, int dtype, const void* delta, void* src, void* x, uint32_t C, uint32_t rows,
                     uint32_t wrows, float eps, cudaStream_t stream) {
@@ -366,10 +416,13 @@ bool blit_vec(const DView& input, const DView& output, cudaStream_t stream) {
     return false;
 }
 
-bool token_shift_vec(const uint32_t* cursors, int wide, const DView& time_mix, const DView& state, const DView& input,
-                     const DView& output, int reversed, cudaStream_t stream) {
+namespace {
+bool shift_vec_args(const uint32_t* cursors, int wide, const DView& time_mix, const DView* bias, const DView& state,
+                    const DView& input, const DView& output, int reversed, ShiftVecArgs* out_args) {
     const uint32_t C = output.shape[0], T = output.shape[1], Z = output.shape[2];
-    __half *in, *out, *mix;
+    __half *in, *out, *mix, *bp = nullptr;
+    if (bias != nullptr && (!dense_as<__half>(*bias, &bp) || bias->shape[0] != C || bias->shape[1] != 1 || bias->shape[2] != Z))
+        return false;
     if (Z == 0 || Z > kShiftMultiMax || !dense_as<__half>(input, &in) || !dense_as<__half>(output, &out) ||
         !dense_as<__half>(time_mix, &mix))
         return false;
@@ -389,9 +442,24 @@ bool token_shift_vec(const uint32_t* cursors, int wide, const DView& time_mix, c
     a.reversed = reversed;
     for (uint32_t z = 0; z < Z; ++z) {
         a.mix[z] = mix + (size_t)z * C * (one_row ? 1 : T);
+        a.bias[z] = bp ? bp + (size_t)z * C : nullptr;
         a.out[z] = out + (size_t)z * C * T;
     }
-    token_shift_vec_kernel<<<vec_grid((size_t)a.c8 * T), kVecThreads, 0, stream>>>(a);
+    *out_args = a;
+    return true;
+}
+}  // namespace
+
+bool token_shift_vec_fits(const DView& time_mix, const DView* bias, const DView& state, const DView& input, const DView& output) {
+    ShiftVecArgs a;
+    return shift_vec_args(nullptr, 0, time_mix, bias, state, input, output, 0, &a);
+}
+
+bool token_shift_vec(const uint32_t* cursors, int wide, const DView& time_mix, const DView* bias, const DView& state,
+                     const DView& input, const DView& output, int reversed, cudaStream_t stream) {
+    ShiftVecArgs a;
+    if (!shift_vec_args(cursors, wide, time_mix, bias, state, input, output, reversed, &a)) return false;
+    token_shift_vec_kernel<<<vec_grid((size_t)a.c8 * a.T), kVecThreads, 0, stream>>>(a);
     return true;
 }
 
@@ -417,17 +485,18 @@ bool token_shift_multi_vec(const ShiftMultiArgs& m, cudaStream_t stream) {
 }
 
 bool channel_mix_vec(const uint32_t* cursors, int wide, const DView& state, int dtype, const void* r, const void* v, void* x,
-                     uint32_t C, uint32_t T, int v7, cudaStream_t stream) {
-    if (C % 8 != 0 || !fits32((size_t)C * T) || !aligned16(v) || !aligned16(x) || (!v7 && !aligned16(r))) return false;
+                     void* xres, uint32_t C, uint32_t T, int v7, cudaStream_t stream) {
+    if (C % 8 != 0 || !fits32((size_t)C * T) || !aligned16(v) || !aligned16(x) || (!v7 && !aligned16(r)) || !aligned16(xres))
+        return false;
     const uint32_t total8 = C / 8 * T;
     if (dtype == WRK_F16)
         channel_mix_vec_kernel<__half><<<vec_grid(total8), kVecThreads, 0, stream>>>(
-            cursors, wide, state, static_cast<const __half*>(r), static_cast<const __half*>(v), static_cast<__half*>(x), C / 8,
-            total8, v7);
+            cursors, wide, state, static_cast<const __half*>(r), static_cast<const __half*>(v), static_cast<__half*>(x),
+            static_cast<__half*>(xres), C / 8, total8, v7);
     else
         channel_mix_vec_kernel<float><<<vec_grid(total8), kVecThreads, 0, stream>>>(
-            cursors, wide, state, static_cast<const float*>(r), static_cast<const float*>(v), static_cast<float*>(x), C / 8, total8,
-            v7);
+            cursors, wide, state, static_cast<const float*>(r), static_cast<const float*>(v), static_cast<float*>(x),
+            static_cast<float*>(xres), C / 8, total8, v7);
     return true;
 }
 

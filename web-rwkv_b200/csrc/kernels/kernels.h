@@ -129,11 +129,18 @@ bool layer_norm_vec(const __half* w, const __half* b, int dtype, const void* del
 bool binary_vec(int is_mul, const DView& input, const DView& output, int act_x, int act_y, int act_out, cudaStream_t stream);
 bool activate_vec(const DView& x, int act, cudaStream_t stream);
 bool blit_vec(const DView& input, const DView& output, cudaStream_t stream);
-bool token_shift_vec(const uint32_t* cursors, int wide, const DView& time_mix, const DView& state, const DView& input,
-                     const DView& output, int reversed, cudaStream_t stream);
+// `bias`: null, or one row [C, 1, Z] added to the factors first (the sum rounded to f16, as a separate add stores it)
+bool token_shift_vec(const uint32_t* cursors, int wide, const DView& time_mix, const DView* bias, const DView& state,
+                     const DView& input, const DView& output, int reversed, cudaStream_t stream);
+bool token_shift_vec_fits(const DView& time_mix, const DView* bias, const DView& state, const DView& input, const DView& output);
 bool token_shift_multi_vec(const ShiftMultiArgs& a, cudaStream_t stream);
+// `xres`: null, or the residual stream, which takes xres + x as well
 bool channel_mix_vec(const uint32_t* cursors, int wide, const DView& state, int dtype, const void* r, const void* v, void* x,
-                     uint32_t C, uint32_t T, int v7, cudaStream_t stream);
+                     void* xres, uint32_t C, uint32_t T, int v7, cudaStream_t stream);
+// group norm of rows of C <= 256 values + copy into f16 + out <- act(gate) * that, in one pass (x is left as it was)
+bool group_norm_gate_supported(const __half* w, const __half* b, const void* x, const __half* gate, const __half* out, uint32_t C);
+cudaError_t group_norm_gate(const __half* w, const __half* b, int dtype, void* x, uint32_t C, uint32_t rows, uint32_t wrows, float eps,
+                            const __half* gate, __half* out, int gate_act, cudaStream_t stream);
 struct PackV7Args {
     const __half *k_k, *k_a;  // [H * S]
     __half *k, *kk, *n;       // [S, H, T] (k updated in place), [S, H, T], [S, H, T, 4]

@@ -464,7 +464,7 @@ cudaError_t token_shift(const uint32_t* cursors, int wide, DView time_mix, DView
                         int reversed, cudaStream_t stream) {
     const size_t total = (size_t)output.shape[0] * output.shape[1] * output.shape[2];
     if (total == 0) return cudaSuccess;
-    if (token_shift_vec(cursors, wide, time_mix, state, input, output, reversed, stream)) return cudaGetLastError();
+    if (token_shift_vec(cursors, wide, time_mix, nullptr, state, input, output, reversed, stream)) return cudaGetLastError();
     token_shift_kernel<<<ew_grid(total), kEw, 0, stream>>>(cursors, wide, time_mix, state, input, output, reversed);
     return cudaGetLastError();
 }
@@ -496,7 +496,7 @@ cudaError_t channel_mix(const uint32_t* cursors, int wide, DView state, int dtyp
                         void* x, uint32_t C, uint32_t T, int v7, cudaStream_t stream) {
     const size_t total = (size_t)C * T;
     if (total == 0) return cudaSuccess;
-    if (channel_mix_vec(cursors, wide, state, dtype, r, v, x, C, T, v7, stream)) return cudaGetLastError();
+    if (channel_mix_vec(cursors, wide, state, dtype, r, v, x, nullptr, C, T, v7, stream)) return cudaGetLastError();
     channel_mix_kernel<<<ew_grid(total), kEw, 0, stream>>>(cursors, wide, state, dtype, r, v, x, C, T, v7);
     return cudaGetLastError();
 }

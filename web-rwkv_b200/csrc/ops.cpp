@@ -690,6 +690,95 @@ int32_t wrk_op_token_shift(wrk_tensor* cursors, const wrk_view* time_mix, const 
     return WRK_OK;
 }
 
+int32_t wrk_op_token_shift_lora(wrk_tensor* cursors, const wrk_view* time_mix, const wrk_view* bias, const wrk_view* state,
+                                wrk_tensor* input, wrk_tensor* output, int32_t reversed, wrk_op** out) {
+    REQ_NN(cursors, time_mix, time_mix->tensor, bias, bias->tensor, state, state->tensor, input, output, out);
+    REQ_DTYPE(state->tensor, WRK_F32, "state");
+    const Shape4 sh = output->shape;
+    const uint32_t C = sh[0], T = sh[1], count = sh[2];
+    WRK_TRY(check_shape("input", input->shape, C, T, 1, 1));
+    WRK_TRY(check_view("time_mix", time_mix, C, T, count, 1));
+    WRK_TRY(check_view("bias", bias, C, 1, count, 1));
+    WRK_TRY(check_view("state", state, C, state->shape[1], state->shape[2], 1));
+    WRK_TRY(check_cursors(cursors, T));
+    const uint32_t* cp = static_cast<const uint32_t*>(cursors->ptr());
+    const int wide = cursors_wide(cursors, T);
+    const DView tm = make_dview(*time_mix), bs = make_dview(*bias), st = make_dview(*state), in = make_dview(input),
+                o = make_dview(output);
+    WRK_REQUIRE(k::token_shift_vec_fits(tm, &bs, st, in, o), WRK_ERR_UNSUPPORTED,
+                "token_shift_lora takes dense f16 tensors of a multiple of 8 channels and at most %u planes", k::kShiftMultiMax);
+    *out = new_atom("token_shift_lora",
+                    [=](cudaStream_t s) {
+                        return k::token_shift_vec(cp, wide, tm, &bs, st, in, o, reversed, s) ? cudaGetLastError() : cudaErrorInvalidValue;
+                    },
+                    {cursors, time_mix->tensor, bias->tensor, state->tensor, input, output});
+    return WRK_OK;
+}
+
+int32_t wrk_op_group_norm_gate(wrk_tensor* w, wrk_tensor* b, wrk_tensor* x, wrk_tensor* gate, wrk_tensor* output, float eps,
+                               int32_t gate_act, wrk_op** out) {
+    REQ_NN(w, b, x, gate, output, out);
+    REQ_FLOAT(x, "x");
+    REQ_DTYPE(w, WRK_F16, "w");
+    REQ_DTYPE(b, WRK_F16, "b");
+    REQ_DTYPE(gate, WRK_F16, "gate");
+    REQ_DTYPE(output, WRK_F16, "output");
+    const Shape4 sh = x->shape;  // [S, H, T]
+    WRK_TRY(check_shape("x", sh, sh[0], sh[1], sh[2], 1));
+    WRK_TRY(check_shape("w", w->shape, sh[0], sh[1], 1, 1));
+    WRK_TRY(check_shape("b", b->shape, sh[0], sh[1], 1, 1));
+    WRK_REQUIRE(gate->len() == x->len() && output->len() == x->len(), WRK_ERR_SHAPE, "gate and output hold x's %zu values", x->len());
+    const __half* wp = static_cast<const __half*>(w->ptr());
+    const __half* bp = static_cast<const __half*>(b->ptr());
+    const __half* gp = static_cast<const __half*>(gate->ptr());
+    __half* op = static_cast<__half*>(output->ptr());
+    void* xp = x->ptr();
+    const int dt = x->dtype;
+    const uint32_t C = sh[0], rows = sh[1] * sh[2], wrows = sh[1];
+    WRK_REQUIRE(k::group_norm_gate_supported(wp, bp, xp, gp, op, C), WRK_ERR_UNSUPPORTED,
+                "group_norm_gate takes heads of 8, 16, ... 256 channels");
+    *out = new_atom("group_norm_gate",
+                    [=](cudaStream_t s) { return k::group_norm_gate(wp, bp, dt, xp, C, rows, wrows, eps, gp, op, gate_act, s); },
+                    {w, b, x, gate, output});
+    return WRK_OK;
+}
+
+int32_t wrk_op_channel_mix_add(wrk_tensor* cursors, const wrk_view* state, wrk_tensor* r, wrk_tensor* v, wrk_tensor* x,
+                               wrk_tensor* residual, int32_t v7, wrk_op** out) {
+    REQ_NN(cursors, state, state->tensor, v, x, residual, out);
+    REQ_FLOAT(x, "x");
+    REQ_DTYPE(v, x->dtype, "v");
+    REQ_DTYPE(residual, x->dtype, "residual");
+    REQ_DTYPE(state->tensor, WRK_F32, "state");
+    const Shape4 sh = x->shape;
+    WRK_TRY(check_shape("x", sh, sh[0], sh[1], 1, 1));
+    WRK_TRY(check_shape("v", v->shape, sh[0], sh[1], 1, 1));
+    WRK_TRY(check_shape("residual", residual->shape, sh[0], sh[1], 1, 1));
+    if (!v7) {
+        REQ_NN(r);
+        REQ_DTYPE(r, x->dtype, "r");
+        WRK_TRY(check_shape("r", r->shape, sh[0], sh[1], 1, 1));
+    }
+    WRK_TRY(check_view("state", state, sh[0], 1, state->shape[2], 1));
+    WRK_TRY(check_cursors(cursors, sh[1]));
+    WRK_REQUIRE(sh[0] % 8 == 0, WRK_ERR_UNSUPPORTED, "channel_mix_add takes a multiple of 8 channels");
+    const uint32_t* cp = static_cast<const uint32_t*>(cursors->ptr());
+    const int wide = cursors_wide(cursors, sh[1]);
+    DView st = make_dview(*state);
+    const void* rp = r ? r->ptr() : nullptr;
+    const void* vp = v->ptr();
+    void* xp = x->ptr();
+    void* res = residual->ptr();
+    const int dt = x->dtype;
+    const uint32_t C = sh[0], T = sh[1];
+    *out = new_atom("channel_mix_add",
+                    [=](cudaStream_t s) {
+                        return k::channel_mix_vec(cp, wide, st, dt, rp, vp, xp, res, C, T, v7, s) ? cudaGetLastError() : cudaErrorInvalidValue;
+                    },
+                    {cursors, state->tensor, r, v, x, residual});
+    return WRK_OK;
+}
+
 static int32_t channel_mix_common(const char* name, int v7, wrk_tensor* cursors, const wrk_view* state, wrk_tensor* r,
                                   wrk_tensor* v, wrk_tensor* x, wrk_op** out) {
     REQ_NN(cursors, state, state->tensor, v, x, out);

@@ -422,6 +422,7 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
     // Runs of elementwise ops as one launch each (bit-identical results) unless the op list is to be the reference's,
     // op for op: with hooks, which sit between those ops, or in strict mode.
     const bool merged = bd->fused && bd->hooks.empty();
+    const bool merged8 = merged && C % 8 == 0 && (!sp.on || sp.Cl % 8 == 0);  // ops that take eight channels per thread
     if (merged) {
         ADD(wrk_op_layer_norm_copy(L.att_ln.w, L.att_ln.b, nullptr, B["x"], B["att_x"], LN_EPS, &_o));
     } else {
@@ -445,9 +446,14 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
         HOOK(POST_ATT_TOKEN_SHIFT_ADAPT_ACTIVATE);
         WRK_TRY(matmul(ops, L.time_mix_w2, V(B["time_mix_t"]), V(B["time_mix"]), WRK_ACT_NONE, turbo));
         HOOK(POST_ATT_TOKEN_SHIFT_ADAPT);
-        WRK_TRY(add(ops, V(L.time_mix), V(B["time_mix"])));
-        HOOK(PRE_ATT_GATED_TOKEN_SHIFT);
-        WRK_TRY(token_shift(ops, cursors, V(B["time_mix"]), state_att(bd, index, S), B["att_x"], B["att_sx"], true));
+        if (merged8) {
+            const wrk_view tm = V(B["time_mix"]), bias = V(L.time_mix), st = state_att(bd, index, S);
+            ADD(wrk_op_token_shift_lora(cursors, &tm, &bias, &st, B["att_x"], B["att_sx"], true, &_o));
+        } else {
+            WRK_TRY(add(ops, V(L.time_mix), V(B["time_mix"])));
+            HOOK(PRE_ATT_GATED_TOKEN_SHIFT);
+            WRK_TRY(token_shift(ops, cursors, V(B["time_mix"]), state_att(bd, index, S), B["att_x"], B["att_sx"], true));
+        }
         HOOK(POST_ATT_GATED_TOKEN_SHIFT);
         HOOK(PRE_ATT_LINEAR);
         WRK_TRY(matmul(ops, L.att_w_k, Vz(B["att_sx"], 1), V(B["att_k"]), WRK_ACT_NONE, turbo));
@@ -460,9 +466,11 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
         HOOK(POST_ATT_TIME_DECAY_ADAPT_ACTIVATE);
         WRK_TRY(matmul(ops, L.time_decay_w2, V(B["att_w"]), V(B["time_decay"]), WRK_ACT_NONE, turbo));
         HOOK(POST_ATT_TIME_DECAY_ADAPT);
-        WRK_TRY(add(ops, V(L.time_decay), V(B["time_decay"])));
-        HOOK(PRE_ATT_TIME_DECAY_ACTIVATE);
-        {
+        if (merged) {  // the sum stays f32 between the two ops: one op with the activation on its output is the same
+            WRK_TRY(add(ops, V(L.time_decay), V(B["time_decay"]), WRK_ACT_STABLE_EXP));
+        } else {
+            WRK_TRY(add(ops, V(L.time_decay), V(B["time_decay"])));
+            HOOK(PRE_ATT_TIME_DECAY_ACTIVATE);
             const wrk_view td = V(B["time_decay"]);
             ADD(wrk_op_activate(&td, WRK_ACT_STABLE_EXP, &_o));
         }
@@ -496,11 +504,13 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
         if (v6) ADD(wrk_op_time_mix_v6(cursors, time_decay, time_first, &st, att_k, att_v, att_r, aux_x, &_o));
         else ADD(wrk_op_time_mix_v5(cursors, time_decay, time_first, &st, att_k, att_v, att_r, aux_x, &_o));
     }
-    ADD(wrk_op_group_norm(L.gn.w, L.gn.b, aux_x, GN_EPS, &_o));
-    WRK_TRY(blit(ops, V(B["aux_x"]), V(att_loc)));
-    HOOK(POST_ATT_TIME_MIX);
-    HOOK(PRE_ATT_GATE);
-    {
+    if (merged8 && S % 8 == 0 && S <= 256 && (S & (S - 1)) == 0) {
+        ADD(wrk_op_group_norm_gate(L.gn.w, L.gn.b, aux_x, B["att_g"], att_loc, GN_EPS, WRK_ACT_SILU, &_o));
+    } else {
+        ADD(wrk_op_group_norm(L.gn.w, L.gn.b, aux_x, GN_EPS, &_o));
+        WRK_TRY(blit(ops, V(B["aux_x"]), V(att_loc)));
+        HOOK(POST_ATT_TIME_MIX);
+        HOOK(PRE_ATT_GATE);
         const wrk_view g = V(B["att_g"]), x = V(att_loc);
         ADD(wrk_op_mul_activate(&g, &x, WRK_ACT_SILU, WRK_ACT_NONE, WRK_ACT_NONE, &_o));
     }
@@ -540,10 +550,14 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
     HOOK(PRE_FFN_CHANNEL_MIX);
     {
         const wrk_view st = state_ffn(bd, index, S);
-        ADD(wrk_op_channel_mix(cursors, &st, B["ffn_r"], B["ffn_v"], B["ffn_x"], &_o));
+        if (merged8) {
+            ADD(wrk_op_channel_mix_add(cursors, &st, B["ffn_r"], B["ffn_v"], B["ffn_x"], B["x"], 0, &_o));
+        } else {
+            ADD(wrk_op_channel_mix(cursors, &st, B["ffn_r"], B["ffn_v"], B["ffn_x"], &_o));
+            HOOK(POST_FFN_CHANNEL_MIX);
+            WRK_TRY(add(ops, V(B["ffn_x"]), V(B["x"])));
+        }
     }
-    HOOK(POST_FFN_CHANNEL_MIX);
-    WRK_TRY(add(ops, V(B["ffn_x"]), V(B["x"])));
     HOOK(POST_FFN);
     if ((index + 1) % bd->model->rescale == 0) ADD(wrk_op_affine(B["x"], 0.5f, 0.0f, &_o));
     return WRK_OK;
@@ -685,10 +699,14 @@ int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, 
     HOOK(PRE_FFN_CHANNEL_MIX);
     {
         const wrk_view st = state_ffn(bd, index, S);
-        ADD(wrk_op_channel_mix_v7(cursors, &st, B["ffn_v"], B["ffn_x"], &_o));
+        if (merged && C % 8 == 0) {
+            ADD(wrk_op_channel_mix_add(cursors, &st, nullptr, B["ffn_v"], B["ffn_x"], B["x"], 1, &_o));
+        } else {
+            ADD(wrk_op_channel_mix_v7(cursors, &st, B["ffn_v"], B["ffn_x"], &_o));
+            HOOK(POST_FFN_CHANNEL_MIX);
+            WRK_TRY(add(ops, V(B["ffn_x"]), V(B["x"])));
+        }
     }
-    HOOK(POST_FFN_CHANNEL_MIX);
-    WRK_TRY(add(ops, V(B["ffn_x"]), V(B["x"])));
     HOOK(POST_FFN);
     if ((index + 1) % bd->model->rescale == 0) ADD(wrk_op_affine(B["x"], 0.5f, 0.0f, &_o));
     return WRK_OK;
