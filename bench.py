@@ -470,9 +470,10 @@ def sweep_matmul(wrk, ctx, rng, kind, K, M, N, reps, matrices, single):
           flush=True)
 
 
-def sweep_wkv(wrk, ctx, rng, version, H, T, reps):
-    """`time_mix_v7` (fp16 r, w, n, x) or `time_mix_v6` (f32 k, v, r, x) on one sequence of T tokens: H heads of
-    64 x 64 f32 state.  The state grows stale over the repetitions, which does not change the work."""
+def sweep_wkv(wrk, ctx, rng, version, H, T, reps, blocks=False):
+    """`time_mix_v7` (fp16 r, w, n, x) or `time_mix_v6` (f32 k, v, r, x; `blocks`: in blocks of 16 tokens) on one
+    sequence of T tokens: H heads of 64 x 64 f32 state.  The state grows stale over the repetitions, which does not
+    change the work."""
     S = 64
     C = S * H
     cursors = ctx.from_numpy(np.array([[0, 0, T]] * T, dtype=np.uint32))  # wide cursors: (batch, token, len) per token
@@ -492,7 +493,10 @@ def sweep_wkv(wrk, ctx, rng, version, H, T, reps):
         k, v, r, x = (ctx.from_numpy(rng.standard_normal((T, H, S)).astype(f) * 0.5) for _ in range(4))
         decay = ctx.from_numpy(np.exp(-np.exp(rng.uniform(-6, 1, (T, H, S)))).astype(f))
         first = ctx.from_numpy(rng.uniform(-1, 1, (H, S)).astype(f))
-        op = wrk.time_mix_v6(cursors, decay, first, state.view(y=(0, S + 1)), k, v, r, x)
+        if blocks:
+            op = wrk.time_mix_blocks(True, cursors, decay, first, state.view(y=(0, S + 1)), k, v, r, x)
+        else:
+            op = wrk.time_mix_v6(cursors, decay, first, state.view(y=(0, S + 1)), k, v, r, x)
         nbytes = 2.0 * C * S * 4 + T * C * 4.0 * 6
     cmd = ctx.encode(wrk.op_list([op]), use_graph=True)
     for _ in range(3):
@@ -503,7 +507,7 @@ def sweep_wkv(wrk, ctx, rng, version, H, T, reps):
         cmd.submit()
     us = ctx.timer_stop() * 1e3 / reps
     flops = (10.0 if version == 7 else 7.0) * C * S * T
-    print(f"time_mix_v{version} H={H} T={T}: {us:8.1f} us  {us / T:6.2f} us/token  {nbytes / us / 1e3:8.1f} GB/s  "
+    print(f"time_mix_{'blocks' if blocks else 'v%d' % version} H={H} T={T}: {us:8.1f} us  {us / T:6.2f} us/token  {nbytes / us / 1e3:8.1f} GB/s  "
           f"{flops / us / 1e6:6.2f} TFLOP/s", flush=True)
 
 
@@ -515,6 +519,8 @@ def sweep(args):
         for version in (7, 6):
             for T in (1, 2, 8, 32, 64, 128, 256, 512):
                 sweep_wkv(wrk, ctx, rng, version, 64, T, args.reps)
+        for T in (16, 32, 64, 128, 256, 512, 2048):
+            sweep_wkv(wrk, ctx, rng, 6, 64, T, args.reps, blocks=True)
         return
     shapes = [tuple(int(v) for v in s.split(",")) for s in (args.shape or ["2048,2048", "2560,8960", "4096,4096"])]
     for kind in args.kind.split(","):

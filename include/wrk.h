@@ -174,6 +174,12 @@ int32_t wrk_op_time_mix_v5(wrk_tensor* cursors, wrk_tensor* time_decay, wrk_tens
 int32_t wrk_op_time_mix_v6(wrk_tensor* cursors, wrk_tensor* time_decay, wrk_tensor* time_first,
                            const wrk_view* state, wrk_tensor* k, wrk_tensor* v, wrk_tensor* r, wrk_tensor* x,
                            wrk_op** out);
+/* No counterpart in the reference: time_mix_v5 (per_token_decay == 0) or time_mix_v6 (!= 0) with the same arguments and
+ * the same result up to fp32 summation order, computed in blocks of 16 tokens (the recurrence unrolled into three small
+ * matrix products per block, so that the tokens of a block do not wait for one another).  Heads of 64 channels;
+ * WRK_ERR_UNSUPPORTED otherwise.  The runtime uses it for jobs of more than 8 tokens outside strict mode. */
+int32_t wrk_op_time_mix_blocks(int32_t per_token_decay, wrk_tensor* cursors, wrk_tensor* time_decay, wrk_tensor* time_first,
+                               const wrk_view* state, wrk_tensor* k, wrk_tensor* v, wrk_tensor* r, wrk_tensor* x, wrk_op** out);
 /* TensorOp::time_mix_v7(cursors, state, r, w, n, x), src/tensor/ops.rs:1679-1741 */
 int32_t wrk_op_time_mix_v7(wrk_tensor* cursors, const wrk_view* state, wrk_tensor* r, wrk_tensor* w,
                            wrk_tensor* n, wrk_tensor* x, wrk_op** out);

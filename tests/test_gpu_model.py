@@ -124,10 +124,19 @@ def test_merged_elementwise_launches_are_bit_identical_to_the_op_list(ctx, confi
         results.append((outs, [bundle.state_back(b) for b in range(2)], ctx.launch_count() - before))
     (a, sa, la), (b, sb, lb) = results
     assert len(a) == len(b)
+    # v7: bit for bit.  v5 / v6 jobs of more than 8 tokens also take the WKV recurrence in blocks of 16 tokens, which
+    # sums in another order (the merged elementwise ops are compared bit for bit one by one in test_gpu_support.py)
+    exact = config == "v7-tiny"
     for i, (x, y) in enumerate(zip(a, b)):
-        assert np.array_equal(x, y), (i, float(np.abs(x - y).max()) if x.size else None)
+        if exact:
+            assert np.array_equal(x, y), (i, float(np.abs(x - y).max()) if x.size else None)
+        elif x.size:
+            assert_close(x, y, f"logits {i}")
     for x, y in zip(sa, sb):
-        assert np.array_equal(x, y), float(np.abs(x - y).max())
+        if exact:
+            assert np.array_equal(x, y), float(np.abs(x - y).max())
+        else:
+            assert_state_close(x, y, "state")
     assert lb - la == saved * model.info.num_layer, (la, lb)
 
 

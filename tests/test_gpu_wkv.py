@@ -24,7 +24,7 @@ def _cursors(seqs, wide):
     return oracle.pack_cursors(cur, wide=wide), tok
 
 
-def _v56_case(wrk, ctx, version, H, seqs, B, wide, dtype=np.float32, seed=0, S=S):
+def _v56_case(wrk, ctx, version, H, seqs, B, wide, dtype=np.float32, seed=0, S=S, blocks=False):
     rng = np.random.default_rng(seed)
     C = S * H
     cursors, T = _cursors(seqs, wide)
@@ -42,6 +42,8 @@ def _v56_case(wrk, ctx, version, H, seqs, B, wide, dtype=np.float32, seed=0, S=S
     t_state = ctx.from_numpy(state)
     t_x = ctx.from_numpy(x)
     fn = wrk.time_mix_v6 if version == 6 else wrk.time_mix_v5
+    if blocks:
+        fn = lambda *args: wrk.time_mix_blocks(version == 6, *args)
     op = fn(ctx.from_numpy(cursors), ctx.from_numpy(w), ctx.from_numpy(u), t_state.view(y=(0, S + 1)),
             ctx.from_numpy(k), ctx.from_numpy(v), ctx.from_numpy(r), t_x)
     ctx.run(op)
@@ -98,6 +100,29 @@ def test_v56_other_head_sizes(wrk, ctx, version, head_size):
     gx, gs, rx, rs = _v56_case(wrk, ctx, version, 3, [(0, 37), (1, 16), (2, 1)], 3, True, seed=40 + head_size, S=head_size)
     assert_close(gx, rx, "x")
     assert_close(gs, rs, "state")
+
+
+@pytest.mark.parametrize("version", [5, 6])
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_v56_blocks_of_16_tokens(wrk, ctx, version, dtype):
+    """The block form against the oracle's serial recurrence: runs shorter than, equal to and longer than a block, an idle
+    slot, single tokens."""
+    gx, gs, rx, rs = _v56_case(wrk, ctx, version, 5, [(1, 130), (0, 16), (3, 1), (4, 47)], 5, True, dtype=dtype, seed=60 + version,
+                               blocks=True)
+    assert_close(gx, rx, "x")
+    assert_close(gs, rs, "state")
+    assert np.array_equal(gs[2], rs[2])
+    assert np.array_equal(gs[:, S + 1], rs[:, S + 1])
+
+
+def test_v6_blocks_long_run_with_strong_decay(wrk, ctx):
+    # 2048 tokens; decays down to exp(-e) per token, so that products over a block underflow towards zero
+    gx, gs, rx, rs = _v56_case(wrk, ctx, 6, 2, [(0, 2048)], 1, True, seed=63, blocks=True)
+    assert_close(gx, rx, "x")
+    assert_close(gs, rs, "state")
+    gx, gs, rx, rs = _v56_case(wrk, ctx, 6, 2, [(0, 256)], 1, False, seed=64, blocks=True)  # packed cursors: len wraps
+    assert_close(gx, rx, "x packed")
+    assert_close(gs, rs, "state packed")
 
 
 def test_v6_long_runs_cross_chunks(wrk, ctx):

@@ -438,6 +438,13 @@ def pack_v7(k_k, k_a, k, v, a, kk, n, eps):
                keep=(k_k, k_a, k, v, a, kk, n))
 
 
+def time_mix_blocks(per_token_decay, cursors, time_decay, time_first, state, k, v, r, x):
+    """time_mix_v5 / time_mix_v6 computed in blocks of 16 tokens (heads of 64 channels)."""
+    ps, ks = _v(state)
+    return _mk("wrk_op_time_mix_blocks", int(per_token_decay), _t(cursors), _t(time_decay), _t(time_first), ps, _t(k), _t(v), _t(r),
+               _t(x), keep=(cursors, time_decay, time_first, ks, k, v, r, x))
+
+
 def token_shift_lora(cursors, time_mix, bias, state, input, output, reversed):
     """token_shift with factors f16(time_mix + bias): the add of the static factors and the shift in one launch."""
     (pt, kt), (pb, kb), (ps, ks) = _v(time_mix), _v(bias), _v(state)

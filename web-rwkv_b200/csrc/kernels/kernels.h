@@ -87,6 +87,8 @@ struct WkvArgs {
     int32_t* status;          // device status word
 };
 cudaError_t time_mix_v56(const WkvArgs& a, cudaStream_t stream);
+bool time_mix_v56_chunked_supported(const WkvArgs& a);
+cudaError_t time_mix_v56_chunked(const WkvArgs& a, cudaStream_t stream);
 cudaError_t time_mix_v7(const WkvArgs& a, cudaStream_t stream);
 cudaError_t time_mix_v4(const uint32_t* cursors, int wide, const float* time_decay, const float* time_first, DView state,
                         int dtype, const void* k, const void* v, const void* r, void* x, uint32_t C, uint32_t T,

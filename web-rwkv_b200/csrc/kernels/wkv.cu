@@ -184,6 +184,222 @@ __global__ void __launch_bounds__((S / 4) * (S / CW)) time_mix_v56_kernel(const 
             static_cast<float*>(a.state.base)[a.state.index(c0 + CW * cg + cc, 1 + 4 * rg + r, slot)] = st[r][cc];
 }
 
+// ---- v5 / v6 in blocks of 16 tokens ("chunk-parallel") ------------------------------------------------------------
+// The recurrence  y_t = r_t . (u k_t v_t^T + S_(t-1)),  S_t = diag(w_t) S_(t-1) + k_t v_t^T  unrolled over a block of
+// L = 16 tokens that starts from state S0 (rows i = key index, columns j = value index, per head):
+//   y_t   = (r_t Pe_t) S0  +  sum_(s<=t) A[t][s] v_s,      S_end = diag(Pe_L) S0 + sum_s (k_s E_s) v_s^T
+//   Pe_t  = prod_(m<t) w_m   (Pe_0 = 1),   E_s = prod_(m>s) w_m,
+//   A[t][s] = sum_i r_t[i] k_s[i] prod_(s<m<t) w_m[i]  (s < t),   A[t][t] = sum_i r_t[i] u[i] k_t[i].
+// Every product of decays is taken forwards (no division, nothing can overflow; what underflows is a contribution that
+// has decayed to nothing).  The work of a block is then three small matrix products - [16 x 64][64 x 64] for the state's
+// share of y, [16 x 16][16 x 64] for the block's own tokens and [64 x 16][16 x 64] for the new state - in which no
+// element waits for another: 4 x 4 register tiles in fp32 on the CUDA cores, operands from shared memory.  The serial
+// kernel above spends about 650 cycles on a token's chain of dependent steps; this one about 130 per token.
+// One CTA of 256 threads per (head of 64 channels, batch slot); the state tile of a thread stays in registers from
+// block to block; the tokens' rows are staged a block ahead as in the serial kernel.
+constexpr int kBlockTokens = 16;
+constexpr int kQtStride = 20;  // row stride of Qt in floats: 16-byte rows whose vector stores do not collide
+constexpr size_t kChunkedSmemFloats = 2 * 4 * kBlockTokens * 64 + 64 * kQtStride + kBlockTokens * 64 + kBlockTokens * kBlockTokens + 64 +
+                                      64 * 64 + 4 * kBlockTokens * 64;
+__global__ void __launch_bounds__(256) time_mix_v56_chunked_kernel(const WkvArgs a) {
+    constexpr int S = 64, L = kBlockTokens;
+    enum { IN_K = 0, IN_R = 1, IN_W = 2, IN_V = 3 };
+    extern __shared__ __align__(16) float wkv_smem[];
+    float(*sin)[4][L][S] = reinterpret_cast<float(*)[4][L][S]>(wkv_smem);              // [2]: staged k, r, w, v
+    float(*Qt)[kQtStride] = reinterpret_cast<float(*)[kQtStride]>(wkv_smem + 2 * 4 * L * S);  // [S]: Qt[i][t] = r_t[i] Pe_t[i]
+    float(*Kd)[S] = reinterpret_cast<float(*)[S]>(&Qt[S][0]);                            // [L]: Kd[s][i] = k_s[i] E_s[i]
+    float(*At)[L] = reinterpret_cast<float(*)[L]>(&Kd[L][0]);                            // [L]: At[s][t] = A[t][s], 0 for s > t
+    float* PL = &At[L][0];                                                               // [S]: the block's whole decay
+    float(*S0)[S] = reinterpret_cast<float(*)[S]>(PL + S);                               // [S]: the state at the block's start
+    float* red = &S0[S][0];  // [4][L][S] partial outputs of the four key ranges; before that [L s][L t][16] partials of A
+    __shared__ RunScratch run;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t h = blockIdx.x, slot = blockIdx.y, C = a.S * a.H, c0 = h * S;
+    const uint32_t ri = tid / 16, cj = tid % 16;               // state tile: rows 4 ri .., columns 4 cj ..
+    const uint32_t tg = tid / 64, tt = (tid % 64) / 16;        // output tile: key range 16 tg .., tokens 4 tt .., columns 4 cj ..
+
+    uint32_t start, count, carry;
+    if (!find_run(a.cursors, a.wide, a.T, slot, &run, start, count, &carry)) return;
+    if (carry != 0 && tid < S)  // the carry row takes the layer input of the run's closing token (nothing here reads the row)
+        static_cast<float*>(a.state.base)[a.state.index(c0 + tid, 0, slot)] = dload(a.x, a.dtype, (size_t)(carry - 1) * C + c0 + tid);
+
+    float st[4][4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc)
+            st[r][cc] = static_cast<const float*>(a.state.base)[a.state.index(c0 + 4 * cj + cc, 1 + 4 * ri + r, slot)];
+    float u4[4];  // time_first of the keys this thread takes in the A partials: 4 (tid % 16) ..
+#pragma unroll
+    for (int e = 0; e < 4; ++e) u4[e] = a.time_first[c0 + 4 * cj + e];
+
+    // staging: thread (tensor = tid / 64, channel = tid % 64) takes the block's 16 tokens of its tensor and channel;
+    // past the run's end k, r, v are 0 and w is 1 (such a token changes nothing)
+    float stage[L];
+    const uint32_t tensor = tid / S, ch = tid % S;
+    auto load_chunk = [&](uint32_t chunk) {
+#pragma unroll
+        for (int n = 0; n < L; ++n) {
+            const uint32_t m = chunk * L + n;
+            const size_t ti = (size_t)(start + m) * C + c0 + ch;
+            float v = tensor == IN_W ? 1.0f : 0.0f;
+            if (m < count) {
+                if (tensor == IN_K) v = dload(a.k, a.dtype, ti);
+                else if (tensor == IN_R) v = dload(a.r, a.dtype, ti);
+                else if (tensor == IN_W) v = a.per_token_decay ? a.time_decay[ti] : a.time_decay[c0 + ch];
+                else v = dload(a.v, a.dtype, ti);
+            }
+            stage[n] = v;
+        }
+    };
+    auto store_chunk = [&](int buf) {
+#pragma unroll
+        for (int n = 0; n < L; ++n) sin[buf][tensor][n][ch] = stage[n];
+    };
+    const uint32_t chunks = (count + L - 1) / L;
+    load_chunk(0);
+    store_chunk(0);
+    __syncthreads();
+
+    for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
+        const int buf = chunk & 1;
+        const bool more = chunk + 1 < chunks;
+        if (more) load_chunk(chunk + 1);  // in flight while this block is computed
+        const float(*sk)[S] = sin[buf][IN_K];
+        const float(*sr)[S] = sin[buf][IN_R];
+        const float(*sw)[S] = sin[buf][IN_W];
+        const float(*sv)[S] = sin[buf][IN_V];
+
+        // (1) the state tile to shared memory; the decay products; the partial sums of A
+#pragma unroll
+        for (int r = 0; r < 4; ++r) *reinterpret_cast<float4*>(&S0[4 * ri + r][4 * cj]) = make_float4(st[r][0], st[r][1], st[r][2], st[r][3]);
+        {
+            // thread (key i = tid % 64, quarter tq = tid / 64): Qt[i][4 tq ..], Kd[4 tq ..][i]; quarter 3 ends on the whole product
+            const uint32_t i = tid % S, tq = tid / S;
+            float pe = 1.0f;
+            for (uint32_t t = 0; t < 4 * tq; ++t) pe *= sw[t][i];
+            float q[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                q[e] = sr[4 * tq + e][i] * pe;
+                pe *= sw[4 * tq + e][i];
+            }
+            *reinterpret_cast<float4*>(&Qt[i][4 * tq]) = make_float4(q[0], q[1], q[2], q[3]);
+            if (tq == 3) PL[i] = pe;
+            float en = 1.0f;
+            for (uint32_t s2 = L - 1; s2 > 4 * tq + 3; --s2) en *= sw[s2][i];
+#pragma unroll
+            for (int e = 3; e >= 0; --e) {
+                Kd[4 * tq + e][i] = sk[4 * tq + e][i] * en;
+                en *= sw[4 * tq + e][i];
+            }
+        }
+        {
+            // thread (s = tid / 16, keys 4 cj ..): its share of A[t][s] for t = s .. L - 1, into red[s][t][cj]
+            const uint32_t s2 = tid / 16;
+            const float4 kq = *reinterpret_cast<const float4*>(&sk[s2][4 * cj]);
+            const float kk[4] = {kq.x, kq.y, kq.z, kq.w};
+            float d[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+            for (uint32_t t = 0; t < s2; ++t) red[(s2 * L + t) * 16 + cj] = 0.0f;
+            {
+                const float4 rq = *reinterpret_cast<const float4*>(&sr[s2][4 * cj]);
+                red[(s2 * L + s2) * 16 + cj] = (rq.x * kk[0] * u4[0] + rq.y * kk[1] * u4[1]) + (rq.z * kk[2] * u4[2] + rq.w * kk[3] * u4[3]);
+            }
+            for (uint32_t t = s2 + 1; t < L; ++t) {
+                const float4 rq = *reinterpret_cast<const float4*>(&sr[t][4 * cj]);
+                const float4 wq = *reinterpret_cast<const float4*>(&sw[t][4 * cj]);
+                red[(s2 * L + t) * 16 + cj] = (rq.x * kk[0] * d[0] + rq.y * kk[1] * d[1]) + (rq.z * kk[2] * d[2] + rq.w * kk[3] * d[3]);
+                d[0] *= wq.x, d[1] *= wq.y, d[2] *= wq.z, d[3] *= wq.w;
+            }
+        }
+        __syncthreads();
+        // (2) A[t][s] summed over the 16 key groups: thread (s, t) = (tid / 16, tid % 16)
+        {
+            const float4* p4 = reinterpret_cast<const float4*>(red + (size_t)tid * 16);
+            const float4 p0 = p4[0], p1 = p4[1], p2 = p4[2], p3 = p4[3];
+            At[tid / 16][tid % 16] = ((p0.x + p0.y) + (p0.z + p0.w)) + ((p1.x + p1.y) + (p1.z + p1.w)) +
+                                     (((p2.x + p2.y) + (p2.z + p2.w)) + ((p3.x + p3.y) + (p3.z + p3.w)));
+        }
+        __syncthreads();
+        // (3) the outputs of tokens 4 tt .. and columns 4 cj .., summed over keys 16 tg .. (the state's share) and over the
+        // block's tokens 4 tg .. (their own share); then the new state tile
+        {
+            float acc[4][4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) acc[e][cc] = 0.0f;
+#pragma unroll 4
+            for (uint32_t i = 16 * tg; i < 16 * tg + 16; ++i) {
+                const float4 q4 = *reinterpret_cast<const float4*>(&Qt[i][4 * tt]);
+                const float4 s4 = *reinterpret_cast<const float4*>(&S0[i][4 * cj]);
+                const float qv[4] = {q4.x, q4.y, q4.z, q4.w}, sv4[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) acc[e][cc] = fmaf(qv[e], sv4[cc], acc[e][cc]);
+            }
+#pragma unroll
+            for (uint32_t s2 = 4 * tg; s2 < 4 * tg + 4; ++s2) {
+                const float4 a4 = *reinterpret_cast<const float4*>(&At[s2][4 * tt]);
+                const float4 v4 = *reinterpret_cast<const float4*>(&sv[s2][4 * cj]);
+                const float av[4] = {a4.x, a4.y, a4.z, a4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) acc[e][cc] = fmaf(av[e], vv[cc], acc[e][cc]);
+            }
+            // red is free again: every thread has passed the barrier that follows its last read in (2)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                *reinterpret_cast<float4*>(&red[((size_t)tg * L + 4 * tt + e) * S + 4 * cj]) = make_float4(acc[e][0], acc[e][1], acc[e][2], acc[e][3]);
+        }
+        {
+            const float4 pl = *reinterpret_cast<const float4*>(&PL[4 * ri]);
+            const float plv[4] = {pl.x, pl.y, pl.z, pl.w};
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) st[r][cc] *= plv[r];
+#pragma unroll 4
+            for (uint32_t s2 = 0; s2 < L; ++s2) {
+                const float4 k4 = *reinterpret_cast<const float4*>(&Kd[s2][4 * ri]);
+                const float4 v4 = *reinterpret_cast<const float4*>(&sv[s2][4 * cj]);
+                const float kv[4] = {k4.x, k4.y, k4.z, k4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) st[r][cc] = fmaf(kv[r], vv[cc], st[r][cc]);
+            }
+        }
+        __syncthreads();
+        // (4) token t = tid / 16, columns 4 cj ..: the four key ranges' partial outputs
+        {
+            const uint32_t t = tid / 16, m = chunk * L + t;
+            if (m < count) {
+                float4 y = *reinterpret_cast<const float4*>(&red[((size_t)0 * L + t) * S + 4 * cj]);
+#pragma unroll
+                for (int g = 1; g < 4; ++g) {
+                    const float4 p = *reinterpret_cast<const float4*>(&red[((size_t)g * L + t) * S + 4 * cj]);
+                    y.x += p.x, y.y += p.y, y.z += p.z, y.w += p.w;
+                }
+                const size_t ti = (size_t)(start + m) * C + c0 + 4 * cj;
+                dstore(a.x, a.dtype, ti, y.x);
+                dstore(a.x, a.dtype, ti + 1, y.y);
+                dstore(a.x, a.dtype, ti + 2, y.z);
+                dstore(a.x, a.dtype, ti + 3, y.w);
+            }
+        }
+        if (more) store_chunk(buf ^ 1);  // last read during the previous block, before its closing barrier
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc)
+            static_cast<float*>(a.state.base)[a.state.index(c0 + 4 * cj + cc, 1 + 4 * ri + r, slot)] = st[r][cc];
+}
+
 // v7: one CTA of (1 + G) * S threads per (head, batch slot).  Thread j of the first S keeps the whole column j of the
 // state in registers, so a token needs no exchange between threads; the other G groups of S threads fetch the tokens'
 // rows a chunk of 768 / S tokens ahead (three pairs: r and the decay; k and v; a and kk, 3 / G pairs per group), apply
@@ -335,6 +551,19 @@ cudaError_t time_mix_v56(const WkvArgs& a, cudaStream_t stream) {
         case 128: time_mix_v56_kernel<128, 4><<<grid, 1024, 0, stream>>>(a); break;
         default: return cudaErrorInvalidValue;
     }
+    return cudaGetLastError();
+}
+
+// The block form of time_mix_v56 (heads of 64 channels only).
+bool time_mix_v56_chunked_supported(const WkvArgs& a) { return a.S == 64; }
+
+cudaError_t time_mix_v56_chunked(const WkvArgs& a, cudaStream_t stream) {
+    if (a.T == 0 || a.B == 0) return cudaSuccess;
+    if (!time_mix_v56_chunked_supported(a)) return cudaErrorInvalidValue;
+    static SmemOptIn opt_in;
+    const size_t smem = kChunkedSmemFloats * sizeof(float);
+    if (cudaError_t e = opt_in.ensure(time_mix_v56_chunked_kernel, (int)smem); e != cudaSuccess) return e;
+    time_mix_v56_chunked_kernel<<<dim3(a.H, a.B), 256, smem, stream>>>(a);
     return cudaGetLastError();
 }
 

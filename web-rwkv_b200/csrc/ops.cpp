@@ -128,7 +128,7 @@ int32_t matmul_common(const char* name, int kind, wrk_tensor* matrix, wrk_tensor
 
 int32_t time_mix_v56(const char* name, int per_token, wrk_tensor* cursors, wrk_tensor* time_decay,
                      wrk_tensor* time_first, const wrk_view* state, wrk_tensor* k, wrk_tensor* v, wrk_tensor* r,
-                     wrk_tensor* x, wrk_op** out) {
+                     wrk_tensor* x, wrk_op** out, bool blocks = false) {
     REQ_NN(cursors, time_decay, time_first, state, state->tensor, k, v, r, x, out);
     REQ_FLOAT(x, "x");
     REQ_DTYPE(k, x->dtype, "k");
@@ -161,6 +161,12 @@ int32_t time_mix_v56(const char* name, int per_token, wrk_tensor* cursors, wrk_t
     a.per_token_decay = per_token;
     a.k = k->ptr(); a.v = v->ptr(); a.r = r->ptr(); a.x = x->ptr();
     a.status = x->ctx->device_status;
+    if (blocks) {
+        WRK_REQUIRE(k::time_mix_v56_chunked_supported(a), WRK_ERR_UNSUPPORTED, "time_mix_blocks takes heads of 64 channels");
+        *out = new_atom(name, [a](cudaStream_t s) { return k::time_mix_v56_chunked(a, s); },
+                        {cursors, time_decay, time_first, state->tensor, k, v, r, x});
+        return WRK_OK;
+    }
     *out = new_atom(name, [a](cudaStream_t s) { return k::time_mix_v56(a, s); },
                     {cursors, time_decay, time_first, state->tensor, k, v, r, x});
     return WRK_OK;
@@ -403,6 +409,11 @@ int32_t wrk_op_time_mix_v5(wrk_tensor* cursors, wrk_tensor* time_decay, wrk_tens
 int32_t wrk_op_time_mix_v6(wrk_tensor* cursors, wrk_tensor* time_decay, wrk_tensor* time_first, const wrk_view* state,
                            wrk_tensor* k, wrk_tensor* v, wrk_tensor* r, wrk_tensor* x, wrk_op** out) {
     return time_mix_v56("time_mix_v6", 1, cursors, time_decay, time_first, state, k, v, r, x, out);
+}
+
+int32_t wrk_op_time_mix_blocks(int32_t per_token_decay, wrk_tensor* cursors, wrk_tensor* time_decay, wrk_tensor* time_first,
+                               const wrk_view* state, wrk_tensor* k, wrk_tensor* v, wrk_tensor* r, wrk_tensor* x, wrk_op** out) {
+    return time_mix_v56("time_mix_blocks", per_token_decay ? 1 : 0, cursors, time_decay, time_first, state, k, v, r, x, out, true);
 }
 
 int32_t wrk_op_time_mix_v7(wrk_tensor* cursors, const wrk_view* state, wrk_tensor* r, wrk_tensor* w, wrk_tensor* n,

@@ -501,7 +501,9 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
     WRK_TRY(blit(ops, Vx(B["att_x"], sp.c0, sp.c0 + sp.Cl), V(B["aux_x"])));
     {
         const wrk_view st = state_wkv(bd, index, S, sp);
-        if (v6) ADD(wrk_op_time_mix_v6(cursors, time_decay, time_first, &st, att_k, att_v, att_r, aux_x, &_o));
+        // blocks of 16 tokens where there are tokens to block; the serial kernel for short jobs and in strict mode
+        if (merged && S == 64 && T > 8) ADD(wrk_op_time_mix_blocks(v6, cursors, time_decay, time_first, &st, att_k, att_v, att_r, aux_x, &_o));
+        else if (v6) ADD(wrk_op_time_mix_v6(cursors, time_decay, time_first, &st, att_k, att_v, att_r, aux_x, &_o));
         else ADD(wrk_op_time_mix_v5(cursors, time_decay, time_first, &st, att_k, att_v, att_r, aux_x, &_o));
     }
     if (merged8 && S % 8 == 0 && S <= 256 && (S & (S - 1)) == 0) {
