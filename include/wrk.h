@@ -293,6 +293,13 @@ int32_t wrk_matrix_matmul_op(wrk_matrix* m, const wrk_view* input, const wrk_vie
 /* Matrix::matmul_op_sparse(input, output, act, turbo), matrix.rs:149-160 */
 int32_t wrk_matrix_matmul_op_sparse(wrk_matrix* m, const wrk_view* input, const wrk_view* output, int32_t act,
                                     int32_t turbo, wrk_op** out);
+/* No counterpart in the reference: up to four Matrix::matmul_op of one point of a layer (e.g. key / value / receptance /
+ * gate, each with its own input, output and activation) as one op.  Matrices of one format, input width and token count
+ * with 16 or more tokens run as the row tiles of a single tensor-core launch, which fills the SMs without splitting K;
+ * anything else becomes the list of the single ops.  Results are those of the single ops up to the order of the fp32
+ * sums over K (a single op may split K over CTAs where the group does not). */
+int32_t wrk_matrix_matmul_group_op(wrk_matrix* const* matrices, const wrk_view* inputs, const wrk_view* outputs, const int32_t* acts,
+                                   uint32_t count, int32_t turbo, wrk_op** out);
 /* The default NF4 table of Float4Quant::new, matrix.rs:48-70. */
 int32_t wrk_nf4_table(float table[16]);
 /* Float4Quant::new_student(nu) / quantile_student, matrix.rs:29-44 and 72-77: the SF4 code book.  The Student-t

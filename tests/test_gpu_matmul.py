@@ -233,3 +233,35 @@ def test_shape_and_type_errors(wrk, ctx):
     with pytest.raises(wrk.WrkError) as e:
         mat.matmul_op(ctx.tensor(wrk.U8, [128, 2]), ctx.tensor(wrk.F32, [64, 2]))
     assert e.value.status == -2
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("n", [64, 256, 40])
+def test_group_of_matrices_in_one_launch(wrk, ctx, kind, n):
+    """key / value / receptance / gate-like: matrices of different heights, inputs and activations as one op, against
+    the oracle and against the single ops."""
+    rng = np.random.default_rng(70 + n)
+    K, heights, acts = 1024, [1024, 384, 1024, 160], [wrk.ACT_NONE, wrk.ACT_SQUARED_RELU, wrk.ACT_NONE, wrk.ACT_TANH]
+    mats, oracles, xs, ys, singles = [], [], [], [], []
+    launches = []
+    for M in heights:
+        w = (rng.standard_normal((M, K), dtype=np.float32) * 0.02).astype(np.float16)
+        mat, o = _make_matrix(wrk, ctx, kind, w)
+        mats.append(mat), oracles.append(o)
+        xs.append(rng.standard_normal((n, K), dtype=np.float32).astype(np.float16))
+        ys.append(ctx.tensor(wrk.F16, [M, n]))
+        singles.append(ctx.tensor(wrk.F16, [M, n]))
+    t_xs = [ctx.from_numpy(x) for x in xs]
+    turbo = n % 32 == 0
+    before = ctx.launch_count()
+    ctx.run(wrk.matmul_group_op(mats, t_xs, ys, acts, turbo=turbo))
+    launches = ctx.launch_count() - before
+    assert launches == (1 if turbo else 4)
+    for mat, x, y, act in zip(mats, t_xs, singles, acts):
+        ctx.run(mat.matmul_op(x, y, act=act, turbo=turbo))
+    for (okind, om, oscale), x, y, single, act, M in zip(oracles, xs, ys, singles, acts, heights):
+        want = np.zeros((n, M), dtype=np.float16)
+        oracle.matmul(okind, om, oscale, x, want, act=act, mode=1 if turbo else 0)
+        assert_close(y.numpy().reshape(n, M), want, f"group {kind} M={M}")
+        assert_close(y.numpy().reshape(n, M), single.numpy().reshape(n, M), f"group vs single {kind} M={M}")
+    assert ctx.device_status() == 0

@@ -532,6 +532,18 @@ class Matrix:
         return _mk(fn, self.handle, pi, po, act, int(turbo), keep=(self, ki, ko))
 
 
+def matmul_group_op(matrices, inputs, outputs, acts=None, turbo=True):
+    """Up to four `Matrix.matmul_op` of one point of a layer as one op (one tensor-core launch where the shapes allow)."""
+    n = len(matrices)
+    acts = list(acts) if acts is not None else [ACT_NONE] * n
+    views = [x.as_view() if isinstance(x, Tensor) else x for x in list(inputs) + list(outputs)]
+    ins = (CView * n)(*[v.c for v in views[:n]])
+    outs = (CView * n)(*[v.c for v in views[n:]])
+    ms = (ctypes.c_void_p * n)(*[m.handle for m in matrices])
+    return _mk("wrk_matrix_matmul_group_op", ms, ins, outs, (ctypes.c_int32 * n)(*acts), ctypes.c_uint32(n), int(turbo),
+               keep=(tuple(matrices), tuple(views)))
+
+
 def gemv_int8_static(ctx, matrix, minmax, x, y, act=ACT_NONE, num_ctas=0, device=None):
     """`wrk_gemv_int8_static` (no counterpart in the reference): y[t][m] = act(W[m][:] . x[t][:]) on the context's
     stream without any allocation; the kernel's row-range table sits in a static device array (512 CTAs at most).

@@ -14,7 +14,14 @@
 //   * warp 8 (one lane) issues tcgen05.mma.cta_group::1.kind::f16 (M = 128, N = token tile, K = 16, four per
 //     step) into a TMEM accumulator of 128 lanes x N fp32 columns and releases the stage with tcgen05.commit;
 //   * after the last step warps 0-7 read the accumulator back with tcgen05.ld (warp w reads lanes
-//     32 (w % 4) ..), apply the activation and store token-major rows.
+//     32 (w % 4) ..), apply the activation and put the tile, in the output's type, into shared memory (the operand
+//     stages are free by then), from where it goes to global memory in 16-byte pieces: the 128 rows of a token are
+//     adjacent elements of the output.
+// A launch takes up to four matrices of one format, K and token count (UmmaGroup): their row tiles share grid.x, so
+// key / value / receptance / gate of a layer fill the SMs together and none has to split K.
+// At 256 tokens the K walk is paced by the L2: every CTA re-reads the whole [tokens x K] activation tile next to its
+// own 128 rows of weights (40 KB per step and CTA; four 4096 x 4096 matrices at 256 tokens: 335 MB in 43 us, 7.7 TB/s),
+// which neither fewer dequantizing instructions (packed add.f32x2 / fma.rn.f32x2) nor a fourth operand stage change much.
 // Where the output tiles alone leave SMs idle, the CTAs of a thread-block cluster (up to 8, along grid.z) split the
 // K range of one tile: each writes its partial accumulator to its own shared memory and, after a cluster barrier,
 // adds its share of the columns over all peers through distributed shared memory.
@@ -56,6 +63,18 @@ struct UmmaParams {
     uint32_t raw;       // raw weight stages (quantized kinds)
     uint32_t splits;    // CTAs along K per output tile (grid.z = the cluster's size)
     int32_t* status;
+};
+
+// Up to kMaxGroup problems of one weight format, K, token count and tiling in one launch: the row tiles of problem i
+// are CTAs tile_start[i] .. tile_start[i + 1] - 1 along grid.x.  Matrices that read different activations at the same
+// point of a layer (key / value / receptance / gate) fill the SMs together, where each alone would have to split K
+// and pay for the exchange of partial tiles.
+constexpr int kMaxGroup = 4;
+struct alignas(64) UmmaGroup {
+    CUtensorMap map_w[kMaxGroup], map_x[kMaxGroup];
+    UmmaParams p[kMaxGroup];
+    uint32_t tile_start[kMaxGroup + 1];
+    uint32_t count;
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -178,16 +197,18 @@ __device__ __forceinline__ void dequant_int8(uint4 q0, uint4 q1, uint32_t minmax
     const float2 mm = __half22float2(*reinterpret_cast<const __half2*>(&minmax));
     const float sc = (mm.y - mm.x) * (1.0f / 255.0f), mn = mm.x;
     const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    const float2 sc2 = make_float2(sc, sc), mn2 = make_float2(mn, mn), bias2 = make_float2(-8388608.0f, -8388608.0f);
     uint32_t h[16];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        // byte b -> float 8388608 + b (0x4B000000 | b), minus 8388608: b exactly
-        const float f0 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7650)) - 8388608.0f;
-        const float f1 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7651)) - 8388608.0f;
-        const float f2 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7652)) - 8388608.0f;
-        const float f3 = __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7653)) - 8388608.0f;
-        h[2 * i] = pack_half2(__floats2half2_rn(fmaf(f0, sc, mn), fmaf(f1, sc, mn)));
-        h[2 * i + 1] = pack_half2(__floats2half2_rn(fmaf(f2, sc, mn), fmaf(f3, sc, mn)));
+        // byte b -> float 8388608 + b (0x4B000000 | b), minus 8388608: b exactly; two weights per instruction from
+        // there on (add.f32x2, fma.rn.f32x2: the same roundings as the scalar forms)
+        const float2 f01 = make_float2(__uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7650)),
+                                       __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7651)));
+        const float2 f23 = make_float2(__uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7652)),
+                                       __uint_as_float(__byte_perm(words[i], 0x4B000000u, 0x7653)));
+        h[2 * i] = pack_half2(__float22half2_rn(__ffma2_rn(__fadd2_rn(f01, bias2), sc2, mn2)));
+        h[2 * i + 1] = pack_half2(__float22half2_rn(__ffma2_rn(__fadd2_rn(f23, bias2), sc2, mn2)));
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) out[j] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
@@ -201,7 +222,7 @@ __device__ __forceinline__ void dequant_nf4(uint4 q, float am, const float2* lut
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             const float2 pair = lut2[(words[i] >> (8 * b)) & 0xffu];  // (table[lo nibble], table[hi nibble])
-            h[4 * i + b] = pack_half2(__floats2half2_rn(pair.x * am, pair.y * am));
+            h[4 * i + b] = pack_half2(__float22half2_rn(__fmul2_rn(pair, make_float2(am, am))));
         }
 #pragma unroll
     for (int j = 0; j < 4; ++j) out[j] = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
@@ -210,8 +231,15 @@ __device__ __forceinline__ void dequant_nf4(uint4 q, float am, const float2* lut
 // One instantiation per weight format: the dequantizing loop holds only its own format's code.
 template <int KIND>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
-matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x) {
+matmul_umma_kernel(const __grid_constant__ UmmaGroup grp) {
     extern __shared__ uint8_t smem_raw[];
+    uint32_t gi = 0;
+#pragma unroll
+    for (uint32_t i = 1; i < (uint32_t)kMaxGroup; ++i)
+        if (i < grp.count && blockIdx.x >= grp.tile_start[i]) gi = i;
+    const UmmaParams& p = grp.p[gi];
+    const CUtensorMap& map_w = grp.map_w[gi];
+    const CUtensorMap& map_x = grp.map_x[gi];
     __shared__ uint64_t ab_full[kMaxStages], ab_empty[kMaxStages], raw_full[kMaxRaw], raw_empty[kMaxRaw], done_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ float2 lut2[256];
@@ -226,7 +254,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
     const uint32_t raw_bytes = BM * raw_row;
     uint8_t* raw_base = smem + (size_t)p.stages * stage_bytes;              // raw weight stages
     uint8_t* scale_base = raw_base + (size_t)p.raw * raw_bytes;             // [2 groups][2 slots][BM][8 bytes]
-    const uint32_t m0 = blockIdx.x * BM, n0 = blockIdx.y * p.n_tile;
+    const uint32_t m0 = (blockIdx.x - grp.tile_start[gi]) * BM, n0 = blockIdx.y * p.n_tile;
     // this CTA's share of the K steps (split-K: grid.z CTAs per output tile)
     const uint32_t nk_all = p.K / BK;
     const uint32_t k_begin = (uint32_t)((uint64_t)nk_all * blockIdx.z / p.splits);
@@ -315,6 +343,13 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
         // split K: the partial tile goes to this CTA's own shared memory (the operand stages are free once every
         // MMA has completed), column-major [n_tile][BM] floats, for the cluster-wide sum below
         float* ws_mine = reinterpret_cast<float*>(smem);
+        const size_t col_stride = p.out.stride[0], out_row = p.out.index(m < p.M ? m : 0, n0, 0);
+        const bool act_none = p.act == WRK_ACT_NONE;
+        // one CTA per output tile: the tile goes through shared memory when 16-byte pieces of a column are aligned in
+        // the output (its first element of the tile 16-byte aligned, columns a multiple of 16 bytes apart)
+        const uint32_t osize = p.out.dtype == WRK_F16 ? 2u : 4u;
+        const bool staged = p.splits == 1 && (reinterpret_cast<uintptr_t>(p.out.base) + p.out.index(m0, n0, 0) * osize) % 16 == 0 &&
+                            (col_stride * osize) % 16 == 0;
         // up to four 8-column accumulator loads are in flight before the single wait
         for (uint32_t c0 = c_begin; c0 < c_end; c0 += 32) {
             uint32_t v[4][8];
@@ -322,6 +357,12 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
             for (uint32_t q = 0; q < 4; ++q)
                 if (c0 + 8 * q < c_end) tmem_ld8(tmem_d + ((quad * 32) << 16) + c0 + 8 * q, v[q]);
             tmem_ld_wait();
+            if (!act_none && p.splits == 1) {  // the activation once, outside the store loops (which then hold no branch)
+#pragma unroll
+                for (uint32_t q = 0; q < 4; ++q)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[q][j] = __float_as_uint(activate_f(p.act, __uint_as_float(v[q][j])));
+            }
 #pragma unroll
             for (uint32_t q = 0; q < 4; ++q) {
                 const uint32_t c = c0 + 8 * q;
@@ -329,13 +370,54 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
                 if (p.splits > 1) {
 #pragma unroll
                     for (int j = 0; j < 8; ++j) ws_mine[(size_t)(c + j) * BM + quad * 32 + lane] = __uint_as_float(v[q][j]);
-                } else if (m < p.M) {
+                } else if (staged) {
+                    // the finished values, in the output's type, into a [column][row] tile in shared memory
+                    if (p.out.dtype == WRK_F16) {
+                        __half* t = reinterpret_cast<__half*>(smem);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const uint32_t n = n0 + c + j;
-                        if (n < p.N)
-                            dstore(p.out.base, p.out.dtype, p.out.index(m, n, 0), activate_f(p.act, __uint_as_float(v[q][j])));
+                        for (int j = 0; j < 8; ++j)
+                            t[(size_t)(c + j) * BM + quad * 32 + lane] =
+                                __float2half_rn(__uint_as_float(v[q][j]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            ws_mine[(size_t)(c + j) * BM + quad * 32 + lane] =
+                                __uint_as_float(v[q][j]);
                     }
+                } else if (m < p.M) {
+                    // element (m, n) of the output lies col_stride elements after (m, n - 1): one address, then steps
+                    const size_t at = out_row + (size_t)c * col_stride;
+                    if (p.out.dtype == WRK_F16) {
+                        __half* o = static_cast<__half*>(p.out.base) + at;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (n0 + c + j < p.N) o[(size_t)j * col_stride] = __float2half_rn(__uint_as_float(v[q][j]));
+                    } else {
+                        float* o = static_cast<float*>(p.out.base) + at;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (n0 + c + j < p.N) o[(size_t)j * col_stride] = __uint_as_float(v[q][j]);
+                    }
+                }
+            }
+        }
+        if (staged) {
+            // ... and from there to global memory in 16-byte pieces: the 128 rows of a column are adjacent elements of
+            // the output, so a warp writes whole 256- or 512-byte runs instead of 64 bytes per instruction
+            asm volatile("bar.sync 1, %0;\n" ::"n"(kDequantWarps * 32) : "memory");
+            const uint32_t esize = p.out.dtype == WRK_F16 ? 2u : 4u, per_col = BM * esize / 16, per_vec = 16 / esize;
+            const uint32_t cols = min(p.n_tile, p.N - n0);
+            const size_t col0 = p.out.index(m0, n0, 0);
+            for (uint32_t i = threadIdx.x; i < cols * per_col; i += kDequantWarps * 32) {
+                const uint32_t c = i / per_col, r = (i % per_col) * per_vec;  // column, first row of the piece
+                if (m0 + r >= p.M) continue;
+                const uint4 piece = *reinterpret_cast<const uint4*>(smem + ((size_t)c * BM + r) * esize);
+                uint8_t* dst = static_cast<uint8_t*>(p.out.base) + (col0 + (size_t)c * col_stride + r) * esize;
+                if (m0 + r + per_vec <= p.M) {
+                    *reinterpret_cast<uint4*>(dst) = piece;
+                } else {  // the matrix ends inside the piece
+                    const uint8_t* src = reinterpret_cast<const uint8_t*>(&piece);
+                    for (uint32_t e = 0; e < (p.M - m0 - r) * esize; ++e) dst[e] = src[e];
                 }
             }
         }
@@ -405,6 +487,7 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
             const uint32_t c_lo = p.n_tile * rank / p.splits, c_hi = p.n_tile * (rank + 1) / p.splits;
             const uint32_t v_lo = c_lo * (BM / 4), v_hi = c_hi * (BM / 4);  // groups of four rows
             const uint32_t base_addr = smem_addr(smem);
+            const bool out_vec = reinterpret_cast<uintptr_t>(p.out.base) % 16 == 0;
             for (uint32_t base = v_lo; base < v_hi; base += kGroups * kReduceThreads) {
                 float4 sum[kGroups];
 #pragma unroll
@@ -433,10 +516,24 @@ matmul_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap map_w
                     const uint32_t c = pos / (BM / 4), row = (pos % (BM / 4)) * 4;
                     const uint32_t n = n0 + c, m = m0 + row;
                     if (n >= p.N) continue;
-                    const float r4[4] = {sum[u].x, sum[u].y, sum[u].z, sum[u].w};
+                    float r4[4] = {sum[u].x, sum[u].y, sum[u].z, sum[u].w};
+                    if (p.act != WRK_ACT_NONE) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                        if (m + e < p.M) dstore(p.out.base, p.out.dtype, p.out.index(m + e, n, 0), activate_f(p.act, r4[e]));
+                        for (int e = 0; e < 4; ++e) r4[e] = activate_f(p.act, r4[e]);
+                    }
+                    const size_t at = p.out.index(m, n, 0);  // rows m .. m + 3 of a column are adjacent elements
+                    if (m + 3 < p.M && (at & 3) == 0 && out_vec) {
+                        if (p.out.dtype == WRK_F16) {
+                            const __half2 lo = __floats2half2_rn(r4[0], r4[1]), hi = __floats2half2_rn(r4[2], r4[3]);
+                            *reinterpret_cast<uint2*>(static_cast<__half*>(p.out.base) + at) = make_uint2(pack_half2(lo), pack_half2(hi));
+                        } else {
+                            *reinterpret_cast<float4*>(static_cast<float*>(p.out.base) + at) = make_float4(r4[0], r4[1], r4[2], r4[3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (m + e < p.M) dstore(p.out.base, p.out.dtype, at + e, r4[e]);
+                    }
                 }
             }
         }
@@ -487,17 +584,30 @@ bool matmul_umma_supported(const MatmulArgs& a) {
     return encode_tiled() != nullptr;
 }
 
-cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t stream) {
+bool matmul_umma_group_supported(const MatmulArgs* a, int count) {
+    if (count < 1 || count > kMaxGroup) return false;
+    for (int i = 0; i < count; ++i) {
+        if (!matmul_umma_supported(a[i])) return false;
+        if (a[i].kind != a[0].kind || a[i].K != a[0].K || a[i].N != a[0].N) return false;
+    }
+    return true;
+}
+
+cudaError_t matmul_umma_group(const MatmulArgs* args, int count, int32_t* status, cudaStream_t stream) {
+    if (!matmul_umma_group_supported(args, count)) return cudaErrorInvalidValue;
+    const MatmulArgs& a = args[0];
+    UmmaGroup g{};
+    g.count = (uint32_t)count;
+    uint32_t row_tiles = 0;
+    for (int i = 0; i < count; ++i) {
+        g.tile_start[i] = row_tiles;
+        row_tiles += (args[i].M + BM - 1) / BM;
+    }
+    for (int i = count; i <= kMaxGroup; ++i) g.tile_start[i] = row_tiles;
     UmmaParams p{};
-    p.w = static_cast<const uint8_t*>(a.matrix);
-    p.scale = a.scale;
-    p.table = a.table;
     p.kind = a.kind;
     p.K = a.K;
-    p.M = a.M;
     p.N = a.N;
-    p.out = a.out;
-    p.act = a.act;
     p.status = status;
     const uint32_t nk = a.K / BK;
     // Output tiles are 128 rows x n_tile tokens; K is split across the CTAs of a thread-block cluster while the
@@ -508,7 +618,6 @@ cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t strea
     // would double instead, 31 -> 37 us, so those keep 256.)
     int sms = 148, device = 0;
     if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    const uint32_t row_tiles = (a.M + BM - 1) / BM;
     auto splits_for = [&](uint32_t n_tile) {
         const uint32_t tiles = row_tiles * ((a.N + n_tile - 1) / n_tile);
         uint32_t want = std::max<uint32_t>(1, (uint32_t)sms / tiles);
@@ -527,41 +636,55 @@ cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t strea
     while (p.tmem_cols < p.n_tile) p.tmem_cols *= 2;
     const uint32_t stage_bytes = A_STAGE_BYTES + p.n_tile * BK * 2;
     const uint32_t raw_bytes = a.kind == MAT_INT8 ? BM * 64 : a.kind == MAT_NF4 ? BM * 32 : 0;
-    const uint32_t budget = 200u * 1024;
+    // all of an SM's shared memory but the static part and the alignment slack: at 256-token tiles (48 KB operand
+    // stages) that is four stages, one pair for each group of dequantizing warps, instead of three
+    const uint32_t budget = 222u * 1024;
     p.raw = a.kind == MAT_FP16 ? 0 : std::min<uint32_t>(kMaxRaw, std::max<uint32_t>(2, nk));
     p.stages = std::min<uint32_t>(kMaxStages, std::max<uint32_t>(2, nk));
     while (p.stages * stage_bytes + p.raw * raw_bytes + 4 * SCALE_SLOT_BYTES > budget) {
         if (p.raw > 4) --p.raw;
-        else if (p.stages > 2) --p.stages;
+        else if (p.stages > 4) --p.stages;
         else if (p.raw > 2) --p.raw;
+        else if (p.stages > 2) --p.stages;
         else break;
     }
-
-    CUtensorMap map_w, map_x;
-    bool ok;
-    if (a.kind == MAT_FP16)
-        ok = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a.matrix, a.K, a.M, (uint64_t)a.K * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
-    else if (a.kind == MAT_INT8)
-        ok = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.matrix, a.K, a.M, a.K, 64, BM, CU_TENSOR_MAP_SWIZZLE_NONE);
-    else
-        ok = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.matrix, a.K / 2, a.M, a.K / 2, 32, BM, CU_TENSOR_MAP_SWIZZLE_NONE);
-    const __half* x0 = static_cast<const __half*>(a.in.base) + a.in.index(0, 0, 0);
-    ok = ok && make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x0, a.K, a.N, (uint64_t)a.in.stride[0] * 2, BK, p.n_tile,
-                           CU_TENSOR_MAP_SWIZZLE_128B);
-    if (!ok) return cudaErrorInvalidValue;
-
-    static SmemOptIn opt_in[3];
-    auto kernel = a.kind == MAT_INT8 ? matmul_umma_kernel<MAT_INT8> : a.kind == MAT_NF4 ? matmul_umma_kernel<MAT_NF4> : matmul_umma_kernel<MAT_FP16>;
-    if (cudaError_t e = opt_in[a.kind == MAT_INT8 ? 0 : a.kind == MAT_NF4 ? 1 : 2].ensure(kernel, 208 * 1024); e != cudaSuccess) return e;
-    dim3 grid((a.M + BM - 1) / BM, (a.N + p.n_tile - 1) / p.n_tile, 1);
-    grid.z = p.splits;
     if (p.splits > 1) {
         const uint32_t nk_split = nk / p.splits;
         p.stages = std::min<uint32_t>(p.stages, std::max<uint32_t>(2, nk_split));
         if (p.raw) p.raw = std::min<uint32_t>(p.raw, std::max<uint32_t>(2, nk_split));
     }
+
+    for (int i = 0; i < count; ++i) {
+        const MatmulArgs& ai = args[i];
+        UmmaParams& pi = g.p[i];
+        pi = p;
+        pi.w = static_cast<const uint8_t*>(ai.matrix);
+        pi.scale = ai.scale;
+        pi.table = ai.table;
+        pi.M = ai.M;
+        pi.out = ai.out;
+        pi.act = ai.act;
+        bool ok;
+        if (a.kind == MAT_FP16)
+            ok = make_map_2d(&g.map_w[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, ai.matrix, a.K, ai.M, (uint64_t)a.K * 2, BK, BM,
+                             CU_TENSOR_MAP_SWIZZLE_128B);
+        else if (a.kind == MAT_INT8)
+            ok = make_map_2d(&g.map_w[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, ai.matrix, a.K, ai.M, a.K, 64, BM, CU_TENSOR_MAP_SWIZZLE_NONE);
+        else
+            ok = make_map_2d(&g.map_w[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, ai.matrix, a.K / 2, ai.M, a.K / 2, 32, BM,
+                             CU_TENSOR_MAP_SWIZZLE_NONE);
+        const __half* x0 = static_cast<const __half*>(ai.in.base) + ai.in.index(0, 0, 0);
+        ok = ok && make_map_2d(&g.map_x[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x0, a.K, a.N, (uint64_t)ai.in.stride[0] * 2, BK, p.n_tile,
+                               CU_TENSOR_MAP_SWIZZLE_128B);
+        if (!ok) return cudaErrorInvalidValue;
+    }
+
+    static SmemOptIn opt_in[3];
+    auto kernel = a.kind == MAT_INT8 ? matmul_umma_kernel<MAT_INT8> : a.kind == MAT_NF4 ? matmul_umma_kernel<MAT_NF4> : matmul_umma_kernel<MAT_FP16>;
+    if (cudaError_t e = opt_in[a.kind == MAT_INT8 ? 0 : a.kind == MAT_NF4 ? 1 : 2].ensure(kernel, 223 * 1024); e != cudaSuccess) return e;
+    dim3 grid(row_tiles, (a.N + p.n_tile - 1) / p.n_tile, p.splits);
     size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.raw * raw_bytes + 4 * SCALE_SLOT_BYTES + 1024;
-    if (p.splits > 1) smem = std::max<size_t>(smem, (size_t)p.n_tile * BM * sizeof(float) + 1024);  // the partial tile
+    smem = std::max<size_t>(smem, (size_t)p.n_tile * BM * sizeof(float) + 1024);  // the partial tile / the staged output tile
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(kUmmaThreads, 1, 1);
@@ -574,8 +697,10 @@ cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t strea
     attr[0].val.clusterDim.z = p.splits;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, p, map_w, map_x);
+    return cudaLaunchKernelEx(&cfg, kernel, g);
 }
+
+cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t stream) { return matmul_umma_group(&a, 1, status, stream); }
 
 }  // namespace k
 }  // namespace wrk

@@ -52,6 +52,10 @@ cudaError_t matmul_small(const MatmulArgs& a, int num_sms, cudaStream_t stream);
 // Tensor-memory (tcgen05) GEMM for N >= 16 tokens (gemm_umma.cu).
 bool matmul_umma_supported(const MatmulArgs& a);
 cudaError_t matmul_umma(const MatmulArgs& a, int32_t* status, cudaStream_t stream);
+// Up to four matrices of one weight format, K and token count (each with its own activations, output and activation
+// function) as the row tiles of one launch.
+bool matmul_umma_group_supported(const MatmulArgs* a, int count);
+cudaError_t matmul_umma_group(const MatmulArgs* a, int count, int32_t* status, cudaStream_t stream);
 
 // ---- one-shot all-reduce over peer memory (peer_reduce.cu) --------------------------------------------
 constexpr int kMaxPeers = 8;

@@ -33,9 +33,10 @@ int32_t check_cursors(const wrk_tensor* cursors, uint32_t T) {
         for (auto q : _p) WRK_REQUIRE(q, WRK_ERR_INVALID_ARGUMENT, "null argument");     \
     } while (0)
 
-int32_t matmul_common(const char* name, int kind, wrk_tensor* matrix, wrk_tensor* scale, wrk_tensor* quant,
-                      const wrk_view* input, const wrk_view* output, int32_t act, wrk_op** out) {
-    REQ_NN(matrix, input, output, out, input->tensor, output->tensor);
+// Checks the operands of out = act(W x) and fills the kernels' argument block.
+int32_t matmul_args(int kind, wrk_tensor* matrix, wrk_tensor* scale, wrk_tensor* quant, const wrk_view* input,
+                    const wrk_view* output, int32_t act, k::MatmulArgs* args) {
+    REQ_NN(matrix, input, output, input->tensor, output->tensor);
     REQ_FLOAT(input->tensor, "input");
     REQ_FLOAT(output->tensor, "output");
     WRK_REQUIRE(act >= WRK_ACT_NONE && act <= WRK_ACT_SILU, WRK_ERR_INVALID_ARGUMENT, "unknown activation %d", act);
@@ -64,7 +65,8 @@ int32_t matmul_common(const char* name, int kind, wrk_tensor* matrix, wrk_tensor
     WRK_TRY(check_view("input", input, k, n, b, 1));
     WRK_TRY(check_view("output", output, m, n, b, 1));
 
-    k::MatmulArgs a{};
+    k::MatmulArgs& a = *args;
+    a = k::MatmulArgs{};
     a.kind = kind;
     a.matrix = matrix->ptr();
     a.scale = scale ? static_cast<const __half*>(scale->ptr()) : nullptr;
@@ -77,6 +79,16 @@ int32_t matmul_common(const char* name, int kind, wrk_tensor* matrix, wrk_tensor
     a.out = make_dview(*output);
     a.act = act;
     a.status = matrix->ctx->device_status;
+    return WRK_OK;
+}
+
+int32_t matmul_common(const char* name, int kind, wrk_tensor* matrix, wrk_tensor* scale, wrk_tensor* quant,
+                      const wrk_view* input, const wrk_view* output, int32_t act, wrk_op** out) {
+    REQ_NN(out);
+    k::MatmulArgs a;
+    WRK_TRY(matmul_args(kind, matrix, scale, quant, input, output, act, &a));
+    const uint32_t m = a.M, n = a.N, b = a.B, k = a.K;
+    (void)m;
     const int sms = matrix->ctx->num_sms;
     // few tokens, fp16 activations, whole rows: the weight-streaming kernel of the decode path
     const uint32_t need = kind == k::MAT_FP16 ? 32 : 128;
@@ -1116,6 +1128,44 @@ int32_t wrk_matrix_matmul_op(wrk_matrix* m, const wrk_view* input, const wrk_vie
 int32_t wrk_matrix_matmul_op_sparse(wrk_matrix* m, const wrk_view* input, const wrk_view* output, int32_t act,
                                     int32_t turbo, wrk_op** out) {
     return matrix_matmul(m, input, output, act, turbo, 1, out);
+}
+
+int32_t wrk_matrix_matmul_group_op(wrk_matrix* const* matrices, const wrk_view* inputs, const wrk_view* outputs, const int32_t* acts,
+                                   uint32_t count, int32_t turbo, wrk_op** out) {
+    REQ_NN(matrices, inputs, outputs, acts, out);
+    WRK_REQUIRE(count >= 1 && count <= 4, WRK_ERR_INVALID_ARGUMENT, "a group holds 1 to 4 matrices, not %u", count);
+    k::MatmulArgs args[4];
+    bool one_launch = turbo != 0;
+    for (uint32_t i = 0; i < count && one_launch; ++i) {
+        wrk_matrix* m = matrices[i];
+        REQ_NN(m);
+        const int kind = m->kind == 0 ? k::MAT_FP16 : m->kind == 1 ? k::MAT_INT8 : k::MAT_NF4;
+        WRK_TRY(matmul_args(kind, m->w, m->m, m->q, &inputs[i], &outputs[i], acts[i], &args[i]));
+    }
+    one_launch = one_launch && k::matmul_umma_group_supported(args, (int)count);
+    if (one_launch) {
+        std::vector<k::MatmulArgs> all(args, args + count);
+        int32_t* status = args[0].status;
+        wrk_op* op = new_atom("matmul_group", [all, status](cudaStream_t s) { return k::matmul_umma_group(all.data(), (int)all.size(), status, s); },
+                              {});
+        for (uint32_t i = 0; i < count; ++i) {
+            for (wrk_tensor* t : {matrices[i]->w, matrices[i]->m, matrices[i]->q, inputs[i].tensor, outputs[i].tensor})
+                if (t != nullptr && t->buf) op->keep.push_back(t->buf);
+        }
+        *out = op;
+        return WRK_OK;
+    }
+    // shapes the grouped kernel does not take: the same work as a list of single matmuls
+    std::vector<wrk_op*> ops;
+    int32_t status = WRK_OK;
+    for (uint32_t i = 0; i < count && status == WRK_OK; ++i) {
+        wrk_op* o = nullptr;
+        status = matrix_matmul(matrices[i], &inputs[i], &outputs[i], acts[i], turbo, 0, &o);
+        if (status == WRK_OK) ops.push_back(o);
+    }
+    if (status == WRK_OK) status = wrk_op_list(ops.data(), ops.size(), out);
+    for (wrk_op* o : ops) wrk_op_release(o);
+    return status;
 }
 
 }  // extern "C"

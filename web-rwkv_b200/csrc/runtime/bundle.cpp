@@ -249,6 +249,25 @@ int32_t matmul(OpList& ops, wrk_matrix* m, wrk_view in, wrk_view out, int32_t ac
     return WRK_OK;
 }
 
+struct GroupItem {
+    wrk_matrix* m;
+    wrk_view in, out;
+    int32_t act;
+};
+int32_t matmul_group(OpList& ops, std::initializer_list<GroupItem> items, bool turbo) {
+    wrk_matrix* ms[4];
+    wrk_view ins[4], outs[4];
+    int32_t acts[4];
+    uint32_t n = 0;
+    for (const GroupItem& it : items) {
+        if (n == 4) return set_error(WRK_ERR_INVALID_ARGUMENT, "a group holds at most 4 matrices");
+        ms[n] = it.m, ins[n] = it.in, outs[n] = it.out, acts[n] = it.act;
+        ++n;
+    }
+    ADD(wrk_matrix_matmul_group_op(ms, ins, outs, acts, n, turbo, &_o));
+    return WRK_OK;
+}
+
 int32_t token_shift(OpList& ops, wrk_tensor* cursors, wrk_view mix, wrk_view state, wrk_tensor* in, wrk_tensor* out,
                     bool reversed) {
     ADD(wrk_op_token_shift(cursors, &mix, &state, in, out, reversed, &_o));
@@ -456,10 +475,17 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
         }
         HOOK(POST_ATT_GATED_TOKEN_SHIFT);
         HOOK(PRE_ATT_LINEAR);
-        WRK_TRY(matmul(ops, L.att_w_k, Vz(B["att_sx"], 1), V(B["att_k"]), WRK_ACT_NONE, turbo));
-        WRK_TRY(matmul(ops, L.att_w_v, Vz(B["att_sx"], 2), V(B["att_v"]), WRK_ACT_NONE, turbo));
-        WRK_TRY(matmul(ops, L.att_w_r, Vz(B["att_sx"], 3), V(B["att_r"]), WRK_ACT_NONE, turbo));
-        WRK_TRY(matmul(ops, L.att_w_g, Vz(B["att_sx"], 4), V(B["att_g"]), WRK_ACT_NONE, turbo));
+        if (merged) {  // the four matrices as the row tiles of one launch
+            WRK_TRY(matmul_group(ops, {{L.att_w_k, Vz(B["att_sx"], 1), V(B["att_k"]), WRK_ACT_NONE},
+                                       {L.att_w_v, Vz(B["att_sx"], 2), V(B["att_v"]), WRK_ACT_NONE},
+                                       {L.att_w_r, Vz(B["att_sx"], 3), V(B["att_r"]), WRK_ACT_NONE},
+                                       {L.att_w_g, Vz(B["att_sx"], 4), V(B["att_g"]), WRK_ACT_NONE}}, turbo));
+        } else {
+            WRK_TRY(matmul(ops, L.att_w_k, Vz(B["att_sx"], 1), V(B["att_k"]), WRK_ACT_NONE, turbo));
+            WRK_TRY(matmul(ops, L.att_w_v, Vz(B["att_sx"], 2), V(B["att_v"]), WRK_ACT_NONE, turbo));
+            WRK_TRY(matmul(ops, L.att_w_r, Vz(B["att_sx"], 3), V(B["att_r"]), WRK_ACT_NONE, turbo));
+            WRK_TRY(matmul(ops, L.att_w_g, Vz(B["att_sx"], 4), V(B["att_g"]), WRK_ACT_NONE, turbo));
+        }
         HOOK(POST_ATT_LINEAR);
         HOOK(PRE_ATT_TIME_DECAY_ADAPT);
         WRK_TRY(matmul(ops, L.time_decay_w1, Vz(B["att_sx"], 0), V(B["att_w"]), WRK_ACT_TANH, turbo));
@@ -480,10 +506,10 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
         wrk_tensor* const mixes[4] = {L.time_mix_k, L.time_mix_v, L.time_mix_r, L.time_mix_g};
         wrk_tensor* const outs[4] = {B["att_kx"], B["att_vx"], B["att_rx"], B["att_gx"]};
         ADD(wrk_op_token_shift_multi(cursors, &sa, B["att_x"], 4, mixes, outs, false, &_o));
-        WRK_TRY(matmul(ops, L.att_w_k, V(B["att_kx"]), V(B["att_k"]), WRK_ACT_NONE, turbo));
-        WRK_TRY(matmul(ops, L.att_w_v, V(B["att_vx"]), V(B["att_v"]), WRK_ACT_NONE, turbo));
-        WRK_TRY(matmul(ops, L.att_w_r, V(B["att_rx"]), V(B["att_r"]), WRK_ACT_NONE, turbo));
-        WRK_TRY(matmul(ops, L.att_w_g, V(B["att_gx"]), V(B["att_g"]), WRK_ACT_NONE, turbo));
+        WRK_TRY(matmul_group(ops, {{L.att_w_k, V(B["att_kx"]), V(B["att_k"]), WRK_ACT_NONE},
+                                   {L.att_w_v, V(B["att_vx"]), V(B["att_v"]), WRK_ACT_NONE},
+                                   {L.att_w_r, V(B["att_rx"]), V(B["att_r"]), WRK_ACT_NONE},
+                                   {L.att_w_g, V(B["att_gx"]), V(B["att_g"]), WRK_ACT_NONE}}, turbo));
     } else {
         WRK_TRY(token_shift(ops, cursors, V(L.time_mix_k), state_att(bd, index, S), B["att_x"], B["att_kx"], false));
         WRK_TRY(token_shift(ops, cursors, V(L.time_mix_v), state_att(bd, index, S), B["att_x"], B["att_vx"], false));
@@ -543,11 +569,16 @@ int32_t layer_v56(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index,
     }
     HOOK(POST_FFN_TOKEN_SHIFT);
     HOOK(PRE_FFN_LINEAR);
-    WRK_TRY(matmul(ops, L.ffn_w_k, V(B["ffn_kx"]), V(B["ffn_k"]), WRK_ACT_SQUARED_RELU, turbo));
-    HOOK(POST_FFN_ACTIVATE);
+    if (merged) {  // key and receptance read different shifts of one input: one launch; value follows
+        WRK_TRY(matmul_group(ops, {{L.ffn_w_k, V(B["ffn_kx"]), V(B["ffn_k"]), WRK_ACT_SQUARED_RELU},
+                                   {L.ffn_w_r, V(B["ffn_rx"]), V(B["ffn_r"]), WRK_ACT_NONE}}, turbo));
+    } else {
+        WRK_TRY(matmul(ops, L.ffn_w_k, V(B["ffn_kx"]), V(B["ffn_k"]), WRK_ACT_SQUARED_RELU, turbo));
+        HOOK(POST_FFN_ACTIVATE);
+    }
     WRK_TRY(matmul(ops, L.ffn_w_v, V(B["ffn_k"]), V(sp.on ? partial_of(B, 1) : B["ffn_v"]), WRK_ACT_NONE, turbo, true));
     if (sp.on) WRK_TRY(reduce_partial(bd, ops, B, B["ffn_v"], 1));
-    WRK_TRY(matmul(ops, L.ffn_w_r, V(B["ffn_rx"]), V(B["ffn_r"]), WRK_ACT_NONE, turbo));
+    if (!merged) WRK_TRY(matmul(ops, L.ffn_w_r, V(B["ffn_rx"]), V(B["ffn_r"]), WRK_ACT_NONE, turbo));
     HOOK(POST_FFN_LINEAR);
     HOOK(PRE_FFN_CHANNEL_MIX);
     {
@@ -606,9 +637,15 @@ int32_t layer_v7(wrk_bundle* bd, OpList& ops, const Buffers& B, uint32_t index, 
     }
     HOOK(POST_ATT_TOKEN_SHIFT);
     HOOK(PRE_ATT_LINEAR);
-    WRK_TRY(matmul(ops, L.att_w_r, V(B["att_rx"]), V(B["att_r"]), WRK_ACT_NONE, turbo));
-    WRK_TRY(matmul(ops, L.att_w_k, V(B["att_kx"]), V(B["att_k"]), WRK_ACT_NONE, turbo));
-    WRK_TRY(matmul(ops, L.att_w_v, V(B["att_vx"]), V(B["att_v"]), WRK_ACT_NONE, turbo));
+    if (merged) {
+        WRK_TRY(matmul_group(ops, {{L.att_w_r, V(B["att_rx"]), V(B["att_r"]), WRK_ACT_NONE},
+                                   {L.att_w_k, V(B["att_kx"]), V(B["att_k"]), WRK_ACT_NONE},
+                                   {L.att_w_v, V(B["att_vx"]), V(B["att_v"]), WRK_ACT_NONE}}, turbo));
+    } else {
+        WRK_TRY(matmul(ops, L.att_w_r, V(B["att_rx"]), V(B["att_r"]), WRK_ACT_NONE, turbo));
+        WRK_TRY(matmul(ops, L.att_w_k, V(B["att_kx"]), V(B["att_k"]), WRK_ACT_NONE, turbo));
+        WRK_TRY(matmul(ops, L.att_w_v, V(B["att_vx"]), V(B["att_v"]), WRK_ACT_NONE, turbo));
+    }
     HOOK(POST_ATT_LINEAR);
     HOOK(PRE_ATT_ADAPT);
     WRK_TRY(matmul(ops, L.w1, V(B["att_wx"]), V(B["aux_w"]), WRK_ACT_TANH, turbo));
