@@ -524,6 +524,90 @@ __global__ void __launch_bounds__((1 + G) * S) time_mix_v7_kernel(const WkvArgs 
     }
 }
 
+// v7, runs of a few tokens (batched decode: many sequences, a token or two each): S threads per (head, batch slot),
+// thread j with column j of the state, a token's shared vectors through double-buffered shared memory.  Such a job
+// streams the states (S x S floats per head and sequence, in and out) and little else; the small CTA keeps six of
+// them on an SM where the staged kernel above fits one.
+template <int S>
+__global__ void __launch_bounds__(S) time_mix_v7_short_kernel(const WkvArgs a) {
+    __shared__ float sr[2][S], sw[2][S], sk[2][S], sa[2][S], sb[2][S];
+    __shared__ RunScratch run;
+    const uint32_t h = blockIdx.x, slot = blockIdx.y, j = threadIdx.x;
+    const uint32_t C = a.S * a.H, c = h * S + j;
+    const size_t plane = (size_t)a.T * C;
+
+    uint32_t start, count;
+    if (!find_run(a.cursors, a.wide, a.T, slot, &run, start, count)) return;
+
+    float st[S];
+#pragma unroll
+    for (int i = 0; i < S; ++i) st[i] = static_cast<const float*>(a.state.base)[a.state.index(c, 1 + i, slot)];
+
+    auto decay = [](float w) { return expf(-0.606531f * (1.0f / (1.0f + expf(-w)))); };
+    {
+        const size_t ti = (size_t)start * C + c;
+        sr[0][j] = dload(a.r, a.dtype, ti);
+        sw[0][j] = decay(dload(a.w, a.dtype, ti));
+        sk[0][j] = dload(a.n, a.dtype, ti);
+        const float av = dload(a.n, a.dtype, ti + 2 * plane), kk = dload(a.n, a.dtype, ti + 3 * plane);
+        sa[0][j] = -kk;
+        sb[0][j] = kk * av;
+    }
+    __syncthreads();
+
+    for (uint32_t n = 0; n < count; ++n) {
+        const uint32_t t = start + n;
+        const int cur = n & 1, nxt = cur ^ 1;
+        const size_t ti = (size_t)t * C + c;
+        const bool more = n + 1 < count;
+        float nr = 0.f, nw = 0.f, nk = 0.f, na = 0.f, nkk = 0.f;
+        if (more) {
+            nr = dload(a.r, a.dtype, ti + C);
+            nw = dload(a.w, a.dtype, ti + C);
+            nk = dload(a.n, a.dtype, ti + C);
+            na = dload(a.n, a.dtype, ti + C + 2 * plane);
+            nkk = dload(a.n, a.dtype, ti + C + 3 * plane);
+        }
+        const float vj = dload(a.n, a.dtype, ti + plane);
+        const float xin = dload(a.x, a.dtype, ti);
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < S; i += 4) {
+            s0 = fmaf(st[i], sa[cur][i], s0);
+            s1 = fmaf(st[i + 1], sa[cur][i + 1], s1);
+            s2 = fmaf(st[i + 2], sa[cur][i + 2], s2);
+            s3 = fmaf(st[i + 3], sa[cur][i + 3], s3);
+        }
+        const float sav = (s0 + s1) + (s2 + s3);
+        float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < S; i += 4) {
+            st[i] = st[i] * sw[cur][i] + sk[cur][i] * vj + sav * sb[cur][i];
+            y0 = fmaf(sr[cur][i], st[i], y0);
+            st[i + 1] = st[i + 1] * sw[cur][i + 1] + sk[cur][i + 1] * vj + sav * sb[cur][i + 1];
+            y1 = fmaf(sr[cur][i + 1], st[i + 1], y1);
+            st[i + 2] = st[i + 2] * sw[cur][i + 2] + sk[cur][i + 2] * vj + sav * sb[cur][i + 2];
+            y2 = fmaf(sr[cur][i + 2], st[i + 2], y2);
+            st[i + 3] = st[i + 3] * sw[cur][i + 3] + sk[cur][i + 3] * vj + sav * sb[cur][i + 3];
+            y3 = fmaf(sr[cur][i + 3], st[i + 3], y3);
+        }
+        const CursorD cu = cursor_at(a.cursors, a.wide, t);
+        if (t - cu.token + 1u == cu.len)
+            static_cast<float*>(a.state.base)[a.state.index(c, 0, slot)] = xin;
+        dstore(a.x, a.dtype, ti, (y0 + y1) + (y2 + y3));
+        if (more) {
+            sr[nxt][j] = nr;
+            sw[nxt][j] = decay(nw);
+            sk[nxt][j] = nk;
+            sa[nxt][j] = -nkk;
+            sb[nxt][j] = nkk * na;
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < S; ++i) static_cast<float*>(a.state.base)[a.state.index(c, 1 + i, slot)] = st[i];
+}
+
 // x_j += (sum_i u_i k_i r_i) * v_j per (token, head): one warp per (token, head).
 __global__ void time_first_v7_kernel(const __half* u, int dtype, const void* r, const void* n, void* x, uint32_t S,
                                      uint32_t H, uint32_t T) {
@@ -570,6 +654,15 @@ cudaError_t time_mix_v56_chunked(const WkvArgs& a, cudaStream_t stream) {
 cudaError_t time_mix_v7(const WkvArgs& a, cudaStream_t stream) {
     if (a.T == 0 || a.B == 0) return cudaSuccess;
     dim3 grid(a.H, a.B);
+    if (a.T <= 4 * a.B) {  // at most four tokens per sequence on average
+        switch (a.S) {
+            case 32: time_mix_v7_short_kernel<32><<<grid, 32, 0, stream>>>(a); break;
+            case 64: time_mix_v7_short_kernel<64><<<grid, 64, 0, stream>>>(a); break;
+            case 128: time_mix_v7_short_kernel<128><<<grid, 128, 0, stream>>>(a); break;
+            default: return cudaErrorInvalidValue;
+        }
+        return cudaGetLastError();
+    }
     switch (a.S) {
         case 32: time_mix_v7_kernel<32, 3><<<grid, 128, 0, stream>>>(a); break;
         case 64: time_mix_v7_kernel<64, 3><<<grid, 256, 0, stream>>>(a); break;
