@@ -290,6 +290,58 @@ def device_decode(wrk, rt, ctx, bundle, embeds, decode, steps, warmup, sync):
 TP_CONFIG, TP_BATCH = "v7-7b", 64
 
 
+def c3_only(args):
+    """BASELINE config 3 on one GPU: v6 3B-shaped (n_embd 2560, 32 layers, FFN 8960), all layers NF4, prefill of
+    4 sequences x 2048 uniform-random tokens with token_chunk_size 256 through `wrk_runtime_infer` (host tokens in,
+    last-token logits out per job).  `python bench.py --c3-only [--layers n]`."""
+    host_threads()
+    wrk = importlib.import_module("web-rwkv_b200")
+    rt = importlib.import_module("web-rwkv_b200.runtime")
+    synth = importlib.import_module("web-rwkv_b200.synth")
+    ctx = wrk.Context(0)
+    config, batch, length, chunk = "v6-3b", 4, 2048, 256
+    version, C, L, F, V = synth.CONFIGS[config]
+    L = args.layers or L
+    t0 = time.perf_counter()
+    builder = rt.ModelBuilder(ctx)
+    for name, arr in synth.iter_tensors(config, SEED_WEIGHTS, L):
+        builder.add_tensor(name, arr)
+    builder.quant({i: wrk.QUANT_NF4 for i in range(L)})
+    model = builder.build()
+    del builder
+    ctx.synchronize()
+    build_s = time.perf_counter() - t0
+    bundle = rt.Bundle(model, batch)
+    rng = np.random.default_rng(SEED_TOKENS)
+    logits = np.empty((batch, bundle.vocab), dtype=np.float32)
+
+    def one_pass():
+        seqs = [(rng.integers(0, V - 1, length).tolist(), wrk.RNN_LAST) for _ in range(batch)]
+        inp = rt.RnnInput(seqs, chunk)
+        jobs = 0
+        while inp.num_token():
+            bundle.infer(inp, logits)
+            jobs += 1
+        return jobs
+
+    one_pass()  # builds the jobs' graphs
+    ctx.synchronize()
+    launches0 = ctx.launch_count()
+    t0 = time.perf_counter()
+    jobs = 0
+    for _ in range(args.steps):
+        jobs += one_pass()
+    ctx.synchronize()
+    seconds = time.perf_counter() - t0
+    tokens = args.steps * batch * length
+    flops_per_token = 2.0 * L * (5 * C * C + 2 * C * F)  # the seven large matrices of a layer
+    print(json.dumps({"c3": {"workload": f"RWKV-v6-shaped {config} random-init (n_embd {C}, {L} layers, FFN {F}, vocab {V}), all layers NF4, "
+                                         f"prefill of {batch} sequences x {length} tokens, token_chunk_size {chunk}, host tokens in",
+                             "value": tokens / seconds, "unit": "tokens/s", "passes": args.steps, "jobs": jobs,
+                             "kernels_per_job": (ctx.launch_count() - launches0) / max(1, jobs),
+                             "tensor_tflops": tokens / seconds * flops_per_token / 1e12, "model_build_s": build_s}, "n_gpus": 1}))
+
+
 def tp_only(args):
     """The split-model leg alone, for profiling: `python bench.py --tp-only [--tp-layers 2] --steps K` (one GPU) or under
     torch.distributed.run."""
@@ -439,10 +491,29 @@ def check_fused_against_strict(wrk, rt, model, prompt, vocab, mode):
 BYTES_PER_WEIGHT = {"int8": 1.0 + 4.0 / 128.0, "nf4": 0.5 + 2.0 / 64.0, "fp16": 2.0}
 
 
-def sweep_matmul(wrk, ctx, rng, kind, K, M, N, reps, matrices, single):
+def sweep_matmul(wrk, ctx, rng, kind, K, M, N, reps, matrices, single, group=0):
     """CUDA-event time per launch of a graph holding `matrices` different weight matrices of the shape (so that
     consecutive launches do not re-read one matrix from L2); `single` submits one op per launch without a graph
-    (the form used under a profiler)."""
+    (the form used under a profiler); `group` = g > 0 times `matrices` grouped ops of g matrices each (each matrix with
+    its own activations and output), per group."""
+    if group:
+        sets = []
+        for _ in range(matrices):
+            ws = [ctx.from_numpy((rng.standard_normal((M, K), dtype=np.float32) * 0.02).astype(np.float16)) for _ in range(group)]
+            sets.append([wrk.Matrix.quant_u8(w) if kind == "int8" else wrk.Matrix.quant_nf4(w) if kind == "nf4" else wrk.Matrix.fp16(w)
+                         for w in ws])
+        xs = [ctx.from_numpy(rng.standard_normal((N, K), dtype=np.float32).astype(np.float16)) for _ in range(group)]
+        ys = [ctx.tensor(wrk.F16, [M, N]) for _ in range(group)]
+        cmd = ctx.encode(wrk.op_list([wrk.matmul_group_op(ms, xs, ys, turbo=(N % 32 == 0)) for ms in sets]), use_graph=True)
+        for _ in range(3):
+            cmd.submit()
+        ctx.synchronize()
+        ctx.timer_start()
+        for _ in range(reps):
+            cmd.submit()
+        us = ctx.timer_stop() * 1e3 / (reps * matrices)
+        print(f"{kind} K={K} M={M} N={N} group of {group}: {us:8.1f} us  {2.0 * K * M * N * group / us / 1e6:8.1f} TFLOP/s", flush=True)
+        return
     def make():
         w = ctx.from_numpy((rng.standard_normal((M, K), dtype=np.float32) * 0.02).astype(np.float16))
         return wrk.Matrix.quant_u8(w) if kind == "int8" else wrk.Matrix.quant_nf4(w) if kind == "nf4" else wrk.Matrix.fp16(w)
@@ -526,7 +597,7 @@ def sweep(args):
     for kind in args.kind.split(","):
         for K, M in shapes:
             for N in (int(v) for v in args.tokens.split(",")):
-                sweep_matmul(wrk, ctx, rng, kind, K, M, N, args.reps, args.matrices, args.single)
+                sweep_matmul(wrk, ctx, rng, kind, K, M, N, args.reps, args.matrices, args.single, args.group)
 
 
 def main():
@@ -547,6 +618,7 @@ def main():
                     help="decode job: 2 = one launch per fused phase (default), 1 = one persistent kernel, 3 = persistent, mma.sync only")
     ap.add_argument("--tp-only", action="store_true", help="only the split-model leg (for profiles); --tp-layers cuts the model")
     ap.add_argument("--tp-layers", type=int, default=0)
+    ap.add_argument("--c3-only", action="store_true", help="only BASELINE config 3: NF4 3B-shaped prefill, 4 x 2048 tokens, chunk 256")
     ap.add_argument("--no-tp", action="store_true", help="skip the split-model leg (v7 7B-shaped, 64 sequences)")
     ap.add_argument("--no-serialize", action="store_true", help="skip the save / load timing of the quantized model")
     ap.add_argument("--sweep", choices=["matmul", "wkv"], help="op-level sweep instead of the model benchmark")
@@ -556,12 +628,15 @@ def main():
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--matrices", type=int, default=8)
     ap.add_argument("--single", action="store_true")
+    ap.add_argument("--group", type=int, default=0, help="sweep matmul: time grouped ops of this many matrices (1-4)")
     args = ap.parse_args()
 
     if args.sweep:
         return sweep(args)
     if args.tp_only:
         return tp_only(args)
+    if args.c3_only:
+        return c3_only(args)
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
