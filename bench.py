@@ -662,7 +662,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     ctx = wrk.Context(local_rank)
-    keep = rank == 0 and not args.no_cpu_baseline
+    keep = rank == 0 and world == 1 and not args.no_cpu_baseline  # the CPU baseline is an N = 1 figure
     t_build = time.perf_counter()
     model, tensors, _ = build_model(wrk, rt, synth, ctx, args.config, L, keep=keep)
     ctx.synchronize()
@@ -793,7 +793,7 @@ def main():
         del bundle2, embeds2, model2
 
     cpu = None
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:
         cpu_tps, cores = cpu_decode(tensors, dims, args.cpu_sample)
         cpu = {"value": cpu_tps, "unit": "tokens/s", "cores": cores, "kind": "port",
                "sample": f"{args.cpu_sample} greedy decode tokens of the same model after a 1-token prompt"}
